@@ -1,0 +1,219 @@
+/*
+ * rb200_kernels.h — C ABI of the sm_100a augmentation kernels.
+ *
+ * Every entry point takes plain device pointers, POD per-sample tables and a CUDA stream
+ * (passed as void* so that no CUDA header is needed to bind it). Nothing here allocates
+ * unless the comment of the entry point says so. All entry points return 0 on success or a
+ * negative RB200_E_* code; rb200k_last_error() returns the text of the last failure on the
+ * calling thread.
+ *
+ * Image convention (as the reference's loader output, rocAL/source/loaders/image/
+ * image_read_and_decode.cpp:217-244): uint8, interleaved channels (HWC), 3 channels, one
+ * image = `height` rows of `stride` bytes starting `offset` bytes after an arena base. The
+ * valid region of every sample starts at pixel (0,0) of its slot unless an ROI says otherwise.
+ *
+ * Each "replaces" note names the reference code whose work the entry point does. The
+ * reference runs these operators as OpenVX nodes of the vx_rpp extension (one node per
+ * operator per batch); here one launch handles the whole ragged batch.
+ */
+#ifndef RB200_KERNELS_H
+#define RB200_KERNELS_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef RB200_API
+#define RB200_API __attribute__((visibility("default")))
+#endif
+
+#define RB200_OK 0
+#define RB200_E_INVALID (-1)   /* bad argument (null pointer, size out of range, bad enum) */
+#define RB200_E_CUDA (-2)      /* a CUDA runtime call failed; see rb200k_last_error()    */
+#define RB200_E_LIMIT (-3)     /* size beyond a documented maximum of the entry point    */
+
+/* Output element types and layouts; numeric values follow RocalTensorOutputType and
+ * RocalTensorLayout (rocAL/include/api/rocal_api_types.h:211-232,195-206). */
+enum { RB200_FP32 = 0, RB200_FP16 = 1, RB200_UINT8 = 2 };
+enum { RB200_NHWC = 0, RB200_NCHW = 1 };
+
+/* ---------------------------------------------------------------------------------------
+ * Bilinear resample family: [crop ->] resize(bilinear) [-> crop] [-> mirror] [-> normalize]
+ * ------------------------------------------------------------------------------------- */
+
+/* One sample of a resample launch (64 bytes).
+ *   roi_*   : rectangle of the source that is resized (whole image for a plain resize; the
+ *             crop window for crop->resize chains).
+ *   dst_w/h : size of the (virtual) resized image.
+ *   crop_*  : window of the resized image that is written to the output; crop_w/crop_h are
+ *             the valid output extent of this sample.
+ *   mirror  : 1 = output column x shows resized column crop_x + crop_w-1-x.
+ */
+typedef struct rb200_resample_sample {
+    uint64_t src_offset;
+    uint32_t src_stride;
+    int32_t roi_x, roi_y, roi_w, roi_h;
+    int32_t dst_w, dst_h;
+    int32_t crop_x, crop_y, crop_w, crop_h;
+    int32_t mirror;
+    int32_t reserved[2];
+} rb200_resample_sample;
+
+/* Launch-wide description of the output tensor and of the arithmetic after interpolation.
+ *   out            : device pointer, N samples of out_h*out_w*3 elements each.
+ *   out_dtype      : RB200_FP32 / RB200_FP16 / RB200_UINT8.
+ *   out_layout     : RB200_NCHW ([N][3][out_h][out_w]) or RB200_NHWC ([N][out_h][out_w][3]).
+ *   normalize      : 0 = store the rounded uint8 value of the resized pixel as is;
+ *                    1 = store fma(u8, mul[c], add[c]) (for RB200_UINT8: rounded to nearest
+ *                        even and saturated).
+ *   fill_padding   : 1 = elements outside a sample's crop_w x crop_h are written as 0;
+ *                    0 = they are left untouched (the reference leaves them undefined).
+ */
+typedef struct rb200_resample_params {
+    void* out;
+    int32_t out_w, out_h;
+    int32_t out_dtype, out_layout;
+    int32_t normalize, fill_padding;
+    float mul[3];
+    float add[3];
+} rb200_resample_params;
+
+/* Resize / ResizeCropMirror / ResizeMirrorNormalize / fused Resize+CropMirrorNormalize.
+ * replaces: vxExtRppResize (rocAL/source/augmentations/geometry_augmentations/node_resize.cpp:56),
+ *           vxExtRppCropMirrorNormalize (node_crop_mirror_normalize.cpp:87),
+ *           vxExtRppResizeCropMirror (node_resize_crop_mirror.cpp:59),
+ *           vxExtRppResizeMirrorNormalize (node_resize_mirror_normalize.cpp:90), and the HIP
+ *           kernel resize_bilinear_pkd_hip_tensor (rocAL/rocAL_hip/rocal_hip_kernels.cpp:446-485)
+ *           whose interpolation arithmetic it follows.
+ * `samples` is a DEVICE pointer to n structs; `h_samples` is the same table in HOST memory
+ * (used to size the launch; not retained after return).
+ */
+RB200_API int rb200k_resample(const uint8_t* arena, const rb200_resample_sample* samples,
+                    const rb200_resample_sample* h_samples, int n,
+                    const rb200_resample_params* params, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Pointwise family: crop / flip / colour ops / normalize / layout+dtype conversion
+ * ------------------------------------------------------------------------------------- */
+
+enum {
+    RB200_COLOR_NONE = 0,        /* copy (crop, flip, CropMirrorNormalize, to_tensor)        */
+    RB200_COLOR_BRIGHTNESS = 1,  /* y = alpha*x + beta                                       */
+    RB200_COLOR_CONTRAST = 2,    /* y = (x - beta)*alpha + beta  (alpha=factor, beta=center) */
+    RB200_COLOR_TWIST = 3        /* hue/saturation in HSV, then y = alpha*x + beta           */
+};
+
+/* One sample of a pointwise launch (64 bytes). The window roi_w x roi_h at (roi_x, roi_y) of
+ * the source is written to output (0,0)..(roi_w-1, roi_h-1); flip_h / flip_v reverse the
+ * column / row order inside the window. */
+typedef struct rb200_pointwise_sample {
+    uint64_t src_offset;
+    uint32_t src_stride;
+    int32_t roi_x, roi_y, roi_w, roi_h;
+    int32_t flip_h, flip_v;
+    float alpha, beta, hue, sat;
+    int32_t reserved[3];
+} rb200_pointwise_sample;
+
+typedef struct rb200_pointwise_params {
+    void* out;
+    int32_t out_w, out_h;
+    int32_t out_dtype, out_layout;
+    int32_t color_op;            /* RB200_COLOR_*                                            */
+    int32_t normalize, fill_padding;
+    int32_t reverse_channels;    /* 1 = output channel c shows source channel 2-c            */
+    float mul[3];
+    float add[3];
+} rb200_pointwise_params;
+
+/* Crop / Flip / CropMirrorNormalize / Brightness / Contrast / Hue / Saturation / ColorTwist
+ * (+ fused Flip) / u8 -> fp32|fp16 NCHW|NHWC conversion.
+ * replaces: vxExtRppCrop (node_crop.cpp:47, node_ssd_random_crop.cpp:58), vxExtRppFlip
+ *           (node_flip.cpp:44), vxExtRppCropMirrorNormalize (node_crop_mirror_normalize.cpp:87),
+ *           vxExtRppBrightness / Contrast / Hue / Saturation / ColorTwist
+ *           (color_augmentations/node_*.cpp), the converters Hip_CopyInt8ToNHWC_* /
+ *           Hip_CopyInt8ToNCHW_* (rocAL/rocAL_hip/rocal_hip_kernels.cpp:40-217) and the CPU
+ *           loop of MasterGraph::to_tensor (rocAL/source/pipeline/master_graph.cpp:672-853).
+ */
+RB200_API int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                     const rb200_pointwise_sample* h_samples, int n,
+                     const rb200_pointwise_params* params, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Affine gather family: WarpAffine / Rotate
+ * ------------------------------------------------------------------------------------- */
+
+/* One sample (64 bytes). m = {m00, m01, m10, m11, t0, t1} in the packing order of the
+ * reference ([x0, y0, x1, y1, o0, o1], node_warp_affine.cpp:43-48). For output pixel (x,y):
+ *   dx = x - (float)(out_w/2), dy = y - (float)(out_h/2)                   (integer halves)
+ *   sx = m00*dx + m01*dy + t0 + src_w/2.f ;  sy = m10*dx + m11*dy + t1 + src_h/2.f
+ * bilinear sample at (sx, sy); a tap position whose floor lies outside the source gives 0. */
+typedef struct rb200_warp_sample {
+    uint64_t src_offset;
+    uint32_t src_stride;
+    int32_t src_w, src_h;
+    float m[6];
+    int32_t dst_w, dst_h;        /* valid output extent of this sample (<= out_w, out_h)     */
+    int32_t reserved[3];
+} rb200_warp_sample;
+
+typedef struct rb200_warp_params {
+    void* out;                   /* uint8 NHWC [N][out_h][out_w][3]                          */
+    int32_t out_w, out_h;
+    int32_t fill_padding;
+    int32_t reserved;
+} rb200_warp_params;
+
+/* replaces: vxExtRppWarpAffine (node_warp_affine.cpp:61), vxExtRppRotate (node_rotate.cpp:43). */
+RB200_API int rb200k_warp_affine(const uint8_t* arena, const rb200_warp_sample* samples, int n,
+                       const rb200_warp_params* params, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * SSD box encoder
+ * ------------------------------------------------------------------------------------- */
+
+typedef struct rb200_box_encoder_params {
+    const float* anchors;        /* device, [num_anchors][4] ltrb                            */
+    int32_t num_anchors;
+    float criteria;
+    float means[4];
+    float inv_stds[4];           /* (float)(1.0 / stds[i]), evaluated in double              */
+    int32_t offset;              /* 1 = offset encoding                                      */
+    float scale;
+} rb200_box_encoder_params;
+
+/* Matches every anchor of every sample with a ground-truth box and writes the encoded box
+ * and label. boxes: device [total][4] ltrb; labels: device [total]; box_offsets: device
+ * [n+1] prefix of box counts (sample i owns boxes box_offsets[i] .. box_offsets[i+1]-1, at
+ * least one). out_boxes: device [n][num_anchors][4] fp32 (xc,yc,w,h); out_labels: device
+ * [n][num_anchors] int32. Tie rules are those of the CPU encoder: the best anchor of a box
+ * is the lowest index among equals; the best box of an anchor is the highest index among
+ * equals. max_boxes_per_sample must be >= the largest count in the batch (<= 1024).
+ * replaces: BoundingBoxGraph::update_box_encoder_meta_data
+ *           (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) and BoxEncoderGpu::Run +
+ *           BoxEncode<256> (rocAL/rocAL_hip/box_encoder_hip.cpp:123-278).
+ */
+RB200_API int rb200k_box_encode(const float* boxes, const int32_t* labels, const int32_t* box_offsets,
+                      int n, int max_boxes_per_sample, const rb200_box_encoder_params* params,
+                      float* out_boxes, int32_t* out_labels, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Misc
+ * ------------------------------------------------------------------------------------- */
+
+/* Text of the last error on the calling thread ("" if none). */
+RB200_API const char* rb200k_last_error(void);
+
+/* Number of kernel launches issued through this library by the calling process so far. */
+RB200_API uint64_t rb200k_launch_count(void);
+
+/* Build identification: "rocal_b200 <version> sm_100a". */
+RB200_API const char* rb200k_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RB200_KERNELS_H */

@@ -1,0 +1,440 @@
+/*
+ * oracle.c — CPU restatement of the rocAL augmentation hot path. TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is the checker the CUDA kernels are compared with. It is never part of the
+ * product path: only the tests, the smoke check and the benchmark's CPU-baseline leg load it.
+ *
+ * Parity status
+ *   - orc_box_encode: PINNED. It is checked against the reference's own
+ *     BoundingBoxGraph::update_box_encoder_meta_data compiled from the reference sources
+ *     (see ref_driver.cpp) and against golden vectors generated from that build.
+ *   - orc_resample / orc_pointwise / orc_warp_affine: PARITY UNPINNED. The reference executes
+ *     these operators inside the RPP library through MIVisionX/OpenVX; neither is present in
+ *     the reference tree, and the reference's golden images live in an external data tree.
+ *     The arithmetic below follows the only in-tree pixel code (the HIP bilinear kernel
+ *     in rocAL/rocAL_hip/rocal_hip_kernels.cpp) and the node / meta-node / API files
+ *     cited at each function.
+ *
+ * All float arithmetic is IEEE binary32 with one rounding per written operation (build with
+ * -ffp-contract=off); fused multiply-adds are spelled fmaf().
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../include/rb200_kernels.h"
+
+#define ORC_API __attribute__((visibility("default")))
+
+static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* Round to nearest even and saturate to [0,255]: the packing step of the HIP kernels
+ * (cvt_pk_u8_f32, rocAL/rocAL_hip/rocal_hip_kernels.cpp:425-430). */
+static inline uint8_t sat_u8(float v) {
+    float r = nearbyintf(v);
+    if (!(r > 0.f)) return 0; /* also NaN */
+    if (r > 255.f) return 255;
+    return (uint8_t)r;
+}
+
+static inline uint16_t f32_to_f16_bits(float f) {
+    _Float16 h = (_Float16)f; /* round to nearest even, as __float2half (rocal_hip_kernels.cpp:119-121) */
+    uint16_t b;
+    memcpy(&b, &h, 2);
+    return b;
+}
+
+static inline void store_elem(void* out, int dtype, size_t idx, float v) {
+    if (dtype == RB200_FP32)
+        ((float*)out)[idx] = v;
+    else if (dtype == RB200_FP16)
+        ((uint16_t*)out)[idx] = f32_to_f16_bits(v);
+    else
+        ((uint8_t*)out)[idx] = sat_u8(v);
+}
+
+static inline size_t out_index(int layout, int out_w, int out_h, int n, int c, int y, int x) {
+    if (layout == RB200_NCHW) return (((size_t)n * 3 + c) * out_h + y) * out_w + x;
+    return (((size_t)n * out_h + y) * out_w + x) * 3 + c;
+}
+
+static void fill_sample_zero(void* out, int dtype, int out_w, int out_h, int n) {
+    size_t elems = (size_t)3 * out_w * out_h;
+    size_t esz = dtype == RB200_FP32 ? 4 : (dtype == RB200_FP16 ? 2 : 1);
+    memset((uint8_t*)out + (size_t)n * elems * esz, 0, elems * esz);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Bilinear sample of one source position, 3 channels.
+ * Follows rocAL/rocAL_hip/rocal_hip_kernels.cpp:
+ *   :388-409  floor, weights = frac / 1-frac, optional range check -> 0
+ *   :340-343  both taps clamped to [roi.x, roi.z-1] x [roi.y, roi.w-1], roi.z/.w being the
+ *             inclusive right/bottom coordinate (:469-472)
+ *   :332-337  fmaf nesting  TL*(1-wy)(1-wx) + (TR*(1-wy)wx + (BL*wy(1-wx) + BR*wy*wx))
+ * The upper clamp bound is kept >= the lower one so that 1-pixel-wide sources stay in range.
+ * ---------------------------------------------------------------------------------------- */
+static inline int bilinear3(const uint8_t* img, uint32_t stride, int x_lo, int y_lo, int x_hi_incl,
+                            int y_hi_incl, float sx, float sy, int check_range, float out[3]) {
+    float fx = floorf(sx), fy = floorf(sy);
+    if (check_range && (fx < (float)x_lo || fy < (float)y_lo || fx > (float)x_hi_incl || fy > (float)y_hi_incl)) {
+        out[0] = out[1] = out[2] = 0.f;
+        return 0;
+    }
+    float wx = sx - fx, wy = sy - fy;
+    float owx = 1.0f - wx, owy = 1.0f - wy;
+    int cx_hi = x_hi_incl - 1 > x_lo ? x_hi_incl - 1 : x_lo;
+    int cy_hi = y_hi_incl - 1 > y_lo ? y_hi_incl - 1 : y_lo;
+    int x0 = (int)fminf(fmaxf(fx, (float)x_lo), (float)cx_hi);
+    int y0 = (int)fminf(fmaxf(fy, (float)y_lo), (float)cy_hi);
+    int x1 = (int)fminf(fmaxf(fx + 1.0f, (float)x_lo), (float)cx_hi);
+    int y1 = (int)fminf(fmaxf(fy + 1.0f, (float)y_lo), (float)cy_hi);
+    const uint8_t* r0 = img + (size_t)y0 * stride;
+    const uint8_t* r1 = img + (size_t)y1 * stride;
+    float w00 = owy * owx, w01 = owy * wx, w10 = wy * owx;
+    for (int c = 0; c < 3; c++) {
+        float tl = (float)r0[x0 * 3 + c], tr = (float)r0[x1 * 3 + c];
+        float bl = (float)r1[x0 * 3 + c], br = (float)r1[x1 * 3 + c];
+        out[c] = fmaf(tl, w00, fmaf(tr, w01, fmaf(bl, w10, br * wy * wx)));
+    }
+    return 1;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Resample family. Per sample: resize the source rectangle roi to dst_w x dst_h (bilinear),
+ * quantise to uint8 (the reference's Resize node outputs uint8 before the next node reads
+ * it), take the window crop_*, mirror, then either store the uint8 or fma(u8, mul, add).
+ *   source location: dst*ratio + (ratio-1)/2 + roi.x, ratio = roi_dim/dst_dim
+ *                    (rocal_hip_kernels.cpp:311-329)
+ *   crop+mirror+normalize: out = (src - mean)/std evaluated as x*(1/std) + (-mean*(1/std)),
+ *                    the two tables the node builds (node_crop_mirror_normalize.cpp:46-70)
+ * ---------------------------------------------------------------------------------------- */
+ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, int n,
+                         const rb200_resample_params* p) {
+    if (!arena || !s || !p || !p->out || n < 0) return RB200_E_INVALID;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        const rb200_resample_sample* q = &s[i];
+        const uint8_t* img = arena + q->src_offset;
+        if (p->fill_padding) fill_sample_zero(p->out, p->out_dtype, p->out_w, p->out_h, i);
+        float ratio_w = (float)q->roi_w / (float)q->dst_w;
+        float ratio_h = (float)q->roi_h / (float)q->dst_h;
+        float off_w = (ratio_w - 1.0f) * 0.5f;
+        float off_h = (ratio_h - 1.0f) * 0.5f;
+        int x_hi = q->roi_x + q->roi_w - 1, y_hi = q->roi_y + q->roi_h - 1;
+        int cw = q->crop_w < p->out_w ? q->crop_w : p->out_w;
+        int ch = q->crop_h < p->out_h ? q->crop_h : p->out_h;
+        for (int y = 0; y < ch; y++) {
+            int ry = q->crop_y + y;
+            float sy = (float)ry * ratio_h + off_h + (float)q->roi_y;
+            for (int x = 0; x < cw; x++) {
+                int rx = q->crop_x + (q->mirror ? (q->crop_w - 1 - x) : x);
+                float sx = (float)rx * ratio_w + off_w + (float)q->roi_x;
+                float v[3];
+                bilinear3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, sx, sy, 0, v);
+                for (int c = 0; c < 3; c++) {
+                    float u = (float)sat_u8(v[c]);
+                    float o = p->normalize ? fmaf(u, p->mul[c], p->add[c]) : u;
+                    store_elem(p->out, p->out_dtype, out_index(p->out_layout, p->out_w, p->out_h, i, c, y, x), o);
+                }
+            }
+        }
+    }
+    return RB200_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Colour arithmetic (float32 on the 0..255 scale).
+ *   brightness: y = alpha*x + beta              (rocAL/include/api/rocal_api_augmentation.h:226-236)
+ *   contrast  : y = (x - center)*factor + center (rocal_api_augmentation.h:290-301)
+ *   twist     : RGB -> HSV (H in degrees, S in [0,1], V on the 0..255 scale), H += hue (wrapped
+ *               to [0,360)), S = clamp(S*sat, 0, 1), HSV -> RGB, then y = alpha*x + beta
+ *               (parameter meaning: rocal_api_augmentation.h:866-877). The reference holds no
+ *               arithmetic for this operator (it runs in RPP): the formula is this
+ *               restatement's own, the textbook hexcone model.
+ * ---------------------------------------------------------------------------------------- */
+static inline void color_twist_px(float r, float g, float b, float hue, float sat, float out[3]) {
+    float cmax = fmaxf(r, fmaxf(g, b));
+    float cmin = fminf(r, fminf(g, b));
+    float delta = cmax - cmin;
+    float h = 0.f, s = 0.f, v = cmax;
+    if (delta > 0.f) {
+        s = delta / cmax;
+        if (cmax == r) {
+            h = 60.f * ((g - b) / delta);
+            if (h < 0.f) h = h + 360.f;
+        } else if (cmax == g) {
+            h = 60.f * ((b - r) / delta) + 120.f;
+        } else {
+            h = 60.f * ((r - g) / delta) + 240.f;
+        }
+    }
+    h = h + hue;
+    h = h - 360.f * floorf(h * (1.0f / 360.f));
+    s = s * sat;
+    s = fminf(fmaxf(s, 0.f), 1.f);
+    float hp = h * (1.0f / 60.f);
+    float fi = floorf(hp);
+    float f = hp - fi;
+    int sector = (int)fi;
+    if (sector >= 6) sector -= 6;
+    if (sector < 0) sector = 0;
+    float pp = v * (1.f - s);
+    float qq = v * (1.f - s * f);
+    float tt = v * (1.f - s * (1.f - f));
+    switch (sector) {
+        case 0: out[0] = v; out[1] = tt; out[2] = pp; break;
+        case 1: out[0] = qq; out[1] = v; out[2] = pp; break;
+        case 2: out[0] = pp; out[1] = v; out[2] = tt; break;
+        case 3: out[0] = pp; out[1] = qq; out[2] = v; break;
+        case 4: out[0] = tt; out[1] = pp; out[2] = v; break;
+        default: out[0] = v; out[1] = pp; out[2] = qq; break;
+    }
+}
+
+/* Pointwise family: window + flips (pure indexing; vxExtRppCrop / vxExtRppFlip semantics of
+ * node_crop.cpp:101-119 and node_flip.cpp:31-64, bbox twin in meta_node_flip.cpp:40-55),
+ * colour op, uint8 quantisation of the colour result, optional per-channel fma and channel
+ * reversal (x*mult+off of rocal_hip_kernels.cpp:40-217 / master_graph.cpp:672-853). */
+ORC_API int orc_pointwise(const uint8_t* arena, const rb200_pointwise_sample* s, int n,
+                          const rb200_pointwise_params* p) {
+    if (!arena || !s || !p || !p->out || n < 0) return RB200_E_INVALID;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        const rb200_pointwise_sample* q = &s[i];
+        const uint8_t* img = arena + q->src_offset;
+        if (p->fill_padding) fill_sample_zero(p->out, p->out_dtype, p->out_w, p->out_h, i);
+        int w = q->roi_w < p->out_w ? q->roi_w : p->out_w;
+        int h = q->roi_h < p->out_h ? q->roi_h : p->out_h;
+        for (int y = 0; y < h; y++) {
+            int sy = q->roi_y + (q->flip_v ? (q->roi_h - 1 - y) : y);
+            const uint8_t* row = img + (size_t)sy * q->src_stride;
+            for (int x = 0; x < w; x++) {
+                int sx = q->roi_x + (q->flip_h ? (q->roi_w - 1 - x) : x);
+                float px[3] = {(float)row[sx * 3], (float)row[sx * 3 + 1], (float)row[sx * 3 + 2]};
+                float v[3];
+                switch (p->color_op) {
+                    case RB200_COLOR_BRIGHTNESS:
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * px[c] + q->beta);
+                        break;
+                    case RB200_COLOR_CONTRAST:
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8((px[c] - q->beta) * q->alpha + q->beta);
+                        break;
+                    case RB200_COLOR_TWIST: {
+                        float t[3];
+                        color_twist_px(px[0], px[1], px[2], q->hue, q->sat, t);
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * t[c] + q->beta);
+                        break;
+                    }
+                    default:
+                        v[0] = px[0]; v[1] = px[1]; v[2] = px[2];
+                }
+                for (int c = 0; c < 3; c++) {
+                    int sc = p->reverse_channels ? 2 - c : c;
+                    float o = p->normalize ? fmaf(v[sc], p->mul[c], p->add[c]) : v[sc];
+                    store_elem(p->out, p->out_dtype, out_index(p->out_layout, p->out_w, p->out_h, i, c, y, x), o);
+                }
+            }
+        }
+    }
+    return RB200_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Affine gather. Table packing [m00, m01, m10, m11, t0, t1] = [x0, y0, x1, y1, o0, o1]
+ * (node_warp_affine.cpp:43-48). Centres: output coordinates relative to the integer half of
+ * the output size, source coordinates relative to half the source size in float — the
+ * centres the rotate bbox twin uses (meta_data/meta_node_rotate.cpp:60-64). Positions whose
+ * floor lies outside the source give 0 (the range-check branch, rocal_hip_kernels.cpp:396-398).
+ * ---------------------------------------------------------------------------------------- */
+ORC_API int orc_warp_affine(const uint8_t* arena, const rb200_warp_sample* s, int n,
+                            const rb200_warp_params* p) {
+    if (!arena || !s || !p || !p->out || n < 0) return RB200_E_INVALID;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        const rb200_warp_sample* q = &s[i];
+        const uint8_t* img = arena + q->src_offset;
+        if (p->fill_padding) fill_sample_zero(p->out, RB200_UINT8, p->out_w, p->out_h, i);
+        int w = q->dst_w < p->out_w ? q->dst_w : p->out_w;
+        int h = q->dst_h < p->out_h ? q->dst_h : p->out_h;
+        float cx = (float)(q->dst_w / 2), cy = (float)(q->dst_h / 2);
+        float t0 = q->m[4] + (float)q->src_w * 0.5f;
+        float t1 = q->m[5] + (float)q->src_h * 0.5f;
+        uint8_t* out = (uint8_t*)p->out + (size_t)i * p->out_w * p->out_h * 3;
+        for (int y = 0; y < h; y++) {
+            float dy = (float)y - cy;
+            for (int x = 0; x < w; x++) {
+                float dx = (float)x - cx;
+                float sx = fmaf(q->m[0], dx, fmaf(q->m[1], dy, t0));
+                float sy = fmaf(q->m[2], dx, fmaf(q->m[3], dy, t1));
+                float v[3];
+                bilinear3(img, q->src_stride, 0, 0, q->src_w - 1, q->src_h - 1, sx, sy, 1, v);
+                for (int c = 0; c < 3; c++) out[((size_t)y * p->out_w + x) * 3 + c] = sat_u8(v[c]);
+            }
+        }
+    }
+    return RB200_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * SSD box encoder. Restates BoundingBoxGraph::update_box_encoder_meta_data
+ * (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) with its helpers:
+ *   :61-69    IoU = inter / (area1 + area2 - inter)
+ *   :120-136  per box: IoU against every anchor; best anchor by strict '>' (lowest index
+ *             among equals) gets IoU 2.0
+ *   :138-148  per anchor: best box by '>=' (highest index among equals)
+ *   :173-216  match if IoU > criteria; offset encoding or plain xcycwh; unmatched anchors
+ *             give label 0 and zeros (offset) or the anchor as xcycwh.
+ * All pointers are host pointers.
+ * ---------------------------------------------------------------------------------------- */
+static inline float iou_ltrb(const float* b1, float area1, const float* b2) {
+    float xa = fmaxf(b1[0], b2[0]), ya = fmaxf(b1[1], b2[1]);
+    float xb = fminf(b1[2], b2[2]), yb = fminf(b1[3], b2[3]);
+    float inter = fmaxf(0.f, xb - xa) * fmaxf(0.f, yb - ya);
+    float area2 = (b2[3] - b2[1]) * (b2[2] - b2[0]);
+    return inter / (area1 + area2 - inter);
+}
+
+ORC_API int orc_box_encode(const float* boxes, const int32_t* labels, const int32_t* box_offsets, int n,
+                           const float* anchors, int num_anchors, float criteria, const float* means,
+                           const float* stds, int offset, float scale, float* out_boxes,
+                           int32_t* out_labels) {
+    if (!boxes || !labels || !box_offsets || !anchors || !out_boxes || !out_labels) return RB200_E_INVALID;
+    float inv_stds[4];
+    for (int k = 0; k < 4; k++) inv_stds[k] = (float)(1. / stds[k]);
+    float half_scale = (float)(0.5 * scale);
+    int A = num_anchors;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        int nb = box_offsets[i + 1] - box_offsets[i];
+        const float* bb = boxes + (size_t)box_offsets[i] * 4;
+        const int32_t* bl = labels + box_offsets[i];
+        float* ob = out_boxes + (size_t)i * A * 4;
+        int32_t* ol = out_labels + (size_t)i * A;
+        float* ious = (float*)malloc(sizeof(float) * (size_t)nb * A);
+        for (int b = 0; b < nb; b++) {
+            const float* box = bb + b * 4;
+            float* row = ious + (size_t)b * A;
+            float area = (box[3] - box[1]) * (box[2] - box[0]);
+            int best = 0;
+            row[0] = iou_ltrb(box, area, anchors);
+            float best_iou = row[0];
+            for (int a = 1; a < A; a++) {
+                row[a] = iou_ltrb(box, area, anchors + a * 4);
+                if (row[a] > best_iou) { best_iou = row[a]; best = a; }
+            }
+            row[best] = 2.f;
+        }
+        for (int a = 0; a < A; a++) {
+            const float* an = anchors + a * 4;
+            int best = 0;
+            float best_iou = ious[a];
+            for (int b = 1; b < nb; b++) {
+                float v = ious[(size_t)b * A + a];
+                if (v >= best_iou) { best_iou = v; best = b; }
+            }
+            const float* box = bb + best * 4;
+            if (ious[(size_t)best * A + a] > criteria) {
+                float xc, yc, w, h;
+                if (offset) {
+                    xc = (box[0] + box[2]) * half_scale;
+                    yc = (box[1] + box[3]) * half_scale;
+                    w = (box[2] - box[0]) * scale;
+                    h = (box[3] - box[1]) * scale;
+                    float axc = (an[0] + an[2]) * half_scale, ayc = (an[1] + an[3]) * half_scale;
+                    float aw = (an[2] - an[0]) * scale, ah = (an[3] - an[1]) * scale;
+                    xc = ((xc - axc) / aw - means[0]) * inv_stds[0];
+                    yc = ((yc - ayc) / ah - means[1]) * inv_stds[1];
+                    w = (logf(w / aw) - means[2]) * inv_stds[2];
+                    h = (logf(h / ah) - means[3]) * inv_stds[3];
+                } else {
+                    xc = (float)(0.5 * (box[0] + box[2]));
+                    yc = (float)(0.5 * (box[1] + box[3]));
+                    w = box[2] - box[0];
+                    h = box[3] - box[1];
+                }
+                ob[a * 4 + 0] = xc; ob[a * 4 + 1] = yc; ob[a * 4 + 2] = w; ob[a * 4 + 3] = h;
+                ol[a] = bl[best];
+            } else {
+                if (offset) {
+                    ob[a * 4 + 0] = ob[a * 4 + 1] = ob[a * 4 + 2] = ob[a * 4 + 3] = 0.f;
+                } else {
+                    ob[a * 4 + 0] = (float)(0.5 * (an[0] + an[2]));
+                    ob[a * 4 + 1] = (float)(0.5 * (an[1] + an[3]));
+                    ob[a * 4 + 2] = -an[0] + an[2];
+                    ob[a * 4 + 3] = -an[1] + an[3];
+                }
+                ol[a] = 0;
+            }
+        }
+        free(ious);
+    }
+    return RB200_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Host-side size rules.
+ * ---------------------------------------------------------------------------------------- */
+
+/* Target size of one resized sample: ResizeNode::adjust_out_roi_size
+ * (rocAL/source/augmentations/geometry_augmentations/node_resize.cpp:98-138) followed by the
+ * clamp to the output tensor's maximum shape (:71-72). mode follows RocalResizeScalingMode
+ * (0 default, 1 stretch, 2 not-smaller, 3 not-larger). */
+ORC_API void orc_resize_dst_size(unsigned src_w, unsigned src_h, unsigned dst_w, unsigned dst_h, int mode,
+                                 unsigned max_w, unsigned max_h, unsigned cap_w, unsigned cap_h,
+                                 unsigned* out_w, unsigned* out_h) {
+    int has_max = (max_w | max_h) > 0;
+    if (mode == 1) {
+        if (!dst_w) dst_w = src_w;
+        if (!dst_h) dst_h = src_h;
+        if (has_max) {
+            if (max_w) dst_w = dst_w < max_w ? dst_w : max_w;
+            if (max_h) dst_h = dst_h < max_h ? dst_h : max_h;
+        }
+    } else if (mode == 0) {
+        if ((!dst_w) & (dst_h != 0)) {
+            dst_w = (unsigned)lroundf(src_w * ((float)dst_h / src_h));
+        } else if ((!dst_h) & (dst_w != 0)) {
+            dst_h = (unsigned)lroundf(src_h * ((float)dst_w / src_w));
+        }
+        if (has_max) {
+            if (max_w) dst_w = dst_w < max_w ? dst_w : max_w;
+            if (max_h) dst_h = dst_h < max_h ? dst_h : max_h;
+        }
+    } else {
+        float scale = 1.0f;
+        float scale_w = (float)dst_w / src_w;
+        float scale_h = (float)dst_h / src_h;
+        if (mode == 2) {
+            scale = scale_w > scale_h ? scale_w : scale_h;
+        } else if (mode == 3) {
+            scale = (scale_w > 0 && scale_h > 0) ? (scale_w < scale_h ? scale_w : scale_h)
+                                                 : ((scale_w > 0) ? scale_w : scale_h);
+        }
+        if (has_max) {
+            if (max_w) scale = fminf(scale, (float)max_w / src_w);
+            if (max_h) scale = fminf(scale, (float)max_h / src_h);
+        }
+        if ((scale_h != scale) || (!dst_h)) dst_h = (unsigned)lroundf(src_h * scale);
+        if ((scale_w != scale) || (!dst_w)) dst_w = (unsigned)lroundf(src_w * scale);
+    }
+    *out_w = dst_w < cap_w ? dst_w : cap_w;
+    *out_h = dst_h < cap_h ? dst_h : cap_h;
+}
+
+/* Fixed-anchor crop window: RocalCropParam::fill_crop_dims, non-random branch
+ * (rocAL/source/parameters/parameter_rocal_crop.cpp:51-61,77-84). */
+ORC_API void orc_crop_fixed(unsigned in_w, unsigned in_h, unsigned crop_w, unsigned crop_h, float anchor_x,
+                            float anchor_y, unsigned* x1, unsigned* y1, unsigned* cw, unsigned* ch) {
+    unsigned w = (crop_w <= in_w && crop_w > 0) ? crop_w : in_w;
+    unsigned h = (crop_h <= in_h && crop_h > 0) ? crop_h : in_h;
+    unsigned x = (unsigned)(size_t)nearbyintf(anchor_x * (in_w - w));
+    unsigned y = (unsigned)(size_t)nearbyintf(anchor_y * (in_h - h));
+    unsigned x2 = x + w, y2 = y + h;
+    if (x2 > in_w) x2 = in_w;
+    if (y2 > in_h) y2 = in_h;
+    *x1 = x; *y1 = y; *cw = w; *ch = h;
+    (void)x2; (void)y2;
+}
+
+ORC_API const char* orc_version(void) { return "rocal_b200 oracle 1"; }

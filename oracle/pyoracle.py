@@ -1,0 +1,266 @@
+"""ctypes front of oracle/liboracle.so (the CPU restatement) and oracle/_ref/libref.so
+(reference-owned CPU code compiled from the reference tree). TEST INFRASTRUCTURE ONLY.
+
+Takes the same numpy tables as the CUDA path (layouts of include/rb200_kernels.h) and returns
+numpy arrays, so a parity test is `np.array_equal(gpu.cpu().numpy(), oracle(...))`.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+FP32, FP16, UINT8 = 0, 1, 2
+NHWC, NCHW = 0, 1
+_NP = {FP32: np.float32, FP16: np.float16, UINT8: np.uint8}
+
+
+class _ResampleParams(ctypes.Structure):
+    _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
+                ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
+                ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3)]
+
+
+class _PointwiseParams(ctypes.Structure):
+    _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
+                ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
+                ("color_op", ctypes.c_int32), ("normalize", ctypes.c_int32),
+                ("fill_padding", ctypes.c_int32), ("reverse_channels", ctypes.c_int32),
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3)]
+
+
+class _WarpParams(ctypes.Structure):
+    _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
+                ("fill_padding", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(_build.build_oracle())
+        _lib.orc_resample.restype = ctypes.c_int
+        _lib.orc_pointwise.restype = ctypes.c_int
+        _lib.orc_warp_affine.restype = ctypes.c_int
+        _lib.orc_box_encode.restype = ctypes.c_int
+    return _lib
+
+
+def ref():
+    """The reference-built library, or None when neither the reference tree nor a prebuilt copy exists."""
+    global _ref
+    if _ref is None:
+        path = _build.build_ref()
+        if path is None:
+            return None
+        _ref = ctypes.CDLL(path)
+    return _ref
+
+
+def set_threads(n):
+    """OpenMP thread count for subsequent oracle calls (used by the CPU-baseline timing)."""
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    try:
+        omp = ctypes.CDLL("libgomp.so.1")
+        omp.omp_set_num_threads(int(n))
+    except OSError:
+        pass
+
+
+def _out_array(n, out_w, out_h, dtype, layout, fill):
+    shape = (n, 3, out_h, out_w) if layout == NCHW else (n, out_h, out_w, 3)
+    return np.zeros(shape, dtype=_NP[dtype]) if fill else np.full(shape, 0, dtype=_NP[dtype])
+
+
+def _ptr(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def resample(arena, samples, out_w, out_h, out_dtype=FP32, out_layout=NCHW, mul=None, add=None,
+             fill_padding=True, out=None):
+    n = len(samples)
+    if out is None:
+        out = _out_array(n, out_w, out_h, out_dtype, out_layout, True)
+    p = _ResampleParams()
+    p.out = out.ctypes.data
+    p.out_w, p.out_h, p.out_dtype, p.out_layout = out_w, out_h, out_dtype, out_layout
+    p.normalize = 1 if mul is not None else 0
+    p.fill_padding = 1 if fill_padding else 0
+    for c in range(3):
+        p.mul[c] = float(mul[c]) if mul is not None else 1.0
+        p.add[c] = float(add[c]) if add is not None else 0.0
+    rc = lib().orc_resample(_ptr(arena), _ptr(samples), ctypes.c_int(n), ctypes.byref(p))
+    assert rc == 0
+    return out
+
+
+def pointwise(arena, samples, out_w, out_h, color_op=0, out_dtype=UINT8, out_layout=NHWC, mul=None, add=None,
+              reverse_channels=False, fill_padding=True, out=None):
+    n = len(samples)
+    if out is None:
+        out = _out_array(n, out_w, out_h, out_dtype, out_layout, True)
+    p = _PointwiseParams()
+    p.out = out.ctypes.data
+    p.out_w, p.out_h, p.out_dtype, p.out_layout = out_w, out_h, out_dtype, out_layout
+    p.color_op = color_op
+    p.normalize = 1 if mul is not None else 0
+    p.fill_padding = 1 if fill_padding else 0
+    p.reverse_channels = 1 if reverse_channels else 0
+    for c in range(3):
+        p.mul[c] = float(mul[c]) if mul is not None else 1.0
+        p.add[c] = float(add[c]) if add is not None else 0.0
+    rc = lib().orc_pointwise(_ptr(arena), _ptr(samples), ctypes.c_int(n), ctypes.byref(p))
+    assert rc == 0
+    return out
+
+
+def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None):
+    n = len(samples)
+    if out is None:
+        out = np.zeros((n, out_h, out_w, 3), dtype=np.uint8)
+    p = _WarpParams()
+    p.out = out.ctypes.data
+    p.out_w, p.out_h = out_w, out_h
+    p.fill_padding = 1 if fill_padding else 0
+    rc = lib().orc_warp_affine(_ptr(arena), _ptr(samples), ctypes.c_int(n), ctypes.byref(p))
+    assert rc == 0
+    return out
+
+
+def _box_call(fn, boxes, labels, offsets, anchors, criteria, means, stds, offset, scale):
+    n = len(offsets) - 1
+    a = anchors.shape[0]
+    boxes = np.ascontiguousarray(boxes, dtype=np.float32)
+    labels = np.ascontiguousarray(labels, dtype=np.int32)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+    anchors = np.ascontiguousarray(anchors, dtype=np.float32)
+    means = np.ascontiguousarray(means, dtype=np.float32)
+    stds = np.ascontiguousarray(stds, dtype=np.float32)
+    ob = np.zeros((n, a, 4), dtype=np.float32)
+    ol = np.zeros((n, a), dtype=np.int32)
+    rc = fn(_ptr(boxes), _ptr(labels), _ptr(offsets), ctypes.c_int(n), _ptr(anchors), ctypes.c_int(a),
+            ctypes.c_float(criteria), _ptr(means), _ptr(stds), ctypes.c_int(1 if offset else 0),
+            ctypes.c_float(scale), _ptr(ob), _ptr(ol))
+    assert rc == 0
+    return ob, ol
+
+
+def box_encode(boxes, labels, offsets, anchors, criteria=0.5, means=(0, 0, 0, 0), stds=(0.1, 0.1, 0.2, 0.2),
+               offset=True, scale=1.0):
+    """The restatement (oracle.c)."""
+    return _box_call(lib().orc_box_encode, boxes, labels, offsets, anchors, criteria, means, stds, offset, scale)
+
+
+def ref_box_encode(boxes, labels, offsets, anchors, criteria=0.5, means=(0, 0, 0, 0), stds=(0.1, 0.1, 0.2, 0.2),
+                   offset=True, scale=1.0):
+    """The reference's own BoundingBoxGraph::update_box_encoder_meta_data (needs _ref/libref.so)."""
+    r = ref()
+    if r is None:
+        raise RuntimeError("oracle/_ref/libref.so is not available")
+    r.ref_box_encode.restype = ctypes.c_int
+    return _box_call(r.ref_box_encode, boxes, labels, offsets, anchors, criteria, means, stds, offset, scale)
+
+
+def resize_dst_size(src_w, src_h, dst_w, dst_h, mode, max_w=0, max_h=0, cap_w=1 << 30, cap_h=1 << 30):
+    ow, oh = ctypes.c_uint(), ctypes.c_uint()
+    lib().orc_resize_dst_size(ctypes.c_uint(src_w), ctypes.c_uint(src_h), ctypes.c_uint(dst_w), ctypes.c_uint(dst_h),
+                              ctypes.c_int(mode), ctypes.c_uint(max_w), ctypes.c_uint(max_h), ctypes.c_uint(cap_w),
+                              ctypes.c_uint(cap_h), ctypes.byref(ow), ctypes.byref(oh))
+    return ow.value, oh.value
+
+
+def crop_fixed(in_w, in_h, crop_w, crop_h, anchor_x, anchor_y):
+    x, y, w, h = ctypes.c_uint(), ctypes.c_uint(), ctypes.c_uint(), ctypes.c_uint()
+    lib().orc_crop_fixed(ctypes.c_uint(in_w), ctypes.c_uint(in_h), ctypes.c_uint(crop_w), ctypes.c_uint(crop_h),
+                         ctypes.c_float(anchor_x), ctypes.c_float(anchor_y), ctypes.byref(x), ctypes.byref(y),
+                         ctypes.byref(w), ctypes.byref(h))
+    return x.value, y.value, w.value, h.value
+
+
+# ---- numpy restatement of the parameter generators ----------------------------------------
+
+def seed_sequence(seed, count=1024):
+    """The seed table of ParameterFactory::set_seed (parameter_factory.cpp:114-119): std::seed_seq{seed}
+    .generate() over `count` 32-bit words, as specified in the C++ standard [rand.util.seedseq]."""
+    v = [seed & 0xFFFFFFFF]
+    n, s = count, 1
+    b = [0x8b8b8b8b] * n
+    t = 11 if n >= 623 else 7 if n >= 68 else 5 if n >= 39 else 3 if n >= 7 else (n - 1) // 2
+    p, q = (n - t) // 2, (n - t) // 2 + t
+    m = max(s + 1, n)
+    M = 0xFFFFFFFF
+
+    def T_(x):
+        return x ^ (x >> 27)
+
+    for k in range(m):
+        r1 = (1664525 * T_(b[k % n] ^ b[(k + p) % n] ^ b[(k - 1) % n])) & M
+        if k == 0:
+            r2 = (r1 + s) & M
+        elif k <= s:
+            r2 = (r1 + (k % n) + v[k - 1]) & M
+        else:
+            r2 = (r1 + (k % n)) & M
+        b[(k + p) % n] = (b[(k + p) % n] + r1) & M
+        b[(k + q) % n] = (b[(k + q) % n] + r2) & M
+        b[k % n] = r2
+    for k in range(m, m + n):
+        r3 = (1566083941 * T_((b[k % n] + b[(k + p) % n] + b[(k - 1) % n]) & M)) & M
+        r4 = (r3 - (k % n)) & M
+        b[(k + p) % n] ^= r3
+        b[(k + q) % n] ^= r4
+        b[k % n] = r4
+    return np.array(b, dtype=np.int64)
+
+
+class UniformRand:
+    """UniformRand<T> (parameter_random.h:37-116): std::mt19937(seed); one draw at construction; each
+    renewal draws `batch` values val/max*(end-start)+start in double, cast to T."""
+
+    def __init__(self, start, end, seed, batch, integer=False):
+        self._rs = np.random.RandomState()
+        self._rs.seed(int(seed) & 0xFFFFFFFF)   # init_genrand, the seeding of std::mt19937(seed)
+        self.start, self.end = (start, max(end, start))
+        self.batch, self.integer = batch, integer
+        self._raw(1)
+
+    def _raw(self, k):
+        return self._rs.randint(0, 1 << 32, size=k, dtype=np.uint64).astype(np.float64)
+
+    def renew(self):
+        raw = self._raw(self.batch)
+        if self.start == self.end:
+            v = np.full(self.batch, self.start, dtype=np.float64)
+        else:
+            s, e = (float(self.start), float(self.end)) if self.integer else (float(np.float32(self.start)), float(np.float32(self.end)))
+            v = raw / 4294967295.0 * (e - s) + s
+        return np.trunc(v).astype(np.int32) if self.integer else v.astype(np.float32)
+
+
+class CustomRand:
+    """CustomRand<int> (parameter_random.h:118-239): cumulative distribution + upper_bound."""
+
+    def __init__(self, values, freqs, seed, batch):
+        self._rs = np.random.RandomState()
+        self._rs.seed(int(seed) & 0xFFFFFFFF)
+        self.values = np.asarray(values)
+        f = np.asarray(freqs, dtype=np.float64)
+        f = np.where(f >= 0, f, 0)
+        self.cdf = np.cumsum(f / f.sum())
+        self.batch = batch
+        if len(self.values) > 1:
+            self._rs.randint(0, 1 << 32, size=1, dtype=np.uint64)
+
+    def renew(self):
+        if len(self.values) == 1:
+            return np.full(self.batch, self.values[0])
+        raw = self._rs.randint(0, 1 << 32, size=self.batch, dtype=np.uint64).astype(np.float64) / 4294967295.0
+        idx = np.searchsorted(self.cdf, raw, side="right")
+        return self.values[idx]

@@ -1,0 +1,93 @@
+/*
+ * ref_driver.cpp — C entry points around reference-owned CPU code. TEST INFRASTRUCTURE ONLY.
+ *
+ * Built by oracle/build.py together with the reference's own
+ * rocAL/source/meta_data/bounding_box_graph.cpp, compiled where it lies in the reference
+ * tree (nothing of the reference is copied here). The result, oracle/_ref/libref.so, is used
+ * to pin the restatement in oracle.c, to generate the golden vectors under tests/golden/ and
+ * as the "reference" CPU baseline of the box encoder.
+ *
+ *   ref_box_encode       -> BoundingBoxGraph::update_box_encoder_meta_data
+ *                           (rocAL/source/meta_data/bounding_box_graph.cpp:150-220)
+ *   ref_uniform_rand_*   -> UniformRand<T> (rocAL/include/parameters/parameter_random.h:37-116)
+ *   ref_custom_rand_int  -> CustomRand<int> (parameter_random.h:118-239)
+ *   ref_seed_sequence    -> the seed table of ParameterFactory::set_seed
+ *                           (rocAL/source/parameters/parameter_factory.cpp:114-119)
+ */
+#include <cstdint>
+#include <memory>
+#include <random>
+#include <vector>
+
+#include "meta_data/bounding_box_graph.h"
+#include "parameters/parameter_random.h"
+
+extern "C" {
+
+__attribute__((visibility("default"))) int ref_box_encode(
+    const float* boxes, const int32_t* labels, const int32_t* box_offsets, int n, const float* anchors,
+    int num_anchors, float criteria, const float* means, const float* stds, int offset, float scale,
+    float* out_boxes, int32_t* out_labels) {
+    auto batch = std::make_shared<BoundingBoxBatch>();
+    batch->resize(n);
+    for (int i = 0; i < n; i++) {
+        BoundingBoxCords cords;
+        Labels lab;
+        for (int b = box_offsets[i]; b < box_offsets[i + 1]; b++) {
+            cords.emplace_back(boxes[b * 4 + 0], boxes[b * 4 + 1], boxes[b * 4 + 2], boxes[b * 4 + 3]);
+            lab.push_back(labels[b]);
+        }
+        batch->get_bb_cords_batch()[i] = cords;
+        batch->get_labels_batch()[i] = lab;
+    }
+    std::vector<float> anc(anchors, anchors + (size_t)num_anchors * 4);
+    std::vector<float> m(means, means + 4), s(stds, stds + 4);
+    BoundingBoxGraph graph;
+    graph.update_box_encoder_meta_data(&anc, batch, criteria, offset != 0, scale, m, s, out_boxes, out_labels);
+    return 0;
+}
+
+/* `batches` renewals of a length-`batch` array, as MasterGraph::update_node_parameters does once
+ * per batch (rocAL/source/pipeline/master_graph.cpp:405-415); out holds batches*batch values. */
+__attribute__((visibility("default"))) void ref_uniform_rand_float(unsigned seed, float start, float end,
+                                                                    unsigned batch, unsigned batches, float* out) {
+    UniformRand<float> p(start, end, seed);
+    p.create_array(batch);
+    for (unsigned b = 0; b < batches; b++) {
+        p.renew();
+        auto v = p.get_array();
+        for (unsigned i = 0; i < batch; i++) out[b * batch + i] = v[i];
+    }
+}
+
+__attribute__((visibility("default"))) void ref_uniform_rand_int(unsigned seed, int start, int end, unsigned batch,
+                                                                  unsigned batches, int* out) {
+    UniformRand<int> p(start, end, seed);
+    p.create_array(batch);
+    for (unsigned b = 0; b < batches; b++) {
+        p.renew();
+        auto v = p.get_array();
+        for (unsigned i = 0; i < batch; i++) out[b * batch + i] = v[i];
+    }
+}
+
+__attribute__((visibility("default"))) void ref_custom_rand_int(unsigned seed, const int* values,
+                                                                 const double* freqs, unsigned size, unsigned batch,
+                                                                 unsigned batches, int* out) {
+    CustomRand<int> p(values, freqs, size, seed);
+    p.create_array(batch);
+    for (unsigned b = 0; b < batches; b++) {
+        p.renew();
+        auto v = p.get_array();
+        for (unsigned i = 0; i < batch; i++) out[b * batch + i] = v[i];
+    }
+}
+
+__attribute__((visibility("default"))) void ref_seed_sequence(unsigned seed, unsigned count, int64_t* out) {
+    std::vector<int64_t> table(count);
+    std::seed_seq ss{seed};
+    ss.generate(table.begin(), table.end());
+    for (unsigned i = 0; i < count; i++) out[i] = table[i];
+}
+
+}  // extern "C"

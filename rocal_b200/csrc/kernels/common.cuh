@@ -1,0 +1,78 @@
+// Shared device helpers and host-side launch bookkeeping of the sm_100a kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rb200_kernels.h"
+
+namespace rb200 {
+
+// ---- host-side bookkeeping (defined in runtime.cu) -------------------------------------
+void set_error(const char* fmt, ...);
+void count_launch();
+int check_cuda(cudaError_t e, const char* what);
+
+#define RB200_CHECK_LAUNCH(what)                                       \
+    do {                                                               \
+        ::rb200::count_launch();                                       \
+        int _rc = ::rb200::check_cuda(cudaGetLastError(), what);       \
+        if (_rc) return _rc;                                           \
+    } while (0)
+
+// ---- arithmetic with one rounding per operation ------------------------------------------
+// The CPU checker is built without contraction, so every product that feeds a sum is written
+// with the non-fusing intrinsics; fused operations are spelled fmaf().
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float div_rn(float a, float b) { return __fdiv_rn(a, b); }
+
+// Round to nearest even for |v| < 2^22 (two adds instead of a conversion round trip).
+__device__ __forceinline__ float rint_small(float v) {
+    return __fsub_rn(__fadd_rn(v, 12582912.0f), 12582912.0f);
+}
+
+// Round to nearest even and saturate to [0,255], result kept as float.
+__device__ __forceinline__ float sat_round_u8f(float v) {
+    // fminf/fmaxf return the non-NaN operand, so NaN maps to 0 like the checker's !(r > 0).
+    float c = fminf(fmaxf(v, 0.0f), 255.0f);
+    return rint_small(c);
+}
+
+template <typename T>
+struct OutConv;
+template <>
+struct OutConv<float> {
+    static __device__ __forceinline__ float cvt(float v) { return v; }
+};
+template <>
+struct OutConv<__half> {
+    static __device__ __forceinline__ __half cvt(float v) { return __float2half_rn(v); }
+};
+template <>
+struct OutConv<uint8_t> {
+    static __device__ __forceinline__ uint8_t cvt(float v) { return (uint8_t)sat_round_u8f(v); }
+};
+
+// Four bytes starting at an arbitrary byte offset of a 4-byte-aligned shared-memory row.
+__device__ __forceinline__ uint32_t lds_unaligned32(const uint8_t* row, int byte_off) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(row + (byte_off & ~3));
+    return __funnelshift_r(w[0], w[1], (byte_off & 3) * 8);
+}
+
+__device__ __forceinline__ float byte_to_float(uint32_t w, int idx) {
+    return (float)((w >> (8 * idx)) & 0xFFu);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+}  // namespace rb200

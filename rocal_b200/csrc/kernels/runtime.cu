@@ -1,0 +1,32 @@
+// Error text, launch counter and version string shared by all kernel entry points.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace rb200 {
+
+static thread_local char g_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return RB200_OK;
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return RB200_E_CUDA;
+}
+
+}  // namespace rb200
+
+extern "C" const char* rb200k_last_error(void) { return rb200::g_error; }
+extern "C" uint64_t rb200k_launch_count(void) { return rb200::g_launches.load(std::memory_order_relaxed); }
+extern "C" const char* rb200k_version(void) { return "rocal_b200 0.1 sm_100a"; }

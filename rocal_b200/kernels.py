@@ -1,0 +1,121 @@
+"""Thin Python front of the kernel-level C-ABI (include/rb200_kernels.h).
+
+torch is used only to own device memory and streams; every computation is a call into
+librocal_b200.so. Inputs: a uint8 CUDA tensor holding the packed source images (the arena) and
+a numpy structured array with one row per sample (dtypes in rocal_b200.tables).
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import tables as T
+from ._lib import (BoxEncoderParams, PointwiseParams, ResampleParams, WarpParams, check, lib)
+
+_TORCH_DTYPE = {T.FP32: torch.float32, T.FP16: torch.float16, T.UINT8: torch.uint8}
+
+
+def _stream_ptr(stream):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def to_device_table(samples, device):
+    """Uploads a structured numpy table as raw bytes."""
+    raw = torch.from_numpy(np.ascontiguousarray(samples).view(np.uint8).reshape(-1))
+    return raw.to(device, non_blocking=False)
+
+
+def _alloc_out(n, out_w, out_h, dtype, layout, device, out):
+    shape = (n, 3, out_h, out_w) if layout == T.NCHW else (n, out_h, out_w, 3)
+    if out is None:
+        out = torch.empty(shape, dtype=_TORCH_DTYPE[dtype], device=device)
+    else:
+        assert tuple(out.shape) == shape and out.dtype == _TORCH_DTYPE[dtype] and out.is_contiguous()
+    return out
+
+
+def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
+             fill_padding=True, out=None, d_samples=None, stream=None, staged=True):
+    """rb200k_resample. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
+    already on the device (uploaded here when None). staged=False withholds the host table from
+    the launch so that the kernel gathers straight from global memory."""
+    n = len(samples)
+    out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
+    if d_samples is None:
+        d_samples = to_device_table(samples, arena.device)
+    p = ResampleParams()
+    p.out = out.data_ptr()
+    p.out_w, p.out_h, p.out_dtype, p.out_layout = out_w, out_h, out_dtype, out_layout
+    p.normalize = 1 if mul is not None else 0
+    p.fill_padding = 1 if fill_padding else 0
+    for c in range(3):
+        p.mul[c] = float(mul[c]) if mul is not None else 1.0
+        p.add[c] = float(add[c]) if add is not None else 0.0
+    h_ptr = samples.ctypes.data_as(ctypes.c_void_p) if staged else None
+    check(lib.rb200k_resample(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
+                              _stream_ptr(stream)), "rb200k_resample")
+    return out
+
+
+def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.UINT8, out_layout=T.NHWC,
+              mul=None, add=None, reverse_channels=False, fill_padding=True, out=None, d_samples=None,
+              stream=None):
+    """rb200k_pointwise."""
+    n = len(samples)
+    out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
+    if d_samples is None:
+        d_samples = to_device_table(samples, arena.device)
+    p = PointwiseParams()
+    p.out = out.data_ptr()
+    p.out_w, p.out_h, p.out_dtype, p.out_layout = out_w, out_h, out_dtype, out_layout
+    p.color_op = color_op
+    p.normalize = 1 if mul is not None else 0
+    p.fill_padding = 1 if fill_padding else 0
+    p.reverse_channels = 1 if reverse_channels else 0
+    for c in range(3):
+        p.mul[c] = float(mul[c]) if mul is not None else 1.0
+        p.add[c] = float(add[c]) if add is not None else 0.0
+    check(lib.rb200k_pointwise(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
+                               ctypes.byref(p), _stream_ptr(stream)), "rb200k_pointwise")
+    return out
+
+
+def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_samples=None, stream=None):
+    """rb200k_warp_affine: uint8 NHWC output."""
+    n = len(samples)
+    out = _alloc_out(n, out_w, out_h, T.UINT8, T.NHWC, arena.device, out)
+    if d_samples is None:
+        d_samples = to_device_table(samples, arena.device)
+    p = WarpParams()
+    p.out = out.data_ptr()
+    p.out_w, p.out_h = out_w, out_h
+    p.fill_padding = 1 if fill_padding else 0
+    check(lib.rb200k_warp_affine(arena.data_ptr(), d_samples.data_ptr(), n, ctypes.byref(p), _stream_ptr(stream)),
+          "rb200k_warp_affine")
+    return out
+
+
+def box_encode(boxes, labels, box_offsets, anchors, criteria, means, stds, offset, scale, max_boxes,
+               out_boxes=None, out_labels=None, stream=None):
+    """rb200k_box_encode. boxes [total,4] f32, labels [total] i32, box_offsets [n+1] i32, anchors
+    [A,4] f32 — all CUDA tensors."""
+    n = box_offsets.numel() - 1
+    a = anchors.shape[0]
+    if out_boxes is None:
+        out_boxes = torch.empty((n, a, 4), dtype=torch.float32, device=boxes.device)
+    if out_labels is None:
+        out_labels = torch.empty((n, a), dtype=torch.int32, device=boxes.device)
+    p = BoxEncoderParams()
+    p.anchors = anchors.data_ptr()
+    p.num_anchors = a
+    p.criteria = float(criteria)
+    for k in range(4):
+        p.means[k] = float(means[k])
+        p.inv_stds[k] = float(np.float32(1.0 / float(np.float32(stds[k]))))
+    p.offset = 1 if offset else 0
+    p.scale = float(scale)
+    check(lib.rb200k_box_encode(boxes.data_ptr(), labels.data_ptr(), box_offsets.data_ptr(), n, int(max_boxes),
+                                ctypes.byref(p), out_boxes.data_ptr(), out_labels.data_ptr(), _stream_ptr(stream)),
+          "rb200k_box_encode")
+    return out_boxes, out_labels

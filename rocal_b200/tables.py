@@ -1,0 +1,31 @@
+"""numpy views of the per-sample tables of include/rb200_kernels.h (same field order and sizes)."""
+import numpy as np
+
+FP32, FP16, UINT8 = 0, 1, 2
+NHWC, NCHW = 0, 1
+COLOR_NONE, COLOR_BRIGHTNESS, COLOR_CONTRAST, COLOR_TWIST = 0, 1, 2, 3
+
+RESAMPLE_SAMPLE = np.dtype([
+    ("src_offset", "<u8"), ("src_stride", "<u4"),
+    ("roi_x", "<i4"), ("roi_y", "<i4"), ("roi_w", "<i4"), ("roi_h", "<i4"),
+    ("dst_w", "<i4"), ("dst_h", "<i4"),
+    ("crop_x", "<i4"), ("crop_y", "<i4"), ("crop_w", "<i4"), ("crop_h", "<i4"),
+    ("mirror", "<i4"), ("reserved", "<i4", (2,))], align=True)
+
+POINTWISE_SAMPLE = np.dtype([
+    ("src_offset", "<u8"), ("src_stride", "<u4"),
+    ("roi_x", "<i4"), ("roi_y", "<i4"), ("roi_w", "<i4"), ("roi_h", "<i4"),
+    ("flip_h", "<i4"), ("flip_v", "<i4"),
+    ("alpha", "<f4"), ("beta", "<f4"), ("hue", "<f4"), ("sat", "<f4"),
+    ("reserved", "<i4", (3,))], align=True)
+
+WARP_SAMPLE = np.dtype([
+    ("src_offset", "<u8"), ("src_stride", "<u4"),
+    ("src_w", "<i4"), ("src_h", "<i4"),
+    ("m", "<f4", (6,)),
+    ("dst_w", "<i4"), ("dst_h", "<i4"),
+    ("reserved", "<i4", (3,))], align=True)
+
+assert RESAMPLE_SAMPLE.itemsize == 64 and POINTWISE_SAMPLE.itemsize == 64 and WARP_SAMPLE.itemsize == 64
+
+NP_DTYPE = {FP32: np.float32, FP16: np.float16, UINT8: np.uint8}

@@ -1,0 +1,311 @@
+"""Parity of the CUDA kernels (called through the C-ABI) with the CPU oracle on seeded inputs.
+
+Tolerances (stated by the task): bit-exact for indexing ops and uint8 paths computed with the
+same operation order; <= 1 LSB for uint8 in general; 1e-5 relative for fp32; 1e-3 for fp16.
+The kernels are written to reproduce the oracle's operation order, so most checks are exact.
+"""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as O
+from rocal_b200 import synthetic as S
+from rocal_b200 import tables as T
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(arena, cuda):
+    import torch
+    return torch.from_numpy(arena).to(cuda)
+
+
+def _assert_fp(gpu, ref, rel, what):
+    gpu = gpu.astype(np.float64)
+    ref = ref.astype(np.float64)
+    err = np.abs(gpu - ref)
+    tol = rel * np.maximum(np.abs(ref), 1e-3)
+    bad = err > tol
+    assert not bad.any(), "%s: %d elements beyond rel %g (max err %g)" % (what, int(bad.sum()), rel, err.max())
+
+
+@pytest.mark.parametrize("dtype,layout", [(T.FP32, T.NCHW), (T.FP16, T.NCHW), (T.FP32, T.NHWC), (T.UINT8, T.NHWC),
+                                          (T.FP16, T.NHWC), (T.UINT8, T.NCHW)])
+def test_resize_cmn_config0(cuda, dtype, layout):
+    """configs[0]: batch 64, 256..512 px sides, resize shorter->256, crop 224, mirror, normalize."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(0)
+    arena, hs, ws, offs = S.make_images(rng, 64, (256, 512), (256, 512))
+    t = S.classification_tables(rng, hs, ws, offs)
+    mul, add = S.normalize_tables()
+    ref = O.resample(arena, t, 224, 224, dtype, layout, mul, add)
+    for staged in (True, False):
+        got = K.resample(_dev(arena, cuda), t, 224, 224, dtype, layout, mul, add, staged=staged).cpu().numpy()
+        if dtype == T.FP32:
+            _assert_fp(got, ref, 1e-5, "fp32")
+            assert np.array_equal(got, ref), "fp32 path is expected to be bit-identical"
+        elif dtype == T.FP16:
+            _assert_fp(got, ref, 1e-3, "fp16")
+            assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+        else:
+            assert np.abs(got.astype(np.int32) - ref.astype(np.int32)).max() <= 1
+            assert np.array_equal(got, ref)
+
+
+def test_resize_cmn_config1_shapes(cuda):
+    """configs[1] shapes (300..1080 px sides, fp16 NCHW) on a 48-image slice."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(1)
+    arena, hs, ws, offs = S.make_images(rng, 48, (300, 1080), (300, 1080))
+    t = S.classification_tables(rng, hs, ws, offs)
+    mul, add = S.normalize_tables()
+    ref = O.resample(arena, t, 224, 224, T.FP16, T.NCHW, mul, add)
+    got = K.resample(_dev(arena, cuda), t, 224, 224, T.FP16, T.NCHW, mul, add).cpu().numpy()
+    _assert_fp(got, ref, 1e-3, "fp16")
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+
+
+def test_resize_only_ragged_output(cuda):
+    """Plain Resize: uint8 HWC out, per-sample output sizes inside a larger max-shape tensor; only
+    the ROI is defined (padding not filled), up- and down-scaling, odd sizes."""
+    from rocal_b200 import kernels as K
+    import torch
+    rng = S.rng_for(10)
+    arena, hs, ws, offs = S.make_images(rng, 12, (1, 90), (1, 130))
+    n = len(hs)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    t["roi_w"], t["roi_h"] = ws, hs
+    t["dst_w"] = rng.integers(1, 300, n)
+    t["dst_h"] = rng.integers(1, 200, n)
+    t["crop_w"], t["crop_h"] = t["dst_w"], t["dst_h"]
+    ow, oh = 300, 200
+    ref = O.resample(arena, t, ow, oh, T.UINT8, T.NHWC, fill_padding=False)
+    canary = torch.full((n, oh, ow, 3), 77, dtype=torch.uint8, device=cuda)
+    got = K.resample(_dev(arena, cuda), t, ow, oh, T.UINT8, T.NHWC, fill_padding=False, out=canary).cpu().numpy()
+    for i in range(n):
+        w, h = int(t[i]["dst_w"]), int(t[i]["dst_h"])
+        assert np.array_equal(got[i, :h, :w], ref[i, :h, :w]), "sample %d" % i
+        assert (got[i, h:, :] == 77).all() and (got[i, :, w:] == 77).all(), "padding of sample %d was written" % i
+
+
+def test_resample_roi_crop_mirror_edges(cuda):
+    """ResizeCropMirror-style chains: source ROI not at the origin, crop window touching every
+    border of the resized image, all-mirror / no-mirror, crop larger than the image (padding
+    zero-filled), batch of one, wide outputs that need more than one tile column."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(11)
+    arena, hs, ws, offs = S.make_images(rng, 9, (40, 120), (300, 700))
+    n = len(hs)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    for i in range(n):
+        rx, ry = int(rng.integers(0, 20)), int(rng.integers(0, 10))
+        t[i]["roi_x"], t[i]["roi_y"] = rx, ry
+        t[i]["roi_w"], t[i]["roi_h"] = ws[i] - rx - int(rng.integers(0, 20)), hs[i] - ry - int(rng.integers(0, 10))
+        t[i]["dst_w"], t[i]["dst_h"] = int(rng.integers(200, 900)), int(rng.integers(30, 200))
+        cw, ch = min(int(rng.integers(100, 640)), t[i]["dst_w"]), min(int(rng.integers(20, 150)), t[i]["dst_h"])
+        corner = i % 4
+        t[i]["crop_x"] = 0 if corner in (0, 2) else t[i]["dst_w"] - cw
+        t[i]["crop_y"] = 0 if corner in (0, 1) else t[i]["dst_h"] - ch
+        t[i]["crop_w"], t[i]["crop_h"] = cw, ch
+        t[i]["mirror"] = i % 2
+    for sl in (slice(0, n), slice(3, 4)):
+        tt = np.ascontiguousarray(t[sl])
+        for dtype, layout in ((T.UINT8, T.NHWC), (T.FP32, T.NCHW)):
+            ref = O.resample(arena, tt, 640, 150, dtype, layout)
+            for staged in (True, False):
+                got = K.resample(_dev(arena, cuda), tt, 640, 150, dtype, layout, staged=staged).cpu().numpy()
+                assert np.array_equal(got, ref)
+
+
+def test_resample_extreme_ratios(cuda):
+    """Heavy down-scaling (ratio > 2: sparse row staging) and up-scaling in one batch."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(12)
+    arena, hs, ws, offs = S.make_images(rng, 6, (900, 1500), (1200, 2000))
+    n = len(hs)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    t["roi_w"], t["roi_h"] = ws, hs
+    t["dst_w"] = [64, 100, 224, 3000, 150, 224]
+    t["dst_h"] = [64, 80, 224, 40, 2500, 224]
+    t["crop_w"] = np.minimum(t["dst_w"], 224)
+    t["crop_h"] = np.minimum(t["dst_h"], 224)
+    t["crop_x"] = (t["dst_w"] - t["crop_w"]) // 2
+    t["crop_y"] = (t["dst_h"] - t["crop_h"]) // 2
+    t["mirror"] = [0, 1, 0, 1, 0, 1]
+    ref = O.resample(arena, t, 224, 224, T.UINT8, T.NHWC)
+    got = K.resample(_dev(arena, cuda), t, 224, 224, T.UINT8, T.NHWC).cpu().numpy()
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("op", [T.COLOR_TWIST, T.COLOR_BRIGHTNESS, T.COLOR_CONTRAST, T.COLOR_NONE])
+def test_color_flip_config2(cuda, op):
+    """configs[2]: batch 256 of 224x224 noise, per-sample alpha/beta/hue/sat, hflip p=.5, uint8 HWC."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(2)
+    arena, hs, ws, offs = S.make_images(rng, 256, (224, 224), (224, 224), content="noise")
+    t = S.color_twist_tables(rng, hs, ws, offs)
+    if op == T.COLOR_CONTRAST:
+        t["beta"] = rng.uniform(60, 200, len(t)).astype(np.float32)
+    ref = O.pointwise(arena, t, 224, 224, op)
+    got = K.pointwise(_dev(arena, cuda), t, 224, 224, op).cpu().numpy()
+    diff = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+    assert diff.max() <= 1
+    assert np.array_equal(got, ref)
+
+
+def test_pointwise_crop_flip_normalize(cuda):
+    """Crop / Flip / CropMirrorNormalize / to_tensor: pure indexing must be bit-exact; windows that
+    touch the borders, vertical + horizontal flips, channel reversal, every dtype and layout."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(13)
+    arena, hs, ws, offs = S.make_images(rng, 10, (1, 70), (1, 300))
+    n = len(hs)
+    t = np.zeros(n, dtype=T.POINTWISE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    for i in range(n):
+        w = int(rng.integers(1, ws[i] + 1))
+        h = int(rng.integers(1, hs[i] + 1))
+        t[i]["roi_w"], t[i]["roi_h"] = w, h
+        t[i]["roi_x"] = (ws[i] - w) if i % 2 else 0
+        t[i]["roi_y"] = (hs[i] - h) if i % 3 else 0
+        t[i]["flip_h"], t[i]["flip_v"] = i & 1, (i >> 1) & 1
+    mul, add = S.normalize_tables()
+    for dtype in (T.UINT8, T.FP32, T.FP16):
+        for layout in (T.NHWC, T.NCHW):
+            for rev in (False, True):
+                norm = dtype != T.UINT8
+                ref = O.pointwise(arena, t, 300, 70, T.COLOR_NONE, dtype, layout, mul if norm else None,
+                                  add if norm else None, reverse_channels=rev)
+                got = K.pointwise(_dev(arena, cuda), t, 300, 70, T.COLOR_NONE, dtype, layout, mul if norm else None,
+                                  add if norm else None, reverse_channels=rev).cpu().numpy()
+                assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+
+
+def test_flip_twice_is_identity(cuda):
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(14)
+    arena, hs, ws, offs = S.make_images(rng, 4, (33, 33), (47, 47), content="noise")
+    t = np.zeros(4, dtype=T.POINTWISE_SAMPLE)
+    t["src_offset"], t["src_stride"], t["roi_w"], t["roi_h"] = offs, ws * 3, ws, hs
+    t["flip_h"], t["flip_v"] = [1, 0, 1, 1], [0, 1, 1, 1]
+    d = _dev(arena, cuda)
+    once = K.pointwise(d, t, 47, 33)
+    t2 = t.copy()
+    t2["src_offset"] = np.arange(4) * 47 * 33 * 3
+    twice = K.pointwise(once.reshape(-1), t2, 47, 33).cpu().numpy()
+    for i in range(4):
+        img = arena[int(offs[i]):int(offs[i]) + 47 * 33 * 3].reshape(33, 47, 3)
+        assert np.array_equal(twice[i], img)
+
+
+def test_warp_affine_config3(cuda):
+    """configs[3]: 480x640 images, rotation +-45 deg, scale 0.8..1.2, shift +-32 px, zero border (batch 32)."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(3)
+    arena, hs, ws, offs = S.make_images(rng, 32, (480, 480), (640, 640))
+    t = S.warp_tables(rng, hs, ws, offs, 640, 480)
+    ref = O.warp_affine(arena, t, 640, 480)
+    got = K.warp_affine(_dev(arena, cuda), t, 640, 480).cpu().numpy()
+    diff = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+    assert diff.max() <= 1
+    assert np.array_equal(got, ref)
+    assert (ref == 0).mean() > 0.01   # the border region exists in this configuration
+
+
+def test_rotate_fixed_and_identity(cuda):
+    """Rotate as a warp table: 0 degrees reproduces the source away from the last row/column;
+    45 degrees (the reference's RotateFixed test case) matches the oracle; ragged source sizes."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(15)
+    arena, hs, ws, offs = S.make_images(rng, 5, (20, 90), (20, 120))
+    n = len(hs)
+    for angle in (0.0, 45.0, -170.0):
+        t = np.zeros(n, dtype=T.WARP_SAMPLE)
+        t["src_offset"], t["src_stride"], t["src_w"], t["src_h"] = offs, ws * 3, ws, hs
+        t["dst_w"], t["dst_h"] = ws, hs
+        t["m"][:] = S.rotate_matrix(angle)
+        ref = O.warp_affine(arena, t, 120, 90)
+        got = K.warp_affine(_dev(arena, cuda), t, 120, 90).cpu().numpy()
+        assert np.array_equal(got, ref)
+        if angle == 0.0:
+            for i in range(n):
+                h, w = int(hs[i]), int(ws[i])
+                if h % 2 == 0 and w % 2 == 0:
+                    img = arena[int(offs[i]):int(offs[i]) + h * w * 3].reshape(h, w, 3)
+                    assert np.array_equal(got[i, :h - 1, :w - 1], img[:h - 1, :w - 1])
+
+
+@pytest.mark.parametrize("offset", [True, False])
+def test_box_encoder_config4(cuda, offset):
+    """configs[4]: 128 samples, 1..50 boxes, 8732 anchors, criteria 0.5; labels (matched indices)
+    bit-exact, encoded boxes within 1e-5 relative (logf differs by an ulp between libm and CUDA)."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(4)
+    anchors = S.ssd300_anchors()
+    boxes, labels, offs = S.random_boxes(rng, 128)
+    rb, rl = O.box_encode(boxes, labels, offs, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), offset, 1.0)
+    gb, gl = K.box_encode(torch.from_numpy(boxes).to(cuda), torch.from_numpy(labels).to(cuda),
+                          torch.from_numpy(offs).to(cuda), torch.from_numpy(anchors).to(cuda), 0.5, (0, 0, 0, 0),
+                          (0.1, 0.1, 0.2, 0.2), offset, 1.0, 50)
+    assert np.array_equal(gl.cpu().numpy(), rl)
+    _assert_fp(gb.cpu().numpy(), rb, 1e-5, "encoded boxes")
+
+
+def test_box_encoder_ties_and_chunks(cuda):
+    """Duplicate boxes (ties between boxes), boxes equal to anchors (IoU 1), one box per sample,
+    more boxes than one shared-memory chunk, a small anchor set, non-zero means and scale != 1."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(16)
+    anchors = S.ssd300_anchors()[::7][:1000].copy()
+    counts = [1, 2, 33, 64, 65, 100, 3]
+    per = []
+    for c in counts:
+        b, _, _ = S.random_boxes(rng, 1, (c, c))
+        b[c // 2] = b[0]
+        if c > 2:
+            b[-1] = anchors[int(rng.integers(0, len(anchors)))]
+        per.append(b)
+    boxes = np.ascontiguousarray(np.concatenate(per))
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    labels = rng.integers(1, 81, len(boxes)).astype(np.int32)
+    for offset, scale, means in ((True, 1.0, (0, 0, 0, 0)), (True, 2.0, (0.1, -0.1, 0.2, 0.05)), (False, 1.0, (0, 0, 0, 0))):
+        rb, rl = O.box_encode(boxes, labels, offs, anchors, 0.45, means, (0.1, 0.1, 0.2, 0.2), offset, scale)
+        gb, gl = K.box_encode(torch.from_numpy(boxes).to(cuda), torch.from_numpy(labels).to(cuda),
+                              torch.from_numpy(offs).to(cuda), torch.from_numpy(anchors).to(cuda), 0.45, means,
+                              (0.1, 0.1, 0.2, 0.2), offset, scale, 100)
+        assert np.array_equal(gl.cpu().numpy(), rl)
+        _assert_fp(gb.cpu().numpy(), rb, 1e-5, "encoded boxes")
+
+
+def test_ssd_chain_config4(cuda):
+    """configs[4] image chain: SSD random crop window -> resize 300x300 -> mirror -> normalize fp32 (batch 32)."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(4)
+    arena, hs, ws, offs = S.make_images(rng, 32, (300, 800), (300, 800))
+    boxes, labels, boffs = S.random_boxes(rng, 32)
+    crops, _, _, _ = S.ssd_random_crop(rng, boxes, labels, boffs)
+    t = S.ssd_resample_tables(rng, hs, ws, offs, crops)
+    mul, add = S.normalize_tables()
+    ref = O.resample(arena, t, 300, 300, T.FP32, T.NCHW, mul, add)
+    got = K.resample(_dev(arena, cuda), t, 300, 300, T.FP32, T.NCHW, mul, add).cpu().numpy()
+    _assert_fp(got, ref, 1e-5, "fp32")
+    assert np.array_equal(got, ref)
+
+
+def test_empty_batch_and_bad_arguments(cuda):
+    import torch
+    from rocal_b200 import kernels as K
+    from rocal_b200._lib import Rb200Error
+    arena = torch.zeros(1024, dtype=torch.uint8, device=cuda)
+    t = np.zeros(0, dtype=T.RESAMPLE_SAMPLE)
+    out = K.resample(arena, t, 8, 8, d_samples=arena)
+    assert out.shape[0] == 0
+    t = np.zeros(1, dtype=T.RESAMPLE_SAMPLE)   # dst size 0 -> rejected on the host, nothing launched
+    with pytest.raises(Rb200Error):
+        K.resample(arena, t, 8, 8, fill_padding=False)
+    with pytest.raises(Rb200Error):
+        K.resample(arena, t, 0, 8)
