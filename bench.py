@@ -1,0 +1,314 @@
+"""Benchmark of the augmentation hot path: fused Resize(shorter->256, bilinear) + CropMirrorNormalize
+(224x224, fp16 NCHW) over batches of 1024 variable-size uint8 images per GPU (BASELINE configs[1]).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the path over one batch. Rank 0 prints one JSON line:
+  value     images/s with the batch already resident in HBM (CUDA events, max over ranks)
+  e2e       images/s through the public call with HOST (pinned) input buffers: H2D of the batch and
+            its tables, the kernel, and a D2H read-back of one output image, all inside the timed region
+  roofline  algorithmic bytes of the resample kernel / its mean launch time, against the measured
+            HBM copy bandwidth (MEASURED_PEAKS.json, else the 6650 GB/s fallback)
+  cpu_baseline  the CPU oracle (OpenMP over samples) on a bounded slice of the same batch
+`--impl reference` times the CPU implementation alone (the oracle port: the reference's own pixel
+code lives in the RPP library, which is not available) and prints the same line shape.
+Under torchrun every rank owns one GPU and one shard of the synthetic dataset
+(shard i of S = indices [floor(N*i/S), floor(N*(i+1)/S)), rocAL's reader partitioning); no
+data-path collective is used.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 1024
+OUT = 224
+RESIZE_SHORTER = 256
+H_RANGE = (300, 1080)
+W_RANGE = (300, 1080)
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one resample launch, scaled to a 1024-image batch
+# from the ncu capture summarised in profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(t):
+    """Per launch: source footprint 3*(ceil(224/s)+1)^2 with s = 256/min(H,W), plus the fp16 output."""
+    short = np.minimum(t["roi_w"], t["roi_h"]).astype(np.float64)
+    s = RESIZE_SHORTER / short
+    fp = 3.0 * (np.ceil(OUT / s) + 1.0) ** 2
+    return float(fp.sum() + len(t) * 3 * OUT * OUT * 2)
+
+
+def shard_range(total, shard_id, num_shards):
+    return (total * shard_id) // num_shards, (total * (shard_id + 1)) // num_shards
+
+
+def make_shard(rank, world):
+    """The global dataset has BATCH*world images; this rank builds only its own shard (seeded per index block)."""
+    from rocal_b200 import synthetic as S
+    lo, hi = shard_range(BATCH * world, rank, world)
+    rng = np.random.Generator(np.random.PCG64([1235, lo]))
+    arena, hs, ws, offs = S.make_images(rng, hi - lo, H_RANGE, W_RANGE)
+    t = S.classification_tables(rng, hs, ws, offs, RESIZE_SHORTER, OUT)
+    return arena, t
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(arena, t, seconds_target=12.0):
+    """Oracle (CPU restatement, OpenMP over samples) on a bounded slice of this batch."""
+    from oracle import pyoracle as O
+    from rocal_b200 import synthetic as S
+    from rocal_b200 import tables as T
+    cores = os.cpu_count() or 1
+    O.set_threads(cores)
+    mul, add = S.normalize_tables()
+    n = min(len(t), max(cores * 2, 32))
+    sl = np.ascontiguousarray(t[:n])
+    O.resample(arena, sl, OUT, OUT, T.FP16, T.NCHW, mul, add)   # warm-up
+    reps, elapsed = 0, 0.0
+    t0 = time.perf_counter()
+    while elapsed < seconds_target and reps < 50:
+        O.resample(arena, sl, OUT, OUT, T.FP16, T.NCHW, mul, add)
+        reps += 1
+        elapsed = time.perf_counter() - t0
+    return {"value": n * reps / elapsed, "unit": "images/s", "cores": cores, "kind": "port",
+            "sample": "%d images of the batch x %d passes, OpenMP over samples" % (n, reps)}, n * reps / elapsed
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle port with all host threads, each step a bounded slice of the batch."""
+    if rank != 0:
+        return
+    from oracle import pyoracle as O
+    from rocal_b200 import synthetic as S
+    from rocal_b200 import tables as T
+    cores = os.cpu_count() or 1
+    O.set_threads(cores)
+    n = 128
+    lo = 0
+    rng = np.random.Generator(np.random.PCG64([1235, lo]))
+    arena, hs, ws, offs = S.make_images(rng, n, H_RANGE, W_RANGE)
+    t = S.classification_tables(rng, hs, ws, offs, RESIZE_SHORTER, OUT)
+    mul, add = S.normalize_tables()
+    for _ in range(max(1, min(args.warmup, 3))):
+        O.resample(arena, t, OUT, OUT, T.FP16, T.NCHW, mul, add)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.resample(arena, t, OUT, OUT, T.FP16, T.NCHW, mul, add)
+    dt = time.perf_counter() - t0
+    value = n * args.steps / dt
+    line = {"impl": "reference", "metric": "augmented images/sec", "value": value, "unit": "images/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(world, sample=n),
+            "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
+                             "sample": "%d images per step (a slice of the 1024-image batch), OpenMP over samples; "
+                                       "the reference's own pixel code (RPP) is not available" % n},
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(world, sample=None):
+    c = {"workload": "configs[1]: Resize(shorter=256, bilinear)+CropMirrorNormalize 224x224 fp16 NCHW, "
+                     "batch 1024/GPU of uint8 RGB images with H,W~U[300,1080]",
+         "batch_per_gpu": BATCH, "sharding": "shard_id/num_shards over %d GPU(s), no collective" % world,
+         "l2": "inputs (~1.4 GB/batch) larger than L2"}
+    if sample is not None:
+        c["images_per_step"] = sample
+    return c
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    global BATCH
+    if args.batch:
+        BATCH = args.batch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import rocal_b200
+    from rocal_b200 import kernels as K
+    from rocal_b200 import synthetic as S
+    from rocal_b200 import tables as T
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    arena_h, t = make_shard(rank, world)
+    n = len(t)
+    mul, add = S.normalize_tables()
+    arena_pinned = torch.from_numpy(arena_h).pin_memory()
+    table_pinned = torch.from_numpy(t.view(np.uint8).reshape(-1).copy()).pin_memory()
+    arena_d = arena_pinned.to(dev)
+    table_d = table_pinned.to(dev)
+    out = torch.empty((n, 3, OUT, OUT), dtype=torch.float16, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def step_resident():
+        K.resample(arena_d, t, OUT, OUT, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=table_d,
+                   stream=stream)
+
+    # ---- device-resident throughput + per-launch kernel time ----
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = rocal_b200.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record(stream)
+    for i in range(args.steps):
+        step_resident()
+        ev[i + 1].record(stream)
+    barrier()
+    launches = rocal_b200.launch_count() - launches0
+    total_ms = ev[0].elapsed_time(ev[-1])
+    launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop()
+
+    # ---- end to end: pinned host buffers -> H2D -> kernel -> D2H of one output image ----
+    arena_e = torch.empty_like(arena_d)
+    table_e = torch.empty_like(table_d)
+    host_back = torch.empty((3, OUT, OUT), dtype=torch.float16).pin_memory()
+
+    def step_e2e():
+        arena_e.copy_(arena_pinned, non_blocking=True)
+        table_e.copy_(table_pinned, non_blocking=True)
+        K.resample(arena_e, t, OUT, OUT, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=table_e,
+                   stream=stream)
+        host_back.copy_(out[0], non_blocking=True)
+
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = min(args.steps, 10)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        step_e2e()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
+        except (OSError, KeyError, ValueError):
+            pass
+        algo = algorithmic_bytes(t)
+        mean_launch_ms = float(np.mean(launch_ms))
+        achieved = algo / (mean_launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": "augmented images/sec", "value": n * world * args.steps / (total_ms * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": n * world * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
+                    "h2d_bytes_per_step": int(arena_pinned.numel() + table_pinned.numel()),
+                    "d2h_bytes_per_step": int(host_back.numel() * 2), "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "resample_kernel<half,NCHW,staged>", "achieved": achieved,
+                         "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                         "algorithmic_bytes_per_launch": algo, "launch_ms": mean_launch_ms,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"], _ = cpu_baseline(arena_h, t)
+        elif world > 1:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -192,12 +192,12 @@ using namespace rb200;
 extern "C" int rb200k_box_encode(const float* boxes, const int32_t* labels, const int32_t* box_offsets, int n,
                                  int max_boxes_per_sample, const rb200_box_encoder_params* p, float* out_boxes,
                                  int32_t* out_labels, void* stream_v) {
+    if (n == 0) return RB200_OK;
     if (!boxes || !labels || !box_offsets || !p || !p->anchors || !out_boxes || !out_labels || n < 0 ||
         p->num_anchors <= 0) {
         set_error("rb200k_box_encode: null pointer or non-positive size");
         return RB200_E_INVALID;
     }
-    if (n == 0) return RB200_OK;
     if (max_boxes_per_sample < 1 || max_boxes_per_sample > 1024) {
         set_error("rb200k_box_encode: max_boxes_per_sample %d outside [1,1024]", max_boxes_per_sample);
         return RB200_E_LIMIT;

@@ -158,11 +158,11 @@ using namespace rb200;
 extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_sample* samples,
                                 const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* p,
                                 void* stream_v) {
+    if (n == 0) return RB200_OK;
     if (!arena || !samples || !p || !p->out || n < 0 || p->out_w <= 0 || p->out_h <= 0) {
         set_error("rb200k_pointwise: null pointer or non-positive size");
         return RB200_E_INVALID;
     }
-    if (n == 0) return RB200_OK;
     if (n > 65535) {
         set_error("rb200k_pointwise: batch %d exceeds 65535", n);
         return RB200_E_LIMIT;

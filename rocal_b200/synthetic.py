@@ -7,6 +7,7 @@ after another (row pitch = width*3, each image start rounded up to 256 bytes) an
 tables of rocal_b200.tables.
 """
 import math
+import os
 
 import numpy as np
 
@@ -29,29 +30,44 @@ def normalize_tables(mean=MEAN, std=STD):
     return mul, add
 
 
-def make_images(rng, n, h_range, w_range, content="gradient_noise"):
-    """Returns (arena uint8[total], heights int32[n], widths int32[n], offsets uint64[n])."""
+def _fill_image(args):
+    arena, o, h, w, seed, content = args
+    rng = np.random.Generator(np.random.PCG64(int(seed)))
+    noise = rng.integers(0, 256, size=(h, w, 3), dtype=np.uint8)
+    if content == "noise":
+        img = noise
+    else:
+        corners = rng.integers(0, 256, size=(2, 2, 3)).astype(np.float32)
+        ty = np.linspace(0.0, 1.0, h, dtype=np.float32)[:, None, None]
+        tx = np.linspace(0.0, 1.0, w, dtype=np.float32)[None, :, None]
+        left = corners[0, 0] * (1 - ty) + corners[1, 0] * ty          # (h,1,3)
+        right = corners[0, 1] * (1 - ty) + corners[1, 1] * ty
+        grad = left + (right - left) * tx                             # (h,w,3) bilinear blend of the corners
+        img = ((grad.astype(np.uint16) + noise + 1) >> 1).astype(np.uint8)
+    arena[o:o + h * w * 3] = img.reshape(-1)
+
+
+def make_images(rng, n, h_range, w_range, content="gradient_noise", threads=None):
+    """Returns (arena uint8[total], heights int32[n], widths int32[n], offsets uint64[n]).
+    Sizes and one child seed per image are drawn from `rng`; the pixels of image i come from its own
+    PCG64(child seed), so the result does not depend on the number of worker threads."""
     hs = rng.integers(h_range[0], h_range[1] + 1, size=n).astype(np.int32)
     ws = rng.integers(w_range[0], w_range[1] + 1, size=n).astype(np.int32)
+    seeds = rng.integers(0, 2 ** 62, size=n)
     sizes = hs.astype(np.int64) * ws.astype(np.int64) * 3
     padded = (sizes + 255) // 256 * 256
     offsets = np.zeros(n, dtype=np.uint64)
     offsets[1:] = np.cumsum(padded)[:-1]
     arena = np.zeros(int(padded.sum()) + 256, dtype=np.uint8)
-    for i in range(n):
-        h, w = int(hs[i]), int(ws[i])
-        noise = rng.integers(0, 256, size=(h, w, 3), dtype=np.uint8)
-        if content == "noise":
-            img = noise
-        else:
-            corners = rng.integers(0, 256, size=(2, 2, 3)).astype(np.float32)
-            ty = np.linspace(0.0, 1.0, h, dtype=np.float32)[:, None, None]
-            tx = np.linspace(0.0, 1.0, w, dtype=np.float32)[None, :, None]
-            grad = (corners[0, 0] * (1 - ty) * (1 - tx) + corners[0, 1] * (1 - ty) * tx +
-                    corners[1, 0] * ty * (1 - tx) + corners[1, 1] * ty * tx)
-            img = ((grad.astype(np.uint16) + noise.astype(np.uint16) + 1) >> 1).astype(np.uint8)
-        o = int(offsets[i])
-        arena[o:o + h * w * 3] = img.reshape(-1)
+    jobs = [(arena, int(offsets[i]), int(hs[i]), int(ws[i]), seeds[i], content) for i in range(n)]
+    threads = threads or min(16, os.cpu_count() or 1)
+    if n >= 16 and threads > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(_fill_image, jobs))
+    else:
+        for j in jobs:
+            _fill_image(j)
     return arena, hs, ws, offsets
 
 
