@@ -1,12 +1,23 @@
 // Bilinear resample family: [crop ->] resize [-> crop] [-> mirror] [-> normalize] in one pass.
 //
 // One launch covers the whole ragged batch: grid = (tiles of the output extent, samples).
-// A CTA owns an output tile of TW columns (one thread per column) by TH rows. It first stages
-// the source rows its taps touch into shared memory with 16-byte cp.async copies (global
-// addresses rounded down to 16 bytes, so every copy is aligned whatever the row pitch of the
-// packed uint8 HWC source), then interpolates from shared memory and writes NCHW/NHWC
-// fp32/fp16/uint8 directly. Column-dependent values (tap offsets, x weights) are computed once
-// per thread and reused for all rows of the tile.
+//
+// Staged kernel (the fast path). A CTA owns an output tile of TH rows. It stages the source rows
+// its taps touch into shared memory with 16-byte cp.async copies (global addresses rounded down
+// to 16 bytes, so every copy is aligned whatever the row pitch of the packed uint8 HWC source;
+// one warp per source row), then every thread interpolates TWO horizontally adjacent output
+// pixels per row from shared memory:
+//   * a tap pair (x0, x0+1) is 6 contiguous bytes: three 32-bit shared loads + two funnel shifts;
+//   * uint8 -> float by PRMT into the mantissa of 2^23 and one subtraction (no conversion unit);
+//   * all float math on the two pixels runs as Blackwell packed f32x2 instructions
+//     (mul/add/fma.rn.f32x2: one rounding per lane, so results equal the scalar sequence);
+//   * the pixel pair leaves as one half2 / float2 store per channel plane.
+// Column-dependent values (tap offsets, x weights) are computed once per thread and reused for
+// all rows of the tile.
+//
+// Direct kernel: same arithmetic, taps read straight from global memory; used when the caller
+// gives no host copy of the table (the launch cannot be sized for staging) or a tile's source
+// span does not fit in shared memory.
 //
 // The interpolation follows the reference's HIP bilinear kernel
 // (rocAL/rocAL_hip/rocal_hip_kernels.cpp:311-343, 388-409, 425-430): source location
@@ -23,6 +34,9 @@ struct ResampleLaunch {
     int tiles_x;
     int th;             // rows per tile
     int pitch;          // bytes per staged row (multiple of 16)
+    int twh;            // staged kernel: threads per row group (each owns two columns)
+    int groups;         // staged kernel: row groups per CTA
+    int pair_ok;        // paired (2-element) stores are aligned
     int normalize, fill_padding;
     float mul[3], add[3];
 };
@@ -30,7 +44,7 @@ struct ResampleLaunch {
 struct RowInfo {
     float wy, owy;
     int off0, off1;     // staged: byte offset of the row's first staged pixel in shared memory
-                        // unstaged: source row index of the two taps
+                        // direct: source row index of the two taps
 };
 
 __device__ __forceinline__ float src_location(int d, float ratio, float offset, int roi_start) {
@@ -40,6 +54,12 @@ __device__ __forceinline__ float src_location(int d, float ratio, float offset, 
 __device__ __forceinline__ void clamp_taps(float f, int lo, int hi, int& t0, int& t1) {
     t0 = (int)fminf(fmaxf(f, (float)lo), (float)hi);
     t1 = (int)fminf(fmaxf(add_rn(f, 1.0f), (float)lo), (float)hi);
+}
+
+template <typename OutT, int LAYOUT>
+__device__ __forceinline__ size_t out_index(int out_w, int out_h, int n, int c, int y, int x) {
+    if (LAYOUT == RB200_NCHW) return (((size_t)n * 3 + c) * out_h + y) * out_w + x;
+    return (((size_t)n * out_h + y) * out_w + x) * 3 + c;
 }
 
 template <typename OutT, int LAYOUT>
@@ -58,16 +78,337 @@ __device__ __forceinline__ void store3(OutT* out, int out_w, int out_h, int n, i
     }
 }
 
-template <typename OutT, int LAYOUT, bool STAGED>
-__global__ void __launch_bounds__(256) resample_kernel(const uint8_t* __restrict__ arena,
-                                                       const rb200_resample_sample* __restrict__ samples,
-                                                       const ResampleLaunch L) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    // Layout: RowInfo[th] | int srow[2*th+2] | (16-byte aligned) staged rows
-    RowInfo* rowinfo = reinterpret_cast<RowInfo*>(smem);
-    int* srow = reinterpret_cast<int*>(smem + sizeof(RowInfo) * L.th);
-    uint8_t* stage = smem + ((sizeof(RowInfo) * L.th + sizeof(int) * (2 * L.th + 2) + 15) & ~(size_t)15);
+// ---- packed f32x2 arithmetic (sm_100): both lanes rounded independently, round-to-nearest ----
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
+    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b);
+    unsigned long long rc = *reinterpret_cast<unsigned long long*>(&c), rd;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    return *reinterpret_cast<float2*>(&rd);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
+    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b), rd;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    return *reinterpret_cast<float2*>(&rd);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
+    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b), rd;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    return *reinterpret_cast<float2*>(&rd);
+}
 
+// Byte `sel & 7` of (w, 0x4B000000) placed in the mantissa of 2^23: the float 8388608 + byte.
+__device__ __forceinline__ float byte_magic(uint32_t w, uint32_t sel) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, sel));
+}
+
+// One column's taps of one source row: words L (bytes b..b+3) and R (bytes b+4..b+7).
+__device__ __forceinline__ void fetch_pair(const uint8_t* stage, int b, uint32_t& l, uint32_t& r) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(stage + (b & ~3));
+    uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    uint32_t sh = (uint32_t)b << 3;
+    l = __funnelshift_r(w0, w1, sh);
+    r = __funnelshift_r(w1, w2, sh);
+}
+
+struct ColumnTaps {
+    int o_left;              // byte offset of the left tap from the first staged pixel
+    uint32_t sel_r, sel_g, sel_b;   // PRMT selectors of the right tap's channels
+    bool same;               // right tap == left tap (clamped at a border)
+};
+
+template <typename OutT>
+struct PairStore;
+template <>
+struct PairStore<float> {
+    static __device__ __forceinline__ void st(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <>
+struct PairStore<__half> {
+    static __device__ __forceinline__ void st(__half* p, float2 v) {
+        *reinterpret_cast<__half2*>(p) = __floats2half2_rn(v.x, v.y);
+    }
+};
+template <>
+struct PairStore<uint8_t> {
+    static __device__ __forceinline__ void st(uint8_t* p, float2 v) {
+        uint32_t a = (uint32_t)sat_round_u8f(v.x), b = (uint32_t)sat_round_u8f(v.y);
+        *reinterpret_cast<uint16_t*>(p) = (uint16_t)(a | (b << 8));
+    }
+};
+
+// Per-tile values every thread needs, computed once by one thread.
+struct TileHeader {
+    float ratio_w, off_w;
+    int x_first, nbytes;     // first staged source column, bytes staged per row
+    int nslots;              // staged source rows
+    int pad[3];
+};
+
+// Row table entry of the staged kernel (32 bytes: one 16-byte and one 8-byte shared load).
+struct StagedRow {
+    float2 wy2, owy2;        // y weights, duplicated for the packed lanes
+    int off0, off1;          // byte offset of the first staged pixel of the two tap rows
+    int pad[2];
+};
+
+template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED>
+__device__ __forceinline__ void staged_rows(const uint8_t* stage, const StagedRow* rows, int j_begin, int j_end,
+                                            const ColumnTaps (&ct)[2], float2 wx2, float2 owx2, bool second,
+                                            const float (&mulv)[3], const float (&addv)[3], OutT* po, size_t row_step,
+                                            size_t plane) {
+    const float2 neg_magic = make_float2(-8388608.0f, -8388608.0f);
+    const float2 rnd = make_float2(12582912.0f, 12582912.0f);
+    const float2 neg_rnd = make_float2(-12582912.0f, -12582912.0f);
+    for (int j = j_begin; j < j_end; j++, po += row_step) {
+        const float4 wts = *reinterpret_cast<const float4*>(&rows[j]);
+        const int2 offs = *reinterpret_cast<const int2*>(&rows[j].off0);
+        const float2 wy2 = make_float2(wts.x, wts.y), owy2 = make_float2(wts.z, wts.w);
+        uint32_t l0[2], r0[2], l1[2], r1[2];
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+            fetch_pair(stage, offs.x + ct[p].o_left, l0[p], r0[p]);
+            fetch_pair(stage, offs.y + ct[p].o_left, l1[p], r1[p]);
+            r0[p] = ct[p].same ? l0[p] : r0[p];
+            r1[p] = ct[p].same ? l1[p] : r1[p];
+        }
+        const float2 w00 = mul2(owy2, owx2), w01 = mul2(owy2, wx2), w10 = mul2(wy2, owx2);
+        float2 v[3];
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            const uint32_t sel_l = 0x7650u + c;
+            float2 tl = make_float2(byte_magic(l0[0], sel_l), byte_magic(l0[1], sel_l));
+            float2 bl = make_float2(byte_magic(l1[0], sel_l), byte_magic(l1[1], sel_l));
+            float2 tr, br;
+            // right tap: its red byte sits in the left word unless the taps coincide
+            if (c == 0) {
+                tr = make_float2(byte_magic(l0[0], ct[0].sel_r), byte_magic(l0[1], ct[1].sel_r));
+                br = make_float2(byte_magic(l1[0], ct[0].sel_r), byte_magic(l1[1], ct[1].sel_r));
+            } else if (c == 1) {
+                tr = make_float2(byte_magic(r0[0], ct[0].sel_g), byte_magic(r0[1], ct[1].sel_g));
+                br = make_float2(byte_magic(r1[0], ct[0].sel_g), byte_magic(r1[1], ct[1].sel_g));
+            } else {
+                tr = make_float2(byte_magic(r0[0], ct[0].sel_b), byte_magic(r0[1], ct[1].sel_b));
+                br = make_float2(byte_magic(r1[0], ct[0].sel_b), byte_magic(r1[1], ct[1].sel_b));
+            }
+            tl = add2(tl, neg_magic);
+            tr = add2(tr, neg_magic);
+            bl = add2(bl, neg_magic);
+            br = add2(br, neg_magic);
+            float2 acc = mul2(mul2(br, wy2), wx2);
+            acc = fma2(bl, w10, acc);
+            acc = fma2(tr, w01, acc);
+            acc = fma2(tl, w00, acc);
+            // The blend of uint8 values with weights in [0,1] stays inside [0,255] up to
+            // rounding, so rounding to nearest even is all the uint8 quantisation needs.
+            acc = add2(add2(acc, rnd), neg_rnd);
+            v[c] = NORMALIZE ? fma2(acc, make_float2(mulv[c], mulv[c]), make_float2(addv[c], addv[c])) : acc;
+        }
+        if (PAIRED) {
+            if (LAYOUT == RB200_NCHW) {
+                PairStore<OutT>::st(po, v[0]);
+                PairStore<OutT>::st(po + plane, v[1]);
+                PairStore<OutT>::st(po + 2 * plane, v[2]);
+            } else {
+                PairStore<OutT>::st(po, make_float2(v[0].x, v[1].x));
+                PairStore<OutT>::st(po + 2, make_float2(v[2].x, v[0].y));
+                PairStore<OutT>::st(po + 4, make_float2(v[1].y, v[2].y));
+            }
+        } else {
+            const size_t cs = LAYOUT == RB200_NCHW ? plane : 1;
+            const size_t xs = LAYOUT == RB200_NCHW ? 1 : 3;
+            po[0] = OutConv<OutT>::cvt(v[0].x);
+            po[cs] = OutConv<OutT>::cvt(v[1].x);
+            po[2 * cs] = OutConv<OutT>::cvt(v[2].x);
+            if (second) {
+                po[xs] = OutConv<OutT>::cvt(v[0].y);
+                po[xs + cs] = OutConv<OutT>::cvt(v[1].y);
+                po[xs + 2 * cs] = OutConv<OutT>::cvt(v[2].y);
+            }
+        }
+    }
+}
+
+template <typename OutT, int LAYOUT, bool NORMALIZE>
+__global__ void __launch_bounds__(256) resample_staged_kernel(const uint8_t* __restrict__ arena,
+                                                              const rb200_resample_sample* __restrict__ samples,
+                                                              const ResampleLaunch L) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    // Layout: TileHeader | StagedRow[th] | int srow[2*th+2] | (16-byte aligned) staged rows
+    TileHeader* hdr = reinterpret_cast<TileHeader*>(smem);
+    StagedRow* rows = reinterpret_cast<StagedRow*>(smem + sizeof(TileHeader));
+    int* srow = reinterpret_cast<int*>(smem + sizeof(TileHeader) + sizeof(StagedRow) * L.th);
+    uint8_t* stage = smem + ((sizeof(TileHeader) + sizeof(StagedRow) * L.th + sizeof(int) * (2 * L.th + 2) + 15) & ~(size_t)15);
+
+    const int n = blockIdx.y;
+    const int tx = blockIdx.x % L.tiles_x;
+    const int ty = blockIdx.x / L.tiles_x;
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    const int TW = 2 * L.twh;
+
+    const rb200_resample_sample* sp = samples + n;
+    const int crop_w = sp->crop_w, crop_h = sp->crop_h;
+    const int cw = min(crop_w, L.out_w);
+    const int ch = min(crop_h, L.out_h);
+    const int tile_x0 = tx * TW;
+    const int tile_y0 = ty * L.th;
+    int grp = 0, col = tid;
+    if (L.groups > 1) { grp = tid / L.twh; col = tid - grp * L.twh; }
+    const int xi0 = tile_x0 + 2 * col;
+    const int rpg = L.th / L.groups;                    // rows per row group
+    const int j_begin = grp * rpg;
+    OutT* out = reinterpret_cast<OutT*>(L.out);
+
+    const int rows_valid = min(L.th, ch - tile_y0);     // rows of this tile inside the crop
+    const int cols_valid = min(TW, cw - tile_x0);       // columns of this tile inside the crop
+
+    if (rows_valid > 0 && cols_valid > 0) {
+        const uint8_t* img = arena + sp->src_offset;
+        const uint32_t stride = sp->src_stride;
+        const int roi_x = sp->roi_x, roi_w = sp->roi_w;
+        const int crop_x = sp->crop_x, mirror = sp->mirror;
+        const int x_lo = roi_x;
+        const int x_hi = max(roi_x + roi_w - 2, roi_x);
+
+        // Warp 0 builds the tile header (lane 0) and the row table (lanes < rows_valid).
+        if (tid < 32) {
+            const int roi_y = sp->roi_y, roi_h = sp->roi_h, crop_y = sp->crop_y;
+            const float ratio_h = div_rn((float)roi_h, (float)sp->dst_h);
+            const float off_h = mul_rn(sub_rn(ratio_h, 1.0f), 0.5f);
+            const float ratio_w = div_rn((float)roi_w, (float)sp->dst_w);
+            const float off_w = mul_rn(sub_rn(ratio_w, 1.0f), 0.5f);
+            const int y_lo = roi_y, y_hi = max(roi_y + roi_h - 2, roi_y);
+            // Source column range of the tile.
+            int x_first, x_last;
+            {
+                int ca = tile_x0, cb = tile_x0 + cols_valid - 1;
+                int ra = crop_x + (mirror ? (crop_w - 1 - ca) : ca);
+                int rb = crop_x + (mirror ? (crop_w - 1 - cb) : cb);
+                int r_lo = min(ra, rb), r_hi = max(ra, rb);
+                int t0, t1;
+                clamp_taps(floorf(src_location(r_lo, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+                x_first = t0;
+                clamp_taps(floorf(src_location(r_hi, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+                x_last = t1;
+            }
+            // Rows are staged as one contiguous range when consecutive output rows share source
+            // rows (ratio <= 2), else as one pair per output row.
+            const bool dense = !(ratio_h > 2.0f);
+            int y_first = 0, nslots = 2 * rows_valid;
+            if (dense) {
+                int t0, t1;
+                clamp_taps(floorf(src_location(crop_y + tile_y0, ratio_h, off_h, roi_y)), y_lo, y_hi, t0, t1);
+                y_first = t0;
+                clamp_taps(floorf(src_location(crop_y + tile_y0 + rows_valid - 1, ratio_h, off_h, roi_y)), y_lo, y_hi, t0, t1);
+                nslots = t1 - y_first + 1;
+            }
+            if (tid == 0) {
+                hdr->ratio_w = ratio_w;
+                hdr->off_w = off_w;
+                hdr->x_first = x_first;
+                hdr->nbytes = (x_last - x_first + 1) * 3;
+                hdr->nslots = nslots;
+            }
+            if (tid < rows_valid) {
+                float sy = src_location(crop_y + tile_y0 + tid, ratio_h, off_h, roi_y);
+                float fy = floorf(sy);
+                int y0, y1;
+                clamp_taps(fy, y_lo, y_hi, y0, y1);
+                StagedRow ri;
+                float wy = sub_rn(sy, fy), owy = sub_rn(1.0f, wy);
+                ri.wy2 = make_float2(wy, wy);
+                ri.owy2 = make_float2(owy, owy);
+                int s0 = dense ? (y0 - y_first) : 2 * tid;
+                int s1 = dense ? (y1 - y_first) : 2 * tid + 1;
+                uint32_t m0 = (uint32_t)((uintptr_t)(img + (size_t)y0 * stride + (size_t)x_first * 3) & 15);
+                uint32_t m1 = (uint32_t)((uintptr_t)(img + (size_t)y1 * stride + (size_t)x_first * 3) & 15);
+                ri.off0 = s0 * L.pitch + (int)m0;
+                ri.off1 = s1 * L.pitch + (int)m1;
+                ri.pad[0] = ri.pad[1] = 0;
+                if (!dense) { srow[2 * tid] = y0; srow[2 * tid + 1] = y1; }
+                rows[tid] = ri;
+            }
+            if (dense) {
+                for (int r = tid; r < nslots; r += 32) srow[r] = y_first + r;
+            }
+        }
+        __syncthreads();
+        const float ratio_w = hdr->ratio_w, off_w = hdr->off_w;
+        const int x_first = hdr->x_first;
+
+        // Stage: one warp per source row, 16 bytes per lane and step.
+        {
+            const int nbytes = hdr->nbytes, nslots = hdr->nslots;
+            const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+            // a trailing partial warp (block sizes are multiples of 16) takes no rows
+            for (int r = warp < nwarps ? warp : nslots; r < nslots; r += nwarps) {
+                const uint8_t* g = img + (size_t)srow[r] * stride + (size_t)x_first * 3;
+                const uint32_t m = (uint32_t)((uintptr_t)g & 15);
+                const int need = (int)(m + nbytes + 15) >> 4;
+                const uint8_t* ga = g - m;
+                uint8_t* sd = stage + (size_t)r * L.pitch;
+                for (int ck = lane; ck < need; ck += 32) cp_async16(sd + ck * 16, ga + ck * 16);
+            }
+            cp_async_commit_wait_all();
+            __syncthreads();
+        }
+
+        if (2 * col < cols_valid && j_begin < rows_valid) {
+            const bool second = (2 * col + 1) < cols_valid;
+            ColumnTaps ct[2];
+            float wxs[2], owxs[2];
+#pragma unroll
+            for (int p = 0; p < 2; p++) {
+                int xi = (p == 1 && !second) ? xi0 : xi0 + p;
+                int rx = crop_x + (mirror ? (crop_w - 1 - xi) : xi);
+                float sx = src_location(rx, ratio_w, off_w, roi_x);
+                float fx = floorf(sx);
+                wxs[p] = sub_rn(sx, fx);
+                owxs[p] = sub_rn(1.0f, wxs[p]);
+                int x0, x1;
+                clamp_taps(fx, x_lo, x_hi, x0, x1);
+                ct[p].o_left = (x0 - x_first) * 3;
+                ct[p].same = (x1 == x0);
+                ct[p].sel_r = ct[p].same ? 0x7650u : 0x7653u;
+                ct[p].sel_g = ct[p].same ? 0x7651u : 0x7650u;
+                ct[p].sel_b = ct[p].same ? 0x7652u : 0x7651u;
+            }
+            const float2 wx2 = make_float2(wxs[0], wxs[1]);
+            const float2 owx2 = make_float2(owxs[0], owxs[1]);
+            const size_t plane = (size_t)L.out_w * L.out_h;
+            OutT* po = out + out_index<OutT, LAYOUT>(L.out_w, L.out_h, n, 0, tile_y0 + j_begin, xi0);
+            const size_t row_step = LAYOUT == RB200_NCHW ? (size_t)L.out_w : (size_t)L.out_w * 3;
+            const int j_end = min(j_begin + rpg, rows_valid);
+            if (second && L.pair_ok)
+                staged_rows<OutT, LAYOUT, NORMALIZE, true>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, po, row_step, plane);
+            else
+                staged_rows<OutT, LAYOUT, NORMALIZE, false>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, po, row_step, plane);
+        }
+    }
+
+    if (L.fill_padding) {
+        // Zero the part of the tile that lies outside the sample's valid extent.
+        const int j_end = min(j_begin + rpg, L.out_h - tile_y0);
+        for (int j = j_begin; j < j_end; j++) {
+            int y = tile_y0 + j;
+#pragma unroll
+            for (int p = 0; p < 2; p++) {
+                int xi = xi0 + p;
+                if (xi < L.out_w && (y >= ch || xi >= cw)) store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, xi, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+}
+
+// Direct variant: one thread per output column, taps read from global memory.
+template <typename OutT, int LAYOUT>
+__global__ void __launch_bounds__(256) resample_direct_kernel(const uint8_t* __restrict__ arena,
+                                                              const rb200_resample_sample* __restrict__ samples,
+                                                              const ResampleLaunch L) {
+    __shared__ RowInfo rowinfo[8];
     const int n = blockIdx.y;
     const int tx = blockIdx.x % L.tiles_x;
     const int ty = blockIdx.x / L.tiles_x;
@@ -83,9 +424,8 @@ __global__ void __launch_bounds__(256) resample_kernel(const uint8_t* __restrict
     const int tile_x0 = tx * TW;
     const int tile_y0 = ty * L.th;
     const int xi = tile_x0 + tid;
-
-    const int rows_valid = min(L.th, ch - tile_y0);     // rows of this tile inside the crop
-    const int cols_valid = min(TW, cw - tile_x0);       // columns of this tile inside the crop
+    const int rows_valid = min(L.th, ch - tile_y0);
+    const int cols_valid = min(TW, cw - tile_x0);
 
     if (rows_valid > 0 && cols_valid > 0) {
         const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
@@ -95,83 +435,16 @@ __global__ void __launch_bounds__(256) resample_kernel(const uint8_t* __restrict
         const int x_lo = s.roi_x, y_lo = s.roi_y;
         const int x_hi = max(s.roi_x + s.roi_w - 2, s.roi_x);
         const int y_hi = max(s.roi_y + s.roi_h - 2, s.roi_y);
-
-        // Source column range of the tile (identical in every thread).
-        int x_first, x_last;
-        {
-            int ca = tile_x0, cb = tile_x0 + cols_valid - 1;
-            int ra = s.crop_x + (s.mirror ? (s.crop_w - 1 - ca) : ca);
-            int rb = s.crop_x + (s.mirror ? (s.crop_w - 1 - cb) : cb);
-            int r_lo = min(ra, rb), r_hi = max(ra, rb);
-            int t0, t1;
-            clamp_taps(floorf(src_location(r_lo, ratio_w, off_w, s.roi_x)), x_lo, x_hi, t0, t1);
-            x_first = t0;
-            clamp_taps(floorf(src_location(r_hi, ratio_w, off_w, s.roi_x)), x_lo, x_hi, t0, t1);
-            x_last = t1;
-        }
-
-        // Row tables: tap rows, y weights, staging slots.
-        const bool dense = !(ratio_h > 2.0f);
-        int y_first = 0;
-        if (STAGED && dense) {
-            int t0, t1;
-            clamp_taps(floorf(src_location(s.crop_y + tile_y0, ratio_h, off_h, s.roi_y)), y_lo, y_hi, t0, t1);
-            y_first = t0;
-        }
-        int nslots = 0;
-        if (STAGED) {
-            if (dense) {
-                int t0, t1;
-                clamp_taps(floorf(src_location(s.crop_y + tile_y0 + rows_valid - 1, ratio_h, off_h, s.roi_y)), y_lo, y_hi, t0, t1);
-                nslots = t1 - y_first + 1;
-            } else {
-                nslots = 2 * rows_valid;
-            }
-        }
         if (tid < rows_valid) {
-            int ry = s.crop_y + tile_y0 + tid;
-            float sy = src_location(ry, ratio_h, off_h, s.roi_y);
+            float sy = src_location(s.crop_y + tile_y0 + tid, ratio_h, off_h, s.roi_y);
             float fy = floorf(sy);
-            int y0, y1;
-            clamp_taps(fy, y_lo, y_hi, y0, y1);
             RowInfo ri;
+            clamp_taps(fy, y_lo, y_hi, ri.off0, ri.off1);
             ri.wy = sub_rn(sy, fy);
             ri.owy = sub_rn(1.0f, ri.wy);
-            if (STAGED) {
-                int s0 = dense ? (y0 - y_first) : 2 * tid;
-                int s1 = dense ? (y1 - y_first) : 2 * tid + 1;
-                uint32_t m0 = (uint32_t)((uintptr_t)(img + (size_t)y0 * s.src_stride + (size_t)x_first * 3) & 15);
-                uint32_t m1 = (uint32_t)((uintptr_t)(img + (size_t)y1 * s.src_stride + (size_t)x_first * 3) & 15);
-                ri.off0 = s0 * L.pitch + (int)m0;
-                ri.off1 = s1 * L.pitch + (int)m1;
-                if (!dense) { srow[2 * tid] = y0; srow[2 * tid + 1] = y1; }
-            } else {
-                ri.off0 = y0;
-                ri.off1 = y1;
-            }
             rowinfo[tid] = ri;
         }
-        if (STAGED && dense) {
-            for (int r = tid; r < nslots; r += TW) srow[r] = y_first + r;
-        }
         __syncthreads();
-
-        if (STAGED) {
-            const int nbytes = (x_last - x_first + 1) * 3;
-            const int cpr = L.pitch >> 4;
-            const int total = nslots * cpr;
-            for (int idx = tid; idx < total; idx += TW) {
-                int r = idx / cpr;
-                int ck = idx - r * cpr;
-                const uint8_t* g = img + (size_t)srow[r] * s.src_stride + (size_t)x_first * 3;
-                uint32_t m = (uint32_t)((uintptr_t)g & 15);
-                int need = (int)(m + nbytes + 15) >> 4;
-                if (ck < need) cp_async16(stage + (size_t)r * L.pitch + ck * 16, g - m + ck * 16);
-            }
-            cp_async_commit_wait_all();
-            __syncthreads();
-        }
-
         if (tid < cols_valid) {
             int rx = s.crop_x + (s.mirror ? (s.crop_w - 1 - xi) : xi);
             float sx = src_location(rx, ratio_w, off_w, s.roi_x);
@@ -180,50 +453,29 @@ __global__ void __launch_bounds__(256) resample_kernel(const uint8_t* __restrict
             float owx = sub_rn(1.0f, wx);
             int x0, x1;
             clamp_taps(fx, x_lo, x_hi, x0, x1);
-            const int oL = STAGED ? (x0 - x_first) * 3 : x0 * 3;
-            const int oR = STAGED ? (x1 - x_first) * 3 : x1 * 3;
-            const float mul0 = L.mul[0], mul1 = L.mul[1], mul2 = L.mul[2];
-            const float add0 = L.add[0], add1 = L.add[1], add2 = L.add[2];
+            const int oL = x0 * 3, oR = x1 * 3;
             for (int j = 0; j < rows_valid; j++) {
                 const RowInfo ri = rowinfo[j];
-                uint32_t tl, tr, bl, br;
-                if (STAGED) {
-                    tl = lds_unaligned32(stage, ri.off0 + oL);
-                    tr = lds_unaligned32(stage, ri.off0 + oR);
-                    bl = lds_unaligned32(stage, ri.off1 + oL);
-                    br = lds_unaligned32(stage, ri.off1 + oR);
-                } else {
-                    const uint8_t* r0 = img + (size_t)ri.off0 * s.src_stride;
-                    const uint8_t* r1 = img + (size_t)ri.off1 * s.src_stride;
-                    tl = __ldg(r0 + oL) | (__ldg(r0 + oL + 1) << 8) | (__ldg(r0 + oL + 2) << 16);
-                    tr = __ldg(r0 + oR) | (__ldg(r0 + oR + 1) << 8) | (__ldg(r0 + oR + 2) << 16);
-                    bl = __ldg(r1 + oL) | (__ldg(r1 + oL + 1) << 8) | (__ldg(r1 + oL + 2) << 16);
-                    br = __ldg(r1 + oR) | (__ldg(r1 + oR + 1) << 8) | (__ldg(r1 + oR + 2) << 16);
-                }
+                const uint8_t* r0 = img + (size_t)ri.off0 * s.src_stride;
+                const uint8_t* r1 = img + (size_t)ri.off1 * s.src_stride;
                 const float w00 = mul_rn(ri.owy, owx), w01 = mul_rn(ri.owy, wx), w10 = mul_rn(ri.wy, owx);
                 float v[3];
 #pragma unroll
                 for (int c = 0; c < 3; c++) {
-                    float ftl = byte_to_float(tl, c), ftr = byte_to_float(tr, c);
-                    float fbl = byte_to_float(bl, c), fbr = byte_to_float(br, c);
+                    float ftl = (float)__ldg(r0 + oL + c), ftr = (float)__ldg(r0 + oR + c);
+                    float fbl = (float)__ldg(r1 + oL + c), fbr = (float)__ldg(r1 + oR + c);
                     float acc = mul_rn(mul_rn(fbr, ri.wy), wx);
                     acc = fmaf(fbl, w10, acc);
                     acc = fmaf(ftr, w01, acc);
                     acc = fmaf(ftl, w00, acc);
                     v[c] = sat_round_u8f(acc);
-                }
-                if (L.normalize) {
-                    v[0] = fmaf(v[0], mul0, add0);
-                    v[1] = fmaf(v[1], mul1, add1);
-                    v[2] = fmaf(v[2], mul2, add2);
+                    if (L.normalize) v[c] = fmaf(v[c], L.mul[c], L.add[c]);
                 }
                 store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, tile_y0 + j, xi, v[0], v[1], v[2]);
             }
         }
     }
-
     if (L.fill_padding && xi < L.out_w) {
-        // Zero the part of the tile that lies outside the sample's valid extent.
         const int rows_in_tile = min(L.th, L.out_h - tile_y0);
         for (int j = 0; j < rows_in_tile; j++) {
             int y = tile_y0 + j;
@@ -233,20 +485,27 @@ __global__ void __launch_bounds__(256) resample_kernel(const uint8_t* __restrict
 }
 
 template <typename OutT, int LAYOUT>
-static int launch_typed(const uint8_t* arena, const rb200_resample_sample* samples, int n, const ResampleLaunch& L,
-                        int tw, bool staged, size_t smem, cudaStream_t stream) {
+static int launch_typed(const uint8_t* arena, const rb200_resample_sample* samples, int n, ResampleLaunch L,
+                        bool staged, size_t smem, cudaStream_t stream) {
     int tiles_y = (L.ext_h + L.th - 1) / L.th;
-    dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
+    L.pair_ok = (L.out_w % 2 == 0) && (((uintptr_t)L.out) % (2 * sizeof(OutT)) == 0);
     if (staged) {
-        auto k = resample_kernel<OutT, LAYOUT, true>;
+        dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
+        auto k = L.normalize ? resample_staged_kernel<OutT, LAYOUT, true> : resample_staged_kernel<OutT, LAYOUT, false>;
         if (smem > 48 * 1024) {
             int rc = check_cuda(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                                 "cudaFuncSetAttribute(resample)");
             if (rc) return rc;
         }
-        k<<<grid, tw, smem, stream>>>(arena, samples, L);
+        k<<<grid, L.twh * L.groups, smem, stream>>>(arena, samples, L);
     } else {
-        resample_kernel<OutT, LAYOUT, false><<<grid, tw, smem, stream>>>(arena, samples, L);
+        int tx = (L.ext_w + 255) / 256;
+        int tw = ((L.ext_w + tx - 1) / tx + 31) & ~31;
+        L.tiles_x = (L.ext_w + tw - 1) / tw;
+        L.th = 8;
+        tiles_y = (L.ext_h + L.th - 1) / L.th;
+        dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
+        resample_direct_kernel<OutT, LAYOUT><<<grid, tw, 0, stream>>>(arena, samples, L);
     }
     RB200_CHECK_LAUNCH("resample_kernel");
     return RB200_OK;
@@ -280,9 +539,10 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     L.out_h = p->out_h;
     L.normalize = p->normalize;
     L.fill_padding = p->fill_padding;
+    L.pair_ok = 0;
     for (int c = 0; c < 3; c++) { L.mul[c] = p->mul[c]; L.add[c] = p->add[c]; }
 
-    // Extent the grid has to cover, and the widest source span a tile can need.
+    // Extent the grid has to cover.
     int ext_w = p->out_w, ext_h = p->out_h;
     if (h_samples) {
         for (int i = 0; i < n; i++) {
@@ -303,33 +563,40 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     }
     L.ext_w = ext_w;
     L.ext_h = ext_h;
-    int tiles_x = (ext_w + 255) / 256;
-    int tw = ((ext_w + tiles_x - 1) / tiles_x + 31) & ~31;
-    L.tiles_x = (ext_w + tw - 1) / tw;
 
+    // Staged geometry: tiles of <= 512 columns, two columns per thread, 1..8 row groups per CTA.
     bool staged = h_samples != nullptr;
-    int pitch = 0, th = 8;
+    int th = 8, pitch = 0;
+    L.tiles_x = (ext_w + 511) / 512;
+    int tile_px = (ext_w + L.tiles_x - 1) / L.tiles_x;
+    int twh = (((tile_px + 1) / 2) + 15) & ~15;
+    // Every thread keeps its column set-up for all rows of its group, so one group per CTA is
+    // preferred; narrow tiles take more groups to reach at least 64 threads.
+    int groups = 1;
+    while (groups < 8 && twh * groups < 64) groups *= 2;
+    L.tiles_x = (ext_w + 2 * twh - 1) / (2 * twh);
     if (staged) {
         int max_span = 1;
         for (int i = 0; i < n; i++) {
             double ratio = (double)h_samples[i].roi_w / (double)h_samples[i].dst_w;
-            long span = (long)(tw * ratio) + 4;
+            long span = (long)(2.0 * twh * ratio) + 4;
             if (span > h_samples[i].roi_w) span = h_samples[i].roi_w;
             if (span > max_span) max_span = (int)span;
         }
-        pitch = (15 + max_span * 3 + 8 + 15) & ~15;
+        pitch = (15 + max_span * 3 + 12 + 15) & ~15;
         const size_t budget = 40 * 1024, hard = 160 * 1024;
-        th = 8;
-        while (th > 1 && (size_t)(2 * th + 2) * pitch > budget) th >>= 1;
+        while (th > groups && (size_t)(2 * th + 2) * pitch > budget) th >>= 1;
+        while (groups > th) groups >>= 1;
         if ((size_t)(2 * th + 2) * pitch > hard) staged = false;
     }
-    if (!staged) { pitch = 0; th = 8; }
     L.th = th;
     L.pitch = pitch;
-    size_t smem = ((sizeof(RowInfo) * th + sizeof(int) * (2 * th + 2) + 15) & ~(size_t)15) +
-                  (staged ? (size_t)(2 * th + 2) * pitch : 0);
+    L.twh = twh;
+    L.groups = groups;
+    size_t smem = ((sizeof(TileHeader) + sizeof(StagedRow) * th + sizeof(int) * (2 * th + 2) + 15) & ~(size_t)15) +
+                  (size_t)(2 * th + 2) * pitch;
 
-#define RB200_DISPATCH(T, LAY) return launch_typed<T, LAY>(arena, samples, n, L, tw, staged, smem, stream)
+#define RB200_DISPATCH(T, LAY) return launch_typed<T, LAY>(arena, samples, n, L, staged, smem, stream)
     if (p->out_layout == RB200_NCHW) {
         if (p->out_dtype == RB200_FP32) RB200_DISPATCH(float, RB200_NCHW);
         if (p->out_dtype == RB200_FP16) RB200_DISPATCH(__half, RB200_NCHW);
