@@ -1,0 +1,201 @@
+/*
+ * rb200.h — plain C ABI of the augmentation pipeline (handles, ints, pointers and sizes only).
+ *
+ * This is what a foreign-function binding (ctypes, cgo, JNI, N-API ...) attaches to. Every
+ * function is the C-callable twin of one rocAL API call declared in rocal_api.h (named in its
+ * comment, with the reference declaration it replaces), or an extension marked [extension]:
+ * something the benchmark configurations need and the reference API cannot express.
+ *
+ * Status-returning functions give 0 (ROCAL_OK) or a RocalStatus value; handle-returning
+ * functions give NULL on failure. The failure text is kept per context:
+ * rb200_get_error_message(). No function throws.
+ */
+#ifndef RB200_H
+#define RB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "rb200_kernels.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* rb200_context; /* RocalContext */
+typedef void* rb200_tensor;  /* RocalTensor (rocalTensor*) */
+typedef void* rb200_param;   /* RocalIntParam / RocalFloatParam */
+
+/* ---- life cycle: rocalCreate / rocalVerify / rocalRun / rocalRelease (rocal_api.h:83-110) ---- */
+RB200_API rb200_context rb200_create(size_t batch_size, int affinity, int gpu_id, size_t cpu_thread_count,
+                                     size_t prefetch_queue_depth, int output_tensor_data_type);
+RB200_API int rb200_verify(rb200_context ctx);
+RB200_API int rb200_run(rb200_context ctx);
+RB200_API int rb200_release(rb200_context ctx);
+/* rocalGetStatus / rocalGetErrorMessage / rocalGetTimingInfo (rocal_api_info.h:90-106); timing = 4 values in us */
+RB200_API int rb200_get_status(rb200_context ctx);
+RB200_API const char* rb200_get_error_message(rb200_context ctx);
+RB200_API void rb200_get_timing(rb200_context ctx, unsigned long long out_load_decode_process_transfer[4]);
+/* rocalGetRemainingImages / rocalIsEmpty (rocal_api_info.h:66-74): fed but not yet returned samples */
+RB200_API size_t rb200_get_remaining_images(rb200_context ctx);
+
+/* ---- parameters (rocal_api_parameters.h:39-161) ---- */
+RB200_API void rb200_set_seed(unsigned seed);
+RB200_API unsigned rb200_get_seed(void);
+RB200_API rb200_param rb200_create_int_uniform_rand(int start, int end);
+RB200_API rb200_param rb200_create_float_uniform_rand(float start, float end);
+RB200_API rb200_param rb200_create_int_rand(const int* values, const double* frequencies, unsigned size);
+RB200_API rb200_param rb200_create_float_rand(const float* values, const double* frequencies, unsigned size);
+RB200_API rb200_param rb200_create_int_parameter(int value);
+RB200_API rb200_param rb200_create_float_parameter(float value);
+RB200_API int rb200_update_int_parameter(int value, rb200_param p);
+RB200_API int rb200_update_float_parameter(float value, rb200_param p);
+RB200_API int rb200_update_int_uniform_rand(int start, int end, rb200_param p);
+RB200_API int rb200_update_float_uniform_rand(float start, float end, rb200_param p);
+RB200_API int rb200_get_int_value(rb200_param p);
+RB200_API float rb200_get_float_value(rb200_param p);
+
+/* ---- input ---- */
+/* rocalJpegExternalFileSource with ROCAL_EXTSOURCE_RAW_UNCOMPRESSED (rocal_api_data_loaders.h:961-970) */
+RB200_API rb200_tensor rb200_external_source(rb200_context ctx, int color_format, int is_output, unsigned max_width,
+                                             unsigned max_height, int external_source_mode);
+/* rocalExternalSourceFeedInput (rocal_api_data_transfer.h:101-105): n buffers of max_height x max_width x
+ * channels bytes, roi_xywh = 4*n unsigned. The buffers must stay valid until the batch has been
+ * returned by rb200_run (the reference queues the pointers too: external_source_reader.cpp:220-233). */
+RB200_API int rb200_feed_input(rb200_context ctx, const unsigned char* const* buffers, const unsigned* roi_xywh,
+                               size_t n, unsigned max_width, unsigned max_height, unsigned channels, int mode,
+                               int layout, int eos);
+
+/* One image of a ragged batch: tightly packed, rows `stride` bytes apart. */
+typedef struct rb200_image_desc {
+    uint64_t offset; /* of pixel (0,0) from the arena base, bytes */
+    uint32_t stride;
+    uint32_t width, height;
+} rb200_image_desc;
+enum { RB200_MEM_HOST = 0, RB200_MEM_HOST_PINNED = 1, RB200_MEM_DEVICE = 2 };
+/* [extension] Feeds one batch as a single arena + per-image descriptors instead of n max-size slots
+ * (which would move 3-4x the bytes for variable-size images). mem_kind says where the arena lives;
+ * a device arena is used in place (no copy), a host arena is uploaded with one asynchronous copy.
+ * The arena must stay valid until the batch has been returned by rb200_run. */
+RB200_API int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes,
+                                const rb200_image_desc* descs, size_t n, int mem_kind);
+/* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
+ * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
+RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);
+/* [extension] Per-sample crop anchors in [0,1] for the next batch of a CropMirrorNormalize output
+ * (the reference's start_x/start_y are one scalar pair for the whole batch). */
+RB200_API int rb200_set_crop_anchors(rb200_context ctx, rb200_tensor cmn_output, const float* anchor_x,
+                                     const float* anchor_y, size_t n);
+/* [extension] Per-sample affine tables [n][6] = {x0,y0,x1,y1,o0,o1} for the next batch of a WarpAffine
+ * output (the reference draws the six coefficients independently, node_warp_affine.cpp:92-101). */
+RB200_API int rb200_set_affine(rb200_context ctx, rb200_tensor warp_output, const float* m6, size_t n);
+
+/* ---- augmentations: same arguments as the rocal* calls of rocal_api.h, std::vector flattened ---- */
+RB200_API rb200_tensor rb200_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                    int is_output, int scaling_mode, unsigned max_w, unsigned max_h,
+                                    unsigned resize_shorter, unsigned resize_longer, int interpolation,
+                                    int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_resize_mirror_normalize(rb200_context ctx, rb200_tensor in, unsigned dest_width,
+                                                     unsigned dest_height, const float* mean, const float* std_dev,
+                                                     size_t n_mean, int is_output, int scaling_mode, unsigned max_w,
+                                                     unsigned max_h, unsigned resize_shorter, unsigned resize_longer,
+                                                     int interpolation, rb200_param mirror, int out_layout,
+                                                     int out_dtype);
+RB200_API rb200_tensor rb200_crop_mirror_normalize(rb200_context ctx, rb200_tensor in, unsigned crop_height,
+                                                   unsigned crop_width, float start_x, float start_y,
+                                                   const float* mean, const float* std_dev, size_t n_mean,
+                                                   int is_output, rb200_param mirror, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200_param crop_width,
+                                  rb200_param crop_height, rb200_param crop_pos_x, rb200_param crop_pos_y,
+                                  int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_crop_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width, unsigned crop_height,
+                                        int is_output, float crop_pos_x, float crop_pos_y, int out_layout,
+                                        int out_dtype);
+RB200_API rb200_tensor rb200_crop_center_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width,
+                                               unsigned crop_height, int is_output, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_resize_crop_mirror_fixed(rb200_context ctx, rb200_tensor in, unsigned dest_width,
+                                                      unsigned dest_height, int is_output, unsigned crop_h,
+                                                      unsigned crop_w, rb200_param mirror, int out_layout,
+                                                      int out_dtype);
+RB200_API rb200_tensor rb200_resize_crop_mirror(rb200_context ctx, rb200_tensor in, unsigned dest_width,
+                                                unsigned dest_height, int is_output, rb200_param crop_height,
+                                                rb200_param crop_width, rb200_param mirror, int out_layout,
+                                                int out_dtype);
+RB200_API rb200_tensor rb200_ssd_random_crop(rb200_context ctx, rb200_tensor in, int is_output, int num_of_attempts,
+                                             int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_flip(rb200_context ctx, rb200_tensor in, int is_output, rb200_param horizontal,
+                                  rb200_param vertical, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_brightness(rb200_context ctx, rb200_tensor in, int is_output, rb200_param alpha,
+                                        rb200_param beta, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_contrast(rb200_context ctx, rb200_tensor in, int is_output, rb200_param factor,
+                                      rb200_param center, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout,
+                                 int out_dtype);
+RB200_API rb200_tensor rb200_saturation(rb200_context ctx, rb200_tensor in, int is_output, rb200_param sat,
+                                        int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_color_twist(rb200_context ctx, rb200_tensor in, int is_output, rb200_param alpha,
+                                         rb200_param beta, rb200_param hue, rb200_param sat, int out_layout,
+                                         int out_dtype);
+RB200_API rb200_tensor rb200_warp_affine(rb200_context ctx, rb200_tensor in, int is_output, unsigned dest_height,
+                                         unsigned dest_width, rb200_param x0, rb200_param x1, rb200_param y0,
+                                         rb200_param y1, rb200_param o0, rb200_param o1, int interpolation,
+                                         int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_rotate(rb200_context ctx, rb200_tensor in, int is_output, rb200_param angle,
+                                    unsigned dest_width, unsigned dest_height, int interpolation, int out_layout,
+                                    int out_dtype);
+
+/* ---- outputs: rocalGetOutputTensors (rocal_api_data_transfer.h:83) + rocalTensor accessors
+ * (rocal_api_tensor.h:38-61). Output buffers are device memory owned by the context and stay valid
+ * until the next rb200_run. ---- */
+/* rocalSetOutputs (rocal_api_data_transfer.h:75): marks tensors as pipeline outputs; before rb200_verify. */
+RB200_API int rb200_set_outputs(rb200_context ctx, const rb200_tensor* tensors, size_t n);
+RB200_API size_t rb200_output_count(rb200_context ctx);
+RB200_API rb200_tensor rb200_output(rb200_context ctx, size_t index);
+RB200_API void* rb200_tensor_buffer(rb200_tensor t);
+RB200_API unsigned rb200_tensor_num_dims(rb200_tensor t);
+RB200_API void rb200_tensor_dims(rb200_tensor t, size_t* out_dims);
+RB200_API void rb200_tensor_strides(rb200_tensor t, size_t* out_strides_bytes);
+RB200_API int rb200_tensor_layout(rb200_tensor t);
+RB200_API int rb200_tensor_dtype(rb200_tensor t);
+RB200_API size_t rb200_tensor_data_size(rb200_tensor t);
+/* rocalTensor::copy_data(user_buffer, mem_type): mem_type = RocalOutputMemType (0 host, 1 gpu, 2 pinned) */
+RB200_API unsigned rb200_tensor_copy_data(rb200_tensor t, void* user_buffer, int mem_type);
+/* rocalTensor::copy_roi: n x 4 unsigned (x, y, w, h) */
+RB200_API void rb200_tensor_copy_roi(rb200_tensor t, void* roi_buffer);
+/* DLPack export (__dlpack__ of rocAL_pybind/rocal_pybind.cpp:305-366, device type kDLCUDA): returns a
+ * DLManagedTensor* whose deleter frees only the descriptor; the memory stays owned by the context. */
+RB200_API void* rb200_tensor_dlpack(rb200_tensor t);
+RB200_API int rb200_device_id(rb200_context ctx);
+/* CUDA stream (cudaStream_t) the context launches on; outputs returned by rb200_run are complete. */
+RB200_API void* rb200_stream(rb200_context ctx);
+/* rocalToTensor (rocal_api_data_transfer.h:62-66): first output, uint8 -> fp32/fp16, x*multiplier+offset */
+RB200_API int rb200_to_tensor(rb200_context ctx, void* out_ptr, int layout, int dtype, const float* multiplier3,
+                              const float* offset3, int reverse_channels, int output_mem_type);
+
+/* ---- SSD box encoder: rocalBoxEncoder / rocalCopyEncodedBoxesAndLables / rocalGetEncodedBoxesAndLables
+ * (rocal_api_meta_data.h:270-286) ---- */
+RB200_API int rb200_box_encoder(rb200_context ctx, const float* anchors_ltrb, size_t num_anchors, float criteria,
+                                const float* means4, const float* stds4, int offset, float scale);
+RB200_API int rb200_copy_encoded_boxes_and_labels(rb200_context ctx, float* boxes_buf, int* labels_buf);
+RB200_API int rb200_get_encoded_boxes_and_labels(rb200_context ctx, float** boxes_dev, int** labels_dev,
+                                                 size_t* num_anchors);
+
+/* Boxes of the batch returned by the last rb200_run, after the graph's crops and mirrors: the data
+ * of rocalGetBoundingBoxCount / rocalGetBoundingBoxCords / rocalGetBoundingBoxLabel
+ * (rocal_api_meta_data.h:179-211) as flat arrays. Returns the total number of boxes; the arrays may be
+ * NULL to query the size. counts holds one entry per sample. */
+RB200_API size_t rb200_get_bounding_boxes(rb200_context ctx, float* ltrb, int* labels, int* counts);
+
+/* [extension] Inspection of what the last returned batch used. rb200_get_crop_windows: n x {x, y, w, h}
+ * source window of the crop-type operator (Crop*, CropMirrorNormalize, ResizeCropMirror, SSDRandomCrop)
+ * that produced `t`. rb200_get_int_array / rb200_get_float_array: the current per-sample values of a
+ * parameter (n = batch size; the parameter must be in use by a verified graph); they return the number
+ * of values written. */
+RB200_API int rb200_get_crop_windows(rb200_context ctx, rb200_tensor t, unsigned* xywh);
+RB200_API size_t rb200_get_int_array(rb200_param p, int* out, size_t n);
+RB200_API size_t rb200_get_float_array(rb200_param p, float* out, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RB200_H */

@@ -1,0 +1,1257 @@
+#include "pipeline.h"
+
+#include <chrono>
+#include <cmath>
+#include <cstring>
+
+namespace rb200 {
+
+static inline unsigned long long now_us() {
+    return (unsigned long long)std::chrono::duration_cast<std::chrono::microseconds>(
+               std::chrono::steady_clock::now().time_since_epoch())
+        .count();
+}
+
+// ------------------------------------------------------------------------------------------
+// Host-side size rules
+// ------------------------------------------------------------------------------------------
+
+// Target size of one resized sample: ResizeNode::adjust_out_roi_size
+// (source/augmentations/geometry_augmentations/node_resize.cpp:98-138).
+static void resize_target(unsigned src_w, unsigned src_h, unsigned dst_w, unsigned dst_h, int mode, unsigned max_w,
+                          unsigned max_h, unsigned& out_w, unsigned& out_h) {
+    bool has_max = (max_w | max_h) > 0;
+    if (mode == ROCAL_SCALING_MODE_STRETCH) {
+        if (!dst_w) dst_w = src_w;
+        if (!dst_h) dst_h = src_h;
+        if (has_max) {
+            if (max_w) dst_w = std::min(dst_w, max_w);
+            if (max_h) dst_h = std::min(dst_h, max_h);
+        }
+    } else if (mode == ROCAL_SCALING_MODE_DEFAULT) {
+        if ((!dst_w) & (dst_h != 0)) {
+            dst_w = (unsigned)std::lround(src_w * (static_cast<float>(dst_h) / src_h));
+        } else if ((!dst_h) & (dst_w != 0)) {
+            dst_h = (unsigned)std::lround(src_h * (static_cast<float>(dst_w) / src_w));
+        }
+        if (has_max) {
+            if (max_w) dst_w = std::min(dst_w, max_w);
+            if (max_h) dst_h = std::min(dst_h, max_h);
+        }
+    } else {
+        float scale = 1.0f;
+        float scale_w = static_cast<float>(dst_w) / src_w;
+        float scale_h = static_cast<float>(dst_h) / src_h;
+        if (mode == ROCAL_SCALING_MODE_NOT_SMALLER) {
+            scale = std::max(scale_w, scale_h);
+        } else if (mode == ROCAL_SCALING_MODE_NOT_LARGER) {
+            scale = (scale_w > 0 && scale_h > 0) ? std::min(scale_w, scale_h) : ((scale_w > 0) ? scale_w : scale_h);
+        }
+        if (has_max) {
+            if (max_w) scale = std::min(scale, static_cast<float>(max_w) / src_w);
+            if (max_h) scale = std::min(scale, static_cast<float>(max_h) / src_h);
+        }
+        if ((scale_h != scale) || (!dst_h)) dst_h = (unsigned)std::lround(src_h * scale);
+        if ((scale_w != scale) || (!dst_w)) dst_w = (unsigned)std::lround(src_w * scale);
+    }
+    out_w = dst_w;
+    out_h = dst_h;
+}
+
+void CropSpec::update(const std::vector<int>& in_w, const std::vector<int>& in_h) {
+    size_t n = in_w.size();
+    x1v.resize(n);
+    y1v.resize(n);
+    cwv.resize(n);
+    chv.resize(n);
+    for (size_t i = 0; i < n; i++) {
+        unsigned w = (unsigned)in_w[i], h = (unsigned)in_h[i];
+        if (mode != RANDOM) {
+            cwv[i] = (crop_w <= w && crop_w > 0) ? crop_w : w;
+            chv[i] = (crop_h <= h && crop_h > 0) ? crop_h : h;
+            if (mode == FIXED_ANCHOR) {
+                float ax = next_anchor_x.size() == n ? next_anchor_x[i] : anchor_x;
+                float ay = next_anchor_y.size() == n ? next_anchor_y[i] : anchor_y;
+                x1v[i] = static_cast<unsigned>(static_cast<size_t>(std::nearbyintf(ax * (w - cwv[i]))));
+                y1v[i] = static_cast<unsigned>(static_cast<size_t>(std::nearbyintf(ay * (h - chv[i]))));
+            } else {
+                x1v[i] = (x1 >= w) ? 0 : x1;
+                y1v[i] = (y1 >= h) ? 0 : y1;
+            }
+        } else {
+            h_factor->renew();
+            float hf = h_factor->get();
+            w_factor->renew();
+            float wf = w_factor->get();
+            cwv[i] = static_cast<unsigned>(static_cast<size_t>(wf * w));
+            chv[i] = static_cast<unsigned>(static_cast<size_t>(hf * h));
+            x_drift->renew();
+            y_drift->renew();
+            float xd = x_drift->get(), yd = y_drift->get();
+            x1v[i] = static_cast<unsigned>(static_cast<size_t>(xd * (w - cwv[i])));
+            y1v[i] = static_cast<unsigned>(static_cast<size_t>(yd * (h - chv[i])));
+        }
+        // The window handed to the kernel never leaves the image (the reference clamps x2/y2 only).
+        if (x1v[i] >= w) x1v[i] = w ? w - 1 : 0;
+        if (y1v[i] >= h) y1v[i] = h ? h - 1 : 0;
+        cwv[i] = std::max(1u, std::min(cwv[i], w - x1v[i]));
+        chv[i] = std::max(1u, std::min(chv[i], h - y1v[i]));
+    }
+    next_anchor_x.clear();
+    next_anchor_y.clear();
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensors
+// ------------------------------------------------------------------------------------------
+
+TensorImpl::TensorImpl(Pipeline* p, int id_, int n_, int mw, int mh, RocalTensorOutputType dt, RocalTensorLayout l,
+                       bool out, bool src)
+    : pipe(p), id(id_), n(n_), max_w(mw), max_h(mh), dtype(dt), lay(l), is_output(out), is_source(src) {
+    roi_w.assign(n, mw);
+    roi_h.assign(n, mh);
+    user_roi.assign((size_t)n * 4, 0);
+}
+
+std::vector<size_t> TensorImpl::dims() {
+    if (!custom_dims.empty()) return custom_dims;
+    if (lay == ROCAL_NCHW) return {(size_t)n, 3, (size_t)max_h, (size_t)max_w};
+    return {(size_t)n, (size_t)max_h, (size_t)max_w, 3};
+}
+
+std::vector<size_t> TensorImpl::strides() {
+    size_t e = elem_size();
+    if (!custom_dims.empty()) {
+        std::vector<size_t> st(custom_dims.size(), e);
+        for (int k = (int)custom_dims.size() - 2; k >= 0; k--) st[k] = st[k + 1] * custom_dims[k + 1];
+        return st;
+    }
+    if (lay == ROCAL_NCHW) return {(size_t)3 * max_h * max_w * e, (size_t)max_h * max_w * e, (size_t)max_w * e, e};
+    return {(size_t)max_h * max_w * 3 * e, (size_t)max_w * 3 * e, 3 * e, e};
+}
+
+unsigned TensorImpl::copy_data(void* user_buffer, RocalOutputMemType external_mem_type) {
+    if (!current || !user_buffer) return 1;
+    try {
+        pipe->sync_copy(user_buffer, current, data_size(),
+                        external_mem_type == ROCAL_MEMCPY_GPU ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost);
+    } catch (const std::exception& e) {
+        pipe->capture_error(e.what());
+        return 1;
+    }
+    return 0;
+}
+
+unsigned TensorImpl::copy_data(void* user_buffer, unsigned x_offset, unsigned y_offset, unsigned max_cols, unsigned max_rows) {
+    // Copies the window (x_offset, y_offset, max_cols, max_rows) of every sample to host memory, tightly packed.
+    if (!current || !user_buffer) return 1;
+    if (x_offset + max_cols > (unsigned)max_w || y_offset + max_rows > (unsigned)max_h) return 1;
+    size_t e = elem_size();
+    try {
+        cudaSetDevice(pipe->gpu_id());
+        uint8_t* dst = (uint8_t*)user_buffer;
+        const uint8_t* src = (const uint8_t*)current;
+        if (lay == ROCAL_NCHW) {
+            for (int i = 0; i < n * 3; i++) {
+                RB200_CUDA(cudaMemcpy2D(dst + (size_t)i * max_rows * max_cols * e, max_cols * e,
+                                        src + ((size_t)i * max_h * max_w + (size_t)y_offset * max_w + x_offset) * e,
+                                        (size_t)max_w * e, max_cols * e, max_rows, cudaMemcpyDeviceToHost));
+            }
+        } else {
+            for (int i = 0; i < n; i++) {
+                RB200_CUDA(cudaMemcpy2D(dst + (size_t)i * max_rows * max_cols * 3 * e, max_cols * 3 * e,
+                                        src + ((size_t)i * max_h * max_w + (size_t)y_offset * max_w + x_offset) * 3 * e,
+                                        (size_t)max_w * 3 * e, max_cols * 3 * e, max_rows, cudaMemcpyDeviceToHost));
+            }
+        }
+    } catch (const std::exception& ex) {
+        pipe->capture_error(ex.what());
+        return 1;
+    }
+    return 0;
+}
+
+void TensorImpl::copy_roi(void* roi_buffer) { std::memcpy(roi_buffer, user_roi.data(), user_roi.size() * sizeof(unsigned)); }
+
+// ------------------------------------------------------------------------------------------
+// Pipeline: construction and graph building
+// ------------------------------------------------------------------------------------------
+
+Pipeline::Pipeline(size_t batch, int gpu_id, size_t depth, RocalTensorOutputType out_dtype)
+    : _batch(batch), _gpu_id(gpu_id), _depth(depth < 2 ? 2 : depth), _out_dtype(out_dtype) {
+    if (batch == 0 || batch > 65535) RB200_THROW("batch size must be in [1, 65535]");
+    int count = 0;
+    RB200_CUDA(cudaGetDeviceCount(&count));
+    if (gpu_id < 0 || gpu_id >= count) RB200_THROW("invalid gpu_id " + std::to_string(gpu_id));
+    RB200_CUDA(cudaSetDevice(gpu_id));
+    RB200_CUDA(cudaStreamCreateWithFlags(&_stream, cudaStreamNonBlocking));
+}
+
+Pipeline::~Pipeline() {
+    {
+        std::lock_guard<std::mutex> lk(_m);
+        _stop = true;
+    }
+    _cv_work.notify_all();
+    _cv_ready.notify_all();
+    if (_worker.joinable()) _worker.join();
+    cudaSetDevice(_gpu_id);
+    if (_stream) cudaStreamSynchronize(_stream);
+    for (auto& t : _tensors) {
+        for (void* p : t->ring) cudaFree(p);
+        if (t->scratch) cudaFree(t->scratch);
+    }
+    for (auto& s : _slots) {
+        if (s.done) cudaEventDestroy(s.done);
+        if (s.d_tables) cudaFree(s.d_tables);
+        if (s.h_tables) cudaFreeHost(s.h_tables);
+        if (s.d_enc_boxes) cudaFree(s.d_enc_boxes);
+        if (s.d_enc_labels) cudaFree(s.d_enc_labels);
+    }
+    for (int k = 0; k < 2; k++) {
+        if (_arena[k]) cudaFree(_arena[k]);
+        if (_arena_free[k]) cudaEventDestroy(_arena_free[k]);
+    }
+    if (_d_anchors) cudaFree(_d_anchors);
+    if (_d_boxes) cudaFree(_d_boxes);
+    if (_d_labels) cudaFree(_d_labels);
+    if (_d_offsets) cudaFree(_d_offsets);
+    if (_h_box_stage) cudaFreeHost(_h_box_stage);
+    if (_stream) cudaStreamDestroy(_stream);
+}
+
+bool Pipeline::owns(const void* t) const {
+    for (auto& p : _tensors)
+        if (p.get() == t) return true;
+    return false;
+}
+
+TensorImpl* Pipeline::add_source(unsigned max_w, unsigned max_h, bool is_output) {
+    if (_verified) RB200_THROW("the graph is already verified");
+    if (_source >= 0) RB200_THROW("only one external source per context is supported");
+    if (max_w == 0 || max_h == 0) RB200_THROW("max_width and max_height must be given for raw uncompressed input");
+    int id = (int)_tensors.size();
+    _tensors.emplace_back(new TensorImpl(this, id, (int)_batch, (int)max_w, (int)max_h, ROCAL_UINT8, ROCAL_NHWC, is_output, true));
+    _source = id;
+    return _tensors.back().get();
+}
+
+TensorImpl* Pipeline::add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
+                               RocalTensorOutputType dt, bool is_output) {
+    if (_verified) RB200_THROW("the graph is already verified");
+    if (!owns(in)) RB200_THROW("input tensor does not belong to this context");
+    if (out_w == 0 || out_h == 0) RB200_THROW("output dimensions must be non-zero");
+    if (lay == ROCAL_NONE) lay = in->lay;
+    if (lay != ROCAL_NHWC && lay != ROCAL_NCHW) RB200_THROW("only NHWC and NCHW image layouts are supported");
+    if (dt != ROCAL_UINT8 && dt != ROCAL_FP32 && dt != ROCAL_FP16) RB200_THROW("output type must be UINT8, FP32 or FP16");
+    int id = (int)_tensors.size();
+    _tensors.emplace_back(new TensorImpl(this, id, (int)_batch, (int)out_w, (int)out_h, dt, lay, is_output, false));
+    node.in = in->id;
+    node.out = id;
+    _tensors.back()->producer = (int)_nodes.size();
+    in->consumers++;
+    _nodes.push_back(std::move(node));
+    return _tensors.back().get();
+}
+
+void Pipeline::set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
+                               const float* stds, bool offset, float scale) {
+    if (_verified) RB200_THROW("the graph is already verified");
+    if (!anchors || num_anchors == 0) RB200_THROW("box encoder needs a non-empty anchor list");
+    _anchors.assign(anchors, anchors + num_anchors * 4);
+    _enc.num_anchors = (int32_t)num_anchors;
+    _enc.criteria = criteria;
+    for (int k = 0; k < 4; k++) {
+        _enc.means[k] = means[k];
+        _enc.inv_stds[k] = (float)(1. / stds[k]);
+    }
+    _enc.offset = offset ? 1 : 0;
+    _enc.scale = scale;
+    _box_encoder = true;
+}
+
+// ------------------------------------------------------------------------------------------
+// verify(): fusion plan + allocation + worker start
+// ------------------------------------------------------------------------------------------
+
+static bool is_color(NodeKind k) {
+    return k == NodeKind::BRIGHTNESS || k == NodeKind::CONTRAST || k == NodeKind::HUE || k == NodeKind::SATURATION ||
+           k == NodeKind::COLOR_TWIST;
+}
+
+void Pipeline::plan() {
+    auto fusable_mid = [&](int tensor_id) {
+        TensorImpl* t = _tensors[tensor_id].get();
+        return !t->is_output && t->consumers == 1 && t->dtype == ROCAL_UINT8 && t->lay == ROCAL_NHWC;
+    };
+    auto consumer_of = [&](int tensor_id) {
+        for (size_t k = 0; k < _nodes.size(); k++)
+            if (_nodes[k].in == tensor_id) return (int)k;
+        return -1;
+    };
+    for (size_t k = 0; k < _nodes.size(); k++) {
+        Node& nd = _nodes[k];
+        if (!fusable_mid(nd.out)) continue;
+        int c = consumer_of(nd.out);
+        if (c < 0) continue;
+        NodeKind ck = _nodes[c].kind;
+        if ((nd.kind == NodeKind::CROP || nd.kind == NodeKind::SSD_RANDOM_CROP) &&
+            (ck == NodeKind::RESIZE || ck == NodeKind::RESIZE_MIRROR_NORMALIZE))
+            nd.absorbed_by = c;
+        else if (nd.kind == NodeKind::RESIZE && ck == NodeKind::CROP_MIRROR_NORMALIZE)
+            nd.absorbed_by = c;
+        else if (is_color(nd.kind) && ck == NodeKind::FLIP)
+            nd.absorbed_by = c;
+    }
+    for (size_t k = 0; k < _nodes.size(); k++) {
+        Node& nd = _nodes[k];
+        if (nd.absorbed_by >= 0) continue;
+        Step st;
+        st.out_tensor = nd.out;
+        st.in_tensor = nd.in;
+        auto producer_absorbed = [&](int tensor_id) {
+            int p = _tensors[tensor_id]->producer;
+            return (p >= 0 && _nodes[p].absorbed_by == (int)k) ? p : -1;
+        };
+        switch (nd.kind) {
+            case NodeKind::CROP_MIRROR_NORMALIZE: {
+                int r = producer_absorbed(nd.in);
+                if (r >= 0) {
+                    st.kind = Step::RESAMPLE;
+                    st.post = (int)k;
+                    st.resize = r;
+                    st.in_tensor = _nodes[r].in;
+                    int p = _tensors[_nodes[r].in]->producer;
+                    if (p >= 0 && _nodes[p].absorbed_by == r) {
+                        st.pre_crop = p;
+                        st.in_tensor = _nodes[p].in;
+                    }
+                } else {
+                    st.kind = Step::POINTWISE;
+                    st.window = (int)k;
+                }
+                break;
+            }
+            case NodeKind::RESIZE:
+            case NodeKind::RESIZE_MIRROR_NORMALIZE:
+            case NodeKind::RESIZE_CROP_MIRROR: {
+                st.kind = Step::RESAMPLE;
+                st.resize = (int)k;
+                int p = producer_absorbed(nd.in);
+                if (p >= 0) {
+                    st.pre_crop = p;
+                    st.in_tensor = _nodes[p].in;
+                }
+                break;
+            }
+            case NodeKind::CROP:
+            case NodeKind::SSD_RANDOM_CROP:
+                st.kind = Step::POINTWISE;
+                st.window = (int)k;
+                break;
+            case NodeKind::FLIP: {
+                st.kind = Step::POINTWISE;
+                st.flip = (int)k;
+                int c = producer_absorbed(nd.in);
+                if (c >= 0) {
+                    st.color = c;
+                    st.in_tensor = _nodes[c].in;
+                }
+                break;
+            }
+            case NodeKind::WARP_AFFINE:
+            case NodeKind::ROTATE:
+                st.kind = Step::WARP;
+                st.warp = (int)k;
+                break;
+            default:
+                st.kind = Step::POINTWISE;
+                st.color = (int)k;
+        }
+        TensorImpl* in = _tensors[st.in_tensor].get();
+        TensorImpl* out = _tensors[st.out_tensor].get();
+        if (in->dtype != ROCAL_UINT8 || in->lay != ROCAL_NHWC)
+            RB200_THROW("the input of an augmentation must be a uint8 NHWC tensor");
+        if (st.kind == Step::WARP && (out->dtype != ROCAL_UINT8 || out->lay != ROCAL_NHWC))
+            RB200_THROW("WarpAffine/Rotate produce uint8 NHWC output");
+        out->materialized = true;
+        _steps.push_back(st);
+    }
+}
+
+void Pipeline::verify() {
+    if (_verified) RB200_THROW("rocalVerify was already called");
+    if (_source < 0) RB200_THROW("the graph has no input source");
+    RB200_CUDA(cudaSetDevice(_gpu_id));
+    plan();
+    _slots.resize(_depth);
+    size_t table_bytes = std::max<size_t>(1, _steps.size()) * _batch * 64;
+    for (auto& t : _tensors) {
+        if (t->is_source) {
+            if (t->is_output) t->materialized = false;   // the source is exposed through the input arena
+            continue;
+        }
+        if (!t->materialized) continue;
+        if (t->is_output) {
+            t->ring.resize(_depth, nullptr);
+            for (size_t s = 0; s < _depth; s++) RB200_CUDA(cudaMalloc(&t->ring[s], t->data_size()));
+        } else {
+            RB200_CUDA(cudaMalloc(&t->scratch, t->data_size()));
+        }
+    }
+    for (auto& t : _tensors)
+        if (t->is_output && !t->is_source) _output_list.items.push_back(t.get());
+    for (auto& s : _slots) {
+        RB200_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+        RB200_CUDA(cudaMalloc(&s.d_tables, table_bytes));
+        RB200_CUDA(cudaHostAlloc(&s.h_tables, table_bytes, cudaHostAllocDefault));
+        s.rois.assign(_tensors.size(), std::vector<unsigned>());
+        s.windows.assign(_nodes.size(), std::vector<unsigned>());
+        if (_box_encoder) {
+            RB200_CUDA(cudaMalloc((void**)&s.d_enc_boxes, _batch * (size_t)_enc.num_anchors * 4 * sizeof(float)));
+            RB200_CUDA(cudaMalloc((void**)&s.d_enc_labels, _batch * (size_t)_enc.num_anchors * sizeof(int)));
+        }
+    }
+    for (int k = 0; k < 2; k++) RB200_CUDA(cudaEventCreateWithFlags(&_arena_free[k], cudaEventDisableTiming));
+    if (_box_encoder) {
+        RB200_CUDA(cudaMalloc((void**)&_d_anchors, _anchors.size() * sizeof(float)));
+        RB200_CUDA(cudaMemcpy(_d_anchors, _anchors.data(), _anchors.size() * sizeof(float), cudaMemcpyHostToDevice));
+        _enc.anchors = _d_anchors;
+        _box_capacity = _batch * 64;
+        RB200_CUDA(cudaMalloc((void**)&_d_boxes, _box_capacity * 4 * sizeof(float)));
+        RB200_CUDA(cudaMalloc((void**)&_d_labels, _box_capacity * sizeof(int)));
+        RB200_CUDA(cudaMalloc((void**)&_d_offsets, (_batch + 1) * sizeof(int)));
+        RB200_CUDA(cudaHostAlloc(&_h_box_stage, _box_capacity * 5 * sizeof(float) + (_batch + 1) * sizeof(int), cudaHostAllocDefault));
+        _enc_boxes_t.reset(new TensorImpl(this, -1, (int)_batch, 4, _enc.num_anchors, ROCAL_FP32, ROCAL_NHWC, false, false));
+        _enc_labels_t.reset(new TensorImpl(this, -2, (int)_batch, 1, _enc.num_anchors, ROCAL_INT32, ROCAL_NHWC, false, false));
+        _enc_boxes_t->custom_dims = {_batch, (size_t)_enc.num_anchors, 4};
+        _enc_labels_t->custom_dims = {_batch, (size_t)_enc.num_anchors};
+        _enc_list_boxes.items = {_enc_boxes_t.get()};
+        _enc_list_labels.items = {_enc_labels_t.get()};
+        _enc_meta.lists = {&_enc_list_labels, &_enc_list_boxes};
+    }
+    // Parameters that feed per-sample tables keep one value per sample.
+    for (auto& nd : _nodes) {
+        for (auto* p : {nd.mirror, nd.flip_h, nd.flip_v})
+            if (p) p->create_array((unsigned)_batch);
+        for (auto* p : nd.color)
+            if (p) p->create_array((unsigned)_batch);
+        if (nd.angle) nd.angle->create_array((unsigned)_batch);
+    }
+    _verified = true;
+    _worker = std::thread(&Pipeline::worker_loop, this);
+}
+
+// ------------------------------------------------------------------------------------------
+// Feeding
+// ------------------------------------------------------------------------------------------
+
+void Pipeline::stage_boxes(const float* ltrb, const int* labels, const int* counts, size_t n) {
+    if (n != _batch) RB200_THROW("rb200_feed_boxes: expected one count per sample of the batch");
+    size_t total = 0;
+    for (size_t i = 0; i < n; i++) {
+        if (counts[i] < 0) RB200_THROW("rb200_feed_boxes: negative box count");
+        total += (size_t)counts[i];
+    }
+    _staged.boxes.assign(ltrb, ltrb + total * 4);
+    _staged.labels.assign(labels, labels + total);
+    _staged.counts.assign(counts, counts + n);
+    _staged.has_boxes = true;
+}
+
+void Pipeline::stage_anchors(TensorImpl* t, const float* ax, const float* ay, size_t n) {
+    if (!owns(t) || t->producer < 0 || _nodes[t->producer].kind != NodeKind::CROP_MIRROR_NORMALIZE)
+        RB200_THROW("rb200_set_crop_anchors: the tensor is not the output of a CropMirrorNormalize call");
+    if (n != _batch) RB200_THROW("rb200_set_crop_anchors: expected one anchor pair per sample");
+    _staged.anchors_x.emplace_back(t->producer, std::vector<float>(ax, ax + n));
+    _staged.anchors_y.emplace_back(t->producer, std::vector<float>(ay, ay + n));
+}
+
+void Pipeline::stage_affine(TensorImpl* t, const float* m6, size_t n) {
+    if (!owns(t) || t->producer < 0 || _nodes[t->producer].kind != NodeKind::WARP_AFFINE)
+        RB200_THROW("rb200_set_affine: the tensor is not the output of a WarpAffine call");
+    if (n != _batch) RB200_THROW("rb200_set_affine: expected one table per sample");
+    _staged.affines.emplace_back(t->producer, std::vector<float>(m6, m6 + n * 6));
+}
+
+void Pipeline::feed(InputBatch&& b) {
+    if (!_verified) RB200_THROW("rocalVerify must be called before feeding input");
+    if (b.n != _batch) RB200_THROW("a fed batch must hold exactly batch_size samples (got " + std::to_string(b.n) + ")");
+    TensorImpl* src = _tensors[_source].get();
+    if (b.kind == InputBatch::SLOTS) {
+        for (size_t i = 0; i < b.n; i++) {
+            if (!b.bufs[i]) RB200_THROW("null input buffer");
+            unsigned x = b.roi[i * 4], y = b.roi[i * 4 + 1], w = b.roi[i * 4 + 2], h = b.roi[i * 4 + 3];
+            if (w == 0 || h == 0 || x + w > b.max_w || y + h > b.max_h)
+                RB200_THROW("input ROI of sample " + std::to_string(i) + " is empty or exceeds max_width x max_height");
+        }
+    } else {
+        if (!b.arena) RB200_THROW("null input arena");
+        for (size_t i = 0; i < b.n; i++) {
+            const auto& d = b.descs[i];
+            if (d.width == 0 || d.height == 0 || d.stride < d.width * 3 ||
+                d.offset + (uint64_t)(d.height - 1) * d.stride + (uint64_t)d.width * 3 > b.arena_bytes)
+                RB200_THROW("image descriptor " + std::to_string(i) + " is empty or exceeds the arena");
+            if (d.width > (unsigned)src->max_w || d.height > (unsigned)src->max_h)
+                RB200_THROW("image " + std::to_string(i) + " exceeds the source's max_width x max_height");
+        }
+    }
+    b.has_boxes = _staged.has_boxes;
+    b.boxes = std::move(_staged.boxes);
+    b.labels = std::move(_staged.labels);
+    b.counts = std::move(_staged.counts);
+    b.anchors_x = std::move(_staged.anchors_x);
+    b.anchors_y = std::move(_staged.anchors_y);
+    b.affines = std::move(_staged.affines);
+    _staged = InputBatch();
+    {
+        std::lock_guard<std::mutex> lk(_m);
+        _queue.push_back(std::move(b));
+        _in_flight++;
+    }
+    _cv_work.notify_one();
+}
+
+size_t Pipeline::remaining() {
+    std::lock_guard<std::mutex> lk(_m);
+    return _in_flight * _batch;
+}
+
+// ------------------------------------------------------------------------------------------
+// Worker: upload -> tables -> launches -> event
+// ------------------------------------------------------------------------------------------
+
+void Pipeline::worker_loop() {
+    cudaSetDevice(_gpu_id);
+    for (;;) {
+        InputBatch b;
+        size_t slot_idx;
+        {
+            std::unique_lock<std::mutex> lk(_m);
+            _cv_work.wait(lk, [&] { return _stop || (!_queue.empty() && _slots[_write].state == Slot::FREE); });
+            if (_stop) return;
+            b = std::move(_queue.front());
+            _queue.pop_front();
+            slot_idx = _write;
+        }
+        Slot& s = _slots[slot_idx];
+        s.error.clear();
+        try {
+            process(b, s, (int)slot_idx);
+        } catch (const std::exception& e) {
+            s.error = e.what();
+        }
+        {
+            std::lock_guard<std::mutex> lk(_m);
+            s.state = Slot::READY;
+            _write = (_write + 1) % _depth;
+        }
+        _cv_ready.notify_all();
+    }
+}
+
+void Pipeline::ensure_arena(int which, size_t bytes) {
+    if (_arena_cap[which] >= bytes) return;
+    if (_arena[which]) {
+        RB200_CUDA(cudaStreamSynchronize(_stream));
+        RB200_CUDA(cudaFree(_arena[which]));
+        _arena[which] = nullptr;
+        _arena_cap[which] = 0;
+    }
+    size_t cap = bytes + bytes / 8 + 4096;
+    RB200_CUDA(cudaMalloc(&_arena[which], cap));
+    _arena_cap[which] = cap;
+}
+
+void Pipeline::sync_copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
+    RB200_CUDA(cudaSetDevice(_gpu_id));
+    unsigned long long t0 = now_us();
+    RB200_CUDA(cudaMemcpy(dst, src, bytes, kind));
+    _t_transfer += now_us() - t0;
+}
+
+// Seeded SSD random crop. The reference's node draws from std::random_device and its width/height
+// draws are shadowed (source/augmentations/node_ssd_random_crop.cpp:90-136), so the window is produced
+// by this sampler instead, with the node's structure: an option out of 7 minimum-IoU settings
+// (option 0 = keep the whole image), width and height factors in [0.3, 1], aspect ratio in [0.5, 2],
+// uniform position, every box IoU >= the option, at least one box centre inside.
+void Pipeline::ssd_crop(Node& nd, const std::vector<int>& in_w, const std::vector<int>& in_h, Slot& s) {
+    static const float kMinIou[7] = {0.0f, 0.1f, 0.3f, 0.5f, 0.45f, 0.35f, 0.0f};
+    size_t n = in_w.size();
+    nd.crop.x1v.assign(n, 0);
+    nd.crop.y1v.assign(n, 0);
+    nd.crop.cwv.resize(n);
+    nd.crop.chv.resize(n);
+    unsigned base_seed = ParameterFactory::instance().get_seed();
+    unsigned batch_id = nd.batch_counter++;
+    size_t box0 = 0;
+    std::vector<float> crops(n * 4);
+    for (size_t i = 0; i < n; i++) {
+        std::mt19937 gen(base_seed * 2654435761u + batch_id * 40503u + (unsigned)i);
+        auto uni = [&](float lo, float hi) {
+            return (float)(((double)gen() / 4294967295.0) * ((double)hi - (double)lo) + (double)lo);
+        };
+        int nb = s.counts.empty() ? 0 : s.counts[i];
+        const float* bb = s.boxes.data() + box0 * 4;
+        float l = 0.f, t = 0.f, r = 1.f, b = 1.f;
+        for (int round = 0; round < 64; round++) {
+            int option = (int)(gen() % 7u);
+            if (option == 0) break;
+            float min_iou = kMinIou[option];
+            bool found = false;
+            for (int a = 0; a < nd.ssd_attempts && !found; a++) {
+                float w = uni(0.3f, 1.0f), h = uni(0.3f, 1.0f);
+                float ar = w / h;
+                if (ar < 0.5f || ar > 2.0f) continue;
+                float x = uni(0.0f, 1.0f - w), y = uni(0.0f, 1.0f - h);
+                float cl = x, ct = y, cr = x + w, cb = y + h;
+                bool ok = true;
+                int centres = 0;
+                for (int j = 0; j < nb && ok; j++) {
+                    const float* q = bb + j * 4;
+                    float xa = std::max(q[0], cl), ya = std::max(q[1], ct), xb = std::min(q[2], cr), yb = std::min(q[3], cb);
+                    float inter = std::max(0.f, xb - xa) * std::max(0.f, yb - ya);
+                    float a1 = (q[2] - q[0]) * (q[3] - q[1]), a2 = (cr - cl) * (cb - ct);
+                    float iou = inter / (a1 + a2 - inter);
+                    if (iou < min_iou) ok = false;
+                    float xc = 0.5f * (q[0] + q[2]), yc = 0.5f * (q[1] + q[3]);
+                    if (xc > cl && xc < cr && yc > ct && yc < cb) centres++;
+                }
+                if (!ok || (nb > 0 && centres == 0)) continue;
+                l = cl; t = ct; r = cr; b = cb;
+                found = true;
+            }
+            if (found) break;
+        }
+        crops[i * 4] = l; crops[i * 4 + 1] = t; crops[i * 4 + 2] = r; crops[i * 4 + 3] = b;
+        unsigned W = (unsigned)in_w[i], H = (unsigned)in_h[i];
+        unsigned x1 = (unsigned)(l * W), y1 = (unsigned)(t * H);
+        unsigned cw = (unsigned)((r - l) * W), ch = (unsigned)((b - t) * H);
+        if (x1 >= W) x1 = W - 1;
+        if (y1 >= H) y1 = H - 1;
+        nd.crop.x1v[i] = x1;
+        nd.crop.y1v[i] = y1;
+        nd.crop.cwv[i] = std::max(1u, std::min(cw, W - x1));
+        nd.crop.chv[i] = std::max(1u, std::min(ch, H - y1));
+        box0 += (size_t)nb;
+    }
+    transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in_w, in_h);
+}
+
+// Boxes follow a crop window: those whose centre lies outside are dropped, the rest are clipped and
+// re-normalised to the window (mask + clip of update_random_bbox_meta_data,
+// source/meta_data/bounding_box_graph.cpp:98-110); a sample left without boxes gets one empty box
+// with label 0, as the reference's meta nodes do.
+void Pipeline::transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, const std::vector<unsigned>& y1,
+                                      const std::vector<unsigned>& cw, const std::vector<unsigned>& ch,
+                                      const std::vector<int>& in_w, const std::vector<int>& in_h) {
+    if (s.counts.empty()) return;
+    std::vector<float> nb;
+    std::vector<int> nl, nc(s.counts.size(), 0);
+    size_t box0 = 0;
+    for (size_t i = 0; i < s.counts.size(); i++) {
+        float l = (float)x1[i] / in_w[i], t = (float)y1[i] / in_h[i];
+        float r = (float)(x1[i] + cw[i]) / in_w[i], b = (float)(y1[i] + ch[i]) / in_h[i];
+        float w = r - l, h = b - t;
+        for (int j = 0; j < s.counts[i]; j++) {
+            const float* q = s.boxes.data() + (box0 + j) * 4;
+            float xc = 0.5f * (q[0] + q[2]), yc = 0.5f * (q[1] + q[3]);
+            if (xc > l && xc < r && yc > t && yc < b) {
+                nb.push_back((std::max(q[0], l) - l) / w);
+                nb.push_back((std::max(q[1], t) - t) / h);
+                nb.push_back((std::min(q[2], r) - l) / w);
+                nb.push_back((std::min(q[3], b) - t) / h);
+                nl.push_back(s.labels[box0 + j]);
+                nc[i]++;
+            }
+        }
+        if (nc[i] == 0) {
+            nb.insert(nb.end(), {0.f, 0.f, 0.f, 0.f});
+            nl.push_back(0);
+            nc[i] = 1;
+        }
+        box0 += (size_t)s.counts[i];
+    }
+    s.boxes.swap(nb);
+    s.labels.swap(nl);
+    s.counts.swap(nc);
+}
+
+// Horizontal mirror of normalized ltrb boxes (meta_node_flip.cpp:40-55, meta_node_crop_mirror_normalize.cpp:53-74).
+void Pipeline::mirror_boxes(Slot& s, const std::vector<int>& flags) {
+    if (s.counts.empty()) return;
+    size_t box0 = 0;
+    for (size_t i = 0; i < s.counts.size(); i++) {
+        if (flags[i]) {
+            for (int j = 0; j < s.counts[i]; j++) {
+                float* q = s.boxes.data() + (box0 + j) * 4;
+                float l = 1.0f - q[2], r = 1.0f - q[0];
+                q[0] = l;
+                q[2] = r;
+            }
+        }
+        box0 += (size_t)s.counts[i];
+    }
+}
+
+void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
+    size_t n = _batch;
+    for (auto& a : b.anchors_x) _nodes[a.first].crop.next_anchor_x = a.second;
+    for (auto& a : b.anchors_y) _nodes[a.first].crop.next_anchor_y = a.second;
+    for (auto& a : b.affines) _nodes[a.first].next_affine = a.second;
+    ParameterFactory::instance().renew_parameters();
+    for (auto& nd : _nodes) {
+        TensorImpl* in = _tensors[nd.in].get();
+        TensorImpl* out = _tensors[nd.out].get();
+        auto int_array = [&](Parameter<int>* p, std::vector<int>& dst) {
+            dst.assign(n, 0);
+            if (!p) return;
+            const auto& a = p->array();
+            for (size_t i = 0; i < n; i++) dst[i] = a.size() == n ? a[i] : p->get();
+        };
+        switch (nd.kind) {
+            case NodeKind::RESIZE:
+            case NodeKind::RESIZE_MIRROR_NORMALIZE: {
+                nd.dst_w.resize(n);
+                nd.dst_h.resize(n);
+                for (size_t i = 0; i < n; i++) {
+                    unsigned w, h;
+                    resize_target((unsigned)in->roi_w[i], (unsigned)in->roi_h[i], nd.dest_w, nd.dest_h, nd.scaling_mode,
+                                  nd.max_w, nd.max_h, w, h);
+                    nd.dst_w[i] = (int)std::max(1u, std::min(w, (unsigned)out->max_w));
+                    nd.dst_h[i] = (int)std::max(1u, std::min(h, (unsigned)out->max_h));
+                }
+                out->roi_w = nd.dst_w;
+                out->roi_h = nd.dst_h;
+                if (nd.kind == NodeKind::RESIZE_MIRROR_NORMALIZE) {
+                    std::vector<int> m;
+                    int_array(nd.mirror, m);
+                    mirror_boxes(s, m);
+                }
+                break;
+            }
+            case NodeKind::RESIZE_CROP_MIRROR: {
+                nd.crop.update(in->roi_w, in->roi_h);
+                nd.dst_w.assign(n, (int)nd.dest_w);
+                nd.dst_h.assign(n, (int)nd.dest_h);
+                out->roi_w = nd.dst_w;
+                out->roi_h = nd.dst_h;
+                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h);
+                std::vector<int> m;
+                int_array(nd.mirror, m);
+                mirror_boxes(s, m);
+                break;
+            }
+            case NodeKind::CROP:
+            case NodeKind::CROP_MIRROR_NORMALIZE: {
+                nd.crop.update(in->roi_w, in->roi_h);
+                for (size_t i = 0; i < n; i++) {
+                    out->roi_w[i] = (int)std::min(nd.crop.cwv[i], (unsigned)out->max_w);
+                    out->roi_h[i] = (int)std::min(nd.crop.chv[i], (unsigned)out->max_h);
+                }
+                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h);
+                if (nd.kind == NodeKind::CROP_MIRROR_NORMALIZE) {
+                    std::vector<int> m;
+                    int_array(nd.mirror, m);
+                    mirror_boxes(s, m);
+                }
+                break;
+            }
+            case NodeKind::SSD_RANDOM_CROP: {
+                ssd_crop(nd, in->roi_w, in->roi_h, s);
+                for (size_t i = 0; i < n; i++) {
+                    out->roi_w[i] = (int)std::min(nd.crop.cwv[i], (unsigned)out->max_w);
+                    out->roi_h[i] = (int)std::min(nd.crop.chv[i], (unsigned)out->max_h);
+                }
+                break;
+            }
+            case NodeKind::FLIP: {
+                out->roi_w = in->roi_w;
+                out->roi_h = in->roi_h;
+                std::vector<int> m;
+                int_array(nd.flip_h, m);
+                mirror_boxes(s, m);
+                break;
+            }
+            case NodeKind::WARP_AFFINE: {
+                nd.affine_v.resize(n * 6);
+                if (nd.next_affine.size() == n * 6) {
+                    nd.affine_v = nd.next_affine;
+                    nd.next_affine.clear();
+                } else {
+                    // x0, y0, x1, y1, o0, o1: the packing of WarpAffineNode::update_affine_array
+                    // (node_warp_affine.cpp:67-75), one renewal per sample and coefficient.
+                    static const int order[6] = {0, 2, 1, 3, 4, 5};
+                    for (size_t i = 0; i < n; i++)
+                        for (int k = 0; k < 6; k++) {
+                            Parameter<float>* p = nd.affine[order[k]];
+                            p->renew();
+                            nd.affine_v[i * 6 + k] = p->get();
+                        }
+                }
+                for (size_t i = 0; i < n; i++) {
+                    out->roi_w[i] = out->max_w;
+                    out->roi_h[i] = out->max_h;
+                }
+                break;
+            }
+            case NodeKind::ROTATE: {
+                nd.affine_v.resize(n * 6);
+                const auto& a = nd.angle->array();
+                for (size_t i = 0; i < n; i++) {
+                    float deg = a.size() == n ? a[i] : nd.angle->get();
+                    float rad = deg * (float)(M_PI / 180.0);
+                    float c = (float)std::cos((double)rad), sn = (float)std::sin((double)rad);
+                    float* m = &nd.affine_v[i * 6];
+                    m[0] = c; m[1] = -sn; m[2] = sn; m[3] = c; m[4] = 0.f; m[5] = 0.f;
+                    out->roi_w[i] = out->max_w;
+                    out->roi_h[i] = out->max_h;
+                }
+                break;
+            }
+            default:   // colour operators keep the geometry
+                out->roi_w = in->roi_w;
+                out->roi_h = in->roi_h;
+        }
+    }
+}
+
+void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
+    const size_t n = _batch;
+    TensorImpl* src = _tensors[_source].get();
+    unsigned long long t0 = now_us();
+
+    // ---- 1. input: device views of the n source images ----
+    _src_views.resize(n);
+    if (b.kind == InputBatch::RAGGED) {
+        for (size_t i = 0; i < n; i++) {
+            _src_views[i] = {b.descs[i].offset, b.descs[i].stride};
+            src->roi_w[i] = (int)b.descs[i].width;
+            src->roi_h[i] = (int)b.descs[i].height;
+        }
+        if (b.mem_kind == RB200_MEM_DEVICE) {
+            _src_base = (const uint8_t*)b.arena;
+        } else {
+            int a = _arena_next;
+            _arena_next ^= 1;
+            RB200_CUDA(cudaEventSynchronize(_arena_free[a]));
+            ensure_arena(a, b.arena_bytes);
+            RB200_CUDA(cudaMemcpyAsync(_arena[a], b.arena, b.arena_bytes, cudaMemcpyHostToDevice, _stream));
+            _src_base = (const uint8_t*)_arena[a];
+        }
+    } else {
+        size_t total = 0;
+        for (size_t i = 0; i < n; i++) {
+            unsigned w = b.roi[i * 4 + 2], h = b.roi[i * 4 + 3];
+            _src_views[i] = {total, w * 3};
+            src->roi_w[i] = (int)w;
+            src->roi_h[i] = (int)h;
+            total += ((size_t)w * h * 3 + 255) & ~(size_t)255;
+        }
+        int a = _arena_next;
+        _arena_next ^= 1;
+        RB200_CUDA(cudaEventSynchronize(_arena_free[a]));
+        ensure_arena(a, total + 256);
+        for (size_t i = 0; i < n; i++) {
+            unsigned x = b.roi[i * 4], y = b.roi[i * 4 + 1], w = b.roi[i * 4 + 2], h = b.roi[i * 4 + 3];
+            const unsigned char* p = b.bufs[i] + ((size_t)y * b.max_w + x) * 3;
+            RB200_CUDA(cudaMemcpy2DAsync((uint8_t*)_arena[a] + _src_views[i].offset, (size_t)w * 3, p, (size_t)b.max_w * 3,
+                                         (size_t)w * 3, h, cudaMemcpyHostToDevice, _stream));
+        }
+        _src_base = (const uint8_t*)_arena[a];
+    }
+    int arena_used = (b.kind == InputBatch::RAGGED && b.mem_kind == RB200_MEM_DEVICE) ? -1 : (_arena_next ^ 1);
+    _t_load += now_us() - t0;
+    t0 = now_us();
+
+    // ---- 2. per-sample tables ----
+    s.boxes = b.boxes;
+    s.labels = b.labels;
+    s.counts = b.counts;
+    update_nodes(b, s);
+
+    auto view_of = [&](int tensor_id, size_t i, const uint8_t*& base) -> SampleView {
+        TensorImpl* t = _tensors[tensor_id].get();
+        if (t->is_source) {
+            base = _src_base;
+            return _src_views[i];
+        }
+        base = (const uint8_t*)(t->is_output ? t->ring[slot_idx] : t->scratch);
+        return {(uint64_t)i * t->max_h * t->max_w * 3, (uint32_t)t->max_w * 3};
+    };
+
+    uint8_t* h_tab = (uint8_t*)s.h_tables;
+    for (size_t k = 0; k < _steps.size(); k++) {
+        const Step& st = _steps[k];
+        TensorImpl* in = _tensors[st.in_tensor].get();
+        const uint8_t* base = nullptr;
+        if (st.kind == Step::RESAMPLE) {
+            auto* tab = reinterpret_cast<rb200_resample_sample*>(h_tab + k * n * 64);
+            const Node& R = _nodes[st.resize];
+            for (size_t i = 0; i < n; i++) {
+                SampleView v = view_of(st.in_tensor, i, base);
+                rb200_resample_sample& q = tab[i];
+                std::memset(&q, 0, sizeof(q));
+                q.src_offset = v.offset;
+                q.src_stride = v.stride;
+                if (st.pre_crop >= 0) {
+                    const CropSpec& c = _nodes[st.pre_crop].crop;
+                    q.roi_x = (int)c.x1v[i]; q.roi_y = (int)c.y1v[i]; q.roi_w = (int)c.cwv[i]; q.roi_h = (int)c.chv[i];
+                } else if (R.kind == NodeKind::RESIZE_CROP_MIRROR) {
+                    q.roi_x = (int)R.crop.x1v[i]; q.roi_y = (int)R.crop.y1v[i];
+                    q.roi_w = (int)R.crop.cwv[i]; q.roi_h = (int)R.crop.chv[i];
+                } else {
+                    q.roi_w = in->roi_w[i];
+                    q.roi_h = in->roi_h[i];
+                }
+                q.dst_w = R.dst_w[i];
+                q.dst_h = R.dst_h[i];
+                if (st.post >= 0) {
+                    const Node& C = _nodes[st.post];
+                    q.crop_x = (int)C.crop.x1v[i]; q.crop_y = (int)C.crop.y1v[i];
+                    q.crop_w = (int)C.crop.cwv[i]; q.crop_h = (int)C.crop.chv[i];
+                    const auto& ma = C.mirror->array();
+                    q.mirror = (ma.size() == n ? ma[i] : C.mirror->get()) ? 1 : 0;
+                } else {
+                    q.crop_w = q.dst_w;
+                    q.crop_h = q.dst_h;
+                    if (R.mirror) {
+                        const auto& ma = R.mirror->array();
+                        q.mirror = (ma.size() == n ? ma[i] : R.mirror->get()) ? 1 : 0;
+                    }
+                }
+            }
+        } else if (st.kind == Step::POINTWISE) {
+            auto* tab = reinterpret_cast<rb200_pointwise_sample*>(h_tab + k * n * 64);
+            for (size_t i = 0; i < n; i++) {
+                SampleView v = view_of(st.in_tensor, i, base);
+                rb200_pointwise_sample& q = tab[i];
+                std::memset(&q, 0, sizeof(q));
+                q.src_offset = v.offset;
+                q.src_stride = v.stride;
+                q.roi_w = in->roi_w[i];
+                q.roi_h = in->roi_h[i];
+                q.alpha = 1.f; q.sat = 1.f;
+                if (st.window >= 0) {
+                    const Node& W = _nodes[st.window];
+                    q.roi_x = (int)W.crop.x1v[i]; q.roi_y = (int)W.crop.y1v[i];
+                    q.roi_w = (int)W.crop.cwv[i]; q.roi_h = (int)W.crop.chv[i];
+                    if (W.mirror) {
+                        const auto& ma = W.mirror->array();
+                        q.flip_h = (ma.size() == n ? ma[i] : W.mirror->get()) ? 1 : 0;
+                    }
+                }
+                if (st.flip >= 0) {
+                    const Node& F = _nodes[st.flip];
+                    const auto& ha = F.flip_h->array();
+                    const auto& va = F.flip_v->array();
+                    q.flip_h = (ha.size() == n ? ha[i] : F.flip_h->get()) ? 1 : 0;
+                    q.flip_v = (va.size() == n ? va[i] : F.flip_v->get()) ? 1 : 0;
+                }
+                if (st.color >= 0) {
+                    const Node& C = _nodes[st.color];
+                    auto val = [&](int slot, float dflt) {
+                        Parameter<float>* p = C.color[slot];
+                        if (!p) return dflt;
+                        const auto& a = p->array();
+                        return a.size() == n ? a[i] : p->get();
+                    };
+                    switch (C.kind) {
+                        case NodeKind::BRIGHTNESS: q.alpha = val(0, 1.f); q.beta = val(1, 0.f); break;
+                        case NodeKind::CONTRAST: q.alpha = val(0, 1.f); q.beta = val(1, 0.f); break;
+                        case NodeKind::HUE: q.hue = val(2, 0.f); break;
+                        case NodeKind::SATURATION: q.sat = val(3, 1.f); break;
+                        default: q.alpha = val(0, 1.f); q.beta = val(1, 0.f); q.hue = val(2, 0.f); q.sat = val(3, 1.f);
+                    }
+                }
+            }
+        } else {
+            auto* tab = reinterpret_cast<rb200_warp_sample*>(h_tab + k * n * 64);
+            const Node& W = _nodes[st.warp];
+            TensorImpl* out = _tensors[st.out_tensor].get();
+            for (size_t i = 0; i < n; i++) {
+                SampleView v = view_of(st.in_tensor, i, base);
+                rb200_warp_sample& q = tab[i];
+                std::memset(&q, 0, sizeof(q));
+                q.src_offset = v.offset;
+                q.src_stride = v.stride;
+                q.src_w = in->roi_w[i];
+                q.src_h = in->roi_h[i];
+                for (int c = 0; c < 6; c++) q.m[c] = W.affine_v[i * 6 + c];
+                q.dst_w = out->max_w;
+                q.dst_h = out->max_h;
+            }
+        }
+    }
+    if (!_steps.empty())
+        RB200_CUDA(cudaMemcpyAsync(s.d_tables, s.h_tables, _steps.size() * n * 64, cudaMemcpyHostToDevice, _stream));
+
+    // ---- 3. launches ----
+    for (size_t k = 0; k < _steps.size(); k++) {
+        const Step& st = _steps[k];
+        TensorImpl* out = _tensors[st.out_tensor].get();
+        const uint8_t* base = nullptr;
+        view_of(st.in_tensor, 0, base);
+        void* out_ptr = out->is_output ? out->ring[slot_idx] : out->scratch;
+        const void* d_tab = (const uint8_t*)s.d_tables + k * n * 64;
+        const void* h_tabk = h_tab + k * n * 64;
+        int out_dtype = out->dtype == ROCAL_FP32 ? RB200_FP32 : (out->dtype == ROCAL_FP16 ? RB200_FP16 : RB200_UINT8);
+        int out_layout = out->lay == ROCAL_NCHW ? RB200_NCHW : RB200_NHWC;
+        int rc = 0;
+        if (st.kind == Step::RESAMPLE) {
+            rb200_resample_params p{};
+            p.out = out_ptr;
+            p.out_w = out->max_w;
+            p.out_h = out->max_h;
+            p.out_dtype = out_dtype;
+            p.out_layout = out_layout;
+            const Node* norm = st.post >= 0 ? &_nodes[st.post] : &_nodes[st.resize];
+            p.normalize = norm->normalize ? 1 : 0;
+            for (int c = 0; c < 3; c++) { p.mul[c] = norm->mul[c]; p.add[c] = norm->add[c]; }
+            // A fixed-size output (crop or stretch target) is fully defined, padding zeroed; a
+            // plain resize into its max-shape tensor defines only the ROI, as the reference does.
+            p.fill_padding = (st.post >= 0 || _nodes[st.resize].kind != NodeKind::RESIZE) ? 1 : 0;
+            rc = rb200k_resample(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk, (int)n, &p, _stream);
+        } else if (st.kind == Step::POINTWISE) {
+            rb200_pointwise_params p{};
+            p.out = out_ptr;
+            p.out_w = out->max_w;
+            p.out_h = out->max_h;
+            p.out_dtype = out_dtype;
+            p.out_layout = out_layout;
+            p.color_op = RB200_COLOR_NONE;
+            if (st.color >= 0) {
+                NodeKind ck = _nodes[st.color].kind;
+                p.color_op = ck == NodeKind::BRIGHTNESS ? RB200_COLOR_BRIGHTNESS
+                             : ck == NodeKind::CONTRAST ? RB200_COLOR_CONTRAST : RB200_COLOR_TWIST;
+            }
+            for (int c = 0; c < 3; c++) { p.mul[c] = 1.f; p.add[c] = 0.f; }
+            if (st.window >= 0 && _nodes[st.window].normalize) {
+                p.normalize = 1;
+                for (int c = 0; c < 3; c++) { p.mul[c] = _nodes[st.window].mul[c]; p.add[c] = _nodes[st.window].add[c]; }
+            }
+            p.fill_padding = (st.window >= 0) ? 1 : 0;
+            rc = rb200k_pointwise(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p, _stream);
+        } else {
+            rb200_warp_params p{};
+            p.out = out_ptr;
+            p.out_w = out->max_w;
+            p.out_h = out->max_h;
+            p.fill_padding = 1;
+            rc = rb200k_warp_affine(base, (const rb200_warp_sample*)d_tab, (int)n, &p, _stream);
+        }
+        if (rc != 0) RB200_THROW(rb200k_last_error());
+    }
+    if (arena_used >= 0) RB200_CUDA(cudaEventRecord(_arena_free[arena_used], _stream));
+
+    // ---- 4. box encoder ----
+    if (_box_encoder) {
+        if (s.counts.size() != n) RB200_THROW("the box encoder needs boxes for every batch (rb200_feed_boxes)");
+        size_t total = s.labels.size();
+        int max_boxes = 1;
+        for (int c : s.counts) max_boxes = std::max(max_boxes, c);
+        if (total > _box_capacity) {
+            RB200_CUDA(cudaStreamSynchronize(_stream));
+            cudaFree(_d_boxes);
+            cudaFree(_d_labels);
+            cudaFreeHost(_h_box_stage);
+            _box_capacity = total * 2;
+            RB200_CUDA(cudaMalloc((void**)&_d_boxes, _box_capacity * 4 * sizeof(float)));
+            RB200_CUDA(cudaMalloc((void**)&_d_labels, _box_capacity * sizeof(int)));
+            RB200_CUDA(cudaHostAlloc(&_h_box_stage, _box_capacity * 5 * sizeof(float) + (_batch + 1) * sizeof(int), cudaHostAllocDefault));
+        } else {
+            // the staging block is reused: the previous batch's copies must have been issued and done
+            RB200_CUDA(cudaStreamSynchronize(_stream));
+        }
+        float* hb = (float*)_h_box_stage;
+        int* hl = (int*)(hb + _box_capacity * 4);
+        int* ho = hl + _box_capacity;
+        std::memcpy(hb, s.boxes.data(), total * 4 * sizeof(float));
+        std::memcpy(hl, s.labels.data(), total * sizeof(int));
+        ho[0] = 0;
+        for (size_t i = 0; i < n; i++) ho[i + 1] = ho[i] + s.counts[i];
+        RB200_CUDA(cudaMemcpyAsync(_d_boxes, hb, total * 4 * sizeof(float), cudaMemcpyHostToDevice, _stream));
+        RB200_CUDA(cudaMemcpyAsync(_d_labels, hl, total * sizeof(int), cudaMemcpyHostToDevice, _stream));
+        RB200_CUDA(cudaMemcpyAsync(_d_offsets, ho, (n + 1) * sizeof(int), cudaMemcpyHostToDevice, _stream));
+        int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _stream);
+        if (rc != 0) RB200_THROW(rb200k_last_error());
+    }
+
+    // ---- 5. snapshot of the ROIs the user will see, completion event ----
+    for (auto& t : _tensors) {
+        auto& r = s.rois[t->id];
+        r.resize(n * 4);
+        for (size_t i = 0; i < n; i++) {
+            r[i * 4] = 0; r[i * 4 + 1] = 0;
+            r[i * 4 + 2] = (unsigned)t->roi_w[i];
+            r[i * 4 + 3] = (unsigned)t->roi_h[i];
+        }
+    }
+    for (size_t k = 0; k < _nodes.size(); k++) {
+        const CropSpec& c = _nodes[k].crop;
+        auto& w = s.windows[k];
+        w.clear();
+        if (c.x1v.size() != n) continue;
+        w.resize(n * 4);
+        for (size_t i = 0; i < n; i++) {
+            w[i * 4] = c.x1v[i]; w[i * 4 + 1] = c.y1v[i]; w[i * 4 + 2] = c.cwv[i]; w[i * 4 + 3] = c.chv[i];
+        }
+    }
+    s.n = n;
+    RB200_CUDA(cudaEventRecord(s.done, _stream));
+    _t_process += now_us() - t0;
+}
+
+// ------------------------------------------------------------------------------------------
+// run(): hand the next finished batch to the user (MasterGraph::run, master_graph.cpp:193-223)
+// ------------------------------------------------------------------------------------------
+
+void Pipeline::run() {
+    if (!_verified) RB200_THROW("rocalVerify must be called before rocalRun");
+    size_t idx;
+    {
+        std::unique_lock<std::mutex> lk(_m);
+        if (_held >= 0) {
+            _slots[_held].state = Slot::FREE;
+            _held = -1;
+            _cv_work.notify_all();
+        }
+        if (_in_flight == 0) RB200_THROW("rocalRun: no input batch has been fed");
+        _cv_ready.wait(lk, [&] { return _stop || _slots[_read].state == Slot::READY; });
+        if (_stop) RB200_THROW("the context is shutting down");
+        idx = _read;
+        _read = (_read + 1) % _depth;
+        _slots[idx].state = Slot::HELD;
+        _held = (int)idx;
+        _in_flight--;
+    }
+    Slot& s = _slots[idx];
+    if (!s.error.empty()) RB200_THROW(s.error);
+    RB200_CUDA(cudaSetDevice(_gpu_id));
+    unsigned long long t0 = now_us();
+    RB200_CUDA(cudaEventSynchronize(s.done));
+    _t_process += now_us() - t0;
+    for (auto& t : _tensors) {
+        if (t->is_output && !t->is_source) t->current = t->ring[idx];
+        t->user_roi = s.rois[t->id];
+    }
+    if (_box_encoder) {
+        _enc_boxes_t->current = s.d_enc_boxes;
+        _enc_labels_t->current = s.d_enc_labels;
+    }
+}
+
+MetaListImpl* Pipeline::encoded_meta() {
+    if (!_box_encoder || _held < 0) return nullptr;
+    return &_enc_meta;
+}
+
+void Pipeline::encoded(float** boxes, int** labels, size_t* num_anchors) {
+    if (!_box_encoder) RB200_THROW("no box encoder in this graph");
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    *boxes = _slots[_held].d_enc_boxes;
+    *labels = _slots[_held].d_enc_labels;
+    *num_anchors = (size_t)_enc.num_anchors;
+}
+
+void Pipeline::copy_encoded(float* boxes, int* labels) {
+    float* db;
+    int* dl;
+    size_t a;
+    encoded(&db, &dl, &a);
+    sync_copy(boxes, db, _batch * a * 4 * sizeof(float), cudaMemcpyDeviceToHost);
+    sync_copy(labels, dl, _batch * a * sizeof(int), cudaMemcpyDeviceToHost);
+}
+
+void Pipeline::current_boxes(std::vector<float>& ltrb, std::vector<int>& labels, std::vector<int>& counts) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    ltrb = _slots[_held].boxes;
+    labels = _slots[_held].labels;
+    counts = _slots[_held].counts;
+}
+
+void Pipeline::crop_windows(TensorImpl* t, unsigned* xywh) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    if (!owns(t) || t->producer < 0 || _slots[_held].windows[t->producer].empty())
+        RB200_THROW("the tensor is not the output of a crop-type operator");
+    const auto& w = _slots[_held].windows[t->producer];
+    std::memcpy(xywh, w.data(), w.size() * sizeof(unsigned));
+}
+
+// rocalToTensor: first output (uint8 NHWC) -> fp32/fp16 NCHW/NHWC with x*mult+off, optional channel
+// reversal (MasterGraph::to_tensor, master_graph.cpp:514-856).
+void Pipeline::to_tensor(void* out_ptr, int layout, int dtype, const float* mul, const float* add, bool reverse, int mem_type) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    if (_output_list.items.empty()) RB200_THROW("the graph has no output");
+    TensorImpl* t = static_cast<TensorImpl*>(_output_list.items[0]);
+    if (t->dtype != ROCAL_UINT8 || t->lay != ROCAL_NHWC) RB200_THROW("rocalToTensor converts a uint8 NHWC output");
+    if (dtype != ROCAL_FP32 && dtype != ROCAL_FP16) RB200_THROW("rocalToTensor produces FP32 or FP16");
+    RB200_CUDA(cudaSetDevice(_gpu_id));
+    size_t n = _batch, e = dtype == ROCAL_FP32 ? 4 : 2;
+    size_t bytes = n * t->max_w * t->max_h * 3 * e;
+    void* d_out = out_ptr;
+    void* tmp = nullptr;
+    if (mem_type != ROCAL_MEMCPY_GPU) {
+        RB200_CUDA(cudaMalloc(&tmp, bytes));
+        d_out = tmp;
+    }
+    std::vector<rb200_pointwise_sample> tab(n);
+    for (size_t i = 0; i < n; i++) {
+        std::memset(&tab[i], 0, sizeof(tab[i]));
+        tab[i].src_offset = (uint64_t)i * t->max_h * t->max_w * 3;
+        tab[i].src_stride = (uint32_t)t->max_w * 3;
+        tab[i].roi_w = t->max_w;
+        tab[i].roi_h = t->max_h;
+        tab[i].alpha = 1.f;
+        tab[i].sat = 1.f;
+    }
+    void* d_tab = nullptr;
+    cudaError_t err = cudaMalloc(&d_tab, n * 64);
+    if (err == cudaSuccess) err = cudaMemcpy(d_tab, tab.data(), n * 64, cudaMemcpyHostToDevice);
+    int rc = 0;
+    if (err == cudaSuccess) {
+        rb200_pointwise_params p{};
+        p.out = d_out;
+        p.out_w = t->max_w;
+        p.out_h = t->max_h;
+        p.out_dtype = dtype == ROCAL_FP32 ? RB200_FP32 : RB200_FP16;
+        p.out_layout = layout == ROCAL_NCHW ? RB200_NCHW : RB200_NHWC;
+        p.normalize = 1;
+        p.reverse_channels = reverse ? 1 : 0;
+        for (int c = 0; c < 3; c++) { p.mul[c] = mul[c]; p.add[c] = add[c]; }
+        rc = rb200k_pointwise((const uint8_t*)t->current, (const rb200_pointwise_sample*)d_tab, tab.data(), (int)n, &p, _stream);
+        if (rc == 0) err = cudaStreamSynchronize(_stream);
+        if (rc == 0 && err == cudaSuccess && tmp) err = cudaMemcpy(out_ptr, tmp, bytes, cudaMemcpyDeviceToHost);
+    }
+    if (d_tab) cudaFree(d_tab);
+    if (tmp) cudaFree(tmp);
+    if (rc != 0) RB200_THROW(rb200k_last_error());
+    if (err != cudaSuccess) RB200_THROW(std::string("rocalToTensor: ") + cudaGetErrorString(err));
+}
+
+TimingInfo Pipeline::timing() {
+    TimingInfo t;
+    t.load_time = _t_load.load();
+    t.decode_time = 0;
+    t.process_time = _t_process.load();
+    t.transfer_time = _t_transfer.load();
+    return t;
+}
+
+void Pipeline::capture_error(const std::string& msg) {
+    std::lock_guard<std::mutex> lk(_err_m);
+    _error = msg;
+    _status = ROCAL_RUNTIME_ERROR;
+}
+
+RocalStatus Pipeline::status() {
+    std::lock_guard<std::mutex> lk(_err_m);
+    return _status;
+}
+
+const char* Pipeline::error_message() {
+    std::lock_guard<std::mutex> lk(_err_m);
+    return _error.c_str();
+}
+
+}  // namespace rb200

@@ -1,0 +1,314 @@
+// Pipeline runtime behind the rocAL API subset: graph of augmentation nodes, fusion into kernel
+// launches, per-batch parameter tables, device buffers, ring of output slots, worker thread.
+//
+// What it stands in for in the reference (paths under rocAL/):
+//   Context / MasterGraph        include/pipeline/context.h:29-53, source/pipeline/master_graph.cpp
+//   Node::update_node()          source/augmentations/**/node_*.cpp (per-batch tables)
+//   RingBuffer                   source/pipeline/ring_buffer.cpp:113-279,360-387
+//   DeviceManagerHip             source/device/device_manager_hip.cpp:53-77 (one stream per context)
+//   output_routine thread        source/pipeline/master_graph.cpp:950-1050
+// There is no OpenVX graph: verify() fuses node chains into the three kernel families of
+// rb200_kernels.h and every batch is a handful of launches on one CUDA stream.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "params.h"
+#include "rb200.h"
+#include "rocal_api.h"
+
+namespace rb200 {
+
+enum class NodeKind {
+    RESIZE, RESIZE_CROP_MIRROR, RESIZE_MIRROR_NORMALIZE, CROP, CROP_MIRROR_NORMALIZE, SSD_RANDOM_CROP, FLIP,
+    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, WARP_AFFINE, ROTATE
+};
+
+// Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85).
+struct CropSpec {
+    enum Mode { ABSOLUTE, FIXED_ANCHOR, RANDOM } mode = ABSOLUTE;
+    unsigned crop_w = 0, crop_h = 0, x1 = 0, y1 = 0;
+    float anchor_x = 0.5f, anchor_y = 0.5f;
+    Parameter<float>*h_factor = nullptr, *w_factor = nullptr, *x_drift = nullptr, *y_drift = nullptr;
+    std::vector<float> next_anchor_x, next_anchor_y;   // per-sample anchors of the next batch (extension)
+    std::vector<unsigned> x1v, y1v, cwv, chv;          // results of the current batch
+    void update(const std::vector<int>& in_w, const std::vector<int>& in_h);
+};
+
+struct Node {
+    NodeKind kind;
+    int in = -1, out = -1;
+    // resize family
+    unsigned dest_w = 0, dest_h = 0, max_w = 0, max_h = 0;
+    int scaling_mode = ROCAL_SCALING_MODE_STRETCH;
+    std::vector<int> dst_w, dst_h;
+    // crop family
+    CropSpec crop;
+    // mirror / flips
+    Parameter<int>*mirror = nullptr, *flip_h = nullptr, *flip_v = nullptr;
+    // normalisation tables as the CropMirrorNormalize node builds them
+    bool normalize = false;
+    float mul[3] = {1, 1, 1}, add[3] = {0, 0, 0};
+    // colour: alpha, beta, hue, sat
+    Parameter<float>* color[4] = {nullptr, nullptr, nullptr, nullptr};
+    // warp: x0, x1, y0, y1, o0, o1 (API order) or angle
+    Parameter<float>* affine[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    Parameter<float>* angle = nullptr;
+    std::vector<float> next_affine;    // [n][6] of the next batch (extension)
+    std::vector<float> affine_v;       // [n][6] packed {x0,y0,x1,y1,o0,o1}
+    int ssd_attempts = 20;
+    unsigned batch_counter = 0;        // batches this node has seen (seeds the SSD crop sampler)
+    // fusion
+    int absorbed_by = -1;              // node index of the consumer this node is fused into
+};
+
+class Pipeline;
+
+class TensorImpl : public rocalTensor {
+   public:
+    TensorImpl(Pipeline* p, int id, int n, int max_w, int max_h, RocalTensorOutputType dt, RocalTensorLayout lay,
+               bool is_output, bool is_source);
+    void* buffer() override { return current; }
+    unsigned copy_data(void* user_buffer, RocalOutputMemType external_mem_type) override;
+    unsigned copy_data(void* user_buffer, unsigned x_offset, unsigned y_offset, unsigned max_cols, unsigned max_rows) override;
+    unsigned num_of_dims() override { return custom_dims.empty() ? 4u : (unsigned)custom_dims.size(); }
+    unsigned batch_size() override { return (unsigned)n; }
+    std::vector<size_t> dims() override;
+    std::vector<size_t> strides() override;
+    RocalTensorLayout layout() override { return lay; }
+    RocalTensorBackend backend() override { return ROCAL_GPU; }
+    RocalTensorOutputType data_type() override { return dtype; }
+    RocalOutputMemType mem_type() override { return ROCAL_MEMCPY_GPU; }
+    size_t data_size() override {
+        if (!custom_dims.empty()) {
+            size_t e = elem_size();
+            for (size_t d : custom_dims) e *= d;
+            return e;
+        }
+        return (size_t)n * max_w * max_h * 3 * elem_size();
+    }
+    RocalROICordsType roi_type() override { return RocalROICordsType::ROCAL_XYWH; }
+    size_t get_roi_dims_size() override { return 2; }
+    void copy_roi(void* roi_buffer) override;
+    std::vector<size_t> shape() override { return dims(); }
+    void set_dims(std::vector<size_t>) override {}
+    void set_mem_handle(void* b) override { current = b; }
+    void set_tensor_layout(RocalTensorLayout l) override { lay = l; }
+    uint64_t data_type_size() override { return elem_size(); }
+    size_t elem_size() const {
+        switch (dtype) {
+            case ROCAL_FP32: case ROCAL_INT32: case ROCAL_UINT32: return 4;
+            case ROCAL_FP16: case ROCAL_INT16: return 2;
+            default: return 1;
+        }
+    }
+    std::vector<size_t> custom_dims;     // non-image tensors (encoded boxes / labels)
+
+    Pipeline* pipe;
+    int id, n, max_w, max_h;
+    RocalTensorOutputType dtype;
+    RocalTensorLayout lay;
+    bool is_output, is_source;
+    int producer = -1, consumers = 0;
+    bool materialized = false;
+    std::vector<int> roi_w, roi_h;       // valid extent per sample (worker side, current batch)
+    std::vector<void*> ring;             // one device buffer per slot (outputs)
+    void* scratch = nullptr;             // device buffer of a non-output intermediate
+    void* current = nullptr;             // what the user sees after rocalRun
+    std::vector<unsigned> user_roi;      // n x {x,y,w,h} of the batch the user holds
+};
+
+class TensorListImpl : public rocalTensorList {
+   public:
+    uint64_t size() override { return items.size(); }
+    rocalTensor* at(size_t i) override { return i < items.size() ? items[i] : nullptr; }
+    std::vector<rocalTensor*> items;
+};
+class MetaListImpl : public rocalListOfTensorList {
+   public:
+    uint64_t size() override { return lists.size(); }
+    rocalTensorList* at(size_t i) override { return i < lists.size() ? lists[i] : nullptr; }
+    std::vector<rocalTensorList*> lists;
+};
+
+// A device view used as kernel input: base pointer + per-sample offset/stride.
+struct SampleView {
+    uint64_t offset;
+    uint32_t stride;
+};
+
+struct InputBatch {
+    enum Kind { SLOTS, RAGGED } kind = SLOTS;
+    size_t n = 0;
+    std::vector<const unsigned char*> bufs;   // SLOTS
+    std::vector<unsigned> roi;                // SLOTS: n x {x,y,w,h}
+    unsigned max_w = 0, max_h = 0;
+    const void* arena = nullptr;              // RAGGED
+    size_t arena_bytes = 0;
+    int mem_kind = RB200_MEM_HOST;
+    std::vector<rb200_image_desc> descs;
+    bool has_boxes = false;
+    std::vector<float> boxes;                 // ltrb, normalized
+    std::vector<int> labels, counts;
+    // per-node extensions captured at feed time
+    std::vector<std::pair<int, std::vector<float>>> anchors_x, anchors_y, affines;
+};
+
+struct Step {
+    enum Kind { RESAMPLE, POINTWISE, WARP } kind;
+    int in_tensor, out_tensor;
+    int pre_crop = -1, resize = -1, post = -1;   // RESAMPLE: node indices
+    int window = -1, color = -1, flip = -1;      // POINTWISE
+    int warp = -1;                               // WARP
+};
+
+struct Slot {
+    enum State { FREE, READY, HELD } state = FREE;
+    cudaEvent_t done = nullptr;
+    void* d_tables = nullptr;        // device copy of all step tables of this slot
+    void* h_tables = nullptr;        // pinned host copy
+    std::vector<std::vector<unsigned>> rois;   // per output tensor: n x 4
+    std::vector<std::vector<unsigned>> windows;   // per node: n x {x,y,w,h} source window (crop-type nodes)
+    float* d_enc_boxes = nullptr;
+    int* d_enc_labels = nullptr;
+    std::vector<float> boxes;        // metadata after the graph (normalized ltrb)
+    std::vector<int> labels, counts;
+    size_t n = 0;
+    std::string error;
+};
+
+class Pipeline {
+   public:
+    Pipeline(size_t batch, int gpu_id, size_t prefetch_depth, RocalTensorOutputType out_dtype);
+    ~Pipeline();
+
+    // ---- graph building (user thread, before verify) ----
+    TensorImpl* add_source(unsigned max_w, unsigned max_h, bool is_output);
+    TensorImpl* add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
+                         RocalTensorOutputType dt, bool is_output);
+    void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
+                         const float* stds, bool offset, float scale);
+    void verify();
+
+    // ---- feeding (user thread) ----
+    void feed(InputBatch&& b);
+    void stage_boxes(const float* ltrb, const int* labels, const int* counts, size_t n);
+    void stage_anchors(TensorImpl* t, const float* ax, const float* ay, size_t n);
+    void stage_affine(TensorImpl* t, const float* m6, size_t n);
+
+    // ---- running ----
+    void run();
+    size_t remaining();
+
+    // ---- access ----
+    int batch() const { return (int)_batch; }
+    int gpu_id() const { return _gpu_id; }
+    cudaStream_t stream() const { return _stream; }
+    TensorListImpl* outputs() { return &_output_list; }
+    TensorImpl* tensor(int id) { return _tensors[id].get(); }
+    bool owns(const void* t) const;
+    MetaListImpl* encoded_meta();
+    void encoded(float** boxes, int** labels, size_t* num_anchors);
+    void copy_encoded(float* boxes, int* labels);
+    void current_boxes(std::vector<float>& ltrb, std::vector<int>& labels, std::vector<int>& counts);
+    void crop_windows(TensorImpl* t, unsigned* xywh);
+    void to_tensor(void* out_ptr, int layout, int dtype, const float* mul, const float* add, bool reverse, int mem_type);
+    TimingInfo timing();
+    RocalTensorOutputType default_dtype() const { return _out_dtype; }
+
+    // ---- error capture (Context::capture_error, include/pipeline/context.h:41-51) ----
+    void capture_error(const std::string& msg);
+    RocalStatus status();
+    const char* error_message();
+    bool verified() const { return _verified; }
+
+    void sync_copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind);
+
+   private:
+    void worker_loop();
+    void process(InputBatch& b, Slot& s, int slot_idx);
+    void update_nodes(const InputBatch& b, Slot& s);
+    void ensure_arena(int which, size_t bytes);
+    void plan();
+    void ssd_crop(Node& nd, const std::vector<int>& in_w, const std::vector<int>& in_h, Slot& s);
+    void transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, const std::vector<unsigned>& y1,
+                                const std::vector<unsigned>& cw, const std::vector<unsigned>& ch,
+                                const std::vector<int>& in_w, const std::vector<int>& in_h);
+    void mirror_boxes(Slot& s, const std::vector<int>& flags);
+
+    size_t _batch;
+    int _gpu_id;
+    size_t _depth;
+    RocalTensorOutputType _out_dtype;
+    cudaStream_t _stream = nullptr;
+    bool _verified = false;
+
+    std::vector<std::unique_ptr<TensorImpl>> _tensors;
+    std::vector<Node> _nodes;
+    std::vector<Step> _steps;
+    TensorListImpl _output_list;
+    int _source = -1;
+
+    // box encoder
+    bool _box_encoder = false;
+    std::vector<float> _anchors;
+    float* _d_anchors = nullptr;
+    rb200_box_encoder_params _enc{};
+    float* _d_boxes = nullptr;
+    int *_d_labels = nullptr, *_d_offsets = nullptr;
+    void* _h_box_stage = nullptr;
+    size_t _box_capacity = 0;
+    std::unique_ptr<TensorImpl> _enc_boxes_t, _enc_labels_t;   // views handed out by rocalGetEncodedBoxesAndLables
+    TensorListImpl _enc_list_boxes, _enc_list_labels;
+    MetaListImpl _enc_meta;
+
+    // staging for extensions (attached to the next fed batch)
+    InputBatch _staged;
+
+    // input arenas (double buffered)
+    void* _arena[2] = {nullptr, nullptr};
+    size_t _arena_cap[2] = {0, 0};
+    cudaEvent_t _arena_free[2] = {nullptr, nullptr};
+    int _arena_next = 0;
+    const uint8_t* _src_base = nullptr;
+    std::vector<SampleView> _src_views;
+
+    // ring
+    std::vector<Slot> _slots;
+    size_t _write = 0, _read = 0;
+    int _held = -1;
+    std::deque<InputBatch> _queue;
+    size_t _in_flight = 0;
+    std::mutex _m;
+    std::condition_variable _cv_work, _cv_ready;
+    std::thread _worker;
+    bool _stop = false;
+
+    // status
+    std::mutex _err_m;
+    std::string _error;
+    RocalStatus _status = ROCAL_OK;
+
+    // timing (us)
+    std::atomic<unsigned long long> _t_load{0}, _t_process{0}, _t_transfer{0};
+};
+
+#define RB200_THROW(msg) throw std::runtime_error(std::string(msg))
+#define RB200_CUDA(call)                                                                              \
+    do {                                                                                              \
+        cudaError_t _e = (call);                                                                      \
+        if (_e != cudaSuccess)                                                                        \
+            throw std::runtime_error(std::string(#call) + ": " + cudaGetErrorString(_e));             \
+    } while (0)
+
+}  // namespace rb200

@@ -1,0 +1,750 @@
+// Plain C ABI of the pipeline (include/rb200.h). Every entry point validates its handles, runs the
+// call inside try/catch, stores a failure in the context and prints it to stderr — the error
+// convention of the reference's API layer (rocAL/include/api/rocal_api.h:42-62,
+// rocAL/include/pipeline/context.h:41-51).
+#include <cstdio>
+#include <cstring>
+#include <iostream>
+
+#include "pipeline.h"
+
+using namespace rb200;
+
+namespace {
+
+inline Pipeline* P(rb200_context c) { return static_cast<Pipeline*>(c); }
+inline TensorImpl* T(rb200_tensor t) { return static_cast<TensorImpl*>(static_cast<rocalTensor*>(t)); }
+inline IntParam* IP(rb200_param p) { return static_cast<IntParam*>(p); }
+inline FloatParam* FP(rb200_param p) { return static_cast<FloatParam*>(p); }
+
+void report(Pipeline* p, const std::exception& e) {
+    p->capture_error(e.what());
+    std::cerr << e.what() << '\n';
+}
+
+#define CTX_OR(ret)                                        \
+    if (ctx == nullptr) {                                  \
+        std::cerr << "[ERR] Invalid rocal context\n";      \
+        return ret;                                        \
+    }
+#define IN_OR_NULL                                         \
+    if (in == nullptr) {                                   \
+        std::cerr << "[ERR] Invalid input image\n";        \
+        return nullptr;                                    \
+    }
+
+Parameter<int>* int_param(rb200_param p, int lo, int hi) {
+    return p ? IP(p)->core : ParameterFactory::instance().default_uniform_int(lo, hi);
+}
+Parameter<float>* float_param(rb200_param p, float lo, float hi) {
+    return p ? FP(p)->core : ParameterFactory::instance().default_uniform_float(lo, hi);
+}
+
+// The normalisation tables of CropMirrorNormalizeNode::create_node (node_crop_mirror_normalize.cpp:46-70):
+// 1/std and -(mean * (1/std)) per channel.
+void set_normalize(Node& nd, const float* mean, const float* std_dev, size_t n) {
+    if (!mean || !std_dev || n == 0) RB200_THROW("Mean or std dev array is empty");
+    for (int c = 0; c < 3; c++) {
+        float m = mean[n >= 3 ? c : 0], s = std_dev[n >= 3 ? c : 0];
+        if (!s) RB200_THROW("Standard deviation value cannot be 0");
+        float inv = 1 / s;
+        nd.mul[c] = inv;
+        nd.add[c] = -(m * inv);
+    }
+    nd.normalize = true;
+}
+
+// Output shape rules of rocalResize (source/api/rocal_api_augmentation.cpp:449-506).
+void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling_mode, unsigned max_w, unsigned max_h,
+                   unsigned resize_shorter, unsigned resize_longer, Node& nd, unsigned& out_max_w, unsigned& out_max_h) {
+    const unsigned kMaxAspectRatio = 6;   // MAX_ASPECT_RATIO, include/pipeline/commons.h:39
+    if ((dest_w | dest_h | resize_longer | resize_shorter) == 0)
+        RB200_THROW("Atleast one size 'dest_width' or 'dest_height' or 'resize_shorter' or 'resize_longer' must be specified");
+    if ((dest_w | dest_h) && (resize_longer | resize_shorter))
+        RB200_THROW("Only one method of specifying size can be used \ndest_width and/or dest_height\nresize_shorter\nresize_longer");
+    if (resize_longer && resize_shorter)
+        RB200_THROW("'resize_longer' and 'resize_shorter' cannot be passed together. They are mutually exclusive.");
+    unsigned out_w, out_h;
+    int mode;
+    if (resize_shorter) {
+        mode = ROCAL_SCALING_MODE_NOT_SMALLER;
+        out_w = out_h = resize_shorter;
+    } else if (resize_longer) {
+        mode = ROCAL_SCALING_MODE_NOT_LARGER;
+        out_w = out_h = resize_longer;
+    } else {
+        mode = scaling_mode;
+        out_w = dest_w;
+        out_h = dest_h;
+    }
+    if (mode == ROCAL_SCALING_MODE_MIN_MAX) RB200_THROW("ROCAL_SCALING_MODE_MIN_MAX is not supported");
+    if (max_w != 0 && max_h != 0) {
+        out_max_w = max_w;
+        out_max_h = max_h;
+    } else {
+        if (mode == ROCAL_SCALING_MODE_STRETCH) {
+            out_max_w = out_w ? out_w : (unsigned)in->max_w;
+            out_max_h = out_h ? out_h : (unsigned)in->max_h;
+        } else if (mode == ROCAL_SCALING_MODE_NOT_SMALLER) {
+            out_max_w = (out_w ? out_w : out_h) * kMaxAspectRatio;
+            out_max_h = (out_h ? out_h : out_w) * kMaxAspectRatio;
+        } else {
+            out_max_w = out_w ? out_w : out_h * kMaxAspectRatio;
+            out_max_h = out_h ? out_h : out_w * kMaxAspectRatio;
+        }
+        if (max_w) out_max_w = max_w;
+        if (max_h) out_max_h = max_h;
+    }
+    nd.dest_w = out_w;
+    nd.dest_h = out_h;
+    nd.scaling_mode = mode;
+    nd.max_w = max_w;
+    nd.max_h = max_h;
+}
+
+void check_interpolation(int interpolation) {
+    if (interpolation != ROCAL_LINEAR_INTERPOLATION)
+        RB200_THROW("only ROCAL_LINEAR_INTERPOLATION is implemented");
+}
+
+rb200_tensor finish(Pipeline* p, Node&& nd, TensorImpl* in, unsigned w, unsigned h, int lay, int dt, int is_output) {
+    return static_cast<rocalTensor*>(
+        p->add_node(std::move(nd), in, w, h, (RocalTensorLayout)lay, (RocalTensorOutputType)dt, is_output != 0));
+}
+
+// ---- DLPack (v0 ABI) ----
+struct DLDevice { int32_t device_type; int32_t device_id; };
+struct DLDataType { uint8_t code; uint8_t bits; uint16_t lanes; };
+struct DLTensor { void* data; DLDevice device; int32_t ndim; DLDataType dtype; int64_t* shape; int64_t* strides; uint64_t byte_offset; };
+struct DLManagedTensor { DLTensor dl_tensor; void* manager_ctx; void (*deleter)(DLManagedTensor*); };
+void dl_deleter(DLManagedTensor* m) {
+    if (!m) return;
+    delete[] m->dl_tensor.shape;
+    delete[] m->dl_tensor.strides;
+    delete m;
+}
+
+}  // namespace
+
+extern "C" {
+
+rb200_context rb200_create(size_t batch_size, int affinity, int gpu_id, size_t cpu_thread_count,
+                           size_t prefetch_queue_depth, int output_tensor_data_type) {
+    (void)cpu_thread_count;
+    try {
+        if (affinity != ROCAL_PROCESS_GPU)
+            RB200_THROW("this library has no CPU backend: create the context with ROCAL_PROCESS_GPU");
+        auto* p = new Pipeline(batch_size, gpu_id, prefetch_queue_depth, (RocalTensorOutputType)output_tensor_data_type);
+        // MasterGraph's constructor seeds the parameter factory with 0 (master_graph.cpp:186).
+        ParameterFactory::instance().set_seed(0);
+        return p;
+    } catch (const std::exception& e) {
+        std::cerr << "rocalCreate: " << e.what() << '\n';
+        return nullptr;
+    }
+}
+
+int rb200_verify(rb200_context ctx) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->verify();
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_run(rb200_context ctx) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->run();
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_release(rb200_context ctx) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        delete P(ctx);
+    } catch (const std::exception& e) {
+        std::cerr << e.what() << '\n';
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_status(rb200_context ctx) {
+    if (!ctx) return ROCAL_CONTEXT_INVALID;
+    return P(ctx)->status();
+}
+const char* rb200_get_error_message(rb200_context ctx) {
+    if (!ctx) return "Invalid rocal context";
+    return P(ctx)->error_message();
+}
+void rb200_get_timing(rb200_context ctx, unsigned long long out[4]) {
+    out[0] = out[1] = out[2] = out[3] = 0;
+    if (!ctx) return;
+    TimingInfo t = P(ctx)->timing();
+    out[0] = t.load_time; out[1] = t.decode_time; out[2] = t.process_time; out[3] = t.transfer_time;
+}
+size_t rb200_get_remaining_images(rb200_context ctx) { return ctx ? P(ctx)->remaining() : 0; }
+
+// ---- parameters ----
+void rb200_set_seed(unsigned seed) { ParameterFactory::instance().set_seed(seed); }
+unsigned rb200_get_seed(void) { return ParameterFactory::instance().get_seed(); }
+rb200_param rb200_create_int_uniform_rand(int start, int end) { return ParameterFactory::instance().create_uniform_int(start, end); }
+rb200_param rb200_create_float_uniform_rand(float start, float end) { return ParameterFactory::instance().create_uniform_float(start, end); }
+rb200_param rb200_create_int_rand(const int* values, const double* frequencies, unsigned size) {
+    if (!values || !frequencies || size == 0) return nullptr;
+    return ParameterFactory::instance().create_custom_int(values, frequencies, size);
+}
+rb200_param rb200_create_float_rand(const float* values, const double* frequencies, unsigned size) {
+    if (!values || !frequencies || size == 0) return nullptr;
+    return ParameterFactory::instance().create_custom_float(values, frequencies, size);
+}
+rb200_param rb200_create_int_parameter(int value) { return ParameterFactory::instance().create_int(value); }
+rb200_param rb200_create_float_parameter(float value) { return ParameterFactory::instance().create_float(value); }
+int rb200_update_int_parameter(int value, rb200_param p) {
+    if (!p || !ParameterFactory::instance().owns(p)) return ROCAL_UPDATE_PARAMETER_FAILED;
+    if (IP(p)->kind != ParamKind::DETERMINISTIC) return ROCAL_INVALID_PARAMETER_TYPE;
+    static_cast<SimpleParameter<int>*>(IP(p)->core)->update(value);
+    return ROCAL_OK;
+}
+int rb200_update_float_parameter(float value, rb200_param p) {
+    if (!p || !ParameterFactory::instance().owns(p)) return ROCAL_UPDATE_PARAMETER_FAILED;
+    if (FP(p)->kind != ParamKind::DETERMINISTIC) return ROCAL_INVALID_PARAMETER_TYPE;
+    static_cast<SimpleParameter<float>*>(FP(p)->core)->update(value);
+    return ROCAL_OK;
+}
+int rb200_update_int_uniform_rand(int start, int end, rb200_param p) {
+    if (!p || !ParameterFactory::instance().owns(p)) return ROCAL_UPDATE_PARAMETER_FAILED;
+    if (IP(p)->kind != ParamKind::RANDOM_UNIFORM) return ROCAL_INVALID_PARAMETER_TYPE;
+    static_cast<UniformRand<int>*>(IP(p)->core)->update(start, end);
+    return ROCAL_OK;
+}
+int rb200_update_float_uniform_rand(float start, float end, rb200_param p) {
+    if (!p || !ParameterFactory::instance().owns(p)) return ROCAL_UPDATE_PARAMETER_FAILED;
+    if (FP(p)->kind != ParamKind::RANDOM_UNIFORM) return ROCAL_INVALID_PARAMETER_TYPE;
+    static_cast<UniformRand<float>*>(FP(p)->core)->update(start, end);
+    return ROCAL_OK;
+}
+int rb200_get_int_value(rb200_param p) { return p ? IP(p)->core->get() : 0; }
+float rb200_get_float_value(rb200_param p) { return p ? FP(p)->core->get() : 0.f; }
+
+// ---- input ----
+rb200_tensor rb200_external_source(rb200_context ctx, int color_format, int is_output, unsigned max_width,
+                                   unsigned max_height, int external_source_mode) {
+    CTX_OR(nullptr);
+    try {
+        if (external_source_mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED)
+            RB200_THROW("only ROCAL_EXTSOURCE_RAW_UNCOMPRESSED input is supported (image decoding is not part of this library)");
+        if (color_format != ROCAL_COLOR_RGB24 && color_format != ROCAL_COLOR_BGR24)
+            RB200_THROW("only 3-channel interleaved colour formats are supported");
+        return static_cast<rocalTensor*>(P(ctx)->add_source(max_width, max_height, is_output != 0));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return nullptr;
+    }
+}
+
+int rb200_feed_input(rb200_context ctx, const unsigned char* const* buffers, const unsigned* roi_xywh, size_t n,
+                     unsigned max_width, unsigned max_height, unsigned channels, int mode, int layout, int eos) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    (void)eos;
+    try {
+        if (mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED) RB200_THROW("only ROCAL_EXTSOURCE_RAW_UNCOMPRESSED input is supported");
+        if (channels != 3) RB200_THROW("only 3-channel input is supported");
+        if (layout != ROCAL_NHWC) RB200_THROW("raw input must be NHWC");
+        if (!buffers || !roi_xywh) RB200_THROW("null input buffers or ROI");
+        InputBatch b;
+        b.kind = InputBatch::SLOTS;
+        b.n = n;
+        b.bufs.assign(buffers, buffers + n);
+        b.roi.assign(roi_xywh, roi_xywh + n * 4);
+        b.max_w = max_width;
+        b.max_h = max_height;
+        P(ctx)->feed(std::move(b));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes, const rb200_image_desc* descs, size_t n,
+                      int mem_kind) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!descs) RB200_THROW("null image descriptors");
+        if (mem_kind < RB200_MEM_HOST || mem_kind > RB200_MEM_DEVICE) RB200_THROW("bad mem_kind");
+        InputBatch b;
+        b.kind = InputBatch::RAGGED;
+        b.n = n;
+        b.arena = arena;
+        b.arena_bytes = arena_bytes;
+        b.mem_kind = mem_kind;
+        b.descs.assign(descs, descs + n);
+        P(ctx)->feed(std::move(b));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!ltrb || !labels || !counts) RB200_THROW("null box arrays");
+        P(ctx)->stage_boxes(ltrb, labels, counts, n);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_set_crop_anchors(rb200_context ctx, rb200_tensor t, const float* ax, const float* ay, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!t || !ax || !ay) RB200_THROW("null argument");
+        P(ctx)->stage_anchors(T(t), ax, ay, n);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_set_affine(rb200_context ctx, rb200_tensor t, const float* m6, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!t || !m6) RB200_THROW("null argument");
+        P(ctx)->stage_affine(T(t), m6, n);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+// ---- augmentations ----
+#define API_BEGIN     \
+    CTX_OR(nullptr);  \
+    IN_OR_NULL;       \
+    Pipeline* p = P(ctx); \
+    try {
+#define API_END                        \
+    }                                  \
+    catch (const std::exception& e) {  \
+        report(p, e);                  \
+        return nullptr;                \
+    }
+
+rb200_tensor rb200_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height, int is_output,
+                          int scaling_mode, unsigned max_w, unsigned max_h, unsigned resize_shorter,
+                          unsigned resize_longer, int interpolation, int out_layout, int out_dtype) {
+    API_BEGIN
+    check_interpolation(interpolation);
+    Node nd;
+    nd.kind = NodeKind::RESIZE;
+    unsigned mw, mh;
+    resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh);
+    return finish(p, std::move(nd), T(in), mw, mh, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_resize_mirror_normalize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                           const float* mean, const float* std_dev, size_t n_mean, int is_output,
+                                           int scaling_mode, unsigned max_w, unsigned max_h, unsigned resize_shorter,
+                                           unsigned resize_longer, int interpolation, rb200_param mirror, int out_layout,
+                                           int out_dtype) {
+    API_BEGIN
+    check_interpolation(interpolation);
+    Node nd;
+    nd.kind = NodeKind::RESIZE_MIRROR_NORMALIZE;
+    unsigned mw, mh;
+    resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh);
+    set_normalize(nd, mean, std_dev, n_mean);
+    nd.mirror = int_param(mirror, 0, 1);
+    return finish(p, std::move(nd), T(in), mw, mh, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_crop_mirror_normalize(rb200_context ctx, rb200_tensor in, unsigned crop_height, unsigned crop_width,
+                                         float start_x, float start_y, const float* mean, const float* std_dev,
+                                         size_t n_mean, int is_output, rb200_param mirror, int out_layout, int out_dtype) {
+    API_BEGIN
+    if (crop_width == 0 || crop_height == 0) RB200_THROW("Null values passed as input");
+    Node nd;
+    nd.kind = NodeKind::CROP_MIRROR_NORMALIZE;
+    nd.crop.mode = CropSpec::FIXED_ANCHOR;
+    nd.crop.crop_w = crop_width;
+    nd.crop.crop_h = crop_height;
+    nd.crop.anchor_x = start_x;
+    nd.crop.anchor_y = start_y;
+    set_normalize(nd, mean, std_dev, n_mean);
+    nd.mirror = int_param(mirror, 0, 1);
+    return finish(p, std::move(nd), T(in), crop_width, crop_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200_param crop_width, rb200_param crop_height,
+                        rb200_param crop_pos_x, rb200_param crop_pos_y, int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::CROP;
+    nd.crop.mode = CropSpec::RANDOM;
+    nd.crop.w_factor = float_param(crop_width, 0.55f, 0.95f);
+    nd.crop.h_factor = float_param(crop_height, 0.55f, 0.95f);
+    nd.crop.x_drift = float_param(crop_pos_x, 0.01f, 0.99f);
+    nd.crop.y_drift = float_param(crop_pos_y, 0.01f, 0.99f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_crop_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width, unsigned crop_height, int is_output,
+                              float crop_pos_x, float crop_pos_y, int out_layout, int out_dtype) {
+    API_BEGIN
+    if (crop_width == 0 || crop_height == 0) RB200_THROW("Crop node needs to receive non-zero destination dimensions");
+    Node nd;
+    nd.kind = NodeKind::CROP;
+    nd.crop.mode = CropSpec::ABSOLUTE;
+    nd.crop.crop_w = crop_width;
+    nd.crop.crop_h = crop_height;
+    nd.crop.x1 = (unsigned)crop_pos_x;
+    nd.crop.y1 = (unsigned)crop_pos_y;
+    return finish(p, std::move(nd), T(in), crop_width, crop_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_crop_center_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width, unsigned crop_height,
+                                     int is_output, int out_layout, int out_dtype) {
+    API_BEGIN
+    if (crop_width == 0 || crop_height == 0) RB200_THROW("Crop node needs to receive non-zero destination dimensions");
+    Node nd;
+    nd.kind = NodeKind::CROP;
+    nd.crop.mode = CropSpec::FIXED_ANCHOR;
+    nd.crop.crop_w = crop_width;
+    nd.crop.crop_h = crop_height;
+    nd.crop.anchor_x = 0.5f;
+    nd.crop.anchor_y = 0.5f;
+    return finish(p, std::move(nd), T(in), crop_width, crop_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_resize_crop_mirror_fixed(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                            int is_output, unsigned crop_h, unsigned crop_w, rb200_param mirror,
+                                            int out_layout, int out_dtype) {
+    API_BEGIN
+    if (dest_width == 0 || dest_height == 0) RB200_THROW("Crop Mirror node needs tp receive non-zero destination dimensions");
+    Node nd;
+    nd.kind = NodeKind::RESIZE_CROP_MIRROR;
+    nd.dest_w = dest_width;
+    nd.dest_h = dest_height;
+    nd.crop.mode = CropSpec::ABSOLUTE;
+    nd.crop.crop_w = crop_w;
+    nd.crop.crop_h = crop_h;
+    nd.mirror = int_param(mirror, 0, 1);
+    return finish(p, std::move(nd), T(in), dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_resize_crop_mirror(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                      int is_output, rb200_param crop_height, rb200_param crop_width, rb200_param mirror,
+                                      int out_layout, int out_dtype) {
+    API_BEGIN
+    if (dest_width == 0 || dest_height == 0) RB200_THROW("Crop Mirror node needs tp receive non-zero destination dimensions");
+    Node nd;
+    nd.kind = NodeKind::RESIZE_CROP_MIRROR;
+    nd.dest_w = dest_width;
+    nd.dest_h = dest_height;
+    nd.crop.mode = CropSpec::RANDOM;
+    nd.crop.h_factor = float_param(crop_height, 0.55f, 0.95f);
+    nd.crop.w_factor = float_param(crop_width, 0.55f, 0.95f);
+    nd.crop.x_drift = float_param(nullptr, 0.01f, 0.99f);
+    nd.crop.y_drift = float_param(nullptr, 0.01f, 0.99f);
+    nd.mirror = int_param(mirror, 0, 1);
+    return finish(p, std::move(nd), T(in), dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_ssd_random_crop(rb200_context ctx, rb200_tensor in, int is_output, int num_of_attempts, int out_layout,
+                                   int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::SSD_RANDOM_CROP;
+    nd.ssd_attempts = num_of_attempts > 0 ? num_of_attempts : 20;
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_flip(rb200_context ctx, rb200_tensor in, int is_output, rb200_param horizontal, rb200_param vertical,
+                        int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::FLIP;
+    nd.flip_h = int_param(horizontal, 0, 1);
+    nd.flip_v = int_param(vertical, 0, 1);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+// Default ranges: include/augmentations/color_augmentations/node_*.h (ALPHA_RANGE, BETA_RANGE, ...).
+rb200_tensor rb200_brightness(rb200_context ctx, rb200_tensor in, int is_output, rb200_param alpha, rb200_param beta,
+                              int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::BRIGHTNESS;
+    nd.color[0] = float_param(alpha, 0.1f, 1.95f);
+    nd.color[1] = float_param(beta, 0.f, 25.f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_contrast(rb200_context ctx, rb200_tensor in, int is_output, rb200_param factor, rb200_param center,
+                            int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::CONTRAST;
+    nd.color[0] = float_param(factor, 0.1f, 1.95f);
+    nd.color[1] = float_param(center, 60.f, 90.f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::HUE;
+    nd.color[2] = float_param(hue, -359.0f, 359.0f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_saturation(rb200_context ctx, rb200_tensor in, int is_output, rb200_param sat, int out_layout,
+                              int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::SATURATION;
+    nd.color[3] = float_param(sat, -0.5f, 0.5f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_color_twist(rb200_context ctx, rb200_tensor in, int is_output, rb200_param alpha, rb200_param beta,
+                               rb200_param hue, rb200_param sat, int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::COLOR_TWIST;
+    nd.color[0] = float_param(alpha, 0.1f, 1.95f);
+    nd.color[1] = float_param(beta, 0.1f, 25.0f);
+    nd.color[2] = float_param(hue, 5.0f, 170.0f);
+    nd.color[3] = float_param(sat, 0.1f, 0.4f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_warp_affine(rb200_context ctx, rb200_tensor in, int is_output, unsigned dest_height, unsigned dest_width,
+                               rb200_param x0, rb200_param x1, rb200_param y0, rb200_param y1, rb200_param o0,
+                               rb200_param o1, int interpolation, int out_layout, int out_dtype) {
+    API_BEGIN
+    check_interpolation(interpolation);
+    if (dest_width == 0 || dest_height == 0) {
+        dest_width = (unsigned)T(in)->max_w;
+        dest_height = (unsigned)T(in)->max_h;
+    }
+    Node nd;
+    nd.kind = NodeKind::WARP_AFFINE;
+    // COEFFICIENT_RANGE_1 for x0/y1, _0 for x1/y0, _OFFSET for o0/o1 (node_warp_affine.h:50-52, .cpp:30-35)
+    nd.affine[0] = float_param(x0, 0.65f, 1.35f);
+    nd.affine[1] = float_param(x1, -0.35f, 0.35f);
+    nd.affine[2] = float_param(y0, -0.35f, 0.35f);
+    nd.affine[3] = float_param(y1, 0.65f, 1.35f);
+    nd.affine[4] = float_param(o0, -10.0f, 10.0f);
+    nd.affine[5] = float_param(o1, -10.0f, 10.0f);
+    return finish(p, std::move(nd), T(in), dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_rotate(rb200_context ctx, rb200_tensor in, int is_output, rb200_param angle, unsigned dest_width,
+                          unsigned dest_height, int interpolation, int out_layout, int out_dtype) {
+    API_BEGIN
+    check_interpolation(interpolation);
+    if (dest_width == 0 || dest_height == 0) {
+        dest_width = (unsigned)T(in)->max_w;
+        dest_height = (unsigned)T(in)->max_h;
+    }
+    Node nd;
+    nd.kind = NodeKind::ROTATE;
+    nd.angle = float_param(angle, 0.f, 180.f);   // ROTATE_ANGLE_RANGE, node_rotate.h:47
+    return finish(p, std::move(nd), T(in), dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+// ---- outputs ----
+int rb200_set_outputs(rb200_context ctx, const rb200_tensor* tensors, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (P(ctx)->verified()) RB200_THROW("outputs must be set before rocalVerify");
+        for (size_t i = 0; i < n; i++) {
+            if (!tensors || !tensors[i] || !P(ctx)->owns(T(tensors[i]))) RB200_THROW("rocalSetOutputs: not a tensor of this context");
+            T(tensors[i])->is_output = true;
+        }
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+size_t rb200_output_count(rb200_context ctx) { return ctx ? (size_t)P(ctx)->outputs()->size() : 0; }
+rb200_tensor rb200_output(rb200_context ctx, size_t index) { return ctx ? P(ctx)->outputs()->at(index) : nullptr; }
+void* rb200_tensor_buffer(rb200_tensor t) { return t ? T(t)->buffer() : nullptr; }
+unsigned rb200_tensor_num_dims(rb200_tensor t) { return t ? T(t)->num_of_dims() : 0; }
+void rb200_tensor_dims(rb200_tensor t, size_t* out) {
+    if (!t) return;
+    auto d = T(t)->dims();
+    std::copy(d.begin(), d.end(), out);
+}
+void rb200_tensor_strides(rb200_tensor t, size_t* out) {
+    if (!t) return;
+    auto d = T(t)->strides();
+    std::copy(d.begin(), d.end(), out);
+}
+int rb200_tensor_layout(rb200_tensor t) { return t ? (int)T(t)->layout() : -1; }
+int rb200_tensor_dtype(rb200_tensor t) { return t ? (int)T(t)->data_type() : -1; }
+size_t rb200_tensor_data_size(rb200_tensor t) { return t ? T(t)->data_size() : 0; }
+unsigned rb200_tensor_copy_data(rb200_tensor t, void* user_buffer, int mem_type) {
+    return t ? T(t)->copy_data(user_buffer, (RocalOutputMemType)mem_type) : 1;
+}
+void rb200_tensor_copy_roi(rb200_tensor t, void* roi_buffer) {
+    if (t && roi_buffer) T(t)->copy_roi(roi_buffer);
+}
+
+void* rb200_tensor_dlpack(rb200_tensor t) {
+    if (!t || !T(t)->buffer()) return nullptr;
+    TensorImpl* x = T(t);
+    auto* m = new DLManagedTensor();
+    auto dims = x->dims();
+    auto strides = x->strides();
+    size_t e = x->elem_size();
+    m->dl_tensor.data = x->buffer();
+    m->dl_tensor.device = {2 /* kDLCUDA */, x->pipe->gpu_id()};
+    m->dl_tensor.ndim = (int32_t)dims.size();
+    uint8_t code = (x->dtype == ROCAL_FP32 || x->dtype == ROCAL_FP16) ? 2 /* float */
+                   : (x->dtype == ROCAL_UINT8 || x->dtype == ROCAL_UINT32) ? 1 /* uint */ : 0 /* int */;
+    m->dl_tensor.dtype = {code, (uint8_t)(e * 8), 1};
+    m->dl_tensor.shape = new int64_t[dims.size()];
+    m->dl_tensor.strides = new int64_t[dims.size()];
+    for (size_t k = 0; k < dims.size(); k++) {
+        m->dl_tensor.shape[k] = (int64_t)dims[k];
+        m->dl_tensor.strides[k] = (int64_t)(strides[k] / e);
+    }
+    m->dl_tensor.byte_offset = 0;
+    m->manager_ctx = nullptr;
+    m->deleter = dl_deleter;
+    return m;
+}
+
+int rb200_device_id(rb200_context ctx) { return ctx ? P(ctx)->gpu_id() : -1; }
+void* rb200_stream(rb200_context ctx) { return ctx ? (void*)P(ctx)->stream() : nullptr; }
+
+int rb200_to_tensor(rb200_context ctx, void* out_ptr, int layout, int dtype, const float* multiplier3, const float* offset3,
+                    int reverse_channels, int output_mem_type) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!out_ptr || !multiplier3 || !offset3) RB200_THROW("null argument");
+        P(ctx)->to_tensor(out_ptr, layout, dtype, multiplier3, offset3, reverse_channels != 0, output_mem_type);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+// ---- box encoder ----
+int rb200_box_encoder(rb200_context ctx, const float* anchors_ltrb, size_t num_anchors, float criteria, const float* means4,
+                      const float* stds4, int offset, float scale) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!means4 || !stds4) RB200_THROW("means and stds must hold 4 values");
+        P(ctx)->set_box_encoder(anchors_ltrb, num_anchors, criteria, means4, stds4, offset != 0, scale);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_copy_encoded_boxes_and_labels(rb200_context ctx, float* boxes_buf, int* labels_buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!boxes_buf || !labels_buf) RB200_THROW("null output buffer");
+        P(ctx)->copy_encoded(boxes_buf, labels_buf);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_encoded_boxes_and_labels(rb200_context ctx, float** boxes_dev, int** labels_dev, size_t* num_anchors) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->encoded(boxes_dev, labels_dev, num_anchors);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+size_t rb200_get_bounding_boxes(rb200_context ctx, float* ltrb, int* labels, int* counts) {
+    CTX_OR(0);
+    try {
+        std::vector<float> b;
+        std::vector<int> l, c;
+        P(ctx)->current_boxes(b, l, c);
+        if (ltrb) std::memcpy(ltrb, b.data(), b.size() * sizeof(float));
+        if (labels) std::memcpy(labels, l.data(), l.size() * sizeof(int));
+        if (counts) std::memcpy(counts, c.data(), c.size() * sizeof(int));
+        return l.size();
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return 0;
+    }
+}
+
+int rb200_get_crop_windows(rb200_context ctx, rb200_tensor t, unsigned* xywh) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!t || !xywh) RB200_THROW("null argument");
+        P(ctx)->crop_windows(T(t), xywh);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+size_t rb200_get_int_array(rb200_param p, int* out, size_t n) {
+    if (!p || !out || !ParameterFactory::instance().owns(p)) return 0;
+    const auto& a = IP(p)->core->array();
+    size_t k = std::min(n, a.size());
+    std::copy(a.begin(), a.begin() + k, out);
+    return k;
+}
+
+size_t rb200_get_float_array(rb200_param p, float* out, size_t n) {
+    if (!p || !out || !ParameterFactory::instance().owns(p)) return 0;
+    const auto& a = FP(p)->core->array();
+    size_t k = std::min(n, a.size());
+    std::copy(a.begin(), a.begin() + k, out);
+    return k;
+}
+
+}  // extern "C"

@@ -39,6 +39,8 @@ struct ResampleLaunch {
     int pair_ok;        // paired (2-element) stores are aligned
     int normalize, fill_padding;
     float mul[3], add[3];
+    uint32_t magic;     // 0x4B000000 (bits of 2^23), passed as a parameter so that PRMT reads it
+                        // from the constant bank instead of a re-materialised register
 };
 
 struct RowInfo {
@@ -99,9 +101,9 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     return *reinterpret_cast<float2*>(&rd);
 }
 
-// Byte `sel & 7` of (w, 0x4B000000) placed in the mantissa of 2^23: the float 8388608 + byte.
-__device__ __forceinline__ float byte_magic(uint32_t w, uint32_t sel) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, sel));
+// Byte `sel & 7` of (w, magic = 0x4B000000) placed in the mantissa of 2^23: the float 8388608 + byte.
+__device__ __forceinline__ float byte_magic(uint32_t w, uint32_t magic, uint32_t sel) {
+    return __uint_as_float(__byte_perm(w, magic, sel));
 }
 
 // One column's taps of one source row: words L (bytes b..b+3) and R (bytes b+4..b+7).
@@ -157,8 +159,8 @@ struct StagedRow {
 template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED>
 __device__ __forceinline__ void staged_rows(const uint8_t* stage, const StagedRow* rows, int j_begin, int j_end,
                                             const ColumnTaps (&ct)[2], float2 wx2, float2 owx2, bool second,
-                                            const float (&mulv)[3], const float (&addv)[3], OutT* po, size_t row_step,
-                                            size_t plane) {
+                                            const float (&mulv)[3], const float (&addv)[3], const uint32_t magic,
+                                            OutT* po, size_t row_step, size_t plane) {
     const float2 neg_magic = make_float2(-8388608.0f, -8388608.0f);
     const float2 rnd = make_float2(12582912.0f, 12582912.0f);
     const float2 neg_rnd = make_float2(-12582912.0f, -12582912.0f);
@@ -179,19 +181,19 @@ __device__ __forceinline__ void staged_rows(const uint8_t* stage, const StagedRo
 #pragma unroll
         for (int c = 0; c < 3; c++) {
             const uint32_t sel_l = 0x7650u + c;
-            float2 tl = make_float2(byte_magic(l0[0], sel_l), byte_magic(l0[1], sel_l));
-            float2 bl = make_float2(byte_magic(l1[0], sel_l), byte_magic(l1[1], sel_l));
+            float2 tl = make_float2(byte_magic(l0[0], magic, sel_l), byte_magic(l0[1], magic, sel_l));
+            float2 bl = make_float2(byte_magic(l1[0], magic, sel_l), byte_magic(l1[1], magic, sel_l));
             float2 tr, br;
             // right tap: its red byte sits in the left word unless the taps coincide
             if (c == 0) {
-                tr = make_float2(byte_magic(l0[0], ct[0].sel_r), byte_magic(l0[1], ct[1].sel_r));
-                br = make_float2(byte_magic(l1[0], ct[0].sel_r), byte_magic(l1[1], ct[1].sel_r));
+                tr = make_float2(byte_magic(l0[0], magic, ct[0].sel_r), byte_magic(l0[1], magic, ct[1].sel_r));
+                br = make_float2(byte_magic(l1[0], magic, ct[0].sel_r), byte_magic(l1[1], magic, ct[1].sel_r));
             } else if (c == 1) {
-                tr = make_float2(byte_magic(r0[0], ct[0].sel_g), byte_magic(r0[1], ct[1].sel_g));
-                br = make_float2(byte_magic(r1[0], ct[0].sel_g), byte_magic(r1[1], ct[1].sel_g));
+                tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_g), byte_magic(r0[1], magic, ct[1].sel_g));
+                br = make_float2(byte_magic(r1[0], magic, ct[0].sel_g), byte_magic(r1[1], magic, ct[1].sel_g));
             } else {
-                tr = make_float2(byte_magic(r0[0], ct[0].sel_b), byte_magic(r0[1], ct[1].sel_b));
-                br = make_float2(byte_magic(r1[0], ct[0].sel_b), byte_magic(r1[1], ct[1].sel_b));
+                tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_b), byte_magic(r0[1], magic, ct[1].sel_b));
+                br = make_float2(byte_magic(r1[0], magic, ct[0].sel_b), byte_magic(r1[1], magic, ct[1].sel_b));
             }
             tl = add2(tl, neg_magic);
             tr = add2(tr, neg_magic);
@@ -383,9 +385,9 @@ __global__ void __launch_bounds__(256) resample_staged_kernel(const uint8_t* __r
             const size_t row_step = LAYOUT == RB200_NCHW ? (size_t)L.out_w : (size_t)L.out_w * 3;
             const int j_end = min(j_begin + rpg, rows_valid);
             if (second && L.pair_ok)
-                staged_rows<OutT, LAYOUT, NORMALIZE, true>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, po, row_step, plane);
+                staged_rows<OutT, LAYOUT, NORMALIZE, true>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, L.magic, po, row_step, plane);
             else
-                staged_rows<OutT, LAYOUT, NORMALIZE, false>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, po, row_step, plane);
+                staged_rows<OutT, LAYOUT, NORMALIZE, false>(stage, rows, j_begin, j_end, ct, wx2, owx2, second, L.mul, L.add, L.magic, po, row_step, plane);
         }
     }
 
@@ -540,6 +542,7 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     L.normalize = p->normalize;
     L.fill_padding = p->fill_padding;
     L.pair_ok = 0;
+    L.magic = 0x4B000000u;
     for (int c = 0; c < 3; c++) { L.mul[c] = p->mul[c]; L.add[c] = p->add[c]; }
 
     // Extent the grid has to cover.

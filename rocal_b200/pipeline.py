@@ -1,0 +1,304 @@
+"""Python face of the pipeline, shaped like amd.rocal.pipeline.Pipeline
+(rocAL_pybind/amd/rocal/pipeline.py:34-273) for the supported subset.
+
+    pipe = Pipeline(batch_size=64, device_id=0, seed=0)
+    with pipe:
+        img = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=512, max_height=512)[0]
+        r = fn.resize(img, resize_shorter=256)
+        out = fn.crop_mirror_normalize(r, crop=[224, 224], mean=..., std=..., mirror=fn.random.coin_flip(),
+                                       output_layout=types.NCHW, output_dtype=types.FLOAT)
+        pipe.set_outputs(out)
+    pipe.build()
+    pipe.feed_ragged(arena, heights, widths, offsets)      # or pipe.feed_input(list_of_hwc_arrays)
+    pipe.run()
+    tensors = pipe.get_output_tensors()                     # list of RocalTensor (DLPack capable)
+"""
+import ctypes
+
+import numpy as np
+
+from . import _capi as C
+from . import types
+
+
+class RocalError(RuntimeError):
+    pass
+
+
+class RocalTensor:
+    """Output tensor handle: device memory owned by the pipeline, valid until the next run()."""
+
+    def __init__(self, pipe, handle):
+        self._pipe, self._h = pipe, handle
+
+    def dims(self):
+        n = C.tensor_num_dims(self._h)
+        buf = (ctypes.c_size_t * n)()
+        C.tensor_dims(self._h, buf)
+        return list(buf)
+
+    def strides(self):
+        n = C.tensor_num_dims(self._h)
+        buf = (ctypes.c_size_t * n)()
+        C.tensor_strides(self._h, buf)
+        return list(buf)
+
+    def layout(self):
+        return C.tensor_layout(self._h)
+
+    def dtype(self):
+        return C.tensor_dtype(self._h)
+
+    def data_size(self):
+        return C.tensor_data_size(self._h)
+
+    def buffer(self):
+        return C.tensor_buffer(self._h)
+
+    def roi(self):
+        n = self.dims()[0]
+        out = np.zeros((n, 4), dtype=np.uint32)
+        C.tensor_copy_roi(self._h, out.ctypes.data_as(ctypes.c_void_p))
+        return out
+
+    def copy_data(self, dst, mem_type=types.HOST_MEMORY):
+        """dst: integer address / ctypes pointer of a buffer of data_size() bytes."""
+        ptr = dst if isinstance(dst, int) else ctypes.cast(dst, ctypes.c_void_p).value
+        if C.tensor_copy_data(self._h, ctypes.c_void_p(ptr), mem_type):
+            raise RocalError(self._pipe.error_message())
+
+    def numpy(self):
+        np_dt = {types.FLOAT: np.float32, types.FLOAT16: np.float16, types.UINT8: np.uint8, types.INT32: np.int32}[self.dtype()]
+        out = np.empty(self.dims(), dtype=np_dt)
+        self.copy_data(out.ctypes.data)
+        return out
+
+    def __dlpack_device__(self):
+        return (2, C.device_id(self._pipe._handle))   # kDLCUDA
+
+    def __dlpack__(self, stream=None, **_):
+        """Zero-copy export. The batch is complete when run() returns, so no stream hand-off is needed."""
+        m = C.tensor_dlpack(self._h)
+        if not m:
+            raise RocalError("no batch is available yet (call run() first)")
+        ctypes.pythonapi.PyCapsule_New.restype = ctypes.py_object
+        ctypes.pythonapi.PyCapsule_New.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+        return ctypes.pythonapi.PyCapsule_New(m, b"dltensor", None)
+
+
+class Pipeline(object):
+    _current_pipeline = None
+
+    def __init__(self, batch_size=-1, num_threads=0, device_id=0, seed=1, exec_pipelined=True, prefetch_queue_depth=2,
+                 exec_async=True, bytes_per_sample=0, rocal_cpu=False, max_streams=-1, default_cuda_stream_priority=0,
+                 tensor_layout=types.NCHW, reverse_channels=False, mean=None, std=None, tensor_dtype=types.FLOAT,
+                 output_memory_type=None):
+        if rocal_cpu:
+            raise RocalError("this library has no CPU backend (rocal_cpu must be False)")
+        self._handle = C.create(batch_size, types.GPU, device_id, max(1, num_threads), prefetch_queue_depth, tensor_dtype)
+        if not self._handle:
+            raise RocalError("Failed creating the pipeline")
+        self._batch_size = batch_size
+        self._device_id = device_id
+        self._tensor_layout = tensor_layout
+        self._tensor_dtype = tensor_dtype
+        self._multiplier = [1.0 / x for x in std] if std else [1.0, 1.0, 1.0]
+        self._offset = [-(m / s) for m, s in zip(mean, std)] if mean and std else [0.0, 0.0, 0.0]
+        self._reverse_channels = reverse_channels
+        self._outputs = []
+        self._keepalive = []
+        self._box_encoder = False
+        self._num_anchors = 0
+        self._external_source_mode = None
+        self._max_w = self._max_h = 0
+        self.set_seed(seed)
+
+    # ---- graph ----
+    def __enter__(self):
+        Pipeline._current_pipeline = self
+        return self
+
+    def __exit__(self, *exc):
+        Pipeline._current_pipeline = None
+
+    def get_handle(self):
+        return self._handle
+
+    def set_seed(self, seed=0):
+        C.set_seed(seed)
+
+    def set_outputs(self, *output_list):
+        self._outputs = list(output_list)
+
+    def build(self):
+        if self._outputs:
+            arr = (ctypes.c_void_p * len(self._outputs))(*self._outputs)
+            self._check(C.set_outputs(self._handle, arr, len(self._outputs)))
+        self._check(C.verify(self._handle))
+        return self
+
+    # ---- parameters (Pipeline.create_int_param ... pipeline.py:173-193) ----
+    def create_int_param(self, value=1):
+        return C.Param(C.create_int_parameter(value), True)
+
+    def create_float_param(self, value=1):
+        return C.Param(C.create_float_parameter(value), False)
+
+    def update_int_param(self, value=1, param=1):
+        return C.update_int_parameter(value, param)
+
+    def update_float_param(self, value=1, param=1):
+        return C.update_float_parameter(value, param)
+
+    def get_int_value(self, param):
+        return C.get_int_value(param)
+
+    def get_float_value(self, param):
+        return C.get_float_value(param)
+
+    # ---- input ----
+    def feed_input(self, images):
+        """The reference's external-source contract: a list of HWC uint8 arrays, each copied into a
+        max_height x max_width slot (Pipeline/external source mode RAW_UNCOMPRESSED)."""
+        n = len(images)
+        slots = np.zeros((n, self._max_h, self._max_w, 3), dtype=np.uint8)
+        roi = np.zeros((n, 4), dtype=np.uint32)
+        for i, im in enumerate(images):
+            h, w = im.shape[:2]
+            slots[i, :h, :w] = im
+            roi[i] = (0, 0, w, h)
+        ptrs = (ctypes.c_void_p * n)(*[slots[i].ctypes.data for i in range(n)])
+        self._keepalive.append((slots, roi, ptrs))
+        self._check(C.feed_input(self._handle, ptrs, roi.ctypes.data_as(ctypes.POINTER(ctypes.c_uint)), n, self._max_w,
+                                 self._max_h, 3, types.EXTSOURCE_RAW_UNCOMPRESSED, types.NHWC, 0))
+
+    def feed_ragged(self, arena, heights, widths, offsets, strides=None, mem_kind=None):
+        """[extension] One packed arena (numpy array, torch tensor — host, pinned or CUDA) + per-image sizes."""
+        n = len(heights)
+        descs = (C.ImageDesc * n)()
+        for i in range(n):
+            descs[i].offset = int(offsets[i])
+            descs[i].stride = int(strides[i]) if strides is not None else int(widths[i]) * 3
+            descs[i].width = int(widths[i])
+            descs[i].height = int(heights[i])
+        if isinstance(arena, np.ndarray):
+            ptr, nbytes, kind = arena.ctypes.data, arena.nbytes, C.MEM_HOST
+        else:   # torch tensor
+            ptr, nbytes = arena.data_ptr(), arena.numel() * arena.element_size()
+            kind = C.MEM_DEVICE if arena.is_cuda else (C.MEM_HOST_PINNED if arena.is_pinned() else C.MEM_HOST)
+        if mem_kind is not None:
+            kind = mem_kind
+        self._keepalive.append((arena, descs))
+        self._check(C.feed_ragged(self._handle, ctypes.c_void_p(ptr), nbytes, descs, n, kind))
+
+    def feed_boxes(self, boxes, labels, counts):
+        """[extension] Normalized ltrb boxes, labels and per-sample counts of the next fed batch."""
+        b = np.ascontiguousarray(boxes, dtype=np.float32)
+        lab = np.ascontiguousarray(labels, dtype=np.int32)
+        c = np.ascontiguousarray(counts, dtype=np.int32)
+        self._check(C.feed_boxes(self._handle, b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                 lab.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+                                 c.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), len(c)))
+
+    def set_crop_anchors(self, cmn_output, anchor_x, anchor_y):
+        ax = np.ascontiguousarray(anchor_x, dtype=np.float32)
+        ay = np.ascontiguousarray(anchor_y, dtype=np.float32)
+        self._check(C.set_crop_anchors(self._handle, cmn_output, ax.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                       ay.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), len(ax)))
+
+    def set_affine(self, warp_output, matrices):
+        m = np.ascontiguousarray(matrices, dtype=np.float32).reshape(-1, 6)
+        self._check(C.set_affine(self._handle, warp_output, m.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), len(m)))
+
+    # ---- run / outputs ----
+    def rocal_run(self):
+        self._check(C.run(self._handle))
+        while len(self._keepalive) > 4:
+            self._keepalive.pop(0)
+        return types.OK
+
+    run = rocal_run
+
+    def get_output_tensors(self):
+        return [RocalTensor(self, C.output(self._handle, i)) for i in range(C.output_count(self._handle))]
+
+    def copyToExternalTensor(self, array, multiplier, offset, reverse_channels, tensor_format, tensor_dtype,
+                             max_roi_height=0, max_roi_width=0):
+        """rocalToTensor into a numpy array (host) or a CUDA torch tensor."""
+        mul = (ctypes.c_float * 3)(*multiplier)
+        off = (ctypes.c_float * 3)(*offset)
+        if isinstance(array, np.ndarray):
+            ptr, mem = array.ctypes.data, types.HOST_MEMORY
+        else:
+            ptr, mem = array.data_ptr(), (types.DEVICE_MEMORY if array.is_cuda else types.HOST_MEMORY)
+        self._check(C.to_tensor(self._handle, ctypes.c_void_p(ptr), tensor_format, tensor_dtype, mul, off,
+                                1 if reverse_channels else 0, mem))
+
+    def copy_encoded_boxes_and_lables(self, bbox_array, label_array):
+        self._check(C.copy_encoded_boxes_and_labels(self._handle, bbox_array.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                                    label_array.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+
+    def get_encoded_boxes_and_lables(self, batch_size=None, num_anchors=None):
+        """Returns (boxes [N, A, 4] float32, labels [N, A] int32) as numpy arrays."""
+        bp, lp, na = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_size_t()
+        self._check(C.get_encoded_boxes_and_labels(self._handle, ctypes.byref(bp), ctypes.byref(lp), ctypes.byref(na)))
+        boxes = np.empty((self._batch_size, na.value, 4), dtype=np.float32)
+        labels = np.empty((self._batch_size, na.value), dtype=np.int32)
+        self.copy_encoded_boxes_and_lables(boxes, labels)
+        return boxes, labels
+
+    def get_bounding_boxes(self):
+        """Boxes of the current batch after the graph's crops and mirrors: (ltrb [T,4], labels [T], counts [N])."""
+        total = C.get_bounding_boxes(self._handle, None, None, None)
+        b = np.zeros((total, 4), dtype=np.float32)
+        lab = np.zeros(total, dtype=np.int32)
+        c = np.zeros(self._batch_size, dtype=np.int32)
+        if total:
+            C.get_bounding_boxes(self._handle, b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                 lab.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), c.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+        return b, lab, c
+
+    def get_crop_windows(self, tensor):
+        """[extension] n x (x, y, w, h) source window used by the crop-type operator that produced `tensor`."""
+        out = np.zeros((self._batch_size, 4), dtype=np.uint32)
+        self._check(C.get_crop_windows(self._handle, tensor, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint))))
+        return out
+
+    def get_int_array(self, param):
+        out = np.zeros(self._batch_size, dtype=np.int32)
+        k = C.get_int_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), self._batch_size)
+        return out[:k]
+
+    def get_float_array(self, param):
+        out = np.zeros(self._batch_size, dtype=np.float32)
+        k = C.get_float_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), self._batch_size)
+        return out[:k]
+
+    def get_remaining_images(self):
+        return C.get_remaining_images(self._handle)
+
+    def is_empty(self):
+        return self.get_remaining_images() == 0
+
+    def timing_info(self):
+        t = (ctypes.c_ulonglong * 4)()
+        C.get_timing(self._handle, t)
+        return {"load_time": t[0], "decode_time": t[1], "process_time": t[2], "transfer_time": t[3]}
+
+    def error_message(self):
+        return C.get_error_message(self._handle).decode()
+
+    def rocal_release(self):
+        if self._handle:
+            C.release(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.rocal_release()
+        except Exception:
+            pass
+
+    def _check(self, status):
+        if status != types.OK:
+            raise RocalError(self.error_message())
