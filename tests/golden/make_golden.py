@@ -1,0 +1,75 @@
+"""Generates the golden vectors of this folder from reference-owned code (oracle/_ref/libref.so, built from
+the reference tree by oracle/build.py). Run in a container that has the reference tree:
+
+    python tests/golden/make_golden.py
+
+box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
+                  (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
+param_rng.npz     UniformRand<float>, UniformRand<int>, CustomRand<int> draws
+                  (rocAL/include/parameters/parameter_random.h) and the std::seed_seq table of
+                  ParameterFactory::set_seed (rocAL/source/parameters/parameter_factory.cpp:114-119)
+"""
+import ctypes
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from oracle import pyoracle as O          # noqa: E402
+from rocal_b200 import synthetic as S     # noqa: E402
+
+
+def main():
+    ref = O.ref()
+    assert ref is not None, "the reference tree is needed to generate golden vectors"
+    rng = np.random.Generator(np.random.PCG64(4242))
+    anchors = S.ssd300_anchors()[::9][:960].copy()
+    counts = [1, 2, 7, 33, 50, 3, 12, 1]
+    per = []
+    for c in counts:
+        b, _, _ = S.random_boxes(rng, 1, (c, c))
+        if c > 2:
+            b[c // 2] = b[0]                                   # tie between boxes
+            b[-1] = anchors[int(rng.integers(0, len(anchors)))]   # IoU 1 with an anchor
+        per.append(b)
+    boxes = np.ascontiguousarray(np.concatenate(per))
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    labels = rng.integers(1, 81, len(boxes)).astype(np.int32)
+    out = {"anchors": anchors, "boxes": boxes, "labels": labels, "offsets": offsets}
+    cases = [("offset", 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0),
+             ("plain", 0.5, (0, 0, 0, 0), (1, 1, 1, 1), False, 1.0),
+             ("scaled", 0.4, (0.05, -0.05, 0.1, 0.0), (0.1, 0.1, 0.2, 0.2), True, 2.0)]
+    for name, crit, means, stds, offset, scale in cases:
+        eb, el = O.ref_box_encode(boxes, labels, offsets, anchors, crit, means, stds, offset, scale)
+        out[name + "_boxes"], out[name + "_labels"] = eb, el
+        out[name + "_args"] = np.array([crit, *means, *stds, float(offset), scale], dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, "box_encoder.npz"), **out)
+
+    rngs = {}
+    f = np.zeros(3 * 16, dtype=np.float32)
+    ref.ref_uniform_rand_float(ctypes.c_uint(123), ctypes.c_float(0.6), ctypes.c_float(1.4), ctypes.c_uint(16), ctypes.c_uint(3),
+                               f.ctypes.data_as(ctypes.c_void_p))
+    rngs["uniform_float_seed123_0.6_1.4_b16x3"] = f
+    i = np.zeros(3 * 16, dtype=np.int32)
+    ref.ref_uniform_rand_int(ctypes.c_uint(77), ctypes.c_int(0), ctypes.c_int(10), ctypes.c_uint(16), ctypes.c_uint(3),
+                             i.ctypes.data_as(ctypes.c_void_p))
+    rngs["uniform_int_seed77_0_10_b16x3"] = i
+    vals = np.array([0, 1], dtype=np.int32)
+    fr = np.array([0.5, 0.5])
+    c = np.zeros(3 * 16, dtype=np.int32)
+    ref.ref_custom_rand_int(ctypes.c_uint(9), vals.ctypes.data_as(ctypes.c_void_p), fr.ctypes.data_as(ctypes.c_void_p),
+                            ctypes.c_uint(2), ctypes.c_uint(16), ctypes.c_uint(3), c.ctypes.data_as(ctypes.c_void_p))
+    rngs["custom_int_seed9_coin_b16x3"] = c
+    for seed in (0, 1, 1234):
+        t = np.zeros(1024, dtype=np.int64)
+        ref.ref_seed_sequence(ctypes.c_uint(seed), ctypes.c_uint(1024), t.ctypes.data_as(ctypes.c_void_p))
+        rngs["seed_seq_%d" % seed] = t
+    np.savez_compressed(os.path.join(HERE, "param_rng.npz"), **rngs)
+    print("wrote box_encoder.npz, param_rng.npz")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,87 @@
+"""The C-ABI without a GPU: the library loads, exports every symbol the headers declare, and its
+host-side parameter machinery reproduces the reference's draws (through the golden vectors)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def _declared_symbols():
+    names = []
+    for header, marker in (("rb200_kernels.h", "RB200_API"), ("rb200.h", "RB200_API"), ("rocal_api.h", "RB200_ROCAL")):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+        text = re.sub(r"#define[^\n]*", " ", text)
+        for m in re.finditer(marker + r"\s+[^;(]*?\b(\w+)\s*\(", text):
+            names.append(m.group(1))
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    from rocal_b200._lib import lib
+    names = _declared_symbols()
+    assert len(names) > 100
+    assert "rb200k_resample" in names and "rocalCropMirrorNormalize" in names and "rb200_feed_ragged" in names
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_version_and_error_text():
+    import rocal_b200
+    assert "sm_100a" in rocal_b200.version()
+    assert rocal_b200.launch_count() >= 0
+    from rocal_b200._lib import lib
+    # argument validation happens before any CUDA call
+    assert lib.rb200k_resample(None, None, None, 4, None, None) == -1
+    assert b"null pointer" in lib.rb200k_last_error()
+    assert lib.rb200k_resample(None, None, None, 0, None, None) == 0      # empty batch is a no-op
+
+
+def test_null_context_convention():
+    import rocal_b200._capi as C
+    from rocal_b200 import types
+    assert C.verify(None) == types.CONTEXT_INVALID
+    assert C.run(None) == types.CONTEXT_INVALID
+    assert C.release(None) == types.CONTEXT_INVALID
+    assert C.get_status(None) == types.CONTEXT_INVALID
+    assert C.output_count(None) == 0
+    assert not C.resize(None, None, 8, 8, 0, 1, 0, 0, 0, 0, 1, 0, 2)
+
+
+def test_parameters_follow_the_reference_draws():
+    """Parameters created through the API take successive entries of the std::seed_seq table and draw as the
+    reference's UniformRand / CustomRand do (pinned by the golden vectors and the numpy restatement)."""
+    import rocal_b200._capi as C
+    from oracle import pyoracle as O
+    g = np.load(os.path.join(GOLDEN, "param_rng.npz"))
+    C.set_seed(1234)
+    assert C.get_seed() == 1234
+    table = g["seed_seq_1234"]
+    # the first value of a fresh generator is its constructor draw; the table index is not observable, so
+    # find which entry this parameter took and check that the next parameters take the following entries
+    p1 = C.create_float_uniform_rand(0.25, 0.75)
+    v1 = C.get_float_value(p1)
+    idx = None
+    for k in range(1024):
+        u = O.UniformRand(0.25, 0.75, int(table[k]), 1)
+        rs = np.random.RandomState()
+        rs.seed(int(table[k]) & 0xFFFFFFFF)
+        first = np.float32(float(rs.randint(0, 1 << 32, dtype=np.uint64)) / 4294967295.0 * (0.75 - 0.25) + 0.25)
+        if first == np.float32(v1):
+            idx = k
+            break
+    assert idx is not None
+    p2 = C.create_int_uniform_rand(0, 1000)
+    rs = np.random.RandomState()
+    rs.seed(int(table[(idx + 1) % 1024]) & 0xFFFFFFFF)
+    assert C.get_int_value(p2) == int(float(rs.randint(0, 1 << 32, dtype=np.uint64)) / 4294967295.0 * 1000.0)
+    # fixed parameters and updates
+    q = C.create_float_parameter(1.5)
+    assert C.get_float_value(q) == 1.5
+    assert C.update_float_parameter(2.5, q) == 0 and C.get_float_value(q) == 2.5
+    assert C.update_float_uniform_rand(0.0, 1.0, q) != 0          # wrong kind
+    assert C.update_int_parameter(3, None) != 0
