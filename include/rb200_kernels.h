@@ -204,6 +204,11 @@ RB200_API int rb200k_box_encode(const float* boxes, const int32_t* labels, const
  * Misc
  * ------------------------------------------------------------------------------------- */
 
+/* Device-side status: 0 = fine; 1 = a kernel gave up on one of its bounded waits (a copy that never
+ * completed) since the last call, its output is then incomplete; -1 = the query itself failed.
+ * Synchronises with the device. */
+RB200_API int rb200k_device_status(void);
+
 /* Text of the last error on the calling thread ("" if none). */
 RB200_API const char* rb200k_last_error(void);
 

@@ -23,6 +23,8 @@
 // (rocAL/rocAL_hip/rocal_hip_kernels.cpp:311-343, 388-409, 425-430): source location
 // dst*ratio + (ratio-1)/2 + roi.x, floor, taps clamped to [roi.x, roi.x2-1], the fmaf nest
 // TL*(1-wy)(1-wx) + (TR*(1-wy)wx + (BL*wy(1-wx) + BR*wy*wx)), round-to-nearest-even uint8.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace rb200 {
@@ -36,6 +38,8 @@ struct ResampleLaunch {
     int pitch;          // bytes per staged row (multiple of 16)
     int twh;            // staged kernel: threads per row group (each owns two columns)
     int groups;         // staged kernel: row groups per CTA
+    int strip_rows;     // stream kernel: output rows per CTA
+    int ns, ns_log2;    // stream kernel: ring stages (power of two)
     int pair_ok;        // paired (2-element) stores are aligned
     int normalize, fill_padding;
     float mul[3], add[3];
@@ -156,78 +160,326 @@ struct StagedRow {
     int pad[2];
 };
 
+// One output row of one thread: two adjacent pixels, three channels, blended from staged rows at byte
+// offsets off0 / off1 (the row's first staged pixel) and stored at po.
+template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED>
+__device__ __forceinline__ void blend_store(const uint8_t* stage, int off0, int off1, float2 wy2, float2 owy2,
+                                            const ColumnTaps (&ct)[2], float2 wx2, float2 owx2, bool second,
+                                            const float (&mulv)[3], const float (&addv)[3], const uint32_t magic,
+                                            OutT* po, size_t plane) {
+    const float2 neg_magic = make_float2(-8388608.0f, -8388608.0f);
+    const float2 rnd = make_float2(12582912.0f, 12582912.0f);
+    const float2 neg_rnd = make_float2(-12582912.0f, -12582912.0f);
+    uint32_t l0[2], r0[2], l1[2], r1[2];
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+        fetch_pair(stage, off0 + ct[p].o_left, l0[p], r0[p]);
+        fetch_pair(stage, off1 + ct[p].o_left, l1[p], r1[p]);
+        r0[p] = ct[p].same ? l0[p] : r0[p];
+        r1[p] = ct[p].same ? l1[p] : r1[p];
+    }
+    const float2 w00 = mul2(owy2, owx2), w01 = mul2(owy2, wx2), w10 = mul2(wy2, owx2);
+    float2 v[3];
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const uint32_t sel_l = 0x7650u + c;
+        float2 tl = make_float2(byte_magic(l0[0], magic, sel_l), byte_magic(l0[1], magic, sel_l));
+        float2 bl = make_float2(byte_magic(l1[0], magic, sel_l), byte_magic(l1[1], magic, sel_l));
+        float2 tr, br;
+        // right tap: its red byte sits in the left word unless the taps coincide
+        if (c == 0) {
+            tr = make_float2(byte_magic(l0[0], magic, ct[0].sel_r), byte_magic(l0[1], magic, ct[1].sel_r));
+            br = make_float2(byte_magic(l1[0], magic, ct[0].sel_r), byte_magic(l1[1], magic, ct[1].sel_r));
+        } else if (c == 1) {
+            tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_g), byte_magic(r0[1], magic, ct[1].sel_g));
+            br = make_float2(byte_magic(r1[0], magic, ct[0].sel_g), byte_magic(r1[1], magic, ct[1].sel_g));
+        } else {
+            tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_b), byte_magic(r0[1], magic, ct[1].sel_b));
+            br = make_float2(byte_magic(r1[0], magic, ct[0].sel_b), byte_magic(r1[1], magic, ct[1].sel_b));
+        }
+        tl = add2(tl, neg_magic);
+        tr = add2(tr, neg_magic);
+        bl = add2(bl, neg_magic);
+        br = add2(br, neg_magic);
+        float2 acc = mul2(mul2(br, wy2), wx2);
+        acc = fma2(bl, w10, acc);
+        acc = fma2(tr, w01, acc);
+        acc = fma2(tl, w00, acc);
+        // The blend of uint8 values with weights in [0,1] stays inside [0,255] up to
+        // rounding, so rounding to nearest even is all the uint8 quantisation needs.
+        acc = add2(add2(acc, rnd), neg_rnd);
+        v[c] = NORMALIZE ? fma2(acc, make_float2(mulv[c], mulv[c]), make_float2(addv[c], addv[c])) : acc;
+    }
+    if (PAIRED) {
+        if (LAYOUT == RB200_NCHW) {
+            PairStore<OutT>::st(po, v[0]);
+            PairStore<OutT>::st(po + plane, v[1]);
+            PairStore<OutT>::st(po + 2 * plane, v[2]);
+        } else {
+            PairStore<OutT>::st(po, make_float2(v[0].x, v[1].x));
+            PairStore<OutT>::st(po + 2, make_float2(v[2].x, v[0].y));
+            PairStore<OutT>::st(po + 4, make_float2(v[1].y, v[2].y));
+        }
+    } else {
+        const size_t cs = LAYOUT == RB200_NCHW ? plane : 1;
+        const size_t xs = LAYOUT == RB200_NCHW ? 1 : 3;
+        po[0] = OutConv<OutT>::cvt(v[0].x);
+        po[cs] = OutConv<OutT>::cvt(v[1].x);
+        po[2 * cs] = OutConv<OutT>::cvt(v[2].x);
+        if (second) {
+            po[xs] = OutConv<OutT>::cvt(v[0].y);
+            po[xs + cs] = OutConv<OutT>::cvt(v[1].y);
+            po[xs + 2 * cs] = OutConv<OutT>::cvt(v[2].y);
+        }
+    }
+}
+
 template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED>
 __device__ __forceinline__ void staged_rows(const uint8_t* stage, const StagedRow* rows, int j_begin, int j_end,
                                             const ColumnTaps (&ct)[2], float2 wx2, float2 owx2, bool second,
                                             const float (&mulv)[3], const float (&addv)[3], const uint32_t magic,
                                             OutT* po, size_t row_step, size_t plane) {
-    const float2 neg_magic = make_float2(-8388608.0f, -8388608.0f);
-    const float2 rnd = make_float2(12582912.0f, 12582912.0f);
-    const float2 neg_rnd = make_float2(-12582912.0f, -12582912.0f);
     for (int j = j_begin; j < j_end; j++, po += row_step) {
         const float4 wts = *reinterpret_cast<const float4*>(&rows[j]);
         const int2 offs = *reinterpret_cast<const int2*>(&rows[j].off0);
-        const float2 wy2 = make_float2(wts.x, wts.y), owy2 = make_float2(wts.z, wts.w);
-        uint32_t l0[2], r0[2], l1[2], r1[2];
+        blend_store<OutT, LAYOUT, NORMALIZE, PAIRED>(stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
+                                                     ct, wx2, owx2, second, mulv, addv, magic, po, plane);
+    }
+}
+
+// Per-thread set-up of the two columns a thread owns.
+__device__ __forceinline__ void column_setup(int xi0, bool second, int crop_x, int crop_w, int mirror, float ratio_w,
+                                             float off_w, int roi_x, int x_lo, int x_hi, int x_first,
+                                             ColumnTaps (&ct)[2], float2& wx2, float2& owx2) {
+    float wxs[2], owxs[2];
 #pragma unroll
-        for (int p = 0; p < 2; p++) {
-            fetch_pair(stage, offs.x + ct[p].o_left, l0[p], r0[p]);
-            fetch_pair(stage, offs.y + ct[p].o_left, l1[p], r1[p]);
-            r0[p] = ct[p].same ? l0[p] : r0[p];
-            r1[p] = ct[p].same ? l1[p] : r1[p];
+    for (int p = 0; p < 2; p++) {
+        int xi = (p == 1 && !second) ? xi0 : xi0 + p;
+        int rx = crop_x + (mirror ? (crop_w - 1 - xi) : xi);
+        float sx = src_location(rx, ratio_w, off_w, roi_x);
+        float fx = floorf(sx);
+        wxs[p] = sub_rn(sx, fx);
+        owxs[p] = sub_rn(1.0f, wxs[p]);
+        int x0, x1;
+        clamp_taps(fx, x_lo, x_hi, x0, x1);
+        ct[p].o_left = (x0 - x_first) * 3;
+        ct[p].same = (x1 == x0);
+        ct[p].sel_r = ct[p].same ? 0x7650u : 0x7653u;
+        ct[p].sel_g = ct[p].same ? 0x7651u : 0x7650u;
+        ct[p].sel_b = ct[p].same ? 0x7652u : 0x7651u;
+    }
+    wx2 = make_float2(wxs[0], wxs[1]);
+    owx2 = make_float2(owxs[0], owxs[1]);
+}
+
+// ------------------------------------------------------------------------------------------
+// Stream kernel: a CTA owns a strip of `strip_rows` output rows of one tile column of one sample.
+// Column set-up happens once per thread for the whole strip. Source rows arrive through a ring of
+// NS stages, each holding the two tap rows of one output row, filled by thread 0 with two 1-D bulk
+// copies (cp.async.bulk, the TMA unit) that complete on the stage's mbarrier; consumers release a
+// stage by arriving on its "empty" mbarrier. Every wait is bounded: on a time-out the kernel sets
+// g_resample_timeout, drains the copies it has in flight (bounded again) and returns.
+// ------------------------------------------------------------------------------------------
+__device__ int g_resample_timeout = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about a second of SM clock.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < (1 << 24); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > 2000000000LL) break;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+struct StreamRow {           // per strip row, built once per CTA (32 bytes + 16 bytes)
+    float2 wy2, owy2;
+    int off0, off1;          // byte offset of the first staged pixel of the two tap rows (stage included)
+    uint32_t b0, b1;         // bytes of the two bulk copies
+};
+struct StreamSrc {
+    const uint8_t *g0, *g1;  // 16-byte aligned global sources of the two copies
+};
+constexpr int kMaxStripRows = 32;
+
+template <typename OutT, int LAYOUT, bool NORMALIZE>
+__global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __restrict__ arena,
+                                                              const rb200_resample_sample* __restrict__ samples,
+                                                              const ResampleLaunch L) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // Layout: full[NS] | empty[NS] (128 bytes reserved) | StreamRow[32] | StreamSrc[32] | stages
+    const int NS = L.ns, ns_mask = L.ns - 1, ns_lg = L.ns_log2;
+    StreamRow* rowtab = reinterpret_cast<StreamRow*>(smem + 128);
+    StreamSrc* srctab = reinterpret_cast<StreamSrc*>(smem + 128 + sizeof(StreamRow) * kMaxStripRows);
+    uint8_t* stage = smem + 128 + (sizeof(StreamRow) + sizeof(StreamSrc)) * kMaxStripRows;
+    const uint32_t bar_base = smem_u32(smem);
+    const uint32_t stage_base = smem_u32(stage);
+
+    const int n = blockIdx.y;
+    const int tx = blockIdx.x % L.tiles_x;
+    const int strip = blockIdx.x / L.tiles_x;
+    const int tid = threadIdx.x;
+    const int TW = 2 * L.twh;
+    const int producer_tid = (int)blockDim.x - 32;      // lane 0 of the last warp
+
+    const rb200_resample_sample* sp = samples + n;
+    const int crop_w = sp->crop_w, crop_h = sp->crop_h;
+    const int cw = min(crop_w, L.out_w);
+    const int ch = min(crop_h, L.out_h);
+    const int tile_x0 = tx * TW;
+    const int y_begin = strip * L.strip_rows;
+    const int xi0 = tile_x0 + 2 * tid;
+    OutT* out = reinterpret_cast<OutT*>(L.out);
+
+    const int rows_valid = min(L.strip_rows, ch - y_begin);
+    const int cols_valid = min(TW, cw - tile_x0);
+
+    if (rows_valid > 0 && cols_valid > 0) {
+        const uint8_t* img = arena + sp->src_offset;
+        const uint32_t stride = sp->src_stride;
+        const int roi_x = sp->roi_x, roi_w = sp->roi_w;
+        const int crop_x = sp->crop_x, mirror = sp->mirror;
+        const int x_lo = roi_x, x_hi = max(roi_x + roi_w - 2, roi_x);
+        const float ratio_w = div_rn((float)roi_w, (float)sp->dst_w);
+        const float off_w = mul_rn(sub_rn(ratio_w, 1.0f), 0.5f);
+        int x_first, x_last;
+        {
+            int ca = tile_x0, cb = tile_x0 + cols_valid - 1;
+            int ra = crop_x + (mirror ? (crop_w - 1 - ca) : ca);
+            int rb = crop_x + (mirror ? (crop_w - 1 - cb) : cb);
+            int r_lo = min(ra, rb), r_hi = max(ra, rb);
+            int t0, t1;
+            clamp_taps(floorf(src_location(r_lo, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+            x_first = t0;
+            clamp_taps(floorf(src_location(r_hi, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+            x_last = t1;
         }
-        const float2 w00 = mul2(owy2, owx2), w01 = mul2(owy2, wx2), w10 = mul2(wy2, owx2);
-        float2 v[3];
+
+        // Row table of the strip (one thread per row) and barrier initialisation.
+        if (tid < rows_valid) {
+            const int roi_y = sp->roi_y, roi_h = sp->roi_h;
+            const float ratio_h = div_rn((float)roi_h, (float)sp->dst_h);
+            const float off_h = mul_rn(sub_rn(ratio_h, 1.0f), 0.5f);
+            const int y_lo = roi_y, y_hi = max(roi_y + roi_h - 2, roi_y);
+            const int nbytes = (x_last - x_first + 1) * 3;
+            const int s = tid & ns_mask;
+            float sy = src_location(sp->crop_y + y_begin + tid, ratio_h, off_h, roi_y);
+            float fy = floorf(sy);
+            int y0, y1;
+            clamp_taps(fy, y_lo, y_hi, y0, y1);
+            const uint8_t* g0 = img + (size_t)y0 * stride + (size_t)x_first * 3;
+            const uint8_t* g1 = img + (size_t)y1 * stride + (size_t)x_first * 3;
+            const uint32_t m0 = (uint32_t)((uintptr_t)g0 & 15), m1 = (uint32_t)((uintptr_t)g1 & 15);
+            float wy = sub_rn(sy, fy), owy = sub_rn(1.0f, wy);
+            StreamRow r;
+            r.wy2 = make_float2(wy, wy);
+            r.owy2 = make_float2(owy, owy);
+            r.off0 = (2 * s) * L.pitch + (int)m0;
+            r.off1 = (2 * s + 1) * L.pitch + (int)m1;
+            r.b0 = ((m0 + nbytes + 15) >> 4) << 4;
+            r.b1 = ((m1 + nbytes + 15) >> 4) << 4;
+            rowtab[tid] = r;
+            srctab[tid].g0 = g0 - m0;
+            srctab[tid].g1 = g1 - m1;
+        }
+        if (tid == producer_tid) {
+            for (int s = 0; s < NS; s++) {
+                mbar_init(bar_base + 8 * s, 1);                   // full: one arrive (+ tx bytes)
+                mbar_init(bar_base + 8 * (NS + s), L.twh);        // empty: every compute thread
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();
+
+        if (tid >= producer_tid) {
+            // ---- producer warp: lane 0 keeps the ring full ----
+            if (tid == producer_tid) {
+                for (int j = 0; j < rows_valid; j++) {
+                    const int s = j & ns_mask;
+                    if (j >= NS && !mbar_wait_bounded(bar_base + 8 * (NS + s), ((j >> ns_lg) - 1) & 1)) {
+                        atomicExch(&g_resample_timeout, 1);
+                        break;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    const uint2 bytes = *reinterpret_cast<const uint2*>(&rowtab[j].b0);
+                    const StreamSrc src = srctab[j];
+                    const uint32_t bar = bar_base + 8 * s;
+                    mbar_expect_tx(bar, bytes.x + bytes.y);
+                    bulk_g2s(stage_base + (2 * s) * L.pitch, src.g0, bytes.x, bar);
+                    bulk_g2s(stage_base + (2 * s + 1) * L.pitch, src.g1, bytes.y, bar);
+                }
+            }
+        } else if (tid < L.twh) {
+            // ---- compute threads ----
+            const bool active = 2 * tid < cols_valid;
+            const bool second = (2 * tid + 1) < cols_valid;
+            ColumnTaps ct[2];
+            float2 wx2, owx2;
+            column_setup(active ? xi0 : tile_x0, second, crop_x, crop_w, mirror, ratio_w, off_w, roi_x, x_lo, x_hi, x_first, ct, wx2, owx2);
+            const size_t plane = (size_t)L.out_w * L.out_h;
+            OutT* po = out + out_index<OutT, LAYOUT>(L.out_w, L.out_h, n, 0, y_begin, active ? xi0 : tile_x0);
+            const size_t row_step = LAYOUT == RB200_NCHW ? (size_t)L.out_w : (size_t)L.out_w * 3;
+            const bool paired = second && L.pair_ok;
+            int j = 0;
+            bool ok = true;
+            for (; j < rows_valid; j++, po += row_step) {
+                const int s = j & ns_mask;
+                if (!mbar_wait_bounded(bar_base + 8 * s, (j >> ns_lg) & 1)) {
+                    ok = false;
+                    break;
+                }
+                if (active) {
+                    const float4 wts = *reinterpret_cast<const float4*>(&rowtab[j]);
+                    const int2 offs = *reinterpret_cast<const int2*>(&rowtab[j].off0);
+                    if (paired)
+                        blend_store<OutT, LAYOUT, NORMALIZE, true>(stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
+                                                                   ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
+                    else
+                        blend_store<OutT, LAYOUT, NORMALIZE, false>(stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
+                                                                    ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
+                }
+                mbar_arrive(bar_base + 8 * (NS + s));
+            }
+            if (!ok) {
+                atomicExch(&g_resample_timeout, 1);
+                // Before the CTA's shared memory is given away, wait (bounded) for the copies that may
+                // still be in flight: the producer is never more than NS rows ahead.
+                if (tid == 0)
+                    for (int jj = j; jj < min(j + NS, rows_valid); jj++) mbar_wait_bounded(bar_base + 8 * (jj & ns_mask), (jj >> ns_lg) & 1);
+            }
+        }
+    }
+
+    if (L.fill_padding && tid < L.twh) {
+        const int j_end = min(L.strip_rows, L.out_h - y_begin);
+        for (int jj = 0; jj < j_end; jj++) {
+            int y = y_begin + jj;
 #pragma unroll
-        for (int c = 0; c < 3; c++) {
-            const uint32_t sel_l = 0x7650u + c;
-            float2 tl = make_float2(byte_magic(l0[0], magic, sel_l), byte_magic(l0[1], magic, sel_l));
-            float2 bl = make_float2(byte_magic(l1[0], magic, sel_l), byte_magic(l1[1], magic, sel_l));
-            float2 tr, br;
-            // right tap: its red byte sits in the left word unless the taps coincide
-            if (c == 0) {
-                tr = make_float2(byte_magic(l0[0], magic, ct[0].sel_r), byte_magic(l0[1], magic, ct[1].sel_r));
-                br = make_float2(byte_magic(l1[0], magic, ct[0].sel_r), byte_magic(l1[1], magic, ct[1].sel_r));
-            } else if (c == 1) {
-                tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_g), byte_magic(r0[1], magic, ct[1].sel_g));
-                br = make_float2(byte_magic(r1[0], magic, ct[0].sel_g), byte_magic(r1[1], magic, ct[1].sel_g));
-            } else {
-                tr = make_float2(byte_magic(r0[0], magic, ct[0].sel_b), byte_magic(r0[1], magic, ct[1].sel_b));
-                br = make_float2(byte_magic(r1[0], magic, ct[0].sel_b), byte_magic(r1[1], magic, ct[1].sel_b));
-            }
-            tl = add2(tl, neg_magic);
-            tr = add2(tr, neg_magic);
-            bl = add2(bl, neg_magic);
-            br = add2(br, neg_magic);
-            float2 acc = mul2(mul2(br, wy2), wx2);
-            acc = fma2(bl, w10, acc);
-            acc = fma2(tr, w01, acc);
-            acc = fma2(tl, w00, acc);
-            // The blend of uint8 values with weights in [0,1] stays inside [0,255] up to
-            // rounding, so rounding to nearest even is all the uint8 quantisation needs.
-            acc = add2(add2(acc, rnd), neg_rnd);
-            v[c] = NORMALIZE ? fma2(acc, make_float2(mulv[c], mulv[c]), make_float2(addv[c], addv[c])) : acc;
-        }
-        if (PAIRED) {
-            if (LAYOUT == RB200_NCHW) {
-                PairStore<OutT>::st(po, v[0]);
-                PairStore<OutT>::st(po + plane, v[1]);
-                PairStore<OutT>::st(po + 2 * plane, v[2]);
-            } else {
-                PairStore<OutT>::st(po, make_float2(v[0].x, v[1].x));
-                PairStore<OutT>::st(po + 2, make_float2(v[2].x, v[0].y));
-                PairStore<OutT>::st(po + 4, make_float2(v[1].y, v[2].y));
-            }
-        } else {
-            const size_t cs = LAYOUT == RB200_NCHW ? plane : 1;
-            const size_t xs = LAYOUT == RB200_NCHW ? 1 : 3;
-            po[0] = OutConv<OutT>::cvt(v[0].x);
-            po[cs] = OutConv<OutT>::cvt(v[1].x);
-            po[2 * cs] = OutConv<OutT>::cvt(v[2].x);
-            if (second) {
-                po[xs] = OutConv<OutT>::cvt(v[0].y);
-                po[xs + cs] = OutConv<OutT>::cvt(v[1].y);
-                po[xs + 2 * cs] = OutConv<OutT>::cvt(v[2].y);
+            for (int p = 0; p < 2; p++) {
+                int xi = xi0 + p;
+                if (xi < L.out_w && (y >= ch || xi >= cw)) store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, xi, 0.f, 0.f, 0.f);
             }
         }
     }
@@ -486,12 +738,25 @@ __global__ void __launch_bounds__(256) resample_direct_kernel(const uint8_t* __r
     }
 }
 
+enum { MODE_DIRECT = 0, MODE_STAGED = 1, MODE_STREAM = 2 };
+
 template <typename OutT, int LAYOUT>
 static int launch_typed(const uint8_t* arena, const rb200_resample_sample* samples, int n, ResampleLaunch L,
-                        bool staged, size_t smem, cudaStream_t stream) {
-    int tiles_y = (L.ext_h + L.th - 1) / L.th;
+                        int mode, size_t smem, cudaStream_t stream) {
     L.pair_ok = (L.out_w % 2 == 0) && (((uintptr_t)L.out) % (2 * sizeof(OutT)) == 0);
-    if (staged) {
+    if (mode == MODE_STREAM) {
+        int strips = (L.ext_h + L.strip_rows - 1) / L.strip_rows;
+        dim3 grid((unsigned)(L.tiles_x * strips), (unsigned)n);
+        auto k = L.normalize ? resample_stream_kernel<OutT, LAYOUT, true> : resample_stream_kernel<OutT, LAYOUT, false>;
+        if (smem > 48 * 1024) {
+            int rc = check_cuda(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                "cudaFuncSetAttribute(resample_stream)");
+            if (rc) return rc;
+        }
+        // compute threads rounded up to whole warps + one producer warp
+        k<<<grid, ((L.twh + 31) & ~31) + 32, smem, stream>>>(arena, samples, L);
+    } else if (mode == MODE_STAGED) {
+        int tiles_y = (L.ext_h + L.th - 1) / L.th;
         dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
         auto k = L.normalize ? resample_staged_kernel<OutT, LAYOUT, true> : resample_staged_kernel<OutT, LAYOUT, false>;
         if (smem > 48 * 1024) {
@@ -505,7 +770,7 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
         int tw = ((L.ext_w + tx - 1) / tx + 31) & ~31;
         L.tiles_x = (L.ext_w + tw - 1) / tw;
         L.th = 8;
-        tiles_y = (L.ext_h + L.th - 1) / L.th;
+        int tiles_y = (L.ext_h + L.th - 1) / L.th;
         dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
         resample_direct_kernel<OutT, LAYOUT><<<grid, tw, 0, stream>>>(arena, samples, L);
     }
@@ -578,6 +843,11 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     int groups = 1;
     while (groups < 8 && twh * groups < 64) groups *= 2;
     L.tiles_x = (ext_w + 2 * twh - 1) / (2 * twh);
+    int mode = staged ? MODE_STAGED : MODE_DIRECT;
+    size_t smem = 0;
+    L.strip_rows = 32;
+    L.ns = 4;
+    L.ns_log2 = 2;
     if (staged) {
         int max_span = 1;
         for (int i = 0; i < n; i++) {
@@ -587,19 +857,37 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
             if (span > max_span) max_span = (int)span;
         }
         pitch = (15 + max_span * 3 + 12 + 15) & ~15;
-        const size_t budget = 40 * 1024, hard = 160 * 1024;
-        while (th > groups && (size_t)(2 * th + 2) * pitch > budget) th >>= 1;
-        while (groups > th) groups >>= 1;
-        if ((size_t)(2 * th + 2) * pitch > hard) staged = false;
+        // Wide tiles stream their rows through the bulk-copy ring; narrow ones use the tile kernel.
+        const char* force = getenv("RB200_RESAMPLE_MODE");
+        bool want_stream = twh >= 64 && !(force && force[0] == 't');
+        if (want_stream) {
+            int ns = 4;
+            if ((size_t)2 * ns * pitch > 96 * 1024) ns = 2;
+            if ((size_t)2 * ns * pitch <= 160 * 1024) {
+                mode = MODE_STREAM;
+                L.ns = ns;
+                L.ns_log2 = ns == 4 ? 2 : 1;
+                int rows = 32;
+                while (rows > 8 && (long)n * L.tiles_x * ((ext_h + rows - 1) / rows) < 4 * 148) rows >>= 1;
+                L.strip_rows = rows;
+                smem = 128 + (sizeof(StreamRow) + sizeof(StreamSrc)) * kMaxStripRows + (size_t)2 * ns * pitch;
+            }
+        }
+        if (mode == MODE_STAGED) {
+            const size_t budget = 40 * 1024, hard = 160 * 1024;
+            while (th > groups && (size_t)(2 * th + 2) * pitch > budget) th >>= 1;
+            while (groups > th) groups >>= 1;
+            if ((size_t)(2 * th + 2) * pitch > hard) mode = MODE_DIRECT;
+            smem = ((sizeof(TileHeader) + sizeof(StagedRow) * th + sizeof(int) * (2 * th + 2) + 15) & ~(size_t)15) +
+                   (size_t)(2 * th + 2) * pitch;
+        }
     }
     L.th = th;
     L.pitch = pitch;
     L.twh = twh;
     L.groups = groups;
-    size_t smem = ((sizeof(TileHeader) + sizeof(StagedRow) * th + sizeof(int) * (2 * th + 2) + 15) & ~(size_t)15) +
-                  (size_t)(2 * th + 2) * pitch;
 
-#define RB200_DISPATCH(T, LAY) return launch_typed<T, LAY>(arena, samples, n, L, staged, smem, stream)
+#define RB200_DISPATCH(T, LAY) return launch_typed<T, LAY>(arena, samples, n, L, mode, smem, stream)
     if (p->out_layout == RB200_NCHW) {
         if (p->out_dtype == RB200_FP32) RB200_DISPATCH(float, RB200_NCHW);
         if (p->out_dtype == RB200_FP16) RB200_DISPATCH(__half, RB200_NCHW);
@@ -610,4 +898,12 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
         RB200_DISPATCH(uint8_t, RB200_NHWC);
     }
 #undef RB200_DISPATCH
+}
+
+// Non-zero when a kernel of this library gave up on a bounded wait since the last call (then cleared).
+extern "C" int rb200k_device_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, rb200::g_resample_timeout, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(rb200::g_resample_timeout, &zero, sizeof(int));
+    return v;
 }

@@ -4,6 +4,8 @@ Tolerances (stated by the task): bit-exact for indexing ops and uint8 paths comp
 same operation order; <= 1 LSB for uint8 in general; 1e-5 relative for fp32; 1e-3 for fp16.
 The kernels are written to reproduce the oracle's operation order, so most checks are exact.
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -12,6 +14,11 @@ from rocal_b200 import synthetic as S
 from rocal_b200 import tables as T
 
 pytestmark = pytest.mark.gpu
+
+
+def _device_status():
+    from rocal_b200._lib import lib
+    return lib.rb200k_device_status()
 
 
 def _dev(arena, cuda):
@@ -38,8 +45,15 @@ def test_resize_cmn_config0(cuda, dtype, layout):
     t = S.classification_tables(rng, hs, ws, offs)
     mul, add = S.normalize_tables()
     ref = O.resample(arena, t, 224, 224, dtype, layout, mul, add)
-    for staged in (True, False):
-        got = K.resample(_dev(arena, cuda), t, 224, 224, dtype, layout, mul, add, staged=staged).cpu().numpy()
+    for staged, force_tile in ((True, False), (True, True), (False, False)):
+        # three code paths: strip-streaming kernel, shared-memory tile kernel, direct gather
+        if force_tile:
+            os.environ["RB200_RESAMPLE_MODE"] = "tile"
+        try:
+            got = K.resample(_dev(arena, cuda), t, 224, 224, dtype, layout, mul, add, staged=staged).cpu().numpy()
+        finally:
+            os.environ.pop("RB200_RESAMPLE_MODE", None)
+        assert _device_status() == 0
         if dtype == T.FP32:
             _assert_fp(got, ref, 1e-5, "fp32")
             assert np.array_equal(got, ref), "fp32 path is expected to be bit-identical"
