@@ -38,9 +38,10 @@ RESIZE_SHORTER = 256
 H_RANGE = (300, 1080)
 W_RANGE = (300, 1080)
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one resample launch, scaled to a 1024-image batch
-# from the ncu capture summarised in profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one resample launch: measured by ncu on a 512-image
+# launch (337.8 MB read + 126.9 MB written) and scaled by the images processed to the 1024-image launch
+# (profiles/resample_stream_fp16_nchw_cfg1.md). Scaled again when --batch overrides the batch size.
+NCU_TRAFFIC_BYTES_PER_IMAGE = (337829376 + 126903808) / 512.0
 
 
 def algorithmic_bytes(t):
@@ -317,10 +318,10 @@ def main():
                     "d2h_bytes_per_step": int(host_back.numel() * 2), "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": dict(clocks, window="warm-up + timed steps + end-to-end steps"),
-            "roofline": {"bound": "hbm", "kernel": "resample_kernel<half,NCHW,staged>", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "resample_stream_kernel<half,NCHW,normalize>", "achieved": achieved,
                          "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                          "algorithmic_bytes_per_launch": algo, "launch_ms": mean_launch_ms,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_IMAGE * n, "traffic_source": "ncu, 512-image launch scaled by images"},
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"], _ = cpu_baseline(arena_h, t)
