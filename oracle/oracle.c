@@ -151,45 +151,44 @@ ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, i
  *               to [0,360)), S = clamp(S*sat, 0, 1), HSV -> RGB, then y = alpha*x + beta
  *               (parameter meaning: rocal_api_augmentation.h:866-877). The reference holds no
  *               arithmetic for this operator (it runs in RPP): the formula is this
- *               restatement's own, the textbook hexcone model.
+ *               restatement's own, the textbook hexcone model, written with reciprocal
+ *               multiplies (S = delta * (1/max), H = 60 * (num * (1/delta)) + offset) and the
+ *               branch-free inverse  channel = V - V*S*clamp(min(k, 4-k), 0, 1).
  * ---------------------------------------------------------------------------------------- */
+static inline float hsv_channel(float v, float vs, float hp, float nshift) {
+    float k = nshift + hp;
+    if (k >= 6.f) k = k - 6.f;
+    float t = fminf(k, 4.f - k);
+    t = fminf(fmaxf(t, 0.f), 1.f);
+    return v - vs * t;
+}
+
 static inline void color_twist_px(float r, float g, float b, float hue, float sat, float out[3]) {
     float cmax = fmaxf(r, fmaxf(g, b));
     float cmin = fminf(r, fminf(g, b));
     float delta = cmax - cmin;
-    float h = 0.f, s = 0.f, v = cmax;
-    if (delta > 0.f) {
-        s = delta / cmax;
-        if (cmax == r) {
-            h = 60.f * ((g - b) / delta);
-            if (h < 0.f) h = h + 360.f;
-        } else if (cmax == g) {
-            h = 60.f * ((b - r) / delta) + 120.f;
-        } else {
-            h = 60.f * ((r - g) / delta) + 240.f;
-        }
-    }
+    /* reciprocals of the (integer valued) range and maximum; 0 stands in for 1/0 so that grey pixels
+     * get hue 0 and saturation 0 */
+    float rd = delta > 0.f ? 1.0f / delta : 0.f;
+    float rm = cmax > 0.f ? 1.0f / cmax : 0.f;
+    float s = delta * rm;
+    float num, offs;
+    if (cmax == r) { num = g - b; offs = 0.f; }
+    else if (cmax == g) { num = b - r; offs = 120.f; }
+    else { num = r - g; offs = 240.f; }
+    float h = 60.f * (num * rd) + offs;
+    if (h < 0.f) h = h + 360.f;
+    float v = cmax;
     h = h + hue;
     h = h - 360.f * floorf(h * (1.0f / 360.f));
     s = s * sat;
     s = fminf(fmaxf(s, 0.f), 1.f);
     float hp = h * (1.0f / 60.f);
-    float fi = floorf(hp);
-    float f = hp - fi;
-    int sector = (int)fi;
-    if (sector >= 6) sector -= 6;
-    if (sector < 0) sector = 0;
-    float pp = v * (1.f - s);
-    float qq = v * (1.f - s * f);
-    float tt = v * (1.f - s * (1.f - f));
-    switch (sector) {
-        case 0: out[0] = v; out[1] = tt; out[2] = pp; break;
-        case 1: out[0] = qq; out[1] = v; out[2] = pp; break;
-        case 2: out[0] = pp; out[1] = v; out[2] = tt; break;
-        case 3: out[0] = pp; out[1] = qq; out[2] = v; break;
-        case 4: out[0] = tt; out[1] = pp; out[2] = v; break;
-        default: out[0] = v; out[1] = pp; out[2] = qq; break;
-    }
+    float vs = v * s;
+    /* HSV -> RGB: channel = V - V*S*clamp(min(k, 4-k), 0, 1), k = (n + H/60) mod 6, n = 5, 3, 1 */
+    out[0] = hsv_channel(v, vs, hp, 5.f);
+    out[1] = hsv_channel(v, vs, hp, 3.f);
+    out[2] = hsv_channel(v, vs, hp, 1.f);
 }
 
 /* Pointwise family: window + flips (pure indexing; vxExtRppCrop / vxExtRppFlip semantics of

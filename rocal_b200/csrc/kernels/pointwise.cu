@@ -1,11 +1,22 @@
 // Pointwise family: window (crop) + flips + colour arithmetic + per-channel fma + layout/dtype
 // conversion, one launch for the whole batch. grid = (tiles of the output extent, samples).
 //
+// Vector kernel (output width a multiple of 4, 16-byte aligned output): a thread owns 4 consecutive
+// output pixels of one row. Their 12 source bytes are contiguous in the packed HWC source whatever
+// the flips (a horizontal flip reverses the pixel order inside the block); they are fetched with
+// four aligned 32-bit loads and three funnel shifts, so the arbitrary byte alignment of a 3-byte
+// pixel row costs nothing, and leave as 16-byte (fp32), 8-byte (fp16) or 4-byte (uint8) stores.
+// Work items (row, 4-pixel group) are flattened over the CTA so that widths that are not a multiple
+// of the block size waste no lanes. The scalar kernel (one pixel per thread) covers other shapes.
+//
 // Colour arithmetic is float32 on the 0..255 scale with one rounding per operation:
 //   brightness  y = alpha*x + beta
 //   contrast    y = (x - center)*factor + center
-//   twist       hexcone RGB->HSV, H += hue (wrapped to [0,360)), S = clamp(S*sat,0,1), HSV->RGB,
-//               then alpha*x + beta
+//   twist       hexcone RGB->HSV with reciprocal multiplies (S = delta*(1/max),
+//               H = 60*(num*(1/delta)) + offset; the reciprocals of the integer-valued delta and max
+//               come from a 256-entry shared-memory table of IEEE 1/k), H += hue wrapped to [0,360),
+//               S = clamp(S*sat,0,1), branch-free HSV->RGB  channel = V - V*S*clamp(min(k,4-k),0,1),
+//               k = (n + H/60) mod 6, then alpha*x + beta
 // The colour result is rounded to nearest even and saturated to uint8 before the optional
 // normalisation (the reference's colour nodes output uint8 tensors).
 #include "common.cuh"
@@ -20,44 +31,81 @@ struct PointwiseLaunch {
     int th;
     int color_op, normalize, fill_padding, reverse_channels;
     float mul[3], add[3];
+    uint32_t magic;      // 0x4B000000, read by PRMT from the constant bank
+    int pitch;           // vector kernel: bytes per staged source row (multiple of 16)
 };
 
-__device__ __forceinline__ void color_twist_px(float r, float g, float b, float hue, float sat, float& o0, float& o1, float& o2) {
-    float cmax = fmaxf(r, fmaxf(g, b));
-    float cmin = fminf(r, fminf(g, b));
-    float delta = sub_rn(cmax, cmin);
-    float h = 0.f, s = 0.f, v = cmax;
-    if (delta > 0.f) {
-        s = div_rn(delta, cmax);
-        if (cmax == r) {
-            h = mul_rn(60.f, div_rn(sub_rn(g, b), delta));
-            if (h < 0.f) h = add_rn(h, 360.f);
-        } else if (cmax == g) {
-            h = add_rn(mul_rn(60.f, div_rn(sub_rn(b, r), delta)), 120.f);
-        } else {
-            h = add_rn(mul_rn(60.f, div_rn(sub_rn(r, g), delta)), 240.f);
-        }
+__device__ int g_pointwise_timeout = 0;   // set when a bounded wait on a bulk copy gave up
+
+__device__ __forceinline__ uint32_t pw_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool pw_mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool pw_mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (pw_mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < (1 << 24); i++) {
+        if (pw_mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > 2000000000LL) break;
     }
+    return false;
+}
+
+__device__ __forceinline__ float hsv_channel(float v, float vs, float hp, float nshift) {
+    float k = add_rn(nshift, hp);
+    if (k >= 6.f) k = sub_rn(k, 6.f);
+    float t = fminf(k, sub_rn(4.f, k));
+    t = fminf(fmaxf(t, 0.f), 1.f);
+    return sub_rn(v, mul_rn(vs, t));
+}
+
+// rcp: table of 1/k for k = 0..255 (entry 0 holds 0).
+__device__ __forceinline__ void color_twist_px(float r, float g, float b, float hue, float sat, const float* rcp,
+                                               float& o0, float& o1, float& o2) {
+    const float cmax = fmaxf(r, fmaxf(g, b));
+    const float cmin = fminf(r, fminf(g, b));
+    const float delta = sub_rn(cmax, cmin);
+    // delta and cmax are integers in [0,255]: their low mantissa byte after adding 2^23 is the index
+    const float rd = rcp[__float_as_uint(__fadd_rn(delta, 8388608.0f)) & 0xFFu];
+    const float rm = rcp[__float_as_uint(__fadd_rn(cmax, 8388608.0f)) & 0xFFu];
+    float s = mul_rn(delta, rm);
+    const bool is_r = cmax == r;
+    const bool is_g = cmax == g;
+    const float num = is_r ? sub_rn(g, b) : (is_g ? sub_rn(b, r) : sub_rn(r, g));
+    const float offs = is_r ? 0.f : (is_g ? 120.f : 240.f);
+    float h = add_rn(mul_rn(60.f, mul_rn(num, rd)), offs);
+    if (h < 0.f) h = add_rn(h, 360.f);
     h = add_rn(h, hue);
     h = sub_rn(h, mul_rn(360.f, floorf(mul_rn(h, 1.0f / 360.f))));
     s = mul_rn(s, sat);
     s = fminf(fmaxf(s, 0.f), 1.f);
-    float hp = mul_rn(h, 1.0f / 60.f);
-    float fi = floorf(hp);
-    float f = sub_rn(hp, fi);
-    int sector = (int)fi;
-    if (sector >= 6) sector -= 6;
-    if (sector < 0) sector = 0;
-    float pp = mul_rn(v, sub_rn(1.f, s));
-    float qq = mul_rn(v, sub_rn(1.f, mul_rn(s, f)));
-    float tt = mul_rn(v, sub_rn(1.f, mul_rn(s, sub_rn(1.f, f))));
-    switch (sector) {
-        case 0: o0 = v; o1 = tt; o2 = pp; break;
-        case 1: o0 = qq; o1 = v; o2 = pp; break;
-        case 2: o0 = pp; o1 = v; o2 = tt; break;
-        case 3: o0 = pp; o1 = qq; o2 = v; break;
-        case 4: o0 = tt; o1 = pp; o2 = v; break;
-        default: o0 = v; o1 = pp; o2 = qq; break;
+    const float hp = mul_rn(h, 1.0f / 60.f);
+    const float vs = mul_rn(cmax, s);
+    o0 = hsv_channel(cmax, vs, hp, 5.f);
+    o1 = hsv_channel(cmax, vs, hp, 3.f);
+    o2 = hsv_channel(cmax, vs, hp, 1.f);
+}
+
+template <int COLOR_OP>
+__device__ __forceinline__ void color_px(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
+                                         const float* rcp) {
+    if (COLOR_OP == RB200_COLOR_BRIGHTNESS) {
+        v0 = sat_round_u8f(add_rn(mul_rn(alpha, v0), beta));
+        v1 = sat_round_u8f(add_rn(mul_rn(alpha, v1), beta));
+        v2 = sat_round_u8f(add_rn(mul_rn(alpha, v2), beta));
+    } else if (COLOR_OP == RB200_COLOR_CONTRAST) {
+        v0 = sat_round_u8f(add_rn(mul_rn(sub_rn(v0, beta), alpha), beta));
+        v1 = sat_round_u8f(add_rn(mul_rn(sub_rn(v1, beta), alpha), beta));
+        v2 = sat_round_u8f(add_rn(mul_rn(sub_rn(v2, beta), alpha), beta));
+    } else if (COLOR_OP == RB200_COLOR_TWIST) {
+        float t0, t1, t2;
+        color_twist_px(v0, v1, v2, hue, sat, rcp, t0, t1, t2);
+        v0 = sat_round_u8f(add_rn(mul_rn(alpha, t0), beta));
+        v1 = sat_round_u8f(add_rn(mul_rn(alpha, t1), beta));
+        v2 = sat_round_u8f(add_rn(mul_rn(alpha, t2), beta));
     }
 }
 
@@ -77,10 +125,249 @@ __device__ __forceinline__ void pw_store3(OutT* out, int out_w, int out_h, int n
     }
 }
 
+// Four consecutive elements of one type, stored as one vector.
+template <typename OutT>
+struct Store4;
+template <>
+struct Store4<float> {
+    static __device__ __forceinline__ void st(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <>
+struct Store4<__half> {
+    static __device__ __forceinline__ void st(__half* p, float a, float b, float c, float d) {
+        __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t*>(&lo);
+        v.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+template <>
+struct Store4<uint8_t> {
+    // Inputs are integer valued in [0,255]: adding 2^23 leaves the value in the low mantissa byte.
+    static __device__ __forceinline__ void st(uint8_t* p, float a, float b, float c, float d) {
+        uint32_t ab = __byte_perm(__float_as_uint(__fadd_rn(a, 8388608.0f)), __float_as_uint(__fadd_rn(b, 8388608.0f)), 0x0040u);
+        uint32_t cd = __byte_perm(__float_as_uint(__fadd_rn(c, 8388608.0f)), __float_as_uint(__fadd_rn(d, 8388608.0f)), 0x0040u);
+        *reinterpret_cast<uint32_t*>(p) = __byte_perm(ab, cd, 0x5410u);
+    }
+};
+
+// Byte-only path of crop / flip for uint8 output: the 12 source bytes d[0..2] of a 4-pixel block are
+// permuted into the three output words without ever becoming floats.
+template <int LAYOUT>
+__device__ __forceinline__ void permute_store_u8(uint8_t* po, size_t plane, const uint32_t (&d)[3], bool flip) {
+    if (LAYOUT == RB200_NHWC) {
+        uint32_t o0 = d[0], o1 = d[1], o2 = d[2];
+        if (flip) {   // pixel order reversed, channel order kept
+            o0 = __byte_perm(d[1], d[2], 0x2765u);
+            o1 = __byte_perm(__byte_perm(d[1], d[2], 0x0043u), d[0], 0x3710u);
+            o2 = __byte_perm(d[0], d[1], 0x2105u);
+        }
+        reinterpret_cast<uint32_t*>(po)[0] = o0;
+        reinterpret_cast<uint32_t*>(po)[1] = o1;
+        reinterpret_cast<uint32_t*>(po)[2] = o2;
+    } else {
+        // channel c of pixels 0..3 = block bytes c, 3+c, 6+c, 9+c
+        uint32_t r = __byte_perm(__byte_perm(d[0], d[1], 0x0630u), d[2], 0x5210u);
+        uint32_t g = __byte_perm(__byte_perm(d[0], d[1], 0x0741u), d[2], 0x6210u);
+        uint32_t b = __byte_perm(__byte_perm(d[0], d[1], 0x0052u), d[2], 0x7410u);
+        // b: bytes 2, 5, 8, 11 = d[0].2, d[1].1, d[2].0, d[2].3
+        if (flip) {
+            r = __byte_perm(r, 0u, 0x0123u);
+            g = __byte_perm(g, 0u, 0x0123u);
+            b = __byte_perm(b, 0u, 0x0123u);
+        }
+        *reinterpret_cast<uint32_t*>(po) = r;
+        *reinterpret_cast<uint32_t*>(po + plane) = g;
+        *reinterpret_cast<uint32_t*>(po + 2 * plane) = b;
+    }
+}
+
+template <typename OutT, int LAYOUT, int COLOR_OP>
+__global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
+                                                            const rb200_pointwise_sample* __restrict__ samples,
+                                                            const PointwiseLaunch L) {
+    // Layout: mbarrier (16 bytes) | rcp[256] | staged source rows (th x pitch)
+    extern __shared__ __align__(16) uint8_t pw_smem[];
+    float* rcp = reinterpret_cast<float*>(pw_smem + 16);
+    uint8_t* stage = pw_smem + 16 + 1024;
+    const uint32_t bar = pw_smem_u32(pw_smem);
+    const int n = blockIdx.y;
+    const int tile_y0 = blockIdx.x * L.th;
+    const rb200_pointwise_sample s = samples[n];
+    const uint8_t* img = arena + s.src_offset;
+    OutT* out = reinterpret_cast<OutT*>(L.out);
+    const int w = min(s.roi_w, L.out_w);
+    const int h = min(s.roi_h, L.out_h);
+    const int rows = min(L.th, h - tile_y0);
+    const size_t plane = (size_t)L.out_w * L.out_h;
+    // first source column of every row of the window (a horizontal flip shows the last w columns)
+    const int x_src0 = s.flip_h ? (s.roi_x + s.roi_w - w) : s.roi_x;
+    bool staged_ok = true;
+
+    if (rows > 0 && w > 0) {
+        // Stage the tile's source rows: lane r of warp 0 issues one bulk copy per row r, r+32, ...
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(min(rows, 32)) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        if (COLOR_OP == RB200_COLOR_TWIST)
+            for (int k = threadIdx.x; k < 256; k += blockDim.x) rcp[k] = k ? div_rn(1.0f, (float)k) : 0.f;
+        __syncthreads();
+        if (threadIdx.x < 32 && (int)threadIdx.x < rows) {
+            uint32_t total = 0;
+            for (int r = threadIdx.x; r < rows; r += 32) {
+                const int y = tile_y0 + r;
+                const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
+                const uint8_t* g = img + (size_t)sy * s.src_stride + (size_t)x_src0 * 3;
+                const uint32_t m = (uint32_t)((uintptr_t)g & 15);
+                total += ((m + (uint32_t)w * 3 + 15) >> 4) << 4;
+            }
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total) : "memory");
+            for (int r = threadIdx.x; r < rows; r += 32) {
+                const int y = tile_y0 + r;
+                const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
+                const uint8_t* g = img + (size_t)sy * s.src_stride + (size_t)x_src0 * 3;
+                const uint32_t m = (uint32_t)((uintptr_t)g & 15);
+                const uint32_t bytes = ((m + (uint32_t)w * 3 + 15) >> 4) << 4;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(pw_smem_u32(stage + (size_t)r * L.pitch)), "l"(g - m), "r"(bytes), "r"(bar) : "memory");
+            }
+        }
+        staged_ok = pw_mbar_wait_bounded(bar, 0);
+        if (!staged_ok) {
+            atomicExch(&g_pointwise_timeout, 1);
+            // give copies still in flight a second bounded chance to land before the CTA's memory is released
+            if (threadIdx.x == 0) pw_mbar_wait_bounded(bar, 0);
+        }
+    }
+
+    if (rows > 0 && w > 0 && staged_ok) {
+        const int gpr = (w + 3) >> 2;                 // 4-pixel groups per row
+        const int items = rows * gpr;
+        // item / gpr by multiply-high: exact while item * gpr < 2^32
+        const uint32_t gpr_magic = (uint32_t)((0x100000000ull + (uint32_t)gpr - 1) / (uint32_t)gpr);
+        const bool bytes_only = COLOR_OP == RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels;
+        // Two work items per iteration: all eight loads are issued before the first use.
+        for (int item0 = threadIdx.x; item0 < items; item0 += 2 * blockDim.x) {
+            uint32_t wv[2][4];
+            uint32_t shv[2];
+            int xv[2], yv[2], npxv[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int item = item0 + u * blockDim.x;
+                npxv[u] = 0;
+                if (item < items) {
+                    const int row = gpr == 1 ? item : (int)__umulhi((uint32_t)item, gpr_magic);
+                    const int g = item - row * gpr;
+                    const int x = g << 2;
+                    const int y = tile_y0 + row;
+                    const int npx = min(4, w - x);
+                    const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
+                    const int sx = s.flip_h ? (s.roi_x + s.roi_w - 1 - (x + npx - 1)) : (s.roi_x + x);
+                    // byte position of the block inside its staged row: the copy started at the row's
+                    // address rounded down to 16 bytes
+                    const uint32_t m = (uint32_t)((uintptr_t)(img + (size_t)sy * s.src_stride + (size_t)x_src0 * 3) & 15);
+                    const uint32_t boff = (uint32_t)row * L.pitch + m + (uint32_t)(sx - x_src0) * 3;
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(stage + (boff & ~3u));
+                    wv[u][0] = wp[0];
+                    wv[u][1] = wp[1];
+                    wv[u][2] = wp[2];
+                    wv[u][3] = wp[3];
+                    shv[u] = (boff & 3u) << 3;
+                    xv[u] = x; yv[u] = y; npxv[u] = npx;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int npx = npxv[u];
+                if (npx == 0) continue;
+                const int x = xv[u], y = yv[u];
+                uint32_t d[3];
+                d[0] = __funnelshift_r(wv[u][0], wv[u][1], shv[u]);
+                d[1] = __funnelshift_r(wv[u][1], wv[u][2], shv[u]);
+                d[2] = __funnelshift_r(wv[u][2], wv[u][3], shv[u]);
+                if (bytes_only && npx == 4) {
+                    uint8_t* pb = reinterpret_cast<uint8_t*>(out) +
+                                  (LAYOUT == RB200_NCHW ? ((size_t)n * 3) * plane + (size_t)y * L.out_w + x
+                                                        : (((size_t)n * L.out_h + y) * L.out_w + x) * 3);
+                    permute_store_u8<LAYOUT>(pb, plane, d, s.flip_h != 0);
+                    continue;
+                }
+                // block pixel k, channel c = byte 3k+c of d[]
+                float v[4][3];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+#pragma unroll
+                    for (int c = 0; c < 3; c++) {
+                        const int bidx = 3 * k + c;
+                        v[k][c] = sub_rn(__uint_as_float(__byte_perm(d[bidx >> 2], L.magic, 0x7650u + (bidx & 3))), 8388608.0f);
+                    }
+                    color_px<COLOR_OP>(v[k][0], v[k][1], v[k][2], s.alpha, s.beta, s.hue, s.sat, rcp);
+                    if (L.reverse_channels) { float t = v[k][0]; v[k][0] = v[k][2]; v[k][2] = t; }
+                    if (L.normalize) {
+                        v[k][0] = fmaf(v[k][0], L.mul[0], L.add[0]);
+                        v[k][1] = fmaf(v[k][1], L.mul[1], L.add[1]);
+                        v[k][2] = fmaf(v[k][2], L.mul[2], L.add[2]);
+                    }
+                }
+                if (npx == 4) {
+                    // output pixel j shows block pixel (flip_h ? 3-j : j)
+                    float o[4][3];
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+#pragma unroll
+                        for (int c = 0; c < 3; c++) {
+                            o[j][c] = s.flip_h ? v[3 - j][c] : v[j][c];
+                            if (sizeof(OutT) == 1 && L.normalize) o[j][c] = sat_round_u8f(o[j][c]);
+                        }
+                    if (LAYOUT == RB200_NCHW) {
+                        OutT* po = out + ((size_t)n * 3) * plane + (size_t)y * L.out_w + x;
+                        Store4<OutT>::st(po, o[0][0], o[1][0], o[2][0], o[3][0]);
+                        Store4<OutT>::st(po + plane, o[0][1], o[1][1], o[2][1], o[3][1]);
+                        Store4<OutT>::st(po + 2 * plane, o[0][2], o[1][2], o[2][2], o[3][2]);
+                    } else {
+                        OutT* po = out + (((size_t)n * L.out_h + y) * L.out_w + x) * 3;
+                        Store4<OutT>::st(po, o[0][0], o[0][1], o[0][2], o[1][0]);
+                        Store4<OutT>::st(po + 4, o[1][1], o[1][2], o[2][0], o[2][1]);
+                        Store4<OutT>::st(po + 8, o[2][2], o[3][0], o[3][1], o[3][2]);
+                    }
+                } else {
+                    for (int j = 0; j < npx; j++) {
+                        const int k = s.flip_h ? (npx - 1 - j) : j;
+                        float a = k == 0 ? v[0][0] : (k == 1 ? v[1][0] : v[2][0]);
+                        float b = k == 0 ? v[0][1] : (k == 1 ? v[1][1] : v[2][1]);
+                        float c = k == 0 ? v[0][2] : (k == 1 ? v[1][2] : v[2][2]);
+                        pw_store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, x + j, a, b, c);
+                    }
+                }
+            }
+        }
+    }
+    if (L.fill_padding && (w < L.out_w || h < L.out_h)) {
+        const int rows_in_tile = min(L.th, L.out_h - tile_y0);
+        for (int item = threadIdx.x; item < rows_in_tile * L.out_w; item += blockDim.x) {
+            const int row = item / L.out_w;
+            const int x = item - row * L.out_w;
+            const int y = tile_y0 + row;
+            if (y >= h || x >= w) pw_store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, x, 0.f, 0.f, 0.f);
+        }
+    }
+}
+
+// Scalar kernel: one thread per output column, any width and alignment.
 template <typename OutT, int LAYOUT, int COLOR_OP>
 __global__ void __launch_bounds__(256) pointwise_kernel(const uint8_t* __restrict__ arena,
                                                         const rb200_pointwise_sample* __restrict__ samples,
                                                         const PointwiseLaunch L) {
+    __shared__ float rcp[256];
+    if (COLOR_OP == RB200_COLOR_TWIST) {
+        for (int k = threadIdx.x; k < 256; k += blockDim.x) rcp[k] = k ? div_rn(1.0f, (float)k) : 0.f;
+        __syncthreads();
+    }
     const int n = blockIdx.y;
     const int tx = blockIdx.x % L.tiles_x;
     const int ty = blockIdx.x / L.tiles_x;
@@ -100,25 +387,8 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const uint8_t* __restric
             const int y = tile_y0 + j;
             const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
             const uint8_t* px = img + (size_t)sy * s.src_stride + (size_t)sx * 3;
-            float p0 = (float)__ldg(px), p1 = (float)__ldg(px + 1), p2 = (float)__ldg(px + 2);
-            float v0, v1, v2;
-            if (COLOR_OP == RB200_COLOR_BRIGHTNESS) {
-                v0 = sat_round_u8f(add_rn(mul_rn(s.alpha, p0), s.beta));
-                v1 = sat_round_u8f(add_rn(mul_rn(s.alpha, p1), s.beta));
-                v2 = sat_round_u8f(add_rn(mul_rn(s.alpha, p2), s.beta));
-            } else if (COLOR_OP == RB200_COLOR_CONTRAST) {
-                v0 = sat_round_u8f(add_rn(mul_rn(sub_rn(p0, s.beta), s.alpha), s.beta));
-                v1 = sat_round_u8f(add_rn(mul_rn(sub_rn(p1, s.beta), s.alpha), s.beta));
-                v2 = sat_round_u8f(add_rn(mul_rn(sub_rn(p2, s.beta), s.alpha), s.beta));
-            } else if (COLOR_OP == RB200_COLOR_TWIST) {
-                float t0, t1, t2;
-                color_twist_px(p0, p1, p2, s.hue, s.sat, t0, t1, t2);
-                v0 = sat_round_u8f(add_rn(mul_rn(s.alpha, t0), s.beta));
-                v1 = sat_round_u8f(add_rn(mul_rn(s.alpha, t1), s.beta));
-                v2 = sat_round_u8f(add_rn(mul_rn(s.alpha, t2), s.beta));
-            } else {
-                v0 = p0; v1 = p1; v2 = p2;
-            }
+            float v0 = (float)__ldg(px), v1 = (float)__ldg(px + 1), v2 = (float)__ldg(px + 2);
+            color_px<COLOR_OP>(v0, v1, v2, s.alpha, s.beta, s.hue, s.sat, rcp);
             if (L.reverse_channels) { float t = v0; v0 = v2; v2 = t; }
             if (L.normalize) {
                 v0 = fmaf(v0, L.mul[0], L.add[0]);
@@ -137,14 +407,25 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const uint8_t* __restric
     }
 }
 
+template <typename OutT, int LAYOUT, int COLOR_OP>
+static void launch_one(bool vec, dim3 grid, int threads, size_t smem, cudaStream_t stream, const uint8_t* arena,
+                       const rb200_pointwise_sample* samples, const PointwiseLaunch& L) {
+    if (vec) {
+        auto k = pointwise_vec_kernel<OutT, LAYOUT, COLOR_OP>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<grid, threads, smem, stream>>>(arena, samples, L);
+    } else
+        pointwise_kernel<OutT, LAYOUT, COLOR_OP><<<grid, threads, 0, stream>>>(arena, samples, L);
+}
+
 template <typename OutT, int LAYOUT>
-static int launch_color(int color_op, dim3 grid, int tw, cudaStream_t stream, const uint8_t* arena,
+static int launch_color(int color_op, bool vec, dim3 grid, int threads, size_t smem, cudaStream_t stream, const uint8_t* arena,
                         const rb200_pointwise_sample* samples, const PointwiseLaunch& L) {
     switch (color_op) {
-        case RB200_COLOR_NONE: pointwise_kernel<OutT, LAYOUT, RB200_COLOR_NONE><<<grid, tw, 0, stream>>>(arena, samples, L); break;
-        case RB200_COLOR_BRIGHTNESS: pointwise_kernel<OutT, LAYOUT, RB200_COLOR_BRIGHTNESS><<<grid, tw, 0, stream>>>(arena, samples, L); break;
-        case RB200_COLOR_CONTRAST: pointwise_kernel<OutT, LAYOUT, RB200_COLOR_CONTRAST><<<grid, tw, 0, stream>>>(arena, samples, L); break;
-        case RB200_COLOR_TWIST: pointwise_kernel<OutT, LAYOUT, RB200_COLOR_TWIST><<<grid, tw, 0, stream>>>(arena, samples, L); break;
+        case RB200_COLOR_NONE: launch_one<OutT, LAYOUT, RB200_COLOR_NONE>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case RB200_COLOR_BRIGHTNESS: launch_one<OutT, LAYOUT, RB200_COLOR_BRIGHTNESS>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case RB200_COLOR_CONTRAST: launch_one<OutT, LAYOUT, RB200_COLOR_CONTRAST>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case RB200_COLOR_TWIST: launch_one<OutT, LAYOUT, RB200_COLOR_TWIST>(vec, grid, threads, smem, stream, arena, samples, L); break;
         default: set_error("rb200k_pointwise: bad color_op %d", color_op); return RB200_E_INVALID;
     }
     RB200_CHECK_LAUNCH("pointwise_kernel");
@@ -180,6 +461,7 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     L.normalize = p->normalize;
     L.fill_padding = p->fill_padding;
     L.reverse_channels = p->reverse_channels;
+    L.magic = 0x4B000000u;
     for (int c = 0; c < 3; c++) { L.mul[c] = p->mul[c]; L.add[c] = p->add[c]; }
     int ext_w = p->out_w, ext_h = p->out_h;
     if (h_samples && !p->fill_padding) {
@@ -193,14 +475,41 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     }
     L.ext_w = ext_w;
     L.ext_h = ext_h;
-    int tiles_x = (ext_w + 255) / 256;
-    int tw = ((ext_w + tiles_x - 1) / tiles_x + 31) & ~31;
-    L.tiles_x = (ext_w + tw - 1) / tw;
-    L.th = 8;
-    int tiles_y = (ext_h + L.th - 1) / L.th;
-    dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
+    const bool vec = (p->out_w % 4 == 0) && (((uintptr_t)p->out & 15) == 0);
+    dim3 grid;
+    int threads;
+    L.pitch = 0;
+    size_t smem = 0;
+    if (vec) {
+        // a tile = th full source rows staged in shared memory (~16 KB), about 4-5 work items per thread
+        int pitch = (15 + ext_w * 3 + 16 + 15) & ~15;
+        int gpr = (ext_w + 3) / 4;
+        int th = (5 * 256 + gpr - 1) / gpr;
+        if (th * pitch > 24 * 1024) th = 24 * 1024 / pitch;
+        if (th < 1) th = 1;
+        if (th > ext_h) th = ext_h;
+        // keep at least ~4 CTAs per SM in flight for small batches
+        while (th > 1 && (long)n * ((ext_h + th - 1) / th) < 4 * 148) th = (th + 1) / 2;
+        L.th = th;
+        L.pitch = pitch;
+        L.tiles_x = 1;
+        threads = 256;
+        grid = dim3((unsigned)((ext_h + th - 1) / th), (unsigned)n);
+        smem = 16 + 1024 + (size_t)th * pitch;
+        if (smem > 200 * 1024) {
+            set_error("rb200k_pointwise: rows of %d pixels are too wide", ext_w);
+            return RB200_E_LIMIT;
+        }
+    } else {
+        int tiles_x = (ext_w + 255) / 256;
+        threads = ((ext_w + tiles_x - 1) / tiles_x + 31) & ~31;
+        L.tiles_x = (ext_w + threads - 1) / threads;
+        L.th = 8;
+        int tiles_y = (ext_h + L.th - 1) / L.th;
+        grid = dim3((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
+    }
 
-#define RB200_DISPATCH(T, LAY) return launch_color<T, LAY>(p->color_op, grid, tw, stream, arena, samples, L)
+#define RB200_DISPATCH(T, LAY) return launch_color<T, LAY>(p->color_op, vec, grid, threads, smem, stream, arena, samples, L)
     if (p->out_layout == RB200_NCHW) {
         if (p->out_dtype == RB200_FP32) RB200_DISPATCH(float, RB200_NCHW);
         if (p->out_dtype == RB200_FP16) RB200_DISPATCH(__half, RB200_NCHW);
@@ -212,3 +521,13 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     }
 #undef RB200_DISPATCH
 }
+
+namespace rb200 {
+// Reads and clears the time-out flag of the pointwise kernels (used by rb200k_device_status).
+int pointwise_timeout_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_pointwise_timeout, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_pointwise_timeout, &zero, sizeof(int));
+    return v;
+}
+}  // namespace rb200

@@ -1,0 +1,137 @@
+"""Per-operator device-resident benchmark of the kernel C-ABI on the benchmark configurations.
+
+    python -m rocal_b200.opbench [--ops color_twist,warp,box_encoder,ssd_chain,cfg0,brightness,flip] [--steps 50]
+
+Prints one JSON line per operator: images/s, mean launch time (CUDA events on the launching stream),
+algorithmic bytes per launch and the fraction of the measured HBM copy bandwidth. Every operator rotates
+through enough distinct batches that one pass over its inputs and outputs exceeds the 126 MB L2.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+FALLBACK_HBM_GBS = 6650.0
+
+
+def _peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def _time(fn_list, steps, warmup=5):
+    """fn_list: one launch closure per rotating batch. Returns mean ms per launch."""
+    import torch
+    k = len(fn_list)
+    for i in range(warmup):
+        fn_list[i % k]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn_list[i % k]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="cfg0,color_twist,brightness,flip,warp,ssd_chain,box_encoder")
+    ap.add_argument("--steps", type=int, default=50)
+    args = ap.parse_args()
+    import torch
+    from rocal_b200 import kernels as K
+    from rocal_b200 import synthetic as S
+    from rocal_b200 import tables as T
+    dev = torch.device("cuda:0")
+    peak, peak_src = _peak()
+    mul, add = S.normalize_tables()
+
+    def report(name, n, ms, algo_bytes, extra=None):
+        line = {"op": name, "images_per_launch": n, "launch_ms": ms, "images_per_s": n / (ms * 1e-3),
+                "algorithmic_bytes_per_launch": algo_bytes, "achieved_gbs": algo_bytes / (ms * 1e-3) / 1e9,
+                "peak_gbs": peak, "peak_source": peak_src, "frac": algo_bytes / (ms * 1e-3) / 1e9 / peak}
+        if extra:
+            line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    for op in args.ops.split(","):
+        if op == "cfg0":
+            n, rot = 64, 6
+            fns, algo = [], 0.0
+            for r in range(rot):
+                rng = S.rng_for(0, 100 + r)
+                arena, hs, ws, offs = S.make_images(rng, n, (256, 512), (256, 512))
+                t = S.classification_tables(rng, hs, ws, offs)
+                short = np.minimum(hs, ws).astype(np.float64)
+                algo = float((3.0 * (np.ceil(224 / (256 / short)) + 1) ** 2).sum() + n * 3 * 224 * 224 * 4)
+                a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
+                out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device=dev)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
+            report("cfg0 resize+CMN fp32 NCHW (batch 64, 256..512 px)", n, _time(fns, args.steps), algo)
+        elif op in ("color_twist", "brightness", "flip"):
+            n, rot = 256, 4
+            code = {"color_twist": T.COLOR_TWIST, "brightness": T.COLOR_BRIGHTNESS, "flip": T.COLOR_NONE}[op]
+            fns = []
+            for r in range(rot):
+                rng = S.rng_for(2, 100 + r)
+                arena, hs, ws, offs = S.make_images(rng, n, (224, 224), (224, 224), content="noise")
+                t = S.color_twist_tables(rng, hs, ws, offs)
+                a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
+                out = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.pointwise(a, t, 224, 224, code, out=out, d_samples=dt, fill_padding=False))
+            report("cfg2 %s(+flip) u8 HWC 224x224 (batch 256)" % op, n, _time(fns, args.steps), n * 2 * 3 * 224 * 224)
+        elif op == "warp":
+            n, rot = 128, 2
+            fns = []
+            for r in range(rot):
+                rng = S.rng_for(3, 100 + r)
+                arena, hs, ws, offs = S.make_images(rng, n, (480, 480), (640, 640))
+                t = S.warp_tables(rng, hs, ws, offs, 640, 480)
+                a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
+                out = torch.empty((n, 480, 640, 3), dtype=torch.uint8, device=dev)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.warp_affine(a, t, 640, 480, out=out, d_samples=dt))
+            report("cfg3 warp_affine u8 480x640 (batch 128)", n, _time(fns, args.steps), n * 2 * 3 * 480 * 640)
+        elif op == "ssd_chain":
+            n, rot = 128, 2
+            fns, algo = [], 0.0
+            for r in range(rot):
+                rng = S.rng_for(4, 100 + r)
+                arena, hs, ws, offs = S.make_images(rng, n, (300, 800), (300, 800))
+                boxes, labels, boffs = S.random_boxes(rng, n)
+                crops, _, _, _ = S.ssd_random_crop(rng, boxes, labels, boffs)
+                t = S.ssd_resample_tables(rng, hs, ws, offs, crops)
+                algo = float((3.0 * t["roi_w"].astype(np.float64) * t["roi_h"]).sum() + n * 3 * 300 * 300 * 4)
+                a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
+                out = torch.empty((n, 3, 300, 300), dtype=torch.float32, device=dev)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 300, 300, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
+            report("cfg4 crop->resize 300x300->CMN fp32 NCHW (batch 128)", n, _time(fns, args.steps), algo)
+        elif op == "box_encoder":
+            n, rot = 128, 4
+            anchors = torch.from_numpy(S.ssd300_anchors()).to(dev)
+            fns, nbox = [], 0
+            for r in range(rot):
+                rng = S.rng_for(4, 200 + r)
+                boxes, labels, boffs = S.random_boxes(rng, n)
+                nbox = len(labels)
+                b, l, o = torch.from_numpy(boxes).to(dev), torch.from_numpy(labels).to(dev), torch.from_numpy(boffs).to(dev)
+                ob = torch.empty((n, 8732, 4), dtype=torch.float32, device=dev)
+                ol = torch.empty((n, 8732), dtype=torch.int32, device=dev)
+                fns.append(lambda b=b, l=l, o=o, ob=ob, ol=ol: K.box_encode(b, l, o, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0, 50, ob, ol))
+            ms = _time(fns, args.steps)
+            report("cfg4 box_encoder 8732 anchors (batch 128)", n, ms, n * 8732 * 20 + nbox * 20 + 8732 * 16,
+                   {"us_per_batch": ms * 1e3, "boxes_per_batch": nbox})
+        else:
+            print(json.dumps({"op": op, "error": "unknown operator"}))
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, ROOT)
+    main()
