@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                                                             const PointwiseLaunch L) {
     // Layout: mbarrier (16 bytes) | rcp[256] | staged source rows (th x pitch)
     extern __shared__ __align__(16) uint8_t pw_smem[];
+    __shared__ int stage_flag;
     float* rcp = reinterpret_cast<float*>(pw_smem + 16);
     uint8_t* stage = pw_smem + 16 + 1024;
     const uint32_t bar = pw_smem_u32(pw_smem);
@@ -237,12 +238,19 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                              ::"r"(pw_smem_u32(stage + (size_t)r * L.pitch)), "l"(g - m), "r"(bytes), "r"(bar) : "memory");
             }
         }
-        staged_ok = pw_mbar_wait_bounded(bar, 0);
-        if (!staged_ok) {
-            atomicExch(&g_pointwise_timeout, 1);
-            // give copies still in flight a second bounded chance to land before the CTA's memory is released
-            if (threadIdx.x == 0) pw_mbar_wait_bounded(bar, 0);
+        // Warp 0 waits for the copies (bounded); the other warps sleep at the barrier instead of polling.
+        if (threadIdx.x < 32) {
+            const bool ok = pw_mbar_wait_bounded(bar, 0);
+            if (threadIdx.x == 0) {
+                stage_flag = ok ? 1 : 0;
+                if (!ok) {
+                    atomicExch(&g_pointwise_timeout, 1);
+                    pw_mbar_wait_bounded(bar, 0);   // second bounded chance for copies still in flight
+                }
+            }
         }
+        __syncthreads();
+        staged_ok = stage_flag != 0;
     }
 
     if (rows > 0 && w > 0 && staged_ok) {

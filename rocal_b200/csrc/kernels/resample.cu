@@ -901,12 +901,13 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
 }
 
 // Non-zero when a kernel of this library gave up on a bounded wait since the last call (then cleared).
-namespace rb200 { int pointwise_timeout_status(); }
+namespace rb200 { int pointwise_timeout_status(); int warp_timeout_status(); }
 extern "C" int rb200k_device_status(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, rb200::g_resample_timeout, sizeof(int)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(rb200::g_resample_timeout, &zero, sizeof(int));
     int pw = rb200::pointwise_timeout_status();
-    if (pw < 0) return -1;
-    return (v || pw) ? 1 : 0;
+    int wa = rb200::warp_timeout_status();
+    if (pw < 0 || wa < 0) return -1;
+    return (v || pw || wa) ? 1 : 0;
 }
