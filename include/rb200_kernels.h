@@ -187,11 +187,13 @@ typedef struct rb200_box_encoder_params {
 
 /* Matches every anchor of every sample with a ground-truth box and writes the encoded box
  * and label. boxes: device [total][4] ltrb; labels: device [total]; box_offsets: device
- * [n+1] prefix of box counts (sample i owns boxes box_offsets[i] .. box_offsets[i+1]-1, at
- * least one). out_boxes: device [n][num_anchors][4] fp32 (xc,yc,w,h); out_labels: device
+ * [n+1] prefix of box counts (sample i owns boxes box_offsets[i] .. box_offsets[i+1]-1; a
+ * sample without boxes, which the reference does not define, leaves every anchor unmatched).
+ * out_boxes: device [n][num_anchors][4] fp32 (xc,yc,w,h); out_labels: device
  * [n][num_anchors] int32. Tie rules are those of the CPU encoder: the best anchor of a box
  * is the lowest index among equals; the best box of an anchor is the highest index among
- * equals. max_boxes_per_sample must be >= the largest count in the batch (<= 1024).
+ * equals. max_boxes_per_sample must be >= the largest count in the batch (<= 1024);
+ * num_anchors <= 65536, n <= 65535. boxes, anchors and out_boxes must be 16-byte aligned.
  * replaces: BoundingBoxGraph::update_box_encoder_meta_data
  *           (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) and BoxEncoderGpu::Run +
  *           BoxEncode<256> (rocAL/rocAL_hip/box_encoder_hip.cpp:123-278).

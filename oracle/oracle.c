@@ -327,13 +327,15 @@ ORC_API int orc_box_encode(const float* boxes, const int32_t* labels, const int3
         for (int a = 0; a < A; a++) {
             const float* an = anchors + a * 4;
             int best = 0;
-            float best_iou = ious[a];
+            /* A sample without boxes: the reference reads the first IoU row regardless (undefined
+             * behaviour there); here every anchor of such a sample is unmatched. */
+            float best_iou = nb > 0 ? ious[a] : -1.f;
             for (int b = 1; b < nb; b++) {
                 float v = ious[(size_t)b * A + a];
                 if (v >= best_iou) { best_iou = v; best = b; }
             }
             const float* box = bb + best * 4;
-            if (ious[(size_t)best * A + a] > criteria) {
+            if (nb > 0 && ious[(size_t)best * A + a] > criteria) {
                 float xc, yc, w, h;
                 if (offset) {
                     xc = (box[0] + box[2]) * half_scale;

@@ -84,27 +84,6 @@ __device__ __forceinline__ void store3(OutT* out, int out_w, int out_h, int n, i
     }
 }
 
-// ---- packed f32x2 arithmetic (sm_100): both lanes rounded independently, round-to-nearest ----
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
-    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b);
-    unsigned long long rc = *reinterpret_cast<unsigned long long*>(&c), rd;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-    return *reinterpret_cast<float2*>(&rd);
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
-    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b), rd;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-    return *reinterpret_cast<float2*>(&rd);
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a);
-    unsigned long long rb = *reinterpret_cast<unsigned long long*>(&b), rd;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-    return *reinterpret_cast<float2*>(&rd);
-}
-
 // Byte `sel & 7` of (w, magic = 0x4B000000) placed in the mantissa of 2^23: the float 8388608 + byte.
 __device__ __forceinline__ float byte_magic(uint32_t w, uint32_t magic, uint32_t sel) {
     return __uint_as_float(__byte_perm(w, magic, sel));

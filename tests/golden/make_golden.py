@@ -5,6 +5,7 @@ the reference tree by oracle/build.py). Run in a container that has the referenc
 
 box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
                   (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
+box_encoder_degenerate.npz   the same on zero-area / inverted boxes and a degenerate anchor 0
 param_rng.npz     UniformRand<float>, UniformRand<int>, CustomRand<int> draws
                   (rocAL/include/parameters/parameter_random.h) and the std::seed_seq table of
                   ParameterFactory::set_seed (rocAL/source/parameters/parameter_factory.cpp:114-119)
@@ -48,6 +49,26 @@ def main():
         out[name + "_args"] = np.array([crit, *means, *stds, float(offset), scale], dtype=np.float64)
     np.savez_compressed(os.path.join(HERE, "box_encoder.npz"), **out)
 
+    # Degenerate geometry: zero-area and inverted boxes, a degenerate anchor 0 (0/0 IoUs, negative IoUs).
+    # Every sample has at least one box: the reference indexes the first IoU row of a sample unconditionally.
+    rng = np.random.Generator(np.random.PCG64(4243))
+    anchors = S.ssd300_anchors()[::5][:1500].copy()
+    anchors[0] = (0.0, 0.0, 0.0, 0.0)
+    counts = [4, 6, 1, 3]
+    boxes, _, _ = S.random_boxes(rng, 1, (sum(counts), sum(counts)))
+    boxes[0] = (0.3, 0.3, 0.3, 0.3)
+    boxes[1] = (0.6, 0.6, 0.2, 0.2)
+    boxes[4] = (0.0, 0.0, 0.0, 0.0)
+    boxes[10] = (0.5, 0.2, 0.5, 0.9)
+    boxes[11] = boxes[12] = (0.25, 0.25, 0.25, 0.25)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    labels = rng.integers(1, 81, len(boxes)).astype(np.int32)
+    out = {"anchors": anchors, "boxes": boxes, "labels": labels, "offsets": offsets}
+    for name, offset in (("offset", True), ("plain", False)):
+        eb, el = O.ref_box_encode(boxes, labels, offsets, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), offset, 1.0)
+        out[name + "_boxes"], out[name + "_labels"] = eb, el
+    np.savez_compressed(os.path.join(HERE, "box_encoder_degenerate.npz"), **out)
+
     rngs = {}
     f = np.zeros(3 * 16, dtype=np.float32)
     ref.ref_uniform_rand_float(ctypes.c_uint(123), ctypes.c_float(0.6), ctypes.c_float(1.4), ctypes.c_uint(16), ctypes.c_uint(3),
@@ -68,7 +89,7 @@ def main():
         ref.ref_seed_sequence(ctypes.c_uint(seed), ctypes.c_uint(1024), t.ctypes.data_as(ctypes.c_void_p))
         rngs["seed_seq_%d" % seed] = t
     np.savez_compressed(os.path.join(HERE, "param_rng.npz"), **rngs)
-    print("wrote box_encoder.npz, param_rng.npz")
+    print("wrote box_encoder.npz, box_encoder_degenerate.npz, param_rng.npz")
 
 
 if __name__ == "__main__":

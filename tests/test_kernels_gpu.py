@@ -251,6 +251,38 @@ def test_rotate_fixed_and_identity(cuda):
                     assert np.array_equal(got[i, :h - 1, :w - 1], img[:h - 1, :w - 1])
 
 
+def test_warp_affine_edges(cuda):
+    """Output width not a multiple of four (byte stores), strong minification (footprint too large to
+    stage: global gathers), 1-pixel-wide and 1-pixel-high sources, a table holding NaN and huge entries,
+    destination smaller than the output canvas with and without zero fill."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(16)
+    arena, hs, ws, offs = S.make_images(rng, 8, (1, 200), (1, 300))
+    hs, ws = hs.copy(), ws.copy()
+    n = len(hs)
+    t = np.zeros(n, dtype=T.WARP_SAMPLE)
+    # sources narrower than their allocation: the stride stays that of the allocation
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    ws[0], hs[1] = 1, 1
+    t["src_w"], t["src_h"] = ws, hs
+    mats = np.stack([S.rotate_matrix(a) for a in (0.0, 10.0, 33.0, 90.0, 181.0, -45.0, 5.0, 60.0)])
+    mats[2, :4] *= 6.0            # minification by 6: staged footprint exceeds the shared-memory budget
+    mats[3, :4] *= 0.2            # magnification by 5
+    mats[4, 4:] = (7.25, -3.5)
+    mats[6, 0] = np.nan
+    mats[7, 1] = 3.0e38
+    t["m"][:] = mats
+    for out_w, out_h, dw, dh in ((117, 93, 117, 93), (160, 96, 101, 77), (64, 64, 200, 200)):
+        t["dst_w"], t["dst_h"] = dw, dh
+        for fill in (True, False):
+            base = np.full((n, out_h, out_w, 3), 7, dtype=np.uint8)
+            ref = O.warp_affine(arena, t, out_w, out_h, fill_padding=fill, out=base.copy())
+            got = K.warp_affine(_dev(arena, cuda), t, out_w, out_h, fill_padding=fill,
+                                out=torch.from_numpy(base.copy()).to(cuda)).cpu().numpy()
+            assert np.array_equal(got, ref), (out_w, out_h, dw, dh, fill)
+
+
 @pytest.mark.parametrize("offset", [True, False])
 def test_box_encoder_config4(cuda, offset):
     """configs[4]: 128 samples, 1..50 boxes, 8732 anchors, criteria 0.5; labels (matched indices)
@@ -293,6 +325,40 @@ def test_box_encoder_ties_and_chunks(cuda):
                               (0.1, 0.1, 0.2, 0.2), offset, scale, 100)
         assert np.array_equal(gl.cpu().numpy(), rl)
         _assert_fp(gb.cpu().numpy(), rb, 1e-5, "encoded boxes")
+
+
+def test_box_encoder_degenerate_and_large_tables(cuda):
+    """Zero-area and inverted boxes (IoU 0/0 = NaN and negative IoU follow the CPU loop's seeding rules),
+    a sample without boxes, and anchor tables large enough for the 8- and 16-anchors-per-thread kernels."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(17)
+    base = S.ssd300_anchors()
+    counts = [4, 0, 6, 1, 3]
+    boxes, _, _ = S.random_boxes(rng, 1, (sum(counts), sum(counts)))
+    boxes[0] = (0.3, 0.3, 0.3, 0.3)                 # a point: area 0
+    boxes[1] = (0.6, 0.6, 0.2, 0.2)                 # inverted
+    boxes[4] = (0.0, 0.0, 0.0, 0.0)                 # equals the degenerate anchor below
+    boxes[10] = (0.5, 0.2, 0.5, 0.9)                # zero width
+    boxes[11] = boxes[12] = (0.25, 0.25, 0.25, 0.25)
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    labels = rng.integers(1, 81, len(boxes)).astype(np.int32)
+    for num in (37, 8732, 20000, 40000):
+        reps = -(-num // len(base))
+        jitter = rng.uniform(-0.01, 0.01, (reps * len(base), 4)).astype(np.float32)
+        anchors = np.ascontiguousarray((np.tile(base, (reps, 1)) + jitter)[:num])
+        anchors[0] = (0.0, 0.0, 0.0, 0.0)           # anchor 0 degenerate: its IoU with a point box is NaN
+        for offset in (True, False):
+            rb, rl = O.box_encode(boxes, labels, offs, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), offset, 1.0)
+            gb, gl = K.box_encode(torch.from_numpy(boxes).to(cuda), torch.from_numpy(labels).to(cuda),
+                                  torch.from_numpy(offs).to(cuda), torch.from_numpy(anchors).to(cuda), 0.5,
+                                  (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), offset, 1.0, 50)
+            assert np.array_equal(gl.cpu().numpy(), rl), (num, offset)
+            got, ref = gb.cpu().numpy(), rb
+            assert np.array_equal(np.isnan(got), np.isnan(ref)), (num, offset)
+            assert np.array_equal(np.isinf(got), np.isinf(ref)), (num, offset)
+            fin = np.isfinite(ref)
+            _assert_fp(got[fin], ref[fin], 1e-5, "encoded boxes")
 
 
 def test_ssd_chain_config4(cuda):

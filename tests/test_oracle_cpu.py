@@ -25,6 +25,16 @@ def test_box_encoder_matches_golden():
         assert (el > 0).sum() > 0
 
 
+def test_box_encoder_degenerate_matches_golden():
+    """Zero-area and inverted boxes, degenerate anchor 0: NaN and negative IoUs follow the reference's seeding."""
+    g = np.load(os.path.join(GOLDEN, "box_encoder_degenerate.npz"))
+    for name, offset in (("offset", True), ("plain", False)):
+        eb, el = O.box_encode(g["boxes"], g["labels"], g["offsets"], g["anchors"], 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2),
+                              offset, 1.0)
+        assert np.array_equal(el, g[name + "_labels"]), name
+        assert np.array_equal(eb, g[name + "_boxes"], equal_nan=True), name
+
+
 def test_box_encoder_matches_reference_build():
     if O.ref() is None:
         pytest.skip("reference tree not present: oracle/_ref/libref.so cannot be built")
