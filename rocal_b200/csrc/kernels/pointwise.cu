@@ -89,24 +89,47 @@ __device__ __forceinline__ void color_twist_px(float r, float g, float b, float 
     o2 = hsv_channel(cmax, vs, hp, 1.f);
 }
 
+// The colour result before rounding and saturation.
 template <int COLOR_OP>
-__device__ __forceinline__ void color_px(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
-                                         const float* rcp) {
+__device__ __forceinline__ void color_raw(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
+                                          const float* rcp) {
     if (COLOR_OP == RB200_COLOR_BRIGHTNESS) {
-        v0 = sat_round_u8f(add_rn(mul_rn(alpha, v0), beta));
-        v1 = sat_round_u8f(add_rn(mul_rn(alpha, v1), beta));
-        v2 = sat_round_u8f(add_rn(mul_rn(alpha, v2), beta));
+        v0 = add_rn(mul_rn(alpha, v0), beta);
+        v1 = add_rn(mul_rn(alpha, v1), beta);
+        v2 = add_rn(mul_rn(alpha, v2), beta);
     } else if (COLOR_OP == RB200_COLOR_CONTRAST) {
-        v0 = sat_round_u8f(add_rn(mul_rn(sub_rn(v0, beta), alpha), beta));
-        v1 = sat_round_u8f(add_rn(mul_rn(sub_rn(v1, beta), alpha), beta));
-        v2 = sat_round_u8f(add_rn(mul_rn(sub_rn(v2, beta), alpha), beta));
+        v0 = add_rn(mul_rn(sub_rn(v0, beta), alpha), beta);
+        v1 = add_rn(mul_rn(sub_rn(v1, beta), alpha), beta);
+        v2 = add_rn(mul_rn(sub_rn(v2, beta), alpha), beta);
     } else if (COLOR_OP == RB200_COLOR_TWIST) {
         float t0, t1, t2;
         color_twist_px(v0, v1, v2, hue, sat, rcp, t0, t1, t2);
-        v0 = sat_round_u8f(add_rn(mul_rn(alpha, t0), beta));
-        v1 = sat_round_u8f(add_rn(mul_rn(alpha, t1), beta));
-        v2 = sat_round_u8f(add_rn(mul_rn(alpha, t2), beta));
+        v0 = add_rn(mul_rn(alpha, t0), beta);
+        v1 = add_rn(mul_rn(alpha, t1), beta);
+        v2 = add_rn(mul_rn(alpha, t2), beta);
     }
+}
+
+template <int COLOR_OP>
+__device__ __forceinline__ void color_px(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
+                                         const float* rcp) {
+    if (COLOR_OP != RB200_COLOR_NONE) {
+        color_raw<COLOR_OP>(v0, v1, v2, alpha, beta, hue, sat, rcp);
+        v0 = sat_round_u8f(v0);
+        v1 = sat_round_u8f(v1);
+        v2 = sat_round_u8f(v2);
+    }
+}
+
+// Round to nearest even and saturate to [0,255] in one conversion (NaN gives 0): the same result as
+// sat_round_u8f, as an integer.
+__device__ __forceinline__ uint32_t cvt_sat_u8(float v) {
+    uint32_t r;
+    asm("cvt.rni.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack4_u8(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
 }
 
 template <typename OutT, int LAYOUT>
@@ -259,6 +282,16 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
         // item / gpr by multiply-high: exact while item * gpr < 2^32
         const uint32_t gpr_magic = (uint32_t)((0x100000000ull + (uint32_t)gpr - 1) / (uint32_t)gpr);
         const bool bytes_only = COLOR_OP == RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels;
+        // Per-thread constants of the index arithmetic: source row of tile row r is sy0 + sy_step * r; a
+        // staged row starts at the source row's address rounded down to 16 bytes, so the block of group
+        // column x sits at (row address mod 16) + 3 * (x, or w - x - npx under a horizontal flip).
+        const int sy0 = s.roi_y + (s.flip_v ? (s.roi_h - 1 - tile_y0) : tile_y0);
+        const int sy_step = s.flip_v ? -1 : 1;
+        const uint32_t base_mod = (uint32_t)((uintptr_t)(img + (size_t)x_src0 * 3) & 15);
+        const uint32_t stride_mod = s.src_stride & 15;
+        // element (tile row 0, column 0) of the output; an item adds a 32-bit offset
+        OutT* const out_tile = out + (LAYOUT == RB200_NCHW ? ((size_t)n * 3) * plane + (size_t)tile_y0 * L.out_w
+                                                             : ((size_t)n * L.out_h + tile_y0) * L.out_w * 3);
         // Two work items per iteration: all eight loads are issued before the first use.
         for (int item0 = threadIdx.x; item0 < items; item0 += 2 * blockDim.x) {
             uint32_t wv[2][4];
@@ -270,23 +303,18 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                 npxv[u] = 0;
                 if (item < items) {
                     const int row = gpr == 1 ? item : (int)__umulhi((uint32_t)item, gpr_magic);
-                    const int g = item - row * gpr;
-                    const int x = g << 2;
-                    const int y = tile_y0 + row;
+                    const int x = (item - row * gpr) << 2;
                     const int npx = min(4, w - x);
-                    const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
-                    const int sx = s.flip_h ? (s.roi_x + s.roi_w - 1 - (x + npx - 1)) : (s.roi_x + x);
-                    // byte position of the block inside its staged row: the copy started at the row's
-                    // address rounded down to 16 bytes
-                    const uint32_t m = (uint32_t)((uintptr_t)(img + (size_t)sy * s.src_stride + (size_t)x_src0 * 3) & 15);
-                    const uint32_t boff = (uint32_t)row * L.pitch + m + (uint32_t)(sx - x_src0) * 3;
+                    const int sy = sy0 + sy_step * row;
+                    const uint32_t m = (base_mod + (uint32_t)sy * stride_mod) & 15u;
+                    const uint32_t boff = (uint32_t)row * L.pitch + m + (uint32_t)(s.flip_h ? (w - x - npx) : x) * 3u;
                     const uint32_t* wp = reinterpret_cast<const uint32_t*>(stage + (boff & ~3u));
                     wv[u][0] = wp[0];
                     wv[u][1] = wp[1];
                     wv[u][2] = wp[2];
                     wv[u][3] = wp[3];
-                    shv[u] = (boff & 3u) << 3;
-                    xv[u] = x; yv[u] = y; npxv[u] = npx;
+                    shv[u] = boff << 3;      // the funnel shift reads the low five bits
+                    xv[u] = x; yv[u] = tile_y0 + row; npxv[u] = npx;
                 }
             }
 #pragma unroll
@@ -294,15 +322,63 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                 const int npx = npxv[u];
                 if (npx == 0) continue;
                 const int x = xv[u], y = yv[u];
+                // element offset of the block's first output pixel inside the tile
+                const uint32_t eoff = (uint32_t)((y - tile_y0) * L.out_w + x) * (LAYOUT == RB200_NCHW ? 1u : 3u);
                 uint32_t d[3];
                 d[0] = __funnelshift_r(wv[u][0], wv[u][1], shv[u]);
                 d[1] = __funnelshift_r(wv[u][1], wv[u][2], shv[u]);
                 d[2] = __funnelshift_r(wv[u][2], wv[u][3], shv[u]);
                 if (bytes_only && npx == 4) {
-                    uint8_t* pb = reinterpret_cast<uint8_t*>(out) +
-                                  (LAYOUT == RB200_NCHW ? ((size_t)n * 3) * plane + (size_t)y * L.out_w + x
-                                                        : (((size_t)n * L.out_h + y) * L.out_w + x) * 3);
+                    uint8_t* pb = reinterpret_cast<uint8_t*>(out_tile) + eoff;
                     permute_store_u8<LAYOUT>(pb, plane, d, s.flip_h != 0);
+                    continue;
+                }
+                if (COLOR_OP != RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels && npx == 4) {
+                    // uint8 in, uint8 out: the 12 result bytes are rebuilt in block order and leave through the
+                    // same byte permutation as a plain crop / flip.
+                    uint32_t e[3];
+                    if (COLOR_OP == RB200_COLOR_TWIST) {
+                        uint32_t q[12];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            float c3[3];
+#pragma unroll
+                            for (int c = 0; c < 3; c++) {
+                                const int bidx = 3 * k + c;
+                                c3[c] = sub_rn(__uint_as_float(__byte_perm(d[bidx >> 2], L.magic, 0x7650u + (bidx & 3))), 8388608.0f);
+                            }
+                            color_raw<COLOR_OP>(c3[0], c3[1], c3[2], s.alpha, s.beta, s.hue, s.sat, rcp);
+#pragma unroll
+                            for (int c = 0; c < 3; c++) q[3 * k + c] = cvt_sat_u8(c3[c]);
+                        }
+#pragma unroll
+                        for (int wd = 0; wd < 3; wd++) e[wd] = pack4_u8(q[4 * wd], q[4 * wd + 1], q[4 * wd + 2], q[4 * wd + 3]);
+                    } else {
+                        // brightness / contrast: two bytes per packed f32x2 instruction
+                        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
+                        const float2 a2 = make_float2(s.alpha, s.alpha), b2 = make_float2(s.beta, s.beta);
+                        const float2 nb2 = make_float2(-s.beta, -s.beta);
+#pragma unroll
+                        for (int wd = 0; wd < 3; wd++) {
+                            uint32_t q[4];
+#pragma unroll
+                            for (int hb = 0; hb < 4; hb += 2) {
+                                float2 x;
+                                x.x = __uint_as_float(__byte_perm(d[wd], L.magic, 0x7650u + hb));
+                                x.y = __uint_as_float(__byte_perm(d[wd], L.magic, 0x7651u + hb));
+                                x = add2(x, nk23);
+                                if (COLOR_OP == RB200_COLOR_BRIGHTNESS)
+                                    x = add2(mul2(a2, x), b2);
+                                else
+                                    x = add2(mul2(add2(x, nb2), a2), b2);
+                                q[hb] = cvt_sat_u8(x.x);
+                                q[hb + 1] = cvt_sat_u8(x.y);
+                            }
+                            e[wd] = pack4_u8(q[0], q[1], q[2], q[3]);
+                        }
+                    }
+                    uint8_t* pb = reinterpret_cast<uint8_t*>(out_tile) + eoff;
+                    permute_store_u8<LAYOUT>(pb, plane, e, s.flip_h != 0);
                     continue;
                 }
                 // block pixel k, channel c = byte 3k+c of d[]
@@ -333,12 +409,12 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                             if (sizeof(OutT) == 1 && L.normalize) o[j][c] = sat_round_u8f(o[j][c]);
                         }
                     if (LAYOUT == RB200_NCHW) {
-                        OutT* po = out + ((size_t)n * 3) * plane + (size_t)y * L.out_w + x;
+                        OutT* po = out_tile + eoff;
                         Store4<OutT>::st(po, o[0][0], o[1][0], o[2][0], o[3][0]);
                         Store4<OutT>::st(po + plane, o[0][1], o[1][1], o[2][1], o[3][1]);
                         Store4<OutT>::st(po + 2 * plane, o[0][2], o[1][2], o[2][2], o[3][2]);
                     } else {
-                        OutT* po = out + (((size_t)n * L.out_h + y) * L.out_w + x) * 3;
+                        OutT* po = out_tile + eoff;
                         Store4<OutT>::st(po, o[0][0], o[0][1], o[0][2], o[1][0]);
                         Store4<OutT>::st(po + 4, o[1][1], o[1][2], o[2][0], o[2][1]);
                         Store4<OutT>::st(po + 8, o[2][2], o[3][0], o[3][1], o[3][2]);
