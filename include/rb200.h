@@ -38,6 +38,20 @@ RB200_API const char* rb200_get_error_message(rb200_context ctx);
 RB200_API void rb200_get_timing(rb200_context ctx, unsigned long long out_load_decode_process_transfer[4]);
 /* rocalGetRemainingImages / rocalIsEmpty (rocal_api_info.h:66-74): fed but not yet returned samples */
 RB200_API size_t rb200_get_remaining_images(rb200_context ctx);
+/* Extensions without a reference counterpart: how host-resident source pixels reach the kernels.
+ *   RB200_UPLOAD_WHOLE      every image is copied to the device whole;
+ *   RB200_UPLOAD_FOOTPRINT  one strided copy per image of the rectangle the batch's kernels can read
+ *                           (the crop window mapped back through the resize);
+ *   RB200_UPLOAD_ZERO_COPY  (default) a batch fed with rb200_feed_ragged from RB200_MEM_HOST_PINNED memory
+ *                           that one resample or pointwise step consumes is not copied: the kernel's bulk
+ *                           copies read the rows it needs from the pinned buffer, which must stay valid and
+ *                           unchanged until rb200_run has returned that batch. Other batches fall back to
+ *                           RB200_UPLOAD_FOOTPRINT.
+ * rb200_get_h2d_bytes returns the bytes that have crossed to the device for the context so far (pixels -
+ * in zero-copy mode the footprint rectangles - plus per-sample tables and boxes). */
+enum { RB200_UPLOAD_WHOLE = 0, RB200_UPLOAD_FOOTPRINT = 1, RB200_UPLOAD_ZERO_COPY = 2 };
+RB200_API unsigned long long rb200_get_h2d_bytes(rb200_context ctx);
+RB200_API int rb200_set_upload_mode(rb200_context ctx, int mode);
 
 /* ---- parameters (rocal_api_parameters.h:39-161) ---- */
 RB200_API void rb200_set_seed(unsigned seed);

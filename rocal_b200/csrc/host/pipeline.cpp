@@ -816,29 +816,108 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
     }
 }
 
+// The rectangle of source image i that the kernels of this batch can read, from the step tables that
+// were just built: every step that consumes the source tensor contributes the bounding box of its taps
+// (resample: crop window of the resized image mapped back through the ratio, with a margin that covers the
+// half-pixel offset, both taps and rounding; pointwise: its window). Steps whose reach is not a simple
+// rectangle (affine gathers), or a source that is itself an output, ask for the whole image.
+bool Pipeline::source_footprint(const uint8_t* h_tab, size_t i, int W, int H, int& x0, int& y0, int& x1, int& y1) const {
+    const size_t n = _batch;
+    if (_tensors[_source]->is_output) return false;
+    int fx0 = W, fy0 = H, fx1 = -1, fy1 = -1;
+    bool any = false;
+    for (size_t k = 0; k < _steps.size(); k++) {
+        const Step& st = _steps[k];
+        if (st.in_tensor != _source) continue;
+        int ax0, ay0, ax1, ay1;
+        if (st.kind == Step::RESAMPLE) {
+            const rb200_resample_sample& q = reinterpret_cast<const rb200_resample_sample*>(h_tab + k * n * 64)[i];
+            if (q.dst_w <= 0 || q.dst_h <= 0 || q.roi_w <= 0 || q.roi_h <= 0) return false;
+            const double rx = (double)q.roi_w / q.dst_w, ry = (double)q.roi_h / q.dst_h;
+            ax0 = q.roi_x + (int)std::floor(q.crop_x * rx - 1.0) - 1;
+            ay0 = q.roi_y + (int)std::floor(q.crop_y * ry - 1.0) - 1;
+            ax1 = q.roi_x + (int)std::ceil((q.crop_x + q.crop_w) * rx) + 2;
+            ay1 = q.roi_y + (int)std::ceil((q.crop_y + q.crop_h) * ry) + 2;
+            ax0 = std::max(ax0, q.roi_x); ay0 = std::max(ay0, q.roi_y);
+            ax1 = std::min(ax1, q.roi_x + q.roi_w - 1); ay1 = std::min(ay1, q.roi_y + q.roi_h - 1);
+        } else if (st.kind == Step::POINTWISE) {
+            const rb200_pointwise_sample& q = reinterpret_cast<const rb200_pointwise_sample*>(h_tab + k * n * 64)[i];
+            ax0 = q.roi_x; ay0 = q.roi_y; ax1 = q.roi_x + q.roi_w - 1; ay1 = q.roi_y + q.roi_h - 1;
+        } else {
+            return false;
+        }
+        fx0 = std::min(fx0, ax0); fy0 = std::min(fy0, ay0);
+        fx1 = std::max(fx1, ax1); fy1 = std::max(fy1, ay1);
+        any = true;
+    }
+    if (!any) return false;
+    x0 = std::max(fx0, 0); y0 = std::max(fy0, 0);
+    x1 = std::min(fx1, W - 1); y1 = std::min(fy1, H - 1);
+    return x0 <= x1 && y0 <= y1;
+}
+
+// Host -> device copy of the batch's source pixels into arena `a`. Only the footprint rectangle of every
+// image travels (one strided copy per image, placed where the whole image would be, so tables and kernels
+// do not change); when the footprints add up to nearly everything a ragged arena goes up in one copy.
+void Pipeline::upload_sources(InputBatch& b, int a, const uint8_t* h_tab) {
+    const size_t n = _batch;
+    TensorImpl* src = _tensors[_source].get();
+    std::vector<int> rect(n * 4);
+    size_t need = 0, full = 0;
+    for (size_t i = 0; i < n; i++) {
+        const int W = src->roi_w[i], H = src->roi_h[i];
+        int x0 = 0, y0 = 0, x1 = W - 1, y1 = H - 1;
+        if (_upload_mode != UPLOAD_WHOLE) source_footprint(h_tab, i, W, H, x0, y0, x1, y1);
+        rect[i * 4] = x0; rect[i * 4 + 1] = y0; rect[i * 4 + 2] = x1; rect[i * 4 + 3] = y1;
+        need += (size_t)(x1 - x0 + 1) * (y1 - y0 + 1) * 3;
+        full += (size_t)W * H * 3;
+    }
+    if (a < 0) {            // zero copy: the kernels fetch (at most) these rectangles themselves
+        _h2d_bytes += need;
+        return;
+    }
+    uint8_t* dst = (uint8_t*)_arena[a];
+    if (b.kind == InputBatch::RAGGED && (double)need > 0.9 * (double)b.arena_bytes) {
+        RB200_CUDA(cudaMemcpyAsync(dst, b.arena, b.arena_bytes, cudaMemcpyHostToDevice, _stream));
+        _h2d_bytes += b.arena_bytes;
+        return;
+    }
+    for (size_t i = 0; i < n; i++) {
+        const int x0 = rect[i * 4], y0 = rect[i * 4 + 1], x1 = rect[i * 4 + 2], y1 = rect[i * 4 + 3];
+        if (x1 < x0 || y1 < y0) continue;
+        const size_t dpitch = _src_views[i].stride;
+        const size_t width = (size_t)(x1 - x0 + 1) * 3, height = (size_t)(y1 - y0 + 1);
+        uint8_t* d = dst + _src_views[i].offset + (size_t)y0 * dpitch + (size_t)x0 * 3;
+        const uint8_t* h;
+        size_t spitch;
+        if (b.kind == InputBatch::RAGGED) {
+            spitch = dpitch;
+            h = (const uint8_t*)b.arena + _src_views[i].offset + (size_t)y0 * spitch + (size_t)x0 * 3;
+        } else {
+            spitch = (size_t)b.max_w * 3;
+            h = b.bufs[i] + ((size_t)(b.roi[i * 4 + 1] + y0) * b.max_w + b.roi[i * 4] + x0) * 3;
+        }
+        RB200_CUDA(cudaMemcpy2DAsync(d, dpitch, h, spitch, width, height, cudaMemcpyHostToDevice, _stream));
+        _h2d_bytes += width * height;
+    }
+}
+
 void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     const size_t n = _batch;
     TensorImpl* src = _tensors[_source].get();
     unsigned long long t0 = now_us();
 
-    // ---- 1. input: device views of the n source images ----
+    // ---- 1. input: device views of the n source images (the upload itself follows the tables) ----
     _src_views.resize(n);
+    const bool host_input = !(b.kind == InputBatch::RAGGED && b.mem_kind == RB200_MEM_DEVICE);
+    int arena_used = -1;
     if (b.kind == InputBatch::RAGGED) {
         for (size_t i = 0; i < n; i++) {
             _src_views[i] = {b.descs[i].offset, b.descs[i].stride};
             src->roi_w[i] = (int)b.descs[i].width;
             src->roi_h[i] = (int)b.descs[i].height;
         }
-        if (b.mem_kind == RB200_MEM_DEVICE) {
-            _src_base = (const uint8_t*)b.arena;
-        } else {
-            int a = _arena_next;
-            _arena_next ^= 1;
-            RB200_CUDA(cudaEventSynchronize(_arena_free[a]));
-            ensure_arena(a, b.arena_bytes);
-            RB200_CUDA(cudaMemcpyAsync(_arena[a], b.arena, b.arena_bytes, cudaMemcpyHostToDevice, _stream));
-            _src_base = (const uint8_t*)_arena[a];
-        }
+        if (!host_input) _src_base = (const uint8_t*)b.arena;
     } else {
         size_t total = 0;
         for (size_t i = 0; i < n; i++) {
@@ -848,19 +927,37 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             src->roi_h[i] = (int)h;
             total += ((size_t)w * h * 3 + 255) & ~(size_t)255;
         }
-        int a = _arena_next;
-        _arena_next ^= 1;
-        RB200_CUDA(cudaEventSynchronize(_arena_free[a]));
-        ensure_arena(a, total + 256);
-        for (size_t i = 0; i < n; i++) {
-            unsigned x = b.roi[i * 4], y = b.roi[i * 4 + 1], w = b.roi[i * 4 + 2], h = b.roi[i * 4 + 3];
-            const unsigned char* p = b.bufs[i] + ((size_t)y * b.max_w + x) * 3;
-            RB200_CUDA(cudaMemcpy2DAsync((uint8_t*)_arena[a] + _src_views[i].offset, (size_t)w * 3, p, (size_t)b.max_w * 3,
-                                         (size_t)w * 3, h, cudaMemcpyHostToDevice, _stream));
-        }
-        _src_base = (const uint8_t*)_arena[a];
+        b.arena_bytes = total + 256;
     }
-    int arena_used = (b.kind == InputBatch::RAGGED && b.mem_kind == RB200_MEM_DEVICE) ? -1 : (_arena_next ^ 1);
+    // Pinned host input that exactly one staging kernel consumes is not uploaded at all: the kernel's bulk
+    // copies read the tap rows straight from host memory, so only the bytes the batch needs cross the link.
+    bool zero_copy = false;
+    if (host_input && _upload_mode == UPLOAD_ZERO_COPY && b.kind == InputBatch::RAGGED &&
+        b.mem_kind == RB200_MEM_HOST_PINNED && !src->is_output) {
+        int consumers = 0;
+        bool gather = false;
+        for (const Step& st : _steps)
+            if (st.in_tensor == _source) {
+                consumers++;
+                gather = gather || st.kind == Step::WARP;
+            }
+        if (consumers == 1 && !gather) {
+            void* dp = nullptr;
+            if (cudaHostGetDevicePointer(&dp, const_cast<void*>(b.arena), 0) == cudaSuccess && dp) {
+                _src_base = (const uint8_t*)dp;
+                zero_copy = true;
+            } else {
+                cudaGetLastError();   // not mapped into the device's address space: upload instead
+            }
+        }
+    }
+    if (host_input && !zero_copy) {
+        arena_used = _arena_next;
+        _arena_next ^= 1;
+        RB200_CUDA(cudaEventSynchronize(_arena_free[arena_used]));
+        ensure_arena(arena_used, b.arena_bytes);
+        _src_base = (const uint8_t*)_arena[arena_used];
+    }
     _t_load += now_us() - t0;
     t0 = now_us();
 
@@ -983,8 +1080,15 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             }
         }
     }
-    if (!_steps.empty())
+    if (host_input) {
+        unsigned long long tl = now_us();
+        upload_sources(b, arena_used, (const uint8_t*)s.h_tables);
+        _t_load += now_us() - tl;
+    }
+    if (!_steps.empty()) {
         RB200_CUDA(cudaMemcpyAsync(s.d_tables, s.h_tables, _steps.size() * n * 64, cudaMemcpyHostToDevice, _stream));
+        _h2d_bytes += _steps.size() * n * 64;
+    }
 
     // ---- 3. launches ----
     for (size_t k = 0; k < _steps.size(); k++) {
@@ -1073,6 +1177,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         RB200_CUDA(cudaMemcpyAsync(_d_boxes, hb, total * 4 * sizeof(float), cudaMemcpyHostToDevice, _stream));
         RB200_CUDA(cudaMemcpyAsync(_d_labels, hl, total * sizeof(int), cudaMemcpyHostToDevice, _stream));
         RB200_CUDA(cudaMemcpyAsync(_d_offsets, ho, (n + 1) * sizeof(int), cudaMemcpyHostToDevice, _stream));
+        _h2d_bytes += total * 20 + (n + 1) * sizeof(int);
         int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _stream);
         if (rc != 0) RB200_THROW(rb200k_last_error());
     }

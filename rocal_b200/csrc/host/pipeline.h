@@ -147,6 +147,9 @@ struct SampleView {
     uint32_t stride;
 };
 
+// How host-resident source pixels reach the kernels.
+enum UploadMode { UPLOAD_WHOLE = 0, UPLOAD_FOOTPRINT = 1, UPLOAD_ZERO_COPY = 2 };
+
 struct InputBatch {
     enum Kind { SLOTS, RAGGED } kind = SLOTS;
     size_t n = 0;
@@ -224,6 +227,8 @@ class Pipeline {
     void crop_windows(TensorImpl* t, unsigned* xywh);
     void to_tensor(void* out_ptr, int layout, int dtype, const float* mul, const float* add, bool reverse, int mem_type);
     TimingInfo timing();
+    unsigned long long h2d_bytes() const { return _h2d_bytes.load(); }
+    void set_upload_mode(int mode) { _upload_mode = mode; }
     RocalTensorOutputType default_dtype() const { return _out_dtype; }
 
     // ---- error capture (Context::capture_error, include/pipeline/context.h:41-51) ----
@@ -239,6 +244,8 @@ class Pipeline {
     void process(InputBatch& b, Slot& s, int slot_idx);
     void update_nodes(const InputBatch& b, Slot& s);
     void ensure_arena(int which, size_t bytes);
+    bool source_footprint(const uint8_t* h_tab, size_t i, int W, int H, int& x0, int& y0, int& x1, int& y1) const;
+    void upload_sources(InputBatch& b, int a, const uint8_t* h_tab);
     void plan();
     void ssd_crop(Node& nd, const std::vector<int>& in_w, const std::vector<int>& in_h, Slot& s);
     void transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, const std::vector<unsigned>& y1,
@@ -301,6 +308,8 @@ class Pipeline {
 
     // timing (us)
     std::atomic<unsigned long long> _t_load{0}, _t_process{0}, _t_transfer{0};
+    std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
+    int _upload_mode = UPLOAD_ZERO_COPY;
 };
 
 #define RB200_THROW(msg) throw std::runtime_error(std::string(msg))

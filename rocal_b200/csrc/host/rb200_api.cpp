@@ -192,6 +192,12 @@ void rb200_get_timing(rb200_context ctx, unsigned long long out[4]) {
     out[0] = t.load_time; out[1] = t.decode_time; out[2] = t.process_time; out[3] = t.transfer_time;
 }
 size_t rb200_get_remaining_images(rb200_context ctx) { return ctx ? P(ctx)->remaining() : 0; }
+unsigned long long rb200_get_h2d_bytes(rb200_context ctx) { return ctx ? P(ctx)->h2d_bytes() : 0; }
+int rb200_set_upload_mode(rb200_context ctx, int mode) {
+    if (!ctx || mode < 0 || mode > 2) return -1;
+    P(ctx)->set_upload_mode(mode);
+    return 0;
+}
 
 // ---- parameters ----
 void rb200_set_seed(unsigned seed) { ParameterFactory::instance().set_seed(seed); }

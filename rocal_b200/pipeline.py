@@ -285,6 +285,18 @@ class Pipeline(object):
         C.get_timing(self._handle, t)
         return {"load_time": t[0], "decode_time": t[1], "process_time": t[2], "transfer_time": t[3]}
 
+    def h2d_bytes(self):
+        """Bytes this pipeline has uploaded so far (pixels, per-sample tables, boxes); no reference counterpart."""
+        return int(C.get_h2d_bytes(self._handle))
+
+    UPLOAD_WHOLE, UPLOAD_FOOTPRINT, UPLOAD_ZERO_COPY = 0, 1, 2
+
+    def set_upload_mode(self, mode):
+        """How host-resident source pixels reach the kernels: whole images, the rectangle each image's kernels
+        can read, or (default, pinned ragged input) no copy at all - the kernel reads the pinned buffer."""
+        if C.set_upload_mode(self._handle, int(mode)) != 0:
+            raise ValueError("upload mode must be 0, 1 or 2")
+
     def error_message(self):
         return C.get_error_message(self._handle).decode()
 

@@ -76,6 +76,40 @@ def test_config0_pipeline(cuda, out_dtype):
     pipe.rocal_release()
 
 
+def test_upload_modes(cuda):
+    """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
+    copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
+    The device arenas are poisoned first (a batch of 0xFF images) so that a row the footprint missed would show."""
+    import torch
+    from rocal_b200 import types
+    moved = {}
+    for mode in (2, 1, 0):
+        rng = S.rng_for(21)
+        pipe, out, mirror = _classification_pipeline(16, types.FLOAT, max_side=700, seed=11)
+        pipe.set_upload_mode(mode)
+        arena, hs, ws, offs = S.make_images(rng, 16, (300, 700), (300, 700))
+        for _ in range(2):                               # both arenas
+            pipe.set_crop_anchors(out, np.full(16, 0.5, np.float32), np.full(16, 0.5, np.float32))
+            pipe.feed_ragged(np.full_like(arena, 255), hs, ws, offs)
+            pipe.run()
+        ax, ay = rng.random(16).astype(np.float32), rng.random(16).astype(np.float32)
+        ax[0], ay[0], ax[1], ay[1] = 0.0, 0.0, 1.0, 1.0   # windows at the corners
+        before = pipe.h2d_bytes()
+        pipe.set_crop_anchors(out, ax, ay)
+        fed = torch.from_numpy(arena).pin_memory() if mode == 2 else arena
+        pipe.feed_ragged(fed, hs, ws, offs)
+        pipe.run()
+        moved[mode] = pipe.h2d_bytes() - before
+        m = pipe.get_int_array(mirror)
+        got = pipe.get_output_tensors()[0].numpy()
+        exp = _expected_classification(arena, hs, ws, offs, ax, ay, m, T.FP32)
+        assert np.array_equal(got, exp), mode
+        pipe.rocal_release()
+    whole = int((hs.astype(np.int64) * ws * 3).sum())
+    assert whole <= moved[0] < whole + 4096
+    assert moved[1] < 0.85 * whole and moved[2] < 0.85 * whole
+
+
 def test_slot_feed_and_prefetch_order(cuda):
     """The reference's feed contract (max-size slots + ROI per sample), two batches queued before the
     first run: results come back in feed order and match the ragged path's expectation."""
