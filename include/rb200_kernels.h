@@ -202,6 +202,24 @@ RB200_API int rb200k_box_encode(const float* boxes, const int32_t* labels, const
                       int n, int max_boxes_per_sample, const rb200_box_encoder_params* params,
                       float* out_boxes, int32_t* out_labels, void* stream);
 
+/* Box IoU matcher: out_matches[n][num_anchors] int32 = index (within the sample) of the box with the
+ * highest IoU for each anchor, -1 where that IoU is below low_threshold, -2 where it is below
+ * high_threshold; with allow_low_quality_matches every anchor whose IoU with some box is within 1e-6
+ * of that box's best IoU keeps its match. boxes / box_offsets as for rb200k_box_encode (device
+ * pointers, boxes and anchors 16-byte aligned); at most 1024 boxes per sample, any number of anchors.
+ * An anchor that no box matches at all (sample without boxes, NaN IoUs) starts from -1.
+ * replaces: BoundingBoxGraph::update_box_iou_matcher
+ *           (rocAL/source/meta_data/bounding_box_graph.cpp:222-284). */
+typedef struct rb200_box_matcher_params {
+    const float* anchors;        /* device, [num_anchors][4] ltrb */
+    int32_t num_anchors;
+    float high_threshold, low_threshold;
+    int32_t allow_low_quality_matches;
+} rb200_box_matcher_params;
+
+RB200_API int rb200k_box_iou_match(const float* boxes, const int32_t* box_offsets, int n, int max_boxes_per_sample,
+                         const rb200_box_matcher_params* params, int32_t* out_matches, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Misc
  * ------------------------------------------------------------------------------------- */

@@ -374,6 +374,58 @@ ORC_API int orc_box_encode(const float* boxes, const int32_t* labels, const int3
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Box IoU matcher. Restates BoundingBoxGraph::update_box_iou_matcher
+ * (rocAL/source/meta_data/bounding_box_graph.cpp:222-284):
+ *   :247-251  per anchor: the box with the highest IoU by strict '>' from -1 (lowest box index among
+ *             equals; NaN never matches)
+ *   :254-256  per box: the highest IoU over the anchors, by strict '>' from -1
+ *   :259-264  low-quality matches: every anchor whose IoU with a box lies within 1e-6 of that box's
+ *             maximum keeps its match whatever the thresholds
+ *   :268-277  otherwise a best IoU below low_threshold gives -1, below high_threshold -2.
+ * An anchor that no box beats (a sample without boxes, NaN IoUs) keeps the entry the reference finds in
+ * its output buffer; here that entry is -1 before the threshold rules apply.
+ * All pointers are host pointers.
+ * ---------------------------------------------------------------------------------------- */
+ORC_API int orc_box_iou_match(const float* boxes, const int32_t* box_offsets, int n, const float* anchors,
+                              int num_anchors, float high_threshold, float low_threshold, int allow_low_quality,
+                              int32_t* out_matches) {
+    if (!boxes || !box_offsets || !anchors || !out_matches) return RB200_E_INVALID;
+    int A = num_anchors;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        int nb = box_offsets[i + 1] - box_offsets[i];
+        const float* bb = boxes + (size_t)box_offsets[i] * 4;
+        int32_t* m = out_matches + (size_t)i * A;
+        float* vals = (float*)malloc(sizeof(float) * (size_t)A);
+        float* row = (float*)malloc(sizeof(float) * (size_t)A);
+        uint8_t* lq = (uint8_t*)calloc((size_t)A, 1);
+        for (int a = 0; a < A; a++) { vals[a] = -1.f; m[a] = -1; }
+        for (int b = 0; b < nb; b++) {
+            const float* box = bb + b * 4;
+            float area = (box[3] - box[1]) * (box[2] - box[0]);
+            float best = -1.f;
+            for (int a = 0; a < A; a++) {
+                float v = iou_ltrb(box, area, anchors + a * 4);
+                row[a] = v;
+                if (v > vals[a]) { vals[a] = v; m[a] = b; }
+                if (allow_low_quality && v > best) best = v;
+            }
+            if (allow_low_quality)
+                for (int a = 0; a < A; a++)
+                    if ((double)fabsf(row[a] - best) < 1e-6) lq[a] = 1;
+        }
+        for (int a = 0; a < A; a++) {
+            if (!(allow_low_quality && lq[a])) {
+                if (vals[a] < low_threshold) m[a] = -1;
+                else if (vals[a] < high_threshold) m[a] = -2;
+            }
+        }
+        free(vals); free(row); free(lq);
+    }
+    return RB200_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
  * Host-side size rules.
  * ---------------------------------------------------------------------------------------- */
 

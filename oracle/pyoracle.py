@@ -168,6 +168,35 @@ def ref_box_encode(boxes, labels, offsets, anchors, criteria=0.5, means=(0, 0, 0
     return _box_call(r.ref_box_encode, boxes, labels, offsets, anchors, criteria, means, stds, offset, scale)
 
 
+def _match_call(fn, boxes, offsets, anchors, high, low, allow):
+    n = len(offsets) - 1
+    a = anchors.shape[0]
+    boxes = np.ascontiguousarray(boxes, dtype=np.float32)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+    anchors = np.ascontiguousarray(anchors, dtype=np.float32)
+    out = np.zeros((n, a), dtype=np.int32)
+    fn.restype = ctypes.c_int
+    rc = fn(_ptr(boxes), _ptr(offsets), ctypes.c_int(n), _ptr(anchors), ctypes.c_int(a), ctypes.c_float(high),
+            ctypes.c_float(low), ctypes.c_int(1 if allow else 0), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def box_iou_match(boxes, offsets, anchors, high_threshold=0.5, low_threshold=0.4, allow_low_quality_matches=True):
+    """The restatement (oracle.c) of the box IoU matcher: matched box index per anchor, -1 / -2 below the thresholds."""
+    return _match_call(lib().orc_box_iou_match, boxes, offsets, anchors, high_threshold, low_threshold,
+                       allow_low_quality_matches)
+
+
+def ref_box_iou_match(boxes, offsets, anchors, high_threshold=0.5, low_threshold=0.4, allow_low_quality_matches=True):
+    """The reference's own BoundingBoxGraph::update_box_iou_matcher (needs _ref/libref.so)."""
+    r = ref()
+    if r is None:
+        raise RuntimeError("oracle/_ref/libref.so is not available")
+    return _match_call(r.ref_box_iou_match, boxes, offsets, anchors, high_threshold, low_threshold,
+                       allow_low_quality_matches)
+
+
 def resize_dst_size(src_w, src_h, dst_w, dst_h, mode, max_w=0, max_h=0, cap_w=1 << 30, cap_h=1 << 30):
     ow, oh = ctypes.c_uint(), ctypes.c_uint()
     lib().orc_resize_dst_size(ctypes.c_uint(src_w), ctypes.c_uint(src_h), ctypes.c_uint(dst_w), ctypes.c_uint(dst_h),

@@ -9,6 +9,8 @@
  *
  *   ref_box_encode       -> BoundingBoxGraph::update_box_encoder_meta_data
  *                           (rocAL/source/meta_data/bounding_box_graph.cpp:150-220)
+ *   ref_box_iou_match    -> BoundingBoxGraph::update_box_iou_matcher (bounding_box_graph.cpp:222-284);
+ *                           the output buffer is pre-filled with -1 (the reference leaves unmatched entries as found)
  *   ref_uniform_rand_*   -> UniformRand<T> (rocAL/include/parameters/parameter_random.h:37-116)
  *   ref_custom_rand_int  -> CustomRand<int> (parameter_random.h:118-239)
  *   ref_seed_sequence    -> the seed table of ParameterFactory::set_seed
@@ -44,6 +46,33 @@ __attribute__((visibility("default"))) int ref_box_encode(
     std::vector<float> m(means, means + 4), s(stds, stds + 4);
     BoundingBoxGraph graph;
     graph.update_box_encoder_meta_data(&anc, batch, criteria, offset != 0, scale, m, s, out_boxes, out_labels);
+    return 0;
+}
+
+__attribute__((visibility("default"))) int ref_box_iou_match(
+    const float* boxes, const int32_t* box_offsets, int n, const float* anchors, int num_anchors,
+    float high_threshold, float low_threshold, int allow_low_quality, int32_t* out_matches) {
+    auto batch = std::make_shared<BoundingBoxBatch>();
+    batch->resize(n);
+    for (int i = 0; i < n; i++) {
+        BoundingBoxCords cords;
+        Labels lab;
+        for (int b = box_offsets[i]; b < box_offsets[i + 1]; b++) {
+            cords.emplace_back(boxes[b * 4 + 0], boxes[b * 4 + 1], boxes[b * 4 + 2], boxes[b * 4 + 3]);
+            lab.push_back(0);
+        }
+        batch->get_bb_cords_batch()[i] = cords;
+        batch->get_labels_batch()[i] = lab;
+    }
+    std::vector<float> anc(anchors, anchors + (size_t)num_anchors * 4);
+    BoxIouMatcherInfo info;
+    info.anchors = &anc;
+    info.high_threshold = high_threshold;
+    info.low_threshold = low_threshold;
+    info.allow_low_quality_matches = allow_low_quality != 0;
+    for (size_t k = 0; k < (size_t)n * num_anchors; k++) out_matches[k] = -1;
+    BoundingBoxGraph graph;
+    graph.update_box_iou_matcher(info, out_matches, batch);
     return 0;
 }
 

@@ -42,6 +42,11 @@ class BoxEncoderParams(ctypes.Structure):
                 ("offset", ctypes.c_int32), ("scale", ctypes.c_float)]
 
 
+class BoxMatcherParams(ctypes.Structure):
+    _fields_ = [("anchors", c_void_p), ("num_anchors", ctypes.c_int32), ("high_threshold", ctypes.c_float),
+                ("low_threshold", ctypes.c_float), ("allow_low_quality_matches", ctypes.c_int32)]
+
+
 lib.rb200k_resample.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(ResampleParams), c_void_p]
 lib.rb200k_resample.restype = c_int
 lib.rb200k_pointwise.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(PointwiseParams), c_void_p]
@@ -51,6 +56,8 @@ lib.rb200k_warp_affine.restype = c_int
 lib.rb200k_box_encode.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(BoxEncoderParams),
                                   c_void_p, c_void_p, c_void_p]
 lib.rb200k_box_encode.restype = c_int
+lib.rb200k_box_iou_match.argtypes = [c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(BoxMatcherParams), c_void_p, c_void_p]
+lib.rb200k_box_iou_match.restype = c_int
 lib.rb200k_last_error.restype = c_char_p
 lib.rb200k_launch_count.restype = c_uint64
 lib.rb200k_version.restype = c_char_p

@@ -19,6 +19,7 @@
 // cluster until the final coalesced write.
 #include <cooperative_groups.h>
 
+#include "box_common.cuh"
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -39,18 +40,6 @@ struct BoxLaunch {
     int offset;
     float scale, half_scale;
 };
-
-__device__ __forceinline__ float iou_ltrb(const float4 b, float area_b, const float4 a, float area_a) {
-    float xa = fmaxf(b.x, a.x), ya = fmaxf(b.y, a.y);
-    float xb = fminf(b.z, a.z), yb = fminf(b.w, a.w);
-    float inter = mul_rn(fmaxf(0.f, sub_rn(xb, xa)), fmaxf(0.f, sub_rn(yb, ya)));
-    float uni = sub_rn(add_rn(area_b, area_a), inter);
-    // Most box/anchor pairs do not overlap. 0 / u is a zero for every non-zero, non-NaN u, and the IEEE
-    // division of a zero numerator takes the slow path of the division sequence, so it is answered here;
-    // the sign of that zero never matters to the comparisons that consume the value.
-    if (inter == 0.f && (uni > 0.f || uni < 0.f)) return 0.f;
-    return div_rn(inter, uni);
-}
 
 // Larger value wins, lower anchor index among equals (the CPU loop's strict '>' over ascending anchors).
 __device__ __forceinline__ bool beats(float ov, int oi, float tv, int ti) {
@@ -80,8 +69,7 @@ __device__ __forceinline__ void box_step(const float4 b, int j, int box, const f
     // Warp argmax with two redux instructions: the value as an order-preserving integer key, then the
     // lowest anchor index among the lanes that hold the maximum. A thread's candidate is NaN only when it
     // is anchor 0's seed, which the CPU loop never replaces: NaN takes the highest key.
-    const uint32_t bits = __float_as_uint(tv);
-    uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    uint32_t key = float_key(tv);
     if (tv != tv) key = 0xffffffffu;
     const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
     ti = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (uint32_t)ti : 0xffffffffu);

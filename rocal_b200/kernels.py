@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 from . import tables as T
-from ._lib import (BoxEncoderParams, PointwiseParams, ResampleParams, WarpParams, check, lib)
+from ._lib import (BoxEncoderParams, BoxMatcherParams, PointwiseParams, ResampleParams, WarpParams, check, lib)
 
 _TORCH_DTYPE = {T.FP32: torch.float32, T.FP16: torch.float16, T.UINT8: torch.uint8}
 
@@ -119,3 +119,21 @@ def box_encode(boxes, labels, box_offsets, anchors, criteria, means, stds, offse
                                 ctypes.byref(p), out_boxes.data_ptr(), out_labels.data_ptr(), _stream_ptr(stream)),
           "rb200k_box_encode")
     return out_boxes, out_labels
+
+
+def box_iou_match(boxes, box_offsets, anchors, high_threshold, low_threshold, allow_low_quality_matches, max_boxes,
+                  out=None, stream=None):
+    """rb200k_box_iou_match. boxes [total,4] f32, box_offsets [n+1] i32, anchors [A,4] f32 - CUDA tensors.
+    Returns int32 [n, A]: matched box index per anchor, -1 / -2 below the low / high threshold."""
+    n = box_offsets.numel() - 1
+    a = anchors.shape[0]
+    if out is None:
+        out = torch.empty((n, a), dtype=torch.int32, device=boxes.device)
+    p = BoxMatcherParams()
+    p.anchors = anchors.data_ptr()
+    p.num_anchors = a
+    p.high_threshold, p.low_threshold = float(high_threshold), float(low_threshold)
+    p.allow_low_quality_matches = 1 if allow_low_quality_matches else 0
+    check(lib.rb200k_box_iou_match(boxes.data_ptr(), box_offsets.data_ptr(), n, int(max_boxes), ctypes.byref(p),
+                                   out.data_ptr(), _stream_ptr(stream)), "rb200k_box_iou_match")
+    return out

@@ -1,6 +1,6 @@
 """Per-operator device-resident benchmark of the kernel C-ABI on the benchmark configurations.
 
-    python -m rocal_b200.opbench [--ops color_twist,warp,box_encoder,ssd_chain,cfg0,brightness,flip] [--steps 50]
+    python -m rocal_b200.opbench [--ops color_twist,warp,box_encoder,box_matcher,ssd_chain,cfg0,brightness,flip] [--steps 50]
 
 Prints one JSON line per operator: images/s, mean launch time (CUDA events on the launching stream),
 algorithmic bytes per launch and the fraction of the measured HBM copy bandwidth. Every operator rotates
@@ -127,6 +127,25 @@ def main():
                 fns.append(lambda b=b, l=l, o=o, ob=ob, ol=ol: K.box_encode(b, l, o, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0, 50, ob, ol))
             ms = _time(fns, args.steps)
             report("cfg4 box_encoder 8732 anchors (batch 128)", n, ms, n * 8732 * 20 + nbox * 20 + 8732 * 16,
+                   {"us_per_batch": ms * 1e3, "boxes_per_batch": nbox})
+        elif op == "box_matcher":
+            # RetinaNet-sized anchor table (120 087 boxes), batch 32, 1..50 boxes per sample
+            n, rot = 32, 4
+            base = S.ssd300_anchors()
+            reps = -(-120087 // len(base))
+            rng = S.rng_for(4, 300)
+            big = (np.tile(base, (reps, 1)) + rng.uniform(-0.02, 0.02, (reps * len(base), 4)).astype(np.float32))[:120087]
+            anchors = torch.from_numpy(np.ascontiguousarray(big)).to(dev)
+            fns, nbox = [], 0
+            for r in range(rot):
+                rng = S.rng_for(4, 300 + r)
+                boxes, labels, boffs = S.random_boxes(rng, n)
+                nbox = len(labels)
+                b, o = torch.from_numpy(boxes).to(dev), torch.from_numpy(boffs).to(dev)
+                om = torch.empty((n, 120087), dtype=torch.int32, device=dev)
+                fns.append(lambda b=b, o=o, om=om: K.box_iou_match(b, o, anchors, 0.5, 0.4, True, 50, om))
+            ms = _time(fns, args.steps)
+            report("box_iou_matcher 120087 anchors, low-quality matches on (batch 32)", n, ms, n * 120087 * 4 + nbox * 16 + 120087 * 16,
                    {"us_per_batch": ms * 1e3, "boxes_per_batch": nbox})
         else:
             print(json.dumps({"op": op, "error": "unknown operator"}))

@@ -5,7 +5,8 @@ the reference tree by oracle/build.py). Run in a container that has the referenc
 
 box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
                   (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
-box_encoder_degenerate.npz   the same on zero-area / inverted boxes and a degenerate anchor 0
+box_encoder_degenerate.npz   the same on zero-area / inverted boxes and a degenerate anchor 0, plus the IoU matcher on them
+box_iou_matcher.npz          BoundingBoxGraph::update_box_iou_matcher (bounding_box_graph.cpp:222-284), three settings
 param_rng.npz     UniformRand<float>, UniformRand<int>, CustomRand<int> draws
                   (rocAL/include/parameters/parameter_random.h) and the std::seed_seq table of
                   ParameterFactory::set_seed (rocAL/source/parameters/parameter_factory.cpp:114-119)
@@ -67,7 +68,19 @@ def main():
     for name, offset in (("offset", True), ("plain", False)):
         eb, el = O.ref_box_encode(boxes, labels, offsets, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), offset, 1.0)
         out[name + "_boxes"], out[name + "_labels"] = eb, el
+    for name, allow in (("match_lq", True), ("match_plain", False)):
+        out[name] = O.ref_box_iou_match(boxes, offsets, anchors, 0.5, 0.4, allow)
     np.savez_compressed(os.path.join(HERE, "box_encoder_degenerate.npz"), **out)
+
+    # Box IoU matcher on ordinary boxes (BoundingBoxGraph::update_box_iou_matcher)
+    rng = np.random.Generator(np.random.PCG64(4244))
+    anchors = S.ssd300_anchors()[::3][:2500].copy()
+    boxes, _, offsets = S.random_boxes(rng, 6, (1, 40))
+    boxes[1] = boxes[0]
+    out = {"anchors": anchors, "boxes": boxes, "offsets": offsets}
+    for name, hi, lo, allow in (("lq_05_04", 0.5, 0.4, True), ("plain_05_04", 0.5, 0.4, False), ("lq_07_03", 0.7, 0.3, True)):
+        out[name] = O.ref_box_iou_match(boxes, offsets, anchors, hi, lo, allow)
+    np.savez_compressed(os.path.join(HERE, "box_iou_matcher.npz"), **out)
 
     rngs = {}
     f = np.zeros(3 * 16, dtype=np.float32)
@@ -89,7 +102,7 @@ def main():
         ref.ref_seed_sequence(ctypes.c_uint(seed), ctypes.c_uint(1024), t.ctypes.data_as(ctypes.c_void_p))
         rngs["seed_seq_%d" % seed] = t
     np.savez_compressed(os.path.join(HERE, "param_rng.npz"), **rngs)
-    print("wrote box_encoder.npz, box_encoder_degenerate.npz, param_rng.npz")
+    print("wrote box_encoder.npz, box_encoder_degenerate.npz, box_iou_matcher.npz, param_rng.npz")
 
 
 if __name__ == "__main__":

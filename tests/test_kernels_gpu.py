@@ -361,6 +361,40 @@ def test_box_encoder_degenerate_and_large_tables(cuda):
             _assert_fp(got[fin], ref[fin], 1e-5, "encoded boxes")
 
 
+@pytest.mark.parametrize("allow", [True, False])
+def test_box_iou_matcher(cuda, allow):
+    """Matched box index per anchor with the -1 / -2 threshold codes and the low-quality rule: SSD-300 table
+    with 1..50 boxes, a RetinaNet-sized table (120 087 anchors: 15 register groups per CTA), a tiny table,
+    degenerate boxes, a sample without boxes, exact ties between boxes; all indices must be equal."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(18)
+    base = S.ssd300_anchors()
+    boxes, labels, offs = S.random_boxes(rng, 24)
+    cases = [(base, boxes, offs, 0.5, 0.4)]
+    reps = -(-120087 // len(base))
+    big = np.ascontiguousarray((np.tile(base, (reps, 1)) + rng.uniform(-0.02, 0.02, (reps * len(base), 4)).astype(np.float32))[:120087])
+    cases.append((big, boxes[:int(offs[6])], offs[:7], 0.5, 0.4))
+    counts = [4, 0, 6, 1, 3]
+    db, _, _ = S.random_boxes(rng, 1, (sum(counts), sum(counts)))
+    db[0] = (0.3, 0.3, 0.3, 0.3)
+    db[1] = (0.6, 0.6, 0.2, 0.2)
+    db[5] = db[4]                                   # two identical boxes: the lower index keeps the anchors
+    db[10] = (0.5, 0.2, 0.5, 0.9)
+    db[12] = base[4000]                             # IoU 1 with one anchor
+    doffs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    small = base[::200][:37].copy()
+    small[0] = (0.0, 0.0, 0.0, 0.0)
+    cases.append((base, db, doffs, 0.7, 0.3))
+    cases.append((small, db, doffs, 0.5, 0.4))
+    for anchors, bx, of, hi, lo in cases:
+        ref = O.box_iou_match(bx, of, anchors, hi, lo, allow)
+        got = K.box_iou_match(torch.from_numpy(np.ascontiguousarray(bx)).to(cuda), torch.from_numpy(np.ascontiguousarray(of)).to(cuda),
+                              torch.from_numpy(anchors).to(cuda), hi, lo, allow, 64).cpu().numpy()
+        assert np.array_equal(got, ref), (len(anchors), hi, lo)
+        assert (ref >= 0).sum() > 0
+
+
 def test_ssd_chain_config4(cuda):
     """configs[4] image chain: SSD random crop window -> resize 300x300 -> mirror -> normalize fp32 (batch 32)."""
     from rocal_b200 import kernels as K

@@ -35,6 +35,17 @@ def test_box_encoder_degenerate_matches_golden():
         assert np.array_equal(eb, g[name + "_boxes"], equal_nan=True), name
 
 
+def test_box_iou_matcher_matches_golden():
+    g = np.load(os.path.join(GOLDEN, "box_iou_matcher.npz"))
+    for name, hi, lo, allow in (("lq_05_04", 0.5, 0.4, True), ("plain_05_04", 0.5, 0.4, False), ("lq_07_03", 0.7, 0.3, True)):
+        m = O.box_iou_match(g["boxes"], g["offsets"], g["anchors"], hi, lo, allow)
+        assert np.array_equal(m, g[name]), name
+        assert (m >= 0).sum() > 0 and (m == -2).sum() > 0
+    g = np.load(os.path.join(GOLDEN, "box_encoder_degenerate.npz"))
+    for name, allow in (("match_lq", True), ("match_plain", False)):
+        assert np.array_equal(O.box_iou_match(g["boxes"], g["offsets"], g["anchors"], 0.5, 0.4, allow), g[name]), name
+
+
 def test_box_encoder_matches_reference_build():
     if O.ref() is None:
         pytest.skip("reference tree not present: oracle/_ref/libref.so cannot be built")
