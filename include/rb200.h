@@ -194,6 +194,14 @@ RB200_API int rb200_copy_encoded_boxes_and_labels(rb200_context ctx, float* boxe
 RB200_API int rb200_get_encoded_boxes_and_labels(rb200_context ctx, float** boxes_dev, int** labels_dev,
                                                  size_t* num_anchors);
 
+/* ---- box IoU matcher: rocalBoxIouMatcher / rocalGetMatchedIndices (rocal_api_meta_data.h:302-318).
+ * Matched box index per anchor of the batch returned by the last rb200_run ([batch][num_anchors] int32 on
+ * the device, valid until the next rb200_run); rb200_copy_matched_indices copies them to host memory. ---- */
+RB200_API int rb200_box_iou_matcher(rb200_context ctx, const float* anchors_ltrb, size_t num_anchors, float high_threshold,
+                                    float low_threshold, int allow_low_quality_matches);
+RB200_API int rb200_get_matched_indices(rb200_context ctx, int** matches_dev, size_t* num_anchors);
+RB200_API int rb200_copy_matched_indices(rb200_context ctx, int* matches_buf);
+
 /* Boxes of the batch returned by the last rb200_run, after the graph's crops and mirrors: the data
  * of rocalGetBoundingBoxCount / rocalGetBoundingBoxCords / rocalGetBoundingBoxLabel
  * (rocal_api_meta_data.h:179-211) as flat arrays. Returns the total number of boxes; the arrays may be

@@ -298,6 +298,11 @@ RB200_ROCAL void ROCAL_API_CALL rocalBoxEncoder(RocalContext p_context, std::vec
 RB200_ROCAL void ROCAL_API_CALL rocalCopyEncodedBoxesAndLables(RocalContext p_context, float* boxes_buf, int* labels_buf);
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalGetEncodedBoxesAndLables(RocalContext p_context, int num_encoded_boxes);
 
+/* ---- box IoU matcher (rocal_api_meta_data.h:302-318) ---- */
+RB200_ROCAL void ROCAL_API_CALL rocalBoxIouMatcher(RocalContext p_context, std::vector<float>& anchors, float high_threshold,
+                                                   float low_threshold, bool allow_low_quality_matches = true);
+RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetMatchedIndices(RocalContext p_context);
+
 /* ---- info (rocal_api_info.h:41-114) ---- */
 RB200_ROCAL int ROCAL_API_CALL rocalGetOutputWidth(RocalContext rocal_context);
 RB200_ROCAL int ROCAL_API_CALL rocalGetOutputHeight(RocalContext rocal_context);

@@ -102,6 +102,9 @@ stream = _proto("rb200_stream", _P, _P)
 to_tensor = _proto("rb200_to_tensor", c_int, _P, c_void_p, c_int, c_int, POINTER(c_float), POINTER(c_float), c_int, c_int)
 box_encoder = _proto("rb200_box_encoder", c_int, _P, POINTER(c_float), c_size_t, c_float, POINTER(c_float),
                      POINTER(c_float), c_int, c_float)
+box_iou_matcher = _proto("rb200_box_iou_matcher", c_int, _P, POINTER(c_float), c_size_t, c_float, c_float, c_int)
+get_matched_indices = _proto("rb200_get_matched_indices", c_int, _P, POINTER(c_void_p), POINTER(c_size_t))
+copy_matched_indices = _proto("rb200_copy_matched_indices", c_int, _P, POINTER(c_int))
 copy_encoded_boxes_and_labels = _proto("rb200_copy_encoded_boxes_and_labels", c_int, _P, POINTER(c_float), POINTER(c_int))
 get_encoded_boxes_and_labels = _proto("rb200_get_encoded_boxes_and_labels", c_int, _P, POINTER(c_void_p), POINTER(c_void_p),
                                       POINTER(c_size_t))

@@ -207,12 +207,14 @@ Pipeline::~Pipeline() {
         if (s.h_tables) cudaFreeHost(s.h_tables);
         if (s.d_enc_boxes) cudaFree(s.d_enc_boxes);
         if (s.d_enc_labels) cudaFree(s.d_enc_labels);
+        if (s.d_matches) cudaFree(s.d_matches);
     }
     for (int k = 0; k < 2; k++) {
         if (_arena[k]) cudaFree(_arena[k]);
         if (_arena_free[k]) cudaEventDestroy(_arena_free[k]);
     }
     if (_d_anchors) cudaFree(_d_anchors);
+    if (_d_match_anchors) cudaFree(_d_match_anchors);
     if (_d_boxes) cudaFree(_d_boxes);
     if (_d_labels) cudaFree(_d_labels);
     if (_d_offsets) cudaFree(_d_offsets);
@@ -268,6 +270,18 @@ void Pipeline::set_box_encoder(const float* anchors, size_t num_anchors, float c
     _enc.offset = offset ? 1 : 0;
     _enc.scale = scale;
     _box_encoder = true;
+}
+
+// rocalBoxIouMatcher (source/api/rocal_api_meta_data.cpp:474-483): matched box index per anchor.
+void Pipeline::set_box_matcher(const float* anchors, size_t num_anchors, float high, float low, bool allow_low_quality) {
+    if (_verified) RB200_THROW("the graph is already verified");
+    if (!anchors || num_anchors == 0) RB200_THROW("box IoU matcher needs a non-empty anchor list");
+    _match_anchors.assign(anchors, anchors + num_anchors * 4);
+    _match.num_anchors = (int32_t)num_anchors;
+    _match.high_threshold = high;
+    _match.low_threshold = low;
+    _match.allow_low_quality_matches = allow_low_quality ? 1 : 0;
+    _box_matcher = true;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -411,17 +425,28 @@ void Pipeline::verify() {
             RB200_CUDA(cudaMalloc((void**)&s.d_enc_boxes, _batch * (size_t)_enc.num_anchors * 4 * sizeof(float)));
             RB200_CUDA(cudaMalloc((void**)&s.d_enc_labels, _batch * (size_t)_enc.num_anchors * sizeof(int)));
         }
+        if (_box_matcher) RB200_CUDA(cudaMalloc((void**)&s.d_matches, _batch * (size_t)_match.num_anchors * sizeof(int)));
     }
     for (int k = 0; k < 2; k++) RB200_CUDA(cudaEventCreateWithFlags(&_arena_free[k], cudaEventDisableTiming));
-    if (_box_encoder) {
-        RB200_CUDA(cudaMalloc((void**)&_d_anchors, _anchors.size() * sizeof(float)));
-        RB200_CUDA(cudaMemcpy(_d_anchors, _anchors.data(), _anchors.size() * sizeof(float), cudaMemcpyHostToDevice));
-        _enc.anchors = _d_anchors;
+    if (_box_matcher) {
+        RB200_CUDA(cudaMalloc((void**)&_d_match_anchors, _match_anchors.size() * sizeof(float)));
+        RB200_CUDA(cudaMemcpy(_d_match_anchors, _match_anchors.data(), _match_anchors.size() * sizeof(float), cudaMemcpyHostToDevice));
+        _match.anchors = _d_match_anchors;
+        _matches_t.reset(new TensorImpl(this, -3, (int)_batch, 1, _match.num_anchors, ROCAL_INT32, ROCAL_NHWC, false, false));
+        _matches_t->custom_dims = {_batch, (size_t)_match.num_anchors};
+        _match_list.items = {_matches_t.get()};
+    }
+    if (_box_encoder || _box_matcher) {
         _box_capacity = _batch * 64;
         RB200_CUDA(cudaMalloc((void**)&_d_boxes, _box_capacity * 4 * sizeof(float)));
         RB200_CUDA(cudaMalloc((void**)&_d_labels, _box_capacity * sizeof(int)));
         RB200_CUDA(cudaMalloc((void**)&_d_offsets, (_batch + 1) * sizeof(int)));
         RB200_CUDA(cudaHostAlloc(&_h_box_stage, _box_capacity * 5 * sizeof(float) + (_batch + 1) * sizeof(int), cudaHostAllocDefault));
+    }
+    if (_box_encoder) {
+        RB200_CUDA(cudaMalloc((void**)&_d_anchors, _anchors.size() * sizeof(float)));
+        RB200_CUDA(cudaMemcpy(_d_anchors, _anchors.data(), _anchors.size() * sizeof(float), cudaMemcpyHostToDevice));
+        _enc.anchors = _d_anchors;
         _enc_boxes_t.reset(new TensorImpl(this, -1, (int)_batch, 4, _enc.num_anchors, ROCAL_FP32, ROCAL_NHWC, false, false));
         _enc_labels_t.reset(new TensorImpl(this, -2, (int)_batch, 1, _enc.num_anchors, ROCAL_INT32, ROCAL_NHWC, false, false));
         _enc_boxes_t->custom_dims = {_batch, (size_t)_enc.num_anchors, 4};
@@ -1148,9 +1173,9 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     }
     if (arena_used >= 0) RB200_CUDA(cudaEventRecord(_arena_free[arena_used], _stream));
 
-    // ---- 4. box encoder ----
-    if (_box_encoder) {
-        if (s.counts.size() != n) RB200_THROW("the box encoder needs boxes for every batch (rb200_feed_boxes)");
+    // ---- 4. box encoder / box IoU matcher ----
+    if (_box_encoder || _box_matcher) {
+        if (s.counts.size() != n) RB200_THROW("the box encoder / matcher needs boxes for every batch (rb200_feed_boxes)");
         size_t total = s.labels.size();
         int max_boxes = 1;
         for (int c : s.counts) max_boxes = std::max(max_boxes, c);
@@ -1178,8 +1203,14 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         RB200_CUDA(cudaMemcpyAsync(_d_labels, hl, total * sizeof(int), cudaMemcpyHostToDevice, _stream));
         RB200_CUDA(cudaMemcpyAsync(_d_offsets, ho, (n + 1) * sizeof(int), cudaMemcpyHostToDevice, _stream));
         _h2d_bytes += total * 20 + (n + 1) * sizeof(int);
-        int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _stream);
-        if (rc != 0) RB200_THROW(rb200k_last_error());
+        if (_box_encoder) {
+            int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _stream);
+            if (rc != 0) RB200_THROW(rb200k_last_error());
+        }
+        if (_box_matcher) {
+            int rc = rb200k_box_iou_match(_d_boxes, _d_offsets, (int)n, max_boxes, &_match, s.d_matches, _stream);
+            if (rc != 0) RB200_THROW(rb200k_last_error());
+        }
     }
 
     // ---- 5. snapshot of the ROIs the user will see, completion event ----
@@ -1244,6 +1275,19 @@ void Pipeline::run() {
         _enc_boxes_t->current = s.d_enc_boxes;
         _enc_labels_t->current = s.d_enc_labels;
     }
+    if (_box_matcher) _matches_t->current = s.d_matches;
+}
+
+TensorListImpl* Pipeline::matched_indices() {
+    if (!_box_matcher || _held < 0) return nullptr;
+    return &_match_list;
+}
+
+void Pipeline::matches(int** dev, size_t* num_anchors) {
+    if (!_box_matcher) RB200_THROW("no box IoU matcher in this graph");
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    *dev = _slots[_held].d_matches;
+    *num_anchors = (size_t)_match.num_anchors;
 }
 
 MetaListImpl* Pipeline::encoded_meta() {

@@ -184,6 +184,7 @@ struct Slot {
     std::vector<std::vector<unsigned>> windows;   // per node: n x {x,y,w,h} source window (crop-type nodes)
     float* d_enc_boxes = nullptr;
     int* d_enc_labels = nullptr;
+    int* d_matches = nullptr;         // box IoU matcher output [n][anchors]
     std::vector<float> boxes;        // metadata after the graph (normalized ltrb)
     std::vector<int> labels, counts;
     size_t n = 0;
@@ -201,6 +202,7 @@ class Pipeline {
                          RocalTensorOutputType dt, bool is_output);
     void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
                          const float* stds, bool offset, float scale);
+    void set_box_matcher(const float* anchors, size_t num_anchors, float high, float low, bool allow_low_quality);
     void verify();
 
     // ---- feeding (user thread) ----
@@ -223,6 +225,8 @@ class Pipeline {
     MetaListImpl* encoded_meta();
     void encoded(float** boxes, int** labels, size_t* num_anchors);
     void copy_encoded(float* boxes, int* labels);
+    TensorListImpl* matched_indices();
+    void matches(int** dev, size_t* num_anchors);
     void current_boxes(std::vector<float>& ltrb, std::vector<int>& labels, std::vector<int>& counts);
     void crop_windows(TensorImpl* t, unsigned* xywh);
     void to_tensor(void* out_ptr, int layout, int dtype, const float* mul, const float* add, bool reverse, int mem_type);
@@ -278,6 +282,14 @@ class Pipeline {
     std::unique_ptr<TensorImpl> _enc_boxes_t, _enc_labels_t;   // views handed out by rocalGetEncodedBoxesAndLables
     TensorListImpl _enc_list_boxes, _enc_list_labels;
     MetaListImpl _enc_meta;
+
+    // box IoU matcher
+    bool _box_matcher = false;
+    std::vector<float> _match_anchors;
+    float* _d_match_anchors = nullptr;
+    rb200_box_matcher_params _match{};
+    std::unique_ptr<TensorImpl> _matches_t;
+    TensorListImpl _match_list;
 
     // staging for extensions (attached to the next fed batch)
     InputBatch _staged;

@@ -709,6 +709,46 @@ int rb200_get_encoded_boxes_and_labels(rb200_context ctx, float** boxes_dev, int
     return ROCAL_OK;
 }
 
+// ---- box IoU matcher ----
+int rb200_box_iou_matcher(rb200_context ctx, const float* anchors_ltrb, size_t num_anchors, float high_threshold,
+                          float low_threshold, int allow_low_quality_matches) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->set_box_matcher(anchors_ltrb, num_anchors, high_threshold, low_threshold, allow_low_quality_matches != 0);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_matched_indices(rb200_context ctx, int** matches_dev, size_t* num_anchors) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!matches_dev || !num_anchors) RB200_THROW("null output pointer");
+        P(ctx)->matches(matches_dev, num_anchors);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_copy_matched_indices(rb200_context ctx, int* matches_buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!matches_buf) RB200_THROW("null output buffer");
+        int* dev;
+        size_t a;
+        P(ctx)->matches(&dev, &a);
+        P(ctx)->sync_copy(matches_buf, dev, (size_t)P(ctx)->batch() * a * sizeof(int), cudaMemcpyDeviceToHost);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
 size_t rb200_get_bounding_boxes(rb200_context ctx, float* ltrb, int* labels, int* counts) {
     CTX_OR(0);
     try {

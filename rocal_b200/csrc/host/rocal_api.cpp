@@ -257,6 +257,26 @@ RocalMetaData ROCAL_API_CALL rocalGetEncodedBoxesAndLables(RocalContext c, int n
     return P(c)->encoded_meta();
 }
 
+void ROCAL_API_CALL rocalBoxIouMatcher(RocalContext c, std::vector<float>& anchors, float high_threshold, float low_threshold,
+                                       bool allow_low_quality_matches) {
+    if (!c) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return;
+    }
+    if (anchors.empty() || anchors.size() % 4 != 0) {
+        P(c)->capture_error("rocalBoxIouMatcher: anchors must hold 4 values per box");
+        return;
+    }
+    rb200_box_iou_matcher(c, anchors.data(), anchors.size() / 4, high_threshold, low_threshold, allow_low_quality_matches);
+}
+RocalTensorList ROCAL_API_CALL rocalGetMatchedIndices(RocalContext c) {
+    if (!c) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    return P(c)->matched_indices();
+}
+
 int ROCAL_API_CALL rocalGetOutputWidth(RocalContext c) {
     if (!c || P(c)->outputs()->size() == 0) return 0;
     return static_cast<TensorImpl*>(P(c)->outputs()->at(0))->max_w;

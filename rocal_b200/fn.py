@@ -171,6 +171,15 @@ def rotate(*inputs, angle=None, dest_width=0, dest_height=0, interpolation_type=
                             output_layout, output_dtype))
 
 
+def box_iou_matcher(*inputs, anchors, high_threshold=0.5, low_threshold=0.4, allow_low_quality_matches=True, device=None):
+    """amd.rocal.fn.box_iou_matcher: enables the matcher; read the result with Pipeline.get_matched_indices()."""
+    p = _pipe()
+    flat = [float(v) for v in (anchors.reshape(-1) if hasattr(anchors, "reshape") else anchors)]
+    p._check(C.box_iou_matcher(p._handle, _farr(flat), len(flat) // 4, high_threshold, low_threshold,
+                               1 if allow_low_quality_matches else 0))
+    return None, []
+
+
 def box_encoder(*inputs, anchors, criteria=0.5, means=None, offset=False, scale=1.0, stds=None, device=None):
     p = _pipe()
     means = means if means else [0.0, 0.0, 0.0, 0.0]

@@ -247,6 +247,14 @@ class Pipeline(object):
         self.copy_encoded_boxes_and_lables(boxes, labels)
         return boxes, labels
 
+    def get_matched_indices(self):
+        """rocalGetMatchedIndices: matched box index per anchor, [N, A] int32 (numpy)."""
+        mp, na = ctypes.c_void_p(), ctypes.c_size_t()
+        self._check(C.get_matched_indices(self._handle, ctypes.byref(mp), ctypes.byref(na)))
+        out = np.empty((self._batch_size, na.value), dtype=np.int32)
+        self._check(C.copy_matched_indices(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        return out
+
     def get_bounding_boxes(self):
         """Boxes of the current batch after the graph's crops and mirrors: (ltrb [T,4], labels [T], counts [N])."""
         total = C.get_bounding_boxes(self._handle, None, None, None)

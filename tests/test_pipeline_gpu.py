@@ -247,7 +247,7 @@ def test_config3_warp_affine_and_rotate_pipeline(cuda):
 
 def test_config4_ssd_pipeline(cuda):
     """configs[4] through the API: rocalSSDRandomCrop -> rocalResize(300x300) -> rocalCropMirrorNormalize fp32 NCHW
-    fused into one launch, plus rocalBoxEncoder on the boxes that followed the crop and the mirror."""
+    fused into one launch, plus rocalBoxEncoder and rocalBoxIouMatcher on the boxes that followed the crop and the mirror."""
     from rocal_b200 import fn, types
     from rocal_b200.pipeline import Pipeline
     rng = S.rng_for(4)
@@ -262,6 +262,7 @@ def test_config4_ssd_pipeline(cuda):
         out = fn.crop_mirror_normalize(r, crop=[300, 300], crop_pos_x=0.0, crop_pos_y=0.0, mean=MEAN, std=STD, mirror=mirror,
                                        output_layout=types.NCHW, output_dtype=types.FLOAT)
         fn.box_encoder(anchors=anchors, criteria=0.5, means=[0, 0, 0, 0], stds=[0.1, 0.1, 0.2, 0.2], offset=True, scale=1.0)
+        fn.box_iou_matcher(anchors=anchors, high_threshold=0.5, low_threshold=0.4, allow_low_quality_matches=True)
         pipe.set_outputs(out)
     pipe.build()
     for _ in range(2):
@@ -294,6 +295,8 @@ def test_config4_ssd_pipeline(cuda):
         gb, gl = pipe.get_encoded_boxes_and_lables()
         assert np.array_equal(gl, el)
         assert np.allclose(gb, eb, rtol=1e-5, atol=1e-6)
+        # rocalBoxIouMatcher on the same boxes
+        assert np.array_equal(pipe.get_matched_indices(), O.box_iou_match(b2, o2, anchors, 0.5, 0.4, True))
     pipe.rocal_release()
 
 
