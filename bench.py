@@ -320,11 +320,12 @@ def main():
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": n * world * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
-                    "h2d_bytes_per_step": int(h2d_per_step), "h2d_whole_images_bytes": int(arena_pinned.numel()),
+                    "h2d_bytes_per_step": int(h2d_per_step) * world, "h2d_whole_images_bytes": int(arena_pinned.numel()) * world,
+                    "h2d_note": "rank 0's bytes x ranks",
                     "h2d": {0: "whole images, one copy", 1: "one strided copy per image of the rectangle the crop can read",
                             2: "zero-copy: the kernel's bulk copies read the tap rows from the pinned arena; bytes = "
                                "footprint rectangles, an upper bound of what crosses the link"}[upload_mode],
-                    "d2h_bytes_per_step": int(host_back.numel() * 2), "steps": e2e_steps},
+                    "d2h_bytes_per_step": int(host_back.numel() * 2) * world, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": dict(clocks, window="warm-up + timed steps + end-to-end steps"),
             "roofline": {"bound": "hbm", "kernel": "resample_stream_kernel<half,NCHW,normalize>", "achieved": achieved,

@@ -71,7 +71,13 @@ typedef struct rb200_resample_sample {
  *                        even and saturated).
  *   fill_padding   : 1 = elements outside a sample's crop_w x crop_h are written as 0;
  *                    0 = they are left untouched (the reference leaves them undefined).
+ *   interpolation  : RB200_INTERP_BILINEAR (2 x 2 taps) or RB200_INTERP_TRIANGULAR (a triangle
+ *                    filter whose support grows with the down-scale ratio: ceil(2*max(ratio,1))
+ *                    taps per axis, normalised weights, result truncated to uint8), the
+ *                    arithmetic of resize_generic_pln1_hip_tensor
+ *                    (rocAL/rocAL_hip/rocal_hip_kernels.cpp:487-589) applied to each channel.
  */
+enum { RB200_INTERP_BILINEAR = 0, RB200_INTERP_TRIANGULAR = 1 };
 typedef struct rb200_resample_params {
     void* out;
     int32_t out_w, out_h;
@@ -79,6 +85,7 @@ typedef struct rb200_resample_params {
     int32_t normalize, fill_padding;
     float mul[3];
     float add[3];
+    int32_t interpolation;
 } rb200_resample_params;
 
 /* Resize / ResizeCropMirror / ResizeMirrorNormalize / fused Resize+CropMirrorNormalize.

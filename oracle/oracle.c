@@ -101,6 +101,78 @@ static inline int bilinear3(const uint8_t* img, uint32_t stride, int x_lo, int y
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Triangular ("generic") resize of one output position, 3 channels. Follows
+ * resize_generic_pln1_hip_tensor and its helpers (rocAL/rocAL_hip/rocal_hip_kernels.cpp):
+ *   :508-513  ratio > 1: radius = ratio, scale = 1/ratio; else radius = scale = 1
+ *   :553-556  offset = (ratio-1)/2 - radius, kernel size = ceil(2*radius)
+ *   :487-492  first tap = ceil(dst*ratio + offset + roi), weight = first - raw, first clamped from
+ *             above to the last source index
+ *   :494-497  coefficient = max(0, 1 - |(weight - radius + j) * scale|)
+ *   :567-580  rows outer, columns inner, taps clamped to the source, out += src * (col*row)
+ *   :582-587  out *= 1 / (row_sum * col_sum) (a zero sum counts as 1), clamp to [0,255], truncate.
+ * The in-tree kernel handles one channel; here it runs on each of the three interleaved channels, and
+ * the clamp range is the sample's ROI. Products feeding the running sum are one fmaf each.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+    float radius, scale, offset;
+    int ksize;
+} tri_axis;
+
+static inline tri_axis tri_axis_make(float ratio) {
+    tri_axis a;
+    if (ratio > 1.0f) { a.radius = ratio; a.scale = 1.0f / ratio; } else { a.radius = 1.0f; a.scale = 1.0f; }
+    a.offset = (ratio - 1.0f) * 0.5f - a.radius;
+    a.ksize = (int)ceilf(a.radius * 2.0f);
+    return a;
+}
+
+static inline void tri_loc(const tri_axis* a, float ratio, int dst, int roi_lo, int limit, int* first, float* weight) {
+    float raw = fmaf((float)dst, ratio, a->offset) + (float)roi_lo;
+    int r = (int)ceilf(raw);
+    *weight = (float)r - raw;
+    *first = r > limit ? limit : r;
+}
+
+static inline float tri_coeff(const tri_axis* a, float weight, int j) {
+    float c = 1.0f - fabsf(((weight - a->radius) + (float)j) * a->scale);
+    return c < 0.f ? 0.f : c;
+}
+
+static inline uint8_t trunc_u8(float v) {
+    v = fmaxf(fminf(v, 255.f), 0.f);   /* NaN -> 0 through fmaxf */
+    return (uint8_t)v;
+}
+
+static void triangular3(const uint8_t* img, uint32_t stride, int x_lo, int y_lo, int x_hi, int y_hi,
+                        const tri_axis* ax, const tri_axis* ay, float ratio_w, float ratio_h, int dx, int dy,
+                        uint8_t out[3]) {
+    int fx, fy;
+    float wx, wy;
+    tri_loc(ax, ratio_w, dx, x_lo, x_hi, &fx, &wx);
+    tri_loc(ay, ratio_h, dy, y_lo, y_hi, &fy, &wy);
+    float acc[3] = {0.f, 0.f, 0.f};
+    float row_sum = 0.f, col_sum = 0.f;
+    for (int j = 0; j < ay->ksize; j++) {
+        int row = clampi(fy + j, y_lo, y_hi);
+        const uint8_t* r = img + (size_t)row * stride;
+        float rc = tri_coeff(ay, wy, j);
+        row_sum += rc;
+        col_sum = 0.f;
+        for (int k = 0; k < ax->ksize; k++) {
+            int col = clampi(fx + k, x_lo, x_hi);
+            float cc = tri_coeff(ax, wx, k);
+            col_sum += cc;
+            float coeff = cc * rc;
+            for (int c = 0; c < 3; c++) acc[c] = fmaf((float)r[col * 3 + c], coeff, acc[c]);
+        }
+    }
+    if (row_sum == 0.f) row_sum = 1.f;
+    if (col_sum == 0.f) col_sum = 1.f;
+    float inv = 1.0f / (row_sum * col_sum);
+    for (int c = 0; c < 3; c++) out[c] = trunc_u8(acc[c] * inv);
+}
+
+/* ------------------------------------------------------------------------------------------
  * Resample family. Per sample: resize the source rectangle roi to dst_w x dst_h (bilinear),
  * quantise to uint8 (the reference's Resize node outputs uint8 before the next node reads
  * it), take the window crop_*, mirror, then either store the uint8 or fma(u8, mul, add).
@@ -124,16 +196,21 @@ ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, i
         int x_hi = q->roi_x + q->roi_w - 1, y_hi = q->roi_y + q->roi_h - 1;
         int cw = q->crop_w < p->out_w ? q->crop_w : p->out_w;
         int ch = q->crop_h < p->out_h ? q->crop_h : p->out_h;
+        tri_axis ax = tri_axis_make(ratio_w), ay = tri_axis_make(ratio_h);
         for (int y = 0; y < ch; y++) {
             int ry = q->crop_y + y;
             float sy = (float)ry * ratio_h + off_h + (float)q->roi_y;
             for (int x = 0; x < cw; x++) {
                 int rx = q->crop_x + (q->mirror ? (q->crop_w - 1 - x) : x);
                 float sx = (float)rx * ratio_w + off_w + (float)q->roi_x;
-                float v[3];
-                bilinear3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, sx, sy, 0, v);
+                float v[3] = {0.f, 0.f, 0.f};
+                uint8_t t3[3] = {0, 0, 0};
+                if (p->interpolation == RB200_INTERP_TRIANGULAR)
+                    triangular3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, &ax, &ay, ratio_w, ratio_h, rx, ry, t3);
+                else
+                    bilinear3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, sx, sy, 0, v);
                 for (int c = 0; c < 3; c++) {
-                    float u = (float)sat_u8(v[c]);
+                    float u = p->interpolation == RB200_INTERP_TRIANGULAR ? (float)t3[c] : (float)sat_u8(v[c]);
                     float o = p->normalize ? fmaf(u, p->mul[c], p->add[c]) : u;
                     store_elem(p->out, p->out_dtype, out_index(p->out_layout, p->out_w, p->out_h, i, c, y, x), o);
                 }

@@ -22,7 +22,7 @@ class _ResampleParams(ctypes.Structure):
     _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
-                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3)]
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32)]
 
 
 class _PointwiseParams(ctypes.Structure):
@@ -84,7 +84,7 @@ def _ptr(a):
 
 
 def resample(arena, samples, out_w, out_h, out_dtype=FP32, out_layout=NCHW, mul=None, add=None,
-             fill_padding=True, out=None):
+             fill_padding=True, out=None, interpolation=0):
     n = len(samples)
     if out is None:
         out = _out_array(n, out_w, out_h, out_dtype, out_layout, True)
@@ -93,6 +93,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=FP32, out_layout=NCHW, mul=
     p.out_w, p.out_h, p.out_dtype, p.out_layout = out_w, out_h, out_dtype, out_layout
     p.normalize = 1 if mul is not None else 0
     p.fill_padding = 1 if fill_padding else 0
+    p.interpolation = int(interpolation)
     for c in range(3):
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0

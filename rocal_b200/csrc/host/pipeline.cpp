@@ -859,10 +859,14 @@ bool Pipeline::source_footprint(const uint8_t* h_tab, size_t i, int W, int H, in
             const rb200_resample_sample& q = reinterpret_cast<const rb200_resample_sample*>(h_tab + k * n * 64)[i];
             if (q.dst_w <= 0 || q.dst_h <= 0 || q.roi_w <= 0 || q.roi_h <= 0) return false;
             const double rx = (double)q.roi_w / q.dst_w, ry = (double)q.roi_h / q.dst_h;
-            ax0 = q.roi_x + (int)std::floor(q.crop_x * rx - 1.0) - 1;
-            ay0 = q.roi_y + (int)std::floor(q.crop_y * ry - 1.0) - 1;
-            ax1 = q.roi_x + (int)std::ceil((q.crop_x + q.crop_w) * rx) + 2;
-            ay1 = q.roi_y + (int)std::ceil((q.crop_y + q.crop_h) * ry) + 2;
+            // reach of the filter on each side of the mapped position: one tap for bilinear, the radius
+            // max(ratio, 1) for the triangular filter
+            const bool tri = _nodes[st.resize].interpolation == RB200_INTERP_TRIANGULAR;
+            const double mx = tri ? std::max(rx, 1.0) + 1.0 : 1.0, my = tri ? std::max(ry, 1.0) + 1.0 : 1.0;
+            ax0 = q.roi_x + (int)std::floor(q.crop_x * rx - mx) - 1;
+            ay0 = q.roi_y + (int)std::floor(q.crop_y * ry - my) - 1;
+            ax1 = q.roi_x + (int)std::ceil((q.crop_x + q.crop_w) * rx + mx - 1.0) + 2;
+            ay1 = q.roi_y + (int)std::ceil((q.crop_y + q.crop_h) * ry + my - 1.0) + 2;
             ax0 = std::max(ax0, q.roi_x); ay0 = std::max(ay0, q.roi_y);
             ax1 = std::min(ax1, q.roi_x + q.roi_w - 1); ay1 = std::min(ay1, q.roi_y + q.roi_h - 1);
         } else if (st.kind == Step::POINTWISE) {
@@ -964,7 +968,10 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         for (const Step& st : _steps)
             if (st.in_tensor == _source) {
                 consumers++;
-                gather = gather || st.kind == Step::WARP;
+                // kernels that fetch every tap on its own (affine gathers, the triangular filter) would cross
+                // the link once per tap
+                gather = gather || st.kind == Step::WARP ||
+                         (st.kind == Step::RESAMPLE && _nodes[st.resize].interpolation != RB200_INTERP_BILINEAR);
             }
         if (consumers == 1 && !gather) {
             void* dp = nullptr;
@@ -1140,6 +1147,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             // A fixed-size output (crop or stretch target) is fully defined, padding zeroed; a
             // plain resize into its max-shape tensor defines only the ROI, as the reference does.
             p.fill_padding = (st.post >= 0 || _nodes[st.resize].kind != NodeKind::RESIZE) ? 1 : 0;
+            p.interpolation = _nodes[st.resize].interpolation;
             rc = rb200k_resample(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk, (int)n, &p, _stream);
         } else if (st.kind == Step::POINTWISE) {
             rb200_pointwise_params p{};

@@ -51,6 +51,7 @@ struct Node {
     // resize family
     unsigned dest_w = 0, dest_h = 0, max_w = 0, max_h = 0;
     int scaling_mode = ROCAL_SCALING_MODE_STRETCH;
+    int interpolation = RB200_INTERP_BILINEAR;   // resize-type nodes
     std::vector<int> dst_w, dst_h;
     // crop family
     CropSpec crop;

@@ -102,9 +102,16 @@ void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling
     nd.max_h = max_h;
 }
 
+// Resize-type operators take the bilinear and the triangular filter.
+int resize_interpolation(int interpolation) {
+    if (interpolation == ROCAL_LINEAR_INTERPOLATION) return RB200_INTERP_BILINEAR;
+    if (interpolation == ROCAL_TRIANGULAR_INTERPOLATION) return RB200_INTERP_TRIANGULAR;
+    RB200_THROW("resize implements ROCAL_LINEAR_INTERPOLATION and ROCAL_TRIANGULAR_INTERPOLATION only");
+}
+
 void check_interpolation(int interpolation) {
     if (interpolation != ROCAL_LINEAR_INTERPOLATION)
-        RB200_THROW("only ROCAL_LINEAR_INTERPOLATION is implemented");
+        RB200_THROW("only ROCAL_LINEAR_INTERPOLATION is implemented for this operator");
 }
 
 rb200_tensor finish(Pipeline* p, Node&& nd, TensorImpl* in, unsigned w, unsigned h, int lay, int dt, int is_output) {
@@ -355,8 +362,8 @@ rb200_tensor rb200_resize(rb200_context ctx, rb200_tensor in, unsigned dest_widt
                           int scaling_mode, unsigned max_w, unsigned max_h, unsigned resize_shorter,
                           unsigned resize_longer, int interpolation, int out_layout, int out_dtype) {
     API_BEGIN
-    check_interpolation(interpolation);
     Node nd;
+    nd.interpolation = resize_interpolation(interpolation);
     nd.kind = NodeKind::RESIZE;
     unsigned mw, mh;
     resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh);
@@ -370,8 +377,8 @@ rb200_tensor rb200_resize_mirror_normalize(rb200_context ctx, rb200_tensor in, u
                                            unsigned resize_longer, int interpolation, rb200_param mirror, int out_layout,
                                            int out_dtype) {
     API_BEGIN
-    check_interpolation(interpolation);
     Node nd;
+    nd.interpolation = resize_interpolation(interpolation);
     nd.kind = NodeKind::RESIZE_MIRROR_NORMALIZE;
     unsigned mw, mh;
     resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh);

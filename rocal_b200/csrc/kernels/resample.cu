@@ -717,7 +717,106 @@ __global__ void __launch_bounds__(256) resample_direct_kernel(const uint8_t* __r
     }
 }
 
-enum { MODE_DIRECT = 0, MODE_STAGED = 1, MODE_STREAM = 2 };
+// ---- triangular ("generic") interpolation -------------------------------------------------------
+// One thread per output column, th rows per CTA, taps gathered through L1/L2. Arithmetic of
+// resize_generic_pln1_hip_tensor (rocAL/rocAL_hip/rocal_hip_kernels.cpp:487-589) on each channel:
+// per axis radius = max(ratio, 1), scale = 1/radius, ceil(2*radius) taps starting at
+// ceil(dst*ratio + (ratio-1)/2 - radius + roi), triangle weights max(0, 1 - |(w - radius + j)*scale|),
+// rows outer / columns inner accumulation with one fmaf per tap and channel, normalisation by
+// 1 / (row_sum * col_sum), clamp to [0,255] and truncation.
+struct TriAxis {
+    float radius, scale, offset;
+    int ksize;
+};
+__device__ __forceinline__ TriAxis tri_axis_make(float ratio) {
+    TriAxis a;
+    if (ratio > 1.0f) { a.radius = ratio; a.scale = div_rn(1.0f, ratio); } else { a.radius = 1.0f; a.scale = 1.0f; }
+    a.offset = sub_rn(mul_rn(sub_rn(ratio, 1.0f), 0.5f), a.radius);
+    a.ksize = (int)ceilf(mul_rn(a.radius, 2.0f));
+    return a;
+}
+__device__ __forceinline__ void tri_loc(const TriAxis& a, float ratio, int dst, int roi_lo, int limit, int& first, float& weight) {
+    const float raw = add_rn(fmaf((float)dst, ratio, a.offset), (float)roi_lo);
+    const int r = (int)ceilf(raw);
+    weight = sub_rn((float)r, raw);
+    first = min(r, limit);
+}
+__device__ __forceinline__ float tri_coeff(const TriAxis& a, float weight, int j) {
+    const float c = sub_rn(1.0f, fabsf(mul_rn(add_rn(sub_rn(weight, a.radius), (float)j), a.scale)));
+    return c < 0.f ? 0.f : c;
+}
+
+template <typename OutT, int LAYOUT>
+__global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t* __restrict__ arena,
+                                                                  const rb200_resample_sample* __restrict__ samples,
+                                                                  const ResampleLaunch L) {
+    const int n = blockIdx.y;
+    const int tx = blockIdx.x % L.tiles_x;
+    const int ty = blockIdx.x / L.tiles_x;
+    const int xi = tx * blockDim.x + threadIdx.x;
+    const int tile_y0 = ty * L.th;
+
+    const rb200_resample_sample s = samples[n];
+    const uint8_t* img = arena + s.src_offset;
+    OutT* out = reinterpret_cast<OutT*>(L.out);
+    const int cw = min(s.crop_w, L.out_w);
+    const int ch = min(s.crop_h, L.out_h);
+    const int rows_valid = min(L.th, ch - tile_y0);
+
+    if (rows_valid > 0 && xi < cw) {
+        const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
+        const float ratio_h = div_rn((float)s.roi_h, (float)s.dst_h);
+        const TriAxis ax = tri_axis_make(ratio_w), ay = tri_axis_make(ratio_h);
+        const int x_lo = s.roi_x, y_lo = s.roi_y;
+        const int x_hi = s.roi_x + s.roi_w - 1, y_hi = s.roi_y + s.roi_h - 1;
+        const int rx = s.crop_x + (s.mirror ? (s.crop_w - 1 - xi) : xi);
+        int fx;
+        float wx;
+        tri_loc(ax, ratio_w, rx, x_lo, x_hi, fx, wx);
+        for (int j0 = 0; j0 < rows_valid; j0++) {
+            int fy;
+            float wy;
+            tri_loc(ay, ratio_h, s.crop_y + tile_y0 + j0, y_lo, y_hi, fy, wy);
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, row_sum = 0.f, col_sum = 0.f;
+            for (int j = 0; j < ay.ksize; j++) {
+                const int row = min(max(fy + j, y_lo), y_hi);
+                const uint8_t* r = img + (size_t)row * s.src_stride;
+                const float rc = tri_coeff(ay, wy, j);
+                row_sum = add_rn(row_sum, rc);
+                col_sum = 0.f;
+                for (int k = 0; k < ax.ksize; k++) {
+                    const int col = min(max(fx + k, x_lo), x_hi);
+                    const float cc = tri_coeff(ax, wx, k);
+                    col_sum = add_rn(col_sum, cc);
+                    const float coeff = mul_rn(cc, rc);
+                    const uint8_t* px = r + col * 3;
+                    acc0 = fmaf((float)__ldg(px), coeff, acc0);
+                    acc1 = fmaf((float)__ldg(px + 1), coeff, acc1);
+                    acc2 = fmaf((float)__ldg(px + 2), coeff, acc2);
+                }
+            }
+            if (row_sum == 0.f) row_sum = 1.f;
+            if (col_sum == 0.f) col_sum = 1.f;
+            const float inv = div_rn(1.0f, mul_rn(row_sum, col_sum));
+            float v[3] = {mul_rn(acc0, inv), mul_rn(acc1, inv), mul_rn(acc2, inv)};
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                v[c] = truncf(fmaxf(fminf(v[c], 255.f), 0.f));     // fmaxf sends NaN to 0
+                if (L.normalize) v[c] = fmaf(v[c], L.mul[c], L.add[c]);
+            }
+            store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, tile_y0 + j0, xi, v[0], v[1], v[2]);
+        }
+    }
+    if (L.fill_padding && xi < L.out_w) {
+        const int rows_in_tile = min(L.th, L.out_h - tile_y0);
+        for (int j = 0; j < rows_in_tile; j++) {
+            int y = tile_y0 + j;
+            if (y >= ch || xi >= cw) store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, xi, 0.f, 0.f, 0.f);
+        }
+    }
+}
+
+enum { MODE_DIRECT = 0, MODE_STAGED = 1, MODE_STREAM = 2, MODE_TRIANGULAR = 3 };
 
 template <typename OutT, int LAYOUT>
 static int launch_typed(const uint8_t* arena, const rb200_resample_sample* samples, int n, ResampleLaunch L,
@@ -751,7 +850,10 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
         L.th = 8;
         int tiles_y = (L.ext_h + L.th - 1) / L.th;
         dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
-        resample_direct_kernel<OutT, LAYOUT><<<grid, tw, 0, stream>>>(arena, samples, L);
+        if (mode == MODE_TRIANGULAR)
+            resample_triangular_kernel<OutT, LAYOUT><<<grid, tw, 0, stream>>>(arena, samples, L);
+        else
+            resample_direct_kernel<OutT, LAYOUT><<<grid, tw, 0, stream>>>(arena, samples, L);
     }
     RB200_CHECK_LAUNCH("resample_kernel");
     return RB200_OK;
@@ -775,6 +877,10 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     }
     if (p->out_dtype < 0 || p->out_dtype > 2 || (p->out_layout != RB200_NCHW && p->out_layout != RB200_NHWC)) {
         set_error("rb200k_resample: bad out_dtype %d / out_layout %d", p->out_dtype, p->out_layout);
+        return RB200_E_INVALID;
+    }
+    if (p->interpolation != RB200_INTERP_BILINEAR && p->interpolation != RB200_INTERP_TRIANGULAR) {
+        set_error("rb200k_resample: bad interpolation %d", p->interpolation);
         return RB200_E_INVALID;
     }
     cudaStream_t stream = (cudaStream_t)stream_v;
@@ -861,6 +967,7 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
                    (size_t)(2 * th + 2) * pitch;
         }
     }
+    if (p->interpolation == RB200_INTERP_TRIANGULAR) mode = MODE_TRIANGULAR;
     L.th = th;
     L.pitch = pitch;
     L.twh = twh;

@@ -1,6 +1,6 @@
 """Per-operator device-resident benchmark of the kernel C-ABI on the benchmark configurations.
 
-    python -m rocal_b200.opbench [--ops color_twist,warp,box_encoder,box_matcher,ssd_chain,cfg0,brightness,flip] [--steps 50]
+    python -m rocal_b200.opbench [--ops color_twist,warp,box_encoder,box_matcher,triangular,ssd_chain,cfg0,brightness,flip] [--steps 50]
 
 Prints one JSON line per operator: images/s, mean launch time (CUDA events on the launching stream),
 algorithmic bytes per launch and the fraction of the measured HBM copy bandwidth. Every operator rotates
@@ -128,6 +128,21 @@ def main():
             ms = _time(fns, args.steps)
             report("cfg4 box_encoder 8732 anchors (batch 128)", n, ms, n * 8732 * 20 + nbox * 20 + 8732 * 16,
                    {"us_per_batch": ms * 1e3, "boxes_per_batch": nbox})
+        elif op == "triangular":
+            # configs[1] geometry (Resize shorter->256 + crop 224 + mirror + normalize, fp16 NCHW) with the triangular filter
+            n, rot = 256, 2
+            fns, algo = [], 0.0
+            for r in range(rot):
+                rng = S.rng_for(1, 400 + r)
+                arena, hs, ws, offs = S.make_images(rng, n, (300, 1080), (300, 1080))
+                t = S.classification_tables(rng, hs, ws, offs)
+                short = np.minimum(hs, ws).astype(np.float64)
+                algo = float((3.0 * (np.ceil(224 / (256 / short)) + 1) ** 2).sum() + n * 3 * 224 * 224 * 2)
+                a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
+                out = torch.empty((n, 3, 224, 224), dtype=torch.float16, device=dev)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out,
+                                                                       d_samples=dt, interpolation=1))
+            report("cfg1 geometry, triangular filter, fp16 NCHW (batch 256, 300..1080 px)", n, _time(fns, args.steps), algo)
         elif op == "box_matcher":
             # RetinaNet-sized anchor table (120 087 boxes), batch 32, 1..50 boxes per sample
             n, rot = 32, 4

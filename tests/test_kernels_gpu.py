@@ -214,6 +214,31 @@ def test_flip_twice_is_identity(cuda):
         assert np.array_equal(twice[i], img)
 
 
+@pytest.mark.parametrize("dtype,layout", [(T.UINT8, T.NHWC), (T.FP32, T.NCHW), (T.FP16, T.NCHW)])
+def test_resample_triangular(cuda, dtype, layout):
+    """Triangular filter (ROCAL_TRIANGULAR_INTERPOLATION): down-scale ratios 1.2..4.2 with their growing tap
+    counts, up-scaling (two taps per axis), a crop -> resize chain with mirror, ragged sizes; bit-exact against
+    the restatement of the reference's generic resize kernel."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(19)
+    arena, hs, ws, offs = S.make_images(rng, 12, (60, 400), (60, 400))
+    t = S.classification_tables(rng, hs, ws, offs, resize_shorter=96, crop=80)
+    # samples 0..2: up-scaling; 3..5: a window of the source resized to a fixed size
+    for i in range(3):
+        t[i]["dst_w"], t[i]["dst_h"] = int(ws[i] * 1.7), int(hs[i] * 1.3)
+        t[i]["crop_x"], t[i]["crop_y"] = 3, 2
+    for i in range(3, 6):
+        t[i]["roi_x"], t[i]["roi_y"] = ws[i] // 5, hs[i] // 7
+        t[i]["roi_w"], t[i]["roi_h"] = ws[i] // 2, hs[i] // 2
+        t[i]["dst_w"], t[i]["dst_h"], t[i]["crop_x"], t[i]["crop_y"] = 80, 80, 0, 0
+    mul, add = S.normalize_tables() if dtype != T.UINT8 else (None, None)
+    ref = O.resample(arena, t, 80, 80, dtype, layout, mul, add, interpolation=1)
+    got = K.resample(_dev(arena, cuda), t, 80, 80, dtype, layout, mul, add, interpolation=1).cpu().numpy()
+    assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+    bil = O.resample(arena, t, 80, 80, dtype, layout, mul, add)
+    assert not np.array_equal(bil.view(np.uint8), ref.view(np.uint8))      # it is a different filter
+
+
 def test_warp_affine_config3(cuda):
     """configs[3]: 480x640 images, rotation +-45 deg, scale 0.8..1.2, shift +-32 px, zero border (batch 32)."""
     from rocal_b200 import kernels as K

@@ -76,6 +76,43 @@ def test_config0_pipeline(cuda, out_dtype):
     pipe.rocal_release()
 
 
+def test_triangular_resize_pipeline(cuda):
+    """rocalResize(interpolation_type=ROCAL_TRIANGULAR_INTERPOLATION) -> rocalCropMirrorNormalize, the filter of the
+    reference's imagenet example, fused into one launch; host input goes up as footprint rectangles widened by the
+    filter radius."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(22)
+    n = 8
+    pipe = Pipeline(batch_size=n, device_id=0, seed=5)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=600, max_height=600)
+        r = fn.resize(img, resize_shorter=128, interpolation_type=types.TRIANGULAR_INTERPOLATION)
+        mirror = fn.random.coin_flip()
+        out = fn.crop_mirror_normalize(r, crop=[112, 112], mean=MEAN, std=STD, mirror=mirror, output_layout=types.NCHW,
+                                       output_dtype=types.FLOAT)
+        pipe.set_outputs(out)
+    pipe.build()
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (150, 600), (150, 600))
+        ax, ay = rng.random(n).astype(np.float32), rng.random(n).astype(np.float32)
+        pipe.set_crop_anchors(out, ax, ay)
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        m = pipe.get_int_array(mirror)
+        t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        for i in range(n):
+            dw, dh = O.resize_dst_size(int(ws[i]), int(hs[i]), 128, 128, 2, cap_w=768, cap_h=768)
+            x1, y1, cw, ch = O.crop_fixed(dw, dh, 112, 112, float(ax[i]), float(ay[i]))
+            t[i]["src_offset"], t[i]["src_stride"] = offs[i], ws[i] * 3
+            t[i]["roi_w"], t[i]["roi_h"], t[i]["dst_w"], t[i]["dst_h"] = ws[i], hs[i], dw, dh
+            t[i]["crop_x"], t[i]["crop_y"], t[i]["crop_w"], t[i]["crop_h"], t[i]["mirror"] = x1, y1, cw, ch, m[i]
+        mul, add = S.normalize_tables()
+        exp = O.resample(arena, t, 112, 112, T.FP32, T.NCHW, mul, add, interpolation=1)
+        assert np.array_equal(pipe.get_output_tensors()[0].numpy(), exp)
+    pipe.rocal_release()
+
+
 def test_upload_modes(cuda):
     """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
     copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
@@ -319,7 +356,7 @@ def test_error_convention(cuda):
     assert src
     assert not C.resize(ctx, src, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 2)     # no size given
     assert b"must be specified" in C.get_error_message(ctx)
-    assert not C.resize(ctx, src, 10, 10, 0, 1, 0, 0, 0, 0, types.TRIANGULAR_INTERPOLATION, 0, 2)
+    assert not C.resize(ctx, src, 10, 10, 0, 1, 0, 0, 0, 0, types.CUBIC_INTERPOLATION, 0, 2)
     assert C.run(ctx) == types.RUNTIME_ERROR                            # not verified
     r = C.resize(ctx, src, 10, 10, 1, 1, 0, 0, 0, 0, 1, 0, 2)
     assert r and C.verify(ctx) == types.OK
