@@ -223,3 +223,55 @@ def test_warp_properties():
         if hs[i] % 2 == 0 and ws[i] % 2 == 0:
             img = arena[int(offs[i]):int(offs[i]) + hs[i] * ws[i] * 3].reshape(hs[i], ws[i], 3)
             assert np.array_equal(o[i, 2:hs[i], 2:ws[i]], img[::-1, ::-1][1:hs[i] - 1, 1:ws[i] - 1])
+
+
+def test_triangular_properties():
+    """The triangular filter: identity at ratio 1, two-tap behaviour when up-scaling, and an independent numpy
+    statement of the same sums on a small down-scale case."""
+    rng = S.rng_for(31)
+    arena, hs, ws, offs = S.make_images(rng, 3, (20, 40), (20, 50))
+    n = 3
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    t["roi_w"], t["roi_h"], t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = ws, hs, ws, hs, ws, hs
+    out = O.resample(arena, t, 50, 40, T.UINT8, T.NHWC, interpolation=1)
+    for i in range(n):
+        o, h, w = int(offs[i]), int(hs[i]), int(ws[i])
+        assert np.array_equal(out[i, :h, :w], arena[o:o + h * w * 3].reshape(h, w, 3))
+    # independent float32 statement, sample 0 down-scaled by 2.5 x 1.6
+    o, h, w = int(offs[0]), int(hs[0]), int(ws[0])
+    img = arena[o:o + h * w * 3].reshape(h, w, 3)
+    dw, dh = int(w / 2.5), int(h / 1.6)
+    t1 = t[:1].copy()
+    t1["dst_w"], t1["dst_h"], t1["crop_w"], t1["crop_h"] = dw, dh, dw, dh
+    got = O.resample(arena, t1, dw, dh, T.UINT8, T.NHWC, interpolation=1)[0]
+    f = np.float32
+
+    def axis(src, dst):
+        ratio = f(src) / f(dst)
+        radius, scale = (ratio, f(1) / ratio) if ratio > 1 else (f(1), f(1))
+        return ratio, radius, scale, (ratio - f(1)) * f(0.5) - radius, int(np.ceil(radius * f(2)))
+
+    rw, radw, scw, offw, kw = axis(w, dw)
+    rh, radh, sch, offh, kh = axis(h, dh)
+    for (x, y) in ((0, 0), (dw - 1, dh - 1), (dw // 2, dh // 3), (1, dh - 2)):
+        rawx = f(np.float32(x) * rw + offw)      # the fused multiply-add rounds once; so does float64 -> float32 here
+        rawx = f(np.float64(x) * np.float64(rw) + np.float64(offw))
+        rawy = f(np.float64(y) * np.float64(rh) + np.float64(offh))
+        fx, fy = int(np.ceil(rawx)), int(np.ceil(rawy))
+        wx, wy = f(fx) - rawx, f(fy) - rawy
+        fx, fy = min(fx, w - 1), min(fy, h - 1)
+        acc = np.zeros(3, dtype=np.float64)
+        rs = f(0)
+        for j in range(kh):
+            rc = max(f(0), f(1) - abs(f(f(wy - radh) + f(j)) * sch))
+            rs = f(rs + rc)
+            cs = f(0)
+            for k in range(kw):
+                cc = max(f(0), f(1) - abs(f(f(wx - radw) + f(k)) * scw))
+                cs = f(cs + cc)
+                px = img[min(max(fy + j, 0), h - 1), min(max(fx + k, 0), w - 1)].astype(np.float64)
+                acc += px * np.float64(f(cc * rc))
+        val = acc / (np.float64(rs) * np.float64(cs))
+        # the float64 accumulation differs from the float32 fmaf chain by far less than one grey level
+        assert np.all(np.abs(got[y, x].astype(np.float64) - np.floor(np.clip(val, 0, 255))) <= 1), (x, y)
