@@ -70,12 +70,17 @@ RB200_API int rb200_get_int_value(rb200_param p);
 RB200_API float rb200_get_float_value(rb200_param p);
 
 /* ---- input ---- */
-/* rocalJpegExternalFileSource with ROCAL_EXTSOURCE_RAW_UNCOMPRESSED (rocal_api_data_loaders.h:961-970) */
+/* rocalJpegExternalFileSource (rocal_api_data_loaders.h:961-970) in its three modes:
+ * ROCAL_EXTSOURCE_RAW_UNCOMPRESSED (decoded pixels), ROCAL_EXTSOURCE_RAW_COMPRESSED (JPEG streams) and
+ * ROCAL_EXTSOURCE_FNAME (JPEG files). JPEG input is decoded on the GPU by NVIDIA's nvJPEG library straight into
+ * the packed arena the kernels read; max_width x max_height bounds the decoded size. */
 RB200_API rb200_tensor rb200_external_source(rb200_context ctx, int color_format, int is_output, unsigned max_width,
                                              unsigned max_height, int external_source_mode);
 /* rocalExternalSourceFeedInput (rocal_api_data_transfer.h:101-105): n buffers of max_height x max_width x
- * channels bytes, roi_xywh = 4*n unsigned. The buffers must stay valid until the batch has been
- * returned by rb200_run (the reference queues the pointers too: external_source_reader.cpp:220-233). */
+ * channels bytes, roi_xywh = 4*n unsigned; in ROCAL_EXTSOURCE_RAW_COMPRESSED mode buffer i is a JPEG stream
+ * whose byte length is roi_xywh[4*i+3] (image_read_and_decode.cpp:123-124). The buffers must stay valid until
+ * the batch has been returned by rb200_run (the reference queues the pointers too:
+ * external_source_reader.cpp:220-233). */
 RB200_API int rb200_feed_input(rb200_context ctx, const unsigned char* const* buffers, const unsigned* roi_xywh,
                                size_t n, unsigned max_width, unsigned max_height, unsigned channels, int mode,
                                int layout, int eos);
@@ -93,6 +98,10 @@ enum { RB200_MEM_HOST = 0, RB200_MEM_HOST_PINNED = 1, RB200_MEM_DEVICE = 2 };
  * The arena must stay valid until the batch has been returned by rb200_run. */
 RB200_API int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes,
                                 const rb200_image_desc* descs, size_t n, int mem_kind);
+/* [extension] JPEG streams with their lengths as size_t (same lifetime rule as rb200_feed_input), and JPEG
+ * files by name (read at feed time; the FNAME mode of rocalExternalSourceFeedInput). */
+RB200_API int rb200_feed_encoded(rb200_context ctx, const unsigned char* const* buffers, const size_t* sizes, size_t n);
+RB200_API int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n);
 /* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
  * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
 RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);

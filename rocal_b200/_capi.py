@@ -39,6 +39,8 @@ release = _proto("rb200_release", c_int, _P)
 get_status = _proto("rb200_get_status", c_int, _P)
 get_error_message = _proto("rb200_get_error_message", c_char_p, _P)
 get_timing = _proto("rb200_get_timing", None, _P, POINTER(ctypes.c_ulonglong))
+feed_encoded = _proto("rb200_feed_encoded", c_int, _P, POINTER(c_void_p), POINTER(c_size_t), c_size_t)
+feed_files = _proto("rb200_feed_files", c_int, _P, POINTER(ctypes.c_char_p), c_size_t)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)
 set_upload_mode = _proto("rb200_set_upload_mode", ctypes.c_int, _P, ctypes.c_int)
 get_remaining_images = _proto("rb200_get_remaining_images", c_size_t, _P)

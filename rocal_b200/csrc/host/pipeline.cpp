@@ -510,6 +510,9 @@ void Pipeline::feed(InputBatch&& b) {
             if (w == 0 || h == 0 || x + w > b.max_w || y + h > b.max_h)
                 RB200_THROW("input ROI of sample " + std::to_string(i) + " is empty or exceeds max_width x max_height");
         }
+    } else if (b.kind == InputBatch::ENCODED) {
+        for (size_t i = 0; i < b.n; i++)
+            if (!b.bufs[i] || b.enc_sizes[i] == 0) RB200_THROW("encoded image " + std::to_string(i) + " is empty");
     } else {
         if (!b.arena) RB200_THROW("null input arena");
         for (size_t i = 0; i < b.n; i++) {
@@ -947,6 +950,22 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             src->roi_h[i] = (int)b.descs[i].height;
         }
         if (!host_input) _src_base = (const uint8_t*)b.arena;
+    } else if (b.kind == InputBatch::ENCODED) {
+        // JPEG streams: sizes from the headers, then one batched decode into the packed arena (below)
+        _jpeg.init();
+        size_t total = 0;
+        for (size_t i = 0; i < n; i++) {
+            int w = 0, h = 0;
+            _jpeg.image_size(b.bufs[i], b.enc_sizes[i], w, h);
+            if (w <= 0 || h <= 0 || w > src->max_w || h > src->max_h)
+                RB200_THROW("decoded image " + std::to_string(i) + " (" + std::to_string(w) + "x" + std::to_string(h) +
+                            ") is empty or exceeds the source's max_width x max_height");
+            _src_views[i] = {total, (uint32_t)w * 3};
+            src->roi_w[i] = w;
+            src->roi_h[i] = h;
+            total += ((size_t)w * h * 3 + 255) & ~(size_t)255;
+        }
+        b.arena_bytes = total + 256;
     } else {
         size_t total = 0;
         for (size_t i = 0; i < n; i++) {
@@ -1112,7 +1131,20 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             }
         }
     }
-    if (host_input) {
+    if (b.kind == InputBatch::ENCODED) {
+        unsigned long long tl = now_us();
+        _jpeg_dst.resize(n);
+        _jpeg_pitch.resize(n);
+        size_t enc = 0;
+        for (size_t i = 0; i < n; i++) {
+            _jpeg_dst[i] = (unsigned char*)_arena[arena_used] + _src_views[i].offset;
+            _jpeg_pitch[i] = _src_views[i].stride;
+            enc += b.enc_sizes[i];
+        }
+        _jpeg.decode_batch(b.bufs.data(), b.enc_sizes.data(), (int)n, _jpeg_dst.data(), _jpeg_pitch.data(), _stream);
+        _h2d_bytes += enc;
+        _t_decode += now_us() - tl;
+    } else if (host_input) {
         unsigned long long tl = now_us();
         upload_sources(b, arena_used, (const uint8_t*)s.h_tables);
         _t_load += now_us() - tl;
@@ -1389,7 +1421,7 @@ void Pipeline::to_tensor(void* out_ptr, int layout, int dtype, const float* mul,
 TimingInfo Pipeline::timing() {
     TimingInfo t;
     t.load_time = _t_load.load();
-    t.decode_time = 0;
+    t.decode_time = _t_decode.load();
     t.process_time = _t_process.load();
     t.transfer_time = _t_transfer.load();
     return t;

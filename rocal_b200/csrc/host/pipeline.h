@@ -23,6 +23,7 @@
 #include <thread>
 #include <vector>
 
+#include "jpeg_decoder.h"
 #include "params.h"
 #include "rb200.h"
 #include "rocal_api.h"
@@ -152,7 +153,7 @@ struct SampleView {
 enum UploadMode { UPLOAD_WHOLE = 0, UPLOAD_FOOTPRINT = 1, UPLOAD_ZERO_COPY = 2 };
 
 struct InputBatch {
-    enum Kind { SLOTS, RAGGED } kind = SLOTS;
+    enum Kind { SLOTS, RAGGED, ENCODED } kind = SLOTS;
     size_t n = 0;
     std::vector<const unsigned char*> bufs;   // SLOTS
     std::vector<unsigned> roi;                // SLOTS: n x {x,y,w,h}
@@ -161,6 +162,8 @@ struct InputBatch {
     size_t arena_bytes = 0;
     int mem_kind = RB200_MEM_HOST;
     std::vector<rb200_image_desc> descs;
+    std::vector<size_t> enc_sizes;                          // ENCODED: byte length of bufs[i]
+    std::vector<std::vector<unsigned char>> enc_owned;      // ENCODED from file names: the bytes read at feed time
     bool has_boxes = false;
     std::vector<float> boxes;                 // ltrb, normalized
     std::vector<int> labels, counts;
@@ -295,6 +298,11 @@ class Pipeline {
     // staging for extensions (attached to the next fed batch)
     InputBatch _staged;
 
+    // JPEG front-end (created when the first encoded batch arrives)
+    JpegDecoder _jpeg;
+    std::vector<unsigned char*> _jpeg_dst;
+    std::vector<size_t> _jpeg_pitch;
+
     // input arenas (double buffered)
     void* _arena[2] = {nullptr, nullptr};
     size_t _arena_cap[2] = {0, 0};
@@ -320,7 +328,7 @@ class Pipeline {
     RocalStatus _status = ROCAL_OK;
 
     // timing (us)
-    std::atomic<unsigned long long> _t_load{0}, _t_process{0}, _t_transfer{0};
+    std::atomic<unsigned long long> _t_load{0}, _t_decode{0}, _t_process{0}, _t_transfer{0};
     std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
     int _upload_mode = UPLOAD_ZERO_COPY;
 };

@@ -253,8 +253,9 @@ rb200_tensor rb200_external_source(rb200_context ctx, int color_format, int is_o
                                    unsigned max_height, int external_source_mode) {
     CTX_OR(nullptr);
     try {
-        if (external_source_mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED)
-            RB200_THROW("only ROCAL_EXTSOURCE_RAW_UNCOMPRESSED input is supported (image decoding is not part of this library)");
+        if (external_source_mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED && external_source_mode != ROCAL_EXTSOURCE_RAW_COMPRESSED &&
+            external_source_mode != ROCAL_EXTSOURCE_FNAME)
+            RB200_THROW("bad external source mode");
         if (color_format != ROCAL_COLOR_RGB24 && color_format != ROCAL_COLOR_BGR24)
             RB200_THROW("only 3-channel interleaved colour formats are supported");
         return static_cast<rocalTensor*>(P(ctx)->add_source(max_width, max_height, is_output != 0));
@@ -269,7 +270,21 @@ int rb200_feed_input(rb200_context ctx, const unsigned char* const* buffers, con
     CTX_OR(ROCAL_CONTEXT_INVALID);
     (void)eos;
     try {
-        if (mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED) RB200_THROW("only ROCAL_EXTSOURCE_RAW_UNCOMPRESSED input is supported");
+        if (mode == ROCAL_EXTSOURCE_RAW_COMPRESSED) {
+            // JPEG streams; the byte length of buffer i travels in roi[i].h
+            // (rocAL/source/loaders/image/image_read_and_decode.cpp:123-124)
+            if (!buffers || !roi_xywh) RB200_THROW("null input buffers or ROI");
+            InputBatch b;
+            b.kind = InputBatch::ENCODED;
+            b.n = n;
+            b.bufs.assign(buffers, buffers + n);
+            b.enc_sizes.resize(n);
+            for (size_t i = 0; i < n; i++) b.enc_sizes[i] = roi_xywh[i * 4 + 3];
+            P(ctx)->feed(std::move(b));
+            return ROCAL_OK;
+        }
+        if (mode != ROCAL_EXTSOURCE_RAW_UNCOMPRESSED)
+            RB200_THROW("rb200_feed_input takes RAW_UNCOMPRESSED or RAW_COMPRESSED buffers; file names go through rb200_feed_files");
         if (channels != 3) RB200_THROW("only 3-channel input is supported");
         if (layout != ROCAL_NHWC) RB200_THROW("raw input must be NHWC");
         if (!buffers || !roi_xywh) RB200_THROW("null input buffers or ROI");
@@ -280,6 +295,59 @@ int rb200_feed_input(rb200_context ctx, const unsigned char* const* buffers, con
         b.roi.assign(roi_xywh, roi_xywh + n * 4);
         b.max_w = max_width;
         b.max_h = max_height;
+        P(ctx)->feed(std::move(b));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_feed_encoded(rb200_context ctx, const unsigned char* const* buffers, const size_t* sizes, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buffers || !sizes) RB200_THROW("null input buffers or sizes");
+        InputBatch b;
+        b.kind = InputBatch::ENCODED;
+        b.n = n;
+        b.bufs.assign(buffers, buffers + n);
+        b.enc_sizes.assign(sizes, sizes + n);
+        P(ctx)->feed(std::move(b));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!paths) RB200_THROW("null file name list");
+        InputBatch b;
+        b.kind = InputBatch::ENCODED;
+        b.n = n;
+        b.enc_owned.resize(n);
+        b.bufs.resize(n);
+        b.enc_sizes.resize(n);
+        for (size_t i = 0; i < n; i++) {
+            if (!paths[i]) RB200_THROW("null file name");
+            FILE* f = std::fopen(paths[i], "rb");
+            if (!f) RB200_THROW(std::string("cannot open ") + paths[i]);
+            std::fseek(f, 0, SEEK_END);
+            long len = std::ftell(f);
+            std::fseek(f, 0, SEEK_SET);
+            if (len <= 0) {
+                std::fclose(f);
+                RB200_THROW(std::string("empty file ") + paths[i]);
+            }
+            b.enc_owned[i].resize((size_t)len);
+            size_t got = std::fread(b.enc_owned[i].data(), 1, (size_t)len, f);
+            std::fclose(f);
+            if (got != (size_t)len) RB200_THROW(std::string("short read on ") + paths[i]);
+            b.bufs[i] = b.enc_owned[i].data();
+            b.enc_sizes[i] = (size_t)len;
+        }
         P(ctx)->feed(std::move(b));
     } catch (const std::exception& e) {
         report(P(ctx), e);

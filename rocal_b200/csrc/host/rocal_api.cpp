@@ -54,11 +54,16 @@ RocalTensor ROCAL_API_CALL rocalJpegExternalFileSource(RocalContext ctx, RocalIm
     return static_cast<RocalTensor>(rb200_external_source(ctx, (int)color, is_output, max_width, max_height, (int)mode));
 }
 
-RocalStatus ROCAL_API_CALL rocalExternalSourceFeedInput(RocalContext ctx, const std::vector<std::string>&, bool,
+RocalStatus ROCAL_API_CALL rocalExternalSourceFeedInput(RocalContext ctx, const std::vector<std::string>& input_images_names, bool,
                                                         const std::vector<unsigned char*>& input_buffer,
                                                         const std::vector<ROIxywh>& roi_xywh, unsigned int max_width,
                                                         unsigned int max_height, unsigned int channels,
                                                         RocalExternalSourceMode mode, RocalTensorLayout layout, bool eos) {
+    if (mode == ROCAL_EXTSOURCE_FNAME) {
+        std::vector<const char*> names;
+        for (const auto& s : input_images_names) names.push_back(s.c_str());
+        return (RocalStatus)rb200_feed_files(ctx, names.data(), names.size());
+    }
     if (input_buffer.size() != roi_xywh.size()) {
         if (ctx) P(ctx)->capture_error("rocalExternalSourceFeedInput: one ROI per input buffer is required");
         std::cerr << "rocalExternalSourceFeedInput: one ROI per input buffer is required\n";

@@ -41,8 +41,9 @@ def _farr(v):
 def external_source(source, device=None, color_format=types.RGB, random_shuffle=False, mode=types.EXTSOURCE_FNAME,
                     max_width=2000, max_height=2000, last_batch_policy=types.LAST_BATCH_FILL,
                     pad_last_batch_repeated=False, stick_to_shard=True, shard_size=-1):
-    """fn.py:1091. Only mode=EXTSOURCE_RAW_UNCOMPRESSED is accepted; batches are fed with Pipeline.feed_input
-    or Pipeline.feed_ragged. Returns (images, labels) like the reference (labels is empty)."""
+    """fn.py:1091. mode=EXTSOURCE_RAW_UNCOMPRESSED takes decoded pixels (Pipeline.feed_input / feed_ragged);
+    EXTSOURCE_RAW_COMPRESSED and EXTSOURCE_FNAME take JPEG streams / files (Pipeline.feed_encoded / feed_files),
+    decoded on the GPU. Returns (images, labels) like the reference (labels is empty)."""
     p = _pipe()
     p._external_source_mode = mode
     p._max_w, p._max_h = max_width, max_height

@@ -143,6 +143,52 @@ def main():
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out,
                                                                        d_samples=dt, interpolation=1))
             report("cfg1 geometry, triangular filter, fp16 NCHW (batch 256, 300..1080 px)", n, _time(fns, args.steps), algo)
+        elif op == "jpeg_e2e":
+            # configs[1] pipeline fed with JPEG streams (quality 90, 4:2:0) instead of raw pixels: GPU decode (nvJPEG)
+            # -> Resize shorter 256 -> CropMirrorNormalize 224 fp16 NCHW, wall clock over whole batches
+            import time
+            import cv2
+            from rocal_b200 import fn, types
+            from rocal_b200.pipeline import Pipeline
+            n, batches = 256, 6
+            rng = S.rng_for(1, 500)
+            streams, raw_bytes = [], 0
+            for _ in range(n):
+                h, w = int(rng.integers(300, 1081)), int(rng.integers(300, 1081))
+                yy, xx = np.mgrid[0:h, 0:w].astype(np.float32)
+                ch = [127 + 100 * np.sin(xx / rng.uniform(20, 90) + rng.uniform(0, 6)) * np.cos(yy / rng.uniform(20, 90)) for _ in range(3)]
+                img = np.clip(np.stack(ch, axis=-1) + rng.normal(0, 6, (h, w, 3)), 0, 255).astype(np.uint8)
+                ok, enc = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, 90])
+                streams.append(enc.tobytes())
+                raw_bytes += h * w * 3
+            pipe = Pipeline(batch_size=n, device_id=0, seed=1, prefetch_queue_depth=2)
+            with pipe:
+                img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_COMPRESSED, max_width=1080, max_height=1080)
+                r = fn.resize(img, resize_shorter=256)
+                out = fn.crop_mirror_normalize(r, crop=[224, 224], mean=list(S.MEAN), std=list(S.STD), mirror=fn.random.coin_flip(),
+                                               output_layout=types.NCHW, output_dtype=types.FLOAT16)
+                pipe.set_outputs(out)
+            pipe.build()
+            pipe.feed_encoded(streams)
+            for _ in range(2):
+                pipe.feed_encoded(streams)
+                pipe.run()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for i in range(batches):
+                if i < batches - 1:
+                    pipe.feed_encoded(streams)
+                pipe.run()
+                torch.from_dlpack(pipe.get_output_tensors()[0])[0, 0, 0, 0].item()
+            torch.cuda.synchronize()
+            ms = (time.perf_counter() - t0) * 1e3 / batches
+            enc_bytes = sum(len(s) for s in streams)
+            tinfo = pipe.timing_info()
+            pipe.rocal_release()
+            print(json.dumps({"op": "cfg1 pipeline from JPEG streams (nvJPEG decode -> resize -> CMN fp16), batch 256", "images_per_batch": n,
+                              "batch_ms": ms, "images_per_s": n / (ms * 1e-3), "encoded_bytes_per_batch": enc_bytes,
+                              "decoded_bytes_per_batch": raw_bytes, "backend": os.environ.get("RB200_NVJPEG_BACKEND", "gpu_hybrid"),
+                              "decode_time_us_total": tinfo["decode_time"]}), flush=True)
         elif op == "box_matcher":
             # RetinaNet-sized anchor table (120 087 boxes), batch 32, 1..50 boxes per sample
             n, rot = 32, 4

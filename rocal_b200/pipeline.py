@@ -191,6 +191,23 @@ class Pipeline(object):
         self._keepalive.append((arena, descs))
         self._check(C.feed_ragged(self._handle, ctypes.c_void_p(ptr), nbytes, descs, n, kind))
 
+    def feed_encoded(self, streams):
+        """JPEG streams (bytes objects or uint8 numpy arrays), one per sample: decoded on the GPU (nvJPEG) into the
+        arena the kernels read. The source must have been created with mode=EXTSOURCE_RAW_COMPRESSED."""
+        n = len(streams)
+        arrs = [np.frombuffer(s, dtype=np.uint8) if isinstance(s, (bytes, bytearray, memoryview)) else np.ascontiguousarray(s, dtype=np.uint8)
+                for s in streams]
+        ptrs = (ctypes.c_void_p * n)(*[a.ctypes.data for a in arrs])
+        sizes = (ctypes.c_size_t * n)(*[a.nbytes for a in arrs])
+        self._keepalive.append((arrs, ptrs, sizes))
+        self._check(C.feed_encoded(self._handle, ptrs, sizes, n))
+
+    def feed_files(self, paths):
+        """JPEG files by name (the FNAME mode of rocalExternalSourceFeedInput)."""
+        n = len(paths)
+        arr = (ctypes.c_char_p * n)(*[str(p).encode() for p in paths])
+        self._check(C.feed_files(self._handle, arr, n))
+
     def feed_boxes(self, boxes, labels, counts):
         """[extension] Normalized ltrb boxes, labels and per-sample counts of the next fed batch."""
         b = np.ascontiguousarray(boxes, dtype=np.float32)

@@ -113,6 +113,77 @@ def test_triangular_resize_pipeline(cuda):
     pipe.rocal_release()
 
 
+def _jpeg_batch(rng, n, size_range):
+    """Smooth synthetic images (JPEG-friendly), their 4:4:4 quality-95 JPEG streams and the host decoder's pixels."""
+    cv2 = pytest.importorskip("cv2")
+    imgs, streams = [], []
+    for _ in range(n):
+        h, w = int(rng.integers(*size_range)), int(rng.integers(*size_range))
+        yy, xx = np.mgrid[0:h, 0:w].astype(np.float32)
+        chans = [127 + 100 * np.sin(xx / rng.uniform(15, 60) + rng.uniform(0, 6)) * np.cos(yy / rng.uniform(15, 60)) for _ in range(3)]
+        rgb = np.clip(np.stack(chans, axis=-1) + rng.normal(0, 3, (h, w, 3)), 0, 255).astype(np.uint8)
+        ok, enc = cv2.imencode(".jpg", rgb[:, :, ::-1], [cv2.IMWRITE_JPEG_QUALITY, 95, cv2.IMWRITE_JPEG_SAMPLING_FACTOR,
+                                                         cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444])
+        assert ok
+        streams.append(enc.tobytes())
+        imgs.append(np.ascontiguousarray(cv2.imdecode(enc, cv2.IMREAD_COLOR)[:, :, ::-1]))
+    return imgs, streams
+
+
+def test_jpeg_external_source(cuda, tmp_path):
+    """rocalJpegExternalFileSource in RAW_COMPRESSED and FNAME mode: JPEG streams are decoded on the GPU into the
+    arena the kernels read. The decoded pixels (through an identity flip) stay within a few grey levels of the host
+    decoder's (the two IDCTs differ in rounding), and Resize + CropMirrorNormalize on them matches the oracle run on
+    the host-decoded pixels to the same degree."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(23)
+    n = 6
+    imgs, streams = _jpeg_batch(rng, n, (120, 400))
+    for mode in (types.EXTSOURCE_RAW_COMPRESSED, types.EXTSOURCE_FNAME):
+        pipe = Pipeline(batch_size=n, device_id=0, seed=3)
+        with pipe:
+            img, _ = fn.external_source(None, mode=mode, max_width=400, max_height=400)
+            ident = fn.flip(img, horizontal=0, vertical=0)
+            r = fn.resize(img, resize_shorter=96)
+            out = fn.crop_mirror_normalize(r, crop=[80, 80], crop_pos_x=0.5, crop_pos_y=0.5, mean=MEAN, std=STD, mirror=0,
+                                           output_layout=types.NCHW, output_dtype=types.FLOAT)
+            pipe.set_outputs(ident, out)
+        pipe.build()
+        if mode == types.EXTSOURCE_FNAME:
+            paths = []
+            for i, sbytes in enumerate(streams):
+                p = tmp_path / ("img%d.jpg" % i)
+                p.write_bytes(sbytes)
+                paths.append(str(p))
+            pipe.feed_files(paths)
+        else:
+            pipe.feed_encoded(streams)
+        pipe.run()
+        dec, res = [t.numpy() for t in pipe.get_output_tensors()]
+        hs = np.array([im.shape[0] for im in imgs])
+        ws = np.array([im.shape[1] for im in imgs])
+        offs = np.concatenate([[0], np.cumsum(hs * ws * 3)])[:-1]
+        arena = np.concatenate([im.reshape(-1) for im in imgs])
+        for i in range(n):
+            d = np.abs(dec[i, :hs[i], :ws[i]].astype(np.int32) - imgs[i].astype(np.int32))
+            assert d.max() <= 6 and d.mean() < 0.7, (i, d.max(), d.mean())
+        # the geometry of _classification_pipeline with shorter side 96 / crop 80
+        t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        for i in range(n):
+            dw, dh = O.resize_dst_size(int(ws[i]), int(hs[i]), 96, 96, 2, cap_w=576, cap_h=576)
+            x1, y1, cw, ch = O.crop_fixed(dw, dh, 80, 80, 0.5, 0.5)
+            t[i]["src_offset"], t[i]["src_stride"] = offs[i], ws[i] * 3
+            t[i]["roi_w"], t[i]["roi_h"], t[i]["dst_w"], t[i]["dst_h"] = ws[i], hs[i], dw, dh
+            t[i]["crop_x"], t[i]["crop_y"], t[i]["crop_w"], t[i]["crop_h"] = x1, y1, cw, ch
+        mul, add = S.normalize_tables()
+        exp = O.resample(arena, t, 80, 80, T.FP32, T.NCHW, mul, add)
+        diff = np.abs(res - exp)
+        assert diff.max() <= 6.5 / 57.0 and diff.mean() < 0.02, (diff.max(), diff.mean())
+        assert pipe.timing_info()["decode_time"] > 0
+        pipe.rocal_release()
+
+
 def test_upload_modes(cuda):
     """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
     copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
@@ -349,8 +420,8 @@ def test_error_convention(cuda):
     assert ctx
     assert not C.create(4, types.CPU, 0, 1, 2, types.FLOAT)            # no CPU backend
     assert not C.create(4, types.GPU, 999, 1, 2, types.FLOAT)          # no such device
-    assert not C.external_source(ctx, types.RGB, 0, 100, 100, types.EXTSOURCE_FNAME)    # decode is out of scope
-    assert b"RAW_UNCOMPRESSED" in C.get_error_message(ctx)
+    assert not C.external_source(ctx, types.RGB, 0, 100, 100, 7)                        # no such mode
+    assert b"external source mode" in C.get_error_message(ctx)
     assert C.get_status(ctx) == types.RUNTIME_ERROR
     src = C.external_source(ctx, types.RGB, 0, 100, 100, types.EXTSOURCE_RAW_UNCOMPRESSED)
     assert src
