@@ -102,6 +102,21 @@ RB200_API int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t are
  * files by name (read at feed time; the FNAME mode of rocalExternalSourceFeedInput). */
 RB200_API int rb200_feed_encoded(rb200_context ctx, const unsigned char* const* buffers, const size_t* sizes, size_t n);
 RB200_API int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n);
+
+/* rocalJpegFileSourceSingleShard + rocalCreateLabelReader (rocal_api_data_loaders.h:80-90,
+ * rocal_api_meta_data.h:43): a folder of JPEG files (one sub-folder per class, numbered in sorted order; a
+ * flat folder is class 0), shard shard_id of shard_count, read and decoded by the context itself - rb200_run
+ * needs no feed call. last_batch_policy: 0 fill, 1 drop, 2 partial (rocal_api_types.h:455-495).
+ * rocalResetLoaders, rocalGetImageLabels, rocalGetImageNameLen / rocalGetImageName (concatenated names of the
+ * current batch, no separators), rocalGetLastBatchPaddedSize. */
+RB200_API rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
+                                              unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
+                                              unsigned max_height, int last_batch_policy, int pad_last_batch_repeated);
+RB200_API int rb200_reset_loaders(rb200_context ctx);
+RB200_API int rb200_get_image_labels(rb200_context ctx, int* labels);
+RB200_API unsigned rb200_get_image_name_len(rb200_context ctx, int* lengths);
+RB200_API int rb200_get_image_name(rb200_context ctx, char* buf);
+RB200_API size_t rb200_get_last_batch_padded_size(rb200_context ctx);
 /* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
  * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
 RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);

@@ -164,10 +164,11 @@ RB200_ROCAL RocalStatus ROCAL_API_CALL rocalUpdateIntRand(const int* values, con
 RB200_ROCAL RocalFloatParam ROCAL_API_CALL rocalCreateFloatRand(const float* values, const double* frequencies, unsigned size);
 RB200_ROCAL RocalStatus ROCAL_API_CALL rocalUpdateFloatRand(const float* values, const double* frequencies, unsigned size, RocalFloatParam updating_obj);
 
-/* ---- input: pre-decoded raw images (rocal_api_data_loaders.h:961-970, rocal_api_data_transfer.h:101-105).
- * Only external_source_mode == ROCAL_EXTSOURCE_RAW_UNCOMPRESSED is accepted (JPEG decode is not part
- * of this library); each fed buffer is a max_height x max_width x channels slot with the valid
- * roi.w x roi.h region at its origin (image_read_and_decode.cpp:217-244 of the reference). ---- */
+/* ---- input: the external source (rocal_api_data_loaders.h:961-970, rocal_api_data_transfer.h:101-105) in its
+ * three modes. ROCAL_EXTSOURCE_RAW_UNCOMPRESSED: each fed buffer is a max_height x max_width x channels slot with
+ * the valid roi.w x roi.h region at its origin (image_read_and_decode.cpp:217-244 of the reference).
+ * ROCAL_EXTSOURCE_RAW_COMPRESSED: each buffer is a JPEG stream whose length is roi.h. ROCAL_EXTSOURCE_FNAME: the
+ * names in input_images_names are JPEG files. JPEG input is decoded on the GPU (nvJPEG). ---- */
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegExternalFileSource(
     RocalContext p_context, RocalImageColor rocal_color_format, bool is_output = false, bool shuffle = false,
     bool loop = false, RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE,
@@ -178,6 +179,30 @@ RB200_ROCAL RocalStatus ROCAL_API_CALL rocalExternalSourceFeedInput(
     RocalContext p_context, const std::vector<std::string>& input_images_names, bool is_labels,
     const std::vector<unsigned char*>& input_buffer, const std::vector<ROIxywh>& roi_xywh, unsigned int max_width,
     unsigned int max_height, unsigned int channels, RocalExternalSourceMode mode, RocalTensorLayout layout, bool eos);
+
+/* ---- input: JPEG files in a folder tree (rocal_api_data_loaders.h:51-90) with the folder label reader
+ * (rocal_api_meta_data.h:43,153-171) and the loader controls (rocal_api_data_loaders.h: rocalResetLoaders;
+ * rocal_api_info.h: rocalGetLastBatchPaddedSize). internal_shard_count must be 1: one context drives one GPU.
+ * max_width / max_height bound the decoded size and must be given. ---- */
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegFileSource(
+    RocalContext context, const char* source_path, RocalImageColor rocal_color_format, unsigned internal_shard_count,
+    bool is_output, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
+    unsigned max_height = 0, RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG,
+    RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegFileSourceSingleShard(
+    RocalContext context, const char* source_path, RocalImageColor rocal_color_format, unsigned shard_id,
+    unsigned shard_count, bool is_output, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
+    unsigned max_height = 0, RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG,
+    RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext rocal_context, const char* source_path,
+                                                              const char* file_list_path = "");
+RB200_ROCAL void ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context, int* buf);
+RB200_ROCAL unsigned ROCAL_API_CALL rocalGetImageNameLen(RocalContext rocal_context, int* buf);
+RB200_ROCAL void ROCAL_API_CALL rocalGetImageName(RocalContext rocal_context, char* buf);
+RB200_ROCAL void ROCAL_API_CALL rocalResetLoaders(RocalContext context);
+RB200_ROCAL size_t ROCAL_API_CALL rocalGetLastBatchPaddedSize(RocalContext rocal_context);
 
 /* ---- augmentations (rocal_api_augmentation.h; line of each reference declaration in brackets) ---- */
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalResize /* [67] */ (
@@ -313,6 +338,5 @@ RB200_ROCAL size_t ROCAL_API_CALL rocalGetAugmentationBranchCount(RocalContext r
 RB200_ROCAL RocalStatus ROCAL_API_CALL rocalGetStatus(RocalContext rocal_context);
 RB200_ROCAL const char* ROCAL_API_CALL rocalGetErrorMessage(RocalContext rocal_context);
 RB200_ROCAL TimingInfo ROCAL_API_CALL rocalGetTimingInfo(RocalContext rocal_context);
-RB200_ROCAL size_t ROCAL_API_CALL rocalGetLastBatchPaddedSize(RocalContext rocal_context);
 
 #endif /* ROCAL_B200_ROCAL_API_H */

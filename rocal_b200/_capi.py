@@ -41,6 +41,12 @@ get_error_message = _proto("rb200_get_error_message", c_char_p, _P)
 get_timing = _proto("rb200_get_timing", None, _P, POINTER(ctypes.c_ulonglong))
 feed_encoded = _proto("rb200_feed_encoded", c_int, _P, POINTER(c_void_p), POINTER(c_size_t), c_size_t)
 feed_files = _proto("rb200_feed_files", c_int, _P, POINTER(ctypes.c_char_p), c_size_t)
+jpeg_file_source = _proto("rb200_jpeg_file_source", _P, _P, c_char_p, c_int, c_uint, c_uint, c_int, c_int, c_int, c_uint, c_uint, c_int, c_int)
+reset_loaders = _proto("rb200_reset_loaders", c_int, _P)
+get_image_labels = _proto("rb200_get_image_labels", c_int, _P, POINTER(c_int))
+get_image_name_len = _proto("rb200_get_image_name_len", c_uint, _P, POINTER(c_int))
+get_image_name = _proto("rb200_get_image_name", c_int, _P, c_char_p)
+get_last_batch_padded_size = _proto("rb200_get_last_batch_padded_size", c_size_t, _P)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)
 set_upload_mode = _proto("rb200_set_upload_mode", ctypes.c_int, _P, ctypes.c_int)
 get_remaining_images = _proto("rb200_get_remaining_images", c_size_t, _P)

@@ -1,10 +1,28 @@
 #include "pipeline.h"
 
+#include <cstdio>
+
 #include <chrono>
 #include <cmath>
 #include <cstring>
 
 namespace rb200 {
+
+static void read_file(const std::string& path, std::vector<unsigned char>& out) {
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) throw std::runtime_error("cannot open " + path);
+    std::fseek(f, 0, SEEK_END);
+    long len = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    if (len <= 0) {
+        std::fclose(f);
+        throw std::runtime_error("empty file " + path);
+    }
+    out.resize((size_t)len);
+    size_t got = std::fread(out.data(), 1, (size_t)len, f);
+    std::fclose(f);
+    if (got != (size_t)len) throw std::runtime_error("short read on " + path);
+}
 
 static inline unsigned long long now_us() {
     return (unsigned long long)std::chrono::duration_cast<std::chrono::microseconds>(
@@ -238,6 +256,63 @@ TensorImpl* Pipeline::add_source(unsigned max_w, unsigned max_h, bool is_output)
     return _tensors.back().get();
 }
 
+// rocalJpegFileSourceSingleShard (rocal_api_data_loaders.h:80-90): the source tensor plus a folder reader that
+// feeds the pipeline by itself.
+TensorImpl* Pipeline::add_file_source(const std::string& root, unsigned shard_id, unsigned shard_count, bool shuffle, bool loop,
+                                      unsigned max_w, unsigned max_h, bool is_output, int last_batch_policy,
+                                      bool pad_last_batch_repeated) {
+    if (max_w == 0 || max_h == 0) RB200_THROW("max_width and max_height must be given (ROCAL_USE_USER_GIVEN_SIZE): they bound the decoded size");
+    std::unique_ptr<FileSource> fs(new FileSource(root, _batch, shard_id, shard_count, shuffle, loop, last_batch_policy,
+                                                  pad_last_batch_repeated, ParameterFactory::instance().get_seed()));
+    TensorImpl* t = add_source(max_w, max_h, is_output);
+    _files = std::move(fs);
+    return t;
+}
+
+// Keeps the ring busy from the folder reader: one batch per free slot.
+void Pipeline::top_up() {
+    if (!_files) return;
+    for (;;) {
+        {
+            std::lock_guard<std::mutex> lk(_m);
+            if (_in_flight >= _depth) return;
+        }
+        FileBatch fb;
+        if (!_files->next(fb)) return;
+        InputBatch b;
+        b.kind = InputBatch::ENCODED;
+        b.n = _batch;
+        b.paths = std::move(fb.paths);
+        b.names = std::move(fb.names);
+        b.file_labels = std::move(fb.labels);
+        b.padded = fb.padded;
+        feed(std::move(b));
+    }
+}
+
+void Pipeline::reset_loaders() {
+    if (!_files) RB200_THROW("rocalResetLoaders: the context has no file source");
+    _files->reset();
+    top_up();
+}
+
+void Pipeline::image_labels(int* buf) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    const Slot& s = _slots[_held];
+    if (s.file_labels.size() != _batch) RB200_THROW("the current batch carries no labels (no file source / label reader)");
+    std::memcpy(buf, s.file_labels.data(), _batch * sizeof(int));
+}
+
+const std::vector<std::string>& Pipeline::image_names() {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    return _slots[_held].names;
+}
+
+size_t Pipeline::last_batch_padded_size() {
+    if (_held < 0) return 0;
+    return _slots[_held].padded;
+}
+
 TensorImpl* Pipeline::add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
                                RocalTensorOutputType dt, bool is_output) {
     if (_verified) RB200_THROW("the graph is already verified");
@@ -465,6 +540,7 @@ void Pipeline::verify() {
     }
     _verified = true;
     _worker = std::thread(&Pipeline::worker_loop, this);
+    top_up();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -511,8 +587,9 @@ void Pipeline::feed(InputBatch&& b) {
                 RB200_THROW("input ROI of sample " + std::to_string(i) + " is empty or exceeds max_width x max_height");
         }
     } else if (b.kind == InputBatch::ENCODED) {
-        for (size_t i = 0; i < b.n; i++)
-            if (!b.bufs[i] || b.enc_sizes[i] == 0) RB200_THROW("encoded image " + std::to_string(i) + " is empty");
+        if (b.paths.empty())
+            for (size_t i = 0; i < b.n; i++)
+                if (!b.bufs[i] || b.enc_sizes[i] == 0) RB200_THROW("encoded image " + std::to_string(i) + " is empty");
     } else {
         if (!b.arena) RB200_THROW("null input arena");
         for (size_t i = 0; i < b.n; i++) {
@@ -542,7 +619,9 @@ void Pipeline::feed(InputBatch&& b) {
 
 size_t Pipeline::remaining() {
     std::lock_guard<std::mutex> lk(_m);
-    return _in_flight * _batch;
+    size_t r = _in_flight * _batch;
+    if (_files) r += _files->batches_left() * _batch;
+    return r;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -952,6 +1031,16 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         if (!host_input) _src_base = (const uint8_t*)b.arena;
     } else if (b.kind == InputBatch::ENCODED) {
         // JPEG streams: sizes from the headers, then one batched decode into the packed arena (below)
+        if (!b.paths.empty()) {
+            b.enc_owned.resize(n);
+            b.bufs.resize(n);
+            b.enc_sizes.resize(n);
+            for (size_t i = 0; i < n; i++) {
+                read_file(b.paths[i], b.enc_owned[i]);
+                b.bufs[i] = b.enc_owned[i].data();
+                b.enc_sizes[i] = b.enc_owned[i].size();
+            }
+        }
         _jpeg.init();
         size_t total = 0;
         for (size_t i = 0; i < n; i++) {
@@ -1016,6 +1105,9 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     s.boxes = b.boxes;
     s.labels = b.labels;
     s.counts = b.counts;
+    s.file_labels = b.file_labels;
+    s.names = b.names;
+    s.padded = b.padded;
     update_nodes(b, s);
 
     auto view_of = [&](int tensor_id, size_t i, const uint8_t*& base) -> SampleView {
@@ -1286,13 +1378,24 @@ void Pipeline::run() {
     if (!_verified) RB200_THROW("rocalVerify must be called before rocalRun");
     size_t idx;
     {
+        // the previous batch goes back first, so that the folder reader can refill its slot
+        std::lock_guard<std::mutex> lk(_m);
+        if (_held >= 0) {
+            _slots[_held].state = Slot::FREE;
+            _held = -1;
+            _cv_work.notify_all();
+        }
+    }
+    top_up();
+    {
         std::unique_lock<std::mutex> lk(_m);
         if (_held >= 0) {
             _slots[_held].state = Slot::FREE;
             _held = -1;
             _cv_work.notify_all();
         }
-        if (_in_flight == 0) RB200_THROW("rocalRun: no input batch has been fed");
+        if (_in_flight == 0) RB200_THROW(_files ? "rocalRun: the file source is exhausted (rocalResetLoaders starts the next epoch)"
+                                                : "rocalRun: no input batch has been fed");
         _cv_ready.wait(lk, [&] { return _stop || _slots[_read].state == Slot::READY; });
         if (_stop) RB200_THROW("the context is shutting down");
         idx = _read;

@@ -23,6 +23,7 @@
 #include <thread>
 #include <vector>
 
+#include "file_source.h"
 #include "jpeg_decoder.h"
 #include "params.h"
 #include "rb200.h"
@@ -164,6 +165,10 @@ struct InputBatch {
     std::vector<rb200_image_desc> descs;
     std::vector<size_t> enc_sizes;                          // ENCODED: byte length of bufs[i]
     std::vector<std::vector<unsigned char>> enc_owned;      // ENCODED from file names: the bytes read at feed time
+    std::vector<std::string> paths;                         // ENCODED from the file source: read by the worker
+    std::vector<std::string> names;                         // file names reported by rocalGetImageName
+    std::vector<int> file_labels;                           // class labels of the file source
+    size_t padded = 0;                                      // samples at the end that pad the last batch
     bool has_boxes = false;
     std::vector<float> boxes;                 // ltrb, normalized
     std::vector<int> labels, counts;
@@ -191,6 +196,9 @@ struct Slot {
     int* d_matches = nullptr;         // box IoU matcher output [n][anchors]
     std::vector<float> boxes;        // metadata after the graph (normalized ltrb)
     std::vector<int> labels, counts;
+    std::vector<int> file_labels;    // file source: class label per sample
+    std::vector<std::string> names;  // file source: file name per sample
+    size_t padded = 0;
     size_t n = 0;
     std::string error;
 };
@@ -202,6 +210,12 @@ class Pipeline {
 
     // ---- graph building (user thread, before verify) ----
     TensorImpl* add_source(unsigned max_w, unsigned max_h, bool is_output);
+    TensorImpl* add_file_source(const std::string& root, unsigned shard_id, unsigned shard_count, bool shuffle, bool loop,
+                                unsigned max_w, unsigned max_h, bool is_output, int last_batch_policy, bool pad_last_batch_repeated);
+    void reset_loaders();
+    void image_labels(int* buf);
+    const std::vector<std::string>& image_names();
+    size_t last_batch_padded_size();
     TensorImpl* add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
                          RocalTensorOutputType dt, bool is_output);
     void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
@@ -249,6 +263,7 @@ class Pipeline {
 
    private:
     void worker_loop();
+    void top_up();
     void process(InputBatch& b, Slot& s, int slot_idx);
     void update_nodes(const InputBatch& b, Slot& s);
     void ensure_arena(int which, size_t bytes);
@@ -297,6 +312,9 @@ class Pipeline {
 
     // staging for extensions (attached to the next fed batch)
     InputBatch _staged;
+
+    // folder reader (rocalJpegFileSource): batches are fed by the pipeline itself
+    std::unique_ptr<FileSource> _files;
 
     // JPEG front-end (created when the first encoded batch arrives)
     JpegDecoder _jpeg;

@@ -327,26 +327,9 @@ int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n) {
         InputBatch b;
         b.kind = InputBatch::ENCODED;
         b.n = n;
-        b.enc_owned.resize(n);
-        b.bufs.resize(n);
-        b.enc_sizes.resize(n);
         for (size_t i = 0; i < n; i++) {
             if (!paths[i]) RB200_THROW("null file name");
-            FILE* f = std::fopen(paths[i], "rb");
-            if (!f) RB200_THROW(std::string("cannot open ") + paths[i]);
-            std::fseek(f, 0, SEEK_END);
-            long len = std::ftell(f);
-            std::fseek(f, 0, SEEK_SET);
-            if (len <= 0) {
-                std::fclose(f);
-                RB200_THROW(std::string("empty file ") + paths[i]);
-            }
-            b.enc_owned[i].resize((size_t)len);
-            size_t got = std::fread(b.enc_owned[i].data(), 1, (size_t)len, f);
-            std::fclose(f);
-            if (got != (size_t)len) RB200_THROW(std::string("short read on ") + paths[i]);
-            b.bufs[i] = b.enc_owned[i].data();
-            b.enc_sizes[i] = (size_t)len;
+            b.paths.emplace_back(paths[i]);
         }
         P(ctx)->feed(std::move(b));
     } catch (const std::exception& e) {
@@ -355,6 +338,79 @@ int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n) {
     }
     return ROCAL_OK;
 }
+
+rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
+                                    unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
+                                    unsigned max_height, int last_batch_policy, int pad_last_batch_repeated) {
+    CTX_OR(nullptr);
+    try {
+        if (!source_path) RB200_THROW("null source path");
+        if (color_format != ROCAL_COLOR_RGB24) RB200_THROW("the file source decodes to ROCAL_COLOR_RGB24 only");
+        return static_cast<rocalTensor*>(P(ctx)->add_file_source(source_path, shard_id, shard_count, shuffle != 0, loop != 0, max_width,
+                                                                 max_height, is_output != 0, last_batch_policy,
+                                                                 pad_last_batch_repeated != 0));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return nullptr;
+    }
+}
+
+int rb200_reset_loaders(rb200_context ctx) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->reset_loaders();
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_image_labels(rb200_context ctx, int* labels) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!labels) RB200_THROW("null output buffer");
+        P(ctx)->image_labels(labels);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+unsigned rb200_get_image_name_len(rb200_context ctx, int* lengths) {
+    if (!ctx) return 0;
+    try {
+        unsigned total = 0;
+        const auto& names = P(ctx)->image_names();
+        for (size_t i = 0; i < names.size(); i++) {
+            if (lengths) lengths[i] = (int)names[i].size();
+            total += (unsigned)names[i].size();
+        }
+        return total;
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return 0;
+    }
+}
+
+int rb200_get_image_name(rb200_context ctx, char* buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buf) RB200_THROW("null output buffer");
+        size_t pos = 0;
+        for (const auto& nm : P(ctx)->image_names()) {
+            std::memcpy(buf + pos, nm.data(), nm.size());
+            pos += nm.size();
+        }
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+size_t rb200_get_last_batch_padded_size(rb200_context ctx) { return ctx ? P(ctx)->last_batch_padded_size() : 0; }
 
 int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes, const rb200_image_desc* descs, size_t n,
                       int mem_kind) {

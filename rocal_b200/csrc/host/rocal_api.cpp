@@ -54,6 +54,40 @@ RocalTensor ROCAL_API_CALL rocalJpegExternalFileSource(RocalContext ctx, RocalIm
     return static_cast<RocalTensor>(rb200_external_source(ctx, (int)color, is_output, max_width, max_height, (int)mode));
 }
 
+RocalTensor ROCAL_API_CALL rocalJpegFileSourceSingleShard(RocalContext ctx, const char* source_path, RocalImageColor color,
+                                                          unsigned shard_id, unsigned shard_count, bool is_output, bool shuffle,
+                                                          bool loop, RocalImageSizeEvaluationPolicy, unsigned max_width,
+                                                          unsigned max_height, RocalDecoderType, RocalShardingInfo si) {
+    return static_cast<RocalTensor>(rb200_jpeg_file_source(ctx, source_path, (int)color, shard_id, shard_count, is_output, shuffle, loop,
+                                                           max_width, max_height, (int)si.last_batch_policy, si.pad_last_batch_repeated));
+}
+RocalTensor ROCAL_API_CALL rocalJpegFileSource(RocalContext ctx, const char* source_path, RocalImageColor color,
+                                               unsigned internal_shard_count, bool is_output, bool shuffle, bool loop,
+                                               RocalImageSizeEvaluationPolicy p, unsigned max_width, unsigned max_height,
+                                               RocalDecoderType d, RocalShardingInfo si) {
+    if (internal_shard_count != 1) {
+        if (ctx) P(ctx)->capture_error("rocalJpegFileSource: internal_shard_count must be 1 (one context drives one GPU; use rocalJpegFileSourceSingleShard per rank)");
+        return nullptr;
+    }
+    return rocalJpegFileSourceSingleShard(ctx, source_path, color, 0, 1, is_output, shuffle, loop, p, max_width, max_height, d, si);
+}
+// The folder reader numbers the classes itself; the label reader call only has to name the same folder
+// (the reference keys labels by file name, label_reader_folders.cpp:95-137).
+RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext ctx, const char* source_path, const char* file_list_path) {
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    if (file_list_path && file_list_path[0]) P(ctx)->capture_error("rocalCreateLabelReader: file lists are not supported");
+    (void)source_path;
+    return nullptr;
+}
+void ROCAL_API_CALL rocalGetImageLabels(RocalContext ctx, int* buf) { rb200_get_image_labels(ctx, buf); }
+unsigned ROCAL_API_CALL rocalGetImageNameLen(RocalContext ctx, int* buf) { return rb200_get_image_name_len(ctx, buf); }
+void ROCAL_API_CALL rocalGetImageName(RocalContext ctx, char* buf) { rb200_get_image_name(ctx, buf); }
+void ROCAL_API_CALL rocalResetLoaders(RocalContext ctx) { rb200_reset_loaders(ctx); }
+size_t ROCAL_API_CALL rocalGetLastBatchPaddedSize(RocalContext ctx) { return rb200_get_last_batch_padded_size(ctx); }
+
 RocalStatus ROCAL_API_CALL rocalExternalSourceFeedInput(RocalContext ctx, const std::vector<std::string>& input_images_names, bool,
                                                         const std::vector<unsigned char*>& input_buffer,
                                                         const std::vector<ROIxywh>& roi_xywh, unsigned int max_width,
@@ -301,6 +335,5 @@ TimingInfo ROCAL_API_CALL rocalGetTimingInfo(RocalContext c) {
     if (c) t = P(c)->timing();
     return t;
 }
-size_t ROCAL_API_CALL rocalGetLastBatchPaddedSize(RocalContext) { return 0; }
 
 }  // extern "C"

@@ -3,7 +3,9 @@
 import ctypes
 
 from . import _capi as C
+from . import decoders  # noqa: F401  (fn.decoders.image)
 from . import random  # noqa: F401  (fn.random.coin_flip)
+from . import readers  # noqa: F401  (fn.readers.file)
 from . import types
 from .pipeline import Pipeline, RocalError
 

@@ -264,6 +264,31 @@ class Pipeline(object):
         self.copy_encoded_boxes_and_lables(boxes, labels)
         return boxes, labels
 
+    def get_image_labels(self):
+        """rocalGetImageLabels: class label of every sample of the current batch (file source), int32 numpy array."""
+        out = np.empty(self._batch_size, dtype=np.int32)
+        self._check(C.get_image_labels(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        return out
+
+    def get_image_names(self):
+        """rocalGetImageNameLen + rocalGetImageName: file names of the current batch."""
+        lens = (ctypes.c_int * self._batch_size)()
+        total = C.get_image_name_len(self._handle, lens)
+        buf = ctypes.create_string_buffer(total + 1)
+        self._check(C.get_image_name(self._handle, buf))
+        raw, names, pos = buf.raw[:total], [], 0
+        for k in lens:
+            names.append(raw[pos:pos + k].decode())
+            pos += k
+        return names
+
+    def reset(self):
+        """rocalResetLoaders: the file source starts its next epoch."""
+        self._check(C.reset_loaders(self._handle))
+
+    def get_last_batch_padded_size(self):
+        return int(C.get_last_batch_padded_size(self._handle))
+
     def get_matched_indices(self):
         """rocalGetMatchedIndices: matched box index per anchor, [N, A] int32 (numpy)."""
         mp, na = ctypes.c_void_p(), ctypes.c_size_t()

@@ -32,4 +32,22 @@ class ROCALGenericIterator(object):
     next = __next__
 
 
-ROCALClassificationIterator = ROCALGenericIterator
+class ROCALClassificationIterator(ROCALGenericIterator):
+    """Yields ([outputs...], labels) for a pipeline with a file source (plugin/pytorch.py:246-294 of the reference):
+    labels are an int32 CUDA tensor of the batch's class indices. Iteration stops when the source is exhausted;
+    reset() starts the next epoch."""
+
+    def __next__(self):
+        if self.loader.is_empty():
+            raise StopIteration
+        self.loader.rocal_run()
+        outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
+        if self.copy:
+            outs = [o.clone() for o in outs]
+        labels = torch.from_numpy(self.loader.get_image_labels()).to(outs[0].device)
+        return outs, labels
+
+    next = __next__
+
+    def reset(self):
+        self.loader.reset()

@@ -1,0 +1,72 @@
+"""The folder reader behind rocalJpegFileSource (rocal_b200/csrc/host/file_source.cpp), compiled into a small
+harness: class numbering, extension filter, shard ranges, last-batch policies, seeded shuffle, looping."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HOST = os.path.join(ROOT, "rocal_b200", "csrc", "host")
+
+
+@pytest.fixture(scope="module")
+def harness(tmp_path_factory):
+    d = tmp_path_factory.mktemp("fs")
+    exe = str(d / "harness")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", HOST, os.path.join(ROOT, "tests", "harness", "file_source_harness.cpp"),
+                    os.path.join(HOST, "file_source.cpp"), "-o", exe], check=True)
+    data = d / "data"
+    for cls, count in (("cat", 3), ("dog", 4), ("emu", 2)):
+        (data / cls).mkdir(parents=True)
+        for i in range(count):
+            (data / cls / ("%s%d.jpg" % (cls, i))).write_bytes(b"x")
+    (data / "cat" / "readme.txt").write_text("not an image")
+    (data / "dog" / "DOG9.JPEG").write_bytes(b"x")          # upper-case extension counts; sorts before the lower-case names
+    flat = d / "flat"
+    flat.mkdir()
+    for i in range(3):
+        (flat / ("f%d.jpeg" % i)).write_bytes(b"x")
+
+    def run(root, batch, shard_id, shard_count, shuffle=0, loop_batches=0, policy=0, pad_repeat=0):
+        out = subprocess.run([exe, str(root), str(batch), str(shard_id), str(shard_count), str(shuffle), str(loop_batches),
+                              str(policy), str(pad_repeat)], capture_output=True, text=True).stdout.strip().splitlines()
+        return out[0], [ln.split("|")[0].split() for ln in out[1:]], [int(ln.split("pad")[1]) for ln in out[1:]]
+    return run, data, flat, d
+
+
+def test_classes_order_and_fill(harness):
+    run, data, flat, _ = harness
+    head, batches, pads = run(data, 4, 0, 1)
+    assert head == "N=10 shard=10 per=3"
+    flat_list = [x for b in batches for x in b]
+    assert flat_list[:10] == ["cat0.jpg:0", "cat1.jpg:0", "cat2.jpg:0", "DOG9.JPEG:1", "dog0.jpg:1", "dog1.jpg:1", "dog2.jpg:1",
+                              "dog3.jpg:1", "emu0.jpg:2", "emu1.jpg:2"]
+    assert flat_list[10:] == ["cat0.jpg:0", "cat1.jpg:0"] and pads == [0, 0, 2]       # FILL wraps to the shard's start
+    _, batches, pads = run(data, 4, 0, 1, pad_repeat=1)
+    assert batches[-1][2:] == ["emu1.jpg:2", "emu1.jpg:2"] and pads[-1] == 2            # ... or repeats the last sample
+    head, batches, _ = run(flat, 2, 0, 1)
+    assert head == "N=3 shard=3 per=2" and all(x.endswith(":0") for b in batches for x in b)
+
+
+def test_shards_and_drop(harness):
+    run, data, _, _ = harness
+    seen = []
+    for shard in range(3):
+        head, batches, pads = run(data, 2, shard, 3, policy=1)
+        n = int(head.split("shard=")[1].split()[0])
+        assert n == 10 * (shard + 1) // 3 - 10 * shard // 3
+        assert len(batches) == n // 2 and all(p == 0 for p in pads)                     # DROP: whole batches only
+        seen += [x for b in batches for x in b]
+    assert len(set(seen)) == len(seen)                                                   # shards do not overlap
+    assert run(data, 2, 3, 3)[0].startswith("ERROR")
+
+
+def test_shuffle_and_loop(harness):
+    run, data, _, _ = harness
+    _, a, _ = run(data, 5, 0, 1, shuffle=1)
+    _, b, _ = run(data, 5, 0, 1, shuffle=1)
+    assert a == b                                                                        # seeded
+    assert sorted(x for bt in a for x in bt) == sorted(x for bt in run(data, 5, 0, 1)[1] for x in bt)
+    assert [x for bt in a for x in bt] != [x for bt in run(data, 5, 0, 1)[1] for x in bt]
+    _, looped, _ = run(data, 5, 0, 1, shuffle=1, loop_batches=4)
+    assert len(looped) == 4 and looped[:2] == a and looped[2:] != a                      # the next epoch is reshuffled

@@ -184,6 +184,63 @@ def test_jpeg_external_source(cuda, tmp_path):
         pipe.rocal_release()
 
 
+def test_file_source_pipeline(cuda, tmp_path):
+    """A folder of JPEG files through fn.readers.file + fn.decoders.image (rocalJpegFileSourceSingleShard with the
+    folder label reader): the pipeline feeds itself; labels, names, batch count and last-batch padding follow the
+    folder; a second epoch after reset(); the images match the oracle on the host-decoded pixels as closely as the
+    two JPEG decoders agree."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    from rocal_b200.plugin.pytorch import ROCALClassificationIterator
+    rng = S.rng_for(24)
+    imgs, streams = _jpeg_batch(rng, 7, (120, 300))
+    classes = ["apple", "apple", "apple", "berry", "berry", "cherry", "cherry"]
+    by_name = {}
+    for i, (cls, sb) in enumerate(zip(classes, streams)):
+        d = tmp_path / cls
+        d.mkdir(exist_ok=True)
+        (d / ("im%d.jpg" % i)).write_bytes(sb)
+        by_name["im%d.jpg" % i] = (imgs[i], sorted(set(classes)).index(cls))
+    n = 3
+    pipe = Pipeline(batch_size=n, device_id=0, seed=4)
+    with pipe:
+        jpegs, _ = fn.readers.file(file_root=str(tmp_path))
+        img = fn.decoders.image(jpegs, file_root=str(tmp_path), shard_id=0, num_shards=1, max_decoded_width=300, max_decoded_height=300,
+                                last_batch_policy=types.LAST_BATCH_FILL, pad_last_batch=True)
+        r = fn.resize(img, resize_shorter=96)
+        out = fn.crop_mirror_normalize(r, crop=[80, 80], crop_pos_x=0.5, crop_pos_y=0.5, mean=MEAN, std=STD, mirror=0,
+                                       output_layout=types.NCHW, output_dtype=types.FLOAT)
+        pipe.set_outputs(out)
+    pipe.build()
+    assert pipe.get_remaining_images() == 9          # 7 files padded to 3 batches of 3
+    mul, add = S.normalize_tables()
+    for epoch in range(2):
+        seen = []
+        for k, (outs, labels) in enumerate(ROCALClassificationIterator(pipe)):
+            names = pipe.get_image_names()
+            assert labels.is_cuda and labels.cpu().tolist() == [by_name[nm][1] for nm in names]
+            res = outs[0].cpu().numpy()
+            for i, nm in enumerate(names):
+                im = by_name[nm][0]
+                h, w = im.shape[:2]
+                t = np.zeros(1, dtype=T.RESAMPLE_SAMPLE)
+                dw, dh = O.resize_dst_size(w, h, 96, 96, 2, cap_w=576, cap_h=576)
+                x1, y1, cw, ch = O.crop_fixed(dw, dh, 80, 80, 0.5, 0.5)
+                t["src_stride"], t["roi_w"], t["roi_h"], t["dst_w"], t["dst_h"] = w * 3, w, h, dw, dh
+                t["crop_x"], t["crop_y"], t["crop_w"], t["crop_h"] = x1, y1, cw, ch
+                exp = O.resample(im.reshape(-1), t, 80, 80, T.FP32, T.NCHW, mul, add)[0]
+                diff = np.abs(res[i] - exp)
+                assert diff.max() <= 6.5 / 57.0 and diff.mean() < 0.02, (nm, diff.max(), diff.mean())
+            seen += names
+            assert pipe.get_last_batch_padded_size() == (2 if k == 2 else 0)
+        assert seen == ["im0.jpg", "im1.jpg", "im2.jpg", "im3.jpg", "im4.jpg", "im5.jpg", "im6.jpg", "im6.jpg", "im6.jpg"]
+        assert pipe.is_empty()
+        with pytest.raises(Exception):
+            pipe.rocal_run()
+        pipe.reset()
+    pipe.rocal_release()
+
+
 def test_upload_modes(cuda):
     """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
     copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
