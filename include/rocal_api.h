@@ -323,6 +323,12 @@ RB200_ROCAL void ROCAL_API_CALL rocalBoxEncoder(RocalContext p_context, std::vec
 RB200_ROCAL void ROCAL_API_CALL rocalCopyEncodedBoxesAndLables(RocalContext p_context, float* boxes_buf, int* labels_buf);
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalGetEncodedBoxesAndLables(RocalContext p_context, int num_encoded_boxes);
 
+/* ---- boxes of the current batch after the graph's crops and mirrors (rocal_api_meta_data.h:173-211): total
+ * count, and one host tensor per sample - [count][4] float32 normalized ltrb, [count] int32 labels ---- */
+RB200_ROCAL unsigned ROCAL_API_CALL rocalGetBoundingBoxCount(RocalContext rocal_context);
+RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxCords(RocalContext rocal_context);
+RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxLabel(RocalContext rocal_context);
+
 /* ---- box IoU matcher (rocal_api_meta_data.h:302-318) ---- */
 RB200_ROCAL void ROCAL_API_CALL rocalBoxIouMatcher(RocalContext p_context, std::vector<float>& anchors, float high_threshold,
                                                    float low_threshold, bool allow_low_quality_matches = true);

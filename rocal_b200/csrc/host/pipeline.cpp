@@ -149,7 +149,22 @@ std::vector<size_t> TensorImpl::strides() {
 }
 
 unsigned TensorImpl::copy_data(void* user_buffer, RocalOutputMemType external_mem_type) {
-    if (!current || !user_buffer) return 1;
+    if (!user_buffer) return 1;
+    if (host_mem) {
+        if (data_size() == 0) return 0;
+        if (!current) return 1;
+        try {
+            if (external_mem_type == ROCAL_MEMCPY_GPU)
+                pipe->sync_copy(user_buffer, current, data_size(), cudaMemcpyHostToDevice);
+            else
+                std::memcpy(user_buffer, current, data_size());
+        } catch (const std::exception& e) {
+            pipe->capture_error(e.what());
+            return 1;
+        }
+        return 0;
+    }
+    if (!current) return 1;
     try {
         pipe->sync_copy(user_buffer, current, data_size(),
                         external_mem_type == ROCAL_MEMCPY_GPU ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost);
@@ -1419,6 +1434,52 @@ void Pipeline::run() {
         _enc_labels_t->current = s.d_enc_labels;
     }
     if (_box_matcher) _matches_t->current = s.d_matches;
+    refresh_box_views();
+}
+
+// Per-sample host tensors over the boxes of the held batch: [count_i][4] float32 ltrb and [count_i] int32
+// (MasterGraph::bbox_meta_data / labels_meta_data, master_graph.cpp).
+void Pipeline::refresh_box_views() {
+    _bbox_t.clear();
+    _bbox_label_t.clear();
+    _bbox_list.items.clear();
+    _bbox_label_list.items.clear();
+    if (_held < 0) return;
+    Slot& s = _slots[_held];
+    if (s.counts.size() != _batch) return;
+    size_t at = 0;
+    for (size_t i = 0; i < _batch; i++) {
+        const size_t c = (size_t)s.counts[i];
+        std::unique_ptr<TensorImpl> b(new TensorImpl(this, -10, 1, 4, (int)c, ROCAL_FP32, ROCAL_NHWC, false, false));
+        b->custom_dims = {c, 4};
+        b->host_mem = true;
+        b->current = c ? (void*)(s.boxes.data() + at * 4) : nullptr;
+        std::unique_ptr<TensorImpl> l(new TensorImpl(this, -11, 1, 1, (int)c, ROCAL_INT32, ROCAL_NHWC, false, false));
+        l->custom_dims = {c};
+        l->host_mem = true;
+        l->current = c ? (void*)(s.labels.data() + at) : nullptr;
+        _bbox_list.items.push_back(b.get());
+        _bbox_label_list.items.push_back(l.get());
+        _bbox_t.push_back(std::move(b));
+        _bbox_label_t.push_back(std::move(l));
+        at += c;
+    }
+}
+
+unsigned Pipeline::bounding_box_count() {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    if (_slots[_held].counts.size() != _batch) RB200_THROW("No label has been loaded for this output image");
+    return (unsigned)_slots[_held].labels.size();
+}
+
+TensorListImpl* Pipeline::bounding_box_cords() {
+    if (_held < 0 || _bbox_list.items.empty()) return nullptr;
+    return &_bbox_list;
+}
+
+TensorListImpl* Pipeline::bounding_box_labels() {
+    if (_held < 0 || _bbox_label_list.items.empty()) return nullptr;
+    return &_bbox_label_list;
 }
 
 TensorListImpl* Pipeline::matched_indices() {

@@ -89,9 +89,9 @@ class TensorImpl : public rocalTensor {
     std::vector<size_t> dims() override;
     std::vector<size_t> strides() override;
     RocalTensorLayout layout() override { return lay; }
-    RocalTensorBackend backend() override { return ROCAL_GPU; }
+    RocalTensorBackend backend() override { return host_mem ? ROCAL_CPU : ROCAL_GPU; }
     RocalTensorOutputType data_type() override { return dtype; }
-    RocalOutputMemType mem_type() override { return ROCAL_MEMCPY_GPU; }
+    RocalOutputMemType mem_type() override { return host_mem ? ROCAL_MEMCPY_HOST : ROCAL_MEMCPY_GPU; }
     size_t data_size() override {
         if (!custom_dims.empty()) {
             size_t e = elem_size();
@@ -116,6 +116,7 @@ class TensorImpl : public rocalTensor {
         }
     }
     std::vector<size_t> custom_dims;     // non-image tensors (encoded boxes / labels)
+    bool host_mem = false;               // metadata tensors (boxes, labels of the batch) live in host memory
 
     Pipeline* pipe;
     int id, n, max_w, max_h;
@@ -244,6 +245,10 @@ class Pipeline {
     void encoded(float** boxes, int** labels, size_t* num_anchors);
     void copy_encoded(float* boxes, int* labels);
     TensorListImpl* matched_indices();
+    // rocalGetBoundingBoxCount / Cords / Label: per-sample host tensors over the held slot's boxes
+    unsigned bounding_box_count();
+    TensorListImpl* bounding_box_cords();
+    TensorListImpl* bounding_box_labels();
     void matches(int** dev, size_t* num_anchors);
     void current_boxes(std::vector<float>& ltrb, std::vector<int>& labels, std::vector<int>& counts);
     void crop_windows(TensorImpl* t, unsigned* xywh);
@@ -301,6 +306,11 @@ class Pipeline {
     std::unique_ptr<TensorImpl> _enc_boxes_t, _enc_labels_t;   // views handed out by rocalGetEncodedBoxesAndLables
     TensorListImpl _enc_list_boxes, _enc_list_labels;
     MetaListImpl _enc_meta;
+
+    // per-sample views of the current batch's boxes (rebuilt by rocalRun)
+    std::vector<std::unique_ptr<TensorImpl>> _bbox_t, _bbox_label_t;
+    TensorListImpl _bbox_list, _bbox_label_list;
+    void refresh_box_views();
 
     // box IoU matcher
     bool _box_matcher = false;

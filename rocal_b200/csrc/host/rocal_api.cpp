@@ -296,6 +296,33 @@ RocalMetaData ROCAL_API_CALL rocalGetEncodedBoxesAndLables(RocalContext c, int n
     return P(c)->encoded_meta();
 }
 
+unsigned ROCAL_API_CALL rocalGetBoundingBoxCount(RocalContext c) {
+    if (!c) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return 0;
+    }
+    try {
+        return P(c)->bounding_box_count();
+    } catch (const std::exception& e) {
+        P(c)->capture_error(e.what());
+        return 0;
+    }
+}
+RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxCords(RocalContext c) {
+    if (!c) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    return P(c)->bounding_box_cords();
+}
+RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxLabel(RocalContext c) {
+    if (!c) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    return P(c)->bounding_box_labels();
+}
+
 void ROCAL_API_CALL rocalBoxIouMatcher(RocalContext c, std::vector<float>& anchors, float high_threshold, float low_threshold,
                                        bool allow_low_quality_matches) {
     if (!c) {

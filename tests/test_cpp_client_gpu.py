@@ -1,0 +1,91 @@
+"""A C++ program written against include/rocal_api.h with the reference's call sequence
+(tests/harness/rocal_cpp_client.cpp) is compiled with g++, linked with librocal_b200.so and run on the GPU;
+what it wrote is checked against the oracle. This is the drop-in boundary exercised from real C++ code:
+std::vector arguments, default arguments, rocalTensor virtual calls, the slot feed contract, metadata getters."""
+import os
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import pyoracle as O
+from rocal_b200 import synthetic as S
+from rocal_b200 import tables as T
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_cpp_client(cuda, tmp_path):
+    lib_dir = os.path.join(ROOT, "rocal_b200")
+    exe = str(tmp_path / "client")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "harness", "rocal_cpp_client.cpp"), "-L", lib_dir, "-lrocal_b200",
+                    "-Wl,-rpath," + lib_dir, "-o", exe], check=True)
+    rng = S.rng_for(25)
+    n = 6
+    arena, hs, ws, offs = S.make_images(rng, n, (300, 520), (300, 520))
+    boxes, labels, boffs = S.random_boxes(rng, n, (1, 12))
+    anchors = S.ssd300_anchors()
+    counts = np.diff(boffs).astype(np.int32)
+    with open(tmp_path / "in.bin", "wb") as f:
+        f.write(struct.pack("<i", n))
+        for i in range(n):
+            f.write(struct.pack("<ii", int(hs[i]), int(ws[i])))
+        for i in range(n):
+            f.write(arena[int(offs[i]):int(offs[i]) + int(hs[i]) * int(ws[i]) * 3].tobytes())
+        f.write(struct.pack("<i", len(labels)))
+        f.write(counts.tobytes())
+        f.write(np.ascontiguousarray(boxes, dtype=np.float32).tobytes())
+        f.write(np.ascontiguousarray(labels, dtype=np.int32).tobytes())
+        f.write(struct.pack("<i", len(anchors)))
+        f.write(np.ascontiguousarray(anchors, dtype=np.float32).tobytes())
+    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-2000:]
+    raw = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
+    pos = 0
+
+    def take(dtype, count):
+        nonlocal pos
+        a = raw[pos:pos + count * np.dtype(dtype).itemsize].view(dtype)
+        pos += count * np.dtype(dtype).itemsize
+        return a
+
+    mul, add = S.normalize_tables()
+    # graph 1
+    got1 = take(np.float32, n * 3 * 224 * 224).reshape(n, 3, 224, 224)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    for i in range(n):
+        dw, dh = O.resize_dst_size(int(ws[i]), int(hs[i]), 256, 256, 2, cap_w=1536, cap_h=1536)
+        x1, y1, cw, ch = O.crop_fixed(dw, dh, 224, 224, 0.5, 0.5)
+        t[i]["src_offset"], t[i]["src_stride"] = offs[i], ws[i] * 3
+        t[i]["roi_w"], t[i]["roi_h"], t[i]["dst_w"], t[i]["dst_h"] = ws[i], hs[i], dw, dh
+        t[i]["crop_x"], t[i]["crop_y"], t[i]["crop_w"], t[i]["crop_h"] = x1, y1, cw, ch
+    assert np.array_equal(got1, O.resample(arena, t, 224, 224, T.FP32, T.NCHW, mul, add))
+    # graph 2
+    got2 = take(np.float32, n * 3 * 300 * 300).reshape(n, 3, 300, 300)
+    win = take(np.uint32, n * 4).reshape(n, 4).astype(np.int64)
+    t2 = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t2["src_offset"], t2["src_stride"] = offs, ws * 3
+    t2["roi_x"], t2["roi_y"], t2["roi_w"], t2["roi_h"] = win[:, 0], win[:, 1], win[:, 2], win[:, 3]
+    t2["dst_w"], t2["dst_h"], t2["crop_w"], t2["crop_h"] = 300, 300, 300, 300
+    assert np.array_equal(got2, O.resample(arena, t2, 300, 300, T.FP32, T.NCHW, mul, add))
+    total = int(take(np.int32, 1)[0])
+    b2, l2, c2 = [], [], []
+    for i in range(n):
+        c = int(take(np.int32, 1)[0])
+        b2.append(take(np.float32, c * 4).reshape(c, 4))
+        l2.append(take(np.int32, c))
+        c2.append(c)
+    assert sum(c2) == total and min(c2) >= 1
+    b2, l2 = np.concatenate(b2), np.concatenate(l2)
+    assert b2.min() >= 0.0 and b2.max() <= 1.0
+    o2 = np.concatenate([[0], np.cumsum(c2)]).astype(np.int32)
+    eb, el = O.box_encode(b2, l2, o2, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
+    gb = take(np.float32, n * len(anchors) * 4).reshape(n, len(anchors), 4)
+    gl = take(np.int32, n * len(anchors)).reshape(n, len(anchors))
+    assert pos == len(raw)
+    assert np.array_equal(gl, el)
+    assert np.allclose(gb, eb, rtol=1e-5, atol=1e-6)
