@@ -117,6 +117,10 @@ RB200_API int rb200_get_image_labels(rb200_context ctx, int* labels);
 RB200_API unsigned rb200_get_image_name_len(rb200_context ctx, int* lengths);
 RB200_API int rb200_get_image_name(rb200_context ctx, char* buf);
 RB200_API size_t rb200_get_last_batch_padded_size(rb200_context ctx);
+/* rocalGetOneHotImageLabels (label k > 0 sets position k-1, label 0 the last position; int32 [batch][num_classes],
+ * output_mem_type 0 = host, 1 = device) and rocalGetImageSizes (width, height of every source image). */
+RB200_API int rb200_get_one_hot_image_labels(rb200_context ctx, void* buf, int num_classes, int output_mem_type);
+RB200_API int rb200_get_image_sizes(rb200_context ctx, int* width_height_pairs);
 /* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
  * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
 RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);

@@ -199,6 +199,9 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegFileSourceSingleShard(
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext rocal_context, const char* source_path,
                                                               const char* file_list_path = "");
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context, int* buf);
+RB200_ROCAL void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext rocal_context, void* buf, int numOfClasses,
+                                                         RocalOutputMemType output_mem_type);
+RB200_ROCAL void ROCAL_API_CALL rocalGetImageSizes(RocalContext rocal_context, int* buf);
 RB200_ROCAL unsigned ROCAL_API_CALL rocalGetImageNameLen(RocalContext rocal_context, int* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageName(RocalContext rocal_context, char* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalResetLoaders(RocalContext context);

@@ -46,6 +46,8 @@ reset_loaders = _proto("rb200_reset_loaders", c_int, _P)
 get_image_labels = _proto("rb200_get_image_labels", c_int, _P, POINTER(c_int))
 get_image_name_len = _proto("rb200_get_image_name_len", c_uint, _P, POINTER(c_int))
 get_image_name = _proto("rb200_get_image_name", c_int, _P, c_char_p)
+get_one_hot_image_labels = _proto("rb200_get_one_hot_image_labels", c_int, _P, c_void_p, c_int, c_int)
+get_image_sizes = _proto("rb200_get_image_sizes", c_int, _P, POINTER(c_int))
 get_last_batch_padded_size = _proto("rb200_get_last_batch_padded_size", c_size_t, _P)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)
 set_upload_mode = _proto("rb200_set_upload_mode", ctypes.c_int, _P, ctypes.c_int)

@@ -323,6 +323,15 @@ const std::vector<std::string>& Pipeline::image_names() {
     return _slots[_held].names;
 }
 
+void Pipeline::source_sizes(int* wh) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    const auto& r = _slots[_held].rois[_source];
+    for (size_t i = 0; i < _batch; i++) {
+        wh[i * 2] = (int)r[i * 4 + 2];
+        wh[i * 2 + 1] = (int)r[i * 4 + 3];
+    }
+}
+
 size_t Pipeline::last_batch_padded_size() {
     if (_held < 0) return 0;
     return _slots[_held].padded;

@@ -217,6 +217,7 @@ class Pipeline {
     void image_labels(int* buf);
     const std::vector<std::string>& image_names();
     size_t last_batch_padded_size();
+    void source_sizes(int* wh);
     TensorImpl* add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
                          RocalTensorOutputType dt, bool is_output);
     void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,

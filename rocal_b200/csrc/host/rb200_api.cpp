@@ -410,6 +410,45 @@ int rb200_get_image_name(rb200_context ctx, char* buf) {
     return ROCAL_OK;
 }
 
+// rocalGetOneHotImageLabels (source/api/rocal_api_meta_data.cpp:229-266): label k > 0 sets position k-1, label 0
+// sets the last position, anything else leaves the row at zero.
+int rb200_get_one_hot_image_labels(rb200_context ctx, void* buf, int num_classes, int output_mem_type) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buf || num_classes <= 0) RB200_THROW("null buffer or non-positive class count");
+        const size_t n = (size_t)P(ctx)->batch();
+        std::vector<int> labels(n);
+        P(ctx)->image_labels(labels.data());
+        std::vector<int> hot(n * (size_t)num_classes, 0);
+        for (size_t i = 0; i < n; i++) {
+            const int k = labels[i];
+            if (k > 0 && k <= num_classes) hot[i * num_classes + k - 1] = 1;
+            else if (k == 0) hot[i * num_classes + num_classes - 1] = 1;
+        }
+        if (output_mem_type == ROCAL_MEMCPY_HOST)
+            std::memcpy(buf, hot.data(), hot.size() * sizeof(int));
+        else
+            P(ctx)->sync_copy(buf, hot.data(), hot.size() * sizeof(int), cudaMemcpyHostToDevice);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+// rocalGetImageSizes (rocal_api_meta_data.cpp:335-349): width, height of every source image of the batch.
+int rb200_get_image_sizes(rb200_context ctx, int* buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buf) RB200_THROW("null output buffer");
+        P(ctx)->source_sizes(buf);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
 size_t rb200_get_last_batch_padded_size(rb200_context ctx) { return ctx ? P(ctx)->last_batch_padded_size() : 0; }
 
 int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes, const rb200_image_desc* descs, size_t n,

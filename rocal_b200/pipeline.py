@@ -270,6 +270,23 @@ class Pipeline(object):
         self._check(C.get_image_labels(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
         return out
 
+    def get_one_hot_encoded_labels(self, num_classes, device=None):
+        """rocalGetOneHotImageLabels: int32 [N, num_classes]; a numpy array, or a CUDA torch tensor when device is given."""
+        if device is None:
+            out = np.zeros((self._batch_size, num_classes), dtype=np.int32)
+            self._check(C.get_one_hot_image_labels(self._handle, ctypes.c_void_p(out.ctypes.data), num_classes, types.HOST_MEMORY))
+            return out
+        import torch
+        out = torch.zeros((self._batch_size, num_classes), dtype=torch.int32, device=device)
+        self._check(C.get_one_hot_image_labels(self._handle, ctypes.c_void_p(out.data_ptr()), num_classes, types.DEVICE_MEMORY))
+        return out
+
+    def get_image_sizes(self):
+        """rocalGetImageSizes: (width, height) of every source image of the batch, int32 [N, 2]."""
+        out = np.zeros((self._batch_size, 2), dtype=np.int32)
+        self._check(C.get_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        return out
+
     def get_image_names(self):
         """rocalGetImageNameLen + rocalGetImageName: file names of the current batch."""
         lens = (ctypes.c_int * self._batch_size)()

@@ -219,6 +219,12 @@ def test_file_source_pipeline(cuda, tmp_path):
         for k, (outs, labels) in enumerate(ROCALClassificationIterator(pipe)):
             names = pipe.get_image_names()
             assert labels.is_cuda and labels.cpu().tolist() == [by_name[nm][1] for nm in names]
+            hot = pipe.get_one_hot_encoded_labels(3)
+            for i, nm in enumerate(names):      # rocalGetOneHotImageLabels: label k > 0 -> position k-1, label 0 -> last
+                lab = by_name[nm][1]
+                assert hot[i].tolist() == [1 if p == (lab - 1 if lab > 0 else 2) else 0 for p in range(3)]
+            assert np.array_equal(hot, pipe.get_one_hot_encoded_labels(3, device="cuda:0").cpu().numpy())
+            assert pipe.get_image_sizes().tolist() == [[by_name[nm][0].shape[1], by_name[nm][0].shape[0]] for nm in names]
             res = outs[0].cpu().numpy()
             for i, nm in enumerate(names):
                 im = by_name[nm][0]
