@@ -21,6 +21,10 @@ from . import _capi as C
 from . import types
 
 
+_IMAGE_DESC = np.dtype({"names": ["offset", "stride", "width", "height"], "formats": [np.uint64, np.uint32, np.uint32, np.uint32],
+                        "offsets": [0, 8, 12, 16], "itemsize": ctypes.sizeof(C.ImageDesc)})
+
+
 class RocalError(RuntimeError):
     pass
 
@@ -175,12 +179,13 @@ class Pipeline(object):
     def feed_ragged(self, arena, heights, widths, offsets, strides=None, mem_kind=None):
         """[extension] One packed arena (numpy array, torch tensor — host, pinned or CUDA) + per-image sizes."""
         n = len(heights)
-        descs = (C.ImageDesc * n)()
-        for i in range(n):
-            descs[i].offset = int(offsets[i])
-            descs[i].stride = int(strides[i]) if strides is not None else int(widths[i]) * 3
-            descs[i].width = int(widths[i])
-            descs[i].height = int(heights[i])
+        # rb200_image_desc rows built in one go (a per-image Python loop costs ~1 us per image)
+        d = np.zeros(n, dtype=_IMAGE_DESC)
+        d["offset"] = offsets
+        d["width"] = widths
+        d["height"] = heights
+        d["stride"] = strides if strides is not None else np.asarray(widths, dtype=np.int64) * 3
+        descs = d.ctypes.data_as(ctypes.POINTER(C.ImageDesc))
         if isinstance(arena, np.ndarray):
             ptr, nbytes, kind = arena.ctypes.data, arena.nbytes, C.MEM_HOST
         else:   # torch tensor
@@ -188,7 +193,7 @@ class Pipeline(object):
             kind = C.MEM_DEVICE if arena.is_cuda else (C.MEM_HOST_PINNED if arena.is_pinned() else C.MEM_HOST)
         if mem_kind is not None:
             kind = mem_kind
-        self._keepalive.append((arena, descs))
+        self._keepalive.append((arena, d))
         self._check(C.feed_ragged(self._handle, ctypes.c_void_p(ptr), nbytes, descs, n, kind))
 
     def feed_encoded(self, streams):
