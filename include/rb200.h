@@ -112,6 +112,14 @@ RB200_API int rb200_feed_files(rb200_context ctx, const char* const* paths, size
 RB200_API rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
                                               unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
                                               unsigned max_height, int last_batch_policy, int pad_last_batch_repeated);
+/* rocalJpegCOCOFileSourceSingleShard + rocalCreateCOCOReader (rocal_api_data_loaders.h:257-269,
+ * rocal_api_meta_data.h:89): images named in a COCO annotation file, looked up under source_path, with their boxes
+ * (bbox [x,y,w,h] -> normalized ltrb) and labels (categories renumbered 1.. in file order unless
+ * avoid_class_remapping); the boxes follow the graph's crops and mirrors and feed the box encoder / matcher. */
+RB200_API rb200_tensor rb200_coco_file_source(rb200_context ctx, const char* source_path, const char* json_path, int color_format,
+                                              unsigned shard_id, unsigned shard_count, int is_output, int shuffle, int loop,
+                                              unsigned max_width, unsigned max_height, int last_batch_policy,
+                                              int pad_last_batch_repeated, int avoid_class_remapping);
 RB200_API int rb200_reset_loaders(rb200_context ctx);
 RB200_API int rb200_get_image_labels(rb200_context ctx, int* labels);
 RB200_API unsigned rb200_get_image_name_len(rb200_context ctx, int* lengths);

@@ -196,6 +196,22 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegFileSourceSingleShard(
     RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
     unsigned max_height = 0, RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG,
     RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+/* COCO detection datasets (rocal_api_meta_data.h:89, rocal_api_data_loaders.h:163-174,257-269): boxes and labels come
+ * from the annotation file and follow the graph's crops and mirrors. */
+RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateCOCOReader(RocalContext rocal_context, const char* source_path, bool is_output,
+                                                             bool mask = false, bool ltrb = true, bool is_box_encoder = false,
+                                                             bool avoid_class_remapping = false, bool aspect_ratio_grouping = false,
+                                                             bool is_box_iou_matcher = false);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSource(
+    RocalContext context, const char* source_path, const char* json_path, RocalImageColor color_format, unsigned internal_shard_count,
+    bool is_output, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0, unsigned max_height = 0,
+    RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourceSingleShard(
+    RocalContext context, const char* source_path, const char* json_path, RocalImageColor color_format, unsigned shard_id,
+    unsigned shard_count, bool is_output, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0, unsigned max_height = 0,
+    RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext rocal_context, const char* source_path,
                                                               const char* file_list_path = "");
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context, int* buf);

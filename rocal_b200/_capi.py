@@ -42,6 +42,7 @@ get_timing = _proto("rb200_get_timing", None, _P, POINTER(ctypes.c_ulonglong))
 feed_encoded = _proto("rb200_feed_encoded", c_int, _P, POINTER(c_void_p), POINTER(c_size_t), c_size_t)
 feed_files = _proto("rb200_feed_files", c_int, _P, POINTER(ctypes.c_char_p), c_size_t)
 jpeg_file_source = _proto("rb200_jpeg_file_source", _P, _P, c_char_p, c_int, c_uint, c_uint, c_int, c_int, c_int, c_uint, c_uint, c_int, c_int)
+coco_file_source = _proto("rb200_coco_file_source", _P, _P, c_char_p, c_char_p, c_int, c_uint, c_uint, c_int, c_int, c_int, c_uint, c_uint, c_int, c_int, c_int)
 reset_loaders = _proto("rb200_reset_loaders", c_int, _P)
 get_image_labels = _proto("rb200_get_image_labels", c_int, _P, POINTER(c_int))
 get_image_name_len = _proto("rb200_get_image_name_len", c_uint, _P, POINTER(c_int))

@@ -44,13 +44,39 @@ std::vector<std::string> sorted_entries(const std::string& dir) {
     return names;
 }
 
+FileEntry make_entry(const std::string& path, const std::string& name, int label) {
+    FileEntry e;
+    e.path = path;
+    e.name = name;
+    e.label = label;
+    return e;
+}
+
 }  // namespace
+
+FileSource::FileSource(std::vector<FileEntry> entries, bool with_boxes, size_t batch, unsigned shard_id, unsigned shard_count,
+                       bool shuffle, bool loop, int last_batch_policy, bool pad_last_batch_repeated, unsigned seed)
+    : _all(std::move(entries)), _with_boxes(with_boxes), _batch(batch), _shuffle(shuffle), _loop(loop), _policy(last_batch_policy),
+      _pad_repeat(pad_last_batch_repeated), _seed(seed) {
+    if (batch == 0) throw std::runtime_error("batch size must be positive");
+    if (_policy < FILL || _policy > PARTIAL) throw std::runtime_error("bad last batch policy");
+    if (_all.empty()) throw std::runtime_error("the dataset holds no image");
+    init_shard(shard_id, shard_count);
+}
+
+void FileSource::init_shard(unsigned shard_id, unsigned shard_count) {
+    if (shard_count == 0 || shard_id >= shard_count) throw std::runtime_error("shard_id must be smaller than shard_count");
+    const size_t N = _all.size();
+    _begin = N * shard_id / shard_count;
+    _end = N * (shard_id + 1) / shard_count;
+    if (_end == _begin) throw std::runtime_error("shard " + std::to_string(shard_id) + " of " + std::to_string(shard_count) + " is empty");
+    begin_epoch();
+}
 
 FileSource::FileSource(const std::string& root, size_t batch, unsigned shard_id, unsigned shard_count, bool shuffle, bool loop,
                        int last_batch_policy, bool pad_last_batch_repeated, unsigned seed)
     : _batch(batch), _shuffle(shuffle), _loop(loop), _policy(last_batch_policy), _pad_repeat(pad_last_batch_repeated), _seed(seed) {
     if (batch == 0) throw std::runtime_error("batch size must be positive");
-    if (shard_count == 0 || shard_id >= shard_count) throw std::runtime_error("shard_id must be smaller than shard_count");
     if (_policy < FILL || _policy > PARTIAL) throw std::runtime_error("bad last batch policy");
     int label = 0;
     bool flat_done = false;
@@ -60,22 +86,18 @@ FileSource::FileSource(const std::string& root, size_t batch, unsigned shard_id,
             if (!is_jpeg_name(n)) continue;
             if (!flat_done) {   // a root that holds files is one class; its files are taken once, sorted
                 for (const std::string& f : sorted_entries(root))
-                    if (is_file(root + "/" + f) && is_jpeg_name(f)) _all.push_back({root + "/" + f, f, 0});
+                    if (is_file(root + "/" + f) && is_jpeg_name(f)) _all.push_back(make_entry(root + "/" + f, f, 0));
                 flat_done = true;
             }
             break;              // "assume directory has only files" (label_reader_folders.cpp:127)
         } else if (is_dir(p)) {
             for (const std::string& f : sorted_entries(p))
-                if (is_file(p + "/" + f) && is_jpeg_name(f)) _all.push_back({p + "/" + f, f, label});
+                if (is_file(p + "/" + f) && is_jpeg_name(f)) _all.push_back(make_entry(p + "/" + f, f, label));
             label++;
         }
     }
     if (_all.empty()) throw std::runtime_error("no JPEG files found under " + root);
-    const size_t N = _all.size();
-    _begin = N * shard_id / shard_count;
-    _end = N * (shard_id + 1) / shard_count;
-    if (_end == _begin) throw std::runtime_error("shard " + std::to_string(shard_id) + " of " + std::to_string(shard_count) + " is empty");
-    begin_epoch();
+    init_shard(shard_id, shard_count);
 }
 
 void FileSource::begin_epoch() {
@@ -113,16 +135,25 @@ bool FileSource::next(FileBatch& out) {
     out.names.clear();
     out.labels.clear();
     out.padded = 0;
+    out.has_boxes = _with_boxes;
+    out.boxes.clear();
+    out.box_labels.clear();
+    out.counts.clear();
     for (size_t k = 0; k < _batch; k++) {
         size_t pos = first + k;
         if (pos >= n) {
             pos = _pad_repeat ? n - 1 : (pos - n) % n;
             out.padded++;
         }
-        const Entry& e = _all[_order[pos]];
+        const FileEntry& e = _all[_order[pos]];
         out.paths.push_back(e.path);
         out.names.push_back(e.name);
         out.labels.push_back(e.label);
+        if (_with_boxes) {
+            out.boxes.insert(out.boxes.end(), e.boxes.begin(), e.boxes.end());
+            out.box_labels.insert(out.box_labels.end(), e.box_labels.begin(), e.box_labels.end());
+            out.counts.push_back((int)e.box_labels.size());
+        }
     }
     _cursor++;
     _last_padded = out.padded;

@@ -26,6 +26,18 @@ struct FileBatch {
     std::vector<std::string> names;   // file name without the folder, as rocalGetImageName reports it
     std::vector<int> labels;
     size_t padded = 0;                // samples at the end of the batch that repeat earlier ones
+    // detection datasets: ground-truth boxes of the batch (normalized ltrb), their labels, boxes per sample
+    bool has_boxes = false;
+    std::vector<float> boxes;
+    std::vector<int> box_labels, counts;
+};
+
+// One sample of a dataset: the file, its class label (classification) and its boxes (detection).
+struct FileEntry {
+    std::string path, name;
+    int label = 0;
+    std::vector<float> boxes;
+    std::vector<int> box_labels;
 };
 
 class FileSource {
@@ -35,6 +47,9 @@ class FileSource {
     // Scans `root`; throws std::runtime_error when it cannot be read or holds no image.
     FileSource(const std::string& root, size_t batch, unsigned shard_id, unsigned shard_count, bool shuffle, bool loop,
                int last_batch_policy, bool pad_last_batch_repeated, unsigned seed);
+    // A prepared list (the COCO reader's images with their boxes), in the order given.
+    FileSource(std::vector<FileEntry> entries, bool with_boxes, size_t batch, unsigned shard_id, unsigned shard_count, bool shuffle,
+               bool loop, int last_batch_policy, bool pad_last_batch_repeated, unsigned seed);
 
     size_t dataset_size() const { return _all.size(); }
     size_t shard_size() const { return _end - _begin; }
@@ -46,13 +61,11 @@ class FileSource {
     size_t last_batch_padded_size() const { return _last_padded; }
 
    private:
-    struct Entry {
-        std::string path, name;
-        int label;
-    };
+    void init_shard(unsigned shard_id, unsigned shard_count);
     void begin_epoch();
 
-    std::vector<Entry> _all;
+    std::vector<FileEntry> _all;
+    bool _with_boxes = false;
     std::vector<size_t> _order;       // indices into _all for the current epoch, shard only
     size_t _begin = 0, _end = 0;
     size_t _batch;

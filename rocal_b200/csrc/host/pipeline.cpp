@@ -284,6 +284,33 @@ TensorImpl* Pipeline::add_file_source(const std::string& root, unsigned shard_id
     return t;
 }
 
+// rocalJpegCOCOFileSourceSingleShard + rocalCreateCOCOReader (rocal_api_data_loaders.h:257-269,
+// rocal_api_meta_data.h:89): the images named by the annotation file, found under `root`, with their boxes.
+TensorImpl* Pipeline::add_coco_source(const std::string& root, const std::string& json_path, bool avoid_class_remapping,
+                                      unsigned shard_id, unsigned shard_count, bool shuffle, bool loop, unsigned max_w, unsigned max_h,
+                                      bool is_output, int last_batch_policy, bool pad_last_batch_repeated) {
+    if (max_w == 0 || max_h == 0) RB200_THROW("max_width and max_height must be given (ROCAL_USE_USER_GIVEN_SIZE): they bound the decoded size");
+    std::vector<CocoImage> images = read_coco_annotations(json_path, avoid_class_remapping);
+    std::vector<FileEntry> entries;
+    for (CocoImage& im : images) {
+        FileEntry e;
+        e.path = root + "/" + im.file_name;
+        FILE* f = std::fopen(e.path.c_str(), "rb");     // images of the file that are not on disk are left out
+        if (!f) continue;
+        std::fclose(f);
+        e.name = im.file_name;
+        e.boxes = std::move(im.boxes);
+        e.box_labels = std::move(im.labels);
+        entries.push_back(std::move(e));
+    }
+    if (entries.empty()) RB200_THROW("none of the images named in " + json_path + " was found under " + root);
+    std::unique_ptr<FileSource> fs(new FileSource(std::move(entries), true, _batch, shard_id, shard_count, shuffle, loop, last_batch_policy,
+                                                  pad_last_batch_repeated, ParameterFactory::instance().get_seed()));
+    TensorImpl* t = add_source(max_w, max_h, is_output);
+    _files = std::move(fs);
+    return t;
+}
+
 // Keeps the ring busy from the folder reader: one batch per free slot.
 void Pipeline::top_up() {
     if (!_files) return;
@@ -301,6 +328,27 @@ void Pipeline::top_up() {
         b.names = std::move(fb.names);
         b.file_labels = std::move(fb.labels);
         b.padded = fb.padded;
+        if (fb.has_boxes) {
+            // an image without annotations keeps one empty box with label 0, as the reference's metadata graph
+            // does (bounding_box_graph.cpp:53-55)
+            std::vector<float> bx;
+            std::vector<int> bl, bc;
+            size_t at = 0;
+            for (size_t i = 0; i < fb.counts.size(); i++) {
+                const int c = fb.counts[i];
+                if (c == 0) {
+                    bx.insert(bx.end(), {0.f, 0.f, 0.f, 0.f});
+                    bl.push_back(0);
+                    bc.push_back(1);
+                } else {
+                    bx.insert(bx.end(), fb.boxes.begin() + at * 4, fb.boxes.begin() + (at + c) * 4);
+                    bl.insert(bl.end(), fb.box_labels.begin() + at, fb.box_labels.begin() + at + c);
+                    bc.push_back(c);
+                }
+                at += (size_t)c;
+            }
+            stage_boxes(bx.data(), bl.data(), bc.data(), bc.size());
+        }
         feed(std::move(b));
     }
 }

@@ -23,6 +23,7 @@
 #include <thread>
 #include <vector>
 
+#include "coco_reader.h"
 #include "file_source.h"
 #include "jpeg_decoder.h"
 #include "params.h"
@@ -213,6 +214,9 @@ class Pipeline {
     TensorImpl* add_source(unsigned max_w, unsigned max_h, bool is_output);
     TensorImpl* add_file_source(const std::string& root, unsigned shard_id, unsigned shard_count, bool shuffle, bool loop,
                                 unsigned max_w, unsigned max_h, bool is_output, int last_batch_policy, bool pad_last_batch_repeated);
+    TensorImpl* add_coco_source(const std::string& root, const std::string& json_path, bool avoid_class_remapping, unsigned shard_id,
+                                unsigned shard_count, bool shuffle, bool loop, unsigned max_w, unsigned max_h, bool is_output,
+                                int last_batch_policy, bool pad_last_batch_repeated);
     void reset_loaders();
     void image_labels(int* buf);
     const std::vector<std::string>& image_names();
@@ -324,6 +328,14 @@ class Pipeline {
     // staging for extensions (attached to the next fed batch)
     InputBatch _staged;
 
+    // rocalCreateCOCOReader only records its arguments; rocalJpegCOCOFileSource builds the reader
+    std::string _coco_json;
+    bool _coco_avoid_remap = false;
+   public:
+    void note_coco_reader(const std::string& json, bool avoid_remap) { _coco_json = json; _coco_avoid_remap = avoid_remap; }
+    const std::string& coco_json() const { return _coco_json; }
+    bool coco_avoid_remap() const { return _coco_avoid_remap; }
+   private:
     // folder reader (rocalJpegFileSource): batches are fed by the pipeline itself
     std::unique_ptr<FileSource> _files;
 

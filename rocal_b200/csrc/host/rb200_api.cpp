@@ -355,6 +355,22 @@ rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, 
     }
 }
 
+rb200_tensor rb200_coco_file_source(rb200_context ctx, const char* source_path, const char* json_path, int color_format,
+                                    unsigned shard_id, unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
+                                    unsigned max_height, int last_batch_policy, int pad_last_batch_repeated, int avoid_class_remapping) {
+    CTX_OR(nullptr);
+    try {
+        if (!source_path || !json_path) RB200_THROW("null source or annotation path");
+        if (color_format != ROCAL_COLOR_RGB24) RB200_THROW("the file source decodes to ROCAL_COLOR_RGB24 only");
+        return static_cast<rocalTensor*>(P(ctx)->add_coco_source(source_path, json_path, avoid_class_remapping != 0, shard_id, shard_count,
+                                                                 shuffle != 0, loop != 0, max_width, max_height, is_output != 0,
+                                                                 last_batch_policy, pad_last_batch_repeated != 0));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return nullptr;
+    }
+}
+
 int rb200_reset_loaders(rb200_context ctx) {
     CTX_OR(ROCAL_CONTEXT_INVALID);
     try {

@@ -82,6 +82,46 @@ RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext ctx, const char
     (void)source_path;
     return nullptr;
 }
+// rocalCreateCOCOReader records the annotation file; the source call that follows builds the reader. Masks,
+// aspect-ratio grouping and xywh output are not supported.
+RocalMetaData ROCAL_API_CALL rocalCreateCOCOReader(RocalContext ctx, const char* source_path, bool is_output, bool mask, bool ltrb,
+                                                   bool is_box_encoder, bool avoid_class_remapping, bool aspect_ratio_grouping,
+                                                   bool is_box_iou_matcher) {
+    (void)is_output; (void)is_box_encoder; (void)is_box_iou_matcher;
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    if (!source_path || mask || !ltrb || aspect_ratio_grouping) {
+        P(ctx)->capture_error("rocalCreateCOCOReader: needs an annotation path; masks, xywh boxes and aspect-ratio grouping are not supported");
+        return nullptr;
+    }
+    P(ctx)->note_coco_reader(source_path, avoid_class_remapping);
+    return nullptr;
+}
+RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourceSingleShard(RocalContext ctx, const char* source_path, const char* json_path,
+                                                              RocalImageColor color, unsigned shard_id, unsigned shard_count,
+                                                              bool is_output, bool shuffle, bool loop, RocalImageSizeEvaluationPolicy,
+                                                              unsigned max_width, unsigned max_height, RocalDecoderType, RocalShardingInfo si) {
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    const std::string json = (json_path && json_path[0]) ? std::string(json_path) : P(ctx)->coco_json();
+    return static_cast<RocalTensor>(rb200_coco_file_source(ctx, source_path, json.c_str(), (int)color, shard_id, shard_count, is_output, shuffle,
+                                                           loop, max_width, max_height, (int)si.last_batch_policy,
+                                                           si.pad_last_batch_repeated, P(ctx)->coco_avoid_remap()));
+}
+RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSource(RocalContext ctx, const char* source_path, const char* json_path, RocalImageColor color,
+                                                   unsigned internal_shard_count, bool is_output, bool shuffle, bool loop,
+                                                   RocalImageSizeEvaluationPolicy p, unsigned max_width, unsigned max_height,
+                                                   RocalDecoderType d, RocalShardingInfo si) {
+    if (internal_shard_count != 1) {
+        if (ctx) P(ctx)->capture_error("rocalJpegCOCOFileSource: internal_shard_count must be 1 (use the SingleShard call per rank)");
+        return nullptr;
+    }
+    return rocalJpegCOCOFileSourceSingleShard(ctx, source_path, json_path, color, 0, 1, is_output, shuffle, loop, p, max_width, max_height, d, si);
+}
 void ROCAL_API_CALL rocalGetImageLabels(RocalContext ctx, int* buf) { rb200_get_image_labels(ctx, buf); }
 void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext ctx, void* buf, int num_classes, RocalOutputMemType m) {
     rb200_get_one_hot_image_labels(ctx, buf, num_classes, (int)m);

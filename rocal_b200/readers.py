@@ -19,3 +19,18 @@ def file(file_root, file_filters=None, file_list='', stick_to_shard=False, pad_l
     p._reader = "labelReader"
     p._file_root = file_root
     return ("labelReader", file_root), []
+
+
+def coco(annotations_file='', ltrb=True, masks=False, ratio=False, avoid_class_remapping=False, pixelwise_masks=False,
+         is_box_encoder=False, is_box_iou_matcher=False, aspect_ratio_grouping=False, stick_to_shard=False, pad_last_batch=False):
+    """readers.py:30. Records the annotation file; decoders.image(file_root=...) creates the source. Boxes are handed on as
+    normalized ltrb (the reference's ratio=True); masks and aspect-ratio grouping are not supported."""
+    p = Pipeline._current_pipeline
+    if p is None:
+        raise RuntimeError("readers.coco must be called inside `with pipeline:`")
+    if masks or pixelwise_masks or aspect_ratio_grouping or not ltrb:
+        raise ValueError("masks, xywh boxes and aspect-ratio grouping are not supported")
+    p._reader = "COCOReader"
+    p._coco_json = annotations_file
+    p._coco_avoid_remap = bool(avoid_class_remapping)
+    return ("COCOReader", annotations_file), [], []

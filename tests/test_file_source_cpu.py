@@ -70,3 +70,45 @@ def test_shuffle_and_loop(harness):
     assert [x for bt in a for x in bt] != [x for bt in run(data, 5, 0, 1)[1] for x in bt]
     _, looped, _ = run(data, 5, 0, 1, shuffle=1, loop_batches=4)
     assert len(looped) == 4 and looped[:2] == a and looped[2:] != a                      # the next epoch is reshuffled
+
+
+def test_coco_annotation_reader(tmp_path):
+    """The COCO reader: categories renumbered in file order (or kept), bbox xywh -> normalized ltrb, annotations that
+    precede the images section, escaped strings, nested values it has to skip, crowd annotations kept, images without
+    annotations kept, unknown images dropped, output sorted by file name."""
+    import json
+    exe = str(tmp_path / "coco")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", HOST, os.path.join(ROOT, "tests", "harness", "coco_reader_harness.cpp"),
+                    os.path.join(HOST, "coco_reader.cpp"), "-o", exe], check=True)
+    doc = {
+        "info": {"description": "synthetic \"set\"", "nested": [1, [2, {"a": None}], True], "year": 2026},
+        "annotations": [
+            {"id": 1, "image_id": 20, "category_id": 18, "bbox": [10.0, 20.0, 30.0, 40.0], "iscrowd": 0, "segmentation": [[1, 2, 3, 4]]},
+            {"id": 2, "image_id": 10, "category_id": 3, "bbox": [0, 0, 50, 25], "iscrowd": 1, "area": 1250.5},
+            {"id": 3, "image_id": 20, "category_id": 3, "bbox": [5.5, 6.5, 7.0, 8.0], "iscrowd": 0},
+            {"id": 4, "image_id": 99, "category_id": 3, "bbox": [1, 1, 1, 1]},
+        ],
+        "categories": [{"id": 3, "name": "car", "supercategory": "vehicle"}, {"id": 18, "name": "dog"}],
+        "images": [
+            {"id": 20, "file_name": "b_img.jpg", "width": 200, "height": 100, "license": 1},
+            {"id": 10, "file_name": "a_img.jpg", "height": 50, "width": 100},
+            {"id": 30, "file_name": "c_empty.jpg", "width": 64, "height": 64},
+        ],
+    }
+    path = tmp_path / "ann.json"
+    path.write_text(json.dumps(doc, indent=1))
+
+    def run(avoid):
+        out = subprocess.run([exe, str(path), str(avoid)], capture_output=True, text=True).stdout.strip().splitlines()
+        return [ln.split(" | ") for ln in out]
+
+    rows = run(0)
+    assert [r[0] for r in rows] == ["a_img.jpg 100 50 1", "b_img.jpg 200 100 2", "c_empty.jpg 64 64 0"]
+    assert rows[0][1] == "1 0.000000 0.000000 0.500000 0.500000"                 # category 3 -> class 1
+    assert rows[1][1] == "2 0.050000 0.200000 0.200000 0.600000"                 # category 18 -> class 2
+    assert rows[1][2] == "1 0.027500 0.065000 0.062500 0.145000"
+    rows = run(1)
+    assert rows[0][1].startswith("3 ") and rows[1][1].startswith("18 ")
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"images": [ {"id": 1, "file_name": "x.jpg" ')
+    assert subprocess.run([exe, str(bad), "0"], capture_output=True, text=True).stdout.startswith("ERROR")

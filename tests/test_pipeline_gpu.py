@@ -247,6 +247,66 @@ def test_file_source_pipeline(cuda, tmp_path):
     pipe.rocal_release()
 
 
+def test_coco_source_pipeline(cuda, tmp_path):
+    """A COCO-format detection dataset through fn.readers.coco + fn.decoders.image: the boxes of the annotation file
+    follow the images through the flip, reach the box encoder and come back through the bounding-box getters."""
+    import json
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(26)
+    n = 4
+    imgs, streams = _jpeg_batch(rng, n, (150, 320))
+    images, anns, truth = [], [], {}
+    for i, (im, sb) in enumerate(zip(imgs, streams)):
+        name = "%03d.jpg" % i
+        (tmp_path / name).write_bytes(sb)
+        h, w = im.shape[:2]
+        images.append({"id": 100 + i, "file_name": name, "width": w, "height": h})
+        k = int(rng.integers(1, 6)) if i != 2 else 0          # one image without annotations
+        bx = []
+        for _ in range(k):
+            x, y = float(rng.uniform(0, w * 0.6)), float(rng.uniform(0, h * 0.6))
+            bw, bh = float(rng.uniform(w * 0.1, w * 0.4)), float(rng.uniform(h * 0.1, h * 0.4))
+            cat = int(rng.choice([7, 21, 44]))
+            anns.append({"id": len(anns), "image_id": 100 + i, "category_id": cat, "bbox": [x, y, bw, bh], "iscrowd": 0})
+            bx.append(([x / w, y / h, (x + bw) / w, (y + bh) / h], {7: 1, 21: 2, 44: 3}[cat]))
+        truth[name] = bx
+    (tmp_path / "ann.json").write_text(json.dumps({"images": images, "annotations": anns,
+                                                    "categories": [{"id": 7}, {"id": 21}, {"id": 44}]}))
+    anchors = S.ssd300_anchors()[::4].copy()
+    pipe = Pipeline(batch_size=n, device_id=0, seed=6)
+    with pipe:
+        jpegs, _, _ = fn.readers.coco(annotations_file=str(tmp_path / "ann.json"), ltrb=True, is_box_encoder=True)
+        img = fn.decoders.image(jpegs, file_root=str(tmp_path), max_decoded_width=320, max_decoded_height=320)
+        r = fn.resize(img, resize_width=128, resize_height=128, scaling_mode=types.SCALING_MODE_STRETCH)
+        out = fn.crop_mirror_normalize(r, crop=[128, 128], crop_pos_x=0.0, crop_pos_y=0.0, mean=MEAN, std=STD, mirror=1,
+                                       output_layout=types.NCHW, output_dtype=types.FLOAT)
+        fn.box_encoder(anchors=anchors, criteria=0.5, means=[0, 0, 0, 0], stds=[0.1, 0.1, 0.2, 0.2], offset=True, scale=1.0)
+        pipe.set_outputs(out)
+    pipe.build()
+    pipe.run()
+    names = pipe.get_image_names()
+    assert names == ["000.jpg", "001.jpg", "002.jpg", "003.jpg"]
+    b2, l2, c2 = pipe.get_bounding_boxes()
+    at = 0
+    for nm, c in zip(names, c2):
+        exp = truth[nm]
+        if not exp:                                   # an image without annotations keeps one empty box, label 0
+            assert c == 1 and l2[at] == 0 and b2[at].tolist() == [1.0, 0.0, 1.0, 0.0]      # the empty box, mirrored
+        else:
+            assert c == len(exp)
+            for k, (box, lab) in enumerate(exp):
+                mirrored = [1.0 - box[2], box[1], 1.0 - box[0], box[3]]        # mirror = 1 flips the boxes with the image
+                assert l2[at + k] == lab and np.allclose(b2[at + k], mirrored, atol=1e-5), (nm, k)
+        at += c
+    o2 = np.concatenate([[0], np.cumsum(c2)]).astype(np.int32)
+    eb, el = O.box_encode(b2, l2, o2, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
+    gb, gl = pipe.get_encoded_boxes_and_lables()
+    assert np.array_equal(gl, el) and np.allclose(gb, eb, rtol=1e-5, atol=1e-6)
+    assert pipe.get_output_tensors()[0].numpy().shape == (n, 3, 128, 128)
+    pipe.rocal_release()
+
+
 def test_upload_modes(cuda):
     """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
     copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
