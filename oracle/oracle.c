@@ -509,12 +509,25 @@ ORC_API int orc_box_iou_match(const float* boxes, const int32_t* box_offsets, in
 /* Target size of one resized sample: ResizeNode::adjust_out_roi_size
  * (rocAL/source/augmentations/geometry_augmentations/node_resize.cpp:98-138) followed by the
  * clamp to the output tensor's maximum shape (:71-72). mode follows RocalResizeScalingMode
- * (0 default, 1 stretch, 2 not-smaller, 3 not-larger). */
+ * (0 default, 1 stretch, 2 not-smaller, 3 not-larger, 4 min-max: ResizeMirrorNormalize only). */
 ORC_API void orc_resize_dst_size(unsigned src_w, unsigned src_h, unsigned dst_w, unsigned dst_h, int mode,
                                  unsigned max_w, unsigned max_h, unsigned cap_w, unsigned cap_h,
                                  unsigned* out_w, unsigned* out_h) {
     int has_max = (max_w | max_h) > 0;
-    if (mode == 1) {
+    if (mode == 4) {
+        /* MIN_MAX (node_resize_mirror_normalize.cpp:138-160): max_w carries the minimum size, max_h the maximum size;
+         * the shorter side becomes min_size unless the longer one would then exceed max_size; integer division. */
+        unsigned min_size = max_w, max_size = max_h, size = min_size;
+        float min_o = (float)(src_w < src_h ? src_w : src_h), max_o = (float)(src_w > src_h ? src_w : src_h);
+        if (max_o / min_o * size > max_size) size = (unsigned)(size_t)roundf(max_size * min_o / max_o);
+        if (src_w < src_h) {
+            dst_w = size;
+            dst_h = (unsigned)((size_t)size * src_h / src_w);
+        } else {
+            dst_h = size;
+            dst_w = (unsigned)((size_t)size * src_w / src_h);
+        }
+    } else if (mode == 1) {
         if (!dst_w) dst_w = src_w;
         if (!dst_h) dst_h = src_h;
         if (has_max) {

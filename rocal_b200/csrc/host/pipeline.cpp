@@ -39,7 +39,20 @@ static inline unsigned long long now_us() {
 static void resize_target(unsigned src_w, unsigned src_h, unsigned dst_w, unsigned dst_h, int mode, unsigned max_w,
                           unsigned max_h, unsigned& out_w, unsigned& out_h) {
     bool has_max = (max_w | max_h) > 0;
-    if (mode == ROCAL_SCALING_MODE_STRETCH) {
+    if (mode == ROCAL_SCALING_MODE_MIN_MAX) {
+        // ResizeMirrorNormalizeNode::adjust_out_roi_size (node_resize_mirror_normalize.cpp:138-160): max_w holds the
+        // minimum size, max_h the maximum size.
+        unsigned min_size = max_w, max_size = max_h, size = min_size;
+        float min_o = static_cast<float>(std::min(src_w, src_h)), max_o = static_cast<float>(std::max(src_w, src_h));
+        if (max_o / min_o * size > max_size) size = static_cast<size_t>(std::round(max_size * min_o / max_o));
+        if (src_w < src_h) {
+            dst_w = size;
+            dst_h = static_cast<size_t>(size * src_h / src_w);
+        } else {
+            dst_h = size;
+            dst_w = static_cast<size_t>(size * src_w / src_h);
+        }
+    } else if (mode == ROCAL_SCALING_MODE_STRETCH) {
         if (!dst_w) dst_w = src_w;
         if (!dst_h) dst_h = src_h;
         if (has_max) {

@@ -54,19 +54,30 @@ void set_normalize(Node& nd, const float* mean, const float* std_dev, size_t n) 
     nd.normalize = true;
 }
 
-// Output shape rules of rocalResize (source/api/rocal_api_augmentation.cpp:449-506).
+// Output shape rules of rocalResize / rocalResizeMirrorNormalize (source/api/rocal_api_augmentation.cpp:449-506,
+// 550-621). allow_min_max: only ResizeMirrorNormalize knows ROCAL_SCALING_MODE_MIN_MAX, where resize_shorter and
+// resize_longer carry the minimum and maximum size and travel to the node in place of max_size.
 void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling_mode, unsigned max_w, unsigned max_h,
-                   unsigned resize_shorter, unsigned resize_longer, Node& nd, unsigned& out_max_w, unsigned& out_max_h) {
+                   unsigned resize_shorter, unsigned resize_longer, Node& nd, unsigned& out_max_w, unsigned& out_max_h,
+                   bool allow_min_max = false) {
     const unsigned kMaxAspectRatio = 6;   // MAX_ASPECT_RATIO, include/pipeline/commons.h:39
+    const bool min_max = scaling_mode == ROCAL_SCALING_MODE_MIN_MAX;
+    if (min_max && !allow_min_max) RB200_THROW("ROCAL_SCALING_MODE_MIN_MAX is a mode of rocalResizeMirrorNormalize only");
     if ((dest_w | dest_h | resize_longer | resize_shorter) == 0)
         RB200_THROW("Atleast one size 'dest_width' or 'dest_height' or 'resize_shorter' or 'resize_longer' must be specified");
-    if ((dest_w | dest_h) && (resize_longer | resize_shorter))
+    if ((dest_w | dest_h) && (resize_longer | resize_shorter) && !min_max)
         RB200_THROW("Only one method of specifying size can be used \ndest_width and/or dest_height\nresize_shorter\nresize_longer");
-    if (resize_longer && resize_shorter)
+    if (resize_longer && resize_shorter && !min_max)
         RB200_THROW("'resize_longer' and 'resize_shorter' cannot be passed together. They are mutually exclusive.");
+    if (min_max && (!resize_shorter || !resize_longer))
+        RB200_THROW("ROCAL_SCALING_MODE_MIN_MAX needs the minimum size in resize_shorter and the maximum size in resize_longer");
     unsigned out_w, out_h;
     int mode;
-    if (resize_shorter) {
+    if (min_max) {
+        mode = scaling_mode;
+        out_w = dest_w;
+        out_h = dest_h;
+    } else if (resize_shorter) {
         mode = ROCAL_SCALING_MODE_NOT_SMALLER;
         out_w = out_h = resize_shorter;
     } else if (resize_longer) {
@@ -77,7 +88,6 @@ void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling
         out_w = dest_w;
         out_h = dest_h;
     }
-    if (mode == ROCAL_SCALING_MODE_MIN_MAX) RB200_THROW("ROCAL_SCALING_MODE_MIN_MAX is not supported");
     if (max_w != 0 && max_h != 0) {
         out_max_w = max_w;
         out_max_h = max_h;
@@ -95,11 +105,15 @@ void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling
         if (max_w) out_max_w = max_w;
         if (max_h) out_max_h = max_h;
     }
+    if (min_max && (out_max_w == 0 || out_max_h == 0)) {
+        // neither dest sizes nor max_size were given: the longer side never exceeds the maximum size
+        out_max_w = out_max_h = resize_longer;
+    }
     nd.dest_w = out_w;
     nd.dest_h = out_h;
     nd.scaling_mode = mode;
-    nd.max_w = max_w;
-    nd.max_h = max_h;
+    nd.max_w = min_max ? resize_shorter : max_w;
+    nd.max_h = min_max ? resize_longer : max_h;
 }
 
 // Resize-type operators take the bilinear and the triangular filter.
@@ -560,7 +574,7 @@ rb200_tensor rb200_resize_mirror_normalize(rb200_context ctx, rb200_tensor in, u
     nd.interpolation = resize_interpolation(interpolation);
     nd.kind = NodeKind::RESIZE_MIRROR_NORMALIZE;
     unsigned mw, mh;
-    resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh);
+    resize_shapes(T(in), dest_width, dest_height, scaling_mode, max_w, max_h, resize_shorter, resize_longer, nd, mw, mh, true);
     set_normalize(nd, mean, std_dev, n_mean);
     nd.mirror = int_param(mirror, 0, 1);
     return finish(p, std::move(nd), T(in), mw, mh, out_layout, out_dtype, is_output);

@@ -101,6 +101,14 @@ def test_resize_size_rules():
         assert O.resize_dst_size(w, h, 256, 256, 2) == S.resize_not_smaller(w, h, 256)
 
 
+def test_min_max_resize_rule():
+    """ROCAL_SCALING_MODE_MIN_MAX of ResizeMirrorNormalize (node_resize_mirror_normalize.cpp:138-160), hand-computed."""
+    assert O.resize_dst_size(640, 480, 0, 0, 4, max_w=800, max_h=1333) == (1066, 800)
+    assert O.resize_dst_size(1000, 300, 0, 0, 4, max_w=800, max_h=1333) == (1333, 400)      # the longer side hits the maximum
+    assert O.resize_dst_size(300, 1000, 0, 0, 4, max_w=800, max_h=1333) == (400, 1333)
+    assert O.resize_dst_size(500, 500, 0, 0, 4, max_w=800, max_h=1333) == (800, 800)
+
+
 def test_crop_rules():
     # fixed-anchor crop (parameter_rocal_crop.cpp:51-61): centre, corners, crop larger than the image
     assert O.crop_fixed(256, 341, 224, 224, 0.5, 0.5) == (16, 58, 224, 224)

@@ -307,6 +307,43 @@ def test_coco_source_pipeline(cuda, tmp_path):
     pipe.rocal_release()
 
 
+def test_resize_mirror_normalize_min_max(cuda):
+    """rocalResizeMirrorNormalize with ROCAL_SCALING_MODE_MIN_MAX (the MaskRCNN resize): the shorter side becomes the
+    minimum size unless the longer one would pass the maximum size; one fused launch, ragged outputs with their ROI."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(27)
+    n = 8
+    pipe = Pipeline(batch_size=n, device_id=0, seed=8)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=400, max_height=400)
+        mirror = fn.random.coin_flip()
+        out = fn.resize_mirror_normalize(img, scaling_mode=types.SCALING_MODE_MIN_MAX, resize_shorter=64, resize_longer=96,
+                                         max_size=[96, 96], mean=MEAN, std=STD, mirror=mirror, output_layout=types.NHWC,
+                                         output_dtype=types.FLOAT)
+        pipe.set_outputs(out)
+    pipe.build()
+    arena, hs, ws, offs = S.make_images(rng, n, (80, 400), (80, 400))
+    hs[0], ws[0] = 90, 390              # the longer side limits this one
+    pipe.feed_ragged(arena, hs, ws, offs)
+    pipe.run()
+    m = pipe.get_int_array(mirror)
+    (t,) = pipe.get_output_tensors()
+    got, roi = t.numpy(), t.roi()
+    tab = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    for i in range(n):
+        dw, dh = O.resize_dst_size(int(ws[i]), int(hs[i]), 0, 0, 4, max_w=64, max_h=96, cap_w=96, cap_h=96)
+        assert (roi[i, 2], roi[i, 3]) == (dw, dh) and min(dw, dh) <= 64 and max(dw, dh) <= 96
+        tab[i]["src_offset"], tab[i]["src_stride"] = offs[i], ws[i] * 3
+        tab[i]["roi_w"], tab[i]["roi_h"], tab[i]["dst_w"], tab[i]["dst_h"] = ws[i], hs[i], dw, dh
+        tab[i]["crop_w"], tab[i]["crop_h"], tab[i]["mirror"] = dw, dh, m[i]
+    mul, add = S.normalize_tables()
+    exp = O.resample(arena, tab, 96, 96, T.FP32, T.NHWC, mul, add)
+    assert np.array_equal(got, exp)
+    assert (int(roi[0, 2]), int(roi[0, 3])) == (95, 22)          # 390 x 90: size = round(96*90/390) = 22, width = 22*390//90
+    pipe.rocal_release()
+
+
 def test_upload_modes(cuda):
     """Host input reaches the kernels whole, as the rectangle the crop can read, or - pinned memory - without a
     copy (the kernel's bulk copies read the pinned buffer): the result is the same, the bytes moved are not.
