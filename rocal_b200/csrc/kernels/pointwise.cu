@@ -89,6 +89,76 @@ __device__ __forceinline__ void color_twist_px(float r, float g, float b, float 
     o2 = hsv_channel(cmax, vs, hp, 1.f);
 }
 
+// ColorTwist of two pixels at once: the same operation sequence as color_twist_px followed by alpha*x + beta,
+// with adds / multiplies that both pixels share issued as one packed f32x2 instruction (each lane rounds on
+// its own, so a lane equals the scalar sequence) and the conditional corrections written as selects.
+//
+// A packed multiply whose result feeds a packed add or subtract is NOT safe: ptxas was measured to merge
+// mul.rn.f32x2 + add.rn.f32x2 into one fused multiply-add (one rounding instead of two, whatever --fmad says),
+// which moves a result across a rounding boundary about once in 10^5 values. A scalar add.rn of a packed
+// product's lanes is never merged, so every such sum goes through lanes_add / lanes_sub.
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return fma2(b, make_float2(-1.0f, -1.0f), a); }   // a - b, one rounding
+__device__ __forceinline__ float2 lanes_add(float2 a, float2 b) { return make_float2(add_rn(a.x, b.x), add_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 lanes_sub(float2 a, float2 b) { return make_float2(sub_rn(a.x, b.x), sub_rn(a.y, b.y)); }
+__device__ __forceinline__ void color_twist_px2(float2 r, float2 g, float2 b, float alpha, float beta, float hue, float sat,
+                                                const float* rcp, float2& o0, float2& o1, float2& o2) {
+    float2 cmax, cmin;
+    cmax.x = fmaxf(r.x, fmaxf(g.x, b.x)); cmax.y = fmaxf(r.y, fmaxf(g.y, b.y));
+    cmin.x = fminf(r.x, fminf(g.x, b.x)); cmin.y = fminf(r.y, fminf(g.y, b.y));
+    const float2 delta = sub2(cmax, cmin);
+    const float2 k23 = make_float2(8388608.0f, 8388608.0f);
+    const float2 di = add2(delta, k23), mi = add2(cmax, k23);     // integers 0..255 in the low mantissa byte
+    float2 rd, rm;
+    rd.x = rcp[__float_as_uint(di.x) & 0xFFu]; rd.y = rcp[__float_as_uint(di.y) & 0xFFu];
+    rm.x = rcp[__float_as_uint(mi.x) & 0xFFu]; rm.y = rcp[__float_as_uint(mi.y) & 0xFFu];
+    float2 s = mul2(delta, rm);
+    const float2 gb = sub2(g, b), br = sub2(b, r), rg = sub2(r, g);
+    float2 num, offs;
+    {
+        const bool ir = cmax.x == r.x, ig = cmax.x == g.x;
+        num.x = ir ? gb.x : (ig ? br.x : rg.x);
+        offs.x = ir ? 0.f : (ig ? 120.f : 240.f);
+    }
+    {
+        const bool ir = cmax.y == r.y, ig = cmax.y == g.y;
+        num.y = ir ? gb.y : (ig ? br.y : rg.y);
+        offs.y = ir ? 0.f : (ig ? 120.f : 240.f);
+    }
+    float2 h = lanes_add(mul2(make_float2(60.f, 60.f), mul2(num, rd)), offs);
+    const float2 hw = add2(h, make_float2(360.f, 360.f));
+    h.x = h.x < 0.f ? hw.x : h.x;
+    h.y = h.y < 0.f ? hw.y : h.y;
+    h = add2(h, make_float2(hue, hue));
+    float2 fl = mul2(h, make_float2(1.0f / 360.f, 1.0f / 360.f));
+    fl.x = floorf(fl.x);
+    fl.y = floorf(fl.y);
+    h = lanes_sub(h, mul2(make_float2(360.f, 360.f), fl));
+    s = mul2(s, make_float2(sat, sat));
+    s.x = fminf(fmaxf(s.x, 0.f), 1.f);
+    s.y = fminf(fmaxf(s.y, 0.f), 1.f);
+    const float2 hp = mul2(h, make_float2(1.0f / 60.f, 1.0f / 60.f));
+    const float2 vs = mul2(cmax, s);
+    const float2 a2 = make_float2(alpha, alpha), b2 = make_float2(beta, beta);
+    float2 out[3];
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const float nshift = c == 0 ? 5.f : (c == 1 ? 3.f : 1.f);
+        float2 k = lanes_add(make_float2(nshift, nshift), hp);
+        const float2 kw = add2(k, make_float2(-6.f, -6.f));
+        k.x = k.x >= 6.f ? kw.x : k.x;
+        k.y = k.y >= 6.f ? kw.y : k.y;
+        const float2 k4 = sub2(make_float2(4.f, 4.f), k);
+        float2 t;
+        t.x = fminf(fmaxf(fminf(k.x, k4.x), 0.f), 1.f);
+        t.y = fminf(fmaxf(fminf(k.y, k4.y), 0.f), 1.f);
+        const float2 ch = lanes_sub(cmax, mul2(vs, t));
+        out[c] = lanes_add(mul2(a2, ch), b2);
+    }
+    o0 = out[0];
+    o1 = out[1];
+    o2 = out[2];
+}
+
 // The colour result before rounding and saturation.
 template <int COLOR_OP>
 __device__ __forceinline__ void color_raw(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
@@ -339,17 +409,21 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                     uint32_t e[3];
                     if (COLOR_OP == RB200_COLOR_TWIST) {
                         uint32_t q[12];
+                        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
 #pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            float c3[3];
+                        for (int k = 0; k < 4; k += 2) {       // pixels k and k+1 of the block in the two lanes
+                            float2 c3[3];
 #pragma unroll
                             for (int c = 0; c < 3; c++) {
-                                const int bidx = 3 * k + c;
-                                c3[c] = sub_rn(__uint_as_float(__byte_perm(d[bidx >> 2], L.magic, 0x7650u + (bidx & 3))), 8388608.0f);
+                                const int ba = 3 * k + c, bb = 3 * (k + 1) + c;
+                                c3[c].x = __uint_as_float(__byte_perm(d[ba >> 2], L.magic, 0x7650u + (ba & 3)));
+                                c3[c].y = __uint_as_float(__byte_perm(d[bb >> 2], L.magic, 0x7650u + (bb & 3)));
+                                c3[c] = add2(c3[c], nk23);
                             }
-                            color_raw<COLOR_OP>(c3[0], c3[1], c3[2], s.alpha, s.beta, s.hue, s.sat, rcp);
-#pragma unroll
-                            for (int c = 0; c < 3; c++) q[3 * k + c] = cvt_sat_u8(c3[c]);
+                            float2 o0, o1, o2;
+                            color_twist_px2(c3[0], c3[1], c3[2], s.alpha, s.beta, s.hue, s.sat, rcp, o0, o1, o2);
+                            q[3 * k + 0] = cvt_sat_u8(o0.x); q[3 * k + 1] = cvt_sat_u8(o1.x); q[3 * k + 2] = cvt_sat_u8(o2.x);
+                            q[3 * k + 3] = cvt_sat_u8(o0.y); q[3 * k + 4] = cvt_sat_u8(o1.y); q[3 * k + 5] = cvt_sat_u8(o2.y);
                         }
 #pragma unroll
                         for (int wd = 0; wd < 3; wd++) e[wd] = pack4_u8(q[4 * wd], q[4 * wd + 1], q[4 * wd + 2], q[4 * wd + 3]);
@@ -368,9 +442,9 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                                 x.y = __uint_as_float(__byte_perm(d[wd], L.magic, 0x7651u + hb));
                                 x = add2(x, nk23);
                                 if (COLOR_OP == RB200_COLOR_BRIGHTNESS)
-                                    x = add2(mul2(a2, x), b2);
+                                    x = lanes_add(mul2(a2, x), b2);
                                 else
-                                    x = add2(mul2(add2(x, nb2), a2), b2);
+                                    x = lanes_add(mul2(add2(x, nb2), a2), b2);
                                 q[hb] = cvt_sat_u8(x.x);
                                 q[hb + 1] = cvt_sat_u8(x.y);
                             }
