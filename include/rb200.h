@@ -129,6 +129,29 @@ RB200_API size_t rb200_get_last_batch_padded_size(rb200_context ctx);
  * output_mem_type 0 = host, 1 = device) and rocalGetImageSizes (width, height of every source image). */
 RB200_API int rb200_get_one_hot_image_labels(rb200_context ctx, void* buf, int num_classes, int output_mem_type);
 RB200_API int rb200_get_image_sizes(rb200_context ctx, int* width_height_pairs);
+/* rocalFusedJpegCropSingleShard (rocal_api_data_loaders.h:493-506; decoders.image_slice and
+ * decoders.image_random_crop of the Python API): the folder source of rb200_jpeg_file_source whose images reach
+ * the graph cut to a random-resized-crop window: area_factor[2] = {min, max} fraction of the image area,
+ * aspect_ratio[2] = {min, max} width / height, num_attempts draws before the clamped fallback
+ * (RocalRandomCropDecParam, parameter_random_crop_decoder.cpp:41-101). The image is decoded whole; the window is a
+ * view into it, so the crop costs no pass over the pixels. The batch seeds come from the context's seed
+ * (the reference draws them from std::random_device). */
+RB200_API rb200_tensor rb200_fused_jpeg_crop_file_source(rb200_context ctx, const char* source_path, int color_format,
+                                                         unsigned shard_id, unsigned shard_count, int is_output,
+                                                         const float* area_factor, const float* aspect_ratio, unsigned num_attempts,
+                                                         int shuffle, int loop, unsigned max_width, unsigned max_height,
+                                                         int last_batch_policy, int pad_last_batch_repeated);
+/* [extension] The same windows for an external source fed with encoded JPEG (rb200_feed_encoded / rb200_feed_files);
+ * call after rb200_external_source and before rb200_verify. */
+RB200_API int rb200_set_random_crop_decoder(rb200_context ctx, const float* area_factor, const float* aspect_ratio,
+                                            unsigned num_attempts);
+/* [extension] Windows {x, y, w, h} of the current batch inside the decoded images, and the batch seed they came from
+ * (either pointer may be null). */
+RB200_API int rb200_get_decoder_crop_windows(rb200_context ctx, unsigned* xywh, unsigned* batch_seed);
+/* [extension] Host only, no context: the n windows that batch seed `batch_seed` gives images of
+ * shapes_hw[n][2] = {height, width}. */
+RB200_API int rb200_random_crop_windows(unsigned batch_seed, const int* shapes_hw, size_t n, const float* area_factor,
+                                        const float* aspect_ratio, unsigned num_attempts, unsigned* out_xywh);
 /* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
  * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
 RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);

@@ -196,6 +196,18 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegFileSourceSingleShard(
     RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
     unsigned max_height = 0, RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG,
     RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+/* rocal_api_data_loaders.h:462-506: the folder source with a random-resized-crop window per image
+ * (area_factor = {min, max} fraction of the image area, aspect_ratio = {min, max} width / height). */
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalFusedJpegCrop(
+    RocalContext context, const char* source_path, RocalImageColor rocal_color_format, unsigned num_threads, bool is_output,
+    std::vector<float>& area_factor, std::vector<float>& aspect_ratio, unsigned num_attempts, bool shuffle = false,
+    bool loop = false, RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
+    unsigned max_height = 0, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalFusedJpegCropSingleShard(
+    RocalContext context, const char* source_path, RocalImageColor color_format, unsigned shard_id, unsigned shard_count,
+    bool is_output, std::vector<float>& area_factor, std::vector<float>& aspect_ratio, unsigned num_attempts,
+    bool shuffle = false, bool loop = false, RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE,
+    unsigned max_width = 0, unsigned max_height = 0, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
 /* COCO detection datasets (rocal_api_meta_data.h:89, rocal_api_data_loaders.h:163-174,257-269): boxes and labels come
  * from the annotation file and follow the graph's crops and mirrors. */
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateCOCOReader(RocalContext rocal_context, const char* source_path, bool is_output,

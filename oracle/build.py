@@ -6,8 +6,9 @@ liboracle.so   the CPU restatement in oracle.c (gcc, -ffp-contract=off so that e
                operation rounds once; -mavx2 -mfma -mf16c are the reference's own CPU flags,
                rocAL/CMakeLists.txt:375).
 _ref/libref.so reference-owned CPU code compiled where it lies (never copied):
-               rocAL/source/meta_data/bounding_box_graph.cpp + ref_driver.cpp, against the
-               stand-in headers in ref_stubs/. Only built when REFERENCE_ROOT exists.
+               rocAL/source/meta_data/bounding_box_graph.cpp, rocAL/source/parameters/
+               parameter_factory.cpp and parameter_random_crop_decoder.cpp + ref_driver.cpp, against
+               the stand-in headers in ref_stubs/. Only built when REFERENCE_ROOT exists.
 """
 import os
 import subprocess
@@ -49,7 +50,10 @@ def build_ref(force=False):
     if not reference_available():
         return REF_SO if os.path.exists(REF_SO) else None
     r = os.path.join(REFERENCE_ROOT, "rocAL")
-    srcs = [os.path.join(r, "source", "meta_data", "bounding_box_graph.cpp"), os.path.join(HERE, "ref_driver.cpp")]
+    srcs = [os.path.join(r, "source", "meta_data", "bounding_box_graph.cpp"),
+            os.path.join(r, "source", "parameters", "parameter_factory.cpp"),
+            os.path.join(r, "source", "parameters", "parameter_random_crop_decoder.cpp"),
+            os.path.join(HERE, "ref_driver.cpp")]
     if force or _stale(REF_SO, srcs):
         os.makedirs(REF_DIR, exist_ok=True)
         cmd = ["g++", "-std=c++17", "-O3", "-fPIC", "-shared", "-fopenmp", "-ffp-contract=off",

@@ -294,3 +294,139 @@ class CustomRand:
         raw = self._rs.randint(0, 1 << 32, size=self.batch, dtype=np.uint64).astype(np.float64) / 4294967295.0
         idx = np.searchsorted(self.cdf, raw, side="right")
         return self.values[idx]
+
+
+# ---- random-resized-crop windows of the fused JPEG crop source ----------------------------
+
+class _Mt19937:
+    """Raw 32-bit outputs of std::mt19937(seed)."""
+
+    def __init__(self, seed):
+        self._rs = np.random.RandomState()
+        self._rs.seed(int(seed) & 0xFFFFFFFF)
+
+    def __call__(self):
+        return int(self._rs.randint(0, 1 << 32, size=1, dtype=np.uint64)[0])
+
+
+def _uniform_real_f32(gen, a, b):
+    """std::uniform_real_distribution<float>(a, b)(mt19937) as libstdc++ evaluates it: one 32-bit draw, converted
+    to float (round to nearest), divided by 2^32, pulled below 1 when the conversion rounded up to 2^32
+    (std::generate_canonical<float, 24>), then canonical * (b - a) + a in float."""
+    f32 = np.float32
+    c = f32(f32(gen()) / f32(4294967296.0))
+    if c >= f32(1.0):
+        c = np.nextafter(f32(1.0), f32(0.0))
+    return f32(f32(c * f32(f32(b) - f32(a))) + f32(a))
+
+
+def _uniform_int(gen, lo, hi):
+    """std::uniform_int_distribution<int>(lo, hi)(mt19937) as libstdc++ (GCC 11 and later) evaluates it for a
+    32-bit engine: the multiply-and-reject method on a 64-bit product."""
+    span = (hi - lo + 1) & 0xFFFFFFFF
+    if span == 0:
+        return lo + gen()
+    prod = gen() * span
+    low = prod & 0xFFFFFFFF
+    if low < span:
+        threshold = ((1 << 32) - span) % span
+        while low < threshold:
+            prod = gen() * span
+            low = prod & 0xFFFFFFFF
+    return lo + (prod >> 32)
+
+
+_libm = None
+
+
+def _libm_f32(name, x):
+    """logf / expf of the C library (std::log / std::exp on a float)."""
+    global _libm
+    if _libm is None:
+        _libm = ctypes.CDLL("libm.so.6")
+        for fn in ("logf", "expf"):
+            getattr(_libm, fn).restype = ctypes.c_float
+            getattr(_libm, fn).argtypes = [ctypes.c_float]
+    return np.float32(getattr(_libm, name)(float(np.float32(x))))
+
+
+def _roundf_int(x):
+    """(int)roundf(x) for a non-negative float below 2^23: halves away from zero."""
+    return int(np.floor(np.float64(x) + 0.5))
+
+
+def random_crop_window(height, width, sample_seed, aspect=(3.0 / 4, 4.0 / 3), area=(0.08, 1.0), num_attempts=10):
+    """RocalRandomCropDecParam::generate_crop_window (parameter_random_crop_decoder.cpp:41-101) for one image:
+    returns (x, y, w, h). Every intermediate keeps the C type of the reference's expression."""
+    f32 = np.float32
+    H, W = int(height), int(width)
+    if H <= 0 or W <= 0:
+        return (0, 0, 1, 1)
+    gen = _Mt19937(sample_seed)
+    a_lo, a_hi = f32(aspect[0]), f32(aspect[1])
+    s_lo, s_hi = f32(area[0]), f32(area[1])
+    log_lo, log_hi = _libm_f32("logf", a_lo), _libm_f32("logf", a_hi)
+    max_hw = f32(f32(1.0) / a_lo)
+    min_area = f32(f32(W * H) * s_lo)
+    max_w = max(1, int(f32(f32(H) * a_hi)))
+    max_h = max(1, int(f32(f32(W) * max_hw)))
+    if f32(H * max_w) < min_area:
+        ch, cw = H, max_w
+    elif f32(W * max_h) < min_area:
+        ch, cw = max_h, W
+    else:
+        left = num_attempts
+        ch = cw = 1
+        while left > 0:
+            scale = _uniform_real_f32(gen, s_lo, s_hi)
+            target = f32(scale * f32(H * W))
+            ratio = _libm_f32("expf", _uniform_real_f32(gen, log_lo, log_hi))
+            cw = max(1, _roundf_int(np.sqrt(f32(target * ratio))))
+            ch = max(1, _roundf_int(np.sqrt(f32(target / ratio))))
+            got = f32(f32(cw) / f32(ch))
+            if cw <= W and ch <= H and a_lo <= got <= a_hi:
+                break
+            left -= 1
+        if left <= 0:
+            max_area = f32(f32(s_hi * f32(W)) * f32(H))
+            whole = f32(f32(W) / f32(H))
+            if whole > a_hi:
+                ch, cw = H, max_w
+            elif whole < a_lo:
+                ch, cw = max_h, W
+            else:
+                ch, cw = H, W
+            shrink = min(f32(1.0), f32(max_area / f32(cw * ch)))
+            side = np.sqrt(f32(shrink))
+            cw = max(1, int(f32(f32(cw) * side)))
+            ch = max(1, int(f32(f32(ch) * side)))
+    x = _uniform_int(gen, 0, W - cw)
+    y = _uniform_int(gen, 0, H - ch)
+    return (x, y, cw, ch)
+
+
+def random_crop_windows(batch_seed, shapes_hw, aspect=(3.0 / 4, 4.0 / 3), area=(0.08, 1.0), num_attempts=10):
+    """The windows of one batch: sample seeds = std::seed_seq{batch_seed}.generate()
+    (RocalRandomCropDecParam::generate_random_seeds, parameter_random_crop_decoder.cpp:104-108), then one
+    window per (height, width). Returns an (n, 4) uint32 array of x, y, w, h."""
+    shapes = np.asarray(shapes_hw, dtype=np.int64).reshape(-1, 2)
+    seeds = seed_sequence(int(batch_seed), count=len(shapes))
+    out = np.zeros((len(shapes), 4), dtype=np.uint32)
+    for i, (h, w) in enumerate(shapes):
+        out[i] = random_crop_window(h, w, int(seeds[i]), aspect, area, num_attempts)
+    return out
+
+
+def ref_random_crop_windows(shapes_hw, aspect=(3.0 / 4, 4.0 / 3), area=(0.08, 1.0), num_attempts=10):
+    """The reference build's windows for one batch and the batch seed its std::random_device drew:
+    (batch_seed, (n, 4) uint32 array). None when the reference build is absent."""
+    r = ref()
+    if r is None:
+        return None
+    shapes = np.ascontiguousarray(np.asarray(shapes_hw, dtype=np.int32).reshape(-1, 2))
+    out = np.zeros((len(shapes), 4), dtype=np.uint32)
+    r.ref_random_crop_windows.restype = ctypes.c_uint
+    seed = r.ref_random_crop_windows(_ptr(shapes), ctypes.c_int(len(shapes)), ctypes.c_float(aspect[0]),
+                                     ctypes.c_float(aspect[1]), ctypes.c_float(area[0]), ctypes.c_float(area[1]),
+                                     ctypes.c_int(num_attempts), _ptr(out))
+    return int(seed), out

@@ -15,6 +15,10 @@
  *   ref_custom_rand_int  -> CustomRand<int> (parameter_random.h:118-239)
  *   ref_seed_sequence    -> the seed table of ParameterFactory::set_seed
  *                           (rocAL/source/parameters/parameter_factory.cpp:114-119)
+ *   ref_random_crop_windows -> RocalRandomCropDecParam::generate_random_seeds + generate_crop_window
+ *                           (rocAL/source/parameters/parameter_random_crop_decoder.cpp:41-108, compiled in place
+ *                           with parameter_factory.cpp); the batch seed is the reference's own std::random_device
+ *                           draw and is handed back so that a restatement can start from the same value
  */
 #include <cstdint>
 #include <memory>
@@ -22,7 +26,9 @@
 #include <vector>
 
 #include "meta_data/bounding_box_graph.h"
+#include "parameters/parameter_factory.h"
 #include "parameters/parameter_random.h"
+#include "parameters/parameter_random_crop_decoder.h"
 
 extern "C" {
 
@@ -117,6 +123,24 @@ __attribute__((visibility("default"))) void ref_seed_sequence(unsigned seed, uns
     std::seed_seq ss{seed};
     ss.generate(table.begin(), table.end());
     for (unsigned i = 0; i < count; i++) out[i] = table[i];
+}
+
+// shapes_hw: n x {height, width}; out_xywh: n x {x, y, w, h}; returns the batch seed the windows came from.
+__attribute__((visibility("default"))) unsigned ref_random_crop_windows(const int* shapes_hw, int n, float aspect_lo,
+                                                                        float aspect_hi, float area_lo, float area_hi,
+                                                                        int num_attempts, unsigned* out_xywh) {
+    RocalRandomCropDecParam param({aspect_lo, aspect_hi}, {area_lo, area_hi}, 0, num_attempts, n);
+    param.generate_random_seeds();
+    const unsigned batch_seed = ParameterFactory::instance()->get_seed();
+    for (int i = 0; i < n; i++) {
+        Shape shape = {(size_t)shapes_hw[i * 2], (size_t)shapes_hw[i * 2 + 1]};
+        CropWindow w = param.generate_crop_window(shape, i);
+        out_xywh[i * 4 + 0] = w.x;
+        out_xywh[i * 4 + 1] = w.y;
+        out_xywh[i * 4 + 2] = w.W;
+        out_xywh[i * 4 + 3] = w.H;
+    }
+    return batch_seed;
 }
 
 }  // extern "C"

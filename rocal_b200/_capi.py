@@ -48,6 +48,12 @@ get_image_labels = _proto("rb200_get_image_labels", c_int, _P, POINTER(c_int))
 get_image_name_len = _proto("rb200_get_image_name_len", c_uint, _P, POINTER(c_int))
 get_image_name = _proto("rb200_get_image_name", c_int, _P, c_char_p)
 get_one_hot_image_labels = _proto("rb200_get_one_hot_image_labels", c_int, _P, c_void_p, c_int, c_int)
+fused_jpeg_crop_file_source = _proto("rb200_fused_jpeg_crop_file_source", _P, _P, c_char_p, c_int, c_uint, c_uint, c_int,
+                                     POINTER(c_float), POINTER(c_float), c_uint, c_int, c_int, c_uint, c_uint, c_int, c_int)
+set_random_crop_decoder = _proto("rb200_set_random_crop_decoder", c_int, _P, POINTER(c_float), POINTER(c_float), c_uint)
+get_decoder_crop_windows = _proto("rb200_get_decoder_crop_windows", c_int, _P, POINTER(c_uint), POINTER(c_uint))
+random_crop_windows = _proto("rb200_random_crop_windows", c_int, c_uint, POINTER(c_int), c_size_t, POINTER(c_float),
+                             POINTER(c_float), c_uint, POINTER(c_uint))
 get_image_sizes = _proto("rb200_get_image_sizes", c_int, _P, POINTER(c_int))
 get_last_batch_padded_size = _proto("rb200_get_last_batch_padded_size", c_size_t, _P)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)

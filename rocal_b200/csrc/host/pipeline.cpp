@@ -366,6 +366,23 @@ void Pipeline::top_up() {
     }
 }
 
+void Pipeline::set_random_crop_decoder(const RandomCropRanges& r) {
+    if (_verified) RB200_THROW("the graph is already verified");
+    if (_source < 0) RB200_THROW("the context has no source yet");
+    if (_tensors[_source]->is_output) RB200_THROW("the fused JPEG crop source cannot be a graph output");
+    if (!(r.area_lo > 0.f) || r.area_hi < r.area_lo || !(r.aspect_lo > 0.f) || r.aspect_hi < r.aspect_lo || r.num_attempts < 1)
+        RB200_THROW("fused JPEG crop: area_factor and aspect_ratio must be positive ascending pairs, num_attempts >= 1");
+    _crop_dec.reset(new RandomCropWindowSampler(r, ParameterFactory::instance().get_seed()));
+}
+
+void Pipeline::decoder_crop_windows(unsigned* xywh, unsigned* batch_seed) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    const Slot& s = _slots[_held];
+    if (s.decoder_windows.size() != _batch * 4) RB200_THROW("the current batch did not come from a fused JPEG crop source");
+    if (xywh) std::memcpy(xywh, s.decoder_windows.data(), s.decoder_windows.size() * sizeof(unsigned));
+    if (batch_seed) *batch_seed = s.decoder_batch_seed;
+}
+
 void Pipeline::reset_loaders() {
     if (!_files) RB200_THROW("rocalResetLoaders: the context has no file source");
     _files->reset();
@@ -1105,6 +1122,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
 
     // ---- 1. input: device views of the n source images (the upload itself follows the tables) ----
     _src_views.resize(n);
+    s.decoder_windows.clear();
     const bool host_input = !(b.kind == InputBatch::RAGGED && b.mem_kind == RB200_MEM_DEVICE);
     int arena_used = -1;
     if (b.kind == InputBatch::RAGGED) {
@@ -1128,15 +1146,30 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         }
         _jpeg.init();
         size_t total = 0;
+        _decode_off.resize(n);
+        if (_crop_dec) {
+            s.decoder_batch_seed = _crop_dec->next_batch(n);
+            s.decoder_windows.resize(n * 4);
+        }
         for (size_t i = 0; i < n; i++) {
             int w = 0, h = 0;
             _jpeg.image_size(b.bufs[i], b.enc_sizes[i], w, h);
             if (w <= 0 || h <= 0 || w > src->max_w || h > src->max_h)
                 RB200_THROW("decoded image " + std::to_string(i) + " (" + std::to_string(w) + "x" + std::to_string(h) +
                             ") is empty or exceeds the source's max_width x max_height");
+            _decode_off[i] = total;
             _src_views[i] = {total, (uint32_t)w * 3};
             src->roi_w[i] = w;
             src->roi_h[i] = h;
+            if (_crop_dec) {
+                // the whole image is decoded; the graph sees the window as its source image (a view into it)
+                const CropRect win = _crop_dec->window(h, w, i);
+                _src_views[i].offset = total + (size_t)win.y * w * 3 + (size_t)win.x * 3;
+                src->roi_w[i] = (int)win.w;
+                src->roi_h[i] = (int)win.h;
+                unsigned* dw = &s.decoder_windows[i * 4];
+                dw[0] = win.x; dw[1] = win.y; dw[2] = win.w; dw[3] = win.h;
+            }
             total += ((size_t)w * h * 3 + 255) & ~(size_t)255;
         }
         b.arena_bytes = total + 256;
@@ -1314,7 +1347,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         _jpeg_pitch.resize(n);
         size_t enc = 0;
         for (size_t i = 0; i < n; i++) {
-            _jpeg_dst[i] = (unsigned char*)_arena[arena_used] + _src_views[i].offset;
+            _jpeg_dst[i] = (unsigned char*)_arena[arena_used] + _decode_off[i];
             _jpeg_pitch[i] = _src_views[i].stride;
             enc += b.enc_sizes[i];
         }

@@ -27,6 +27,7 @@
 #include "file_source.h"
 #include "jpeg_decoder.h"
 #include "params.h"
+#include "random_crop_window.h"
 #include "rb200.h"
 #include "rocal_api.h"
 
@@ -201,6 +202,8 @@ struct Slot {
     std::vector<int> file_labels;    // file source: class label per sample
     std::vector<std::string> names;  // file source: file name per sample
     size_t padded = 0;
+    std::vector<unsigned> decoder_windows;   // fused JPEG crop: n x {x,y,w,h} inside the decoded images
+    unsigned decoder_batch_seed = 0;
     size_t n = 0;
     std::string error;
 };
@@ -217,6 +220,9 @@ class Pipeline {
     TensorImpl* add_coco_source(const std::string& root, const std::string& json_path, bool avoid_class_remapping, unsigned shard_id,
                                 unsigned shard_count, bool shuffle, bool loop, unsigned max_w, unsigned max_h, bool is_output,
                                 int last_batch_policy, bool pad_last_batch_repeated);
+    // rocalFusedJpegCrop*: every image of an encoded source is cut to a random-resized-crop window before the graph
+    void set_random_crop_decoder(const RandomCropRanges& r);
+    void decoder_crop_windows(unsigned* xywh, unsigned* batch_seed);
     void reset_loaders();
     void image_labels(int* buf);
     const std::vector<std::string>& image_names();
@@ -342,6 +348,8 @@ class Pipeline {
     // JPEG front-end (created when the first encoded batch arrives)
     JpegDecoder _jpeg;
     std::vector<unsigned char*> _jpeg_dst;
+    std::vector<size_t> _decode_off;                       // arena offset of each decoded image (the view may start inside it)
+    std::unique_ptr<RandomCropWindowSampler> _crop_dec;    // fused JPEG crop source
     std::vector<size_t> _jpeg_pitch;
 
     // input arenas (double buffered)

@@ -385,6 +385,83 @@ rb200_tensor rb200_coco_file_source(rb200_context ctx, const char* source_path, 
     }
 }
 
+namespace {
+rb200::RandomCropRanges crop_ranges(const float* area_factor, const float* aspect_ratio, unsigned num_attempts) {
+    if (!area_factor || !aspect_ratio) RB200_THROW("area_factor and aspect_ratio must point to two floats each");
+    rb200::RandomCropRanges r;
+    r.area_lo = area_factor[0];
+    r.area_hi = area_factor[1];
+    r.aspect_lo = aspect_ratio[0];
+    r.aspect_hi = aspect_ratio[1];
+    r.num_attempts = (int)num_attempts;
+    if (!(r.area_lo > 0.f) || r.area_hi < r.area_lo || !(r.aspect_lo > 0.f) || r.aspect_hi < r.aspect_lo || r.num_attempts < 1)
+        RB200_THROW("fused JPEG crop: area_factor and aspect_ratio must be positive ascending pairs, num_attempts >= 1");
+    return r;
+}
+}  // namespace
+
+rb200_tensor rb200_fused_jpeg_crop_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
+                                               unsigned shard_count, int is_output, const float* area_factor,
+                                               const float* aspect_ratio, unsigned num_attempts, int shuffle, int loop,
+                                               unsigned max_width, unsigned max_height, int last_batch_policy,
+                                               int pad_last_batch_repeated) {
+    CTX_OR(nullptr);
+    try {
+        if (!source_path) RB200_THROW("null source path");
+        if (color_format != ROCAL_COLOR_RGB24) RB200_THROW("the file source decodes to ROCAL_COLOR_RGB24 only");
+        if (is_output) RB200_THROW("the fused JPEG crop source cannot be a graph output");
+        const rb200::RandomCropRanges r = crop_ranges(area_factor, aspect_ratio, num_attempts);
+        rb200::TensorImpl* t = P(ctx)->add_file_source(source_path, shard_id, shard_count, shuffle != 0, loop != 0, max_width,
+                                                       max_height, false, last_batch_policy, pad_last_batch_repeated != 0);
+        P(ctx)->set_random_crop_decoder(r);
+        return static_cast<rocalTensor*>(t);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return nullptr;
+    }
+}
+
+int rb200_set_random_crop_decoder(rb200_context ctx, const float* area_factor, const float* aspect_ratio, unsigned num_attempts) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->set_random_crop_decoder(crop_ranges(area_factor, aspect_ratio, num_attempts));
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_INVALID_PARAMETER_TYPE;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_decoder_crop_windows(rb200_context ctx, unsigned* xywh, unsigned* batch_seed) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->decoder_crop_windows(xywh, batch_seed);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_random_crop_windows(unsigned batch_seed, const int* shapes_hw, size_t n, const float* area_factor,
+                              const float* aspect_ratio, unsigned num_attempts, unsigned* out_xywh) {
+    try {
+        if (n && (!shapes_hw || !out_xywh)) return ROCAL_INVALID_PARAMETER_TYPE;
+        const rb200::RandomCropRanges r = crop_ranges(area_factor, aspect_ratio, num_attempts);
+        const std::vector<uint32_t> seeds = rb200::random_crop_sample_seeds(batch_seed, n);
+        for (size_t i = 0; i < n; i++) {
+            const rb200::CropRect w = rb200::random_crop_window(shapes_hw[i * 2], shapes_hw[i * 2 + 1], seeds[i], r);
+            out_xywh[i * 4] = w.x;
+            out_xywh[i * 4 + 1] = w.y;
+            out_xywh[i * 4 + 2] = w.w;
+            out_xywh[i * 4 + 3] = w.h;
+        }
+    } catch (const std::exception&) {
+        return ROCAL_INVALID_PARAMETER_TYPE;
+    }
+    return ROCAL_OK;
+}
+
 int rb200_reset_loaders(rb200_context ctx) {
     CTX_OR(ROCAL_CONTEXT_INVALID);
     try {

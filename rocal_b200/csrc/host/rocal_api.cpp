@@ -71,6 +71,32 @@ RocalTensor ROCAL_API_CALL rocalJpegFileSource(RocalContext ctx, const char* sou
     }
     return rocalJpegFileSourceSingleShard(ctx, source_path, color, 0, 1, is_output, shuffle, loop, p, max_width, max_height, d, si);
 }
+RocalTensor ROCAL_API_CALL rocalFusedJpegCropSingleShard(RocalContext ctx, const char* source_path, RocalImageColor color,
+                                                         unsigned shard_id, unsigned shard_count, bool is_output,
+                                                         std::vector<float>& area_factor, std::vector<float>& aspect_ratio,
+                                                         unsigned num_attempts, bool shuffle, bool loop,
+                                                         RocalImageSizeEvaluationPolicy, unsigned max_width, unsigned max_height,
+                                                         RocalShardingInfo si) {
+    if (area_factor.size() != 2 || aspect_ratio.size() != 2) {
+        if (ctx) P(ctx)->capture_error("rocalFusedJpegCrop: area_factor and aspect_ratio must hold two values each");
+        return nullptr;
+    }
+    return static_cast<RocalTensor>(rb200_fused_jpeg_crop_file_source(ctx, source_path, (int)color, shard_id, shard_count, is_output,
+                                                                      area_factor.data(), aspect_ratio.data(), num_attempts, shuffle,
+                                                                      loop, max_width, max_height, (int)si.last_batch_policy,
+                                                                      si.pad_last_batch_repeated));
+}
+RocalTensor ROCAL_API_CALL rocalFusedJpegCrop(RocalContext ctx, const char* source_path, RocalImageColor color, unsigned num_threads,
+                                              bool is_output, std::vector<float>& area_factor, std::vector<float>& aspect_ratio,
+                                              unsigned num_attempts, bool shuffle, bool loop, RocalImageSizeEvaluationPolicy p,
+                                              unsigned max_width, unsigned max_height, RocalShardingInfo si) {
+    if (num_threads != 1) {
+        if (ctx) P(ctx)->capture_error("rocalFusedJpegCrop: num_threads (internal shards) must be 1 (one context drives one GPU; use rocalFusedJpegCropSingleShard per rank)");
+        return nullptr;
+    }
+    return rocalFusedJpegCropSingleShard(ctx, source_path, color, 0, 1, is_output, area_factor, aspect_ratio, num_attempts, shuffle,
+                                         loop, p, max_width, max_height, si);
+}
 // The folder reader numbers the classes itself; the label reader call only has to name the same folder
 // (the reference keys labels by file name, label_reader_folders.cpp:95-137).
 RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext ctx, const char* source_path, const char* file_list_path) {

@@ -292,6 +292,21 @@ class Pipeline(object):
         self._check(C.get_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
         return out
 
+    def set_random_crop_decoder(self, random_area=(0.08, 1.0), random_aspect_ratio=(3.0 / 4, 4.0 / 3), num_attempts=10):
+        """[extension] Random-resized-crop windows on an external source fed with encoded JPEG (what
+        decoders.image_slice does for a folder reader). Call inside `with pipeline:` before build()."""
+        area = (ctypes.c_float * 2)(*random_area)
+        aspect = (ctypes.c_float * 2)(*random_aspect_ratio)
+        self._check(C.set_random_crop_decoder(self._handle, area, aspect, int(num_attempts)))
+
+    def get_decoder_crop_windows(self):
+        """[extension] The crop windows (x, y, w, h) of the current batch inside the decoded images, uint32 [N, 4],
+        and the batch seed they were drawn from."""
+        out = np.zeros((self._batch_size, 4), dtype=np.uint32)
+        seed = ctypes.c_uint(0)
+        self._check(C.get_decoder_crop_windows(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint)), ctypes.byref(seed)))
+        return out, int(seed.value)
+
     def get_image_names(self):
         """rocalGetImageNameLen + rocalGetImageName: file names of the current batch."""
         lens = (ctypes.c_int * self._batch_size)()

@@ -1,7 +1,8 @@
 """Generates the golden vectors of this folder from reference-owned code (oracle/_ref/libref.so, built from
 the reference tree by oracle/build.py). Run in a container that has the reference tree:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py                  # every file
+    python tests/golden/make_golden.py random_crop      # random_crop_windows.npz only
 
 box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
                   (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
@@ -10,6 +11,9 @@ box_iou_matcher.npz          BoundingBoxGraph::update_box_iou_matcher (bounding_
 param_rng.npz     UniformRand<float>, UniformRand<int>, CustomRand<int> draws
                   (rocAL/include/parameters/parameter_random.h) and the std::seed_seq table of
                   ParameterFactory::set_seed (rocAL/source/parameters/parameter_factory.cpp:114-119)
+random_crop_windows.npz   RocalRandomCropDecParam windows (rocAL/source/parameters/parameter_random_crop_decoder.cpp)
+                  for eight batches of 96 image shapes (ordinary, very wide, very tall, tiny; one or many attempts):
+                  the batch seed the reference's std::random_device drew, the shapes, the ranges and the windows
 """
 import ctypes
 import os
@@ -22,6 +26,30 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 from oracle import pyoracle as O          # noqa: E402
 from rocal_b200 import synthetic as S     # noqa: E402
+
+
+def random_crop():
+    assert O.ref() is not None, "the reference tree is needed to generate golden vectors"
+    rng = np.random.Generator(np.random.PCG64(777))
+    out = {}
+    settings = [((0.75, 4.0 / 3), (0.08, 1.0), 10), ((0.75, 1.33333), (0.08, 1.0), 100), ((0.8, 1.25), (0.08, 1.0), 10),
+                ((0.75, 4.0 / 3), (0.08, 1.0), 1), ((0.5, 2.0), (0.3, 0.6), 3), ((0.75, 4.0 / 3), (0.08, 1.0), 10),
+                ((0.75, 4.0 / 3), (0.08, 1.0), 10), ((1.0, 1.0), (0.9, 1.0), 2)]
+    for k, (aspect, area, attempts) in enumerate(settings):
+        n = 96
+        shapes = np.stack([rng.integers(1, 1400, n), rng.integers(1, 1400, n)], axis=1).astype(np.int32)
+        if k == 5:
+            shapes[:, 0] = rng.integers(1, 16, n)       # very wide
+        if k == 6:
+            shapes[:, 1] = rng.integers(1, 16, n)       # very tall
+        if k == 7:
+            shapes = rng.integers(1, 9, (n, 2)).astype(np.int32)
+        seed, win = O.ref_random_crop_windows(shapes, aspect, area, attempts)
+        out["shapes_%d" % k], out["windows_%d" % k] = shapes, win
+        out["params_%d" % k] = np.array([aspect[0], aspect[1], area[0], area[1], attempts], dtype=np.float64)
+        out["seed_%d" % k] = np.array([seed], dtype=np.uint32)
+    np.savez_compressed(os.path.join(HERE, "random_crop_windows.npz"), **out)
+    print("wrote random_crop_windows.npz")
 
 
 def main():
@@ -106,4 +134,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["random_crop"]:
+        random_crop()
+    else:
+        main()
+        random_crop()

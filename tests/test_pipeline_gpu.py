@@ -598,3 +598,132 @@ def test_error_convention(cuda):
     assert C.feed_ragged(ctx, arena.ctypes.data, arena.nbytes, d, 4, 0) == types.RUNTIME_ERROR   # empty descriptors
     assert C.feed_ragged(ctx, arena.ctypes.data, arena.nbytes, d, 3, 0) == types.RUNTIME_ERROR   # wrong batch size
     assert C.release(ctx) == types.OK
+
+
+def _decoded_by_pipeline(streams, max_side):
+    """The GPU decoder's own pixels for a list of JPEG streams (identity flip of an encoded external source)."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    n = len(streams)
+    pipe = Pipeline(batch_size=n, device_id=0, seed=1)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_COMPRESSED, max_width=max_side, max_height=max_side)
+        pipe.set_outputs(fn.flip(img, horizontal=0, vertical=0))
+    pipe.build()
+    pipe.feed_encoded(streams)
+    pipe.run()
+    full = pipe.get_output_tensors()[0].numpy().copy()
+    sizes = pipe.get_image_sizes()
+    pipe.rocal_release()
+    return [np.ascontiguousarray(full[i, :sizes[i, 1], :sizes[i, 0]]) for i in range(n)]
+
+
+def _expected_windowed_resize(pixels, windows, out_w, out_h, interpolation=0):
+    """Oracle resize of window i of image i to out_w x out_h (uint8 NHWC)."""
+    n = len(pixels)
+    offs = np.concatenate([[0], np.cumsum([p.size for p in pixels])])[:-1]
+    arena = np.concatenate([p.reshape(-1) for p in pixels])
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    for i in range(n):
+        x, y, w, h = [int(v) for v in windows[i]]
+        stride = pixels[i].shape[1] * 3
+        t[i]["src_offset"], t[i]["src_stride"] = offs[i] + y * stride + x * 3, stride
+        t[i]["roi_w"], t[i]["roi_h"], t[i]["dst_w"], t[i]["dst_h"] = w, h, out_w, out_h
+        t[i]["crop_w"], t[i]["crop_h"] = out_w, out_h
+    return O.resample(arena, t, out_w, out_h, T.UINT8, T.NHWC, interpolation=interpolation)
+
+
+def test_fused_jpeg_crop_external_source(cuda):
+    """Random-resized-crop windows on an encoded external source: the windows are the restated sampler's for the
+    batch seeds that follow from the pipeline seed, the identity output is exactly that window of the decoded image,
+    and Resize of the window (bilinear and triangular) equals the oracle on the decoder's pixels bit for bit."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(31)
+    n = 6
+    imgs, streams = _jpeg_batch(rng, n, (90, 360))
+    pixels = _decoded_by_pipeline(streams, 360)
+    shapes = np.array([[p.shape[0], p.shape[1]] for p in pixels])
+    area, aspect, attempts = (0.08, 1.0), (0.75, 1.33333), 100
+    seed = 77
+    for interp, flag in ((types.LINEAR_INTERPOLATION, 0), (types.TRIANGULAR_INTERPOLATION, 1)):
+        pipe = Pipeline(batch_size=n, device_id=0, seed=seed)
+        with pipe:
+            img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_COMPRESSED, max_width=360, max_height=360)
+            pipe.set_random_crop_decoder(area, aspect, attempts)
+            ident = fn.flip(img, horizontal=0, vertical=0)
+            r = fn.resize(img, resize_width=64, resize_height=48, interpolation_type=interp)
+            pipe.set_outputs(ident, r)
+        pipe.build()
+        batch_seeds = O._Mt19937(seed)
+        for _ in range(3):
+            pipe.feed_encoded(streams)
+            pipe.run()
+            win, bseed = pipe.get_decoder_crop_windows()
+            assert bseed == batch_seeds()
+            assert np.array_equal(win, O.random_crop_windows(bseed, shapes, aspect, area, attempts))
+            assert pipe.get_image_sizes().tolist() == win[:, 2:].tolist()
+            cut, res = [t.numpy() for t in pipe.get_output_tensors()]
+            for i in range(n):
+                x, y, w, h = [int(v) for v in win[i]]
+                assert x + w <= shapes[i, 1] and y + h <= shapes[i, 0]
+                assert np.array_equal(cut[i, :h, :w], pixels[i][y:y + h, x:x + w])
+            assert np.array_equal(res, _expected_windowed_resize(pixels, win, 64, 48, flag))
+        pipe.rocal_release()
+
+
+def test_fused_jpeg_crop_file_source(cuda, tmp_path):
+    """fn.decoders.image_slice on a folder (rocalFusedJpegCropSingleShard), the train pipeline of the reference's
+    imagenet example: image_slice -> Resize(TRIANGULAR) 224 -> CropMirrorNormalize with a coin flip, read through
+    ROCALClassificationIterator. Windows follow the sampler, labels the folders, pixels the oracle."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    from rocal_b200.plugin.pytorch import ROCALClassificationIterator
+    rng = S.rng_for(32)
+    imgs, streams = _jpeg_batch(rng, 6, (100, 320))
+    classes = ["a", "a", "b", "b", "c", "c"]
+    pixels = dict(zip(["im%d.jpg" % i for i in range(6)], _decoded_by_pipeline(streams, 320)))
+    for i, (cls, sb) in enumerate(zip(classes, streams)):
+        d = tmp_path / cls
+        d.mkdir(exist_ok=True)
+        (d / ("im%d.jpg" % i)).write_bytes(sb)
+    n, crop = 3, 56
+    pipe = Pipeline(batch_size=n, device_id=0, seed=12)
+    with pipe:
+        jpegs, labels = fn.readers.file(file_root=str(tmp_path))
+        dec = fn.decoders.image_slice(jpegs, output_type=types.RGB, file_root=str(tmp_path), shard_id=0, num_shards=1,
+                                      random_shuffle=True, max_decoded_width=320, max_decoded_height=320)
+        res = fn.resize(dec, resize_width=64, resize_height=64, output_layout=types.NHWC, output_dtype=types.UINT8,
+                        interpolation_type=types.TRIANGULAR_INTERPOLATION)
+        coin = fn.random.coin_flip(probability=0.5)
+        out = fn.crop_mirror_normalize(res, output_layout=types.NCHW, output_dtype=types.FLOAT, crop=(crop, crop), mirror=coin,
+                                       mean=MEAN, std=STD)
+        pipe.set_outputs(out)
+    pipe.build()
+    mul, add = S.normalize_tables()
+    seen = []
+    for outs, labs in ROCALClassificationIterator(pipe):
+        names = pipe.get_image_names()
+        seen += names
+        assert labs.cpu().tolist() == ["abc".index(classes[int(nm[2])]) for nm in names]
+        win, bseed = pipe.get_decoder_crop_windows()
+        px = [pixels[nm] for nm in names]
+        shapes = np.array([[p.shape[0], p.shape[1]] for p in px])
+        assert np.array_equal(win, O.random_crop_windows(bseed, shapes, (0.75, 1.33333), (0.08, 1.0), 100))
+        resized = _expected_windowed_resize(px, win, 64, 64, 1)
+        # the reader runs batches ahead, so the coin flips of this batch are no longer the parameter's current
+        # values: every sample must equal the oracle with or without the mirror
+        exp = []
+        for flag in (0, 1):
+            t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+            for i in range(n):
+                x1, y1, cw, ch = O.crop_fixed(64, 64, crop, crop, 0.5, 0.5)
+                t[i]["src_offset"], t[i]["src_stride"] = i * 64 * 64 * 3, 64 * 3
+                t[i]["roi_w"], t[i]["roi_h"], t[i]["dst_w"], t[i]["dst_h"] = 64, 64, 64, 64
+                t[i]["crop_x"], t[i]["crop_y"], t[i]["crop_w"], t[i]["crop_h"], t[i]["mirror"] = x1, y1, cw, ch, flag
+            exp.append(O.resample(resized.reshape(-1), t, crop, crop, T.FP32, T.NCHW, mul, add))
+        got = outs[0].cpu().numpy()
+        for i in range(n):
+            assert np.array_equal(got[i], exp[0][i]) or np.array_equal(got[i], exp[1][i]), names[i]
+    assert sorted(seen) == sorted(pixels)        # shuffled, every file once
+    pipe.rocal_release()
