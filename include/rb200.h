@@ -181,6 +181,27 @@ RB200_API rb200_tensor rb200_crop_mirror_normalize(rb200_context ctx, rb200_tens
 RB200_API rb200_tensor rb200_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200_param crop_width,
                                   rb200_param crop_height, rb200_param crop_pos_x, rb200_param crop_pos_y,
                                   int out_layout, int out_dtype);
+/* rocalRandomCrop, rocalCropResize, rocalCropResizeFixed, rocalROIResize (rocal_api_augmentation.h): windows of
+ * RocalRandomCropParam (up to five area / aspect draws for a window strictly inside the image, else the central crop
+ * clamped to aspect 0.75..1.333; parameter_random_crop.cpp:48-97) - cut out (RandomCrop) or stretched to
+ * dest_width x dest_height in the same launch (CropResize); ROIResize stretches the fixed window roi_w x roi_h at
+ * (roi_pos_x, roi_pos_y). Null parameters take the reference's default ranges. */
+/* [extension] Host only, no context: the random-area windows {x, y, w, h} for n images of wh[n][2] = {width, height},
+ * drawn from the given parameters in sample order (what rb200_random_crop / rb200_crop_resize do per batch). */
+RB200_API int rb200_random_area_windows(const unsigned* wh, size_t n, rb200_param area, rb200_param aspect_ratio,
+                                        rb200_param x_drift, rb200_param y_drift, unsigned* out_xywh);
+RB200_API rb200_tensor rb200_random_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200_param crop_area_factor,
+                                         rb200_param crop_aspect_ratio, rb200_param crop_pos_x, rb200_param crop_pos_y,
+                                         int num_of_attempts, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_crop_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                         int is_output, rb200_param area, rb200_param aspect_ratio, rb200_param x_center_drift,
+                                         rb200_param y_center_drift, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_crop_resize_fixed(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height,
+                                               int is_output, float area, float aspect_ratio, float x_center_drift,
+                                               float y_center_drift, int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_roi_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height, int is_output,
+                                        unsigned roi_h, unsigned roi_w, float roi_pos_x, float roi_pos_y, int interpolation,
+                                        int out_layout, int out_dtype);
 RB200_API rb200_tensor rb200_crop_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width, unsigned crop_height,
                                         int is_output, float crop_pos_x, float crop_pos_y, int out_layout,
                                         int out_dtype);

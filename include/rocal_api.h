@@ -315,6 +315,23 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCrop /* [952] */ (
     RocalFloatParam crop_height = NULL, RocalFloatParam crop_depth = NULL, RocalFloatParam crop_pox_x = NULL,
     RocalFloatParam crop_pos_y = NULL, RocalFloatParam crop_pos_z = NULL, RocalTensorLayout output_layout = ROCAL_NONE,
     RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCropResize /* [125] */ (
+    RocalContext context, RocalTensor input, unsigned dest_width, unsigned dest_height, bool is_output, RocalFloatParam area = NULL,
+    RocalFloatParam aspect_ratio = NULL, RocalFloatParam x_center_drift = NULL, RocalFloatParam y_center_drift = NULL,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCropResizeFixed /* [151] */ (
+    RocalContext context, RocalTensor input, unsigned dest_width, unsigned dest_height, bool is_output, float area,
+    float aspect_ratio, float x_center_drift, float y_center_drift, RocalTensorLayout output_layout = ROCAL_NONE,
+    RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalROIResize /* [175] */ (
+    RocalContext context, RocalTensor input, unsigned dest_width, unsigned dest_height, bool is_output, unsigned roi_h,
+    unsigned roi_w, float roi_pos_x = 0.0f, float roi_pos_y = 0.0f,
+    RocalResizeInterpolationType interpolation_type = ROCAL_LINEAR_INTERPOLATION, RocalTensorLayout output_layout = ROCAL_NONE,
+    RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalRandomCrop /* [1066] */ (
+    RocalContext context, RocalTensor input, bool is_output, RocalFloatParam crop_area_factor = NULL,
+    RocalFloatParam crop_aspect_ratio = NULL, RocalFloatParam crop_pos_x = NULL, RocalFloatParam crop_pos_y = NULL,
+    int num_of_attempts = 20, RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCropFixed /* [977] */ (
     RocalContext context, RocalTensor input, unsigned crop_width, unsigned crop_height, unsigned crop_depth,
     bool is_output, float crop_pox_x, float crop_pos_y, float crop_pos_z,

@@ -7,7 +7,7 @@ liboracle.so   the CPU restatement in oracle.c (gcc, -ffp-contract=off so that e
                rocAL/CMakeLists.txt:375).
 _ref/libref.so reference-owned CPU code compiled where it lies (never copied):
                rocAL/source/meta_data/bounding_box_graph.cpp, rocAL/source/parameters/
-               parameter_factory.cpp and parameter_random_crop_decoder.cpp + ref_driver.cpp, against
+               parameter_{factory,random_crop_decoder,crop,random_crop}.cpp + ref_driver.cpp, against
                the stand-in headers in ref_stubs/. Only built when REFERENCE_ROOT exists.
 """
 import os
@@ -53,6 +53,8 @@ def build_ref(force=False):
     srcs = [os.path.join(r, "source", "meta_data", "bounding_box_graph.cpp"),
             os.path.join(r, "source", "parameters", "parameter_factory.cpp"),
             os.path.join(r, "source", "parameters", "parameter_random_crop_decoder.cpp"),
+            os.path.join(r, "source", "parameters", "parameter_crop.cpp"),
+            os.path.join(r, "source", "parameters", "parameter_random_crop.cpp"),
             os.path.join(HERE, "ref_driver.cpp")]
     if force or _stale(REF_SO, srcs):
         os.makedirs(REF_DIR, exist_ok=True)

@@ -430,3 +430,88 @@ def ref_random_crop_windows(shapes_hw, aspect=(3.0 / 4, 4.0 / 3), area=(0.08, 1.
                                      ctypes.c_float(aspect[1]), ctypes.c_float(area[0]), ctypes.c_float(area[1]),
                                      ctypes.c_int(num_attempts), _ptr(out))
     return int(seed), out
+
+
+# ---- random-area crop windows of RandomCrop / CropResize -----------------------------------
+
+class _SingleValue:
+    """A single-value parameter (create_single_value_param): renew() changes nothing."""
+
+    def __init__(self, v):
+        self.v = np.float32(v)
+
+    def renew(self):
+        return self.v
+
+
+class _UniformOne:
+    """UniformRand<float> without an array: renew() draws one value (parameter_random.h:37-116)."""
+
+    def __init__(self, lo, hi, seed):
+        self._u = UniformRand(lo, hi, seed, 1)
+
+    def renew(self):
+        return np.float32(self._u.renew()[0])
+
+
+def random_area_window(w, h, area, aspect, x_drift, y_drift):
+    """RocalRandomCropParam::fill_crop_dims for one image (parameter_random_crop.cpp:48-97): up to five (area,
+    aspect) renewals for a window strictly smaller than the image, placed by x_drift and y_drift (the latter renewed
+    twice); else the central crop clamped to the aspect range 0.75 .. 1.333. Parameters are objects with renew()
+    returning the new float value. Returns (x, y, cw, ch)."""
+    f32 = np.float32
+    w, h = int(w), int(h)
+    lo, hi = f32(0.7500), f32(1.333)
+    cw = ch = 0
+    for _ in range(5):
+        a, r = area.renew(), aspect.renew()
+        target = float(f32(f32(a * f32(h)) * f32(w)))                 # float product, then held in a double
+        cw = int(np.sqrt(np.float64(target) * np.float64(r)))
+        ch = int(np.sqrt(np.float64(target) * np.float64(f32(f32(1) / r))))
+        if ch < h and cw < w:
+            xd = x_drift.renew()
+            y_drift.renew()
+            yd = y_drift.renew()
+            return (int(f32(xd * f32(w - cw))), int(f32(yd * f32(h - ch))), cw, ch)
+    ratio = f32(f32(w) / f32(h))
+    if ratio < lo:
+        cw = w
+        ch = int(f32(f32(cw) / lo))
+    elif ratio > hi:
+        ch = h
+        cw = int(f32(f32(ch) * hi))
+    else:
+        cw, ch = w, h
+    return ((w - cw) // 2, (h - ch) // 2, cw, ch)
+
+
+def random_area_windows(wh, fixed=None, seed=None, first_entry=0):
+    """Windows for a batch, in sample order. fixed = (area, aspect, x_drift, y_drift) single values, or seed = the
+    ParameterFactory seed whose table entries first_entry .. first_entry+3 start the default ranges of x_drift
+    (0.01..0.99), y_drift (0.01..0.99), area (0.08..0.99) and aspect (0.75..1.333), the order in which the class
+    creates them."""
+    wh = np.asarray(wh).reshape(-1, 2)
+    if fixed is not None:
+        area, aspect, xd, yd = [_SingleValue(v) for v in fixed]
+    else:
+        table = seed_sequence(int(seed), 1024)
+        e = [int(table[(first_entry + k) % 1024]) for k in range(4)]
+        xd = _UniformOne(0.01, 0.99, e[0])
+        yd = _UniformOne(0.01, 0.99, e[1])
+        area = _UniformOne(0.08, 0.99, e[2])
+        aspect = _UniformOne(0.7500, 1.333, e[3])
+    return np.array([random_area_window(w, h, area, aspect, xd, yd) for w, h in wh], dtype=np.uint32)
+
+
+def ref_random_area_windows(wh, fixed=None, seed=0):
+    """The reference build's windows, and the index of the first seed-table entry its parameters took."""
+    r = ref()
+    if r is None:
+        return None
+    wh = np.ascontiguousarray(np.asarray(wh, dtype=np.uint32).reshape(-1, 2))
+    out = np.zeros((len(wh), 4), dtype=np.uint32)
+    f4 = np.asarray(fixed if fixed is not None else (0, 0, 0, 0), dtype=np.float32)
+    r.ref_random_area_windows.restype = ctypes.c_uint
+    first = r.ref_random_area_windows(_ptr(wh), ctypes.c_int(len(wh)), ctypes.c_int(1 if fixed is not None else 0), _ptr(f4),
+                                      ctypes.c_uint(seed), _ptr(out))
+    return out, int(first)

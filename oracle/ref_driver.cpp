@@ -19,6 +19,9 @@
  *                           (rocAL/source/parameters/parameter_random_crop_decoder.cpp:41-108, compiled in place
  *                           with parameter_factory.cpp); the batch seed is the reference's own std::random_device
  *                           draw and is handed back so that a restatement can start from the same value
+ *   ref_random_area_windows -> RocalRandomCropParam::fill_crop_dims (rocAL/source/parameters/parameter_random_crop.cpp:48-97,
+ *                           compiled in place with parameter_crop.cpp) with fixed or default-range parameters; the OpenVX
+ *                           array calls of the class are answered by the do-nothing stand-ins at the end of this file
  */
 #include <cstdint>
 #include <memory>
@@ -28,6 +31,7 @@
 #include "meta_data/bounding_box_graph.h"
 #include "parameters/parameter_factory.h"
 #include "parameters/parameter_random.h"
+#include "parameters/parameter_random_crop.h"
 #include "parameters/parameter_random_crop_decoder.h"
 
 extern "C" {
@@ -143,4 +147,60 @@ __attribute__((visibility("default"))) unsigned ref_random_crop_windows(const in
     return batch_seed;
 }
 
+// wh: n x {width, height}; out_xywh: n x {x, y, w, h}. fixed != 0: the four values of `fixed4` = {area, aspect,
+// x_drift, y_drift} as single-value parameters; fixed == 0: ParameterFactory::set_seed(seed) and the class's own
+// default uniform ranges. Every construction of the class takes the next four entries of the seed table for x_drift,
+// y_drift, area and aspect in that order (set_seed does not rewind the table), so the index of the first entry this
+// call used is returned.
+namespace {
+struct RandomAreaProbe : public RocalRandomCropParam {
+    using RocalRandomCropParam::RocalRandomCropParam;
+    using RocalRandomCropParam::set_area_factor;
+    using RocalRandomCropParam::set_aspect_ratio;
+    using RocalRandomCropParam::fill_crop_dims;
+};
+}  // namespace
+
+__attribute__((visibility("default"))) unsigned ref_random_area_windows(const unsigned* wh, int n, int fixed, const float* fixed4,
+                                                                        unsigned seed, unsigned* out_xywh) {
+    static unsigned constructions = 0;
+    const unsigned first_entry = (constructions++ * 4u) % 1024u;
+    ParameterFactory* f = ParameterFactory::instance();
+    if (!fixed) f->set_seed(seed);
+    RandomAreaProbe p((unsigned)n);
+    if (fixed) {
+        p.set_area_factor(f->create_single_value_param(fixed4[0]));
+        p.set_aspect_ratio(f->create_single_value_param(fixed4[1]));
+        p.set_x_drift_factor(f->create_single_value_param(fixed4[2]));
+        p.set_y_drift_factor(f->create_single_value_param(fixed4[3]));
+    }
+    std::vector<Roi2DCords> rois(n);
+    for (int i = 0; i < n; i++) {
+        rois[i].xywh.x = 0;
+        rois[i].xywh.y = 0;
+        rois[i].xywh.w = wh[i * 2];
+        rois[i].xywh.h = wh[i * 2 + 1];
+    }
+    p.array_init();
+    p.set_image_dimensions(rois.data());
+    p.fill_crop_dims();
+    auto x1 = p.get_x1_arr_val(), y1 = p.get_y1_arr_val(), cw = p.get_cropw_arr_val(), ch = p.get_croph_arr_val();
+    for (int i = 0; i < n; i++) {
+        out_xywh[i * 4 + 0] = x1[i];
+        out_xywh[i * 4 + 1] = y1[i];
+        out_xywh[i * 4 + 2] = cw[i];
+        out_xywh[i * 4 + 3] = ch[i];
+    }
+    return first_entry;
+}
+
 }  // extern "C"
+
+// Stand-ins for the OpenVX array calls that the crop parameter classes make when they mirror their vectors into
+// vx_arrays (never reached by the entry points above, which read the vectors).
+extern "C" {
+vx_context vxGetContext(vx_reference) { return nullptr; }
+vx_array vxCreateArray(vx_context, vx_enum, vx_size) { return nullptr; }
+vx_status vxAddArrayItems(vx_array, vx_size, const void*, vx_size) { return 0; }
+vx_status vxCopyArrayRange(vx_array, vx_size, vx_size, vx_size, void*, vx_enum, vx_enum) { return 0; }
+}

@@ -92,6 +92,10 @@ crop_center_fixed = _proto("rb200_crop_center_fixed", _P, _P, _P, c_uint, c_uint
 resize_crop_mirror_fixed = _proto("rb200_resize_crop_mirror_fixed", _P, _P, _P, c_uint, c_uint, c_int, c_uint, c_uint,
                                   _P, c_int, c_int)
 resize_crop_mirror = _proto("rb200_resize_crop_mirror", _P, _P, _P, c_uint, c_uint, c_int, _P, _P, _P, c_int, c_int)
+random_area_windows = _proto("rb200_random_area_windows", c_int, POINTER(c_uint), c_size_t, _P, _P, _P, _P, POINTER(c_uint))
+random_crop = _proto("rb200_random_crop", _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int)
+crop_resize = _proto("rb200_crop_resize", _P, _P, _P, c_uint, c_uint, c_int, _P, _P, _P, _P, c_int, c_int)
+roi_resize = _proto("rb200_roi_resize", _P, _P, _P, c_uint, c_uint, c_int, c_uint, c_uint, c_float, c_float, c_int, c_int, c_int)
 ssd_random_crop = _proto("rb200_ssd_random_crop", _P, _P, _P, c_int, c_int, c_int, c_int)
 flip = _proto("rb200_flip", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 brightness = _proto("rb200_brightness", _P, _P, _P, c_int, _P, _P, c_int, c_int)

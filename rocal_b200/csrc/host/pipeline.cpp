@@ -97,7 +97,48 @@ void CropSpec::update(const std::vector<int>& in_w, const std::vector<int>& in_h
     chv.resize(n);
     for (size_t i = 0; i < n; i++) {
         unsigned w = (unsigned)in_w[i], h = (unsigned)in_h[i];
-        if (mode != RANDOM) {
+        if (mode == RANDOM_AREA) {
+            // up to five (area, aspect) draws for a window strictly smaller than the image, placed by the two
+            // drifts (the vertical one is renewed twice per success); otherwise the central crop clamped to
+            // the aspect range 0.75 .. 1.333
+            const float kAspectLo = 0.7500f, kAspectHi = 1.333f;
+            bool placed = false;
+            unsigned cw = 0, ch = 0;
+            for (int attempt = 0; attempt < 5 && !placed; attempt++) {
+                area->renew();
+                aspect->renew();
+                const float a = area->get(), r = aspect->get();
+                const double target = (double)(a * (float)h * (float)w);
+                cw = static_cast<unsigned>(static_cast<size_t>(std::sqrt(target * (double)r)));
+                ch = static_cast<unsigned>(static_cast<size_t>(std::sqrt(target * (double)(1 / r))));
+                if (ch < h && cw < w) {
+                    x_drift->renew();
+                    y_drift->renew();
+                    y_drift->renew();
+                    const float xd = x_drift->get(), yd = y_drift->get();
+                    x1v[i] = static_cast<unsigned>(static_cast<size_t>(xd * (float)(w - cw)));
+                    y1v[i] = static_cast<unsigned>(static_cast<size_t>(yd * (float)(h - ch)));
+                    placed = true;
+                }
+            }
+            if (!placed) {
+                const float in_ratio = (float)w / (float)h;
+                if (in_ratio < kAspectLo) {
+                    cw = w;
+                    ch = static_cast<unsigned>((float)cw / kAspectLo);
+                } else if (in_ratio > kAspectHi) {
+                    ch = h;
+                    cw = static_cast<unsigned>((float)ch * kAspectHi);
+                } else {
+                    ch = h;
+                    cw = w;
+                }
+                x1v[i] = (w - cw) / 2;
+                y1v[i] = (h - ch) / 2;
+            }
+            cwv[i] = cw;
+            chv[i] = ch;
+        } else if (mode != RANDOM) {
             cwv[i] = (crop_w <= w && crop_w > 0) ? crop_w : w;
             chv[i] = (crop_h <= h && crop_h > 0) ? crop_h : h;
             if (mode == FIXED_ANCHOR) {
@@ -1628,9 +1669,15 @@ void Pipeline::current_boxes(std::vector<float>& ltrb, std::vector<int>& labels,
 
 void Pipeline::crop_windows(TensorImpl* t, unsigned* xywh) {
     if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
-    if (!owns(t) || t->producer < 0 || _slots[_held].windows[t->producer].empty())
-        RB200_THROW("the tensor is not the output of a crop-type operator");
-    const auto& w = _slots[_held].windows[t->producer];
+    if (!owns(t) || t->producer < 0) RB200_THROW("the tensor is not the output of a crop-type operator");
+    int node = t->producer;
+    if (_slots[_held].windows[node].empty()) {
+        // CropResize / ROIResize: the window belongs to the internal crop node in front of the resize
+        TensorImpl* in = _tensors[_nodes[node].in].get();
+        if (in->producer >= 0 && !in->is_output && !_slots[_held].windows[in->producer].empty()) node = in->producer;
+    }
+    if (_slots[_held].windows[node].empty()) RB200_THROW("the tensor is not the output of a crop-type operator");
+    const auto& w = _slots[_held].windows[node];
     std::memcpy(xywh, w.data(), w.size() * sizeof(unsigned));
 }
 

@@ -38,12 +38,14 @@ enum class NodeKind {
     BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, WARP_AFFINE, ROTATE
 };
 
-// Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85).
+// Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85) and, for
+// RANDOM_AREA, of RocalRandomCropParam::fill_crop_dims (source/parameters/parameter_random_crop.cpp:48-97).
 struct CropSpec {
-    enum Mode { ABSOLUTE, FIXED_ANCHOR, RANDOM } mode = ABSOLUTE;
+    enum Mode { ABSOLUTE, FIXED_ANCHOR, RANDOM, RANDOM_AREA } mode = ABSOLUTE;
     unsigned crop_w = 0, crop_h = 0, x1 = 0, y1 = 0;
     float anchor_x = 0.5f, anchor_y = 0.5f;
     Parameter<float>*h_factor = nullptr, *w_factor = nullptr, *x_drift = nullptr, *y_drift = nullptr;
+    Parameter<float>*area = nullptr, *aspect = nullptr;   // RANDOM_AREA
     std::vector<float> next_anchor_x, next_anchor_y;   // per-sample anchors of the next batch (extension)
     std::vector<unsigned> x1v, y1v, cwv, chv;          // results of the current batch
     void update(const std::vector<int>& in_w, const std::vector<int>& in_h);

@@ -690,6 +690,107 @@ rb200_tensor rb200_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200
     API_END
 }
 
+namespace {
+// The random-area window of RocalRandomCropParam as an internal crop node in front of `consumer`.
+// Null handles become the class's default ranges, created in the class's order from the seed table
+// (include/parameters/parameter_crop.h:48-51, parameter_random_crop.h:30-33,42-43).
+Parameter<float>* table_float_param(rb200_param p, float lo, float hi) {
+    return p ? FP(p)->core : ParameterFactory::instance().create_uniform_float(lo, hi)->core;
+}
+void set_random_area(CropSpec& crop, rb200_param area, rb200_param aspect, rb200_param x_drift, rb200_param y_drift) {
+    crop.mode = CropSpec::RANDOM_AREA;
+    crop.x_drift = table_float_param(x_drift, 0.01f, 0.99f);
+    crop.y_drift = table_float_param(y_drift, 0.01f, 0.99f);
+    crop.area = table_float_param(area, 0.08f, 0.99f);
+    crop.aspect = table_float_param(aspect, 0.7500f, 1.333f);
+}
+}  // namespace
+
+rb200_tensor rb200_random_crop(rb200_context ctx, rb200_tensor in, int is_output, rb200_param crop_area_factor,
+                               rb200_param crop_aspect_ratio, rb200_param crop_pos_x, rb200_param crop_pos_y, int num_of_attempts,
+                               int out_layout, int out_dtype) {
+    API_BEGIN
+    (void)num_of_attempts;   // the reference's window rule always makes five attempts (parameter_random_crop.cpp:52)
+    Node nd;
+    nd.kind = NodeKind::CROP;
+    set_random_area(nd.crop, crop_area_factor, crop_aspect_ratio, crop_pos_x, crop_pos_y);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+int rb200_random_area_windows(const unsigned* wh, size_t n, rb200_param area, rb200_param aspect_ratio, rb200_param x_drift,
+                              rb200_param y_drift, unsigned* out_xywh) {
+    try {
+        if (n && (!wh || !out_xywh)) return ROCAL_INVALID_PARAMETER_TYPE;
+        CropSpec crop;
+        set_random_area(crop, area, aspect_ratio, x_drift, y_drift);
+        std::vector<int> w(n), h(n);
+        for (size_t i = 0; i < n; i++) {
+            w[i] = (int)wh[i * 2];
+            h[i] = (int)wh[i * 2 + 1];
+        }
+        crop.update(w, h);
+        for (size_t i = 0; i < n; i++) {
+            out_xywh[i * 4] = crop.x1v[i];
+            out_xywh[i * 4 + 1] = crop.y1v[i];
+            out_xywh[i * 4 + 2] = crop.cwv[i];
+            out_xywh[i * 4 + 3] = crop.chv[i];
+        }
+    } catch (const std::exception&) {
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+rb200_tensor rb200_crop_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height, int is_output,
+                               rb200_param area, rb200_param aspect_ratio, rb200_param x_center_drift, rb200_param y_center_drift,
+                               int out_layout, int out_dtype) {
+    API_BEGIN
+    if (dest_width == 0 || dest_height == 0) RB200_THROW("CropResize node needs tp receive non-zero destination dimensions");
+    Node window;
+    window.kind = NodeKind::CROP;
+    set_random_area(window.crop, area, aspect_ratio, x_center_drift, y_center_drift);
+    TensorImpl* cut = p->add_node(std::move(window), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, ROCAL_NHWC, ROCAL_UINT8, false);
+    Node nd;
+    nd.kind = NodeKind::RESIZE;
+    nd.dest_w = dest_width;
+    nd.dest_h = dest_height;
+    nd.scaling_mode = ROCAL_SCALING_MODE_STRETCH;
+    return finish(p, std::move(nd), cut, dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_crop_resize_fixed(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height, int is_output,
+                                     float area, float aspect_ratio, float x_center_drift, float y_center_drift, int out_layout,
+                                     int out_dtype) {
+    ParameterFactory& f = ParameterFactory::instance();
+    return rb200_crop_resize(ctx, in, dest_width, dest_height, is_output, f.create_float(area), f.create_float(aspect_ratio),
+                             f.create_float(x_center_drift), f.create_float(y_center_drift), out_layout, out_dtype);
+}
+
+rb200_tensor rb200_roi_resize(rb200_context ctx, rb200_tensor in, unsigned dest_width, unsigned dest_height, int is_output,
+                              unsigned roi_h, unsigned roi_w, float roi_pos_x, float roi_pos_y, int interpolation, int out_layout,
+                              int out_dtype) {
+    API_BEGIN
+    if (dest_width == 0 || dest_height == 0) RB200_THROW("ROI Resize needs to receive non-zero destination dimensions");
+    Node window;
+    window.kind = NodeKind::CROP;
+    window.crop.mode = CropSpec::ABSOLUTE;
+    window.crop.crop_w = roi_w;
+    window.crop.crop_h = roi_h;
+    window.crop.x1 = (unsigned)roi_pos_x;     // the reference stores the two floats in unsigned fields
+    window.crop.y1 = (unsigned)roi_pos_y;
+    TensorImpl* cut = p->add_node(std::move(window), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, ROCAL_NHWC, ROCAL_UINT8, false);
+    Node nd;
+    nd.kind = NodeKind::RESIZE;
+    nd.interpolation = resize_interpolation(interpolation);
+    nd.dest_w = dest_width;
+    nd.dest_h = dest_height;
+    nd.scaling_mode = ROCAL_SCALING_MODE_STRETCH;
+    return finish(p, std::move(nd), cut, dest_width, dest_height, out_layout, out_dtype, is_output);
+    API_END
+}
+
 rb200_tensor rb200_crop_fixed(rb200_context ctx, rb200_tensor in, unsigned crop_width, unsigned crop_height, int is_output,
                               float crop_pos_x, float crop_pos_y, int out_layout, int out_dtype) {
     API_BEGIN

@@ -276,6 +276,25 @@ RocalTensor ROCAL_API_CALL rocalCrop(RocalContext c, RocalTensor in, bool out, R
                                      RocalFloatParam px, RocalFloatParam py, RocalFloatParam, RocalTensorLayout l, RocalTensorOutputType t) {
     return RT(rb200_crop(c, in, out, cw, ch, px, py, (int)l, (int)t));
 }
+RocalTensor ROCAL_API_CALL rocalCropResize(RocalContext c, RocalTensor in, unsigned dw, unsigned dh, bool out, RocalFloatParam area,
+                                           RocalFloatParam aspect, RocalFloatParam xd, RocalFloatParam yd, RocalTensorLayout l,
+                                           RocalTensorOutputType t) {
+    return RT(rb200_crop_resize(c, in, dw, dh, out, area, aspect, xd, yd, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalCropResizeFixed(RocalContext c, RocalTensor in, unsigned dw, unsigned dh, bool out, float area,
+                                                float aspect, float xd, float yd, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_crop_resize_fixed(c, in, dw, dh, out, area, aspect, xd, yd, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalROIResize(RocalContext c, RocalTensor in, unsigned dw, unsigned dh, bool out, unsigned roi_h,
+                                          unsigned roi_w, float px, float py, RocalResizeInterpolationType interp, RocalTensorLayout l,
+                                          RocalTensorOutputType t) {
+    return RT(rb200_roi_resize(c, in, dw, dh, out, roi_h, roi_w, px, py, (int)interp, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalRandomCrop(RocalContext c, RocalTensor in, bool out, RocalFloatParam area, RocalFloatParam aspect,
+                                           RocalFloatParam px, RocalFloatParam py, int attempts, RocalTensorLayout l,
+                                           RocalTensorOutputType t) {
+    return RT(rb200_random_crop(c, in, out, area, aspect, px, py, attempts, (int)l, (int)t));
+}
 RocalTensor ROCAL_API_CALL rocalCropFixed(RocalContext c, RocalTensor in, unsigned cw, unsigned ch, unsigned cd, bool out, float px, float py,
                                           float, RocalTensorLayout l, RocalTensorOutputType t) {
     if (cd == 0) {

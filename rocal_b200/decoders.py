@@ -33,6 +33,7 @@ def image(*inputs, user_feature_key_map=None, path='', file_root='', annotations
         raise RuntimeError(p.error_message())
     p._max_w, p._max_h = max_decoded_width, max_decoded_height
     p._has_file_source = True
+    p._last_batch_policy = last_batch_policy
     return h
 
 
@@ -56,6 +57,7 @@ def _fused_crop(name, file_root, path, shard_id, num_shards, random_shuffle, ran
         raise RuntimeError(p.error_message())
     p._max_w, p._max_h = max_decoded_width, max_decoded_height
     p._has_file_source = True
+    p._last_batch_policy = last_batch_policy
     return h
 
 

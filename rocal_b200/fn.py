@@ -106,6 +106,61 @@ def center_crop(*inputs, crop=[0, 0], crop_h=0, crop_w=0, crop_d=1, device=None,
     return _ret(p, C.crop_center_fixed(p._handle, inputs[0], crop_w, crop_h, 0, output_layout, output_dtype))
 
 
+def centre_crop(*inputs, **kwargs):
+    """fn.py: the British spelling the reference also exports."""
+    return center_crop(*inputs, **kwargs)
+
+
+def random_crop(*inputs, crop_area_factor=None, crop_aspect_ratio=None, crop_pox_x=None, crop_pox_y=None, num_attempts=20,
+                device=None, all_boxes_above_threshold=True, allow_no_crop=True, ltrb=True, output_layout=types.NHWC,
+                output_dtype=types.UINT8):
+    """rocalRandomCrop: a window of random area and aspect ratio (floats, fn.random.uniform parameters, or None for
+    the reference's default ranges 0.08..0.99 and 0.75..1.333)."""
+    p = _pipe()
+    return _ret(p, C.random_crop(p._handle, inputs[0], 0, _fparam(crop_area_factor), _fparam(crop_aspect_ratio),
+                                 _fparam(crop_pox_x), _fparam(crop_pox_y), num_attempts, output_layout, output_dtype))
+
+
+def resize_crop(*inputs, resize_width=0, resize_height=0, crop_area_factor=None, crop_aspect_ratio=None, x_drift=None,
+                y_drift=None, device=None, max_size=[], resize_longer=0, resize_shorter=0,
+                scaling_mode=types.SCALING_MODE_DEFAULT, interpolation_type=types.LINEAR_INTERPOLATION,
+                output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalCropResize: the random window of random_crop stretched to resize_width x resize_height (one launch)."""
+    p = _pipe()
+    return _ret(p, C.crop_resize(p._handle, inputs[0], resize_width, resize_height, 0, _fparam(crop_area_factor),
+                                 _fparam(crop_aspect_ratio), _fparam(x_drift), _fparam(y_drift), output_layout, output_dtype))
+
+
+def roi_resize(*inputs, resize_width=0, resize_height=0, roi_w=None, roi_h=None, roi_pos_x=None, roi_pos_y=None, device=None,
+               interpolation_type=types.LINEAR_INTERPOLATION, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalROIResize: the window roi_w x roi_h at pixel (roi_pos_x, roi_pos_y) stretched to resize_width x resize_height."""
+    p = _pipe()
+    return _ret(p, C.roi_resize(p._handle, inputs[0], resize_width, resize_height, 0, int(roi_h or 0), int(roi_w or 0),
+                                float(roi_pos_x or 0), float(roi_pos_y or 0), interpolation_type, output_layout, output_dtype))
+
+
+def one_hot(*inputs, num_classes=0, device=None):
+    """fn.py:943: asks the classification iterator for one-hot labels with num_classes columns."""
+    p = _pipe()
+    p._num_classes = num_classes
+    p._one_hot_encoding = True
+    return []
+
+
+def uniform(*inputs, range=(-1.0, 1.0), device=None):
+    """fn.py:888: per-sample float, uniform in range (the same parameter as fn.random.uniform)."""
+    return random.uniform(*inputs, range=range, device=device)
+
+
+def nop(*inputs, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalNop / rocalCopy: the input unchanged (a copy into the operator's own output tensor)."""
+    p = _pipe()
+    return _ret(p, C.flip(p._handle, inputs[0], 0, _iparam(0), _iparam(0), output_layout, output_dtype))
+
+
+copy = nop
+
+
 def resize_crop_mirror(*inputs, resize_width=0, resize_height=0, crop_w=0, crop_h=0, mirror=1, device=None, max_size=[],
                        resize_longer=0, resize_shorter=0, scaling_mode=types.SCALING_MODE_DEFAULT,
                        interpolation_type=types.LINEAR_INTERPOLATION, output_layout=types.NHWC, output_dtype=types.UINT8):

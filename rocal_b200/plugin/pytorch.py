@@ -34,8 +34,9 @@ class ROCALGenericIterator(object):
 
 class ROCALClassificationIterator(ROCALGenericIterator):
     """Yields ([outputs...], labels) for a pipeline with a file source (plugin/pytorch.py:246-294 of the reference):
-    labels are an int32 CUDA tensor of the batch's class indices. Iteration stops when the source is exhausted;
-    reset() starts the next epoch."""
+    labels are an int32 CUDA tensor of the batch's class indices, or - after fn.one_hot(num_classes=k) - an int32
+    [N, k] one-hot tensor filled on the device. With LAST_BATCH_PARTIAL the padding samples of the last batch are
+    cut off. Iteration stops when the source is exhausted; reset() starts the next epoch."""
 
     def __next__(self):
         if self.loader.is_empty():
@@ -44,7 +45,15 @@ class ROCALClassificationIterator(ROCALGenericIterator):
         outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
         if self.copy:
             outs = [o.clone() for o in outs]
-        labels = torch.from_numpy(self.loader.get_image_labels()).to(outs[0].device)
+        if getattr(self.loader, "_one_hot_encoding", False):
+            labels = self.loader.get_one_hot_encoded_labels(self.loader._num_classes, device=outs[0].device)
+        else:
+            labels = torch.from_numpy(self.loader.get_image_labels()).to(outs[0].device)
+        from .. import types
+        if getattr(self.loader, "_last_batch_policy", None) == types.LAST_BATCH_PARTIAL:
+            valid = self.loader._batch_size - self.loader.get_last_batch_padded_size()
+            if valid < self.loader._batch_size:
+                return [o[:valid] for o in outs], labels[:valid]
         return outs, labels
 
     next = __next__

@@ -2,7 +2,7 @@
 the reference tree by oracle/build.py). Run in a container that has the reference tree:
 
     python tests/golden/make_golden.py                  # every file
-    python tests/golden/make_golden.py random_crop      # random_crop_windows.npz only
+    python tests/golden/make_golden.py random_crop      # random_crop_windows.npz and random_area_windows.npz only
 
 box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
                   (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
@@ -14,6 +14,9 @@ param_rng.npz     UniformRand<float>, UniformRand<int>, CustomRand<int> draws
 random_crop_windows.npz   RocalRandomCropDecParam windows (rocAL/source/parameters/parameter_random_crop_decoder.cpp)
                   for eight batches of 96 image shapes (ordinary, very wide, very tall, tiny; one or many attempts):
                   the batch seed the reference's std::random_device drew, the shapes, the ranges and the windows
+random_area_windows.npz   RocalRandomCropParam::fill_crop_dims windows (rocAL/source/parameters/parameter_random_crop.cpp:48-97,
+                  the rule of rocalRandomCrop / rocalCropResize) for fixed parameter values and for the class's default
+                  ranges under a ParameterFactory seed (with the index of the first seed-table entry the class took)
 """
 import ctypes
 import os
@@ -50,6 +53,31 @@ def random_crop():
         out["seed_%d" % k] = np.array([seed], dtype=np.uint32)
     np.savez_compressed(os.path.join(HERE, "random_crop_windows.npz"), **out)
     print("wrote random_crop_windows.npz")
+
+
+def random_area():
+    assert O.ref() is not None, "the reference tree is needed to generate golden vectors"
+    rng = np.random.Generator(np.random.PCG64(778))
+    out = {}
+    for k in range(10):
+        n = 64
+        wh = np.stack([rng.integers(1, 1200, n), rng.integers(1, 1200, n)], axis=1).astype(np.uint32)
+        if k % 5 == 1:
+            wh[:, 0] = rng.integers(1, 24, n)
+        if k % 5 == 2:
+            wh[:, 1] = rng.integers(1, 24, n)
+        out["wh_%d" % k] = wh
+        if k % 2:
+            fixed = np.array([rng.uniform(0.05, 1.3), rng.uniform(0.5, 2.0), rng.uniform(0, 1), rng.uniform(0, 1)], dtype=np.float32)
+            win, _ = O.ref_random_area_windows(wh, fixed=fixed)
+            out["fixed_%d" % k] = fixed
+        else:
+            seed = int(rng.integers(0, 2 ** 31))
+            win, first = O.ref_random_area_windows(wh, seed=seed)
+            out["seed_%d" % k] = np.array([seed, first], dtype=np.int64)
+        out["windows_%d" % k] = win
+    np.savez_compressed(os.path.join(HERE, "random_area_windows.npz"), **out)
+    print("wrote random_area_windows.npz")
 
 
 def main():
@@ -136,6 +164,8 @@ def main():
 if __name__ == "__main__":
     if sys.argv[1:] == ["random_crop"]:
         random_crop()
+        random_area()
     else:
         main()
         random_crop()
+        random_area()

@@ -727,3 +727,92 @@ def test_fused_jpeg_crop_file_source(cuda, tmp_path):
             assert np.array_equal(got[i], exp[0][i]) or np.array_equal(got[i], exp[1][i]), names[i]
     assert sorted(seen) == sorted(pixels)        # shuffled, every file once
     pipe.rocal_release()
+
+
+def test_random_crop_crop_resize_roi_resize(cuda):
+    """rocalRandomCrop, rocalCropResize, rocalROIResize and rocalNop on raw pixels. With fixed parameter values the
+    windows are the restated rule's; with the default random ranges they are read back. Pixels equal the oracle:
+    RandomCrop = the window copied, CropResize / ROIResize = the window stretched by the resize kernel."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(41)
+    n = 8
+    fixed = (0.45, 1.2, 0.3, 0.8)
+    pipe = Pipeline(batch_size=n, device_id=0, seed=21)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=400, max_height=400)
+        rc = fn.random_crop(img, crop_area_factor=fixed[0], crop_aspect_ratio=fixed[1], crop_pox_x=fixed[2], crop_pox_y=fixed[3])
+        cr_fixed = fn.resize_crop(img, resize_width=96, resize_height=64, crop_area_factor=fixed[0], crop_aspect_ratio=fixed[1],
+                                  x_drift=fixed[2], y_drift=fixed[3])
+        cr_rand = fn.resize_crop(img, resize_width=80, resize_height=80, output_layout=types.NCHW, output_dtype=types.FLOAT)
+        roi = fn.roi_resize(img, resize_width=72, resize_height=56, roi_w=120, roi_h=90, roi_pos_x=17, roi_pos_y=9,
+                            interpolation_type=types.TRIANGULAR_INTERPOLATION)
+        same = fn.nop(img)
+        pipe.set_outputs(rc, cr_fixed, cr_rand, roi, same)
+    pipe.build()
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (130, 400), (130, 400))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        o_rc, o_fixed, o_rand, o_roi, o_same = [t.numpy() for t in pipe.get_output_tensors()]
+        wh = np.stack([ws, hs], axis=1)
+        exp_win = O.random_area_windows(wh, fixed=fixed)
+        for t in (rc, cr_fixed):
+            assert np.array_equal(pipe.get_crop_windows(t), exp_win)
+        win_rand = pipe.get_crop_windows(cr_rand)
+        assert (win_rand[:, 0] + win_rand[:, 2] <= ws).all() and (win_rand[:, 1] + win_rand[:, 3] <= hs).all()
+        ratio = win_rand[:, 2] / win_rand[:, 3]
+        assert (ratio > 0.6).all() and (ratio < 1.6).all()
+        win_roi = pipe.get_crop_windows(roi)
+        assert win_roi.tolist() == [[17, 9, 120, 90]] * n
+
+        def stretched(win, w, h, dtype, layout, interpolation=0):
+            tab = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+            tab["src_offset"], tab["src_stride"] = offs, ws * 3
+            tab["roi_x"], tab["roi_y"], tab["roi_w"], tab["roi_h"] = win[:, 0], win[:, 1], win[:, 2], win[:, 3]
+            tab["dst_w"], tab["dst_h"], tab["crop_w"], tab["crop_h"] = w, h, w, h
+            return O.resample(arena, tab, w, h, dtype, layout, interpolation=interpolation)
+
+        assert np.array_equal(o_fixed, stretched(exp_win, 96, 64, T.UINT8, T.NHWC))
+        assert np.array_equal(o_rand, stretched(win_rand, 80, 80, T.FP32, T.NCHW))
+        assert np.array_equal(o_roi, stretched(win_roi, 72, 56, T.UINT8, T.NHWC, 1))
+        for i in range(n):
+            ih, iw, o = int(hs[i]), int(ws[i]), int(offs[i])
+            im = arena[o:o + ih * iw * 3].reshape(ih, iw, 3)
+            x, y, w, h = [int(v) for v in exp_win[i]]
+            assert np.array_equal(o_rc[i, :h, :w], im[y:y + h, x:x + w])
+            assert np.array_equal(o_same[i, :ih, :iw], im)
+        assert pipe.get_output_tensors()[0].roi()[:, 2:].tolist() == exp_win[:, 2:].tolist()
+    pipe.rocal_release()
+
+
+def test_one_hot_and_partial_last_batch_iterator(cuda, tmp_path):
+    """fn.one_hot makes ROCALClassificationIterator yield one-hot labels; LAST_BATCH_PARTIAL cuts the padding off
+    the last batch (plugin/pytorch.py:198-231 of the reference)."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    from rocal_b200.plugin.pytorch import ROCALClassificationIterator
+    rng = S.rng_for(42)
+    imgs, streams = _jpeg_batch(rng, 5, (64, 128))
+    classes = ["a", "a", "b", "c", "c"]
+    for i, (cls, sb) in enumerate(zip(classes, streams)):
+        d = tmp_path / cls
+        d.mkdir(exist_ok=True)
+        (d / ("im%d.jpg" % i)).write_bytes(sb)
+    pipe = Pipeline(batch_size=2, device_id=0, seed=2)
+    with pipe:
+        jpegs, labels = fn.readers.file(file_root=str(tmp_path))
+        fn.one_hot(labels, num_classes=3)
+        dec = fn.decoders.image(jpegs, file_root=str(tmp_path), max_decoded_width=128, max_decoded_height=128,
+                                last_batch_policy=types.LAST_BATCH_PARTIAL, pad_last_batch=True)
+        pipe.set_outputs(fn.centre_crop(dec, crop=[32, 32]))
+    pipe.build()
+    sizes, hots = [], []
+    for outs, labs in ROCALClassificationIterator(pipe):
+        sizes.append(outs[0].shape[0])
+        assert labs.shape == (outs[0].shape[0], 3) and labs.is_cuda
+        hots += labs.cpu().tolist()
+    assert sizes == [2, 2, 1]
+    # label k > 0 -> column k-1, label 0 -> last column (rocalGetOneHotImageLabels)
+    assert hots == [[0, 0, 1], [0, 0, 1], [1, 0, 0], [0, 1, 0], [0, 1, 0]]
+    pipe.rocal_release()
