@@ -315,6 +315,9 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCrop /* [952] */ (
     RocalFloatParam crop_height = NULL, RocalFloatParam crop_depth = NULL, RocalFloatParam crop_pox_x = NULL,
     RocalFloatParam crop_pos_y = NULL, RocalFloatParam crop_pos_z = NULL, RocalTensorLayout output_layout = ROCAL_NONE,
     RocalTensorOutputType output_datatype = ROCAL_UINT8);
+/* The input unchanged, in the operator's own output tensor (same layout and type as the input). */
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCopy /* [854] */ (RocalContext context, RocalTensor input, bool is_output);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalNop /* [863] */ (RocalContext context, RocalTensor input, bool is_output);
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalCropResize /* [125] */ (
     RocalContext context, RocalTensor input, unsigned dest_width, unsigned dest_height, bool is_output, RocalFloatParam area = NULL,
     RocalFloatParam aspect_ratio = NULL, RocalFloatParam x_center_drift = NULL, RocalFloatParam y_center_drift = NULL,

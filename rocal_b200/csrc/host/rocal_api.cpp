@@ -276,6 +276,10 @@ RocalTensor ROCAL_API_CALL rocalCrop(RocalContext c, RocalTensor in, bool out, R
                                      RocalFloatParam px, RocalFloatParam py, RocalFloatParam, RocalTensorLayout l, RocalTensorOutputType t) {
     return RT(rb200_crop(c, in, out, cw, ch, px, py, (int)l, (int)t));
 }
+RocalTensor ROCAL_API_CALL rocalCopy(RocalContext c, RocalTensor in, bool out) {
+    return RT(rb200_flip(c, in, out, rb200_create_int_parameter(0), rb200_create_int_parameter(0), (int)ROCAL_NONE, (int)ROCAL_UINT8));
+}
+RocalTensor ROCAL_API_CALL rocalNop(RocalContext c, RocalTensor in, bool out) { return rocalCopy(c, in, out); }
 RocalTensor ROCAL_API_CALL rocalCropResize(RocalContext c, RocalTensor in, unsigned dw, unsigned dh, bool out, RocalFloatParam area,
                                            RocalFloatParam aspect, RocalFloatParam xd, RocalFloatParam yd, RocalTensorLayout l,
                                            RocalTensorOutputType t) {
