@@ -746,6 +746,126 @@ __device__ __forceinline__ float tri_coeff(const TriAxis& a, float weight, int j
     return c < 0.f ? 0.f : c;
 }
 
+// Accumulates the KX taps of one source row. The column coefficients and (for threads at the image border) the
+// clamped byte offsets do not depend on the row, so they live in registers.
+//
+// INTERIOR (every tap inside the ROI): the taps are 3*KX contiguous bytes. They are fetched as the aligned 32-bit
+// words that contain them (each word holds at least one needed byte, so no load leaves the mapped page of the last
+// pixel), brought to byte 0 by funnel shifts, and turned into floats by PRMT into the mantissa of 2^23 plus one
+// packed subtraction per two bytes - no byte loads and no integer-to-float conversion unit, which were the two
+// busiest units of the byte-wise version. Border threads keep byte loads with the same conversion.
+template <int KX, bool INTERIOR>
+__device__ __forceinline__ void tri_row(const uint8_t* __restrict__ r, const float (&cc)[KX], const int (&coff)[KX], float rc,
+                                        float& acc0, float& acc1, float& acc2) {
+    if (INTERIOR) {
+        constexpr int NB = 3 * KX;               // bytes of the taps
+        constexpr int NV = (NB + 3) / 4;         // aligned words after the shift
+        constexpr int NW = (NB + 3 + 3) / 4;     // words to fetch when the first byte sits at offset 3
+        const unsigned sb = (unsigned)(reinterpret_cast<uintptr_t>(r) & 3u);
+        const uint32_t* ab = reinterpret_cast<const uint32_t*>(r - sb);
+        uint32_t w[NW + 1];
+#pragma unroll
+        for (int i = 0; i < NW; i++) w[i] = (4 * i < (int)sb + NB) ? __ldg(ab + i) : 0u;
+        w[NW] = 0u;
+        uint32_t v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; i++) v[i] = __funnelshift_r(w[i], w[i + 1], sb * 8);
+        float x[NB + 1];
+#pragma unroll
+        for (int t = 0; t < NB; t += 2) {
+            float2 p;
+            p.x = __uint_as_float(__byte_perm(v[t / 4], 0x4B000000u, 0x7650u + (t % 4)));
+            p.y = t + 1 < NB ? __uint_as_float(__byte_perm(v[(t + 1) / 4], 0x4B000000u, 0x7650u + ((t + 1) % 4))) : 8388608.0f;
+            p = add2(p, make_float2(-8388608.0f, -8388608.0f));
+            x[t] = p.x;
+            x[t + 1] = p.y;
+        }
+#pragma unroll
+        for (int k = 0; k < KX; k++) {
+            const float coeff = mul_rn(cc[k], rc);
+            acc0 = fmaf(x[3 * k], coeff, acc0);
+            acc1 = fmaf(x[3 * k + 1], coeff, acc1);
+            acc2 = fmaf(x[3 * k + 2], coeff, acc2);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < KX; k++) {
+            const uint8_t* px = r + coff[k];
+            const float coeff = mul_rn(cc[k], rc);
+            acc0 = fmaf(sub_rn(__uint_as_float(0x4B000000u | __ldg(px)), 8388608.0f), coeff, acc0);
+            acc1 = fmaf(sub_rn(__uint_as_float(0x4B000000u | __ldg(px + 1)), 8388608.0f), coeff, acc1);
+            acc2 = fmaf(sub_rn(__uint_as_float(0x4B000000u | __ldg(px + 2)), 8388608.0f), coeff, acc2);
+        }
+    }
+}
+
+// All output rows of one thread for a column filter of exactly KX taps (KX = 0: any tap count, nothing hoisted).
+template <typename OutT, int LAYOUT, int KX>
+__device__ __forceinline__ void tri_column(const uint8_t* __restrict__ img, const rb200_resample_sample& s, const ResampleLaunch& L,
+                                           OutT* out, int n, int xi, int tile_y0, int rows_valid, const TriAxis& ax,
+                                           const TriAxis& ay, float ratio_w, float ratio_h) {
+    const int x_lo = s.roi_x, y_lo = s.roi_y;
+    const int x_hi = s.roi_x + s.roi_w - 1, y_hi = s.roi_y + s.roi_h - 1;
+    const int rx = s.crop_x + (s.mirror ? (s.crop_w - 1 - xi) : xi);
+    int fx;
+    float wx;
+    tri_loc(ax, ratio_w, rx, x_lo, x_hi, fx, wx);
+    constexpr int KA = KX > 0 ? KX : 1;
+    float cc[KA];
+    int coff[KA];
+    float col_sum_fixed = 0.f;
+    bool interior = false;
+    if (KX > 0) {
+#pragma unroll
+        for (int k = 0; k < KA; k++) {
+            cc[k] = tri_coeff(ax, wx, k);
+            col_sum_fixed = add_rn(col_sum_fixed, cc[k]);
+            coff[k] = min(max(fx + k, x_lo), x_hi) * 3;
+        }
+        interior = fx >= x_lo && fx + KX - 1 <= x_hi;
+    }
+    for (int j0 = 0; j0 < rows_valid; j0++) {
+        int fy;
+        float wy;
+        tri_loc(ay, ratio_h, s.crop_y + tile_y0 + j0, y_lo, y_hi, fy, wy);
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, row_sum = 0.f, col_sum = col_sum_fixed;
+        for (int j = 0; j < ay.ksize; j++) {
+            const int row = min(max(fy + j, y_lo), y_hi);
+            const uint8_t* r = img + (size_t)row * s.src_stride;
+            const float rc = tri_coeff(ay, wy, j);
+            row_sum = add_rn(row_sum, rc);
+            if (KX > 0) {
+                if (interior)
+                    tri_row<KA, true>(r + fx * 3, cc, coff, rc, acc0, acc1, acc2);
+                else
+                    tri_row<KA, false>(r, cc, coff, rc, acc0, acc1, acc2);
+            } else {
+                col_sum = 0.f;
+                for (int k = 0; k < ax.ksize; k++) {
+                    const int col = min(max(fx + k, x_lo), x_hi);
+                    const float c1 = tri_coeff(ax, wx, k);
+                    col_sum = add_rn(col_sum, c1);
+                    const float coeff = mul_rn(c1, rc);
+                    const uint8_t* px = r + col * 3;
+                    acc0 = fmaf((float)__ldg(px), coeff, acc0);
+                    acc1 = fmaf((float)__ldg(px + 1), coeff, acc1);
+                    acc2 = fmaf((float)__ldg(px + 2), coeff, acc2);
+                }
+            }
+        }
+        if (row_sum == 0.f) row_sum = 1.f;
+        if (col_sum == 0.f) col_sum = 1.f;
+        const float inv = div_rn(1.0f, mul_rn(row_sum, col_sum));
+        float v[3] = {mul_rn(acc0, inv), mul_rn(acc1, inv), mul_rn(acc2, inv)};
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            v[c] = truncf(fmaxf(fminf(v[c], 255.f), 0.f));     // fmaxf sends NaN to 0
+            if (L.normalize) v[c] = fmaf(v[c], L.mul[c], L.add[c]);
+        }
+        store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, tile_y0 + j0, xi, v[0], v[1], v[2]);
+    }
+}
+
 template <typename OutT, int LAYOUT>
 __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t* __restrict__ arena,
                                                                   const rb200_resample_sample* __restrict__ samples,
@@ -767,44 +887,14 @@ __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t*
         const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
         const float ratio_h = div_rn((float)s.roi_h, (float)s.dst_h);
         const TriAxis ax = tri_axis_make(ratio_w), ay = tri_axis_make(ratio_h);
-        const int x_lo = s.roi_x, y_lo = s.roi_y;
-        const int x_hi = s.roi_x + s.roi_w - 1, y_hi = s.roi_y + s.roi_h - 1;
-        const int rx = s.crop_x + (s.mirror ? (s.crop_w - 1 - xi) : xi);
-        int fx;
-        float wx;
-        tri_loc(ax, ratio_w, rx, x_lo, x_hi, fx, wx);
-        for (int j0 = 0; j0 < rows_valid; j0++) {
-            int fy;
-            float wy;
-            tri_loc(ay, ratio_h, s.crop_y + tile_y0 + j0, y_lo, y_hi, fy, wy);
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, row_sum = 0.f, col_sum = 0.f;
-            for (int j = 0; j < ay.ksize; j++) {
-                const int row = min(max(fy + j, y_lo), y_hi);
-                const uint8_t* r = img + (size_t)row * s.src_stride;
-                const float rc = tri_coeff(ay, wy, j);
-                row_sum = add_rn(row_sum, rc);
-                col_sum = 0.f;
-                for (int k = 0; k < ax.ksize; k++) {
-                    const int col = min(max(fx + k, x_lo), x_hi);
-                    const float cc = tri_coeff(ax, wx, k);
-                    col_sum = add_rn(col_sum, cc);
-                    const float coeff = mul_rn(cc, rc);
-                    const uint8_t* px = r + col * 3;
-                    acc0 = fmaf((float)__ldg(px), coeff, acc0);
-                    acc1 = fmaf((float)__ldg(px + 1), coeff, acc1);
-                    acc2 = fmaf((float)__ldg(px + 2), coeff, acc2);
-                }
-            }
-            if (row_sum == 0.f) row_sum = 1.f;
-            if (col_sum == 0.f) col_sum = 1.f;
-            const float inv = div_rn(1.0f, mul_rn(row_sum, col_sum));
-            float v[3] = {mul_rn(acc0, inv), mul_rn(acc1, inv), mul_rn(acc2, inv)};
-#pragma unroll
-            for (int c = 0; c < 3; c++) {
-                v[c] = truncf(fmaxf(fminf(v[c], 255.f), 0.f));     // fmaxf sends NaN to 0
-                if (L.normalize) v[c] = fmaf(v[c], L.mul[c], L.add[c]);
-            }
-            store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, tile_y0 + j0, xi, v[0], v[1], v[2]);
+        // the tap count is the same for the whole sample, so this switch does not diverge
+        switch (ax.ksize) {
+#define RB200_TRI_CASE(K) \
+    case K: tri_column<OutT, LAYOUT, K>(img, s, L, out, n, xi, tile_y0, rows_valid, ax, ay, ratio_w, ratio_h); break;
+            RB200_TRI_CASE(2) RB200_TRI_CASE(3) RB200_TRI_CASE(4) RB200_TRI_CASE(5) RB200_TRI_CASE(6) RB200_TRI_CASE(7)
+            RB200_TRI_CASE(8)
+#undef RB200_TRI_CASE
+            default: tri_column<OutT, LAYOUT, 0>(img, s, L, out, n, xi, tile_y0, rows_valid, ax, ay, ratio_w, ratio_h); break;
         }
     }
     if (L.fill_padding && xi < L.out_w) {

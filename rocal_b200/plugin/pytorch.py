@@ -7,12 +7,19 @@ import torch
 
 
 class ROCALGenericIterator(object):
-    def __init__(self, pipeline, feeder=None, copy=False, size=-1, auto_reset=False):
+    def __init__(self, pipeline, feeder=None, copy=False, size=-1, auto_reset=False, tensor_layout=None, reverse_channels=False,
+                 multiplier=None, offset=None, tensor_dtype=None, device="cuda", device_id=0, display=False,
+                 fill_last_batch=True, dynamic_shape=False, last_batch_padded=False):
         """feeder(pipeline) -> bool feeds one batch through pipeline.feed_input / feed_ragged and returns
-        False when the data is exhausted."""
+        False when the data is exhausted. The remaining arguments are those of the reference's iterators
+        (plugin/pytorch.py:46, 282-290) and are accepted for source compatibility: layout, type and normalisation
+        are those of the pipeline's output operators, and the tensors live on the pipeline's GPU."""
+        if str(device).startswith("cpu"):
+            raise ValueError("outputs live on the pipeline's GPU (device must be 'cuda' / 'gpu')")
         self.loader = pipeline
         self.feeder = feeder
         self.copy = copy
+        self.auto_reset = auto_reset
 
     def __iter__(self):
         return self
@@ -40,6 +47,8 @@ class ROCALClassificationIterator(ROCALGenericIterator):
 
     def __next__(self):
         if self.loader.is_empty():
+            if self.auto_reset:
+                self.reset()
             raise StopIteration
         self.loader.rocal_run()
         outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
