@@ -109,6 +109,9 @@ RB200_API int rb200_feed_files(rb200_context ctx, const char* const* paths, size
  * needs no feed call. last_batch_policy: 0 fill, 1 drop, 2 partial (rocal_api_types.h:455-495).
  * rocalResetLoaders, rocalGetImageLabels, rocalGetImageNameLen / rocalGetImageName (concatenated names of the
  * current batch, no separators), rocalGetLastBatchPaddedSize. */
+/* rocalCreateLabelReader(file_list_path) / rocalCreateTextFileBasedLabelReader: the folder source created next reads the
+ * files named in this list ("file_name label" per line, names relative to its source_path) instead of scanning. */
+RB200_API int rb200_set_file_list(rb200_context ctx, const char* file_list_path);
 RB200_API rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
                                               unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
                                               unsigned max_height, int last_batch_policy, int pad_last_batch_repeated);

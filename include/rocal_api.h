@@ -226,6 +226,9 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourceSingleShard(
     RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext rocal_context, const char* source_path,
                                                               const char* file_list_path = "");
+/* rocal_api_meta_data.h:108: labels from a text file of "file_name label" lines; the following rocalJpegFileSource* reads
+ * the listed files (relative to its source_path) in the list's order. */
+RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateTextFileBasedLabelReader(RocalContext rocal_context, const char* source_path);
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context, int* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext rocal_context, void* buf, int numOfClasses,
                                                          RocalOutputMemType output_mem_type);

@@ -41,6 +41,7 @@ get_error_message = _proto("rb200_get_error_message", c_char_p, _P)
 get_timing = _proto("rb200_get_timing", None, _P, POINTER(ctypes.c_ulonglong))
 feed_encoded = _proto("rb200_feed_encoded", c_int, _P, POINTER(c_void_p), POINTER(c_size_t), c_size_t)
 feed_files = _proto("rb200_feed_files", c_int, _P, POINTER(ctypes.c_char_p), c_size_t)
+set_file_list = _proto("rb200_set_file_list", c_int, _P, c_char_p)
 jpeg_file_source = _proto("rb200_jpeg_file_source", _P, _P, c_char_p, c_int, c_uint, c_uint, c_int, c_int, c_int, c_uint, c_uint, c_int, c_int)
 coco_file_source = _proto("rb200_coco_file_source", _P, _P, c_char_p, c_char_p, c_int, c_uint, c_uint, c_int, c_int, c_int, c_uint, c_uint, c_int, c_int, c_int)
 reset_loaders = _proto("rb200_reset_loaders", c_int, _P)

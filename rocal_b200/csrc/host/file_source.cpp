@@ -5,6 +5,8 @@
 
 #include <algorithm>
 #include <cctype>
+#include <fstream>
+#include <sstream>
 #include <stdexcept>
 
 namespace rb200 {
@@ -53,6 +55,25 @@ FileEntry make_entry(const std::string& path, const std::string& name, int label
 }
 
 }  // namespace
+
+std::vector<FileEntry> read_file_list(const std::string& list_path, const std::string& root) {
+    std::ifstream in(list_path.c_str());
+    if (!in.good()) throw std::runtime_error("Can't open the metadata file at " + list_path);
+    std::vector<FileEntry> out;
+    std::string line;
+    while (std::getline(in, line)) {
+        std::istringstream fields(line);
+        std::string rel;
+        int label = 0;
+        if (!(fields >> rel >> label)) continue;
+        if (!is_jpeg_name(rel)) continue;
+        const auto slash = rel.find_last_of("\\/");
+        const std::string name = slash == std::string::npos ? rel : rel.substr(slash + 1);
+        out.push_back(make_entry(root.empty() ? rel : root + "/" + rel, name, label));
+    }
+    if (out.empty()) throw std::runtime_error("no JPEG files named in " + list_path);
+    return out;
+}
 
 FileSource::FileSource(std::vector<FileEntry> entries, bool with_boxes, size_t batch, unsigned shard_id, unsigned shard_count,
                        bool shuffle, bool loop, int last_batch_policy, bool pad_last_batch_repeated, unsigned seed)

@@ -40,6 +40,13 @@ struct FileEntry {
     std::vector<int> box_labels;
 };
 
+// A file list (rocalCreateLabelReader with file_list_path / rocalCreateTextFileBasedLabelReader): one
+// whitespace-separated "file_name label" pair per line, names relative to `root`, lines that do not parse are
+// skipped, the order of the list is kept, the reported name is the part after the last slash
+// (rocAL/source/meta_data/text_file_meta_data_reader.cpp:71-93). Throws when the list cannot be opened or names
+// no JPEG file.
+std::vector<FileEntry> read_file_list(const std::string& list_path, const std::string& root);
+
 class FileSource {
    public:
     enum LastBatch { FILL = 0, DROP = 1, PARTIAL = 2 };

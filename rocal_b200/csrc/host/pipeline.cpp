@@ -331,8 +331,13 @@ TensorImpl* Pipeline::add_file_source(const std::string& root, unsigned shard_id
                                       unsigned max_w, unsigned max_h, bool is_output, int last_batch_policy,
                                       bool pad_last_batch_repeated) {
     if (max_w == 0 || max_h == 0) RB200_THROW("max_width and max_height must be given (ROCAL_USE_USER_GIVEN_SIZE): they bound the decoded size");
-    std::unique_ptr<FileSource> fs(new FileSource(root, _batch, shard_id, shard_count, shuffle, loop, last_batch_policy,
-                                                  pad_last_batch_repeated, ParameterFactory::instance().get_seed()));
+    std::unique_ptr<FileSource> fs;
+    if (_file_list.empty())
+        fs.reset(new FileSource(root, _batch, shard_id, shard_count, shuffle, loop, last_batch_policy, pad_last_batch_repeated,
+                                ParameterFactory::instance().get_seed()));
+    else
+        fs.reset(new FileSource(read_file_list(_file_list, root), false, _batch, shard_id, shard_count, shuffle, loop,
+                                last_batch_policy, pad_last_batch_repeated, ParameterFactory::instance().get_seed()));
     TensorImpl* t = add_source(max_w, max_h, is_output);
     _files = std::move(fs);
     return t;

@@ -339,8 +339,11 @@ class Pipeline {
     // rocalCreateCOCOReader only records its arguments; rocalJpegCOCOFileSource builds the reader
     std::string _coco_json;
     bool _coco_avoid_remap = false;
+    std::string _file_list;
    public:
     void note_coco_reader(const std::string& json, bool avoid_remap) { _coco_json = json; _coco_avoid_remap = avoid_remap; }
+    // rocalCreateLabelReader with a file list / rocalCreateTextFileBasedLabelReader: the next folder source reads this list
+    void note_file_list(const std::string& list_path) { _file_list = list_path; }
     const std::string& coco_json() const { return _coco_json; }
     bool coco_avoid_remap() const { return _coco_avoid_remap; }
    private:

@@ -353,6 +353,12 @@ int rb200_feed_files(rb200_context ctx, const char* const* paths, size_t n) {
     return ROCAL_OK;
 }
 
+int rb200_set_file_list(rb200_context ctx, const char* file_list_path) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    P(ctx)->note_file_list(file_list_path ? file_list_path : "");
+    return ROCAL_OK;
+}
+
 rb200_tensor rb200_jpeg_file_source(rb200_context ctx, const char* source_path, int color_format, unsigned shard_id,
                                     unsigned shard_count, int is_output, int shuffle, int loop, unsigned max_width,
                                     unsigned max_height, int last_batch_policy, int pad_last_batch_repeated) {

@@ -104,8 +104,21 @@ RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext ctx, const char
         std::cerr << "[ERR] Invalid rocal context\n";
         return nullptr;
     }
-    if (file_list_path && file_list_path[0]) P(ctx)->capture_error("rocalCreateLabelReader: file lists are not supported");
+    // with a file list the following source reads the listed files in the list's order with the list's labels
+    if (file_list_path && file_list_path[0]) rb200_set_file_list(ctx, file_list_path);
     (void)source_path;
+    return nullptr;
+}
+RocalMetaData ROCAL_API_CALL rocalCreateTextFileBasedLabelReader(RocalContext ctx, const char* source_path) {
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    if (!source_path || !source_path[0]) {
+        P(ctx)->capture_error("rocalCreateTextFileBasedLabelReader: empty path");
+        return nullptr;
+    }
+    rb200_set_file_list(ctx, source_path);
     return nullptr;
 }
 // rocalCreateCOCOReader records the annotation file; the source call that follows builds the reader. Masks,

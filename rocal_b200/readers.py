@@ -6,6 +6,7 @@
 readers.file records the folder (one sub-folder per class, numbered in sorted order); decoders.image creates the
 source. Labels of the current batch come from Pipeline.get_image_labels().
 """
+from . import _capi as C
 from .pipeline import Pipeline
 
 
@@ -14,8 +15,8 @@ def file(file_root, file_filters=None, file_list='', stick_to_shard=False, pad_l
     p = Pipeline._current_pipeline
     if p is None:
         raise RuntimeError("readers.file must be called inside `with pipeline:`")
-    if file_list:
-        raise ValueError("file lists are not supported")
+    if file_list:     # "file_name label" lines; the decoder call that follows reads the listed files in this order
+        C.set_file_list(p._handle, str(file_list).encode())
     p._reader = "labelReader"
     p._file_root = file_root
     return ("labelReader", file_root), []

@@ -27,9 +27,12 @@ def harness(tmp_path_factory):
     for i in range(3):
         (flat / ("f%d.jpeg" % i)).write_bytes(b"x")
 
-    def run(root, batch, shard_id, shard_count, shuffle=0, loop_batches=0, policy=0, pad_repeat=0):
+    def run(root, batch, shard_id, shard_count, shuffle=0, loop_batches=0, policy=0, pad_repeat=0, file_list=None):
         out = subprocess.run([exe, str(root), str(batch), str(shard_id), str(shard_count), str(shuffle), str(loop_batches),
-                              str(policy), str(pad_repeat)], capture_output=True, text=True).stdout.strip().splitlines()
+                              str(policy), str(pad_repeat)] + ([str(file_list)] if file_list else []),
+                             capture_output=True, text=True).stdout.strip().splitlines()
+        if out and out[0].startswith("ERROR"):
+            return out[0], [], []
         return out[0], [ln.split("|")[0].split() for ln in out[1:]], [int(ln.split("pad")[1]) for ln in out[1:]]
     return run, data, flat, d
 
@@ -112,3 +115,16 @@ def test_coco_annotation_reader(tmp_path):
     bad = tmp_path / "bad.json"
     bad.write_text('{"images": [ {"id": 1, "file_name": "x.jpg" ')
     assert subprocess.run([exe, str(bad), "0"], capture_output=True, text=True).stdout.startswith("ERROR")
+
+
+def test_file_list(harness):
+    """A "file_name label" list (rocalCreateLabelReader with file_list_path): list order and list labels, names relative
+    to the root, the reported name without its folder, unparsable lines and non-JPEG names skipped."""
+    run, data, _, d = harness
+    lst = d / "list.txt"
+    lst.write_text("dog/dog2.jpg 7\nemu/emu0.jpg 3\n# a comment\ncat/readme.txt 1\ncat/cat1.jpg 0\nbroken_line\ndog/DOG9.JPEG 7\n")
+    head, batches, pads = run(data, 2, 0, 1, file_list=lst)
+    assert head == "N=4 shard=4 per=2"
+    assert [x for b in batches for x in b] == ["dog2.jpg:7", "emu0.jpg:3", "cat1.jpg:0", "DOG9.JPEG:7"] and pads == [0, 0]
+    head, _, _ = run(data, 2, 0, 1, file_list=d / "missing.txt")
+    assert head.startswith("ERROR")

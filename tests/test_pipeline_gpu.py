@@ -816,3 +816,28 @@ def test_one_hot_and_partial_last_batch_iterator(cuda, tmp_path):
     # label k > 0 -> column k-1, label 0 -> last column (rocalGetOneHotImageLabels)
     assert hots == [[0, 0, 1], [0, 0, 1], [1, 0, 0], [0, 1, 0], [0, 1, 0]]
     pipe.rocal_release()
+
+
+def test_file_list_source(cuda, tmp_path):
+    """fn.readers.file(file_list=...): the listed files, in the list's order, with the list's labels."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    from rocal_b200.plugin.pytorch import ROCALClassificationIterator
+    rng = S.rng_for(43)
+    imgs, streams = _jpeg_batch(rng, 4, (64, 128))
+    (tmp_path / "x").mkdir()
+    for i, sb in enumerate(streams):
+        (tmp_path / "x" / ("im%d.jpg" % i)).write_bytes(sb)
+    lst = tmp_path / "train.txt"
+    lst.write_text("x/im3.jpg 11\nx/im0.jpg 5\nx/im2.jpg 11\n")
+    pipe = Pipeline(batch_size=3, device_id=0, seed=2)
+    with pipe:
+        jpegs, labels = fn.readers.file(file_root=str(tmp_path), file_list=str(lst))
+        dec = fn.decoders.image(jpegs, file_root=str(tmp_path), max_decoded_width=128, max_decoded_height=128)
+        pipe.set_outputs(fn.centre_crop(dec, crop=[32, 32]))
+    pipe.build()
+    got = [(pipe.get_image_names(), labs.cpu().tolist(), pipe.get_image_sizes().tolist()) for _, labs in ROCALClassificationIterator(pipe)]
+    assert len(got) == 1
+    assert got[0][0] == ["im3.jpg", "im0.jpg", "im2.jpg"] and got[0][1] == [11, 5, 11]
+    assert got[0][2] == [[imgs[k].shape[1], imgs[k].shape[0]] for k in (3, 0, 2)]
+    pipe.rocal_release()
