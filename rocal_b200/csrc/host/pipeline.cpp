@@ -1029,6 +1029,7 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                 break;
             }
             case NodeKind::WARP_AFFINE: {
+                if (!s.counts.empty()) RB200_THROW("bounding boxes cannot follow a WarpAffine operator (no metadata rule for it)");
                 nd.affine_v.resize(n * 6);
                 if (nd.next_affine.size() == n * 6) {
                     nd.affine_v = nd.next_affine;
@@ -1051,6 +1052,7 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                 break;
             }
             case NodeKind::ROTATE: {
+                if (!s.counts.empty()) RB200_THROW("bounding boxes cannot follow a Rotate operator (its metadata rule is not implemented)");
                 nd.affine_v.resize(n * 6);
                 const auto& a = nd.angle->array();
                 for (size_t i = 0; i < n; i++) {
