@@ -129,9 +129,12 @@ RB200_API unsigned rb200_get_image_name_len(rb200_context ctx, int* lengths);
 RB200_API int rb200_get_image_name(rb200_context ctx, char* buf);
 RB200_API size_t rb200_get_last_batch_padded_size(rb200_context ctx);
 /* rocalGetOneHotImageLabels (label k > 0 sets position k-1, label 0 the last position; int32 [batch][num_classes],
- * output_mem_type 0 = host, 1 = device) and rocalGetImageSizes (width, height of every source image). */
+ * output_mem_type 0 = host, 1 = device) and rocalGetImageSizes (width, height of every source image as read; a fused JPEG crop does not change it). */
 RB200_API int rb200_get_one_hot_image_labels(rb200_context ctx, void* buf, int num_classes, int output_mem_type);
 RB200_API int rb200_get_image_sizes(rb200_context ctx, int* width_height_pairs);
+/* rocalGetROIImageSizes: width, height of the valid region of every sample after ResizeMirrorNormalize (of the first
+ * output when the graph has no such operator). */
+RB200_API int rb200_get_roi_image_sizes(rb200_context ctx, int* width_height_pairs);
 /* rocalFusedJpegCropSingleShard (rocal_api_data_loaders.h:493-506; decoders.image_slice and
  * decoders.image_random_crop of the Python API): the folder source of rb200_jpeg_file_source whose images reach
  * the graph cut to a random-resized-crop window: area_factor[2] = {min, max} fraction of the image area,

@@ -447,9 +447,26 @@ const std::vector<std::string>& Pipeline::image_names() {
     return _slots[_held].names;
 }
 
+// rocalGetImageSizes: the size of every source image as it was read (a fused JPEG crop does not change it).
 void Pipeline::source_sizes(int* wh) {
     if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
-    const auto& r = _slots[_held].rois[_source];
+    const auto& r = _slots[_held].source_wh;
+    if (r.size() != _batch * 2) RB200_THROW("the current batch carries no image sizes");
+    std::memcpy(wh, r.data(), r.size() * sizeof(int));
+}
+
+// rocalGetROIImageSizes: the valid extent of every sample after ResizeMirrorNormalize, the node that maintains this
+// field in the reference (meta_node_resize_mirror_normalize.cpp:79-82); without such a node, of the first output.
+void Pipeline::roi_image_sizes(int* wh) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    int tensor = -1;
+    for (const Node& nd : _nodes)
+        if (nd.kind == NodeKind::RESIZE_MIRROR_NORMALIZE) tensor = nd.out;
+    if (tensor < 0) {
+        if (_output_list.items.empty()) RB200_THROW("the graph has no output");
+        tensor = static_cast<TensorImpl*>(_output_list.items[0])->id;
+    }
+    const auto& r = _slots[_held].rois[tensor];
     for (size_t i = 0; i < _batch; i++) {
         wh[i * 2] = (int)r[i * 4 + 2];
         wh[i * 2 + 1] = (int)r[i * 4 + 3];
@@ -1195,6 +1212,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         _jpeg.init();
         size_t total = 0;
         _decode_off.resize(n);
+        _decode_h.resize(n);
         if (_crop_dec) {
             s.decoder_batch_seed = _crop_dec->next_batch(n);
             s.decoder_windows.resize(n * 4);
@@ -1206,6 +1224,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                 RB200_THROW("decoded image " + std::to_string(i) + " (" + std::to_string(w) + "x" + std::to_string(h) +
                             ") is empty or exceeds the source's max_width x max_height");
             _decode_off[i] = total;
+            _decode_h[i] = h;
             _src_views[i] = {total, (uint32_t)w * 3};
             src->roi_w[i] = w;
             src->roi_h[i] = h;
@@ -1232,6 +1251,16 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         }
         b.arena_bytes = total + 256;
     }
+    s.source_wh.resize(n * 2);
+    for (size_t i = 0; i < n; i++) {
+        s.source_wh[i * 2] = src->roi_w[i];
+        s.source_wh[i * 2 + 1] = src->roi_h[i];
+    }
+    if (!s.decoder_windows.empty())   // the views show the windows; the images are the stride wide
+        for (size_t i = 0; i < n; i++) {
+            s.source_wh[i * 2] = (int)(_src_views[i].stride / 3);
+            s.source_wh[i * 2 + 1] = (int)_decode_h[i];
+        }
     // Pinned host input that exactly one staging kernel consumes is not uploaded at all: the kernel's bulk
     // copies read the tap rows straight from host memory, so only the bytes the batch needs cross the link.
     bool zero_copy = false;

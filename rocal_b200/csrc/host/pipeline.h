@@ -204,6 +204,7 @@ struct Slot {
     std::vector<int> file_labels;    // file source: class label per sample
     std::vector<std::string> names;  // file source: file name per sample
     size_t padded = 0;
+    std::vector<int> source_wh;              // n x {width, height} of the whole source images (before a decoder crop)
     std::vector<unsigned> decoder_windows;   // fused JPEG crop: n x {x,y,w,h} inside the decoded images
     unsigned decoder_batch_seed = 0;
     size_t n = 0;
@@ -230,6 +231,7 @@ class Pipeline {
     const std::vector<std::string>& image_names();
     size_t last_batch_padded_size();
     void source_sizes(int* wh);
+    void roi_image_sizes(int* wh);
     TensorImpl* add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
                          RocalTensorOutputType dt, bool is_output);
     void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
@@ -353,6 +355,7 @@ class Pipeline {
     // JPEG front-end (created when the first encoded batch arrives)
     JpegDecoder _jpeg;
     std::vector<unsigned char*> _jpeg_dst;
+    std::vector<int> _decode_h;                            // decoded height of each image
     std::vector<size_t> _decode_off;                       // arena offset of each decoded image (the view may start inside it)
     std::unique_ptr<RandomCropWindowSampler> _crop_dec;    // fused JPEG crop source
     std::vector<size_t> _jpeg_pitch;

@@ -562,6 +562,19 @@ int rb200_get_image_sizes(rb200_context ctx, int* buf) {
     return ROCAL_OK;
 }
 
+// rocalGetROIImageSizes (rocal_api_meta_data.cpp:353-372).
+int rb200_get_roi_image_sizes(rb200_context ctx, int* buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buf) RB200_THROW("null output buffer");
+        P(ctx)->roi_image_sizes(buf);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
 size_t rb200_get_last_batch_padded_size(rb200_context ctx) { return ctx ? P(ctx)->last_batch_padded_size() : 0; }
 
 int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes, const rb200_image_desc* descs, size_t n,

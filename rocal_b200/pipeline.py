@@ -287,9 +287,16 @@ class Pipeline(object):
         return out
 
     def get_image_sizes(self):
-        """rocalGetImageSizes: (width, height) of every source image of the batch, int32 [N, 2]."""
+        """rocalGetImageSizes: (width, height) of every source image of the batch as it was read, int32 [N, 2]."""
         out = np.zeros((self._batch_size, 2), dtype=np.int32)
         self._check(C.get_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        return out
+
+    def get_roi_image_sizes(self):
+        """rocalGetROIImageSizes: (width, height) of the valid region of every sample after ResizeMirrorNormalize (of the
+        first output when the graph has none), int32 [N, 2]."""
+        out = np.zeros((self._batch_size, 2), dtype=np.int32)
+        self._check(C.get_roi_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
         return out
 
     def set_random_crop_decoder(self, random_area=(0.08, 1.0), random_aspect_ratio=(3.0 / 4, 4.0 / 3), num_attempts=10):

@@ -341,6 +341,7 @@ def test_resize_mirror_normalize_min_max(cuda):
     exp = O.resample(arena, tab, 96, 96, T.FP32, T.NHWC, mul, add)
     assert np.array_equal(got, exp)
     assert (int(roi[0, 2]), int(roi[0, 3])) == (95, 22)          # 390 x 90: size = round(96*90/390) = 22, width = 22*390//90
+    assert pipe.get_roi_image_sizes().tolist() == roi[:, 2:].tolist()     # rocalGetROIImageSizes follows ResizeMirrorNormalize
     pipe.rocal_release()
 
 
@@ -662,7 +663,8 @@ def test_fused_jpeg_crop_external_source(cuda):
             win, bseed = pipe.get_decoder_crop_windows()
             assert bseed == batch_seeds()
             assert np.array_equal(win, O.random_crop_windows(bseed, shapes, aspect, area, attempts))
-            assert pipe.get_image_sizes().tolist() == win[:, 2:].tolist()
+            assert pipe.get_image_sizes().tolist() == shapes[:, ::-1].tolist()          # the images as decoded
+            assert pipe.get_roi_image_sizes().tolist() == win[:, 2:].tolist()           # what the first output holds
             cut, res = [t.numpy() for t in pipe.get_output_tensors()]
             for i in range(n):
                 x, y, w, h = [int(v) for v in win[i]]
