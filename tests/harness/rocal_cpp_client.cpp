@@ -151,6 +151,47 @@ int main(int argc, char** argv) {
         CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
         rocalRelease(ctx);
     }
+    // ---- graph 3: CropResizeFixed, ROIResize (triangular), RandomCrop with fixed parameters, Copy ----
+    {
+        RocalContext ctx = rocalCreate((size_t)n, ROCAL_PROCESS_GPU, 0, 1, 2, ROCAL_FP32);
+        if (!ctx) return 1;
+        RocalTensor src = rocalJpegExternalFileSource(ctx, ROCAL_COLOR_RGB24, false, false, false, ROCAL_USE_USER_GIVEN_SIZE,
+                                                      (unsigned)max_w, (unsigned)max_h, ROCAL_DECODER_TJPEG, ROCAL_EXTSOURCE_RAW_UNCOMPRESSED);
+        CHECK(ctx, src);
+        RocalTensor cr = rocalCropResizeFixed(ctx, src, 120, 80, true, 0.5f, 1.25f, 0.25f, 0.75f);
+        CHECK(ctx, cr);
+        RocalTensor roi = rocalROIResize(ctx, src, 64, 48, true, 100, 150, 20.f, 30.f, ROCAL_TRIANGULAR_INTERPOLATION);
+        CHECK(ctx, roi);
+        RocalTensor rc = rocalRandomCrop(ctx, src, true, rocalCreateFloatParameter(0.5f), rocalCreateFloatParameter(1.25f),
+                                         rocalCreateFloatParameter(0.25f), rocalCreateFloatParameter(0.75f));
+        CHECK(ctx, rc);
+        RocalTensor cp = rocalCopy(ctx, src, true);
+        CHECK(ctx, cp);
+        CHECK(ctx, rocalVerify(ctx) == ROCAL_OK);
+        CHECK(ctx, rocalGetAugmentationBranchCount(ctx) == 4);
+        CHECK(ctx, rocalExternalSourceFeedInput(ctx, {}, false, bufs, rois, (unsigned)max_w, (unsigned)max_h, 3,
+                                                ROCAL_EXTSOURCE_RAW_UNCOMPRESSED, ROCAL_NHWC, false) == ROCAL_OK);
+        CHECK(ctx, rocalRun(ctx) == ROCAL_OK);
+        RocalTensorList tl = rocalGetOutputTensors(ctx);
+        CHECK(ctx, tl && tl->size() == 4);
+        for (int k = 0; k < 4; k++) {
+            rocalTensor* t = tl->at(k);
+            CHECK(ctx, t->data_type() == ROCAL_UINT8 && t->layout() == ROCAL_NHWC);
+            std::vector<unsigned char> host(t->data_size());
+            CHECK(ctx, t->copy_data(host.data(), ROCAL_MEMCPY_HOST) == 0);
+            const int dims[2] = {(int)t->dims()[1], (int)t->dims()[2]};     // height, width of the padded output
+            fwrite(dims, 4, 2, out);
+            fwrite(host.data(), 1, host.size(), out);
+            std::vector<unsigned> r4((size_t)n * 4);
+            t->copy_roi(r4.data());
+            fwrite(r4.data(), 4, r4.size(), out);
+        }
+        std::vector<int> sizes((size_t)n * 2);
+        rocalGetImageSizes(ctx, sizes.data());
+        fwrite(sizes.data(), 4, sizes.size(), out);
+        CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
+        rocalRelease(ctx);
+    }
     fclose(out);
     printf("ok\n");
     return 0;

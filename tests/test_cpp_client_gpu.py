@@ -86,6 +86,32 @@ def test_cpp_client(cuda, tmp_path):
     eb, el = O.box_encode(b2, l2, o2, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
     gb = take(np.float32, n * len(anchors) * 4).reshape(n, len(anchors), 4)
     gl = take(np.int32, n * len(anchors)).reshape(n, len(anchors))
-    assert pos == len(raw)
     assert np.array_equal(gl, el)
     assert np.allclose(gb, eb, rtol=1e-5, atol=1e-6)
+    # graph 3: CropResizeFixed, ROIResize(triangular), RandomCrop(fixed parameters), Copy
+    wh = np.stack([ws, hs], axis=1)
+    win = O.random_area_windows(wh, fixed=(0.5, 1.25, 0.25, 0.75)).astype(np.int64)
+
+    def stretched(wn, w, h, interpolation=0):
+        tab = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        tab["src_offset"], tab["src_stride"] = offs, ws * 3
+        tab["roi_x"], tab["roi_y"], tab["roi_w"], tab["roi_h"] = wn[:, 0], wn[:, 1], wn[:, 2], wn[:, 3]
+        tab["dst_w"], tab["dst_h"], tab["crop_w"], tab["crop_h"] = w, h, w, h
+        return O.resample(arena, tab, w, h, T.UINT8, T.NHWC, interpolation=interpolation)
+
+    outs = []
+    for k in range(4):
+        oh, ow = [int(v) for v in take(np.int32, 2)]
+        outs.append((take(np.uint8, n * oh * ow * 3).reshape(n, oh, ow, 3), take(np.uint32, n * 4).reshape(n, 4)))
+    sizes = take(np.int32, n * 2).reshape(n, 2)
+    assert pos == len(raw)
+    assert np.array_equal(outs[0][0], stretched(win, 120, 80)) and outs[0][1][:, 2:].tolist() == [[120, 80]] * n
+    fixed_roi = np.tile(np.array([[20, 30, 150, 100]], dtype=np.int64), (n, 1))
+    assert np.array_equal(outs[1][0], stretched(fixed_roi, 64, 48, 1))
+    for i in range(n):
+        ih, iw, o = int(hs[i]), int(ws[i]), int(offs[i])
+        im = arena[o:o + ih * iw * 3].reshape(ih, iw, 3)
+        x, y, w, h = [int(v) for v in win[i]]
+        assert np.array_equal(outs[2][0][i, :h, :w], im[y:y + h, x:x + w]) and outs[2][1][i, 2:].tolist() == [w, h]
+        assert np.array_equal(outs[3][0][i, :ih, :iw], im) and outs[3][1][i, 2:].tolist() == [iw, ih]
+    assert sizes.tolist() == wh.tolist()
