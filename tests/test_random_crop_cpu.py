@@ -68,6 +68,8 @@ def test_restatement_matches_reference_build():
             shapes[:, 1] = rng.integers(1, 20, n)
         aspect = (0.75, 4.0 / 3) if trial % 3 else (0.8, 1.25)
         attempts = 10 if trial % 2 else 1
+        if trial == 3:      # empty, one-pixel and extremely thin images
+            shapes[:7] = [[0, 10], [10, 0], [1, 1], [1, 2000], [2000, 1], [2, 2], [3, 1000]]
         seed, win = O.ref_random_crop_windows(shapes, aspect, (0.08, 1.0), attempts)
         assert np.array_equal(O.random_crop_windows(seed, shapes, aspect, (0.08, 1.0), attempts), win)
         assert np.array_equal(_product_windows(seed, shapes, aspect, (0.08, 1.0), attempts), win)
