@@ -278,6 +278,59 @@ __device__ __forceinline__ void permute_store_u8(uint8_t* po, size_t plane, cons
     }
 }
 
+// uint8 in, uint8 out colour operators on one 4-pixel block: d[] are the 12 source bytes, e[] the 12 result
+// bytes in the same (block) order. COLOR_NONE copies.
+template <int COLOR_OP>
+__device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t (&e)[3], uint32_t magic, float alpha, float beta,
+                                               float hue, float sat, const float* rcp) {
+    if (COLOR_OP == RB200_COLOR_NONE) {
+        e[0] = d[0]; e[1] = d[1]; e[2] = d[2];
+    } else if (COLOR_OP == RB200_COLOR_TWIST) {
+        uint32_t q[12];
+        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
+#pragma unroll
+        for (int k = 0; k < 4; k += 2) {       // pixels k and k+1 of the block in the two lanes
+            float2 c3[3];
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                const int ba = 3 * k + c, bb = 3 * (k + 1) + c;
+                c3[c].x = __uint_as_float(__byte_perm(d[ba >> 2], magic, 0x7650u + (ba & 3)));
+                c3[c].y = __uint_as_float(__byte_perm(d[bb >> 2], magic, 0x7650u + (bb & 3)));
+                c3[c] = add2(c3[c], nk23);
+            }
+            float2 o0, o1, o2;
+            color_twist_px2(c3[0], c3[1], c3[2], alpha, beta, hue, sat, rcp, o0, o1, o2);
+            q[3 * k + 0] = cvt_sat_u8(o0.x); q[3 * k + 1] = cvt_sat_u8(o1.x); q[3 * k + 2] = cvt_sat_u8(o2.x);
+            q[3 * k + 3] = cvt_sat_u8(o0.y); q[3 * k + 4] = cvt_sat_u8(o1.y); q[3 * k + 5] = cvt_sat_u8(o2.y);
+        }
+#pragma unroll
+        for (int wd = 0; wd < 3; wd++) e[wd] = pack4_u8(q[4 * wd], q[4 * wd + 1], q[4 * wd + 2], q[4 * wd + 3]);
+    } else {
+        // brightness / contrast: two bytes per packed f32x2 instruction
+        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
+        const float2 a2 = make_float2(alpha, alpha), b2 = make_float2(beta, beta);
+        const float2 nb2 = make_float2(-beta, -beta);
+#pragma unroll
+        for (int wd = 0; wd < 3; wd++) {
+            uint32_t q[4];
+#pragma unroll
+            for (int hb = 0; hb < 4; hb += 2) {
+                float2 x;
+                x.x = __uint_as_float(__byte_perm(d[wd], magic, 0x7650u + hb));
+                x.y = __uint_as_float(__byte_perm(d[wd], magic, 0x7651u + hb));
+                x = add2(x, nk23);
+                if (COLOR_OP == RB200_COLOR_BRIGHTNESS)
+                    x = lanes_add(mul2(a2, x), b2);
+                else
+                    x = lanes_add(mul2(add2(x, nb2), a2), b2);
+                q[hb] = cvt_sat_u8(x.x);
+                q[hb + 1] = cvt_sat_u8(x.y);
+            }
+            e[wd] = pack4_u8(q[0], q[1], q[2], q[3]);
+        }
+    }
+}
+
 template <typename OutT, int LAYOUT, int COLOR_OP>
 __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
                                                             const rb200_pointwise_sample* __restrict__ samples,
@@ -347,11 +400,17 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
     }
 
     if (rows > 0 && w > 0 && staged_ok) {
-        const int gpr = (w + 3) >> 2;                 // 4-pixel groups per row
+        const bool bytes_only = COLOR_OP == RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels;
+        // uint8 NHWC output without normalisation: the first w16 columns of every row go through 16-pixel units
+        // (48 source bytes -> 48 output bytes per thread and step), which spreads the index arithmetic of an
+        // item over four 4-pixel blocks and lets the result leave as three 16-byte stores; the item loop below
+        // takes the remaining columns (and everything for the other output types).
+        const bool unit_path = sizeof(OutT) == 1 && LAYOUT == RB200_NHWC && !L.normalize && !L.reverse_channels;
+        const int w16 = unit_path ? (w & ~15) : 0;
+        const int gpr = (w - w16 + 3) >> 2;           // 4-pixel groups per row in the item loop
         const int items = rows * gpr;
         // item / gpr by multiply-high: exact while item * gpr < 2^32
-        const uint32_t gpr_magic = (uint32_t)((0x100000000ull + (uint32_t)gpr - 1) / (uint32_t)gpr);
-        const bool bytes_only = COLOR_OP == RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels;
+        const uint32_t gpr_magic = gpr > 0 ? (uint32_t)((0x100000000ull + (uint32_t)gpr - 1) / (uint32_t)gpr) : 0u;
         // Per-thread constants of the index arithmetic: source row of tile row r is sy0 + sy_step * r; a
         // staged row starts at the source row's address rounded down to 16 bytes, so the block of group
         // column x sits at (row address mod 16) + 3 * (x, or w - x - npx under a horizontal flip).
@@ -362,6 +421,50 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
         // element (tile row 0, column 0) of the output; an item adds a 32-bit offset
         OutT* const out_tile = out + (LAYOUT == RB200_NCHW ? ((size_t)n * 3) * plane + (size_t)tile_y0 * L.out_w
                                                              : ((size_t)n * L.out_h + tile_y0) * L.out_w * 3);
+        if (w16 > 0) {
+            const int upr = w16 >> 4;
+            const int units = rows * upr;
+            const uint32_t upr_magic = (uint32_t)((0x100000000ull + (uint32_t)upr - 1) / (uint32_t)upr);
+            uint8_t* const out_bytes = reinterpret_cast<uint8_t*>(out_tile);
+            const bool st16 = ((reinterpret_cast<uintptr_t>(out_bytes) | (uintptr_t)(L.out_w * 3)) & 15u) == 0;
+            for (int unit = threadIdx.x; unit < units; unit += blockDim.x) {
+                const int row = upr == 1 ? unit : (int)__umulhi((uint32_t)unit, upr_magic);
+                const int x = (unit - row * upr) << 4;
+                const int sy = sy0 + sy_step * row;
+                const uint32_t m = (base_mod + (uint32_t)sy * stride_mod) & 15u;
+                const uint32_t boff = (uint32_t)row * L.pitch + m + (uint32_t)(s.flip_h ? (w - x - 16) : x) * 3u;
+                const uint32_t* wp = reinterpret_cast<const uint32_t*>(stage + (boff & ~3u));
+                uint32_t wv[13];
+#pragma unroll
+                for (int i = 0; i < 13; i++) wv[i] = wp[i];
+                const uint32_t sh = boff << 3;          // the funnel shift reads the low five bits
+                uint32_t ee[12];
+#pragma unroll
+                for (int b = 0; b < 4; b++) {           // source block b = source pixels 4b .. 4b+3 of the unit
+                    uint32_t d[3], e[3];
+                    d[0] = __funnelshift_r(wv[3 * b], wv[3 * b + 1], sh);
+                    d[1] = __funnelshift_r(wv[3 * b + 1], wv[3 * b + 2], sh);
+                    d[2] = __funnelshift_r(wv[3 * b + 2], wv[3 * b + 3], sh);
+                    color_block_u8<COLOR_OP>(d, e, L.magic, s.alpha, s.beta, s.hue, s.sat, rcp);
+                    if (s.flip_h) {                     // blocks and the pixels inside a block change places
+                        ee[3 * (3 - b) + 0] = __byte_perm(e[1], e[2], 0x2765u);
+                        ee[3 * (3 - b) + 1] = __byte_perm(__byte_perm(e[1], e[2], 0x0043u), e[0], 0x3710u);
+                        ee[3 * (3 - b) + 2] = __byte_perm(e[0], e[1], 0x2105u);
+                    } else {
+                        ee[3 * b + 0] = e[0]; ee[3 * b + 1] = e[1]; ee[3 * b + 2] = e[2];
+                    }
+                }
+                uint8_t* po = out_bytes + (uint32_t)(row * L.out_w + x) * 3u;
+                if (st16) {
+#pragma unroll
+                    for (int q = 0; q < 3; q++)
+                        reinterpret_cast<uint4*>(po)[q] = make_uint4(ee[4 * q], ee[4 * q + 1], ee[4 * q + 2], ee[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 12; q++) reinterpret_cast<uint32_t*>(po)[q] = ee[q];
+                }
+            }
+        }
         // Two work items per iteration: all eight loads are issued before the first use.
         for (int item0 = threadIdx.x; item0 < items; item0 += 2 * blockDim.x) {
             uint32_t wv[2][4];
@@ -373,7 +476,7 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                 npxv[u] = 0;
                 if (item < items) {
                     const int row = gpr == 1 ? item : (int)__umulhi((uint32_t)item, gpr_magic);
-                    const int x = (item - row * gpr) << 2;
+                    const int x = w16 + ((item - row * gpr) << 2);
                     const int npx = min(4, w - x);
                     const int sy = sy0 + sy_step * row;
                     const uint32_t m = (base_mod + (uint32_t)sy * stride_mod) & 15u;
@@ -407,50 +510,7 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                     // uint8 in, uint8 out: the 12 result bytes are rebuilt in block order and leave through the
                     // same byte permutation as a plain crop / flip.
                     uint32_t e[3];
-                    if (COLOR_OP == RB200_COLOR_TWIST) {
-                        uint32_t q[12];
-                        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
-#pragma unroll
-                        for (int k = 0; k < 4; k += 2) {       // pixels k and k+1 of the block in the two lanes
-                            float2 c3[3];
-#pragma unroll
-                            for (int c = 0; c < 3; c++) {
-                                const int ba = 3 * k + c, bb = 3 * (k + 1) + c;
-                                c3[c].x = __uint_as_float(__byte_perm(d[ba >> 2], L.magic, 0x7650u + (ba & 3)));
-                                c3[c].y = __uint_as_float(__byte_perm(d[bb >> 2], L.magic, 0x7650u + (bb & 3)));
-                                c3[c] = add2(c3[c], nk23);
-                            }
-                            float2 o0, o1, o2;
-                            color_twist_px2(c3[0], c3[1], c3[2], s.alpha, s.beta, s.hue, s.sat, rcp, o0, o1, o2);
-                            q[3 * k + 0] = cvt_sat_u8(o0.x); q[3 * k + 1] = cvt_sat_u8(o1.x); q[3 * k + 2] = cvt_sat_u8(o2.x);
-                            q[3 * k + 3] = cvt_sat_u8(o0.y); q[3 * k + 4] = cvt_sat_u8(o1.y); q[3 * k + 5] = cvt_sat_u8(o2.y);
-                        }
-#pragma unroll
-                        for (int wd = 0; wd < 3; wd++) e[wd] = pack4_u8(q[4 * wd], q[4 * wd + 1], q[4 * wd + 2], q[4 * wd + 3]);
-                    } else {
-                        // brightness / contrast: two bytes per packed f32x2 instruction
-                        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
-                        const float2 a2 = make_float2(s.alpha, s.alpha), b2 = make_float2(s.beta, s.beta);
-                        const float2 nb2 = make_float2(-s.beta, -s.beta);
-#pragma unroll
-                        for (int wd = 0; wd < 3; wd++) {
-                            uint32_t q[4];
-#pragma unroll
-                            for (int hb = 0; hb < 4; hb += 2) {
-                                float2 x;
-                                x.x = __uint_as_float(__byte_perm(d[wd], L.magic, 0x7650u + hb));
-                                x.y = __uint_as_float(__byte_perm(d[wd], L.magic, 0x7651u + hb));
-                                x = add2(x, nk23);
-                                if (COLOR_OP == RB200_COLOR_BRIGHTNESS)
-                                    x = lanes_add(mul2(a2, x), b2);
-                                else
-                                    x = lanes_add(mul2(add2(x, nb2), a2), b2);
-                                q[hb] = cvt_sat_u8(x.x);
-                                q[hb + 1] = cvt_sat_u8(x.y);
-                            }
-                            e[wd] = pack4_u8(q[0], q[1], q[2], q[3]);
-                        }
-                    }
+                    color_block_u8<COLOR_OP>(d, e, L.magic, s.alpha, s.beta, s.hue, s.sat, rcp);
                     uint8_t* pb = reinterpret_cast<uint8_t*>(out_tile) + eoff;
                     permute_store_u8<LAYOUT>(pb, plane, e, s.flip_h != 0);
                     continue;
@@ -639,10 +699,10 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     L.pitch = 0;
     size_t smem = 0;
     if (vec) {
-        // a tile = th full source rows staged in shared memory (~16 KB), about 4-5 work items per thread
+        // a tile = th full source rows staged in shared memory (up to 24 KB), about 8 four-pixel items per thread
         int pitch = (15 + ext_w * 3 + 16 + 15) & ~15;
         int gpr = (ext_w + 3) / 4;
-        int th = (5 * 256 + gpr - 1) / gpr;
+        int th = (8 * 256 + gpr - 1) / gpr;
         if (th * pitch > 24 * 1024) th = 24 * 1024 / pitch;
         if (th < 1) th = 1;
         if (th > ext_h) th = ext_h;

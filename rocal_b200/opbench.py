@@ -77,7 +77,7 @@ def main():
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
             report("cfg0 resize+CMN fp32 NCHW (batch 64, 256..512 px)", n, _time(fns, args.steps), algo)
         elif op in ("color_twist", "brightness", "flip"):
-            n, rot = 256, 4
+            n, rot = int(os.environ.get("RB200_OPBENCH_N", "256")), 4
             code = {"color_twist": T.COLOR_TWIST, "brightness": T.COLOR_BRIGHTNESS, "flip": T.COLOR_NONE}[op]
             fns = []
             for r in range(rot):
@@ -87,7 +87,7 @@ def main():
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.pointwise(a, t, 224, 224, code, out=out, d_samples=dt, fill_padding=False))
-            report("cfg2 %s(+flip) u8 HWC 224x224 (batch 256)" % op, n, _time(fns, args.steps), n * 2 * 3 * 224 * 224)
+            report("cfg2 %s(+flip) u8 HWC 224x224 (batch %d)" % (op, n), n, _time(fns, args.steps), n * 2 * 3 * 224 * 224)
         elif op == "warp":
             n, rot = 128, 2
             fns = []
