@@ -132,6 +132,8 @@ RB200_API size_t rb200_get_last_batch_padded_size(rb200_context ctx);
  * output_mem_type 0 = host, 1 = device) and rocalGetImageSizes (width, height of every source image as read; a fused JPEG crop does not change it). */
 RB200_API int rb200_get_one_hot_image_labels(rb200_context ctx, void* buf, int num_classes, int output_mem_type);
 RB200_API int rb200_get_image_sizes(rb200_context ctx, int* width_height_pairs);
+/* rocalGetImageId: the annotation file's "id" of every image of the batch (COCO source only). */
+RB200_API int rb200_get_image_ids(rb200_context ctx, int* ids);
 /* rocalGetROIImageSizes: width, height of the valid region of every sample after ResizeMirrorNormalize (of the first
  * output when the graph has no such operator). */
 RB200_API int rb200_get_roi_image_sizes(rb200_context ctx, int* width_height_pairs);

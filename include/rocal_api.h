@@ -234,6 +234,7 @@ RB200_ROCAL void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext rocal_con
                                                          RocalOutputMemType output_mem_type);
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageSizes(RocalContext rocal_context, int* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalGetROIImageSizes(RocalContext rocal_context, int* buf);
+RB200_ROCAL void ROCAL_API_CALL rocalGetImageId(RocalContext rocal_context, int* buf);
 RB200_ROCAL unsigned ROCAL_API_CALL rocalGetImageNameLen(RocalContext rocal_context, int* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageName(RocalContext rocal_context, char* buf);
 RB200_ROCAL void ROCAL_API_CALL rocalResetLoaders(RocalContext context);

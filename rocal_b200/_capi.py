@@ -56,6 +56,7 @@ get_decoder_crop_windows = _proto("rb200_get_decoder_crop_windows", c_int, _P, P
 random_crop_windows = _proto("rb200_random_crop_windows", c_int, c_uint, POINTER(c_int), c_size_t, POINTER(c_float),
                              POINTER(c_float), c_uint, POINTER(c_uint))
 get_image_sizes = _proto("rb200_get_image_sizes", c_int, _P, POINTER(c_int))
+get_image_ids = _proto("rb200_get_image_ids", c_int, _P, POINTER(c_int))
 get_roi_image_sizes = _proto("rb200_get_roi_image_sizes", c_int, _P, POINTER(c_int))
 get_last_batch_padded_size = _proto("rb200_get_last_batch_padded_size", c_size_t, _P)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)

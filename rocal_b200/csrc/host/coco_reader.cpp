@@ -183,6 +183,7 @@ std::vector<CocoImage> read_coco_annotations(const std::string& json_path, bool 
                         if (key == "images") {
                             CocoImage im;
                             im.file_name = file_name;
+                            im.id = id;
                             im.width = width;
                             im.height = height;
                             images[id] = im;

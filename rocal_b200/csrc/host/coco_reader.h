@@ -18,6 +18,7 @@ namespace rb200 {
 
 struct CocoImage {
     std::string file_name;
+    long id = 0;                 // "id" of the images entry (what rocalGetImageId reports)
     int width = 0, height = 0;
     std::vector<float> boxes;    // normalized ltrb, 4 per annotation, in file order
     std::vector<int> labels;

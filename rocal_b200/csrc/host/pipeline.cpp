@@ -358,6 +358,7 @@ TensorImpl* Pipeline::add_coco_source(const std::string& root, const std::string
         if (!f) continue;
         std::fclose(f);
         e.name = im.file_name;
+        e.label = (int)im.id;            // a detection sample has no class label: the slot carries the image id
         e.boxes = std::move(im.boxes);
         e.box_labels = std::move(im.labels);
         entries.push_back(std::move(e));
@@ -367,6 +368,7 @@ TensorImpl* Pipeline::add_coco_source(const std::string& root, const std::string
                                                   pad_last_batch_repeated, ParameterFactory::instance().get_seed()));
     TensorImpl* t = add_source(max_w, max_h, is_output);
     _files = std::move(fs);
+    _coco_source = true;
     return t;
 }
 
@@ -440,6 +442,12 @@ void Pipeline::image_labels(int* buf) {
     const Slot& s = _slots[_held];
     if (s.file_labels.size() != _batch) RB200_THROW("the current batch carries no labels (no file source / label reader)");
     std::memcpy(buf, s.file_labels.data(), _batch * sizeof(int));
+}
+
+// rocalGetImageId (rocal_api_meta_data.cpp:185-195): the "id" of every image of the batch in the COCO annotation file.
+void Pipeline::image_ids(int* buf) {
+    if (!_coco_source) RB200_THROW("rocalGetImageId needs a COCO source");
+    image_labels(buf);
 }
 
 const std::vector<std::string>& Pipeline::image_names() {

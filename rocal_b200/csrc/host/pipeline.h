@@ -228,6 +228,7 @@ class Pipeline {
     void decoder_crop_windows(unsigned* xywh, unsigned* batch_seed);
     void reset_loaders();
     void image_labels(int* buf);
+    void image_ids(int* buf);
     const std::vector<std::string>& image_names();
     size_t last_batch_padded_size();
     void source_sizes(int* wh);
@@ -342,6 +343,7 @@ class Pipeline {
     std::string _coco_json;
     bool _coco_avoid_remap = false;
     std::string _file_list;
+    bool _coco_source = false;
    public:
     void note_coco_reader(const std::string& json, bool avoid_remap) { _coco_json = json; _coco_avoid_remap = avoid_remap; }
     // rocalCreateLabelReader with a file list / rocalCreateTextFileBasedLabelReader: the next folder source reads this list

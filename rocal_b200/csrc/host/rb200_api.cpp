@@ -562,6 +562,18 @@ int rb200_get_image_sizes(rb200_context ctx, int* buf) {
     return ROCAL_OK;
 }
 
+int rb200_get_image_ids(rb200_context ctx, int* buf) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        if (!buf) RB200_THROW("null output buffer");
+        P(ctx)->image_ids(buf);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
 // rocalGetROIImageSizes (rocal_api_meta_data.cpp:353-372).
 int rb200_get_roi_image_sizes(rb200_context ctx, int* buf) {
     CTX_OR(ROCAL_CONTEXT_INVALID);

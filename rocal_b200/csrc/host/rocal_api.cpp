@@ -167,6 +167,7 @@ void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext ctx, void* buf, int n
 }
 void ROCAL_API_CALL rocalGetImageSizes(RocalContext ctx, int* buf) { rb200_get_image_sizes(ctx, buf); }
 void ROCAL_API_CALL rocalGetROIImageSizes(RocalContext ctx, int* buf) { rb200_get_roi_image_sizes(ctx, buf); }
+void ROCAL_API_CALL rocalGetImageId(RocalContext ctx, int* buf) { rb200_get_image_ids(ctx, buf); }
 unsigned ROCAL_API_CALL rocalGetImageNameLen(RocalContext ctx, int* buf) { return rb200_get_image_name_len(ctx, buf); }
 void ROCAL_API_CALL rocalGetImageName(RocalContext ctx, char* buf) { rb200_get_image_name(ctx, buf); }
 void ROCAL_API_CALL rocalResetLoaders(RocalContext ctx) { rb200_reset_loaders(ctx); }

@@ -292,6 +292,12 @@ class Pipeline(object):
         self._check(C.get_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
         return out
 
+    def get_image_id(self):
+        """rocalGetImageId: the annotation file's id of every image of the batch (COCO reader), int32 [N]."""
+        out = np.zeros(self._batch_size, dtype=np.int32)
+        self._check(C.get_image_ids(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        return out
+
     def get_roi_image_sizes(self):
         """rocalGetROIImageSizes: (width, height) of the valid region of every sample after ResizeMirrorNormalize (of the
         first output when the graph has none), int32 [N, 2]."""

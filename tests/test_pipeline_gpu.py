@@ -287,6 +287,7 @@ def test_coco_source_pipeline(cuda, tmp_path):
     pipe.run()
     names = pipe.get_image_names()
     assert names == ["000.jpg", "001.jpg", "002.jpg", "003.jpg"]
+    assert pipe.get_image_id().tolist() == [100, 101, 102, 103]            # rocalGetImageId: the file's image ids
     b2, l2, c2 = pipe.get_bounding_boxes()
     at = 0
     for nm, c in zip(names, c2):
