@@ -272,6 +272,9 @@ Pipeline::Pipeline(size_t batch, int gpu_id, size_t depth, RocalTensorOutputType
     if (gpu_id < 0 || gpu_id >= count) RB200_THROW("invalid gpu_id " + std::to_string(gpu_id));
     RB200_CUDA(cudaSetDevice(gpu_id));
     RB200_CUDA(cudaStreamCreateWithFlags(&_stream, cudaStreamNonBlocking));
+    RB200_CUDA(cudaStreamCreateWithFlags(&_meta_stream, cudaStreamNonBlocking));
+    RB200_CUDA(cudaEventCreateWithFlags(&_meta_done, cudaEventDisableTiming));
+    RB200_CUDA(cudaEventCreateWithFlags(&_box_stage_free, cudaEventDisableTiming));
 }
 
 Pipeline::~Pipeline() {
@@ -284,6 +287,7 @@ Pipeline::~Pipeline() {
     if (_worker.joinable()) _worker.join();
     cudaSetDevice(_gpu_id);
     if (_stream) cudaStreamSynchronize(_stream);
+    if (_meta_stream) cudaStreamSynchronize(_meta_stream);
     for (auto& t : _tensors) {
         for (void* p : t->ring) cudaFree(p);
         if (t->scratch) cudaFree(t->scratch);
@@ -306,6 +310,9 @@ Pipeline::~Pipeline() {
     if (_d_labels) cudaFree(_d_labels);
     if (_d_offsets) cudaFree(_d_offsets);
     if (_h_box_stage) cudaFreeHost(_h_box_stage);
+    if (_meta_done) cudaEventDestroy(_meta_done);
+    if (_box_stage_free) cudaEventDestroy(_box_stage_free);
+    if (_meta_stream) cudaStreamDestroy(_meta_stream);
     if (_stream) cudaStreamDestroy(_stream);
 }
 
@@ -1515,7 +1522,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         int max_boxes = 1;
         for (int c : s.counts) max_boxes = std::max(max_boxes, c);
         if (total > _box_capacity) {
-            RB200_CUDA(cudaStreamSynchronize(_stream));
+            RB200_CUDA(cudaStreamSynchronize(_meta_stream));
             cudaFree(_d_boxes);
             cudaFree(_d_labels);
             cudaFreeHost(_h_box_stage);
@@ -1524,8 +1531,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             RB200_CUDA(cudaMalloc((void**)&_d_labels, _box_capacity * sizeof(int)));
             RB200_CUDA(cudaHostAlloc(&_h_box_stage, _box_capacity * 5 * sizeof(float) + (_batch + 1) * sizeof(int), cudaHostAllocDefault));
         } else {
-            // the staging block is reused: the previous batch's copies must have been issued and done
-            RB200_CUDA(cudaStreamSynchronize(_stream));
+            // the staging block is reused: the previous batch's three copies out of it must be done
+            RB200_CUDA(cudaEventSynchronize(_box_stage_free));
         }
         float* hb = (float*)_h_box_stage;
         int* hl = (int*)(hb + _box_capacity * 4);
@@ -1534,18 +1541,21 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         std::memcpy(hl, s.labels.data(), total * sizeof(int));
         ho[0] = 0;
         for (size_t i = 0; i < n; i++) ho[i + 1] = ho[i] + s.counts[i];
-        RB200_CUDA(cudaMemcpyAsync(_d_boxes, hb, total * 4 * sizeof(float), cudaMemcpyHostToDevice, _stream));
-        RB200_CUDA(cudaMemcpyAsync(_d_labels, hl, total * sizeof(int), cudaMemcpyHostToDevice, _stream));
-        RB200_CUDA(cudaMemcpyAsync(_d_offsets, ho, (n + 1) * sizeof(int), cudaMemcpyHostToDevice, _stream));
+        RB200_CUDA(cudaMemcpyAsync(_d_boxes, hb, total * 4 * sizeof(float), cudaMemcpyHostToDevice, _meta_stream));
+        RB200_CUDA(cudaMemcpyAsync(_d_labels, hl, total * sizeof(int), cudaMemcpyHostToDevice, _meta_stream));
+        RB200_CUDA(cudaMemcpyAsync(_d_offsets, ho, (n + 1) * sizeof(int), cudaMemcpyHostToDevice, _meta_stream));
+        RB200_CUDA(cudaEventRecord(_box_stage_free, _meta_stream));
         _h2d_bytes += total * 20 + (n + 1) * sizeof(int);
         if (_box_encoder) {
-            int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _stream);
+            int rc = rb200k_box_encode(_d_boxes, _d_labels, _d_offsets, (int)n, max_boxes, &_enc, s.d_enc_boxes, s.d_enc_labels, _meta_stream);
             if (rc != 0) RB200_THROW(rb200k_last_error());
         }
         if (_box_matcher) {
-            int rc = rb200k_box_iou_match(_d_boxes, _d_offsets, (int)n, max_boxes, &_match, s.d_matches, _stream);
+            int rc = rb200k_box_iou_match(_d_boxes, _d_offsets, (int)n, max_boxes, &_match, s.d_matches, _meta_stream);
             if (rc != 0) RB200_THROW(rb200k_last_error());
         }
+        RB200_CUDA(cudaEventRecord(_meta_done, _meta_stream));
+        RB200_CUDA(cudaStreamWaitEvent(_stream, _meta_done, 0));
     }
 
     // ---- 5. snapshot of the ROIs the user will see, completion event ----

@@ -302,6 +302,10 @@ class Pipeline {
     size_t _depth;
     RocalTensorOutputType _out_dtype;
     cudaStream_t _stream = nullptr;
+    // Box upload, encoder and matcher run on their own stream, beside the pixel kernels of the same batch; the batch's
+    // completion event waits for both.
+    cudaStream_t _meta_stream = nullptr;
+    cudaEvent_t _meta_done = nullptr, _box_stage_free = nullptr;
     bool _verified = false;
 
     std::vector<std::unique_ptr<TensorImpl>> _tensors;
