@@ -76,9 +76,9 @@ def main():
                 out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device=dev)
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
             report("cfg0 resize+CMN fp32 NCHW (batch 64, 256..512 px)", n, _time(fns, args.steps), algo)
-        elif op in ("color_twist", "brightness", "flip"):
+        elif op in ("color_twist", "brightness", "contrast", "flip"):
             n, rot = int(os.environ.get("RB200_OPBENCH_N", "256")), 4
-            code = {"color_twist": T.COLOR_TWIST, "brightness": T.COLOR_BRIGHTNESS, "flip": T.COLOR_NONE}[op]
+            code = {"color_twist": T.COLOR_TWIST, "brightness": T.COLOR_BRIGHTNESS, "contrast": T.COLOR_CONTRAST, "flip": T.COLOR_NONE}[op]
             fns = []
             for r in range(rot):
                 rng = S.rng_for(2, 100 + r)
