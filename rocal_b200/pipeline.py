@@ -292,10 +292,13 @@ class Pipeline(object):
         self._check(C.get_image_sizes(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
         return out
 
-    def get_image_id(self):
-        """rocalGetImageId: the annotation file's id of every image of the batch (COCO reader), int32 [N]."""
+    def get_image_id(self, array=None):
+        """rocalGetImageId: the annotation file's id of every image of the batch (COCO reader), int32 [N]; written into
+        `array` too when one is given (the reference's calling form)."""
         out = np.zeros(self._batch_size, dtype=np.int32)
         self._check(C.get_image_ids(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        if array is not None:
+            np.asarray(array).reshape(-1)[:self._batch_size] = out
         return out
 
     def get_roi_image_sizes(self):
@@ -357,6 +360,50 @@ class Pipeline(object):
             C.get_bounding_boxes(self._handle, b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
                                  lab.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), c.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
         return b, lab, c
+
+    # ---- the reference's method names (rocAL_pybind/amd/rocal/pipeline.py:149-245) ----
+    def get_handle(self):
+        return self._handle
+
+    def get_bounding_box_count(self):
+        """rocalGetBoundingBoxCount: boxes in the whole batch."""
+        return int(self.get_bounding_boxes()[2].sum())
+
+    def get_bounding_box_cords(self):
+        """rocalGetBoundingBoxCords: one float32 [count_i, 4] array (normalized ltrb) per sample."""
+        b, _, c = self.get_bounding_boxes()
+        ends = np.cumsum(c)
+        return [b[e - k:e] for e, k in zip(ends, c)]
+
+    def get_bounding_box_labels(self):
+        """rocalGetBoundingBoxLabel: one int32 [count_i] array per sample."""
+        _, lab, c = self.get_bounding_boxes()
+        ends = np.cumsum(c)
+        return [lab[e - k:e] for e, k in zip(ends, c)]
+
+    def get_image_name_length(self, idx):
+        """rocalGetImageNameLen: fills idx (int32 [N]) with the name lengths, returns their sum."""
+        names = self.get_image_names()
+        for i, nm in enumerate(names):
+            idx[i] = len(nm.encode())
+        return sum(len(nm.encode()) for nm in names)
+
+    def get_image_name(self, array_len=0):
+        """rocalGetImageName: the names of the batch, concatenated."""
+        return "".join(self.get_image_names())
+
+    def get_img_sizes(self, array):
+        """rocalGetImageSizes into array (int32, N x 2: width, height)."""
+        np.asarray(array).reshape(-1)[:2 * self._batch_size] = self.get_image_sizes().reshape(-1)
+        return array
+
+    def get_roi_img_sizes(self, array):
+        """rocalGetROIImageSizes into array (int32, N x 2: width, height)."""
+        np.asarray(array).reshape(-1)[:2 * self._batch_size] = self.get_roi_image_sizes().reshape(-1)
+        return array
+
+    def rocal_reset_loaders(self):
+        return self.reset()
 
     def get_crop_windows(self, tensor):
         """[extension] n x (x, y, w, h) source window used by the crop-type operator that produced `tensor`."""

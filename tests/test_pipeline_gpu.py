@@ -288,6 +288,15 @@ def test_coco_source_pipeline(cuda, tmp_path):
     names = pipe.get_image_names()
     assert names == ["000.jpg", "001.jpg", "002.jpg", "003.jpg"]
     assert pipe.get_image_id().tolist() == [100, 101, 102, 103]            # rocalGetImageId: the file's image ids
+    ids = np.zeros(n, dtype=np.int32)
+    pipe.get_image_id(ids)
+    sizes = np.zeros((n, 2), dtype=np.int32)
+    pipe.get_img_sizes(sizes)
+    lens = np.zeros(n, dtype=np.int32)
+    assert ids.tolist() == [100, 101, 102, 103] and sizes.tolist() == pipe.get_image_sizes().tolist()
+    assert pipe.get_image_name_length(lens) == 28 and lens.tolist() == [7] * 4 and pipe.get_image_name(28) == "".join(names)
+    assert pipe.get_bounding_box_count() == sum(len(x) for x in pipe.get_bounding_box_labels())
+    assert [len(x) for x in pipe.get_bounding_box_cords()] == [len(x) for x in pipe.get_bounding_box_labels()]
     b2, l2, c2 = pipe.get_bounding_boxes()
     at = 0
     for nm, c in zip(names, c2):
