@@ -76,8 +76,15 @@ typedef struct rb200_resample_sample {
  *                    taps per axis, normalised weights, result truncated to uint8), the
  *                    arithmetic of resize_generic_pln1_hip_tensor
  *                    (rocAL/rocAL_hip/rocal_hip_kernels.cpp:487-589) applied to each channel.
+ *                    RB200_INTERP_BICUBIC / _LANCZOS / _GAUSSIAN / _NEAREST run the same skeleton with
+ *                    another weight function and base radius B (support = B*max(ratio,1) per side):
+ *                    bicubic = Keys' cubic with a = -0.5, B = 2; lanczos = sinc(x)*sinc(x/3), B = 3;
+ *                    gaussian = exp(-4 x^2), B = 1; nearest = one tap, B = 0.5. The reference keeps
+ *                    these four filters in the RPP library, so their definitions here are this
+ *                    library's own (rocal_api_types.h:347-367 only names them).
  */
-enum { RB200_INTERP_BILINEAR = 0, RB200_INTERP_TRIANGULAR = 1 };
+enum { RB200_INTERP_BILINEAR = 0, RB200_INTERP_TRIANGULAR = 1, RB200_INTERP_BICUBIC = 2, RB200_INTERP_LANCZOS = 3,
+       RB200_INTERP_GAUSSIAN = 4, RB200_INTERP_NEAREST = 5 };
 typedef struct rb200_resample_params {
     void* out;
     int32_t out_w, out_h;

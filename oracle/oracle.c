@@ -138,6 +138,59 @@ static inline float tri_coeff(const tri_axis* a, float weight, int j) {
     return c < 0.f ? 0.f : c;
 }
 
+/* The other filters of the resize family on the same skeleton. The reference names them
+ * (rocAL/include/api/rocal_api_types.h:347-367) but their arithmetic lives in RPP, so these
+ * definitions are this library's own: base radius B per filter, radius = B * max(ratio, 1),
+ * scale = 1 / max(ratio, 1), the weight function evaluated at (weight - radius + j) * scale. */
+static inline float filter_base_radius(int filter) {
+    switch (filter) {
+        case RB200_INTERP_BICUBIC: return 2.0f;
+        case RB200_INTERP_LANCZOS: return 3.0f;
+        case RB200_INTERP_NEAREST: return 0.5f;
+        default: return 1.0f;   /* triangular, gaussian */
+    }
+}
+
+static inline tri_axis filter_axis_make(float ratio, int filter) {
+    if (filter == RB200_INTERP_TRIANGULAR) return tri_axis_make(ratio);
+    tri_axis a;
+    const float stretch = ratio > 1.0f ? ratio : 1.0f;
+    a.radius = filter_base_radius(filter) * stretch;
+    a.scale = ratio > 1.0f ? 1.0f / ratio : 1.0f;
+    a.offset = (ratio - 1.0f) * 0.5f - a.radius;
+    a.ksize = (int)ceilf(a.radius * 2.0f);
+    if (a.ksize < 1) a.ksize = 1;
+    return a;
+}
+
+static inline float filter_weight(int filter, float x) {
+    const float ax = fabsf(x);
+    switch (filter) {
+        case RB200_INTERP_BICUBIC:   /* Keys, a = -0.5 */
+            if (ax >= 2.0f) return 0.f;
+            if (ax > 1.0f) return fmaf(-4.0f, ax, (ax * ax) * fmaf(-0.5f, ax, 2.5f)) + 2.0f;
+            return fmaf(ax * ax, fmaf(1.5f, ax, -2.5f), 1.0f);
+        case RB200_INTERP_LANCZOS: {
+            if (ax >= 3.0f) return 0.f;
+            if (ax < 1e-5f) return 1.0f;
+            const float px = ax * 3.14159265358979323846f;
+            return (3.0f * (sinf(px) * sinf(px * (1.0f / 3.0f)))) / (px * px);
+        }
+        case RB200_INTERP_GAUSSIAN: return expf(-4.0f * (x * x));
+        case RB200_INTERP_NEAREST: return 1.0f;
+        default: {
+            const float c = 1.0f - ax;
+            return c < 0.f ? 0.f : c;
+        }
+    }
+}
+
+static inline float filter_coeff(const tri_axis* a, int filter, float weight, int j) {
+    if (filter == RB200_INTERP_TRIANGULAR) return tri_coeff(a, weight, j);
+    return filter_weight(filter, ((weight - a->radius) + (float)j) * a->scale);
+}
+
+
 static inline uint8_t trunc_u8(float v) {
     v = fmaxf(fminf(v, 255.f), 0.f);   /* NaN -> 0 through fmaxf */
     return (uint8_t)v;
@@ -145,7 +198,7 @@ static inline uint8_t trunc_u8(float v) {
 
 static void triangular3(const uint8_t* img, uint32_t stride, int x_lo, int y_lo, int x_hi, int y_hi,
                         const tri_axis* ax, const tri_axis* ay, float ratio_w, float ratio_h, int dx, int dy,
-                        uint8_t out[3]) {
+                        int filter, uint8_t out[3]) {
     int fx, fy;
     float wx, wy;
     tri_loc(ax, ratio_w, dx, x_lo, x_hi, &fx, &wx);
@@ -155,12 +208,12 @@ static void triangular3(const uint8_t* img, uint32_t stride, int x_lo, int y_lo,
     for (int j = 0; j < ay->ksize; j++) {
         int row = clampi(fy + j, y_lo, y_hi);
         const uint8_t* r = img + (size_t)row * stride;
-        float rc = tri_coeff(ay, wy, j);
+        float rc = filter_coeff(ay, filter, wy, j);
         row_sum += rc;
         col_sum = 0.f;
         for (int k = 0; k < ax->ksize; k++) {
             int col = clampi(fx + k, x_lo, x_hi);
-            float cc = tri_coeff(ax, wx, k);
+            float cc = filter_coeff(ax, filter, wx, k);
             col_sum += cc;
             float coeff = cc * rc;
             for (int c = 0; c < 3; c++) acc[c] = fmaf((float)r[col * 3 + c], coeff, acc[c]);
@@ -196,7 +249,8 @@ ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, i
         int x_hi = q->roi_x + q->roi_w - 1, y_hi = q->roi_y + q->roi_h - 1;
         int cw = q->crop_w < p->out_w ? q->crop_w : p->out_w;
         int ch = q->crop_h < p->out_h ? q->crop_h : p->out_h;
-        tri_axis ax = tri_axis_make(ratio_w), ay = tri_axis_make(ratio_h);
+        const int generic = p->interpolation != RB200_INTERP_BILINEAR;
+        tri_axis ax = filter_axis_make(ratio_w, p->interpolation), ay = filter_axis_make(ratio_h, p->interpolation);
         for (int y = 0; y < ch; y++) {
             int ry = q->crop_y + y;
             float sy = (float)ry * ratio_h + off_h + (float)q->roi_y;
@@ -205,12 +259,13 @@ ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, i
                 float sx = (float)rx * ratio_w + off_w + (float)q->roi_x;
                 float v[3] = {0.f, 0.f, 0.f};
                 uint8_t t3[3] = {0, 0, 0};
-                if (p->interpolation == RB200_INTERP_TRIANGULAR)
-                    triangular3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, &ax, &ay, ratio_w, ratio_h, rx, ry, t3);
+                if (generic)
+                    triangular3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, &ax, &ay, ratio_w, ratio_h, rx, ry,
+                                p->interpolation, t3);
                 else
                     bilinear3(img, q->src_stride, q->roi_x, q->roi_y, x_hi, y_hi, sx, sy, 0, v);
                 for (int c = 0; c < 3; c++) {
-                    float u = p->interpolation == RB200_INTERP_TRIANGULAR ? (float)t3[c] : (float)sat_u8(v[c]);
+                    float u = generic ? (float)t3[c] : (float)sat_u8(v[c]);
                     float o = p->normalize ? fmaf(u, p->mul[c], p->add[c]) : u;
                     store_elem(p->out, p->out_dtype, out_index(p->out_layout, p->out_w, p->out_h, i, c, y, x), o);
                 }

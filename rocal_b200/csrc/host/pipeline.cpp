@@ -1124,9 +1124,11 @@ bool Pipeline::source_footprint(const uint8_t* h_tab, size_t i, int W, int H, in
             if (q.dst_w <= 0 || q.dst_h <= 0 || q.roi_w <= 0 || q.roi_h <= 0) return false;
             const double rx = (double)q.roi_w / q.dst_w, ry = (double)q.roi_h / q.dst_h;
             // reach of the filter on each side of the mapped position: one tap for bilinear, the radius
-            // max(ratio, 1) for the triangular filter
-            const bool tri = _nodes[st.resize].interpolation == RB200_INTERP_TRIANGULAR;
-            const double mx = tri ? std::max(rx, 1.0) + 1.0 : 1.0, my = tri ? std::max(ry, 1.0) + 1.0 : 1.0;
+            // B * max(ratio, 1) for the generic filters (B = 1 triangular / gaussian, 2 bicubic, 3 lanczos, 0.5 nearest)
+            const int interp = _nodes[st.resize].interpolation;
+            const bool tri = interp != RB200_INTERP_BILINEAR;
+            const double base = interp == RB200_INTERP_BICUBIC ? 2.0 : (interp == RB200_INTERP_LANCZOS ? 3.0 : 1.0);
+            const double mx = tri ? base * std::max(rx, 1.0) + 1.0 : 1.0, my = tri ? base * std::max(ry, 1.0) + 1.0 : 1.0;
             ax0 = q.roi_x + (int)std::floor(q.crop_x * rx - mx) - 1;
             ay0 = q.roi_y + (int)std::floor(q.crop_y * ry - my) - 1;
             ax1 = q.roi_x + (int)std::ceil((q.crop_x + q.crop_w) * rx + mx - 1.0) + 2;

@@ -116,11 +116,17 @@ void resize_shapes(TensorImpl* in, unsigned dest_w, unsigned dest_h, int scaling
     nd.max_h = min_max ? resize_longer : max_h;
 }
 
-// Resize-type operators take the bilinear and the triangular filter.
+// Resize-type operators take every filter of RocalResizeInterpolationType (rocal_api_types.h:347-367).
 int resize_interpolation(int interpolation) {
-    if (interpolation == ROCAL_LINEAR_INTERPOLATION) return RB200_INTERP_BILINEAR;
-    if (interpolation == ROCAL_TRIANGULAR_INTERPOLATION) return RB200_INTERP_TRIANGULAR;
-    RB200_THROW("resize implements ROCAL_LINEAR_INTERPOLATION and ROCAL_TRIANGULAR_INTERPOLATION only");
+    switch (interpolation) {
+        case ROCAL_LINEAR_INTERPOLATION: return RB200_INTERP_BILINEAR;
+        case ROCAL_TRIANGULAR_INTERPOLATION: return RB200_INTERP_TRIANGULAR;
+        case ROCAL_CUBIC_INTERPOLATION: return RB200_INTERP_BICUBIC;
+        case ROCAL_LANCZOS_INTERPOLATION: return RB200_INTERP_LANCZOS;
+        case ROCAL_GAUSSIAN_INTERPOLATION: return RB200_INTERP_GAUSSIAN;
+        case ROCAL_NEAREST_NEIGHBOR_INTERPOLATION: return RB200_INTERP_NEAREST;
+        default: RB200_THROW("unknown interpolation type " + std::to_string(interpolation));
+    }
 }
 
 void check_interpolation(int interpolation) {

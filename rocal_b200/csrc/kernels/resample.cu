@@ -42,6 +42,7 @@ struct ResampleLaunch {
     int ns, ns_log2;    // stream kernel: ring stages (power of two)
     int pair_ok;        // paired (2-element) stores are aligned
     int normalize, fill_padding;
+    int filter;         // generic-filter kernel: RB200_INTERP_* (triangular, bicubic, lanczos, gaussian, nearest)
     float mul[3], add[3];
     uint32_t magic;     // 0x4B000000 (bits of 2^23), passed as a parameter so that PRMT reads it
                         // from the constant bank instead of a re-materialised register
@@ -866,6 +867,88 @@ __device__ __forceinline__ void tri_column(const uint8_t* __restrict__ img, cons
     }
 }
 
+// The other filters of the resize family on the same skeleton (weight functions and base radii of this library's
+// own choosing, see rb200_kernels.h): radius = B * max(ratio, 1), scale = 1 / max(ratio, 1), the weight function
+// evaluated at (weight - radius + j) * scale. Same operation order as the CPU restatement; lanczos and gaussian go
+// through sinf / expf, which differ from the host's by rounding.
+__device__ __forceinline__ TriAxis filter_axis_make(float ratio, int filter) {
+    if (filter == RB200_INTERP_TRIANGULAR) return tri_axis_make(ratio);
+    const float base = filter == RB200_INTERP_BICUBIC ? 2.0f : (filter == RB200_INTERP_LANCZOS ? 3.0f : (filter == RB200_INTERP_NEAREST ? 0.5f : 1.0f));
+    TriAxis a;
+    a.radius = mul_rn(base, ratio > 1.0f ? ratio : 1.0f);
+    a.scale = ratio > 1.0f ? div_rn(1.0f, ratio) : 1.0f;
+    a.offset = sub_rn(mul_rn(sub_rn(ratio, 1.0f), 0.5f), a.radius);
+    a.ksize = max(1, (int)ceilf(mul_rn(a.radius, 2.0f)));
+    return a;
+}
+__device__ __forceinline__ float filter_weight(int filter, float x) {
+    const float ax = fabsf(x);
+    if (filter == RB200_INTERP_BICUBIC) {
+        if (ax >= 2.0f) return 0.f;
+        if (ax > 1.0f) return add_rn(fmaf(-4.0f, ax, mul_rn(mul_rn(ax, ax), fmaf(-0.5f, ax, 2.5f))), 2.0f);
+        return fmaf(mul_rn(ax, ax), fmaf(1.5f, ax, -2.5f), 1.0f);
+    }
+    if (filter == RB200_INTERP_LANCZOS) {
+        if (ax >= 3.0f) return 0.f;
+        if (ax < 1e-5f) return 1.0f;
+        const float px = mul_rn(ax, 3.14159265358979323846f);
+        return div_rn(mul_rn(3.0f, mul_rn(sinf(px), sinf(mul_rn(px, 1.0f / 3.0f)))), mul_rn(px, px));
+    }
+    if (filter == RB200_INTERP_GAUSSIAN) return expf(mul_rn(-4.0f, mul_rn(x, x)));
+    if (filter == RB200_INTERP_NEAREST) return 1.0f;
+    const float c = sub_rn(1.0f, ax);
+    return c < 0.f ? 0.f : c;
+}
+__device__ __forceinline__ float filter_coeff(const TriAxis& a, int filter, float weight, int j) {
+    return filter_weight(filter, mul_rn(add_rn(sub_rn(weight, a.radius), (float)j), a.scale));
+}
+
+// All output rows of one thread for a filter chosen at run time (nothing hoisted).
+template <typename OutT, int LAYOUT>
+__device__ __forceinline__ void filter_column(const uint8_t* __restrict__ img, const rb200_resample_sample& s, const ResampleLaunch& L,
+                                              OutT* out, int n, int xi, int tile_y0, int rows_valid, const TriAxis& ax,
+                                              const TriAxis& ay, float ratio_w, float ratio_h) {
+    const int x_lo = s.roi_x, y_lo = s.roi_y;
+    const int x_hi = s.roi_x + s.roi_w - 1, y_hi = s.roi_y + s.roi_h - 1;
+    const int rx = s.crop_x + (s.mirror ? (s.crop_w - 1 - xi) : xi);
+    int fx;
+    float wx;
+    tri_loc(ax, ratio_w, rx, x_lo, x_hi, fx, wx);
+    for (int j0 = 0; j0 < rows_valid; j0++) {
+        int fy;
+        float wy;
+        tri_loc(ay, ratio_h, s.crop_y + tile_y0 + j0, y_lo, y_hi, fy, wy);
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, row_sum = 0.f, col_sum = 0.f;
+        for (int j = 0; j < ay.ksize; j++) {
+            const int row = min(max(fy + j, y_lo), y_hi);
+            const uint8_t* r = img + (size_t)row * s.src_stride;
+            const float rc = filter_coeff(ay, L.filter, wy, j);
+            row_sum = add_rn(row_sum, rc);
+            col_sum = 0.f;
+            for (int k = 0; k < ax.ksize; k++) {
+                const int col = min(max(fx + k, x_lo), x_hi);
+                const float c1 = filter_coeff(ax, L.filter, wx, k);
+                col_sum = add_rn(col_sum, c1);
+                const float coeff = mul_rn(c1, rc);
+                const uint8_t* px = r + col * 3;
+                acc0 = fmaf((float)__ldg(px), coeff, acc0);
+                acc1 = fmaf((float)__ldg(px + 1), coeff, acc1);
+                acc2 = fmaf((float)__ldg(px + 2), coeff, acc2);
+            }
+        }
+        if (row_sum == 0.f) row_sum = 1.f;
+        if (col_sum == 0.f) col_sum = 1.f;
+        const float inv = div_rn(1.0f, mul_rn(row_sum, col_sum));
+        float v[3] = {mul_rn(acc0, inv), mul_rn(acc1, inv), mul_rn(acc2, inv)};
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            v[c] = truncf(fmaxf(fminf(v[c], 255.f), 0.f));     // fmaxf sends NaN to 0
+            if (L.normalize) v[c] = fmaf(v[c], L.mul[c], L.add[c]);
+        }
+        store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, tile_y0 + j0, xi, v[0], v[1], v[2]);
+    }
+}
+
 template <typename OutT, int LAYOUT>
 __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t* __restrict__ arena,
                                                                   const rb200_resample_sample* __restrict__ samples,
@@ -886,7 +969,10 @@ __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t*
     if (rows_valid > 0 && xi < cw) {
         const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
         const float ratio_h = div_rn((float)s.roi_h, (float)s.dst_h);
-        const TriAxis ax = tri_axis_make(ratio_w), ay = tri_axis_make(ratio_h);
+        const TriAxis ax = filter_axis_make(ratio_w, L.filter), ay = filter_axis_make(ratio_h, L.filter);
+        if (L.filter != RB200_INTERP_TRIANGULAR) {
+            filter_column<OutT, LAYOUT>(img, s, L, out, n, xi, tile_y0, rows_valid, ax, ay, ratio_w, ratio_h);
+        } else
         // the tap count is the same for the whole sample, so this switch does not diverge
         switch (ax.ksize) {
 #define RB200_TRI_CASE(K) \
@@ -969,13 +1055,14 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
         set_error("rb200k_resample: bad out_dtype %d / out_layout %d", p->out_dtype, p->out_layout);
         return RB200_E_INVALID;
     }
-    if (p->interpolation != RB200_INTERP_BILINEAR && p->interpolation != RB200_INTERP_TRIANGULAR) {
+    if (p->interpolation < RB200_INTERP_BILINEAR || p->interpolation > RB200_INTERP_NEAREST) {
         set_error("rb200k_resample: bad interpolation %d", p->interpolation);
         return RB200_E_INVALID;
     }
     cudaStream_t stream = (cudaStream_t)stream_v;
 
     ResampleLaunch L;
+    L.filter = p->interpolation;
     L.out = p->out;
     L.out_w = p->out_w;
     L.out_h = p->out_h;
@@ -1059,7 +1146,7 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
                    (size_t)(2 * th + 2) * pitch;
         }
     }
-    if (p->interpolation == RB200_INTERP_TRIANGULAR) mode = MODE_TRIANGULAR;
+    if (p->interpolation != RB200_INTERP_BILINEAR) mode = MODE_TRIANGULAR;   // the generic-filter kernel
     L.th = th;
     L.pitch = pitch;
     L.twh = twh;

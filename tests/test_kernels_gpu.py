@@ -239,6 +239,39 @@ def test_resample_triangular(cuda, dtype, layout):
     assert not np.array_equal(bil.view(np.uint8), ref.view(np.uint8))      # it is a different filter
 
 
+@pytest.mark.parametrize("interpolation,exact", [(2, True), (5, True), (3, False), (4, False)])
+def test_resample_other_filters(cuda, interpolation, exact):
+    """Bicubic (2), lanczos (3), gaussian (4), nearest (5) on the generic-filter skeleton: down- and up-scaling, a
+    window with mirror, ragged sizes. Bicubic and nearest are bit-exact against the restatement; lanczos and gaussian
+    go through sinf / expf, so a truncated uint8 may differ by one level (tolerance 1 LSB)."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(27)
+    arena, hs, ws, offs = S.make_images(rng, 10, (50, 300), (50, 300))
+    t = S.classification_tables(rng, hs, ws, offs, resize_shorter=72, crop=64)
+    for i in range(3):
+        t[i]["dst_w"], t[i]["dst_h"] = int(ws[i] * 1.6), int(hs[i] * 1.25)
+        t[i]["crop_x"], t[i]["crop_y"] = 2, 1
+    for i in range(3, 5):
+        t[i]["roi_x"], t[i]["roi_y"] = ws[i] // 6, hs[i] // 5
+        t[i]["roi_w"], t[i]["roi_h"] = ws[i] // 2, hs[i] // 2
+        t[i]["dst_w"], t[i]["dst_h"], t[i]["crop_x"], t[i]["crop_y"] = 64, 64, 0, 0
+    for dtype, layout in ((T.UINT8, T.NHWC), (T.FP32, T.NCHW)):
+        mul, add = S.normalize_tables() if dtype != T.UINT8 else (None, None)
+        ref = O.resample(arena, t, 64, 64, dtype, layout, mul, add, interpolation=interpolation)
+        got = K.resample(_dev(arena, cuda), t, 64, 64, dtype, layout, mul, add, interpolation=interpolation).cpu().numpy()
+        if exact:
+            assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+        elif dtype == T.UINT8:
+            d = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+            assert d.max() <= 1 and (d != 0).mean() < 1e-3
+        else:
+            step = float(np.max(np.abs(np.asarray(mul, dtype=np.float32)))) * 1.0001          # one uint8 level after normalisation
+            d = np.abs(got - ref)
+            assert d.max() <= step and (d > 1e-6).mean() < 1e-3
+    tri = O.resample(arena, t, 64, 64, T.UINT8, T.NHWC, interpolation=1)
+    assert not np.array_equal(tri, O.resample(arena, t, 64, 64, T.UINT8, T.NHWC, interpolation=interpolation))
+
+
 def test_warp_affine_config3(cuda):
     """configs[3]: 480x640 images, rotation +-45 deg, scale 0.8..1.2, shift +-32 px, zero border (batch 32)."""
     from rocal_b200 import kernels as K

@@ -283,3 +283,27 @@ def test_triangular_properties():
         val = acc / (np.float64(rs) * np.float64(cs))
         # the float64 accumulation differs from the float32 fmaf chain by far less than one grey level
         assert np.all(np.abs(got[y, x].astype(np.float64) - np.floor(np.clip(val, 0, 255))) <= 1), (x, y)
+
+
+def test_other_filters_properties():
+    """Bicubic, lanczos, gaussian, nearest on the generic skeleton: a constant image stays constant (normalised
+    weights; truncation may cost one level), nearest up-scaling by 2 repeats every pixel, every filter differs from the
+    triangular one on a textured image."""
+    rng = S.rng_for(33)
+    const = np.full((40, 52, 3), 137, dtype=np.uint8)
+    t = np.zeros(1, dtype=T.RESAMPLE_SAMPLE)
+    t["src_stride"], t["roi_w"], t["roi_h"] = 52 * 3, 52, 40
+    for dst in ((17, 13), (90, 70)):
+        t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = dst[0], dst[1], dst[0], dst[1]
+        for interp in (2, 3, 4, 5):
+            out = O.resample(const.reshape(-1), t, dst[0], dst[1], T.UINT8, T.NHWC, interpolation=interp)
+            assert out.min() >= 136 and out.max() <= 137, (interp, dst)
+    img = rng.integers(0, 256, (20, 24, 3), dtype=np.uint8)
+    t["src_stride"], t["roi_w"], t["roi_h"] = 24 * 3, 24, 20
+    t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = 48, 40, 48, 40
+    up = O.resample(img.reshape(-1), t, 48, 40, T.UINT8, T.NHWC, interpolation=5)[0]
+    assert np.array_equal(up, np.repeat(np.repeat(img, 2, axis=0), 2, axis=1))
+    t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = 11, 9, 11, 9
+    tri = O.resample(img.reshape(-1), t, 11, 9, T.UINT8, T.NHWC, interpolation=1)
+    for interp in (2, 3, 4, 5):
+        assert not np.array_equal(tri, O.resample(img.reshape(-1), t, 11, 9, T.UINT8, T.NHWC, interpolation=interp))

@@ -598,7 +598,7 @@ def test_error_convention(cuda):
     assert src
     assert not C.resize(ctx, src, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 2)     # no size given
     assert b"must be specified" in C.get_error_message(ctx)
-    assert not C.resize(ctx, src, 10, 10, 0, 1, 0, 0, 0, 0, types.CUBIC_INTERPOLATION, 0, 2)
+    assert not C.resize(ctx, src, 10, 10, 0, 1, 0, 0, 0, 0, 9, 0, 2)                      # no such interpolation type
     assert C.run(ctx) == types.RUNTIME_ERROR                            # not verified
     r = C.resize(ctx, src, 10, 10, 1, 1, 0, 0, 0, 0, 1, 0, 2)
     assert r and C.verify(ctx) == types.OK
@@ -758,7 +758,7 @@ def test_random_crop_crop_resize_roi_resize(cuda):
                                   x_drift=fixed[2], y_drift=fixed[3])
         cr_rand = fn.resize_crop(img, resize_width=80, resize_height=80, output_layout=types.NCHW, output_dtype=types.FLOAT)
         roi = fn.roi_resize(img, resize_width=72, resize_height=56, roi_w=120, roi_h=90, roi_pos_x=17, roi_pos_y=9,
-                            interpolation_type=types.TRIANGULAR_INTERPOLATION)
+                            interpolation_type=types.CUBIC_INTERPOLATION)
         same = fn.nop(img)
         pipe.set_outputs(rc, cr_fixed, cr_rand, roi, same)
     pipe.build()
@@ -787,7 +787,7 @@ def test_random_crop_crop_resize_roi_resize(cuda):
 
         assert np.array_equal(o_fixed, stretched(exp_win, 96, 64, T.UINT8, T.NHWC))
         assert np.array_equal(o_rand, stretched(win_rand, 80, 80, T.FP32, T.NCHW))
-        assert np.array_equal(o_roi, stretched(win_roi, 72, 56, T.UINT8, T.NHWC, 1))
+        assert np.array_equal(o_roi, stretched(win_roi, 72, 56, T.UINT8, T.NHWC, 2))      # RB200_INTERP_BICUBIC
         for i in range(n):
             ih, iw, o = int(hs[i]), int(ws[i]), int(offs[i])
             im = arena[o:o + ih * iw * 3].reshape(ih, iw, 3)
