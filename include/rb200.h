@@ -231,6 +231,14 @@ RB200_API rb200_tensor rb200_brightness(rb200_context ctx, rb200_tensor in, int 
                                         rb200_param beta, int out_layout, int out_dtype);
 RB200_API rb200_tensor rb200_contrast(rb200_context ctx, rb200_tensor in, int is_output, rb200_param factor,
                                       rb200_param center, int out_layout, int out_dtype);
+/* rocalExposure (x * 2^factor), rocalGamma (255 * (x/255)^gamma), rocalColorTemp (R + adjustment, B - adjustment; an
+ * integer parameter). Null parameters take the reference's default ranges. */
+RB200_API rb200_tensor rb200_exposure(rb200_context ctx, rb200_tensor in, int is_output, rb200_param exposure_factor,
+                                      int out_layout, int out_dtype);
+RB200_API rb200_tensor rb200_gamma(rb200_context ctx, rb200_tensor in, int is_output, rb200_param gamma, int out_layout,
+                                   int out_dtype);
+RB200_API rb200_tensor rb200_color_temp(rb200_context ctx, rb200_tensor in, int is_output, rb200_param adjustment,
+                                        int out_layout, int out_dtype);
 RB200_API rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout,
                                  int out_dtype);
 RB200_API rb200_tensor rb200_saturation(rb200_context ctx, rb200_tensor in, int is_output, rb200_param sat,

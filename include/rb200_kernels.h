@@ -115,9 +115,11 @@ RB200_API int rb200k_resample(const uint8_t* arena, const rb200_resample_sample*
 
 enum {
     RB200_COLOR_NONE = 0,        /* copy (crop, flip, CropMirrorNormalize, to_tensor)        */
-    RB200_COLOR_BRIGHTNESS = 1,  /* y = alpha*x + beta                                       */
+    RB200_COLOR_BRIGHTNESS = 1,  /* y = alpha*x + beta; a non-zero hue field tilts the offset: beta + hue for
+                                    R, beta - hue for B (exposure and colour temperature are this operator)  */
     RB200_COLOR_CONTRAST = 2,    /* y = (x - beta)*alpha + beta  (alpha=factor, beta=center) */
-    RB200_COLOR_TWIST = 3        /* hue/saturation in HSV, then y = alpha*x + beta           */
+    RB200_COLOR_TWIST = 3,       /* hue/saturation in HSV, then y = alpha*x + beta           */
+    RB200_COLOR_GAMMA = 4        /* y = 255 * (x/255)^alpha                                  */
 };
 
 /* One sample of a pointwise launch (64 bytes). The window roi_w x roi_h at (roi_x, roi_y) of

@@ -292,6 +292,24 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalWarpAffineFixed /* [449] */ (
     bool is_output, unsigned int dest_height = 0, unsigned int dest_width = 0,
     RocalResizeInterpolationType interpolation_type = ROCAL_LINEAR_INTERPOLATION,
     RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalGamma /* [269] */ (
+    RocalContext context, RocalTensor input, bool is_output, RocalFloatParam gamma = NULL,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalGammaFixed /* [285] */ (
+    RocalContext context, RocalTensor input, float gamma, bool is_output, RocalTensorLayout output_layout = ROCAL_NONE,
+    RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalColorTemp /* [667] */ (
+    RocalContext context, RocalTensor input, bool is_output, RocalIntParam adjustment = NULL,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalColorTempFixed /* [683] */ (
+    RocalContext context, RocalTensor input, int adjustment, bool is_output, RocalTensorLayout output_layout = ROCAL_NONE,
+    RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalExposure /* [763] */ (
+    RocalContext context, RocalTensor input, bool is_output, RocalFloatParam exposure_factor = NULL,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalExposureFixed /* [779] */ (
+    RocalContext context, RocalTensor input, float exposure_factor, bool is_output, RocalTensorLayout output_layout = ROCAL_NONE,
+    RocalTensorOutputType output_datatype = ROCAL_UINT8);
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalHue /* [794] */ (
     RocalContext context, RocalTensor input, bool is_output, RocalFloatParam hue = NULL,
     RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);

@@ -345,8 +345,13 @@ ORC_API int orc_pointwise(const uint8_t* arena, const rb200_pointwise_sample* s,
                 float px[3] = {(float)row[sx * 3], (float)row[sx * 3 + 1], (float)row[sx * 3 + 2]};
                 float v[3];
                 switch (p->color_op) {
-                    case RB200_COLOR_BRIGHTNESS:
-                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * px[c] + q->beta);
+                    case RB200_COLOR_BRIGHTNESS: {   /* hue tilts the offset: exposure / colour temperature are this case */
+                        const float bc[3] = {q->beta + q->hue, q->beta, q->beta - q->hue};
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * px[c] + bc[c]);
+                        break;
+                    }
+                    case RB200_COLOR_GAMMA:
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(255.0f * powf(px[c] * (1.0f / 255.0f), q->alpha));
                         break;
                     case RB200_COLOR_CONTRAST:
                         for (int c = 0; c < 3; c++) v[c] = (float)sat_u8((px[c] - q->beta) * q->alpha + q->beta);

@@ -104,6 +104,9 @@ flip = _proto("rb200_flip", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 brightness = _proto("rb200_brightness", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 contrast = _proto("rb200_contrast", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 hue = _proto("rb200_hue", _P, _P, _P, c_int, _P, c_int, c_int)
+exposure = _proto("rb200_exposure", _P, _P, _P, c_int, _P, c_int, c_int)
+gamma = _proto("rb200_gamma", _P, _P, _P, c_int, _P, c_int, c_int)
+color_temp = _proto("rb200_color_temp", _P, _P, _P, c_int, _P, c_int, c_int)
 saturation = _proto("rb200_saturation", _P, _P, _P, c_int, _P, c_int, c_int)
 color_twist = _proto("rb200_color_twist", _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int)
 warp_affine = _proto("rb200_warp_affine", _P, _P, _P, c_int, c_uint, c_uint, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int)

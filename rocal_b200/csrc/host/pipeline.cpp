@@ -545,7 +545,7 @@ void Pipeline::set_box_matcher(const float* anchors, size_t num_anchors, float h
 
 static bool is_color(NodeKind k) {
     return k == NodeKind::BRIGHTNESS || k == NodeKind::CONTRAST || k == NodeKind::HUE || k == NodeKind::SATURATION ||
-           k == NodeKind::COLOR_TWIST;
+           k == NodeKind::COLOR_TWIST || k == NodeKind::EXPOSURE || k == NodeKind::GAMMA || k == NodeKind::COLOR_TEMP;
 }
 
 void Pipeline::plan() {
@@ -1410,6 +1410,16 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                     };
                     switch (C.kind) {
                         case NodeKind::BRIGHTNESS: q.alpha = val(0, 1.f); q.beta = val(1, 0.f); break;
+                        // exposure: x * 2^factor; colour temperature: R + adjustment, B - adjustment (brightness
+                        // operator with a tilted offset); gamma: its own operator with alpha = gamma
+                        case NodeKind::EXPOSURE: q.alpha = std::exp2(val(0, 0.f)); q.beta = 0.f; break;
+                        case NodeKind::GAMMA: q.alpha = val(0, 1.f); break;
+                        case NodeKind::COLOR_TEMP: {
+                            const auto& a = C.adjustment->array();
+                            q.alpha = 1.f; q.beta = 0.f;
+                            q.hue = (float)(a.size() == n ? a[i] : C.adjustment->get());
+                            break;
+                        }
                         case NodeKind::CONTRAST: q.alpha = val(0, 1.f); q.beta = val(1, 0.f); break;
                         case NodeKind::HUE: q.hue = val(2, 0.f); break;
                         case NodeKind::SATURATION: q.sat = val(3, 1.f); break;
@@ -1495,8 +1505,9 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             p.color_op = RB200_COLOR_NONE;
             if (st.color >= 0) {
                 NodeKind ck = _nodes[st.color].kind;
-                p.color_op = ck == NodeKind::BRIGHTNESS ? RB200_COLOR_BRIGHTNESS
-                             : ck == NodeKind::CONTRAST ? RB200_COLOR_CONTRAST : RB200_COLOR_TWIST;
+                p.color_op = (ck == NodeKind::BRIGHTNESS || ck == NodeKind::EXPOSURE || ck == NodeKind::COLOR_TEMP) ? RB200_COLOR_BRIGHTNESS
+                             : ck == NodeKind::CONTRAST ? RB200_COLOR_CONTRAST
+                             : ck == NodeKind::GAMMA    ? RB200_COLOR_GAMMA : RB200_COLOR_TWIST;
             }
             for (int c = 0; c < 3; c++) { p.mul[c] = 1.f; p.add[c] = 0.f; }
             if (st.window >= 0 && _nodes[st.window].normalize) {

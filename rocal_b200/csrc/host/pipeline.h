@@ -35,7 +35,7 @@ namespace rb200 {
 
 enum class NodeKind {
     RESIZE, RESIZE_CROP_MIRROR, RESIZE_MIRROR_NORMALIZE, CROP, CROP_MIRROR_NORMALIZE, SSD_RANDOM_CROP, FLIP,
-    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, WARP_AFFINE, ROTATE
+    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, EXPOSURE, GAMMA, COLOR_TEMP, WARP_AFFINE, ROTATE
 };
 
 // Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85) and, for
@@ -68,6 +68,7 @@ struct Node {
     float mul[3] = {1, 1, 1}, add[3] = {0, 0, 0};
     // colour: alpha, beta, hue, sat
     Parameter<float>* color[4] = {nullptr, nullptr, nullptr, nullptr};
+    Parameter<int>* adjustment = nullptr;   // COLOR_TEMP
     // warp: x0, x1, y0, y1, o0, o1 (API order) or angle
     Parameter<float>* affine[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     Parameter<float>* angle = nullptr;

@@ -938,6 +938,38 @@ rb200_tensor rb200_contrast(rb200_context ctx, rb200_tensor in, int is_output, r
     API_END
 }
 
+// rocalExposure / rocalGamma / rocalColorTemp (rocal_api_augmentation.h:763, 269, 667; default ranges
+// node_exposure.h:42, node_gamma.h:41, node_color_temperature.h:43). The reference holds no arithmetic for them
+// (RPP): exposure is x * 2^factor, gamma 255 * (x/255)^gamma, colour temperature R + adjustment / B - adjustment.
+rb200_tensor rb200_exposure(rb200_context ctx, rb200_tensor in, int is_output, rb200_param exposure_factor, int out_layout,
+                            int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::EXPOSURE;
+    nd.color[0] = float_param(exposure_factor, 0.15f, 0.95f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_gamma(rb200_context ctx, rb200_tensor in, int is_output, rb200_param gamma, int out_layout, int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::GAMMA;
+    nd.color[0] = float_param(gamma, 0.3f, 7.00f);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
+rb200_tensor rb200_color_temp(rb200_context ctx, rb200_tensor in, int is_output, rb200_param adjustment, int out_layout,
+                              int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::COLOR_TEMP;
+    nd.adjustment = int_param(adjustment, -99, 99);
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, out_layout, out_dtype, is_output);
+    API_END
+}
+
 rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout, int out_dtype) {
     API_BEGIN
     Node nd;

@@ -258,6 +258,24 @@ RocalTensor ROCAL_API_CALL rocalWarpAffineFixed(RocalContext c, RocalTensor in, 
                                 rb200_create_float_parameter(y0), rb200_create_float_parameter(y1), rb200_create_float_parameter(o0),
                                 rb200_create_float_parameter(o1), (int)it, (int)l, (int)t));
 }
+RocalTensor ROCAL_API_CALL rocalGamma(RocalContext c, RocalTensor in, bool out, RocalFloatParam g, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_gamma(c, in, out, g, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalGammaFixed(RocalContext c, RocalTensor in, float g, bool out, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_gamma(c, in, out, rb200_create_float_parameter(g), (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalColorTemp(RocalContext c, RocalTensor in, bool out, RocalIntParam a, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_color_temp(c, in, out, a, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalColorTempFixed(RocalContext c, RocalTensor in, int a, bool out, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_color_temp(c, in, out, rb200_create_int_parameter(a), (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalExposure(RocalContext c, RocalTensor in, bool out, RocalFloatParam e, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_exposure(c, in, out, e, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalExposureFixed(RocalContext c, RocalTensor in, float e, bool out, RocalTensorLayout l, RocalTensorOutputType t) {
+    return RT(rb200_exposure(c, in, out, rb200_create_float_parameter(e), (int)l, (int)t));
+}
 RocalTensor ROCAL_API_CALL rocalHue(RocalContext c, RocalTensor in, bool out, RocalFloatParam h, RocalTensorLayout l, RocalTensorOutputType t) {
     return RT(rb200_hue(c, in, out, h, (int)l, (int)t));
 }

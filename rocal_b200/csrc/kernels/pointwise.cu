@@ -164,9 +164,13 @@ template <int COLOR_OP>
 __device__ __forceinline__ void color_raw(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
                                           const float* rcp) {
     if (COLOR_OP == RB200_COLOR_BRIGHTNESS) {
-        v0 = add_rn(mul_rn(alpha, v0), beta);
+        v0 = add_rn(mul_rn(alpha, v0), add_rn(beta, hue));     // hue = 0 unless the offset is tilted (colour temperature)
         v1 = add_rn(mul_rn(alpha, v1), beta);
-        v2 = add_rn(mul_rn(alpha, v2), beta);
+        v2 = add_rn(mul_rn(alpha, v2), sub_rn(beta, hue));
+    } else if (COLOR_OP == RB200_COLOR_GAMMA) {
+        v0 = mul_rn(255.0f, powf(mul_rn(v0, 1.0f / 255.0f), alpha));
+        v1 = mul_rn(255.0f, powf(mul_rn(v1, 1.0f / 255.0f), alpha));
+        v2 = mul_rn(255.0f, powf(mul_rn(v2, 1.0f / 255.0f), alpha));
     } else if (COLOR_OP == RB200_COLOR_CONTRAST) {
         v0 = add_rn(mul_rn(sub_rn(v0, beta), alpha), beta);
         v1 = add_rn(mul_rn(sub_rn(v1, beta), alpha), beta);
@@ -310,6 +314,8 @@ __device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t 
         const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
         const float2 a2 = make_float2(alpha, alpha), b2 = make_float2(beta, beta);
         const float2 nb2 = make_float2(-beta, -beta);
+        // brightness: the offset of channel c (byte index mod 3) is beta + hue, beta, beta - hue
+        const float bc[3] = {add_rn(beta, hue), beta, sub_rn(beta, hue)};
 #pragma unroll
         for (int wd = 0; wd < 3; wd++) {
             uint32_t q[4];
@@ -320,7 +326,7 @@ __device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t 
                 x.y = __uint_as_float(__byte_perm(d[wd], magic, 0x7651u + hb));
                 x = add2(x, nk23);
                 if (COLOR_OP == RB200_COLOR_BRIGHTNESS)
-                    x = lanes_add(mul2(a2, x), b2);
+                    x = lanes_add(mul2(a2, x), make_float2(bc[(4 * wd + hb) % 3], bc[(4 * wd + hb + 1) % 3]));
                 else
                     x = lanes_add(mul2(add2(x, nb2), a2), b2);
                 q[hb] = cvt_sat_u8(x.x);
@@ -405,7 +411,8 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
         // (48 source bytes -> 48 output bytes per thread and step), which spreads the index arithmetic of an
         // item over four 4-pixel blocks and lets the result leave as three 16-byte stores; the item loop below
         // takes the remaining columns (and everything for the other output types).
-        const bool unit_path = sizeof(OutT) == 1 && LAYOUT == RB200_NHWC && !L.normalize && !L.reverse_channels;
+        const bool unit_path = sizeof(OutT) == 1 && LAYOUT == RB200_NHWC && !L.normalize && !L.reverse_channels &&
+                               COLOR_OP != RB200_COLOR_GAMMA;
         const int w16 = unit_path ? (w & ~15) : 0;
         const int gpr = (w - w16 + 3) >> 2;           // 4-pixel groups per row in the item loop
         const int items = rows * gpr;
@@ -506,7 +513,8 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                     permute_store_u8<LAYOUT>(pb, plane, d, s.flip_h != 0);
                     continue;
                 }
-                if (COLOR_OP != RB200_COLOR_NONE && sizeof(OutT) == 1 && !L.normalize && !L.reverse_channels && npx == 4) {
+                if (COLOR_OP != RB200_COLOR_NONE && COLOR_OP != RB200_COLOR_GAMMA && sizeof(OutT) == 1 && !L.normalize &&
+                    !L.reverse_channels && npx == 4) {
                     // uint8 in, uint8 out: the 12 result bytes are rebuilt in block order and leave through the
                     // same byte permutation as a plain crop / flip.
                     uint32_t e[3];
@@ -644,6 +652,7 @@ static int launch_color(int color_op, bool vec, dim3 grid, int threads, size_t s
         case RB200_COLOR_BRIGHTNESS: launch_one<OutT, LAYOUT, RB200_COLOR_BRIGHTNESS>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_CONTRAST: launch_one<OutT, LAYOUT, RB200_COLOR_CONTRAST>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_TWIST: launch_one<OutT, LAYOUT, RB200_COLOR_TWIST>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case RB200_COLOR_GAMMA: launch_one<OutT, LAYOUT, RB200_COLOR_GAMMA>(vec, grid, threads, smem, stream, arena, samples, L); break;
         default: set_error("rb200k_pointwise: bad color_op %d", color_op); return RB200_E_INVALID;
     }
     RB200_CHECK_LAUNCH("pointwise_kernel");

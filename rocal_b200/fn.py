@@ -196,6 +196,25 @@ def contrast(*inputs, contrast=None, contrast_center=None, device=None, output_l
     return _ret(p, C.contrast(p._handle, inputs[0], 0, _fparam(contrast), _fparam(contrast_center), output_layout, output_dtype))
 
 
+def exposure(*inputs, exposure=0.5, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalExposure (fn.py:78): x * 2^exposure; a float, a random parameter, or None for the reference's default range
+    0.15 .. 0.95."""
+    p = _pipe()
+    return _ret(p, C.exposure(p._handle, inputs[0], 0, _fparam(exposure), output_layout, output_dtype))
+
+
+def gamma_correction(*inputs, gamma=0.5, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalGamma: 255 * (x / 255)^gamma (None: the reference's default range 0.3 .. 7)."""
+    p = _pipe()
+    return _ret(p, C.gamma(p._handle, inputs[0], 0, _fparam(gamma), output_layout, output_dtype))
+
+
+def color_temp(*inputs, adjustment_value=50, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalColorTemp: R + adjustment, B - adjustment (an integer; None: the reference's default range -99 .. 99)."""
+    p = _pipe()
+    return _ret(p, C.color_temp(p._handle, inputs[0], 0, _iparam(adjustment_value), output_layout, output_dtype))
+
+
 def hue(*inputs, hue=None, device=None, seed=0, output_layout=types.NHWC, output_dtype=types.UINT8):
     p = _pipe()
     return _ret(p, C.hue(p._handle, inputs[0], 0, _fparam(hue), output_layout, output_dtype))

@@ -3,7 +3,7 @@ import numpy as np
 
 FP32, FP16, UINT8 = 0, 1, 2
 NHWC, NCHW = 0, 1
-COLOR_NONE, COLOR_BRIGHTNESS, COLOR_CONTRAST, COLOR_TWIST = 0, 1, 2, 3
+COLOR_NONE, COLOR_BRIGHTNESS, COLOR_CONTRAST, COLOR_TWIST, COLOR_GAMMA = 0, 1, 2, 3, 4
 
 RESAMPLE_SAMPLE = np.dtype([
     ("src_offset", "<u8"), ("src_stride", "<u4"),

@@ -145,12 +145,22 @@ def test_pointwise_properties():
     assert np.array_equal(O.pointwise(arena, t, 60, 40, T.COLOR_BRIGHTNESS), ident)
     t["hue"] = 360.0
     assert np.abs(O.pointwise(arena, t, 60, 40, T.COLOR_TWIST).astype(int) - ident.astype(int)).max() <= 1
-    t["alpha"], t["beta"] = 1.9, 20.0     # the reference's BrightnessFixed test case (unit_tests.cpp:753-756)
+    t["alpha"], t["beta"], t["hue"] = 1.9, 20.0, 0.0     # the reference's BrightnessFixed test case (unit_tests.cpp:753-756)
     b = O.pointwise(arena, t, 60, 40, T.COLOR_BRIGHTNESS)
     i = 0
     img = arena[int(offs[i]):int(offs[i]) + hs[i] * ws[i] * 3].reshape(hs[i], ws[i], 3).astype(np.float32)
     exp = np.clip(np.rint(np.float32(1.9) * img + np.float32(20.0)), 0, 255).astype(np.uint8)
     assert np.array_equal(b[i, :hs[i], :ws[i]], exp)
+    # a non-zero hue field tilts the brightness offset (colour temperature): R + 30, G, B - 30
+    t["alpha"], t["beta"], t["hue"] = 1.0, 0.0, 30.0
+    ct = O.pointwise(arena, t, 60, 40, T.COLOR_BRIGHTNESS)[0, :hs[0], :ws[0]].astype(np.int32)
+    assert np.array_equal(ct, np.clip(img.astype(np.int32) + np.array([30, 0, -30]), 0, 255))
+    # gamma 1 is the identity up to the rounding of powf; gamma 2 squares the normalised value
+    t["alpha"], t["hue"] = 1.0, 0.0
+    assert np.abs(O.pointwise(arena, t, 60, 40, T.COLOR_GAMMA).astype(int) - ident.astype(int)).max() <= 1
+    t["alpha"] = 2.0
+    g2 = O.pointwise(arena, t, 60, 40, T.COLOR_GAMMA)[0, :hs[0], :ws[0]].astype(np.float64)
+    assert np.abs(g2 - np.rint(img.astype(np.float64) ** 2 / 255.0)).max() <= 1
     # saturation 0 gives grey pixels (all channels equal to the value channel)
     t["alpha"], t["beta"], t["hue"], t["sat"] = 1.0, 0.0, 0.0, 0.0
     g = O.pointwise(arena, t, 60, 40, T.COLOR_TWIST)

@@ -853,3 +853,47 @@ def test_file_list_source(cuda, tmp_path):
     assert got[0][0] == ["im3.jpg", "im0.jpg", "im2.jpg"] and got[0][1] == [11, 5, 11]
     assert got[0][2] == [[imgs[k].shape[1], imgs[k].shape[0]] for k in (3, 0, 2)]
     pipe.rocal_release()
+
+
+def test_exposure_gamma_color_temp(cuda):
+    """rocalExposure, rocalGamma, rocalColorTemp through the pipeline against the oracle's definitions (x * 2^e;
+    255 * (x/255)^gamma; R + adjustment, B - adjustment): exposure and colour temperature are exact, gamma goes through
+    powf and may differ by one level."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(44)
+    n = 6
+    pipe = Pipeline(batch_size=n, device_id=0, seed=5)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=160, max_height=160)
+        e = fn.exposure(img, exposure=0.7)
+        g = fn.gamma_correction(img, gamma=2.2)
+        c = fn.color_temp(img, adjustment_value=-37)
+        cf = fn.color_temp(img, adjustment_value=25, output_layout=types.NCHW, output_dtype=types.FLOAT)
+        pipe.set_outputs(e, g, c, cf)
+    pipe.build()
+    arena, hs, ws, offs = S.make_images(rng, n, (64, 160), (64, 160), content="noise")
+    pipe.feed_ragged(arena, hs, ws, offs)
+    pipe.run()
+    oe, og, oc, ocf = [t.numpy() for t in pipe.get_output_tensors()]
+
+    def expected(op, alpha=1.0, beta=0.0, hue=0.0, dtype=T.UINT8, layout=T.NHWC):
+        t = np.zeros(n, dtype=T.POINTWISE_SAMPLE)
+        t["src_offset"], t["src_stride"], t["roi_w"], t["roi_h"] = offs, ws * 3, ws, hs
+        t["alpha"], t["beta"], t["hue"], t["sat"] = alpha, beta, hue, 1.0
+        return O.pointwise(arena, t, 160, 160, color_op=op, out_dtype=dtype, out_layout=layout, fill_padding=False)
+
+    def same_inside(got, exp, tol=0):
+        for i in range(n):
+            a = got[i, :hs[i], :ws[i]].astype(np.int32) if got.ndim == 4 and got.shape[-1] == 3 else got[i, :, :hs[i], :ws[i]]
+            b = exp[i, :hs[i], :ws[i]].astype(np.int32) if exp.ndim == 4 and exp.shape[-1] == 3 else exp[i, :, :hs[i], :ws[i]]
+            assert np.abs(a - b).max() <= tol, i
+
+    same_inside(oe, expected(T.COLOR_BRIGHTNESS, alpha=float(np.exp2(np.float32(0.7)))))
+    same_inside(oc, expected(T.COLOR_BRIGHTNESS, hue=-37.0))
+    same_inside(ocf, expected(T.COLOR_BRIGHTNESS, hue=25.0, dtype=T.FP32, layout=T.NCHW))
+    same_inside(og, expected(T.COLOR_GAMMA, alpha=2.2), tol=1)
+    # what the definitions mean on a pixel
+    i0 = arena[int(offs[0]):int(offs[0]) + 3].astype(np.int32)
+    assert oc[0, 0, 0].tolist() == [max(0, i0[0] - 37), i0[1], min(255, i0[2] + 37)]
+    pipe.rocal_release()
