@@ -197,6 +197,38 @@ def test_pointwise_crop_flip_normalize(cuda):
                 assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
 
 
+@pytest.mark.parametrize("op", [T.COLOR_BRIGHTNESS, T.COLOR_CONTRAST, T.COLOR_TWIST, T.COLOR_GAMMA])
+def test_color_ops_ragged_windows(cuda, op):
+    """Colour operators on ragged windows (widths 1..300, so the 16-pixel units, the 4-pixel items and the partial
+    groups of the uint8 path all run), horizontal / vertical flips, uint8 NHWC and normalised fp32 NCHW outputs."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(14)
+    arena, hs, ws, offs = S.make_images(rng, 12, (1, 70), (1, 300), content="noise")
+    n = len(hs)
+    t = S.color_twist_tables(rng, hs, ws, offs)
+    for i in range(n):
+        w = int(rng.integers(1, ws[i] + 1))
+        h = int(rng.integers(1, hs[i] + 1))
+        t[i]["roi_w"], t[i]["roi_h"] = w, h
+        t[i]["roi_x"] = (ws[i] - w) if i % 2 else 0
+        t[i]["roi_y"] = (hs[i] - h) if i % 3 else 0
+        t[i]["flip_h"], t[i]["flip_v"] = i & 1, (i >> 1) & 1
+    if op == T.COLOR_CONTRAST:
+        t["beta"] = rng.uniform(60, 200, n).astype(np.float32)
+    if op == T.COLOR_GAMMA:
+        t["alpha"] = rng.uniform(0.4, 3.0, n).astype(np.float32)
+    mul, add = S.normalize_tables()
+    for dtype, layout, m, a in ((T.UINT8, T.NHWC, None, None), (T.FP32, T.NCHW, mul, add)):
+        ref = O.pointwise(arena, t, 300, 70, op, dtype, layout, m, a)
+        got = K.pointwise(_dev(arena, cuda), t, 300, 70, op, dtype, layout, m, a).cpu().numpy()
+        if op != T.COLOR_GAMMA:
+            assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+        elif dtype == T.UINT8:
+            assert np.abs(got.astype(np.int32) - ref.astype(np.int32)).max() <= 1
+        else:
+            assert np.abs(got - ref).max() <= float(np.max(np.abs(np.asarray(mul, dtype=np.float32)))) * 1.0001
+
+
 def test_flip_twice_is_identity(cuda):
     from rocal_b200 import kernels as K
     rng = S.rng_for(14)
