@@ -239,6 +239,9 @@ RB200_API rb200_tensor rb200_gamma(rb200_context ctx, rb200_tensor in, int is_ou
                                    int out_dtype);
 RB200_API rb200_tensor rb200_color_temp(rb200_context ctx, rb200_tensor in, int is_output, rb200_param adjustment,
                                         int out_layout, int out_dtype);
+/* rocalBlend: in*ratio + in2*(1 - ratio) per pixel, rounded; both inputs have the same maximum size. */
+RB200_API rb200_tensor rb200_blend(rb200_context ctx, rb200_tensor in, rb200_tensor in2, int is_output, rb200_param ratio,
+                                   int out_layout, int out_dtype);
 RB200_API rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout,
                                  int out_dtype);
 RB200_API rb200_tensor rb200_saturation(rb200_context ctx, rb200_tensor in, int is_output, rb200_param sat,

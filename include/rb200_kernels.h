@@ -119,7 +119,9 @@ enum {
                                     R, beta - hue for B (exposure and colour temperature are this operator)  */
     RB200_COLOR_CONTRAST = 2,    /* y = (x - beta)*alpha + beta  (alpha=factor, beta=center) */
     RB200_COLOR_TWIST = 3,       /* hue/saturation in HSV, then y = alpha*x + beta           */
-    RB200_COLOR_GAMMA = 4        /* y = 255 * (x/255)^alpha                                  */
+    RB200_COLOR_GAMMA = 4,       /* y = 255 * (x/255)^alpha                                  */
+    RB200_COLOR_BLEND = 5        /* y = alpha*x + (1 - alpha)*x2, x2 = the same pixel of a second source image
+                                    at arena + src2_offset (row pitch src2_stride)            */
 };
 
 /* One sample of a pointwise launch (64 bytes). The window roi_w x roi_h at (roi_x, roi_y) of
@@ -131,7 +133,8 @@ typedef struct rb200_pointwise_sample {
     int32_t roi_x, roi_y, roi_w, roi_h;
     int32_t flip_h, flip_v;
     float alpha, beta, hue, sat;
-    int32_t reserved[3];
+    uint32_t src2_offset_lo, src2_offset_hi;   /* RB200_COLOR_BLEND: 64-bit byte offset of the second source image */
+    uint32_t src2_stride;                      /* relative to the arena pointer (wrap-around arithmetic), its pitch */
 } rb200_pointwise_sample;
 
 typedef struct rb200_pointwise_params {

@@ -292,6 +292,12 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalWarpAffineFixed /* [449] */ (
     bool is_output, unsigned int dest_height = 0, unsigned int dest_width = 0,
     RocalResizeInterpolationType interpolation_type = ROCAL_LINEAR_INTERPOLATION,
     RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalBlend /* [382] */ (
+    RocalContext context, RocalTensor input1, RocalTensor input2, bool is_output, RocalFloatParam ratio = NULL,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalBlendFixed /* [399] */ (
+    RocalContext context, RocalTensor input1, RocalTensor input2, float ratio, bool is_output,
+    RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalGamma /* [269] */ (
     RocalContext context, RocalTensor input, bool is_output, RocalFloatParam gamma = NULL,
     RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);

@@ -350,6 +350,13 @@ ORC_API int orc_pointwise(const uint8_t* arena, const rb200_pointwise_sample* s,
                         for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * px[c] + bc[c]);
                         break;
                     }
+                    case RB200_COLOR_BLEND: {
+                        const uint8_t* img2 = arena + (((uint64_t)q->src2_offset_hi << 32) | q->src2_offset_lo);
+                        const uint8_t* p2 = img2 + (size_t)sy * q->src2_stride + (size_t)sx * 3;
+                        const float w2 = 1.0f - q->alpha;
+                        for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(q->alpha * px[c] + w2 * (float)p2[c]);
+                        break;
+                    }
                     case RB200_COLOR_GAMMA:
                         for (int c = 0; c < 3; c++) v[c] = (float)sat_u8(255.0f * powf(px[c] * (1.0f / 255.0f), q->alpha));
                         break;

@@ -104,6 +104,7 @@ flip = _proto("rb200_flip", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 brightness = _proto("rb200_brightness", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 contrast = _proto("rb200_contrast", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 hue = _proto("rb200_hue", _P, _P, _P, c_int, _P, c_int, c_int)
+blend = _proto("rb200_blend", _P, _P, _P, _P, c_int, _P, c_int, c_int)
 exposure = _proto("rb200_exposure", _P, _P, _P, c_int, _P, c_int, c_int)
 gamma = _proto("rb200_gamma", _P, _P, _P, c_int, _P, c_int, c_int)
 color_temp = _proto("rb200_color_temp", _P, _P, _P, c_int, _P, c_int, c_int)

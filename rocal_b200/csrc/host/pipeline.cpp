@@ -1,5 +1,6 @@
 #include "pipeline.h"
 
+#include <algorithm>
 #include <cstdio>
 
 #include <chrono>
@@ -494,15 +495,22 @@ size_t Pipeline::last_batch_padded_size() {
 }
 
 TensorImpl* Pipeline::add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
-                               RocalTensorOutputType dt, bool is_output) {
+                               RocalTensorOutputType dt, bool is_output, TensorImpl* in2) {
     if (_verified) RB200_THROW("the graph is already verified");
-    if (!owns(in)) RB200_THROW("input tensor does not belong to this context");
+    if (!owns(in) || (in2 && !owns(in2))) RB200_THROW("input tensor does not belong to this context");
+    if (in2) {
+        if (in2->max_w != in->max_w || in2->max_h != in->max_h) RB200_THROW("the two inputs must have the same maximum size");
+        if (in2->dtype != ROCAL_UINT8 || in2->lay != ROCAL_NHWC) RB200_THROW("the input of an augmentation must be a uint8 NHWC tensor");
+        node.in2 = in2->id;
+        in2->consumers++;
+    }
     if (out_w == 0 || out_h == 0) RB200_THROW("output dimensions must be non-zero");
     if (lay == ROCAL_NONE) lay = in->lay;
     if (lay != ROCAL_NHWC && lay != ROCAL_NCHW) RB200_THROW("only NHWC and NCHW image layouts are supported");
     if (dt != ROCAL_UINT8 && dt != ROCAL_FP32 && dt != ROCAL_FP16) RB200_THROW("output type must be UINT8, FP32 or FP16");
     int id = (int)_tensors.size();
     _tensors.emplace_back(new TensorImpl(this, id, (int)_batch, (int)out_w, (int)out_h, dt, lay, is_output, false));
+    if (is_output) _output_order.push_back(id);
     node.in = in->id;
     node.out = id;
     _tensors.back()->producer = (int)_nodes.size();
@@ -636,6 +644,7 @@ void Pipeline::plan() {
             default:
                 st.kind = Step::POINTWISE;
                 st.color = (int)k;
+                st.in2_tensor = nd.in2;
         }
         TensorImpl* in = _tensors[st.in_tensor].get();
         TensorImpl* out = _tensors[st.out_tensor].get();
@@ -646,6 +655,13 @@ void Pipeline::plan() {
         out->materialized = true;
         _steps.push_back(st);
     }
+}
+
+void Pipeline::mark_output(TensorImpl* t) {
+    if (_verified) RB200_THROW("outputs must be set before rocalVerify");
+    if (!owns(t)) RB200_THROW("rocalSetOutputs: not a tensor of this context");
+    t->is_output = true;
+    if (std::find(_output_order.begin(), _output_order.end(), t->id) == _output_order.end()) _output_order.push_back(t->id);
 }
 
 void Pipeline::verify() {
@@ -668,8 +684,13 @@ void Pipeline::verify() {
             RB200_CUDA(cudaMalloc(&t->scratch, t->data_size()));
         }
     }
-    for (auto& t : _tensors)
-        if (t->is_output && !t->is_source) _output_list.items.push_back(t.get());
+    for (auto& t : _tensors)          // outputs flagged at creation that never went through mark_output
+        if (t->is_output && std::find(_output_order.begin(), _output_order.end(), t->id) == _output_order.end())
+            _output_order.push_back(t->id);
+    for (int id : _output_order) {
+        TensorImpl* t = _tensors[(size_t)id].get();
+        if (t->is_output && !t->is_source) _output_list.items.push_back(t);
+    }
     for (auto& s : _slots) {
         RB200_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
         RB200_CUDA(cudaMalloc(&s.d_tables, table_bytes));
@@ -1117,6 +1138,7 @@ bool Pipeline::source_footprint(const uint8_t* h_tab, size_t i, int W, int H, in
     bool any = false;
     for (size_t k = 0; k < _steps.size(); k++) {
         const Step& st = _steps[k];
+        if (st.in2_tensor == _source) return false;      // a blend reads the whole second image
         if (st.in_tensor != _source) continue;
         int ax0, ay0, ax1, ay1;
         if (st.kind == Step::RESAMPLE) {
@@ -1285,7 +1307,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         b.mem_kind == RB200_MEM_HOST_PINNED && !src->is_output) {
         int consumers = 0;
         bool gather = false;
-        for (const Step& st : _steps)
+        for (const Step& st : _steps) {
+            if (st.in2_tensor == _source) consumers += 2;    // a second-source reader rules zero-copy out
             if (st.in_tensor == _source) {
                 consumers++;
                 // kernels that fetch every tap on its own (affine gathers, the triangular filter) would cross
@@ -1293,6 +1316,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                 gather = gather || st.kind == Step::WARP ||
                          (st.kind == Step::RESAMPLE && _nodes[st.resize].interpolation != RB200_INTERP_BILINEAR);
             }
+        }
         if (consumers == 1 && !gather) {
             void* dp = nullptr;
             if (cudaHostGetDevicePointer(&dp, const_cast<void*>(b.arena), 0) == cudaSuccess && dp) {
@@ -1414,6 +1438,17 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                         // operator with a tilted offset); gamma: its own operator with alpha = gamma
                         case NodeKind::EXPOSURE: q.alpha = std::exp2(val(0, 0.f)); q.beta = 0.f; break;
                         case NodeKind::GAMMA: q.alpha = val(0, 1.f); break;
+                        case NodeKind::BLEND: {
+                            // the second source's view, as an offset from this step's base pointer
+                            const uint8_t* base2 = nullptr;
+                            const SampleView v2 = view_of(st.in2_tensor, i, base2);
+                            const uint64_t rel = (uint64_t)(uintptr_t)(base2 + v2.offset) - (uint64_t)(uintptr_t)base;
+                            q.src2_offset_lo = (uint32_t)rel;
+                            q.src2_offset_hi = (uint32_t)(rel >> 32);
+                            q.src2_stride = v2.stride;
+                            q.alpha = val(0, 0.5f);
+                            break;
+                        }
                         case NodeKind::COLOR_TEMP: {
                             const auto& a = C.adjustment->array();
                             q.alpha = 1.f; q.beta = 0.f;
@@ -1507,7 +1542,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                 NodeKind ck = _nodes[st.color].kind;
                 p.color_op = (ck == NodeKind::BRIGHTNESS || ck == NodeKind::EXPOSURE || ck == NodeKind::COLOR_TEMP) ? RB200_COLOR_BRIGHTNESS
                              : ck == NodeKind::CONTRAST ? RB200_COLOR_CONTRAST
-                             : ck == NodeKind::GAMMA    ? RB200_COLOR_GAMMA : RB200_COLOR_TWIST;
+                             : ck == NodeKind::GAMMA    ? RB200_COLOR_GAMMA
+                             : ck == NodeKind::BLEND    ? RB200_COLOR_BLEND : RB200_COLOR_TWIST;
             }
             for (int c = 0; c < 3; c++) { p.mul[c] = 1.f; p.add[c] = 0.f; }
             if (st.window >= 0 && _nodes[st.window].normalize) {

@@ -35,7 +35,7 @@ namespace rb200 {
 
 enum class NodeKind {
     RESIZE, RESIZE_CROP_MIRROR, RESIZE_MIRROR_NORMALIZE, CROP, CROP_MIRROR_NORMALIZE, SSD_RANDOM_CROP, FLIP,
-    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, EXPOSURE, GAMMA, COLOR_TEMP, WARP_AFFINE, ROTATE
+    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, EXPOSURE, GAMMA, COLOR_TEMP, BLEND, WARP_AFFINE, ROTATE
 };
 
 // Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85) and, for
@@ -54,6 +54,7 @@ struct CropSpec {
 struct Node {
     NodeKind kind;
     int in = -1, out = -1;
+    int in2 = -1;                      // second input tensor (BLEND)
     // resize family
     unsigned dest_w = 0, dest_h = 0, max_w = 0, max_h = 0;
     int scaling_mode = ROCAL_SCALING_MODE_STRETCH;
@@ -185,6 +186,7 @@ struct InputBatch {
 struct Step {
     enum Kind { RESAMPLE, POINTWISE, WARP } kind;
     int in_tensor, out_tensor;
+    int in2_tensor = -1;                         // POINTWISE with a second source (blend)
     int pre_crop = -1, resize = -1, post = -1;   // RESAMPLE: node indices
     int window = -1, color = -1, flip = -1;      // POINTWISE
     int warp = -1;                               // WARP
@@ -235,10 +237,12 @@ class Pipeline {
     void source_sizes(int* wh);
     void roi_image_sizes(int* wh);
     TensorImpl* add_node(Node node, TensorImpl* in, unsigned out_w, unsigned out_h, RocalTensorLayout lay,
-                         RocalTensorOutputType dt, bool is_output);
+                         RocalTensorOutputType dt, bool is_output, TensorImpl* in2 = nullptr);
     void set_box_encoder(const float* anchors, size_t num_anchors, float criteria, const float* means,
                          const float* stds, bool offset, float scale);
     void set_box_matcher(const float* anchors, size_t num_anchors, float high, float low, bool allow_low_quality);
+    // The user sees the outputs in the order in which they were declared (MasterGraph::set_output, master_graph.cpp:337-349).
+    void mark_output(TensorImpl* t);
     void verify();
 
     // ---- feeding (user thread) ----
@@ -313,6 +317,7 @@ class Pipeline {
     std::vector<Node> _nodes;
     std::vector<Step> _steps;
     TensorListImpl _output_list;
+    std::vector<int> _output_order;   // tensor ids in the order they became outputs (creation with is_output, rocalSetOutputs)
     int _source = -1;
 
     // box encoder

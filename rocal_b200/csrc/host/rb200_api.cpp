@@ -970,6 +970,23 @@ rb200_tensor rb200_color_temp(rb200_context ctx, rb200_tensor in, int is_output,
     API_END
 }
 
+// rocalBlend (rocal_api_augmentation.h:382; default ratio range node_blend.h:42): output = input1*ratio + input2*(1-ratio).
+rb200_tensor rb200_blend(rb200_context ctx, rb200_tensor in, rb200_tensor in2, int is_output, rb200_param ratio, int out_layout,
+                         int out_dtype) {
+    API_BEGIN
+    if (in2 == nullptr) {
+        std::cerr << "[ERR] Invalid input image\n";
+        return nullptr;
+    }
+    Node nd;
+    nd.kind = NodeKind::BLEND;
+    nd.color[0] = float_param(ratio, 0.1f, 0.9f);
+    RocalTensorLayout lay = (RocalTensorLayout)out_layout;
+    return static_cast<rocalTensor*>(p->add_node(std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, lay,
+                                                 (RocalTensorOutputType)out_dtype, is_output != 0, T(in2)));
+    API_END
+}
+
 rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout, int out_dtype) {
     API_BEGIN
     Node nd;
@@ -1045,8 +1062,8 @@ int rb200_set_outputs(rb200_context ctx, const rb200_tensor* tensors, size_t n) 
     try {
         if (P(ctx)->verified()) RB200_THROW("outputs must be set before rocalVerify");
         for (size_t i = 0; i < n; i++) {
-            if (!tensors || !tensors[i] || !P(ctx)->owns(T(tensors[i]))) RB200_THROW("rocalSetOutputs: not a tensor of this context");
-            T(tensors[i])->is_output = true;
+            if (!tensors || !tensors[i]) RB200_THROW("rocalSetOutputs: not a tensor of this context");
+            P(ctx)->mark_output(T(tensors[i]));
         }
     } catch (const std::exception& e) {
         report(P(ctx), e);

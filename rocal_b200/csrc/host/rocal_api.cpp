@@ -258,6 +258,14 @@ RocalTensor ROCAL_API_CALL rocalWarpAffineFixed(RocalContext c, RocalTensor in, 
                                 rb200_create_float_parameter(y0), rb200_create_float_parameter(y1), rb200_create_float_parameter(o0),
                                 rb200_create_float_parameter(o1), (int)it, (int)l, (int)t));
 }
+RocalTensor ROCAL_API_CALL rocalBlend(RocalContext c, RocalTensor in1, RocalTensor in2, bool out, RocalFloatParam r, RocalTensorLayout l,
+                                      RocalTensorOutputType t) {
+    return RT(rb200_blend(c, in1, in2, out, r, (int)l, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalBlendFixed(RocalContext c, RocalTensor in1, RocalTensor in2, float r, bool out, RocalTensorLayout l,
+                                           RocalTensorOutputType t) {
+    return RT(rb200_blend(c, in1, in2, out, rb200_create_float_parameter(r), (int)l, (int)t));
+}
 RocalTensor ROCAL_API_CALL rocalGamma(RocalContext c, RocalTensor in, bool out, RocalFloatParam g, RocalTensorLayout l, RocalTensorOutputType t) {
     return RT(rb200_gamma(c, in, out, g, (int)l, (int)t));
 }

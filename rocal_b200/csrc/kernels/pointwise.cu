@@ -614,7 +614,17 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const uint8_t* __restric
             const int sy = s.roi_y + (s.flip_v ? (s.roi_h - 1 - y) : y);
             const uint8_t* px = img + (size_t)sy * s.src_stride + (size_t)sx * 3;
             float v0 = (float)__ldg(px), v1 = (float)__ldg(px + 1), v2 = (float)__ldg(px + 2);
-            color_px<COLOR_OP>(v0, v1, v2, s.alpha, s.beta, s.hue, s.sat, rcp);
+            if (COLOR_OP == RB200_COLOR_BLEND) {
+                // the same pixel of the second source: alpha*x + (1 - alpha)*x2, rounded and saturated
+                const uint8_t* img2 = arena + (((uint64_t)s.src2_offset_hi << 32) | s.src2_offset_lo);
+                const uint8_t* p2 = img2 + (size_t)sy * s.src2_stride + (size_t)sx * 3;
+                const float w2 = sub_rn(1.0f, s.alpha);
+                v0 = sat_round_u8f(add_rn(mul_rn(s.alpha, v0), mul_rn(w2, (float)__ldg(p2))));
+                v1 = sat_round_u8f(add_rn(mul_rn(s.alpha, v1), mul_rn(w2, (float)__ldg(p2 + 1))));
+                v2 = sat_round_u8f(add_rn(mul_rn(s.alpha, v2), mul_rn(w2, (float)__ldg(p2 + 2))));
+            } else {
+                color_px<COLOR_OP>(v0, v1, v2, s.alpha, s.beta, s.hue, s.sat, rcp);
+            }
             if (L.reverse_channels) { float t = v0; v0 = v2; v2 = t; }
             if (L.normalize) {
                 v0 = fmaf(v0, L.mul[0], L.add[0]);
@@ -653,6 +663,9 @@ static int launch_color(int color_op, bool vec, dim3 grid, int threads, size_t s
         case RB200_COLOR_CONTRAST: launch_one<OutT, LAYOUT, RB200_COLOR_CONTRAST>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_TWIST: launch_one<OutT, LAYOUT, RB200_COLOR_TWIST>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_GAMMA: launch_one<OutT, LAYOUT, RB200_COLOR_GAMMA>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case RB200_COLOR_BLEND:   // two sources: the scalar kernel only
+            pointwise_kernel<OutT, LAYOUT, RB200_COLOR_BLEND><<<grid, threads, 0, stream>>>(arena, samples, L);
+            break;
         default: set_error("rb200k_pointwise: bad color_op %d", color_op); return RB200_E_INVALID;
     }
     RB200_CHECK_LAUNCH("pointwise_kernel");
@@ -702,7 +715,7 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     }
     L.ext_w = ext_w;
     L.ext_h = ext_h;
-    const bool vec = (p->out_w % 4 == 0) && (((uintptr_t)p->out & 15) == 0);
+    const bool vec = (p->out_w % 4 == 0) && (((uintptr_t)p->out & 15) == 0) && p->color_op != RB200_COLOR_BLEND;
     dim3 grid;
     int threads;
     L.pitch = 0;

@@ -196,6 +196,13 @@ def contrast(*inputs, contrast=None, contrast_center=None, device=None, output_l
     return _ret(p, C.contrast(p._handle, inputs[0], 0, _fparam(contrast), _fparam(contrast_center), output_layout, output_dtype))
 
 
+def blend(*inputs, ratio=None, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """rocalBlend (fn.py:37): inputs[0]*ratio + inputs[1]*(1 - ratio); ratio a float, a random parameter, or None for the
+    reference's default range 0.1 .. 0.9."""
+    p = _pipe()
+    return _ret(p, C.blend(p._handle, inputs[0], inputs[1], 0, _fparam(ratio), output_layout, output_dtype))
+
+
 def exposure(*inputs, exposure=0.5, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
     """rocalExposure (fn.py:78): x * 2^exposure; a float, a random parameter, or None for the reference's default range
     0.15 .. 0.95."""

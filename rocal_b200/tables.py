@@ -3,7 +3,7 @@ import numpy as np
 
 FP32, FP16, UINT8 = 0, 1, 2
 NHWC, NCHW = 0, 1
-COLOR_NONE, COLOR_BRIGHTNESS, COLOR_CONTRAST, COLOR_TWIST, COLOR_GAMMA = 0, 1, 2, 3, 4
+COLOR_NONE, COLOR_BRIGHTNESS, COLOR_CONTRAST, COLOR_TWIST, COLOR_GAMMA, COLOR_BLEND = 0, 1, 2, 3, 4, 5
 
 RESAMPLE_SAMPLE = np.dtype([
     ("src_offset", "<u8"), ("src_stride", "<u4"),
@@ -17,7 +17,7 @@ POINTWISE_SAMPLE = np.dtype([
     ("roi_x", "<i4"), ("roi_y", "<i4"), ("roi_w", "<i4"), ("roi_h", "<i4"),
     ("flip_h", "<i4"), ("flip_v", "<i4"),
     ("alpha", "<f4"), ("beta", "<f4"), ("hue", "<f4"), ("sat", "<f4"),
-    ("reserved", "<i4", (3,))], align=True)
+    ("src2_offset_lo", "<u4"), ("src2_offset_hi", "<u4"), ("src2_stride", "<u4")], align=True)
 
 WARP_SAMPLE = np.dtype([
     ("src_offset", "<u8"), ("src_stride", "<u4"),

@@ -897,3 +897,37 @@ def test_exposure_gamma_color_temp(cuda):
     i0 = arena[int(offs[0]):int(offs[0]) + 3].astype(np.int32)
     assert oc[0, 0, 0].tolist() == [max(0, i0[0] - 37), i0[1], min(255, i0[2] + 37)]
     pipe.rocal_release()
+
+
+def test_blend_two_inputs(cuda):
+    """rocalBlend: a node with two inputs - the source with its own flipped copy, and two colour operators of the
+    source - against the oracle's blend (alpha*x + (1-alpha)*x2, rounded)."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(45)
+    n = 5
+    pipe = Pipeline(batch_size=n, device_id=0, seed=6)
+    with pipe:
+        img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=120, max_height=100)
+        flipped = fn.flip(img, horizontal=1, vertical=0)
+        bright = fn.brightness(img, brightness=1.4, brightness_shift=10.0)
+        b1 = fn.blend(img, flipped, ratio=0.3)
+        b2 = fn.blend(bright, flipped, ratio=0.75, output_layout=types.NCHW, output_dtype=types.FLOAT)
+        pipe.set_outputs(b1, b2, flipped, bright)
+    pipe.build()
+    # same-sized images: the flipped copy then covers the same window as the source
+    arena, hs, ws, offs = S.make_images(rng, n, (100, 100), (120, 120), content="noise")
+    pipe.feed_ragged(arena, hs, ws, offs)
+    pipe.run()
+    o1, o2, ofl, obr = [t.numpy() for t in pipe.get_output_tensors()]
+    src = np.stack([arena[int(o):int(o) + 100 * 120 * 3].reshape(100, 120, 3) for o in offs])
+    assert np.array_equal(ofl, src[:, :, ::-1])
+
+    def blend(a, b, ratio):
+        r = np.float32(ratio)
+        v = r * a.astype(np.float32) + np.float32(np.float32(1.0) - r) * b.astype(np.float32)
+        return np.clip(np.rint(v), 0, 255)
+
+    assert np.array_equal(o1, blend(src, ofl, 0.3).astype(np.uint8))
+    assert np.array_equal(o2, blend(obr, ofl, 0.75).transpose(0, 3, 1, 2).astype(np.float32))
+    pipe.rocal_release()
