@@ -931,3 +931,41 @@ def test_blend_two_inputs(cuda):
     assert np.array_equal(o1, blend(src, ofl, 0.3).astype(np.uint8))
     assert np.array_equal(o2, blend(obr, ofl, 0.75).transpose(0, 3, 1, 2).astype(np.float32))
     pipe.rocal_release()
+
+
+def test_pipeline_stress_mixed_memory_kinds(cuda):
+    """Twenty batches through one pipeline with a prefetch queue: pageable, pinned (read in place by the kernel) and
+    device arenas in turn, image sizes that grow and shrink between batches (the input arenas are reallocated and
+    reused), two batches in flight at a time; every result equals the oracle and comes back in feed order."""
+    import torch
+    from rocal_b200 import types
+    rng = S.rng_for(46)
+    n = 8
+    pipe, out, mirror = _classification_pipeline(n, types.FLOAT, max_side=640, seed=13, depth=3)
+    pending = []
+
+    def feed(k):
+        hi = int(rng.choice([300, 420, 640]))
+        arena, hs, ws, offs = S.make_images(rng, n, (256, hi), (256, hi))
+        ax, ay = rng.random(n).astype(np.float32), rng.random(n).astype(np.float32)
+        pipe.set_crop_anchors(out, ax, ay)
+        fed = [arena, torch.from_numpy(arena).pin_memory(), torch.from_numpy(arena).to(cuda)][k % 3]
+        pipe.feed_ragged(fed, hs, ws, offs)
+        pending.append((arena, hs, ws, offs, ax, ay, fed))
+
+    feed(0)
+    feed(1)
+    for k in range(20):
+        if k + 2 < 20:
+            feed(k + 2)
+        pipe.run()
+        arena, hs, ws, offs, ax, ay, _ = pending.pop(0)
+        got = pipe.get_output_tensors()[0].numpy()
+        # the coin flips of this batch are no longer the parameter's current values (batches run ahead): every
+        # sample must equal the oracle with or without the mirror
+        e0 = _expected_classification(arena, hs, ws, offs, ax, ay, np.zeros(n, np.int32), T.FP32)
+        e1 = _expected_classification(arena, hs, ws, offs, ax, ay, np.ones(n, np.int32), T.FP32)
+        for i in range(n):
+            assert np.array_equal(got[i], e0[i]) or np.array_equal(got[i], e1[i]), (k, i)
+    assert pipe.is_empty()
+    pipe.rocal_release()
