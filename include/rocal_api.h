@@ -88,11 +88,14 @@ enum RocalExternalSourceMode {
     ROCAL_EXTSOURCE_FNAME = 0, ROCAL_EXTSOURCE_RAW_COMPRESSED = 1, ROCAL_EXTSOURCE_RAW_UNCOMPRESSED = 2
 };
 enum RocalLastBatchPolicy { ROCAL_LAST_BATCH_FILL = 0, ROCAL_LAST_BATCH_DROP = 1, ROCAL_LAST_BATCH_PARTIAL = 2 };
-struct RocalShardingInfo {
+struct RocalShardingInfo {   /* rocal_api_types.h:470-495: the same members and the same two constructors */
     RocalLastBatchPolicy last_batch_policy = ROCAL_LAST_BATCH_FILL;
     bool pad_last_batch_repeated = false;
     bool stick_to_shard = true;
     int32_t shard_size = -1;
+    RocalShardingInfo() = default;
+    RocalShardingInfo(RocalLastBatchPolicy policy, bool pad_repeated, bool stick, int size)
+        : last_batch_policy(policy), pad_last_batch_repeated(pad_repeated), stick_to_shard(stick), shard_size(size) {}
 };
 
 /* ---- tensors (rocal_api_tensor.h:38-94) ---- */

@@ -3,7 +3,7 @@
 // feeds images from a binary file and writes every result to another one. tests/test_cpp_client_gpu.py compiles
 // it with g++ (no CUDA headers needed), runs it and checks the results against the oracle.
 //
-//   client <in.bin> <out.bin>
+//   client <in.bin> <out.bin> [jpeg_folder]
 // in.bin : int32 n, then n x {int32 h, int32 w}, then the n images (uint8 HWC, tightly packed),
 //          then int32 total_boxes, n x int32 counts, total x 4 float32 ltrb, total x int32 labels,
 //          then int32 num_anchors, num_anchors x 4 float32
@@ -39,7 +39,7 @@ static std::vector<unsigned char> slurp(const char* path) {
     } while (0)
 
 int main(int argc, char** argv) {
-    if (argc != 3) return 2;
+    if (argc != 3 && argc != 4) return 2;
     std::vector<unsigned char> in = slurp(argv[1]);
     const unsigned char* p = in.data();
     auto rd_i32 = [&]() { int v; memcpy(&v, p, 4); p += 4; return v; };
@@ -189,6 +189,52 @@ int main(int argc, char** argv) {
         std::vector<int> sizes((size_t)n * 2);
         rocalGetImageSizes(ctx, sizes.data());
         fwrite(sizes.data(), 4, sizes.size(), out);
+        CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
+        rocalRelease(ctx);
+    }
+    // ---- graph 4 (with a folder of JPEG files): rocalCreateLabelReader + rocalFusedJpegCropSingleShard -> Resize ----
+    if (argc == 4) {
+        const int bs = 2;
+        RocalContext ctx = rocalCreate((size_t)bs, ROCAL_PROCESS_GPU, 0, 1, 2, ROCAL_FP32);
+        if (!ctx) return 1;
+        rocalSetSeed(321);
+        rocalCreateLabelReader(ctx, argv[3]);
+        std::vector<float> area{0.08f, 1.0f}, aspect{0.75f, 1.33333f};
+        RocalShardingInfo sharding(RocalLastBatchPolicy::ROCAL_LAST_BATCH_PARTIAL, true, true, -1);
+        RocalTensor src = rocalFusedJpegCropSingleShard(ctx, argv[3], ROCAL_COLOR_RGB24, 0, 1, false, area, aspect, 100, false, false,
+                                                        ROCAL_USE_USER_GIVEN_SIZE, 400, 400, sharding);
+        CHECK(ctx, src);
+        RocalTensor r = rocalResize(ctx, src, 64, 64, true, ROCAL_SCALING_MODE_STRETCH, {}, 0, 0, ROCAL_TRIANGULAR_INTERPOLATION);
+        CHECK(ctx, r);
+        CHECK(ctx, rocalVerify(ctx) == ROCAL_OK);
+        const int remaining = (int)rocalGetRemainingImages(ctx);
+        fwrite(&remaining, 4, 1, out);
+        int batches = 0;
+        while (!rocalIsEmpty(ctx)) {
+            CHECK(ctx, rocalRun(ctx) == ROCAL_OK);
+            batches++;
+            std::vector<int> labels(bs), sizes(bs * 2), lens(bs);
+            rocalGetImageLabels(ctx, labels.data());
+            rocalGetImageSizes(ctx, sizes.data());
+            const unsigned total = rocalGetImageNameLen(ctx, lens.data());
+            std::vector<char> names(total + 1, 0);
+            rocalGetImageName(ctx, names.data());
+            std::vector<unsigned> win(bs * 4);
+            unsigned seed = 0;
+            CHECK(ctx, rb200_get_decoder_crop_windows(ctx, win.data(), &seed) == 0);
+            const int padded = (int)rocalGetLastBatchPaddedSize(ctx);
+            fwrite(labels.data(), 4, bs, out);
+            fwrite(sizes.data(), 4, bs * 2, out);
+            fwrite(lens.data(), 4, bs, out);
+            fwrite(&total, 4, 1, out);
+            fwrite(names.data(), 1, total, out);
+            fwrite(win.data(), 4, bs * 4, out);
+            fwrite(&seed, 4, 1, out);
+            fwrite(&padded, 4, 1, out);
+            rocalTensor* t = rocalGetOutputTensors(ctx)->at(0);
+            CHECK(ctx, t->dims()[1] == 64 && t->dims()[2] == 64 && t->data_type() == ROCAL_UINT8);
+        }
+        fwrite(&batches, 4, 1, out);
         CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
         rocalRelease(ctx);
     }

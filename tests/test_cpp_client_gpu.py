@@ -42,7 +42,17 @@ def test_cpp_client(cuda, tmp_path):
         f.write(np.ascontiguousarray(labels, dtype=np.int32).tobytes())
         f.write(struct.pack("<i", len(anchors)))
         f.write(np.ascontiguousarray(anchors, dtype=np.float32).tobytes())
-    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True, timeout=300)
+    # a folder of JPEG files for graph 4: two classes, five files of known sizes
+    cv2 = pytest.importorskip("cv2")
+    jpeg_sizes = {}
+    for k, (cls, (jh, jw)) in enumerate([("ant", (120, 200)), ("ant", (300, 150)), ("bee", (90, 90)), ("bee", (240, 320)), ("bee", (64, 400))]):
+        (tmp_path / "jpeg" / cls).mkdir(parents=True, exist_ok=True)
+        pic = rng.integers(0, 256, (jh, jw, 3), dtype=np.uint8)
+        name = "p%d.jpg" % k
+        assert cv2.imwrite(str(tmp_path / "jpeg" / cls / name), pic)
+        jpeg_sizes[name] = (jw, jh, 0 if cls == "ant" else 1)
+    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin"), str(tmp_path / "jpeg")], capture_output=True,
+                       text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-2000:]
     raw = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
     pos = 0
@@ -104,6 +114,28 @@ def test_cpp_client(cuda, tmp_path):
         oh, ow = [int(v) for v in take(np.int32, 2)]
         outs.append((take(np.uint8, n * oh * ow * 3).reshape(n, oh, ow, 3), take(np.uint32, n * 4).reshape(n, 4)))
     sizes = take(np.int32, n * 2).reshape(n, 2)
+    # graph 4: rocalFusedJpegCropSingleShard on the folder, batch 2, LAST_BATCH_PARTIAL with repeated padding
+    assert int(take(np.int32, 1)[0]) == 6                         # 5 files padded to 3 batches of 2
+    seen = []
+    for b in range(3):
+        labels4 = take(np.int32, 2)
+        sizes4 = take(np.int32, 4).reshape(2, 2)
+        lens4 = take(np.int32, 2)
+        total4 = int(take(np.uint32, 1)[0])
+        names_raw = bytes(take(np.uint8, total4)).decode()
+        names4 = [names_raw[:lens4[0]], names_raw[lens4[0]:lens4[0] + lens4[1]]]
+        win4 = take(np.uint32, 8).reshape(2, 4)
+        seed4 = int(take(np.uint32, 1)[0])
+        padded4 = int(take(np.int32, 1)[0])
+        assert total4 == lens4.sum() and padded4 == (1 if b == 2 else 0)
+        for i, nm in enumerate(names4):
+            jw, jh, lab = jpeg_sizes[nm]
+            assert labels4[i] == lab and sizes4[i].tolist() == [jw, jh]
+        shapes = np.array([[jpeg_sizes[nm][1], jpeg_sizes[nm][0]] for nm in names4])
+        assert np.array_equal(win4, O.random_crop_windows(seed4, shapes, (0.75, 1.33333), (0.08, 1.0), 100))
+        seen += names4
+    assert seen == ["p0.jpg", "p1.jpg", "p2.jpg", "p3.jpg", "p4.jpg", "p4.jpg"]
+    assert int(take(np.int32, 1)[0]) == 3
     assert pos == len(raw)
     assert np.array_equal(outs[0][0], stretched(win, 120, 80)) and outs[0][1][:, 2:].tolist() == [[120, 80]] * n
     fixed_roi = np.tile(np.array([[20, 30, 150, 100]], dtype=np.int64), (n, 1))
