@@ -87,6 +87,14 @@ enum class RocalROICordsType { ROCAL_LTRB = 0, ROCAL_XYWH = 1 };
 enum RocalExternalSourceMode {
     ROCAL_EXTSOURCE_FNAME = 0, ROCAL_EXTSOURCE_RAW_COMPRESSED = 1, ROCAL_EXTSOURCE_RAW_UNCOMPRESSED = 2
 };
+/* Types that only absent entry points take; kept so that sources naming them still compile (rocal_api_types.h:163-203,
+ * 411-449, 500-509). */
+enum RocalFlipAxis { ROCAL_FLIP_HORIZONTAL = 0, ROCAL_FLIP_VERTICAL = 1 };
+enum RocalDecodeDevice { ROCAL_HW_DECODE = 0, ROCAL_SW_DECODE = 1 };
+enum RocalAudioBorderType { ROCAL_ZERO = 0, ROCAL_CLAMP = 1, ROCAL_REFLECT = 2 };
+enum RocalOutOfBoundsPolicy { ROCAL_PAD = 0, ROCAL_TRIMTOSHAPE = 1, ROCAL_ERROR = 2 };
+enum RocalMelScaleFormula { ROCAL_MELSCALE_SLANEY = 0, ROCAL_MELSCALE_HTK = 1 };
+enum RocalMissingComponentsBehaviour { ROCAL_MISSING_COMPONENT_ERROR = 0, ROCAL_MISSING_COMPONENT_SKIP = 1, ROCAL_MISSING_COMPONENT_EMPTY = 2 };
 enum RocalLastBatchPolicy { ROCAL_LAST_BATCH_FILL = 0, ROCAL_LAST_BATCH_DROP = 1, ROCAL_LAST_BATCH_PARTIAL = 2 };
 struct RocalShardingInfo {   /* rocal_api_types.h:470-495: the same members and the same two constructors */
     RocalLastBatchPolicy last_batch_policy = ROCAL_LAST_BATCH_FILL;
@@ -232,7 +240,9 @@ RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext roc
 /* rocal_api_meta_data.h:108: labels from a text file of "file_name label" lines; the following rocalJpegFileSource* reads
  * the listed files (relative to its source_path) in the list's order. */
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateTextFileBasedLabelReader(RocalContext rocal_context, const char* source_path);
-RB200_ROCAL void ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context, int* buf);
+/* rocal_api_meta_data.h:171: one one-element int32 host tensor per sample; the buffers are consecutive, so
+ * at(0)->buffer() reads as int[batch] (rb200_get_image_labels copies into a caller's array instead). */
+RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetImageLabels(RocalContext rocal_context);
 RB200_ROCAL void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext rocal_context, void* buf, int numOfClasses,
                                                          RocalOutputMemType output_mem_type);
 RB200_ROCAL void ROCAL_API_CALL rocalGetImageSizes(RocalContext rocal_context, int* buf);

@@ -452,6 +452,29 @@ void Pipeline::image_labels(int* buf) {
     std::memcpy(buf, s.file_labels.data(), _batch * sizeof(int));
 }
 
+// rocalGetImageLabels (rocal_api_meta_data.cpp:197-203): the labels of the current batch as a tensor list, one
+// one-element int32 host tensor per sample whose buffers lie one after the other, so that at(0)->buffer() reads
+// as int[batch] (what the reference's Python binding does, rocal_pybind.cpp:862-871).
+TensorListImpl* Pipeline::image_label_list() {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    const Slot& s = _slots[_held];
+    if (s.file_labels.size() != _batch) RB200_THROW("the current batch carries no labels (no file source / label reader)");
+    _label_values = s.file_labels;
+    if (_label_t.size() != _batch) {
+        _label_t.clear();
+        _label_list.items.clear();
+        for (size_t i = 0; i < _batch; i++) {
+            std::unique_ptr<TensorImpl> l(new TensorImpl(this, -12, 1, 1, 1, ROCAL_INT32, ROCAL_NHWC, false, false));
+            l->custom_dims = {1};
+            l->host_mem = true;
+            _label_list.items.push_back(l.get());
+            _label_t.push_back(std::move(l));
+        }
+    }
+    for (size_t i = 0; i < _batch; i++) _label_t[i]->current = &_label_values[i];
+    return &_label_list;
+}
+
 // rocalGetImageId (rocal_api_meta_data.cpp:185-195): the "id" of every image of the batch in the COCO annotation file.
 void Pipeline::image_ids(int* buf) {
     if (!_coco_source) RB200_THROW("rocalGetImageId needs a COCO source");

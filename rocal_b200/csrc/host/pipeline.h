@@ -231,6 +231,7 @@ class Pipeline {
     void decoder_crop_windows(unsigned* xywh, unsigned* batch_seed);
     void reset_loaders();
     void image_labels(int* buf);
+    TensorListImpl* image_label_list();   // rocalGetImageLabels: one int32 host tensor per sample, buffers consecutive
     void image_ids(int* buf);
     const std::vector<std::string>& image_names();
     size_t last_batch_padded_size();
@@ -336,6 +337,9 @@ class Pipeline {
     // per-sample views of the current batch's boxes (rebuilt by rocalRun)
     std::vector<std::unique_ptr<TensorImpl>> _bbox_t, _bbox_label_t;
     TensorListImpl _bbox_list, _bbox_label_list;
+    std::vector<std::unique_ptr<TensorImpl>> _label_t;
+    std::vector<int> _label_values;
+    TensorListImpl _label_list;
     void refresh_box_views();
 
     // box IoU matcher

@@ -161,7 +161,19 @@ RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSource(RocalContext ctx, const char*
     }
     return rocalJpegCOCOFileSourceSingleShard(ctx, source_path, json_path, color, 0, 1, is_output, shuffle, loop, p, max_width, max_height, d, si);
 }
-void ROCAL_API_CALL rocalGetImageLabels(RocalContext ctx, int* buf) { rb200_get_image_labels(ctx, buf); }
+RocalTensorList ROCAL_API_CALL rocalGetImageLabels(RocalContext ctx) {
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    try {
+        return P(ctx)->image_label_list();
+    } catch (const std::exception& e) {
+        P(ctx)->capture_error(e.what());
+        std::cerr << e.what() << '\n';
+        return nullptr;
+    }
+}
 void ROCAL_API_CALL rocalGetOneHotImageLabels(RocalContext ctx, void* buf, int num_classes, RocalOutputMemType m) {
     rb200_get_one_hot_image_labels(ctx, buf, num_classes, (int)m);
 }

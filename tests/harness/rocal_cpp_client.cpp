@@ -214,7 +214,10 @@ int main(int argc, char** argv) {
             CHECK(ctx, rocalRun(ctx) == ROCAL_OK);
             batches++;
             std::vector<int> labels(bs), sizes(bs * 2), lens(bs);
-            rocalGetImageLabels(ctx, labels.data());
+            RocalTensorList ll = rocalGetImageLabels(ctx);
+            CHECK(ctx, ll && ll->size() == (uint64_t)bs && ll->at(0)->backend() == ROCAL_CPU && ll->at(0)->data_type() == ROCAL_INT32);
+            for (int i = 0; i < bs; i++) labels[i] = static_cast<int*>(ll->at(0)->buffer())[i];
+            CHECK(ctx, *static_cast<int*>(ll->at(1)->buffer()) == labels[1]);
             rocalGetImageSizes(ctx, sizes.data());
             const unsigned total = rocalGetImageNameLen(ctx, lens.data());
             std::vector<char> names(total + 1, 0);
