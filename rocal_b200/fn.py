@@ -170,7 +170,8 @@ def resize_crop_mirror(*inputs, resize_width=0, resize_height=0, crop_w=0, crop_
 
 
 def ssd_random_crop(*inputs, p_threshold=None, crop_area_factor=None, crop_aspect_ratio=None, crop_pos_x=None,
-                    crop_pos_y=None, num_attempts=20, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+                    crop_pos_y=None, num_attempts=20, device=None, all_boxes_above_threshold=True, allow_no_crop=True, ltrb=True,
+                    output_layout=types.NHWC, output_dtype=types.UINT8):
     p = _pipe()
     return _ret(p, C.ssd_random_crop(p._handle, inputs[0], 0, num_attempts, output_layout, output_dtype))
 
@@ -249,7 +250,8 @@ def warp_affine(*inputs, dest_width=0, dest_height=0, matrix=[0, 0, 0, 0, 0, 0],
 
 
 def rotate(*inputs, angle=None, dest_width=0, dest_height=0, interpolation_type=types.LINEAR_INTERPOLATION, device=None,
-           output_layout=types.NHWC, output_dtype=types.UINT8):
+           fill_value=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+    """fill_value is accepted and unused, as in the reference's wrapper (the border is zero)."""
     p = _pipe()
     return _ret(p, C.rotate(p._handle, inputs[0], 0, _fparam(angle), dest_width, dest_height, interpolation_type,
                             output_layout, output_dtype))
