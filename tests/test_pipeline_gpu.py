@@ -969,3 +969,63 @@ def test_pipeline_stress_mixed_memory_kinds(cuda):
             assert np.array_equal(got[i], e0[i]) or np.array_equal(got[i], e1[i]), (k, i)
     assert pipe.is_empty()
     pipe.rocal_release()
+
+
+def test_imagenet_style_train_and_val_pipelines(cuda, tmp_path):
+    """The keyword arguments a training script written for amd.rocal passes (Pipeline(... rocal_cpu, tensor_dtype,
+    tensor_layout, prefetch_queue_depth, mean, std, output_memory_type), decoders.image_slice / decoders.image with their
+    sharding arguments, resize with TRIANGULAR interpolation and SCALING_MODE_NOT_SMALLER, crop_mirror_normalize with a
+    coin flip, ROCALClassificationIterator(pipe, device=..., device_id=...)) are all accepted, and both loaders deliver
+    every file of the folder once per epoch with the folder's labels."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    import torch
+    from rocal_b200.plugin.pytorch import ROCALClassificationIterator
+    rng = S.rng_for(47)
+    imgs, streams = _jpeg_batch(rng, 6, (260, 420))
+    for split in ("train", "val"):
+        for i, sb in enumerate(streams):
+            d = tmp_path / split / ("n%02d" % (i % 3))
+            d.mkdir(parents=True, exist_ok=True)
+            (d / ("img_%d.JPEG" % i)).write_bytes(sb)
+    mean, std = [0.485 * 255, 0.456 * 255, 0.406 * 255], [0.229 * 255, 0.224 * 255, 0.225 * 255]
+    common = dict(batch_size=2, num_threads=4, device_id=0, seed=10, rocal_cpu=False, tensor_dtype=types.FLOAT,
+                  tensor_layout=types.NCHW, prefetch_queue_depth=6, mean=mean, std=std, output_memory_type=types.DEVICE_MEMORY)
+
+    train = Pipeline(**common)
+    with train:
+        jpegs, labels = fn.readers.file(file_root=str(tmp_path / "train"))
+        dec = fn.decoders.image_slice(jpegs, output_type=types.RGB, file_root=str(tmp_path / "train"), shard_id=0, num_shards=1,
+                                      random_shuffle=True, max_decoded_width=500, max_decoded_height=500)
+        res = fn.resize(dec, resize_width=224, resize_height=224, output_layout=types.NHWC, output_dtype=types.UINT8,
+                        interpolation_type=types.TRIANGULAR_INTERPOLATION)
+        out = fn.crop_mirror_normalize(res, output_layout=types.NCHW, output_dtype=types.FLOAT, crop=(224, 224),
+                                       mirror=fn.random.coin_flip(probability=0.5), mean=mean, std=std)
+        train.set_outputs(out)
+    train.build()
+
+    val = Pipeline(**common)
+    with val:
+        jpegs, labels = fn.readers.file(file_root=str(tmp_path / "val"))
+        dec = fn.decoders.image(jpegs, file_root=str(tmp_path / "val"), max_decoded_width=500, max_decoded_height=500,
+                                output_type=types.RGB, shard_id=0, num_shards=1, random_shuffle=False)
+        res = fn.resize(dec, resize_shorter=256, scaling_mode=types.SCALING_MODE_NOT_SMALLER,
+                        interpolation_type=types.TRIANGULAR_INTERPOLATION, output_layout=types.NHWC, output_dtype=types.UINT8)
+        out = fn.crop_mirror_normalize(res, output_layout=types.NCHW, output_dtype=types.FLOAT, crop=(224, 224), mirror=0,
+                                       mean=mean, std=std)
+        val.set_outputs(out)
+    val.build()
+
+    for pipe in (train, val):
+        loader = ROCALClassificationIterator(pipe, device="cuda", device_id=0)
+        for epoch in range(2):
+            seen = []
+            for (batch,), target in loader:
+                assert batch.is_cuda and batch.shape == (2, 3, 224, 224) and batch.dtype == torch.float32
+                assert target.shape == (2,) and bool(torch.isfinite(batch).all())
+                names = pipe.get_image_names()
+                assert target.cpu().tolist() == [int(nm.split("_")[1].split(".")[0]) % 3 for nm in names]
+                seen += names
+            assert sorted(seen) == sorted("img_%d.JPEG" % i for i in range(6))
+            loader.reset()
+        pipe.rocal_release()
