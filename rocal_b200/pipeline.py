@@ -461,3 +461,52 @@ class Pipeline(object):
     def _check(self, status):
         if status != types.OK:
             raise RocalError(self.error_message())
+
+
+def pipeline_def(fn=None, **pipeline_kwargs):
+    """Decorator of amd.rocal.pipeline (pipeline.py:277-407 of the reference): turns a function that builds a graph and
+    returns its outputs into a Pipeline factory.
+
+        @pipeline_def(seed=7)
+        def loader(path, crop=224): ...; return images
+        pipe = loader("/data", batch_size=32, device_id=0)     # Pipeline arguments and the function's own, mixed
+
+    Keyword arguments named like a parameter of the function go to the function, the others must be Pipeline
+    constructor arguments (they override the ones given to the decorator); the function runs inside `with pipe:` and
+    what it returns becomes the pipeline's outputs. The pipeline is returned unbuilt."""
+    import functools
+    import inspect
+
+    def decorate(func):
+        spec = inspect.getfullargspec(func)
+        if spec.varkw is not None:
+            raise TypeError("a graph-defining function may not take **%s" % spec.varkw)
+        own = set(spec.args) | set(spec.kwonlyargs)
+        ctor = set(inspect.getfullargspec(Pipeline.__init__).args) - {"self"}
+
+        @functools.wraps(func)
+        def factory(*args, **kwargs):
+            fn_kwargs = {k: v for k, v in kwargs.items() if k in own}
+            ctor_kwargs = dict(pipeline_kwargs)
+            for k, v in kwargs.items():
+                if k in own:
+                    continue
+                if k == "debug":
+                    continue
+                if k not in ctor:
+                    raise TypeError("%s() got an unexpected keyword argument %r" % (func.__name__, k))
+                ctor_kwargs[k] = v
+            pipe = Pipeline(**ctor_kwargs)
+            with pipe:
+                outputs = func(*args, **fn_kwargs)
+                if outputs is None:
+                    outputs = ()
+                elif not isinstance(outputs, tuple):
+                    outputs = (outputs,)
+                pipe.set_outputs(*outputs)
+            return pipe
+
+        factory._is_pipeline_def = True
+        return factory
+
+    return decorate(fn) if fn is not None else decorate

@@ -1029,3 +1029,33 @@ def test_imagenet_style_train_and_val_pipelines(cuda, tmp_path):
             assert sorted(seen) == sorted("img_%d.JPEG" % i for i in range(6))
             loader.reset()
         pipe.rocal_release()
+
+
+def test_pipeline_def_and_generic_iterator(cuda, tmp_path):
+    """@pipeline_def builds a Pipeline from a graph function (decorator arguments, call-time overrides, the function's
+    own arguments), and plugin.generic.ROCALClassificationIterator hands the batches out as numpy arrays."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import pipeline_def
+    from rocal_b200.plugin.generic import ROCALClassificationIterator
+    rng = S.rng_for(48)
+    imgs, streams = _jpeg_batch(rng, 4, (100, 160))
+    for i, sb in enumerate(streams):
+        d = tmp_path / ("c%d" % (i // 2))
+        d.mkdir(exist_ok=True)
+        (d / ("f%d.jpg" % i)).write_bytes(sb)
+
+    @pipeline_def(seed=3, batch_size=4)
+    def loader(path, crop=48):
+        jpegs, labels = fn.readers.file(file_root=path)
+        images = fn.decoders.image(jpegs, file_root=path, max_decoded_width=160, max_decoded_height=160)
+        images = fn.resize(images, resize_shorter=64, scaling_mode=types.SCALING_MODE_NOT_SMALLER)
+        return fn.centre_crop(images, crop=(crop, crop))
+
+    with pytest.raises(TypeError):
+        loader(str(tmp_path), no_such_argument=1)
+    pipe = loader(str(tmp_path), crop=40, batch_size=2, device_id=0)
+    pipe.build()
+    got = [(outs[0].shape, outs[0].dtype, labels.tolist()) for outs, labels in ROCALClassificationIterator(pipe, device="cpu")]
+    assert [g[2] for g in got] == [[0, 0], [1, 1]]
+    assert all(g[0] == (2, 40, 40, 3) and g[1] == np.uint8 for g in got)
+    pipe.rocal_release()
