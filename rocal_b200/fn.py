@@ -76,7 +76,7 @@ def resize_mirror_normalize(*inputs, max_size=[], resize_longer=0, resize_shorte
 
 
 def crop_mirror_normalize(*inputs, crop=[0, 0], crop_pos_x=0.5, crop_pos_y=0.5, crop_w=0, crop_h=0, mean=[0.0], std=[1.0],
-                          mirror=1, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
+                          mirror=1, device=None, output_layout=types.NHWC, output_dtype=types.UINT8, image_type=None):
     p = _pipe()
     if len(crop) == 2 and (crop[0] or crop[1]):
         crop_h, crop_w = crop[0], crop[1]

@@ -10,8 +10,11 @@ from . import _capi as C
 from .pipeline import Pipeline
 
 
-def file(file_root, file_filters=None, file_list='', stick_to_shard=False, pad_last_batch=False):
-    """readers.py:67. Returns (reader handle, labels placeholder) like the reference."""
+def file(file_root, file_filters=None, file_list='', stick_to_shard=False, pad_last_batch=False, shard_id=0, num_shards=1,
+         random_shuffle=False):
+    """readers.py:67. Returns (reader handle, labels placeholder) like the reference. shard_id / num_shards /
+    random_shuffle are accepted because scripts pass them here as well (docs/examples/image_processing/
+    inference_pipeline.py:98 of the reference); the decoder call that follows is what sets them."""
     p = Pipeline._current_pipeline
     if p is None:
         raise RuntimeError("readers.file must be called inside `with pipeline:`")
