@@ -239,7 +239,13 @@ class Pipeline(object):
             self._keepalive.pop(0)
         return types.OK
 
-    run = rocal_run
+    def run(self):
+        """pipeline.py:262-275 of the reference: runs the next batch and returns its output tensors; StopIteration when
+        a pipeline that reads files itself has reached the end of its data."""
+        if getattr(self, "_has_file_source", False) and self.is_empty():
+            raise StopIteration
+        self.rocal_run()
+        return self.get_output_tensors()
 
     def get_output_tensors(self):
         return [RocalTensor(self, C.output(self._handle, i)) for i in range(C.output_count(self._handle))]

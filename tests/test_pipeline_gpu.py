@@ -622,8 +622,7 @@ def _decoded_by_pipeline(streams, max_side):
         pipe.set_outputs(fn.flip(img, horizontal=0, vertical=0))
     pipe.build()
     pipe.feed_encoded(streams)
-    pipe.run()
-    full = pipe.get_output_tensors()[0].numpy().copy()
+    full = pipe.run()[0].numpy().copy()          # run() returns the output tensors
     sizes = pipe.get_image_sizes()
     pipe.rocal_release()
     return [np.ascontiguousarray(full[i, :sizes[i, 1], :sizes[i, 0]]) for i in range(n)]
