@@ -66,10 +66,31 @@ class RocalTensor:
         return out
 
     def copy_data(self, dst, mem_type=types.HOST_MEMORY):
-        """dst: integer address / ctypes pointer of a buffer of data_size() bytes."""
-        ptr = dst if isinstance(dst, int) else ctypes.cast(dst, ctypes.c_void_p).value
+        """dst: a numpy array (filled in place), an integer address or a ctypes pointer of a buffer of data_size() bytes
+        (the calling forms of the reference's binding, rocal_pybind.cpp:532-557)."""
+        if isinstance(dst, np.ndarray):
+            ptr = dst.ctypes.data
+        else:
+            ptr = dst if isinstance(dst, int) else ctypes.cast(dst, ctypes.c_void_p).value
         if C.tensor_copy_data(self._h, ctypes.c_void_p(ptr), mem_type):
             raise RocalError(self._pipe.error_message())
+
+    # names of the reference's binding (rocal_pybind.cpp:478-531)
+    def max_shape(self):
+        return self.dims()
+
+    def dimensions(self):
+        return self.dims()
+
+    def batch_size(self):
+        return self.dims()[0]
+
+    def roi_dims_size(self):
+        return 2
+
+    def copy_roi(self, array):
+        """Fills a uint32 numpy array with x, y, w, h per sample."""
+        np.asarray(array).reshape(-1)[:4 * self.dims()[0]] = self.roi().reshape(-1)
 
     def numpy(self):
         np_dt = {types.FLOAT: np.float32, types.FLOAT16: np.float16, types.UINT8: np.uint8, types.INT32: np.int32}[self.dtype()]
