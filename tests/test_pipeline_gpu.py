@@ -793,7 +793,14 @@ def test_random_crop_crop_resize_roi_resize(cuda):
             x, y, w, h = [int(v) for v in exp_win[i]]
             assert np.array_equal(o_rc[i, :h, :w], im[y:y + h, x:x + w])
             assert np.array_equal(o_same[i, :ih, :iw], im)
-        assert pipe.get_output_tensors()[0].roi()[:, 2:].tolist() == exp_win[:, 2:].tolist()
+        t0 = pipe.get_output_tensors()[0]
+        assert t0.roi()[:, 2:].tolist() == exp_win[:, 2:].tolist()
+        # the calling forms of the reference's Python binding
+        buf, rois = np.empty(t0.dimensions(), dtype=np.uint8), np.zeros((n, 4), dtype=np.uint32)
+        t0.copy_data(buf)
+        t0.copy_roi(rois)
+        assert np.array_equal(buf, o_rc) and rois[:, 2:].tolist() == exp_win[:, 2:].tolist()
+        assert t0.batch_size() == n and t0.max_shape() == [n, 400, 400, 3] and t0.roi_dims_size() == 2
     pipe.rocal_release()
 
 
