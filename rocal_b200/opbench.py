@@ -143,7 +143,7 @@ def main():
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out,
                                                                        d_samples=dt, interpolation=1))
             report("cfg1 geometry, triangular filter, fp16 NCHW (batch 256, 300..1080 px)", n, _time(fns, args.steps), algo)
-        elif op == "jpeg_e2e":
+        elif op in ("jpeg_e2e", "jpeg_slice_e2e"):
             # configs[1] pipeline fed with JPEG streams (quality 90, 4:2:0) instead of raw pixels: GPU decode (nvJPEG)
             # -> Resize shorter 256 -> CropMirrorNormalize 224 fp16 NCHW, wall clock over whole batches
             import time
@@ -164,7 +164,11 @@ def main():
             pipe = Pipeline(batch_size=n, device_id=0, seed=1, prefetch_queue_depth=2)
             with pipe:
                 img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_COMPRESSED, max_width=1080, max_height=1080)
-                r = fn.resize(img, resize_shorter=256)
+                if op == "jpeg_slice_e2e":     # the training variant: random-resized-crop windows, stretched to 224 x 224
+                    pipe.set_random_crop_decoder()
+                    r = fn.resize(img, resize_width=224, resize_height=224)
+                else:
+                    r = fn.resize(img, resize_shorter=256)
                 out = fn.crop_mirror_normalize(r, crop=[224, 224], mean=list(S.MEAN), std=list(S.STD), mirror=fn.random.coin_flip(),
                                                output_layout=types.NCHW, output_dtype=types.FLOAT16)
                 pipe.set_outputs(out)
@@ -185,7 +189,8 @@ def main():
             enc_bytes = sum(len(s) for s in streams)
             tinfo = pipe.timing_info()
             pipe.rocal_release()
-            print(json.dumps({"op": "cfg1 pipeline from JPEG streams (nvJPEG decode -> resize -> CMN fp16), batch 256", "images_per_batch": n,
+            print(json.dumps({"op": ("cfg1 pipeline from JPEG streams (nvJPEG decode -> resize -> CMN fp16), batch 256" if op == "jpeg_e2e" else
+                                     "JPEG streams -> random-resized-crop window -> resize 224 -> CMN fp16, batch 256"), "images_per_batch": n,
                               "batch_ms": ms, "images_per_s": n / (ms * 1e-3), "encoded_bytes_per_batch": enc_bytes,
                               "decoded_bytes_per_batch": raw_bytes, "backend": os.environ.get("RB200_NVJPEG_BACKEND", "gpu_hybrid"),
                               "decode_time_us_total": tinfo["decode_time"]}), flush=True)
