@@ -5,6 +5,7 @@ import os
 import re
 
 import numpy as np
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(ROOT, "tests", "golden")
@@ -85,3 +86,27 @@ def test_parameters_follow_the_reference_draws():
     assert C.update_float_parameter(2.5, q) == 0 and C.get_float_value(q) == 2.5
     assert C.update_float_uniform_rand(0.0, 1.0, q) != 0          # wrong kind
     assert C.update_int_parameter(3, None) != 0
+
+
+def test_python_mirror_imports_and_pipeline_def_rules():
+    """The Python mirror imports without a GPU; @pipeline_def refuses a graph function with **kwargs (as the reference
+    does) and marks its factories; the types module carries the reference's numeric values."""
+    from rocal_b200 import decoders, fn, readers, types  # noqa: F401
+    from rocal_b200.pipeline import pipeline_def
+    from rocal_b200.plugin import generic, pytorch  # noqa: F401
+    with pytest.raises(TypeError):
+        @pipeline_def
+        def bad(**kwargs):
+            return None
+
+    @pipeline_def(batch_size=4)
+    def good(path, crop=10):
+        return None
+    assert good._is_pipeline_def and good.__name__ == "good"
+    assert (types.TRIANGULAR_INTERPOLATION, types.SCALING_MODE_MIN_MAX, types.LAST_BATCH_PARTIAL, types.USER_GIVEN_SIZE_ORIG,
+            types.EXTSOURCE_RAW_UNCOMPRESSED, types.NONE, types.FLOAT16, types.DECODER_ROCJPEG) == (5, 4, 2, 3, 2, 9, 1, 5)
+    for name in ("resize", "crop_mirror_normalize", "resize_crop", "roi_resize", "random_crop", "blend", "exposure",
+                 "gamma_correction", "color_temp", "one_hot", "box_encoder", "box_iou_matcher", "nop", "copy"):
+        assert callable(getattr(fn, name))
+    for name in ("image", "image_slice", "image_random_crop"):
+        assert callable(getattr(decoders, name))
