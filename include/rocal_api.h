@@ -235,6 +235,20 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourceSingleShard(
     unsigned shard_count, bool is_output, bool shuffle = false, bool loop = false,
     RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0, unsigned max_height = 0,
     RocalDecoderType rocal_decoder_type = ROCAL_DECODER_TJPEG, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+/* rocal_api_data_loaders.h:193-239: the COCO source behind the random-crop decoder; the window cuts the pixels, the
+ * boxes stay those of the whole image (only rocalRandomBBoxCrop, which is not built, moves boxes with a decode window). */
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourcePartial(
+    RocalContext p_context, const char* source_path, const char* json_path, RocalImageColor rocal_color_format,
+    unsigned internal_shard_count, bool is_output, std::vector<float>& area_factor, std::vector<float>& aspect_ratio,
+    unsigned num_attempts, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
+    unsigned max_height = 0, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourcePartialSingleShard(
+    RocalContext p_context, const char* source_path, const char* json_path, RocalImageColor rocal_color_format,
+    unsigned shard_id, unsigned shard_count, bool is_output, std::vector<float>& area_factor, std::vector<float>& aspect_ratio,
+    unsigned num_attempts, bool shuffle = false, bool loop = false,
+    RocalImageSizeEvaluationPolicy decode_size_policy = ROCAL_USE_MOST_FREQUENT_SIZE, unsigned max_width = 0,
+    unsigned max_height = 0, RocalShardingInfo rocal_sharding_info = RocalShardingInfo());
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalCreateLabelReader(RocalContext rocal_context, const char* source_path,
                                                               const char* file_list_path = "");
 /* rocal_api_meta_data.h:108: labels from a text file of "file_name label" lines; the following rocalJpegFileSource* reads

@@ -161,6 +161,46 @@ RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSource(RocalContext ctx, const char*
     }
     return rocalJpegCOCOFileSourceSingleShard(ctx, source_path, json_path, color, 0, 1, is_output, shuffle, loop, p, max_width, max_height, d, si);
 }
+// The COCO source behind the random-crop decoder (rocal_api_data_loaders.cpp:1185-1240: the COCO storage feeds the
+// fused-crop loader node). The decode window cuts the pixels only; the boxes stay those of the whole image, as in
+// the reference, where only rocalRandomBBoxCrop moves boxes with a decode window (image_read_and_decode.cpp:276-329).
+RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourcePartialSingleShard(RocalContext ctx, const char* source_path, const char* json_path,
+                                                                     RocalImageColor color, unsigned shard_id, unsigned shard_count,
+                                                                     bool is_output, std::vector<float>& area_factor,
+                                                                     std::vector<float>& aspect_ratio, unsigned num_attempts, bool shuffle,
+                                                                     bool loop, RocalImageSizeEvaluationPolicy p, unsigned max_width,
+                                                                     unsigned max_height, RocalShardingInfo si) {
+    if (!ctx) {
+        std::cerr << "[ERR] Invalid rocal context\n";
+        return nullptr;
+    }
+    if (area_factor.size() != 2 || aspect_ratio.size() != 2) {
+        P(ctx)->capture_error("rocalJpegCOCOFileSourcePartial: area_factor and aspect_ratio must hold two values each");
+        return nullptr;
+    }
+    if (is_output) {
+        P(ctx)->capture_error("rocalJpegCOCOFileSourcePartial: the fused JPEG crop source cannot be a graph output");
+        return nullptr;
+    }
+    RocalTensor t = rocalJpegCOCOFileSourceSingleShard(ctx, source_path, json_path, color, shard_id, shard_count, false, shuffle, loop, p,
+                                                       max_width, max_height, ROCAL_DECODER_TJPEG, si);
+    if (!t) return nullptr;
+    if (rb200_set_random_crop_decoder(ctx, area_factor.data(), aspect_ratio.data(), num_attempts) != ROCAL_OK) return nullptr;
+    return t;
+}
+RocalTensor ROCAL_API_CALL rocalJpegCOCOFileSourcePartial(RocalContext ctx, const char* source_path, const char* json_path,
+                                                          RocalImageColor color, unsigned internal_shard_count, bool is_output,
+                                                          std::vector<float>& area_factor, std::vector<float>& aspect_ratio,
+                                                          unsigned num_attempts, bool shuffle, bool loop,
+                                                          RocalImageSizeEvaluationPolicy p, unsigned max_width, unsigned max_height,
+                                                          RocalShardingInfo si) {
+    if (internal_shard_count != 1) {
+        if (ctx) P(ctx)->capture_error("rocalJpegCOCOFileSourcePartial: internal_shard_count must be 1 (use the SingleShard call per rank)");
+        return nullptr;
+    }
+    return rocalJpegCOCOFileSourcePartialSingleShard(ctx, source_path, json_path, color, 0, 1, is_output, area_factor, aspect_ratio,
+                                                     num_attempts, shuffle, loop, p, max_width, max_height, si);
+}
 RocalTensorList ROCAL_API_CALL rocalGetImageLabels(RocalContext ctx) {
     if (!ctx) {
         std::cerr << "[ERR] Invalid rocal context\n";

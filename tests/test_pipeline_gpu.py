@@ -740,6 +740,45 @@ def test_fused_jpeg_crop_file_source(cuda, tmp_path):
     pipe.rocal_release()
 
 
+def test_coco_source_behind_the_random_crop_decoder(cuda, tmp_path):
+    """fn.decoders.image_slice behind fn.readers.coco (rocalJpegCOCOFileSourcePartialSingleShard): the pixels are cut to
+    the sampler's windows, the boxes stay those of the whole image (only a box-aware crop would move them)."""
+    import json
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(41)
+    n = 3
+    imgs, streams = _jpeg_batch(rng, n, (120, 300))
+    pixels = _decoded_by_pipeline(streams, 320)
+    images, anns, truth = [], [], []
+    for i, (im, sb) in enumerate(zip(imgs, streams)):
+        name = "c%d.jpg" % i
+        (tmp_path / name).write_bytes(sb)
+        h, w = im.shape[:2]
+        images.append({"id": 7 + i, "file_name": name, "width": w, "height": h})
+        x, y, bw, bh = w * 0.1, h * 0.2, w * 0.5, h * 0.4
+        anns.append({"id": i, "image_id": 7 + i, "category_id": 5, "bbox": [x, y, bw, bh], "iscrowd": 0})
+        truth.append([x / w, y / h, (x + bw) / w, (y + bh) / h])
+    (tmp_path / "ann.json").write_text(json.dumps({"images": images, "annotations": anns, "categories": [{"id": 5}]}))
+    pipe = Pipeline(batch_size=n, device_id=0, seed=9)
+    with pipe:
+        jpegs, _, _ = fn.readers.coco(annotations_file=str(tmp_path / "ann.json"), ltrb=True)
+        img = fn.decoders.image_slice(jpegs, file_root=str(tmp_path), random_area=[0.2, 0.9], random_aspect_ratio=[0.5, 2.0],
+                                      num_attempts=20, max_decoded_width=320, max_decoded_height=320)
+        pipe.set_outputs(fn.resize(img, resize_width=64, resize_height=48, scaling_mode=types.SCALING_MODE_STRETCH))
+    pipe.build()
+    out = pipe.run()[0].numpy()
+    assert pipe.get_image_names() == ["c0.jpg", "c1.jpg", "c2.jpg"]
+    win, bseed = pipe.get_decoder_crop_windows()
+    shapes = np.array([[p.shape[0], p.shape[1]] for p in pixels])
+    assert np.array_equal(win, O.random_crop_windows(bseed, shapes, (0.5, 2.0), (0.2, 0.9), 20))
+    assert any(int(win[i, 2]) != shapes[i, 1] or int(win[i, 3]) != shapes[i, 0] for i in range(n))
+    assert np.array_equal(out, _expected_windowed_resize(pixels, win, 64, 48))
+    boxes, labels, counts = pipe.get_bounding_boxes()
+    assert list(counts) == [1] * n and list(labels) == [1] * n and np.allclose(boxes, truth, atol=1e-5)
+    pipe.rocal_release()
+
+
 def test_random_crop_crop_resize_roi_resize(cuda):
     """rocalRandomCrop, rocalCropResize, rocalROIResize and rocalNop on raw pixels. With fixed parameter values the
     windows are the restated rule's; with the default random ranges they are read back. Pixels equal the oracle:
