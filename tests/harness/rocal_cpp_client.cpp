@@ -39,7 +39,7 @@ static std::vector<unsigned char> slurp(const char* path) {
     } while (0)
 
 int main(int argc, char** argv) {
-    if (argc != 3 && argc != 4) return 2;
+    if (argc < 3 || argc > 5) return 2;
     std::vector<unsigned char> in = slurp(argv[1]);
     const unsigned char* p = in.data();
     auto rd_i32 = [&]() { int v; memcpy(&v, p, 4); p += 4; return v; };
@@ -193,7 +193,7 @@ int main(int argc, char** argv) {
         rocalRelease(ctx);
     }
     // ---- graph 4 (with a folder of JPEG files): rocalCreateLabelReader + rocalFusedJpegCropSingleShard -> Resize ----
-    if (argc == 4) {
+    if (argc >= 4) {
         const int bs = 2;
         RocalContext ctx = rocalCreate((size_t)bs, ROCAL_PROCESS_GPU, 0, 1, 2, ROCAL_FP32);
         if (!ctx) return 1;
@@ -238,6 +238,41 @@ int main(int argc, char** argv) {
             CHECK(ctx, t->dims()[1] == 64 && t->dims()[2] == 64 && t->data_type() == ROCAL_UINT8);
         }
         fwrite(&batches, 4, 1, out);
+        CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
+        rocalRelease(ctx);
+    }
+    // ---- graph 5 (folder + COCO annotation file): rocalCreateCOCOReader + rocalJpegCOCOFileSourcePartialSingleShard -> Resize ----
+    if (argc >= 5) {
+        const int bs = 2;
+        RocalContext ctx = rocalCreate((size_t)bs, ROCAL_PROCESS_GPU, 0, 1, 2, ROCAL_FP32);
+        if (!ctx) return 1;
+        rocalSetSeed(99);
+        rocalCreateCOCOReader(ctx, argv[4], true);
+        std::vector<float> area{0.3f, 0.8f}, aspect{0.5f, 2.0f};
+        RocalTensor src = rocalJpegCOCOFileSourcePartialSingleShard(ctx, argv[3], argv[4], ROCAL_COLOR_RGB24, 0, 1, false, area, aspect, 25,
+                                                                    false, false, ROCAL_USE_USER_GIVEN_SIZE, 400, 400);
+        CHECK(ctx, src);
+        CHECK(ctx, rocalResize(ctx, src, 32, 32, true, ROCAL_SCALING_MODE_STRETCH));
+        CHECK(ctx, rocalVerify(ctx) == ROCAL_OK);
+        CHECK(ctx, rocalRun(ctx) == ROCAL_OK);
+        std::vector<int> ids(bs), sizes(bs * 2);
+        rocalGetImageId(ctx, ids.data());
+        rocalGetImageSizes(ctx, sizes.data());
+        std::vector<unsigned> win(bs * 4);
+        unsigned seed = 0;
+        CHECK(ctx, rb200_get_decoder_crop_windows(ctx, win.data(), &seed) == 0);
+        fwrite(ids.data(), 4, bs, out);
+        fwrite(sizes.data(), 4, bs * 2, out);
+        fwrite(win.data(), 4, bs * 4, out);
+        fwrite(&seed, 4, 1, out);
+        RocalTensorList bl = rocalGetBoundingBoxCords(ctx);
+        CHECK(ctx, bl && bl->size() == (uint64_t)bs);
+        for (int i = 0; i < bs; i++) {
+            CHECK(ctx, (int)bl->at(i)->dims()[0] == 1);
+            float b[4];
+            CHECK(ctx, bl->at(i)->copy_data(b, ROCAL_MEMCPY_HOST) == 0);
+            fwrite(b, 4, 4, out);
+        }
         CHECK(ctx, rocalGetStatus(ctx) == ROCAL_OK);
         rocalRelease(ctx);
     }

@@ -51,8 +51,17 @@ def test_cpp_client(cuda, tmp_path):
         name = "p%d.jpg" % k
         assert cv2.imwrite(str(tmp_path / "jpeg" / cls / name), pic)
         jpeg_sizes[name] = (jw, jh, 0 if cls == "ant" else 1)
-    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin"), str(tmp_path / "jpeg")], capture_output=True,
-                       text=True, timeout=300)
+    # a COCO annotation file over two of those files for graph 5: one box each, a tenth of the image in from every side
+    import json
+    coco = {"images": [], "annotations": [], "categories": [{"id": 3}]}
+    for k, rel in enumerate(["ant/p0.jpg", "bee/p3.jpg"]):
+        jw, jh, _ = jpeg_sizes[rel.split("/")[1]]
+        coco["images"].append({"id": 50 + k, "file_name": rel, "width": jw, "height": jh})
+        coco["annotations"].append({"id": k, "image_id": 50 + k, "category_id": 3, "iscrowd": 0,
+                                    "bbox": [jw * 0.1, jh * 0.1, jw * 0.8, jh * 0.8]})
+    (tmp_path / "coco.json").write_text(json.dumps(coco))
+    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin"), str(tmp_path / "jpeg"), str(tmp_path / "coco.json")],
+                       capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-2000:]
     raw = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
     pos = 0
@@ -136,6 +145,14 @@ def test_cpp_client(cuda, tmp_path):
         seen += names4
     assert seen == ["p0.jpg", "p1.jpg", "p2.jpg", "p3.jpg", "p4.jpg", "p4.jpg"]
     assert int(take(np.int32, 1)[0]) == 3
+    # graph 5: rocalJpegCOCOFileSourcePartialSingleShard - ids and sizes of the whole images, the sampler's windows,
+    # boxes of the whole image
+    ids5, sizes5 = take(np.int32, 2), take(np.int32, 4).reshape(2, 2)
+    win5, seed5 = take(np.uint32, 8).reshape(2, 4), int(take(np.uint32, 1)[0])
+    boxes5 = take(np.float32, 8).reshape(2, 4)
+    assert ids5.tolist() == [50, 51] and sizes5.tolist() == [[200, 120], [320, 240]]
+    assert np.array_equal(win5, O.random_crop_windows(seed5, np.array([[120, 200], [240, 320]]), (0.5, 2.0), (0.3, 0.8), 25))
+    assert np.allclose(boxes5, [[0.1, 0.1, 0.9, 0.9]] * 2, atol=1e-5)
     assert pos == len(raw)
     assert np.array_equal(outs[0][0], stretched(win, 120, 80)) and outs[0][1][:, 2:].tolist() == [[120, 80]] * n
     fixed_roi = np.tile(np.array([[20, 30, 150, 100]], dtype=np.int64), (n, 1))
