@@ -5,15 +5,22 @@
  * product path: only the tests, the smoke check and the benchmark's CPU-baseline leg load it.
  *
  * Parity status
- *   - orc_box_encode: PINNED. It is checked against the reference's own
- *     BoundingBoxGraph::update_box_encoder_meta_data compiled from the reference sources
- *     (see ref_driver.cpp) and against golden vectors generated from that build.
- *   - orc_resample / orc_pointwise / orc_warp_affine: PARITY UNPINNED. The reference executes
- *     these operators inside the RPP library through MIVisionX/OpenVX; neither is present in
- *     the reference tree, and the reference's golden images live in an external data tree.
- *     The arithmetic below follows the only in-tree pixel code (the HIP bilinear kernel
- *     in rocAL/rocAL_hip/rocal_hip_kernels.cpp) and the node / meta-node / API files
- *     cited at each function.
+ *   - orc_box_encode, orc_box_iou_match: PINNED against the reference's own BoundingBoxGraph compiled from the
+ *     reference sources (ref_driver.cpp) and against golden vectors generated from that build.
+ *   - orc_resample with bilinear or triangular interpolation on a whole-image ROI, and the x*mul+add
+ *     conversion of orc_pointwise: PINNED against the reference's own pixel kernels — the in-tree HIP kernels
+ *     resize_bilinear_pkd_hip_tensor, resize_generic_pln1_hip_tensor and Hip_CopyInt8To* of
+ *     rocAL/rocAL_hip/rocal_hip_kernels.cpp compiled for the host (ref_hip_driver.cpp, ref_stubs/hip/) — bit
+ *     for bit, on golden vectors from that build and on the live build where the reference tree exists.
+ *     Products that feed a sum inside one expression of those kernels are fused multiply-adds, as the HIP
+ *     compiler builds them; they are spelled fmaf() here.
+ *   - orc_crop_fixed: PINNED against RocalCropParam::fill_crop_dims compiled in place.
+ *   - Everything else in orc_resample / orc_pointwise / orc_warp_affine (crop windows and mirrors applied to the
+ *     resize, the normalisation of CropMirrorNormalize, the colour operators, the affine gather, the other
+ *     filters): PARITY UNPINNED. The reference executes these operators inside the RPP library through
+ *     MIVisionX/OpenVX; neither is present in the reference tree, and the reference's golden images live in
+ *     an external data tree. The arithmetic follows the pinned kernels where they apply (the bilinear tap rule
+ *     and packing) and the node / meta-node / API files cited at each function.
  *
  * All float arithmetic is IEEE binary32 with one rounding per written operation (build with
  * -ffp-contract=off); fused multiply-adds are spelled fmaf().
@@ -253,10 +260,10 @@ ORC_API int orc_resample(const uint8_t* arena, const rb200_resample_sample* s, i
         tri_axis ax = filter_axis_make(ratio_w, p->interpolation), ay = filter_axis_make(ratio_h, p->interpolation);
         for (int y = 0; y < ch; y++) {
             int ry = q->crop_y + y;
-            float sy = (float)ry * ratio_h + off_h + (float)q->roi_y;
+            float sy = fmaf((float)ry, ratio_h, off_h) + (float)q->roi_y;
             for (int x = 0; x < cw; x++) {
                 int rx = q->crop_x + (q->mirror ? (q->crop_w - 1 - x) : x);
-                float sx = (float)rx * ratio_w + off_w + (float)q->roi_x;
+                float sx = fmaf((float)rx, ratio_w, off_w) + (float)q->roi_x;
                 float v[3] = {0.f, 0.f, 0.f};
                 uint8_t t3[3] = {0, 0, 0};
                 if (generic)

@@ -515,3 +515,259 @@ def ref_random_area_windows(wh, fixed=None, seed=0):
     first = r.ref_random_area_windows(_ptr(wh), ctypes.c_int(len(wh)), ctypes.c_int(1 if fixed is not None else 0), _ptr(f4),
                                       ctypes.c_uint(seed), _ptr(out))
     return out, int(first)
+
+
+# ---- the reference's own pixel kernels, compiled for the host (oracle/_ref/libref_hip.so) ----------
+
+_ref_hip = None
+
+
+def ref_hip():
+    """The host build of rocAL/rocAL_hip/rocal_hip_kernels.cpp, or None when neither the reference tree nor a
+    prebuilt copy exists."""
+    global _ref_hip
+    if _ref_hip is None:
+        path = _build.build_ref_hip()
+        if path is None:
+            return None
+        _ref_hip = ctypes.CDLL(path)
+    return _ref_hip
+
+
+def _hip_resize(fn, arena, src_w, src_h, src_stride, src_offset, dst_w, dst_h, channels):
+    n = len(src_w)
+    u32 = lambda a: np.ascontiguousarray(a, dtype=np.uint32)   # noqa: E731
+    sw, sh, ss, dw, dh = u32(src_w), u32(src_h), u32(src_stride), u32(dst_w), u32(dst_h)
+    so = np.ascontiguousarray(src_offset, dtype=np.uint64)
+    mw, mh = int(dw.max()), int(dh.max())
+    out = np.zeros((n, mh, mw, 3) if channels == 3 else (n, mh, mw), dtype=np.uint8)
+    arena = np.ascontiguousarray(arena, dtype=np.uint8)
+    fn.restype = ctypes.c_int
+    rc = fn(_ptr(arena), ctypes.c_size_t(arena.size), ctypes.c_int(n), _ptr(sw), _ptr(sh), _ptr(ss), _ptr(so), _ptr(dw), _ptr(dh),
+            ctypes.c_uint(mw), ctypes.c_uint(mh), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def ref_hip_resize_bilinear(arena, src_w, src_h, src_stride, src_offset, dst_w, dst_h):
+    """resize_bilinear_pkd_hip_tensor (rocal_hip_kernels.cpp:446-485) on interleaved RGB images: returns
+    [n][max dst_h][max dst_w][3] uint8, sample i valid in its dst_h[i] x dst_w[i] corner."""
+    return _hip_resize(ref_hip().ref_hip_resize_bilinear_pkd3, arena, src_w, src_h, src_stride, src_offset, dst_w, dst_h, 3)
+
+
+def ref_hip_resize_generic(arena, src_w, src_h, src_stride, src_offset, dst_w, dst_h):
+    """resize_generic_pln1_hip_tensor (rocal_hip_kernels.cpp:514-589, the triangular filter) on single-channel
+    planes: returns [n][max dst_h][max dst_w] uint8."""
+    return _hip_resize(ref_hip().ref_hip_resize_generic_pln1, arena, src_w, src_h, src_stride, src_offset, dst_w, dst_h, 1)
+
+
+def ref_hip_copy_int8(images, nchw, fp16, mul, add, reverse_channels=False):
+    """Hip_CopyInt8ToNCHW_* / Hip_CopyInt8ToNHWC_* (rocal_hip_kernels.cpp:40-217) on a [n][h][w][3] uint8 batch."""
+    images = np.ascontiguousarray(images, dtype=np.uint8)
+    n, h, w, _ = images.shape
+    out = np.zeros((n, 3, h, w) if nchw else (n, h, w, 3), dtype=np.float16 if fp16 else np.float32)
+    m, a = np.asarray(mul, dtype=np.float32), np.asarray(add, dtype=np.float32)
+    fn = ref_hip().ref_hip_copy_int8
+    fn.restype = ctypes.c_int
+    rc = fn(_ptr(images), ctypes.c_int(n), ctypes.c_int(h), ctypes.c_int(w), ctypes.c_int(1 if nchw else 0),
+            ctypes.c_int(1 if fp16 else 0), _ptr(m), _ptr(a), ctypes.c_int(1 if reverse_channels else 0), _ptr(out))
+    assert rc == 0
+    return out
+
+
+# ---- crop windows of RocalCropParam ---------------------------------------------------------------------
+
+def rocal_crop_windows(wh, mode, crop_w, crop_h, f):
+    """RocalCropParam::fill_crop_dims (parameter_rocal_crop.cpp:49-85) for a batch of input sizes wh = n x {w, h}.
+    mode 0: fixed anchors f = (anchor_x, anchor_y); mode 1: absolute corner f = (x1, y1) (a corner at or beyond the
+    image falls back to 0); mode 2: random branch with the factor values f = (width, height, x drift, y drift) already
+    drawn. Returns n x {x1, y1, crop_w, crop_h, x2, y2} uint32, x2 / y2 clipped to the image as the class does."""
+    f32 = np.float32
+    wh = np.asarray(wh, dtype=np.int64).reshape(-1, 2)
+    out = np.zeros((len(wh), 6), dtype=np.uint32)
+    for i, (w, h) in enumerate(wh):
+        w, h = int(w), int(h)
+        if mode in (0, 1):
+            cw = crop_w if (0 < crop_w <= w) else w
+            ch = crop_h if (0 < crop_h <= h) else h
+            if mode == 0:
+                x1 = int(np.rint(f32(f32(f[0]) * f32(w - cw))))
+                y1 = int(np.rint(f32(f32(f[1]) * f32(h - ch))))
+            else:
+                x1 = 0 if int(f[0]) >= w else int(f[0])
+                y1 = 0 if int(f[1]) >= h else int(f[1])
+        else:
+            cw = int(f32(f32(f[0]) * f32(w)))
+            ch = int(f32(f32(f[1]) * f32(h)))
+            x1 = int(f32(f32(f[2]) * f32(w - cw)))
+            y1 = int(f32(f32(f[3]) * f32(h - ch)))
+        out[i] = (x1, y1, cw, ch, min(x1 + cw, w), min(y1 + ch, h))
+    return out
+
+
+def ref_rocal_crop_windows(wh, mode, crop_w, crop_h, f):
+    """The reference class itself (needs _ref/libref.so)."""
+    r = ref()
+    if r is None:
+        return None
+    wh = np.ascontiguousarray(np.asarray(wh, dtype=np.uint32).reshape(-1, 2))
+    out = np.zeros((len(wh), 6), dtype=np.uint32)
+    f4 = np.zeros(4, dtype=np.float32)
+    f4[:len(f)] = f
+    r.ref_rocal_crop_windows.restype = ctypes.c_int
+    rc = r.ref_rocal_crop_windows(_ptr(wh), ctypes.c_int(len(wh)), ctypes.c_int(mode), ctypes.c_uint(crop_w), ctypes.c_uint(crop_h),
+                                  _ptr(f4), _ptr(out))
+    assert rc == 0
+    return out
+
+
+# ---- bounding boxes that follow the augmentations (the reference's meta nodes) ------------------------
+# Boxes are float32 ltrb in the coordinate space of the node's input; each function takes and returns
+# (boxes [total][4], labels [total], offsets [n+1]).
+
+def _split(boxes, labels, offsets):
+    boxes = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+    labels = np.asarray(labels, dtype=np.int32)
+    return [(boxes[offsets[i]:offsets[i + 1]].copy(), labels[offsets[i]:offsets[i + 1]].copy()) for i in range(len(offsets) - 1)]
+
+
+def _join(per):
+    counts = [len(b) for b, _ in per]
+    boxes = np.concatenate([np.asarray(b, dtype=np.float32).reshape(-1, 4) for b, _ in per]) if per else np.zeros((0, 4), np.float32)
+    labels = np.concatenate([np.asarray(l, dtype=np.int32) for _, l in per]) if per else np.zeros(0, np.int32)
+    return boxes, labels, np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+
+
+def _covered_fraction(box, crop, entire=False):
+    """MetaNode::BBoxIntersectionOverUnion (include/meta_data/meta_node.h:42-58): intersection / area of the box
+    (the default), or the true IoU when `entire`; float32 products, the quotient widened to double."""
+    f32 = np.float32
+    xa, ya = max(box[0], crop[0]), max(box[1], crop[1])
+    xb, yb = min(box[2], crop[2]), min(box[3], crop[3])
+    inter = f32(max(f32(0), f32(xb - xa)) * max(f32(0), f32(yb - ya)))
+    a1 = f32(f32(box[3] - box[1]) * f32(box[2] - box[0]))
+    a2 = f32(f32(crop[3] - crop[1]) * f32(crop[2] - crop[0]))
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return float(f32(inter / f32(f32(a1 + a2) - inter))) if entire else float(f32(inter / a1))
+
+
+def meta_crop(boxes, labels, offsets, windows, mirror=None, resize_to=None, iou_threshold=0.25):
+    """CropMetaNode / CropMirrorNormalizeMetaNode / ResizeCropMirrorMetaNode (meta_node_crop.cpp:44-79,
+    meta_node_crop_mirror_normalize.cpp:53-90, meta_node_resize_crop_mirror.cpp:55-100): a box is kept when at least
+    iou_threshold of its area lies in the window {x1, y1, w, h}; kept boxes are clipped, shifted to the window's
+    origin, mirrored about the window's width and (resize_to = (w, h)) scaled by resize / window. A sample left
+    without boxes gets the whole window with label 0."""
+    f32 = np.float32
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        x1, y1, cw, ch = [f32(v) for v in windows[i][:4]]
+        crop = (x1, y1, f32(x1 + cw), f32(y1 + ch))
+        kb, kl = [], []
+        for q, lab in zip(b, l):
+            if _covered_fraction(q, crop) >= float(f32(iou_threshold)):
+                nl, nt = f32(max(crop[0], q[0]) - crop[0]), f32(max(crop[1], q[1]) - crop[1])
+                nr, nb = f32(min(crop[2], q[2]) - crop[0]), f32(min(crop[3], q[3]) - crop[1])
+                if mirror is not None and mirror[i] == 1:
+                    nl, nr = f32(cw - nr), f32(cw - nl)
+                if resize_to is not None:
+                    sx, sy = f32(f32(resize_to[0]) / cw), f32(f32(resize_to[1]) / ch)
+                    nl, nt, nr, nb = f32(nl * sx), f32(nt * sy), f32(nr * sx), f32(nb * sy)
+                kb.append((nl, nt, nr, nb))
+                kl.append(lab)
+        if not kb:
+            kb, kl = [(f32(0), f32(0), cw, ch)], [0]
+        per.append((kb, kl))
+    return _join(per)
+
+
+def meta_flip(boxes, labels, offsets, roi_wh, h_flip, v_flip):
+    """FlipMetaNode (meta_node_flip.cpp:30-62): l, r -> w - r, w - l and t, b -> h - b, h - t."""
+    f32 = np.float32
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        w, h = f32(roi_wh[i][0]), f32(roi_wh[i][1])
+        for q in b:
+            if h_flip[i]:
+                q[0], q[2] = f32(w - q[2]), f32(w - q[0])
+            if v_flip[i]:
+                q[1], q[3] = f32(h - q[3]), f32(h - q[1])
+        per.append((b, l))
+    return _join(per)
+
+
+def meta_resize(boxes, labels, offsets, src_wh, dst_wh):
+    """ResizeMetaNode (meta_node_resize.cpp:25-55): every coordinate times dst / src of its axis."""
+    f32 = np.float32
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        sx = f32(f32(dst_wh[i][0]) / f32(src_wh[i][0]))
+        sy = f32(f32(dst_wh[i][1]) / f32(src_wh[i][1]))
+        b[:, 0::2] = (b[:, 0::2] * sx).astype(np.float32)
+        b[:, 1::2] = (b[:, 1::2] * sy).astype(np.float32)
+        per.append((b, l))
+    return _join(per)
+
+
+def meta_ssd_random_crop(boxes, labels, offsets, windows, iou_range=(0.0, 1.0), entire_iou=False):
+    """SSDRandomCropMetaNode (meta_node_ssd_random_crop.cpp:31-85): a box is kept when its centre lies in the
+    closed window and its covered fraction (or IoU) lies in iou_range; kept boxes are clipped and divided by
+    the window's size (they leave normalised to the crop). No stand-in box is added."""
+    f32 = np.float32
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        x1, y1, cw, ch = [f32(v) for v in windows[i][:4]]
+        crop = (x1, y1, f32(x1 + cw), f32(y1 + ch))
+        kb, kl = [], []
+        for q, lab in zip(b, l):
+            xc, yc = f32(f32(0.5) * f32(q[0] + q[2])), f32(f32(0.5) * f32(q[1] + q[3]))
+            inside = crop[0] <= xc <= crop[2] and crop[1] <= yc <= crop[3]
+            v = f32(_covered_fraction(q, crop, entire_iou))
+            if f32(iou_range[0]) <= v <= f32(iou_range[1]) and inside:
+                w, h = f32(crop[2] - crop[0]), f32(crop[3] - crop[1])
+                kb.append((f32(f32(max(crop[0], q[0]) - crop[0]) / w), f32(f32(max(crop[1], q[1]) - crop[1]) / h),
+                           f32(f32(min(crop[2], q[2]) - crop[0]) / w), f32(f32(min(crop[3], q[3]) - crop[1]) / h)))
+                kl.append(lab)
+        per.append((kb, kl))
+    return _join(per)
+
+
+def random_bbox_meta(boxes, labels, offsets, crop_xywh, roi_wh):
+    """BoundingBoxGraph::update_random_bbox_meta_data (bounding_box_graph.cpp:71-118) as written: the window is
+    l = x * roi_w, t = y * roi_h, r = (l + w) * roi_w, b = (t + h) * roi_h (the already scaled corner enters the
+    second product); a box is kept when its centre, evaluated in double, lies strictly inside; kept boxes are
+    clipped and shifted; a sample left without boxes gets one zero box with label 0."""
+    f32 = np.float32
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        rw, rh = f32(roi_wh[i][0]), f32(roi_wh[i][1])
+        cl, ct = f32(f32(crop_xywh[i][0]) * rw), f32(f32(crop_xywh[i][1]) * rh)
+        cr, cb = f32(f32(cl + f32(crop_xywh[i][2])) * rw), f32(f32(ct + f32(crop_xywh[i][3])) * rh)
+        kb, kl = [], []
+        for q, lab in zip(b, l):
+            xc, yc = 0.5 * float(f32(q[0] + q[2])), 0.5 * float(f32(q[1] + q[3]))
+            if float(cl) < xc < float(cr) and float(ct) < yc < float(cb):
+                kb.append((f32(max(cl, q[0]) - cl), f32(max(ct, q[1]) - ct), f32(min(cr, q[2]) - cl), f32(min(cb, q[3]) - ct)))
+                kl.append(lab)
+        if not kb:
+            kb, kl = [(0, 0, 0, 0)], [0]
+        per.append((kb, kl))
+    return _join(per)
+
+
+def ref_random_bbox_meta(boxes, labels, offsets, crop_xywh, roi_wh):
+    """The reference's own update_random_bbox_meta_data (needs _ref/libref.so)."""
+    r = ref()
+    if r is None:
+        return None
+    boxes = np.ascontiguousarray(boxes, dtype=np.float32).reshape(-1, 4)
+    labels = np.ascontiguousarray(labels, dtype=np.int32)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+    n = len(offsets) - 1
+    crops = np.ascontiguousarray(crop_xywh, dtype=np.float32).reshape(n, 4)
+    roi = np.ascontiguousarray(roi_wh, dtype=np.uint32).reshape(n, 2)
+    cap = max(len(boxes), n) + n
+    ob, ol, oc = np.zeros((cap, 4), np.float32), np.zeros(cap, np.int32), np.zeros(n, np.int32)
+    r.ref_random_bbox_meta.restype = ctypes.c_int
+    k = r.ref_random_bbox_meta(_ptr(boxes), _ptr(labels), _ptr(offsets), ctypes.c_int(n), _ptr(crops), _ptr(roi), _ptr(ob),
+                               _ptr(ol), _ptr(oc))
+    return ob[:k].copy(), ol[:k].copy(), np.concatenate([[0], np.cumsum(oc)]).astype(np.int32)

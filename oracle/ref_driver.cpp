@@ -22,6 +22,11 @@
  *   ref_random_area_windows -> RocalRandomCropParam::fill_crop_dims (rocAL/source/parameters/parameter_random_crop.cpp:48-97,
  *                           compiled in place with parameter_crop.cpp) with fixed or default-range parameters; the OpenVX
  *                           array calls of the class are answered by the do-nothing stand-ins at the end of this file
+ *   ref_rocal_crop_windows  -> RocalCropParam::update_array -> fill_crop_dims (rocAL/source/parameters/
+ *                           parameter_rocal_crop.cpp:45-85): the window rule of rocalCrop / rocalCropFixed /
+ *                           rocalCropCenterFixed / rocalCropMirrorNormalize / rocalResizeCropMirror
+ *   ref_random_bbox_meta    -> BoundingBoxGraph::update_random_bbox_meta_data (bounding_box_graph.cpp:71-118): boxes
+ *                           that follow a crop window (centre-inside mask, clip, shift)
  */
 #include <cstdint>
 #include <memory>
@@ -33,6 +38,7 @@
 #include "parameters/parameter_random.h"
 #include "parameters/parameter_random_crop.h"
 #include "parameters/parameter_random_crop_decoder.h"
+#include "parameters/parameter_rocal_crop.h"
 
 extern "C" {
 
@@ -192,6 +198,106 @@ __attribute__((visibility("default"))) unsigned ref_random_area_windows(const un
         out_xywh[i * 4 + 3] = ch[i];
     }
     return first_entry;
+}
+
+// wh: n x {width, height} of the input ROIs. mode 0: fixed anchors (set_fixed_crop(f[0], f[1]), crop size crop_w x crop_h);
+// mode 1: absolute corner x1 = f[0], y1 = f[1] (neither fixed nor random); mode 2: random branch with the single-value
+// factors f = {width factor, height factor, x drift, y drift}. out: n x {x1, y1, crop_w, crop_h, x2, y2}.
+namespace {
+struct RocalCropProbe : public RocalCropParam {
+    using RocalCropParam::RocalCropParam;
+    std::vector<uint32_t> x2v() { return x2_arr_val; }
+    std::vector<uint32_t> y2v() { return y2_arr_val; }
+};
+}  // namespace
+
+__attribute__((visibility("default"))) int ref_rocal_crop_windows(const unsigned* wh, int n, int mode, unsigned crop_w,
+                                                                  unsigned crop_h, const float* f, unsigned* out) {
+    ParameterFactory* pf = ParameterFactory::instance();
+    pf->set_seed(1);   // the class's default parameters take entries of the seed table, which must exist
+    RocalCropProbe p((unsigned)n);
+    p.crop_w = crop_w;
+    p.crop_h = crop_h;
+    p.x1 = p.y1 = 0;
+    if (mode == 0) {
+        p.set_fixed_crop(f[0], f[1]);
+    } else if (mode == 1) {
+        p.x1 = (unsigned)f[0];
+        p.y1 = (unsigned)f[1];
+    } else {
+        p.set_random();
+        p.set_crop_width_factor(pf->create_single_value_param(f[0]));
+        p.set_crop_height_factor(pf->create_single_value_param(f[1]));
+        p.set_x_drift_factor(pf->create_single_value_param(f[2]));
+        p.set_y_drift_factor(pf->create_single_value_param(f[3]));
+    }
+    std::vector<Roi2DCords> rois(n);
+    for (int i = 0; i < n; i++) {
+        rois[i].xywh.x = 0;
+        rois[i].xywh.y = 0;
+        rois[i].xywh.w = wh[i * 2];
+        rois[i].xywh.h = wh[i * 2 + 1];
+    }
+    p.array_init();
+    p.set_image_dimensions(rois.data());
+    p.update_array();
+    auto x1 = p.get_x1_arr_val(), y1 = p.get_y1_arr_val(), cw = p.get_cropw_arr_val(), ch = p.get_croph_arr_val();
+    auto x2 = p.x2v(), y2 = p.y2v();
+    for (int i = 0; i < n; i++) {
+        out[i * 6 + 0] = x1[i];
+        out[i * 6 + 1] = y1[i];
+        out[i * 6 + 2] = cw[i];
+        out[i * 6 + 3] = ch[i];
+        out[i * 6 + 4] = x2[i];
+        out[i * 6 + 5] = y2[i];
+    }
+    return 0;
+}
+
+// boxes: [total][4] ltrb, labels [total], box_offsets [n+1]; crop_xywh: n x {x, y, w, h} as the random-bbox-crop reader
+// reports them; roi_wh: n x {roi width, roi height} of the decoded images. out_boxes / out_labels hold at most
+// max(total, n) entries; out_counts[n]. Returns the number of boxes written.
+__attribute__((visibility("default"))) int ref_random_bbox_meta(const float* boxes, const int32_t* labels,
+                                                                const int32_t* box_offsets, int n, const float* crop_xywh,
+                                                                const uint32_t* roi_wh, float* out_boxes,
+                                                                int32_t* out_labels, int32_t* out_counts) {
+    auto in = std::make_shared<BoundingBoxBatch>();
+    auto out = std::make_shared<BoundingBoxBatch>();
+    in->resize(n);
+    out->resize(n);
+    DecodedDataInfo info;
+    CropImageInfo crops;
+    for (int i = 0; i < n; i++) {
+        BoundingBoxCords cords;
+        Labels lab;
+        for (int b = box_offsets[i]; b < box_offsets[i + 1]; b++) {
+            cords.emplace_back(boxes[b * 4 + 0], boxes[b * 4 + 1], boxes[b * 4 + 2], boxes[b * 4 + 3]);
+            lab.push_back(labels[b]);
+        }
+        in->get_bb_cords_batch()[i] = cords;
+        in->get_labels_batch()[i] = lab;
+        info._roi_width.push_back(roi_wh[i * 2]);
+        info._roi_height.push_back(roi_wh[i * 2 + 1]);
+        info._original_width.push_back(roi_wh[i * 2]);
+        info._original_height.push_back(roi_wh[i * 2 + 1]);
+        crops._crop_image_coords.push_back({crop_xywh[i * 4], crop_xywh[i * 4 + 1], crop_xywh[i * 4 + 2], crop_xywh[i * 4 + 3]});
+    }
+    BoundingBoxGraph graph;
+    graph.update_random_bbox_meta_data(in, out, info, crops);
+    int k = 0;
+    for (int i = 0; i < n; i++) {
+        auto& c = out->get_bb_cords_batch()[i];
+        auto& l = out->get_labels_batch()[i];
+        out_counts[i] = (int)c.size();
+        for (size_t j = 0; j < c.size(); j++, k++) {
+            out_boxes[k * 4 + 0] = c[j].l;
+            out_boxes[k * 4 + 1] = c[j].t;
+            out_boxes[k * 4 + 2] = c[j].r;
+            out_boxes[k * 4 + 3] = c[j].b;
+            out_labels[k] = l[j];
+        }
+    }
+    return k;
 }
 
 }  // extern "C"

@@ -55,7 +55,7 @@ struct RowInfo {
 };
 
 __device__ __forceinline__ float src_location(int d, float ratio, float offset, int roi_start) {
-    return add_rn(add_rn(mul_rn((float)d, ratio), offset), (float)roi_start);
+    return add_rn(fmaf((float)d, ratio, offset), (float)roi_start);
 }
 
 __device__ __forceinline__ void clamp_taps(float f, int lo, int hi, int& t0, int& t1) {

@@ -3,6 +3,7 @@ the reference tree by oracle/build.py). Run in a container that has the referenc
 
     python tests/golden/make_golden.py                  # every file
     python tests/golden/make_golden.py random_crop      # random_crop_windows.npz and random_area_windows.npz only
+    python tests/golden/make_golden.py pins             # hip_pixels.npz and crop_and_boxes.npz only
 
 box_encoder.npz   inputs + outputs of BoundingBoxGraph::update_box_encoder_meta_data
                   (rocAL/source/meta_data/bounding_box_graph.cpp:150-220) for offset / plain encodings
@@ -17,6 +18,13 @@ random_crop_windows.npz   RocalRandomCropDecParam windows (rocAL/source/paramete
 random_area_windows.npz   RocalRandomCropParam::fill_crop_dims windows (rocAL/source/parameters/parameter_random_crop.cpp:48-97,
                   the rule of rocalRandomCrop / rocalCropResize) for fixed parameter values and for the class's default
                   ranges under a ParameterFactory seed (with the index of the first seed-table entry the class took)
+hip_pixels.npz    the reference's own pixel kernels (rocAL/rocAL_hip/rocal_hip_kernels.cpp, compiled for the host by
+                  oracle/build.py into oracle/_ref/libref_hip.so) on small images: resize_bilinear_pkd_hip_tensor,
+                  resize_generic_pln1_hip_tensor (triangular filter, one plane per channel) and the four
+                  Hip_CopyInt8To* converters; inputs and outputs are stored
+crop_and_boxes.npz   RocalCropParam::fill_crop_dims windows in its three modes (parameter_rocal_crop.cpp:49-85) and
+                  BoundingBoxGraph::update_random_bbox_meta_data (bounding_box_graph.cpp:71-118) on normalised and
+                  pixel boxes
 """
 import ctypes
 import os
@@ -78,6 +86,98 @@ def random_area():
         out["windows_%d" % k] = win
     np.savez_compressed(os.path.join(HERE, "random_area_windows.npz"), **out)
     print("wrote random_area_windows.npz")
+
+
+def hip_case_images(rng, n, lo, hi):
+    """n small interleaved RGB images packed one after another: (arena, widths, heights, strides, offsets)."""
+    ws = rng.integers(lo, hi + 1, n).astype(np.uint32)
+    hs = rng.integers(lo, hi + 1, n).astype(np.uint32)
+    offs = np.zeros(n, dtype=np.uint64)
+    offs[1:] = np.cumsum(ws.astype(np.uint64) * hs * 3)[:-1]
+    arena = rng.integers(0, 256, int((ws.astype(np.int64) * hs * 3).sum()) + 16, dtype=np.uint8)
+    # half of the images smooth (a ramp plus a little noise): interpolated values then sit near .5 boundaries
+    for i in range(0, n, 2):
+        w, h = int(ws[i]), int(hs[i])
+        ramp = (np.add.outer(np.arange(h) * 3, np.arange(w) * 2)[:, :, None] + np.array([0, 40, 90])) % 256
+        img = np.clip(ramp + rng.integers(-2, 3, (h, w, 3)), 0, 255).astype(np.uint8)
+        arena[int(offs[i]):int(offs[i]) + w * h * 3] = img.reshape(-1)
+    return arena, ws, hs, ws * 3, offs
+
+
+def planes_of(arena, ws, hs, offs, c):
+    """Channel c of every image as single-channel planes packed one after another."""
+    pl, po, off = [], [], 0
+    for i in range(len(ws)):
+        w, h = int(ws[i]), int(hs[i])
+        img = arena[int(offs[i]):int(offs[i]) + w * h * 3].reshape(h, w, 3)[:, :, c]
+        pl.append(img.reshape(-1).copy())
+        po.append(off)
+        off += w * h
+    return np.concatenate(pl + [np.zeros(16, np.uint8)]), np.array(po, dtype=np.uint64)
+
+
+def hip_pixels():
+    assert O.ref_hip() is not None, "the reference tree is needed to generate golden vectors"
+    rng = np.random.Generator(np.random.PCG64(779))
+    n = 10
+    arena, ws, hs, ss, offs = hip_case_images(rng, n, 2, 36)
+    dws = rng.integers(1, 44, n).astype(np.uint32)
+    dhs = rng.integers(1, 44, n).astype(np.uint32)
+    dws[0], dhs[0] = ws[0], hs[0]                  # identity
+    dws[1], dhs[1] = ws[1] * 2, hs[1] * 2 + 1      # up-scale
+    out = {"arena": arena, "src_w": ws, "src_h": hs, "src_offset": offs, "dst_w": dws, "dst_h": dhs}
+    out["bilinear"] = O.ref_hip_resize_bilinear(arena, ws, hs, ss, offs, dws, dhs)
+    for c in range(3):
+        planes, po = planes_of(arena, ws, hs, offs, c)
+        out["triangular_c%d" % c] = O.ref_hip_resize_generic(planes, ws, hs, ws, po, dws, dhs)
+    img = rng.integers(0, 256, (2, 9, 13, 3), dtype=np.uint8)
+    mul, add = S.normalize_tables()
+    out["convert_src"], out["convert_mul"], out["convert_add"] = img, np.array(mul, np.float32), np.array(add, np.float32)
+    for nchw in (0, 1):
+        for fp16 in (0, 1):
+            for rev in (0, 1):
+                # the half-precision NHWC converter indexes rows by y*W + x*3 (rocal_hip_kernels.cpp:110), which only
+                # addresses a one-row image correctly: that variant is recorded on the first row of the batch
+                src = img[:, :1] if (fp16 and not nchw) else img
+                out["convert_nchw%d_fp16%d_rev%d" % (nchw, fp16, rev)] = O.ref_hip_copy_int8(src, nchw, fp16, mul, add, rev)
+    np.savez_compressed(os.path.join(HERE, "hip_pixels.npz"), **out)
+    print("wrote hip_pixels.npz")
+
+
+def crop_and_boxes():
+    assert O.ref() is not None, "the reference tree is needed to generate golden vectors"
+    rng = np.random.Generator(np.random.PCG64(780))
+    out = {}
+    for k in range(9):
+        mode = k % 3
+        wh = rng.integers(1, 900, (48, 2)).astype(np.uint32)
+        cw, ch = int(rng.integers(0, 700)), int(rng.integers(0, 700))
+        if k == 0:
+            cw = ch = 224
+        f = rng.uniform(0, 1, 4).astype(np.float32) if mode != 1 else np.array([rng.integers(0, 900), rng.integers(0, 900), 0, 0], np.float32)
+        out["crop_wh_%d" % k], out["crop_args_%d" % k] = wh, np.array([mode, cw, ch, *f], dtype=np.float64)
+        out["crop_windows_%d" % k] = O.ref_rocal_crop_windows(wh, mode, cw, ch, f)
+    for k in range(4):
+        n = 12
+        counts = rng.integers(0, 10, n)
+        tot = int(counts.sum())
+        roi = rng.integers(50, 900, (n, 2)).astype(np.uint32)
+        ctr, sz = rng.uniform(0, 1, (tot, 2)), rng.uniform(0.02, 0.6, (tot, 2))
+        boxes = np.concatenate([np.clip(ctr - sz / 2, 0, 1), np.clip(ctr + sz / 2, 0, 1)], 1).astype(np.float32)
+        if k % 2:
+            rep = np.repeat(roi, counts, axis=0).astype(np.float32)
+            boxes = (boxes * np.concatenate([rep, rep], 1)).astype(np.float32)
+        labels = rng.integers(1, 81, tot).astype(np.int32)
+        offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        crops = np.concatenate([rng.uniform(0, 0.5, (n, 2)), rng.uniform(0.3, 1, (n, 2))], 1).astype(np.float32)
+        if k < 2:
+            crops[:, 2:] = 1.0
+        ob, ol, oo = O.ref_random_bbox_meta(boxes, labels, offsets, crops, roi)
+        for name, v in (("boxes", boxes), ("labels", labels), ("offsets", offsets), ("crops", crops), ("roi", roi),
+                        ("out_boxes", ob), ("out_labels", ol), ("out_offsets", oo)):
+            out["bbox_%s_%d" % (name, k)] = v
+    np.savez_compressed(os.path.join(HERE, "crop_and_boxes.npz"), **out)
+    print("wrote crop_and_boxes.npz")
 
 
 def main():
@@ -165,7 +265,12 @@ if __name__ == "__main__":
     if sys.argv[1:] == ["random_crop"]:
         random_crop()
         random_area()
+    elif sys.argv[1:] == ["pins"]:
+        hip_pixels()
+        crop_and_boxes()
     else:
         main()
         random_crop()
         random_area()
+        hip_pixels()
+        crop_and_boxes()
