@@ -85,6 +85,10 @@ typedef struct rb200_resample_sample {
  */
 enum { RB200_INTERP_BILINEAR = 0, RB200_INTERP_TRIANGULAR = 1, RB200_INTERP_BICUBIC = 2, RB200_INTERP_LANCZOS = 3,
        RB200_INTERP_GAUSSIAN = 4, RB200_INTERP_NEAREST = 5 };
+/* Kernel choice for bilinear launches. AUTO picks by output width and source span; TILE forces the shared-memory
+ * tile kernel where AUTO would stream rows through the bulk-copy ring; withholding h_samples selects the direct
+ * (global gather) kernel. All three compute the same values. */
+enum { RB200_RESAMPLE_PATH_AUTO = 0, RB200_RESAMPLE_PATH_TILE = 1 };
 typedef struct rb200_resample_params {
     void* out;
     int32_t out_w, out_h;
@@ -93,6 +97,7 @@ typedef struct rb200_resample_params {
     float mul[3];
     float add[3];
     int32_t interpolation;
+    int32_t path;                /* RB200_RESAMPLE_PATH_*: which of the bilinear kernels runs; the results are identical */
 } rb200_resample_params;
 
 /* Resize / ResizeCropMirror / ResizeMirrorNormalize / fused Resize+CropMirrorNormalize.

@@ -22,7 +22,7 @@ class _ResampleParams(ctypes.Structure):
     _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
-                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32)]
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32)]
 
 
 class _PointwiseParams(ctypes.Structure):

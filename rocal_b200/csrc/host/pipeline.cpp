@@ -966,16 +966,20 @@ void Pipeline::ssd_crop(Node& nd, const std::vector<int>& in_w, const std::vecto
         nd.crop.chv[i] = std::max(1u, std::min(ch, H - y1));
         box0 += (size_t)nb;
     }
-    transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in_w, in_h);
+    transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in_w, in_h, true);
 }
 
-// Boxes follow a crop window: those whose centre lies outside are dropped, the rest are clipped and
-// re-normalised to the window (mask + clip of update_random_bbox_meta_data,
-// source/meta_data/bounding_box_graph.cpp:98-110); a sample left without boxes gets one empty box
-// with label 0, as the reference's meta nodes do.
+// Boxes follow a crop window, in normalized ltrb (a box times the image size is the reference's pixel box).
+// by_centre = true: the rule of the SSD crop, update_random_bbox_meta_data (source/meta_data/bounding_box_graph.cpp:
+// 98-110) — a box is kept when its centre lies strictly inside the window; a sample left without boxes gets one
+// empty box with label 0. by_centre = false: the rule of the Crop / CropMirrorNormalize / ResizeCropMirror meta nodes
+// (source/meta_data/meta_node_crop.cpp:59-78, meta_node_crop_mirror_normalize.cpp:53-90,
+// meta_node_resize_crop_mirror.cpp:66-100) — a box is kept when at least a quarter of its area lies in the window
+// (MetaNode::BBoxIntersectionOverUnion without is_iou, threshold 0.25, include/meta_data/meta_node.h:39-58); a sample
+// left without boxes gets the whole window with label 0. Kept boxes are clipped to the window and re-normalised to it.
 void Pipeline::transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, const std::vector<unsigned>& y1,
                                       const std::vector<unsigned>& cw, const std::vector<unsigned>& ch,
-                                      const std::vector<int>& in_w, const std::vector<int>& in_h) {
+                                      const std::vector<int>& in_w, const std::vector<int>& in_h, bool by_centre) {
     if (s.counts.empty()) return;
     std::vector<float> nb;
     std::vector<int> nl, nc(s.counts.size(), 0);
@@ -986,8 +990,17 @@ void Pipeline::transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, 
         float w = r - l, h = b - t;
         for (int j = 0; j < s.counts[i]; j++) {
             const float* q = s.boxes.data() + (box0 + j) * 4;
-            float xc = 0.5f * (q[0] + q[2]), yc = 0.5f * (q[1] + q[3]);
-            if (xc > l && xc < r && yc > t && yc < b) {
+            bool keep;
+            if (by_centre) {
+                float xc = 0.5f * (q[0] + q[2]), yc = 0.5f * (q[1] + q[3]);
+                keep = xc > l && xc < r && yc > t && yc < b;
+            } else {
+                float xa = std::max(q[0], l), ya = std::max(q[1], t), xb = std::min(q[2], r), yb = std::min(q[3], b);
+                float inter = std::max(0.f, xb - xa) * std::max(0.f, yb - ya);
+                float area = (q[3] - q[1]) * (q[2] - q[0]);
+                keep = inter / area >= 0.25f;      // 0/0 (an empty box) is NaN and drops the box, as in the reference
+            }
+            if (keep) {
                 nb.push_back((std::max(q[0], l) - l) / w);
                 nb.push_back((std::max(q[1], t) - t) / h);
                 nb.push_back((std::min(q[2], r) - l) / w);
@@ -997,7 +1010,8 @@ void Pipeline::transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, 
             }
         }
         if (nc[i] == 0) {
-            nb.insert(nb.end(), {0.f, 0.f, 0.f, 0.f});
+            if (by_centre) nb.insert(nb.end(), {0.f, 0.f, 0.f, 0.f});
+            else nb.insert(nb.end(), {0.f, 0.f, 1.f, 1.f});
             nl.push_back(0);
             nc[i] = 1;
         }
@@ -1008,17 +1022,19 @@ void Pipeline::transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, 
     s.counts.swap(nc);
 }
 
-// Horizontal mirror of normalized ltrb boxes (meta_node_flip.cpp:40-55, meta_node_crop_mirror_normalize.cpp:53-74).
-void Pipeline::mirror_boxes(Slot& s, const std::vector<int>& flags) {
+// Horizontal mirror of normalized ltrb boxes (meta_node_flip.cpp:40-55, meta_node_crop_mirror_normalize.cpp:53-74);
+// `vertical` mirrors top and bottom instead (the v_flip branch of meta_node_flip.cpp:56-60).
+void Pipeline::mirror_boxes(Slot& s, const std::vector<int>& flags, bool vertical) {
     if (s.counts.empty()) return;
     size_t box0 = 0;
+    const int lo = vertical ? 1 : 0, hi = vertical ? 3 : 2;
     for (size_t i = 0; i < s.counts.size(); i++) {
         if (flags[i]) {
             for (int j = 0; j < s.counts[i]; j++) {
                 float* q = s.boxes.data() + (box0 + j) * 4;
-                float l = 1.0f - q[2], r = 1.0f - q[0];
-                q[0] = l;
-                q[2] = r;
+                float l = 1.0f - q[hi], r = 1.0f - q[lo];
+                q[lo] = l;
+                q[hi] = r;
             }
         }
         box0 += (size_t)s.counts[i];
@@ -1067,7 +1083,7 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                 nd.dst_h.assign(n, (int)nd.dest_h);
                 out->roi_w = nd.dst_w;
                 out->roi_h = nd.dst_h;
-                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h);
+                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h, false);
                 std::vector<int> m;
                 int_array(nd.mirror, m);
                 mirror_boxes(s, m);
@@ -1080,7 +1096,7 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                     out->roi_w[i] = (int)std::min(nd.crop.cwv[i], (unsigned)out->max_w);
                     out->roi_h[i] = (int)std::min(nd.crop.chv[i], (unsigned)out->max_h);
                 }
-                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h);
+                transform_boxes_window(s, nd.crop.x1v, nd.crop.y1v, nd.crop.cwv, nd.crop.chv, in->roi_w, in->roi_h, false);
                 if (nd.kind == NodeKind::CROP_MIRROR_NORMALIZE) {
                     std::vector<int> m;
                     int_array(nd.mirror, m);
@@ -1102,6 +1118,8 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                 std::vector<int> m;
                 int_array(nd.flip_h, m);
                 mirror_boxes(s, m);
+                int_array(nd.flip_v, m);
+                mirror_boxes(s, m, true);
                 break;
             }
             case NodeKind::WARP_AFFINE: {

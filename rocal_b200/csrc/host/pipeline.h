@@ -300,8 +300,8 @@ class Pipeline {
     void ssd_crop(Node& nd, const std::vector<int>& in_w, const std::vector<int>& in_h, Slot& s);
     void transform_boxes_window(Slot& s, const std::vector<unsigned>& x1, const std::vector<unsigned>& y1,
                                 const std::vector<unsigned>& cw, const std::vector<unsigned>& ch,
-                                const std::vector<int>& in_w, const std::vector<int>& in_h);
-    void mirror_boxes(Slot& s, const std::vector<int>& flags);
+                                const std::vector<int>& in_w, const std::vector<int>& in_h, bool by_centre);
+    void mirror_boxes(Slot& s, const std::vector<int>& flags, bool vertical = false);
 
     size_t _batch;
     int _gpu_id;

@@ -1059,6 +1059,10 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
         set_error("rb200k_resample: bad interpolation %d", p->interpolation);
         return RB200_E_INVALID;
     }
+    if (p->path != RB200_RESAMPLE_PATH_AUTO && p->path != RB200_RESAMPLE_PATH_TILE) {
+        set_error("rb200k_resample: bad path %d", p->path);
+        return RB200_E_INVALID;
+    }
     cudaStream_t stream = (cudaStream_t)stream_v;
 
     ResampleLaunch L;
@@ -1120,8 +1124,7 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
         }
         pitch = (15 + max_span * 3 + 12 + 15) & ~15;
         // Wide tiles stream their rows through the bulk-copy ring; narrow ones use the tile kernel.
-        const char* force = getenv("RB200_RESAMPLE_MODE");
-        bool want_stream = twh >= 64 && !(force && force[0] == 't');
+        bool want_stream = twh >= 64 && p->path != RB200_RESAMPLE_PATH_TILE;
         if (want_stream) {
             int ns = 4;
             if ((size_t)2 * ns * pitch > 96 * 1024) ns = 2;

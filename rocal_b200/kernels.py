@@ -36,10 +36,11 @@ def _alloc_out(n, out_w, out_h, dtype, layout, device, out):
 
 
 def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
-             fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0):
+             fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0):
     """rb200k_resample. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
     already on the device (uploaded here when None). staged=False withholds the host table from
-    the launch so that the kernel gathers straight from global memory."""
+    the launch so that the kernel gathers straight from global memory; path=1 (RB200_RESAMPLE_PATH_TILE)
+    forces the shared-memory tile kernel."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
     if d_samples is None:
@@ -50,6 +51,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
     p.normalize = 1 if mul is not None else 0
     p.fill_padding = 1 if fill_padding else 0
     p.interpolation = int(interpolation)
+    p.path = int(path)
     for c in range(3):
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0

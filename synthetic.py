@@ -6,12 +6,18 @@ exact input. The builders return host-side numpy data: a packed uint8 arena with
 after another (row pitch = width*3, each image start rounded up to 256 bytes) and the per-sample
 tables of rocal_b200.tables.
 """
+import importlib.util
 import math
 import os
 
 import numpy as np
 
-from . import tables as T
+# The table layouts come from the package's tables.py, loaded by path: importing the package itself would load the
+# CUDA library, which the CPU arm of the benchmark and the oracle-only tests must not need.
+_spec = importlib.util.spec_from_file_location(
+    "_rocal_b200_tables", os.path.join(os.path.dirname(os.path.abspath(__file__)), "rocal_b200", "tables.py"))
+T = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(T)
 
 MEAN = (123.675, 116.28, 103.53)
 STD = (58.395, 57.12, 57.375)

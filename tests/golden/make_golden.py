@@ -36,7 +36,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 from oracle import pyoracle as O          # noqa: E402
-from rocal_b200 import synthetic as S     # noqa: E402
+import synthetic as S     # noqa: E402
 
 
 def random_crop():

@@ -1,0 +1,228 @@
+"""Operators of the augmentation path through the rocAL-facing API (rocal_b200.fn over the rb200_* C-ABI) with
+per-sample random parameters: ResizeCropMirror, Contrast, Hue, Saturation, Crop / CropFixed / CropCenterFixed, and
+bounding boxes that follow crops, mirrors, flips and resizes. Expected tables are rebuilt here from the parameters
+read back from the pipeline; pixels are compared bit for bit with the oracle, boxes with the restatements of the
+reference's meta nodes."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as O
+import synthetic as S
+from rocal_b200 import tables as T
+
+pytestmark = pytest.mark.gpu
+
+
+def _source(max_w, max_h):
+    from rocal_b200 import fn, types
+    img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=max_w, max_height=max_h)
+    return img
+
+
+def _pointwise_table(hs, ws, offs):
+    t = np.zeros(len(hs), dtype=T.POINTWISE_SAMPLE)
+    t["src_offset"], t["src_stride"], t["roi_w"], t["roi_h"] = offs, ws * 3, ws, hs
+    t["alpha"], t["sat"] = 1.0, 1.0
+    return t
+
+
+def _valid_equal(got, exp, ws, hs):
+    for i in range(len(ws)):
+        assert np.array_equal(got[i, :hs[i], :ws[i]], exp[i, :hs[i], :ws[i]]), "sample %d" % i
+
+
+def test_contrast_hue_saturation_random_parameters(cuda):
+    """rocalContrast / rocalHue / rocalSaturation with uniform random parameters, three outputs of one graph; ragged
+    image sizes inside max-shape outputs."""
+    from rocal_b200 import fn
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(30)
+    n = 24
+    pipe = Pipeline(batch_size=n, device_id=0, seed=13)
+    with pipe:
+        img = _source(300, 260)
+        cf, cc = fn.random.uniform(range=(0.2, 1.9)), fn.random.uniform(range=(60.0, 90.0))
+        hu = fn.random.uniform(range=(-359.0, 359.0))
+        sa = fn.random.uniform(range=(0.0, 2.0))
+        o_c = fn.contrast(img, contrast=cf, contrast_center=cc)
+        o_h = fn.hue(img, hue=hu)
+        o_s = fn.saturation(img, saturation=sa)
+        pipe.set_outputs(o_c, o_h, o_s)
+    pipe.build()
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (40, 260), (40, 300))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        t_c, t_h, t_s = pipe.get_output_tensors()
+        tab = _pointwise_table(hs, ws, offs)
+        tab["alpha"], tab["beta"] = pipe.get_float_array(cf), pipe.get_float_array(cc)
+        assert len(np.unique(tab["alpha"])) > n // 2 and tab["beta"].min() >= 60.0
+        _valid_equal(t_c.numpy(), O.pointwise(arena, tab, 300, 260, T.COLOR_CONTRAST), ws, hs)
+        tab = _pointwise_table(hs, ws, offs)
+        tab["hue"] = pipe.get_float_array(hu)
+        assert tab["hue"].min() < -30 and tab["hue"].max() > 30
+        _valid_equal(t_h.numpy(), O.pointwise(arena, tab, 300, 260, T.COLOR_TWIST), ws, hs)
+        tab = _pointwise_table(hs, ws, offs)
+        tab["sat"] = pipe.get_float_array(sa)
+        _valid_equal(t_s.numpy(), O.pointwise(arena, tab, 300, 260, T.COLOR_TWIST), ws, hs)
+        assert t_c.roi()[:, 2:].tolist() == np.stack([ws, hs], 1).tolist()
+    pipe.rocal_release()
+
+
+def test_resize_crop_mirror_and_crops(cuda):
+    """rocalResizeCropMirrorFixed (a 200 x 160 corner stretched to 320 x 240, coin-flip mirror), rocalCropFixed at an
+    absolute corner, rocalCropCenterFixed and the random rocalCrop: windows against RocalCropParam's rule, pixels
+    against the oracle, output ROIs."""
+    from rocal_b200 import fn
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(31)
+    n = 16
+    pipe = Pipeline(batch_size=n, device_id=0, seed=17)
+    with pipe:
+        img = _source(400, 360)
+        mirror = fn.random.coin_flip()
+        o_rcm = fn.resize_crop_mirror(img, resize_width=320, resize_height=240, crop_w=200, crop_h=160, mirror=mirror)
+        o_fix = fn.crop(img, crop=[150, 180], crop_pos_x=37, crop_pos_y=21)
+        o_ctr = fn.center_crop(img, crop=[224, 224])
+        o_rnd = fn.crop(img)
+        pipe.set_outputs(o_rcm, o_fix, o_ctr, o_rnd)
+    pipe.build()
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (120, 360), (140, 400))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        wh = np.stack([ws, hs], axis=1)
+        t_rcm, t_fix, t_ctr, t_rnd = pipe.get_output_tensors()
+        m = pipe.get_int_array(mirror)
+        assert set(np.unique(m)) == {0, 1}
+        # ResizeCropMirror: window (0, 0, 200, 160) clipped to the image -> 320 x 240 -> mirror
+        win = O.rocal_crop_windows(wh, 1, 200, 160, (0, 0)).astype(np.int64)
+        got_win = pipe.get_crop_windows(o_rcm).astype(np.int64)
+        eff = np.stack([win[:, 0], win[:, 1], win[:, 4] - win[:, 0], win[:, 5] - win[:, 1]], 1)
+        assert np.array_equal(got_win, eff)
+        tab = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        tab["src_offset"], tab["src_stride"] = offs, ws * 3
+        tab["roi_x"], tab["roi_y"], tab["roi_w"], tab["roi_h"] = eff[:, 0], eff[:, 1], eff[:, 2], eff[:, 3]
+        tab["dst_w"], tab["dst_h"], tab["crop_w"], tab["crop_h"], tab["mirror"] = 320, 240, 320, 240, m
+        assert np.array_equal(t_rcm.numpy(), O.resample(arena, tab, 320, 240, T.UINT8, T.NHWC))
+        assert t_rcm.roi()[:, 2:].tolist() == [[320, 240]] * n
+        # fixed corner, centre and random crops: pure indexing
+        for t_out, handle, expect in ((t_fix, o_fix, O.rocal_crop_windows(wh, 1, 180, 150, (37, 21))),
+                                      (t_ctr, o_ctr, O.rocal_crop_windows(wh, 0, 224, 224, (0.5, 0.5))),
+                                      (t_rnd, o_rnd, None)):
+            got_win = pipe.get_crop_windows(handle).astype(np.int64)
+            if expect is not None:
+                e = expect.astype(np.int64)
+                assert np.array_equal(got_win, np.stack([e[:, 0], e[:, 1], e[:, 4] - e[:, 0], e[:, 5] - e[:, 1]], 1))
+            else:   # width and height factors in 0.55 .. 0.95 of the image, inside it
+                assert (got_win[:, 2] >= (0.55 * ws).astype(np.int64) - 1).all() and (got_win[:, 2] <= ws).all()
+                assert (got_win[:, 0] + got_win[:, 2] <= ws).all() and (got_win[:, 1] + got_win[:, 3] <= hs).all()
+            pix = t_out.numpy()
+            for i in range(n):
+                x, y, w, h = [int(v) for v in got_win[i]]
+                im = arena[int(offs[i]):int(offs[i]) + int(hs[i]) * int(ws[i]) * 3].reshape(hs[i], ws[i], 3)
+                assert np.array_equal(pix[i, :h, :w], im[y:y + h, x:x + w]), i
+            assert t_out.roi()[:, 2:].tolist() == got_win[:, 2:].tolist()
+    pipe.rocal_release()
+
+
+def _boxes_px(boxes, boffs, wh):
+    rep = np.repeat(wh, np.diff(boffs), axis=0).astype(np.float32)
+    return (np.asarray(boxes, dtype=np.float32) * np.concatenate([rep, rep], 1)).astype(np.float32)
+
+
+def _compare_boxes(pipe, exp_b, exp_l, exp_o, norm_wh):
+    b, l, c = pipe.get_bounding_boxes()
+    o = np.concatenate([[0], np.cumsum(c)]).astype(np.int32)
+    assert o.tolist() == exp_o.tolist()
+    assert l.tolist() == exp_l.tolist()
+    rep = np.repeat(np.asarray(norm_wh, dtype=np.float32), np.diff(exp_o), axis=0)
+    assert np.allclose(b, exp_b / np.concatenate([rep, rep], 1), atol=3e-6)
+    return int((exp_l > 0).sum())
+
+
+def test_boxes_follow_crop_mirror_flip_resize(cuda):
+    """Boxes through Crop -> Flip(h, v) -> ResizeCropMirror -> Resize, against the restatements of CropMetaNode,
+    FlipMetaNode, ResizeCropMirrorMetaNode and ResizeMetaNode chained in pixel coordinates (the pipeline keeps
+    boxes normalised to the current image, so its output is compared after division by the final size)."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(32)
+    n = 24
+    pipe = Pipeline(batch_size=n, device_id=0, seed=19)
+    with pipe:
+        img = _source(500, 500)
+        c = fn.crop(img, crop=[260, 300], crop_pos_x=40, crop_pos_y=30)
+        hf, vf = fn.random.coin_flip(), fn.random.coin_flip()
+        f = fn.flip(c, horizontal=hf, vertical=vf)
+        mirror = fn.random.coin_flip()
+        r = fn.resize_crop_mirror(f, resize_width=200, resize_height=150, crop_w=180, crop_h=170, mirror=mirror)
+        out = fn.resize(r, resize_width=128, resize_height=96, scaling_mode=types.SCALING_MODE_STRETCH)
+        pipe.set_outputs(out)
+    pipe.build()
+    kept = 0
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (200, 500), (200, 500))
+        boxes, labels, boffs = S.random_boxes(rng, n, (1, 20))
+        pipe.feed_boxes(boxes, labels, np.diff(boffs))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        wh = np.stack([ws, hs], axis=1)
+        w1 = pipe.get_crop_windows(c).astype(np.int64)
+        b, l, o = O.meta_crop(_boxes_px(boxes, boffs, wh), labels, boffs, w1)
+        b, l, o = O.meta_flip(b, l, o, w1[:, 2:], pipe.get_int_array(hf), pipe.get_int_array(vf))
+        w2 = pipe.get_crop_windows(r).astype(np.int64)
+        e2 = O.rocal_crop_windows(w1[:, 2:], 1, 180, 170, (0, 0)).astype(np.int64)
+        assert np.array_equal(w2, np.stack([e2[:, 0], e2[:, 1], e2[:, 4] - e2[:, 0], e2[:, 5] - e2[:, 1]], 1))
+        b, l, o = O.meta_crop(b, l, o, w2, mirror=pipe.get_int_array(mirror), resize_to=(200, 150))
+        b, l, o = O.meta_resize(b, l, o, [(200, 150)] * n, [(128, 96)] * n)
+        kept += _compare_boxes(pipe, b, l, o, [(128, 96)] * n)
+        assert pipe.get_output_tensors()[0].dims() == [n, 96, 128, 3]
+    assert kept > 40
+    pipe.rocal_release()
+
+
+def test_boxes_follow_ssd_crop(cuda):
+    """configs[4]'s metadata path: the boxes behind rocalSSDRandomCrop -> Resize(300 x 300) -> CropMirrorNormalize
+    against the reference's update_random_bbox_meta_data (pinned restatement: centre strictly inside, clip, shift)
+    re-normalised to the window, then the CropMirrorNormalize meta node; the encoder then runs on those boxes."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(33)
+    n = 32
+    anchors = S.ssd300_anchors()
+    pipe = Pipeline(batch_size=n, device_id=0, seed=23)
+    with pipe:
+        img = _source(800, 800)
+        c = fn.ssd_random_crop(img)
+        r = fn.resize(c, resize_width=300, resize_height=300, scaling_mode=types.SCALING_MODE_STRETCH)
+        mirror = fn.random.coin_flip()
+        out = fn.crop_mirror_normalize(r, crop=[300, 300], crop_pos_x=0.0, crop_pos_y=0.0, mean=list(S.MEAN), std=list(S.STD),
+                                       mirror=mirror, output_layout=types.NCHW, output_dtype=types.FLOAT)
+        fn.box_encoder(anchors=anchors, criteria=0.5, means=[0, 0, 0, 0], stds=[0.1, 0.1, 0.2, 0.2], offset=True, scale=1.0)
+        pipe.set_outputs(out)
+    pipe.build()
+    kept = 0
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (300, 800), (300, 800))
+        boxes, labels, boffs = S.random_boxes(rng, n)
+        pipe.feed_boxes(boxes, labels, np.diff(boffs))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        win = pipe.get_crop_windows(c).astype(np.float32)
+        # the window as fractions of the image, a 1 x 1 "decoded size": the function then works on normalised boxes
+        frac = np.stack([win[:, 0] / ws, win[:, 1] / hs, (win[:, 0] + win[:, 2]) / ws - win[:, 0] / ws,
+                         (win[:, 1] + win[:, 3]) / hs - win[:, 1] / hs], 1).astype(np.float32)
+        b, l, o = O.random_bbox_meta(boxes, labels, boffs, frac, np.ones((n, 2), np.uint32))
+        rep = np.repeat(frac[:, 2:], np.diff(o), axis=0)
+        b = (b / np.concatenate([rep, rep], 1)).astype(np.float32)          # re-normalised to the window
+        # CropMirrorNormalize over the whole 300 x 300 image: every box is kept, mirrored where the flag is set
+        b, l, o = O.meta_crop(b * 300.0, l, o, [(0, 0, 300, 300)] * n, mirror=pipe.get_int_array(mirror))
+        kept += _compare_boxes(pipe, b, l, o, [(300, 300)] * n)
+        gb, gl, gc = pipe.get_bounding_boxes()
+        eb, el = O.box_encode(gb, gl, np.concatenate([[0], np.cumsum(gc)]).astype(np.int32), anchors, 0.5, (0, 0, 0, 0),
+                              (0.1, 0.1, 0.2, 0.2), True, 1.0)
+        xb, xl = pipe.get_encoded_boxes_and_lables()
+        assert np.array_equal(xl, el) and np.allclose(xb, eb, rtol=1e-5, atol=1e-6)
+    assert kept > 100
+    pipe.rocal_release()

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from oracle import pyoracle as O
-from rocal_b200 import synthetic as S
+import synthetic as S
 from rocal_b200 import tables as T
 
 pytestmark = pytest.mark.gpu
@@ -164,3 +164,134 @@ def test_cpp_client(cuda, tmp_path):
         assert np.array_equal(outs[2][0][i, :h, :w], im[y:y + h, x:x + w]) and outs[2][1][i, 2:].tolist() == [w, h]
         assert np.array_equal(outs[3][0][i, :ih, :iw], im) and outs[3][1][i, 2:].tolist() == [iw, ih]
     assert sizes.tolist() == wh.tolist()
+
+
+def _pointwise_table(hs, ws, offs, windows=None, flip_h=0, alpha=1.0, beta=0.0, hue=0.0, sat=1.0):
+    n = len(hs)
+    t = np.zeros(n, dtype=T.POINTWISE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    if windows is None:
+        t["roi_w"], t["roi_h"] = ws, hs
+    else:
+        t["roi_x"], t["roi_y"], t["roi_w"], t["roi_h"] = windows[:, 0], windows[:, 1], windows[:, 2], windows[:, 3]
+    t["flip_h"] = flip_h
+    t["alpha"], t["beta"], t["hue"], t["sat"] = alpha, beta, hue, sat
+    return t
+
+
+def test_cpp_ops_client(cuda, tmp_path):
+    """The fixed-parameter operator calls of the reference's unit tests (rocalResizeCropMirrorFixed 400x400 from a
+    200x200 crop, rocalContrastFixed 30/80, rocalHueFixed 150, rocalSaturationFixed 0.3, rocalCropFixed /
+    rocalCropCenterFixed 224, rocalBrightnessFixed 1.9/20, rocalColorTwistFixed, rocalFlipFixed) from C++, every output
+    bit-equal to the oracle on tables built here; and boxes behind a mirrored rocalCropMirrorNormalize against the
+    restatement of the reference's meta node."""
+    lib_dir = os.path.join(ROOT, "rocal_b200")
+    exe = str(tmp_path / "ops_client")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "harness", "rocal_ops_client.cpp"), "-L", lib_dir, "-lrocal_b200",
+                    "-Wl,-rpath," + lib_dir, "-o", exe], check=True)
+    rng = S.rng_for(26)
+    n = 5
+    arena, hs, ws, offs = S.make_images(rng, n, (180, 420), (190, 460))
+    assert hs.min() < 224 < hs.max()                     # some images are smaller than the 224 crop
+    boxes, labels, boffs = S.random_boxes(rng, n, (1, 14))
+    counts = np.diff(boffs).astype(np.int32)
+    with open(tmp_path / "in.bin", "wb") as f:
+        f.write(struct.pack("<i", n))
+        for i in range(n):
+            f.write(struct.pack("<ii", int(hs[i]), int(ws[i])))
+        for i in range(n):
+            f.write(_image(arena, offs, i, hs, ws).tobytes())
+        f.write(struct.pack("<i", len(labels)))
+        f.write(counts.tobytes())
+        f.write(np.ascontiguousarray(boxes, dtype=np.float32).tobytes())
+        f.write(np.ascontiguousarray(labels, dtype=np.int32).tobytes())
+    r = subprocess.run([exe, str(tmp_path / "in.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-2000:]
+    # the oracle reads the same tightly packed images the client was given
+    packed = np.concatenate([_image(arena, offs, i, hs, ws).reshape(-1) for i in range(n)] + [np.zeros(64, np.uint8)])
+    poffs = np.concatenate([[0], np.cumsum(hs.astype(np.int64) * ws * 3)[:-1]]).astype(np.uint64)
+    raw = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
+    pos = 0
+
+    def take(dtype, count):
+        nonlocal pos
+        a = raw[pos:pos + count * np.dtype(dtype).itemsize].view(dtype)
+        pos += count * np.dtype(dtype).itemsize
+        return a
+
+    outs = []
+    for k in range(9):
+        oh, ow = [int(v) for v in take(np.int32, 2)]
+        outs.append((take(np.uint8, n * oh * ow * 3).reshape(n, oh, ow, 3), take(np.uint32, n * 4).reshape(n, 4)))
+    wh = np.stack([ws, hs], axis=1)
+    max_w, max_h = int(ws.max()), int(hs.max())
+
+    # 0: ResizeCropMirrorFixed: the 200 x 200 corner (clipped to the image) stretched to 400 x 400, mirrored
+    win = O.rocal_crop_windows(wh, 1, 200, 200, (0, 0)).astype(np.int64)
+    tab = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    tab["src_offset"], tab["src_stride"] = poffs, ws * 3
+    tab["roi_x"], tab["roi_y"] = win[:, 0], win[:, 1]
+    tab["roi_w"], tab["roi_h"] = win[:, 4] - win[:, 0], win[:, 5] - win[:, 1]
+    tab["dst_w"], tab["dst_h"], tab["crop_w"], tab["crop_h"], tab["mirror"] = 400, 400, 400, 400, 1
+    assert outs[0][0].shape[1:3] == (400, 400)
+    assert np.array_equal(outs[0][0], O.resample(packed, tab, 400, 400, T.UINT8, T.NHWC))
+    assert outs[0][1][:, 2:].tolist() == [[400, 400]] * n
+
+    def colour(k, op, **kw):
+        exp = O.pointwise(packed, _pointwise_table(hs, ws, poffs, **kw), max_w, max_h, op)
+        assert outs[k][0].shape[1:3] == (max_h, max_w), k
+        for i in range(n):
+            assert np.array_equal(outs[k][0][i, :hs[i], :ws[i]], exp[i, :hs[i], :ws[i]]), (k, i)
+        assert outs[k][1][:, 2:].tolist() == wh.tolist(), k
+
+    colour(1, T.COLOR_CONTRAST, alpha=30.0, beta=80.0)
+    colour(2, T.COLOR_TWIST, hue=150.0)
+    colour(3, T.COLOR_TWIST, sat=0.3)
+    colour(6, T.COLOR_BRIGHTNESS, alpha=1.90, beta=20.0)
+    colour(7, T.COLOR_TWIST, alpha=0.2, beta=10.0, hue=100.0, sat=0.25)
+    colour(8, T.COLOR_NONE, flip_h=1)
+    # 4 / 5: CropFixed at the corner, CropCenterFixed: pure indexing
+    for k, win in ((4, O.rocal_crop_windows(wh, 1, 224, 224, (0, 0))), (5, O.rocal_crop_windows(wh, 0, 224, 224, (0.5, 0.5)))):
+        win = win.astype(np.int64)
+        assert outs[k][0].shape[1:3] == (224, 224)
+        for i in range(n):
+            x, y = int(win[i, 0]), int(win[i, 1])
+            w, h = int(win[i, 4]) - x, int(win[i, 5]) - y
+            im = _image(arena, offs, i, hs, ws)
+            assert np.array_equal(outs[k][0][i, :h, :w], im[y:y + h, x:x + w]), (k, i)
+            assert outs[k][1][i].tolist() == [0, 0, w, h], (k, i)
+
+    # graph 2: boxes behind CropMirrorNormalize(120 x 160 window, anchors 0.25 / 0.75, mirror)
+    win2 = take(np.uint32, n * 4).reshape(n, 4).astype(np.int64)
+    exp_win = O.rocal_crop_windows(wh, 0, 160, 120, (0.25, 0.75)).astype(np.int64)
+    assert np.array_equal(win2, np.stack([exp_win[:, 0], exp_win[:, 1], exp_win[:, 4] - exp_win[:, 0], exp_win[:, 5] - exp_win[:, 1]], 1))
+    got_b, got_l, got_c = [], [], []
+    for i in range(n):
+        c = int(take(np.int32, 1)[0])
+        got_b.append(take(np.float32, c * 4).reshape(c, 4))
+        got_l.append(take(np.int32, c))
+        got_c.append(c)
+    assert pos == len(raw)
+    _check_boxes_after_crop(boxes, labels, boffs, wh, win2, [1] * n, got_b, got_l)
+
+
+def _image(arena, offs, i, hs, ws):
+    o, h, w = int(offs[i]), int(hs[i]), int(ws[i])
+    return arena[o:o + h * w * 3].reshape(h, w, 3)
+
+
+def _check_boxes_after_crop(boxes, labels, boffs, wh, windows, mirror, got_b, got_l):
+    """Boxes read back from the pipeline (normalized to the window) against the restatement of the reference's
+    Crop / CropMirrorNormalize meta node run on the same boxes in pixels (meta_node_crop_mirror_normalize.cpp:53-90)."""
+    n = len(wh)
+    rep = np.repeat(wh, np.diff(boffs), axis=0).astype(np.float32)
+    px = (np.asarray(boxes, dtype=np.float32) * np.concatenate([rep, rep], 1)).astype(np.float32)
+    eb, el, eo = O.meta_crop(px, labels, boffs, windows, mirror=mirror)
+    kept = 0
+    for i in range(n):
+        e = eb[eo[i]:eo[i + 1]] / np.array([windows[i][2], windows[i][3]] * 2, dtype=np.float32)
+        assert got_l[i].tolist() == el[eo[i]:eo[i + 1]].tolist(), i
+        assert np.allclose(got_b[i], e, atol=2e-6), i
+        kept += int((el[eo[i]:eo[i + 1]] > 0).sum())
+    assert kept >= 3

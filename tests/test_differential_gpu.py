@@ -8,7 +8,7 @@ import torch
 
 from oracle import pyoracle as O
 from rocal_b200 import kernels as K
-from rocal_b200 import synthetic as S
+import synthetic as S
 from rocal_b200 import tables as T
 
 pytestmark = pytest.mark.gpu

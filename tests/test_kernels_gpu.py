@@ -4,13 +4,12 @@ Tolerances (stated by the task): bit-exact for indexing ops and uint8 paths comp
 same operation order; <= 1 LSB for uint8 in general; 1e-5 relative for fp32; 1e-3 for fp16.
 The kernels are written to reproduce the oracle's operation order, so most checks are exact.
 """
-import os
 
 import numpy as np
 import pytest
 
 from oracle import pyoracle as O
-from rocal_b200 import synthetic as S
+import synthetic as S
 from rocal_b200 import tables as T
 
 pytestmark = pytest.mark.gpu
@@ -47,12 +46,8 @@ def test_resize_cmn_config0(cuda, dtype, layout):
     ref = O.resample(arena, t, 224, 224, dtype, layout, mul, add)
     for staged, force_tile in ((True, False), (True, True), (False, False)):
         # three code paths: strip-streaming kernel, shared-memory tile kernel, direct gather
-        if force_tile:
-            os.environ["RB200_RESAMPLE_MODE"] = "tile"
-        try:
-            got = K.resample(_dev(arena, cuda), t, 224, 224, dtype, layout, mul, add, staged=staged).cpu().numpy()
-        finally:
-            os.environ.pop("RB200_RESAMPLE_MODE", None)
+        got = K.resample(_dev(arena, cuda), t, 224, 224, dtype, layout, mul, add, staged=staged,
+                         path=1 if force_tile else 0).cpu().numpy()
         assert _device_status() == 0
         if dtype == T.FP32:
             _assert_fp(got, ref, 1e-5, "fp32")
@@ -76,6 +71,23 @@ def test_resize_cmn_config1_shapes(cuda):
     got = K.resample(_dev(arena, cuda), t, 224, 224, T.FP16, T.NCHW, mul, add).cpu().numpy()
     _assert_fp(got, ref, 1e-3, "fp16")
     assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+
+
+def test_resize_cmn_config1_full_batch(cuda):
+    """The launch the benchmark times: all 1024 images of configs[1] (300..1080 px sides, fp16 NCHW, 32-row strips,
+    the ring depth picked from the widest source span of the batch), every output bit compared with the oracle."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(1)
+    arena, hs, ws, offs = S.make_images(rng, 1024, (300, 1080), (300, 1080))
+    t = S.classification_tables(rng, hs, ws, offs)
+    mul, add = S.normalize_tables()
+    ref = O.resample(arena, t, 224, 224, T.FP16, T.NCHW, mul, add)
+    got = K.resample(_dev(arena, cuda), t, 224, 224, T.FP16, T.NCHW, mul, add).cpu().numpy()
+    assert _device_status() == 0
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+    # a checksum of per-sample checksums, so that a later change of the generator or the kernel shows up as one number
+    per = got.view(np.uint16).reshape(1024, -1).astype(np.uint64).sum(axis=1)
+    assert int(per.sum()) == int(ref.view(np.uint16).astype(np.uint64).sum())
 
 
 def test_resize_only_ragged_output(cuda):

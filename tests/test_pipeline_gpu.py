@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from oracle import pyoracle as O
-from rocal_b200 import synthetic as S
+import synthetic as S
 from rocal_b200 import tables as T
 
 pytestmark = pytest.mark.gpu

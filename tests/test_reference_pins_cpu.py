@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle import pyoracle as O
-from rocal_b200 import synthetic as S
+import synthetic as S
 from rocal_b200 import tables as T
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
