@@ -301,8 +301,11 @@ def test_coco_source_pipeline(cuda, tmp_path):
     at = 0
     for nm, c in zip(names, c2):
         exp = truth[nm]
-        if not exp:                                   # an image without annotations keeps one empty box, label 0
-            assert c == 1 and l2[at] == 0 and b2[at].tolist() == [1.0, 0.0, 1.0, 0.0]      # the empty box, mirrored
+        if not exp:
+            # an image without annotations arrives with one empty box; CropMirrorNormalize's metadata rule drops it
+            # (no area inside the window) and answers with the whole window and label 0
+            # (meta_node_crop_mirror_normalize.cpp:56,84-88)
+            assert c == 1 and l2[at] == 0 and b2[at].tolist() == [0.0, 0.0, 1.0, 1.0]
         else:
             assert c == len(exp)
             for k, (box, lab) in enumerate(exp):
