@@ -53,6 +53,27 @@ enum { RB200_UPLOAD_WHOLE = 0, RB200_UPLOAD_FOOTPRINT = 1, RB200_UPLOAD_ZERO_COP
 RB200_API unsigned long long rb200_get_h2d_bytes(rb200_context ctx);
 RB200_API int rb200_set_upload_mode(rb200_context ctx, int mode);
 
+/* [extension] Arithmetic of the colour operators for the batches fed from now on: 0 = RB200_ARITH_EXACT (default;
+ * bit-identical to the CPU restatement), 1 = RB200_ARITH_FAST (every uint8 output within one level of EXACT,
+ * about twice the ColorTwist / Hue / Saturation throughput); see rb200_kernels.h. Call between rocalVerify and the
+ * feed of the first batch it should apply to. Returns 0, or -1 for a bad handle or mode. */
+RB200_API int rb200_set_arithmetic(rb200_context ctx, int mode);
+
+/* [extension] Stream hand-off for zero-copy consumers. The output tensors of the batch that rb200_run returned alias
+ * ring buffers that go back to the pipeline at the next rb200_run (the reference's rule, master_graph.cpp:928-938);
+ * the reference's PyTorch plugin copies them synchronously first (rocAL_pybind/amd/rocal/plugin/pytorch.py:118-143).
+ * A consumer that instead reads them in place on its own CUDA stream calls this before the next rb200_run with that
+ * stream (a cudaStream_t; NULL = the legacy default stream): the pipeline records an event there and makes its own
+ * streams wait for it before the buffers are written again. No host synchronisation takes place. Returns 0 / -1. */
+RB200_API int rb200_consumer_fence(rb200_context ctx, void* cuda_stream);
+
+/* [test hook] Self-test of the bounded waits: while wait_cycles is non-zero, the resample and pointwise launches of
+ * the batches fed from now on go through rb200k_resample_probe / rb200k_pointwise_probe with that wait limit (SM
+ * clock cycles) and skip_row (see rb200_kernels.h); rb200_run then reports the batch as failed
+ * (ROCAL_RUNTIME_ERROR, message in rb200_get_error_message) instead of handing out incomplete outputs, and the
+ * context stays usable. wait_cycles = 0 switches the probe off. */
+RB200_API int rb200_set_wait_probe(rb200_context ctx, unsigned long long wait_cycles, int skip_row);
+
 /* ---- parameters (rocal_api_parameters.h:39-161) ---- */
 RB200_API void rb200_set_seed(unsigned seed);
 RB200_API unsigned rb200_get_seed(void);

@@ -98,6 +98,9 @@ typedef struct rb200_resample_params {
     float add[3];
     int32_t interpolation;
     int32_t path;                /* RB200_RESAMPLE_PATH_*: which of the bilinear kernels runs; the results are identical */
+    int32_t* status;             /* where a kernel that gives up on a bounded wait writes 1: a 4-byte word the device can
+                                    write (device memory, or mapped pinned host memory); NULL = the library-wide word of
+                                    this device that rb200k_device_status() reads */
 } rb200_resample_params;
 
 /* Resize / ResizeCropMirror / ResizeMirrorNormalize / fused Resize+CropMirrorNormalize.
@@ -142,6 +145,15 @@ typedef struct rb200_pointwise_sample {
     uint32_t src2_stride;                      /* relative to the arena pointer (wrap-around arithmetic), its pitch */
 } rb200_pointwise_sample;
 
+/* Arithmetic of the colour operators on uint8 output.
+ *   RB200_ARITH_EXACT  every float operation rounds once, in the order of the CPU restatement the tests compare with:
+ *                      results are bit-identical to it.
+ *   RB200_ARITH_FAST   the same functions evaluated with fused multiply-adds, one hardware reciprocal and a periodic
+ *                      form of the HSV -> RGB step (no table, no wrap-around selects): every output byte is within
+ *                      one level of the EXACT result; about twice the ColorTwist / Hue / Saturation throughput.
+ *                      Operators other than ColorTwist / Hue / Saturation, and outputs other than uint8 without
+ *                      normalisation, run the EXACT code under either setting. */
+enum { RB200_ARITH_EXACT = 0, RB200_ARITH_FAST = 1 };
 typedef struct rb200_pointwise_params {
     void* out;
     int32_t out_w, out_h;
@@ -151,6 +163,8 @@ typedef struct rb200_pointwise_params {
     int32_t reverse_channels;    /* 1 = output channel c shows source channel 2-c            */
     float mul[3];
     float add[3];
+    int32_t arith;               /* RB200_ARITH_EXACT (0) or RB200_ARITH_FAST (1), see below */
+    int32_t* status;             /* as rb200_resample_params.status */
 } rb200_pointwise_params;
 
 /* Crop / Flip / CropMirrorNormalize / Brightness / Contrast / Hue / Saturation / ColorTwist
@@ -245,12 +259,30 @@ RB200_API int rb200k_box_iou_match(const float* boxes, const int32_t* box_offset
                          const rb200_box_matcher_params* params, int32_t* out_matches, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Bounded waits
+ * ------------------------------------------------------------------------------------- */
+
+/* The row-streaming resample kernel and the pointwise vector kernel wait on mbarriers for their bulk copies. Every
+ * such wait gives up after a limit (about a second of SM clock): the kernel then writes 1 to its status word, waits
+ * (bounded again) for the copies it may still have in flight, and returns with its output incomplete; the context
+ * stays usable. The two entries below run the same launches with a caller-chosen limit (SM clock cycles) and, for
+ * self-tests, with the producer told not to issue the copies of one row (skip_row, counted inside each CTA's strip or
+ * tile; -1 = issue everything), so that the give-up path can be exercised without any faulting or endless wait: the
+ * skipped copy never starts, so nothing is left in flight. */
+RB200_API int rb200k_resample_probe(const uint8_t* arena, const rb200_resample_sample* samples,
+                          const rb200_resample_sample* h_samples, int n, const rb200_resample_params* params,
+                          void* stream, uint64_t wait_cycles, int skip_row);
+RB200_API int rb200k_pointwise_probe(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                           const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* params,
+                           void* stream, uint64_t wait_cycles, int skip_row);
+
+/* ---------------------------------------------------------------------------------------
  * Misc
  * ------------------------------------------------------------------------------------- */
 
-/* Device-side status: 0 = fine; 1 = a kernel gave up on one of its bounded waits (a copy that never
- * completed) since the last call, its output is then incomplete; -1 = the query itself failed.
- * Synchronises with the device. */
+/* The library-wide status word of the current device: 0 = fine; 1 = a kernel launched without a status pointer of
+ * its own gave up on one of its bounded waits (a copy that never completed) since the last call, its output is then
+ * incomplete; -1 = the query itself failed. Synchronises with the device. */
 RB200_API int rb200k_device_status(void);
 
 /* Text of the last error on the calling thread ("" if none). */

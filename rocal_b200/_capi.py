@@ -61,6 +61,9 @@ get_roi_image_sizes = _proto("rb200_get_roi_image_sizes", c_int, _P, POINTER(c_i
 get_last_batch_padded_size = _proto("rb200_get_last_batch_padded_size", c_size_t, _P)
 get_h2d_bytes = _proto("rb200_get_h2d_bytes", ctypes.c_ulonglong, _P)
 set_upload_mode = _proto("rb200_set_upload_mode", ctypes.c_int, _P, ctypes.c_int)
+set_arithmetic = _proto("rb200_set_arithmetic", ctypes.c_int, _P, ctypes.c_int)
+consumer_fence = _proto("rb200_consumer_fence", ctypes.c_int, _P, ctypes.c_void_p)
+set_wait_probe = _proto("rb200_set_wait_probe", ctypes.c_int, _P, ctypes.c_ulonglong, ctypes.c_int)
 get_remaining_images = _proto("rb200_get_remaining_images", c_size_t, _P)
 set_seed = _proto("rb200_set_seed", None, c_uint)
 get_seed = _proto("rb200_get_seed", c_uint)

@@ -20,7 +20,8 @@ class ResampleParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
-                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32)]
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32),
+                ("status", ctypes.c_void_p)]
 
 
 class PointwiseParams(ctypes.Structure):
@@ -28,7 +29,8 @@ class PointwiseParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("color_op", ctypes.c_int32), ("normalize", ctypes.c_int32),
                 ("fill_padding", ctypes.c_int32), ("reverse_channels", ctypes.c_int32),
-                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3)]
+                ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("arith", ctypes.c_int32),
+                ("status", ctypes.c_void_p)]
 
 
 class WarpParams(ctypes.Structure):
@@ -51,6 +53,11 @@ lib.rb200k_resample.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POIN
 lib.rb200k_resample.restype = c_int
 lib.rb200k_pointwise.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(PointwiseParams), c_void_p]
 lib.rb200k_pointwise.restype = c_int
+lib.rb200k_resample_probe.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(ResampleParams), c_void_p, c_uint64, c_int]
+lib.rb200k_resample_probe.restype = c_int
+lib.rb200k_pointwise_probe.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(PointwiseParams), c_void_p, c_uint64, c_int]
+lib.rb200k_pointwise_probe.restype = c_int
+lib.rb200k_device_status.restype = c_int
 lib.rb200k_warp_affine.argtypes = [c_void_p, c_void_p, c_int, ctypes.POINTER(WarpParams), c_void_p]
 lib.rb200k_warp_affine.restype = c_int
 lib.rb200k_box_encode.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(BoxEncoderParams),

@@ -295,6 +295,8 @@ Pipeline::~Pipeline() {
     }
     for (auto& s : _slots) {
         if (s.done) cudaEventDestroy(s.done);
+        if (s.consumer_done) cudaEventDestroy(s.consumer_done);
+        if (s.h_status) cudaFreeHost(s.h_status);
         if (s.d_tables) cudaFree(s.d_tables);
         if (s.h_tables) cudaFreeHost(s.h_tables);
         if (s.d_enc_boxes) cudaFree(s.d_enc_boxes);
@@ -716,6 +718,10 @@ void Pipeline::verify() {
     }
     for (auto& s : _slots) {
         RB200_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+        RB200_CUDA(cudaEventCreateWithFlags(&s.consumer_done, cudaEventDisableTiming));
+        RB200_CUDA(cudaHostAlloc((void**)&s.h_status, 64, cudaHostAllocMapped));
+        *s.h_status = 0;
+        RB200_CUDA(cudaHostGetDevicePointer((void**)&s.d_status, s.h_status, 0));
         RB200_CUDA(cudaMalloc(&s.d_tables, table_bytes));
         RB200_CUDA(cudaHostAlloc(&s.h_tables, table_bytes, cudaHostAllocDefault));
         s.rois.assign(_tensors.size(), std::vector<unsigned>());
@@ -1264,6 +1270,12 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     const size_t n = _batch;
     TensorImpl* src = _tensors[_source].get();
     unsigned long long t0 = now_us();
+    if (s.consumer_pending) {
+        // a consumer may still be reading this slot's buffers on its own stream (consumer_fence)
+        RB200_CUDA(cudaStreamWaitEvent(_stream, s.consumer_done, 0));
+        RB200_CUDA(cudaStreamWaitEvent(_meta_stream, s.consumer_done, 0));
+        s.consumer_pending = false;
+    }
 
     // ---- 1. input: device views of the n source images (the upload itself follows the tables) ----
     _src_views.resize(n);
@@ -1398,6 +1410,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     };
 
     uint8_t* h_tab = (uint8_t*)s.h_tables;
+    const unsigned long long probe_cycles = _probe_wait_cycles.load();
+    const int probe_skip = _probe_skip_row.load();
     for (size_t k = 0; k < _steps.size(); k++) {
         const Step& st = _steps[k];
         TensorImpl* in = _tensors[st.in_tensor].get();
@@ -1570,7 +1584,10 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             // plain resize into its max-shape tensor defines only the ROI, as the reference does.
             p.fill_padding = (st.post >= 0 || _nodes[st.resize].kind != NodeKind::RESIZE) ? 1 : 0;
             p.interpolation = _nodes[st.resize].interpolation;
-            rc = rb200k_resample(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk, (int)n, &p, _stream);
+            p.status = s.d_status;
+            rc = probe_cycles ? rb200k_resample_probe(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk,
+                                                      (int)n, &p, _stream, probe_cycles, probe_skip)
+                              : rb200k_resample(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk, (int)n, &p, _stream);
         } else if (st.kind == Step::POINTWISE) {
             rb200_pointwise_params p{};
             p.out = out_ptr;
@@ -1592,7 +1609,11 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                 for (int c = 0; c < 3; c++) { p.mul[c] = _nodes[st.window].mul[c]; p.add[c] = _nodes[st.window].add[c]; }
             }
             p.fill_padding = (st.window >= 0) ? 1 : 0;
-            rc = rb200k_pointwise(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p, _stream);
+            p.arith = _arith;
+            p.status = s.d_status;
+            rc = probe_cycles ? rb200k_pointwise_probe(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk,
+                                                       (int)n, &p, _stream, probe_cycles, probe_skip)
+                              : rb200k_pointwise(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p, _stream);
         } else {
             rb200_warp_params p{};
             p.out = out_ptr;
@@ -1673,6 +1694,27 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     _t_process += now_us() - t0;
 }
 
+// The buffers of the held batch go back to the ring at the next run(); work that a consumer queued on its own stream
+// (a training step reading the zero-copy outputs) may still be pending then. The event recorded here makes the
+// worker's streams wait for that work before the slot is written again - no host synchronisation.
+void Pipeline::consumer_fence(void* consumer_stream) {
+    if (_held < 0) return;
+    Slot& s = _slots[_held];
+    RB200_CUDA(cudaSetDevice(_gpu_id));
+    RB200_CUDA(cudaEventRecord(s.consumer_done, (cudaStream_t)consumer_stream));
+    s.consumer_pending = true;
+}
+
+void Pipeline::set_arithmetic(int mode) {
+    if (mode != RB200_ARITH_EXACT && mode != RB200_ARITH_FAST) RB200_THROW("arithmetic mode must be 0 (exact) or 1 (fast)");
+    _arith = mode;
+}
+
+void Pipeline::set_wait_probe(unsigned long long wait_cycles, int skip_row) {
+    _probe_wait_cycles.store(wait_cycles);
+    _probe_skip_row.store(wait_cycles ? skip_row : -1);
+}
+
 // ------------------------------------------------------------------------------------------
 // run(): hand the next finished batch to the user (MasterGraph::run, master_graph.cpp:193-223)
 // ------------------------------------------------------------------------------------------
@@ -1713,6 +1755,11 @@ void Pipeline::run() {
     unsigned long long t0 = now_us();
     RB200_CUDA(cudaEventSynchronize(s.done));
     _t_process += now_us() - t0;
+    if (*static_cast<volatile int*>(s.h_status) != 0) {
+        // a kernel of this batch gave up on a bounded wait for its source rows and left its output incomplete
+        *s.h_status = 0;
+        RB200_THROW("rocalRun: a kernel of this batch gave up waiting for its staged source rows; the batch's outputs are incomplete");
+    }
     for (auto& t : _tensors) {
         if (t->is_output && !t->is_source) t->current = t->ring[idx];
         t->user_roi = s.rois[t->id];

@@ -195,6 +195,10 @@ struct Step {
 struct Slot {
     enum State { FREE, READY, HELD } state = FREE;
     cudaEvent_t done = nullptr;
+    cudaEvent_t consumer_done = nullptr;   // recorded on a consumer's stream by consumer_fence()
+    bool consumer_pending = false;         // the worker must order its streams behind consumer_done before reusing the slot
+    int* h_status = nullptr;         // mapped pinned word the kernels of this slot write 1 to when a bounded wait gives up
+    int* d_status = nullptr;         // the same word as the device sees it
     void* d_tables = nullptr;        // device copy of all step tables of this slot
     void* h_tables = nullptr;        // pinned host copy
     std::vector<std::vector<unsigned>> rois;   // per output tensor: n x 4
@@ -230,6 +234,10 @@ class Pipeline {
     void set_random_crop_decoder(const RandomCropRanges& r);
     void decoder_crop_windows(unsigned* xywh, unsigned* batch_seed);
     void reset_loaders();
+    // Orders the reuse of the held batch's buffers behind the work already queued on `consumer_stream`
+    void consumer_fence(void* consumer_stream);
+    void set_arithmetic(int mode);
+    void set_wait_probe(unsigned long long wait_cycles, int skip_row);
     void image_labels(int* buf);
     TensorListImpl* image_label_list();   // rocalGetImageLabels: one int32 host tensor per sample, buffers consecutive
     void image_ids(int* buf);
@@ -404,6 +412,9 @@ class Pipeline {
     std::atomic<unsigned long long> _t_load{0}, _t_decode{0}, _t_process{0}, _t_transfer{0};
     std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
     int _upload_mode = UPLOAD_ZERO_COPY;
+    int _arith = RB200_ARITH_EXACT;                       // arithmetic of the colour operators (rb200_set_arithmetic)
+    std::atomic<unsigned long long> _probe_wait_cycles{0};  // self-test: non-zero = launch through the probe entries
+    std::atomic<int> _probe_skip_row{-1};
 };
 
 #define RB200_THROW(msg) throw std::runtime_error(std::string(msg))

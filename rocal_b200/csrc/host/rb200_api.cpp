@@ -226,6 +226,32 @@ int rb200_set_upload_mode(rb200_context ctx, int mode) {
     return 0;
 }
 
+int rb200_set_arithmetic(rb200_context ctx, int mode) {
+    if (!ctx) return -1;
+    try {
+        P(ctx)->set_arithmetic(mode);
+        return 0;
+    } catch (const std::exception& e) {
+        P(ctx)->capture_error(e.what());
+        return -1;
+    }
+}
+int rb200_consumer_fence(rb200_context ctx, void* cuda_stream) {
+    if (!ctx) return -1;
+    try {
+        P(ctx)->consumer_fence(cuda_stream);
+        return 0;
+    } catch (const std::exception& e) {
+        P(ctx)->capture_error(e.what());
+        return -1;
+    }
+}
+int rb200_set_wait_probe(rb200_context ctx, unsigned long long wait_cycles, int skip_row) {
+    if (!ctx) return -1;
+    P(ctx)->set_wait_probe(wait_cycles, skip_row);
+    return 0;
+}
+
 // ---- parameters ----
 void rb200_set_seed(unsigned seed) { ParameterFactory::instance().set_seed(seed); }
 unsigned rb200_get_seed(void) { return ParameterFactory::instance().get_seed(); }

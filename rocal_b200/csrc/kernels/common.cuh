@@ -13,6 +13,11 @@ namespace rb200 {
 void set_error(const char* fmt, ...);
 void count_launch();
 int check_cuda(cudaError_t e, const char* what);
+// Device address of the library-wide status word of the current device (runtime.cu); nullptr if the query failed.
+int* default_status_word();
+// Reads and clears that word: 0 / 1, or -1 when the copy failed.
+int read_default_status_word();
+constexpr unsigned long long kDefaultWaitCycles = 2000000000ull;   // about a second of SM clock
 
 #define RB200_CHECK_LAUNCH(what)                                       \
     do {                                                               \

@@ -33,9 +33,10 @@ struct PointwiseLaunch {
     float mul[3], add[3];
     uint32_t magic;      // 0x4B000000, read by PRMT from the constant bank
     int pitch;           // vector kernel: bytes per staged source row (multiple of 16)
+    int* status;         // vector kernel: written with 1 when the bounded wait on the staged rows gives up
+    long long wait_cycles;   // vector kernel: limit of that wait, SM clock cycles
+    int skip_row;        // vector kernel, self-test: the copy of this tile row is never issued (-1: all are)
 };
-
-__device__ int g_pointwise_timeout = 0;   // set when a bounded wait on a bulk copy gave up
 
 __device__ __forceinline__ uint32_t pw_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool pw_mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -44,12 +45,12 @@ __device__ __forceinline__ bool pw_mbar_try_wait(uint32_t bar, uint32_t parity) 
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool pw_mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool pw_mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (pw_mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (int i = 0; i < (1 << 24); i++) {
         if (pw_mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > 2000000000LL) break;
+        if (clock64() - t0 > limit) break;
     }
     return false;
 }
@@ -386,18 +387,20 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
                 const uint8_t* g = img + (size_t)sy * s.src_stride + (size_t)x_src0 * 3;
                 const uint32_t m = (uint32_t)((uintptr_t)g & 15);
                 const uint32_t bytes = ((m + (uint32_t)w * 3 + 15) >> 4) << 4;
+                if (r == L.skip_row) continue;     // self-test: this row's bytes stay expected and never arrive
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(pw_smem_u32(stage + (size_t)r * L.pitch)), "l"(g - m), "r"(bytes), "r"(bar) : "memory");
             }
         }
         // Warp 0 waits for the copies (bounded); the other warps sleep at the barrier instead of polling.
         if (threadIdx.x < 32) {
-            const bool ok = pw_mbar_wait_bounded(bar, 0);
+            const bool ok = pw_mbar_wait_bounded(bar, 0, L.wait_cycles);
             if (threadIdx.x == 0) {
                 stage_flag = ok ? 1 : 0;
                 if (!ok) {
-                    atomicExch(&g_pointwise_timeout, 1);
-                    pw_mbar_wait_bounded(bar, 0);   // second bounded chance for copies still in flight
+                    *reinterpret_cast<volatile int*>(L.status) = 1;
+                    __threadfence_system();
+                    pw_mbar_wait_bounded(bar, 0, L.wait_cycles);   // second bounded chance for copies still in flight
                 }
             }
         }
@@ -676,9 +679,9 @@ static int launch_color(int color_op, bool vec, dim3 grid, int threads, size_t s
 
 using namespace rb200;
 
-extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_sample* samples,
-                                const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* p,
-                                void* stream_v) {
+static int pointwise_launch(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                            const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* p,
+                            void* stream_v, unsigned long long wait_cycles, int skip_row) {
     if (n == 0) return RB200_OK;
     if (!arena || !samples || !p || !p->out || n < 0 || p->out_w <= 0 || p->out_h <= 0) {
         set_error("rb200k_pointwise: null pointer or non-positive size");
@@ -703,6 +706,17 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
     L.reverse_channels = p->reverse_channels;
     L.magic = 0x4B000000u;
     for (int c = 0; c < 3; c++) { L.mul[c] = p->mul[c]; L.add[c] = p->add[c]; }
+    if (p->arith != RB200_ARITH_EXACT && p->arith != RB200_ARITH_FAST) {
+        set_error("rb200k_pointwise: bad arith %d", p->arith);
+        return RB200_E_INVALID;
+    }
+    L.status = p->status ? p->status : default_status_word();
+    if (!L.status) {
+        set_error("rb200k_pointwise: the device's status word cannot be addressed");
+        return RB200_E_CUDA;
+    }
+    L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
+    L.skip_row = skip_row;
     int ext_w = p->out_w, ext_h = p->out_h;
     if (h_samples && !p->fill_padding) {
         ext_w = 1; ext_h = 1;
@@ -762,12 +776,14 @@ extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_samp
 #undef RB200_DISPATCH
 }
 
-namespace rb200 {
-// Reads and clears the time-out flag of the pointwise kernels (used by rb200k_device_status).
-int pointwise_timeout_status() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_pointwise_timeout, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_pointwise_timeout, &zero, sizeof(int));
-    return v;
+extern "C" int rb200k_pointwise(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                                const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* p,
+                                void* stream_v) {
+    return pointwise_launch(arena, samples, h_samples, n, p, stream_v, kDefaultWaitCycles, -1);
 }
-}  // namespace rb200
+
+extern "C" int rb200k_pointwise_probe(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                                      const rb200_pointwise_sample* h_samples, int n, const rb200_pointwise_params* p,
+                                      void* stream_v, uint64_t wait_cycles, int skip_row) {
+    return pointwise_launch(arena, samples, h_samples, n, p, stream_v, wait_cycles, skip_row);
+}

@@ -46,6 +46,9 @@ struct ResampleLaunch {
     float mul[3], add[3];
     uint32_t magic;     // 0x4B000000 (bits of 2^23), passed as a parameter so that PRMT reads it
                         // from the constant bank instead of a re-materialised register
+    int* status;        // stream kernel: written with 1 when a bounded wait gives up
+    long long wait_cycles;   // stream kernel: limit of every mbarrier wait, SM clock cycles
+    int skip_row;       // stream kernel, self-test: the producer issues no copy from this strip row on (-1: all)
 };
 
 struct RowInfo {
@@ -258,9 +261,12 @@ __device__ __forceinline__ void column_setup(int xi0, bool second, int crop_x, i
 // NS stages, each holding the two tap rows of one output row, filled by thread 0 with two 1-D bulk
 // copies (cp.async.bulk, the TMA unit) that complete on the stage's mbarrier; consumers release a
 // stage by arriving on its "empty" mbarrier. Every wait is bounded: on a time-out the kernel sets
-// g_resample_timeout, drains the copies it has in flight (bounded again) and returns.
+// the launch's status word, drains the copies it has in flight (bounded again) and returns.
 // ------------------------------------------------------------------------------------------
-__device__ int g_resample_timeout = 0;
+__device__ __forceinline__ void raise_status(int* status) {
+    *reinterpret_cast<volatile int*>(status) = 1;
+    __threadfence_system();
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -278,13 +284,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after about a second of SM clock.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after `limit` SM clock cycles (and after 2^24 polls at the latest).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (int i = 0; i < (1 << 24); i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > 2000000000LL) break;
+        if (clock64() - t0 > limit) break;
     }
     return false;
 }
@@ -398,8 +404,9 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
             if (tid == producer_tid) {
                 for (int j = 0; j < rows_valid; j++) {
                     const int s = j & ns_mask;
-                    if (j >= NS && !mbar_wait_bounded(bar_base + 8 * (NS + s), ((j >> ns_lg) - 1) & 1)) {
-                        atomicExch(&g_resample_timeout, 1);
+                    if (j == L.skip_row) break;        // self-test: this row's copies (and all later ones) never start
+                    if (j >= NS && !mbar_wait_bounded(bar_base + 8 * (NS + s), ((j >> ns_lg) - 1) & 1, L.wait_cycles)) {
+                        raise_status(L.status);
                         break;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -426,7 +433,7 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
             bool ok = true;
             for (; j < rows_valid; j++, po += row_step) {
                 const int s = j & ns_mask;
-                if (!mbar_wait_bounded(bar_base + 8 * s, (j >> ns_lg) & 1)) {
+                if (!mbar_wait_bounded(bar_base + 8 * s, (j >> ns_lg) & 1, L.wait_cycles)) {
                     ok = false;
                     break;
                 }
@@ -443,11 +450,12 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                 mbar_arrive(bar_base + 8 * (NS + s));
             }
             if (!ok) {
-                atomicExch(&g_resample_timeout, 1);
+                raise_status(L.status);
                 // Before the CTA's shared memory is given away, wait (bounded) for the copies that may
                 // still be in flight: the producer is never more than NS rows ahead.
                 if (tid == 0)
-                    for (int jj = j; jj < min(j + NS, rows_valid); jj++) mbar_wait_bounded(bar_base + 8 * (jj & ns_mask), (jj >> ns_lg) & 1);
+                    for (int jj = j; jj < min(j + NS, rows_valid); jj++)
+                        mbar_wait_bounded(bar_base + 8 * (jj & ns_mask), (jj >> ns_lg) & 1, L.wait_cycles);
             }
         }
     }
@@ -1039,9 +1047,9 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
 
 using namespace rb200;
 
-extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample* samples,
-                               const rb200_resample_sample* h_samples, int n, const rb200_resample_params* p,
-                               void* stream_v) {
+static int resample_launch(const uint8_t* arena, const rb200_resample_sample* samples,
+                           const rb200_resample_sample* h_samples, int n, const rb200_resample_params* p,
+                           void* stream_v, unsigned long long wait_cycles, int skip_row) {
     if (n == 0) return RB200_OK;
     if (!arena || !samples || !p || !p->out || n < 0 || p->out_w <= 0 || p->out_h <= 0) {
         set_error("rb200k_resample: null pointer or non-positive size");
@@ -1075,6 +1083,13 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
     L.pair_ok = 0;
     L.magic = 0x4B000000u;
     for (int c = 0; c < 3; c++) { L.mul[c] = p->mul[c]; L.add[c] = p->add[c]; }
+    L.status = p->status ? p->status : default_status_word();
+    if (!L.status) {
+        set_error("rb200k_resample: the device's status word cannot be addressed");
+        return RB200_E_CUDA;
+    }
+    L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
+    L.skip_row = skip_row;
 
     // Extent the grid has to cover.
     int ext_w = p->out_w, ext_h = p->out_h;
@@ -1168,14 +1183,14 @@ extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample
 #undef RB200_DISPATCH
 }
 
-// Non-zero when a kernel of this library gave up on a bounded wait since the last call (then cleared).
-namespace rb200 { int pointwise_timeout_status(); int warp_timeout_status(); }
-extern "C" int rb200k_device_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, rb200::g_resample_timeout, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(rb200::g_resample_timeout, &zero, sizeof(int));
-    int pw = rb200::pointwise_timeout_status();
-    int wa = rb200::warp_timeout_status();
-    if (pw < 0 || wa < 0) return -1;
-    return (v || pw || wa) ? 1 : 0;
+extern "C" int rb200k_resample(const uint8_t* arena, const rb200_resample_sample* samples,
+                               const rb200_resample_sample* h_samples, int n, const rb200_resample_params* p,
+                               void* stream_v) {
+    return resample_launch(arena, samples, h_samples, n, p, stream_v, kDefaultWaitCycles, -1);
+}
+
+extern "C" int rb200k_resample_probe(const uint8_t* arena, const rb200_resample_sample* samples,
+                                     const rb200_resample_sample* h_samples, int n, const rb200_resample_params* p,
+                                     void* stream_v, uint64_t wait_cycles, int skip_row) {
+    return resample_launch(arena, samples, h_samples, n, p, stream_v, wait_cycles, skip_row);
 }

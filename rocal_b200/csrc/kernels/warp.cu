@@ -292,9 +292,6 @@ __global__ void __launch_bounds__(256, 5) warp_affine_kernel(const uint8_t* __re
     }
 }
 
-// No wait in this kernel can time out; kept so that the device-status query treats all kernels alike.
-int warp_timeout_status() { return 0; }
-
 }  // namespace rb200
 
 using namespace rb200;

@@ -36,11 +36,13 @@ def _alloc_out(n, out_w, out_h, dtype, layout, device, out):
 
 
 def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
-             fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0):
+             fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0,
+             status=None, probe=None):
     """rb200k_resample. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
     already on the device (uploaded here when None). staged=False withholds the host table from
     the launch so that the kernel gathers straight from global memory; path=1 (RB200_RESAMPLE_PATH_TILE)
-    forces the shared-memory tile kernel."""
+    forces the shared-memory tile kernel. status: an int32 CUDA tensor that receives 1 when a bounded wait gives up
+    (None: the library-wide word); probe=(wait_cycles, skip_row) launches through rb200k_resample_probe."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
     if d_samples is None:
@@ -55,16 +57,21 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
     for c in range(3):
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0
+    p.status = status.data_ptr() if status is not None else None
     h_ptr = samples.ctypes.data_as(ctypes.c_void_p) if staged else None
-    check(lib.rb200k_resample(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
-                              _stream_ptr(stream)), "rb200k_resample")
+    if probe is not None:
+        check(lib.rb200k_resample_probe(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
+                                        _stream_ptr(stream), int(probe[0]), int(probe[1])), "rb200k_resample_probe")
+    else:
+        check(lib.rb200k_resample(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
+                                  _stream_ptr(stream)), "rb200k_resample")
     return out
 
 
 def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.UINT8, out_layout=T.NHWC,
               mul=None, add=None, reverse_channels=False, fill_padding=True, out=None, d_samples=None,
-              stream=None):
-    """rb200k_pointwise."""
+              stream=None, arith=0, status=None, probe=None):
+    """rb200k_pointwise. arith: 0 exact, 1 fast colour arithmetic; status / probe as for resample."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
     if d_samples is None:
@@ -79,8 +86,15 @@ def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.U
     for c in range(3):
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0
-    check(lib.rb200k_pointwise(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
-                               ctypes.byref(p), _stream_ptr(stream)), "rb200k_pointwise")
+    p.arith = int(arith)
+    p.status = status.data_ptr() if status is not None else None
+    if probe is not None:
+        check(lib.rb200k_pointwise_probe(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
+                                         ctypes.byref(p), _stream_ptr(stream), int(probe[0]), int(probe[1])),
+              "rb200k_pointwise_probe")
+    else:
+        check(lib.rb200k_pointwise(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
+                                   ctypes.byref(p), _stream_ptr(stream)), "rb200k_pointwise")
     return out
 
 

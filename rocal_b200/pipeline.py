@@ -13,6 +13,7 @@
     pipe.run()
     tensors = pipe.get_output_tensors()                     # list of RocalTensor (DLPack capable)
 """
+import collections
 import ctypes
 
 import numpy as np
@@ -102,7 +103,13 @@ class RocalTensor:
         return (2, C.device_id(self._pipe._handle))   # kDLCUDA
 
     def __dlpack__(self, stream=None, **_):
-        """Zero-copy export. The batch is complete when run() returns, so no stream hand-off is needed."""
+        """Zero-copy export. The batch is complete when run() returns, so the consumer never waits for the pipeline;
+        the other direction is what `stream` is for: the pipeline remembers the consumer's stream (DLPack's
+        convention: None or 1 = the legacy default stream, 2 = the per-thread default stream, -1 = no ordering
+        wanted, anything else a cudaStream_t) and, at the next run(), orders the reuse of this batch's buffers behind
+        whatever the consumer has queued there by then (rb200_consumer_fence)."""
+        if stream != -1:
+            self._pipe._consumer_streams.add(0 if stream in (None, 1) else int(stream))
         m = C.tensor_dlpack(self._h)
         if not m:
             raise RocalError("no batch is available yet (call run() first)")
@@ -131,7 +138,8 @@ class Pipeline(object):
         self._offset = [-(m / s) for m, s in zip(mean, std)] if mean and std else [0.0, 0.0, 0.0]
         self._reverse_channels = reverse_channels
         self._outputs = []
-        self._keepalive = []
+        self._keepalive = collections.deque()    # one entry per fed batch that rocal_run has not returned yet
+        self._consumer_streams = set()           # streams the held batch was exported to through DLPack
         self._box_encoder = False
         self._num_anchors = 0
         self._external_source_mode = None
@@ -232,6 +240,7 @@ class Pipeline(object):
         """JPEG files by name (the FNAME mode of rocalExternalSourceFeedInput)."""
         n = len(paths)
         arr = (ctypes.c_char_p * n)(*[str(p).encode() for p in paths])
+        self._keepalive.append(None)       # keeps the one-entry-per-fed-batch order of the queue
         self._check(C.feed_files(self._handle, arr, n))
 
     def feed_boxes(self, boxes, labels, counts):
@@ -255,10 +264,21 @@ class Pipeline(object):
 
     # ---- run / outputs ----
     def rocal_run(self):
+        for stream in self._consumer_streams:      # consumers of the batch that is about to go back to the ring
+            C.consumer_fence(self._handle, ctypes.c_void_p(stream))
+        self._consumer_streams.clear()
         self._check(C.run(self._handle))
-        while len(self._keepalive) > 4:
-            self._keepalive.pop(0)
+        # the batch just returned has been consumed: its host buffers (oldest entry) may go. Every other entry
+        # belongs to a batch that is still queued, whatever their number.
+        if self._keepalive:
+            self._keepalive.popleft()
         return types.OK
+
+    def set_arithmetic(self, mode):
+        """[extension] 0 = exact (bit-identical to the CPU restatement), 1 = fast colour arithmetic (every uint8
+        output within one level of exact)."""
+        if C.set_arithmetic(self._handle, int(mode)) != 0:
+            raise ValueError("arithmetic mode must be 0 or 1")
 
     def run(self):
         """pipeline.py:262-275 of the reference: runs the next batch and returns its output tensors; StopIteration when

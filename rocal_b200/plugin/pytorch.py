@@ -24,6 +24,17 @@ class ROCALGenericIterator(object):
     def __iter__(self):
         return self
 
+    def _outputs(self):
+        """Zero-copy views of the batch's outputs, valid until the next batch: torch.from_dlpack hands the pipeline
+        the current torch stream, and the pipeline orders the reuse of these buffers behind the work queued there
+        (RocalTensor.__dlpack__). Work on other streams is the caller's to order. With copy=True the views are cloned
+        and the clone has finished before the tensors are returned, as the reference's synchronous copy_data."""
+        outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
+        if self.copy:
+            outs = [o.clone() for o in outs]
+            torch.cuda.current_stream(outs[0].device).synchronize()
+        return outs
+
     def __next__(self):
         if self.feeder is not None and not self.feeder(self.loader):
             if self.loader.is_empty():
@@ -31,9 +42,7 @@ class ROCALGenericIterator(object):
         elif self.feeder is None and self.loader.is_empty():
             raise StopIteration
         self.loader.rocal_run()
-        outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
-        if self.copy:
-            outs = [o.clone() for o in outs]
+        outs = self._outputs()
         return outs
 
     next = __next__
@@ -51,9 +60,7 @@ class ROCALClassificationIterator(ROCALGenericIterator):
                 self.reset()
             raise StopIteration
         self.loader.rocal_run()
-        outs = [torch.from_dlpack(t) for t in self.loader.get_output_tensors()]
-        if self.copy:
-            outs = [o.clone() for o in outs]
+        outs = self._outputs()
         if getattr(self.loader, "_one_hot_encoding", False):
             labels = self.loader.get_one_hot_encoded_labels(self.loader._num_classes, device=outs[0].device)
         else:
