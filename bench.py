@@ -202,7 +202,7 @@ def _time_cpu(fn, images_per_call, seconds_target=4.0):
     return images_per_call * reps / elapsed, reps
 
 
-def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None):
+def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=False):
     """Device-resident launches (CUDA events), the pipeline API from pinned host memory and, if asked, the CPU port
     for one of the configurations 0, 2, 3, 4 on cuda:0. Returns the bench line as a dict."""
     import torch
@@ -257,6 +257,9 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None):
     elif cfg == 2:
         n, rot, name = 256, 4, "configs[2]: ColorTwist(alpha,beta,hue,sat)+Flip u8 HWC 224x224, batch 256"
         kernel = "pointwise_vec_kernel<uint8,NHWC,twist>"
+        if fast:
+            name += " [RB200_ARITH_FAST: every byte within one level of the exact arithmetic]"
+            kernel = "pointwise_vec_kernel<uint8,NHWC,twist_fast>"
         pipe = Pipeline(batch_size=n, device_id=0, seed=1234, prefetch_queue_depth=2)
         with pipe:
             img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=224, max_height=224)
@@ -265,6 +268,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None):
             outn = fn.flip(ct, horizontal=fn.random.coin_flip(), vertical=0)
             pipe.set_outputs(outn)
         pipe.build()
+        pipe.set_arithmetic(1 if fast else 0)
         algo = float(n * 2 * 3 * 224 * 224)
         for k in range(rot):
             rng = S.rng_for(2, 100 + k)
@@ -273,7 +277,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None):
             a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
             o = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
             resident.append(lambda a=a, t=t, dt=dt, o=o: K.pointwise(a, t, 224, 224, T.COLOR_TWIST, out=o, d_samples=dt, fill_padding=False,
-                                                                       stream=stream))
+                                                                       stream=stream, arith=1 if fast else 0))
             ap_ = torch.from_numpy(arena).pin_memory()
             feeders.append(lambda ap_=ap_, hs=hs, ws=ws, offs=offs: pipe.feed_ragged(ap_, hs, ws, offs))
             if k == 0:
@@ -421,8 +425,8 @@ def other_configs(sampler):
     """Short runs of configs[0], [2], [3], [4] on cuda:0 for the default line: what each costs and where it stands
     against the roofline."""
     out = []
-    for cfg in (0, 2, 3, 4):
-        r = measure_config(cfg, steps=40, warmup=5, e2e_steps=12, with_cpu=False, sampler=sampler)
+    for cfg, fast in ((0, False), (2, False), (2, True), (3, False), (4, False)):
+        r = measure_config(cfg, steps=40, warmup=5, e2e_steps=12, with_cpu=False, sampler=sampler, fast=fast)
         out.append({"workload": r["config"]["workload"], "ms_per_step": r["ms_per_step"], "value": r["value"], "unit": r["unit"],
                     "roofline": {"kernel": r["roofline"]["kernel"], "frac": r["roofline"]["frac"], "achieved": r["roofline"]["achieved"],
                                  "algorithmic_bytes_per_launch": r["roofline"]["algorithmic_bytes_per_launch"]},
@@ -494,8 +498,9 @@ def run_ops(args):
                 t = S.color_twist_tables(rng, hs, ws, offs)
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
-                fns.append(lambda a=a, t=t, dt=dt, out=out: K.pointwise(a, t, 224, 224, code, out=out, d_samples=dt, fill_padding=False))
-            report("cfg2 %s(+flip) u8 HWC 224x224 (batch %d)" % (op, n), n, _time_launches(fns, args.steps), n * 2 * 3 * 224 * 224)
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.pointwise(a, t, 224, 224, code, out=out, d_samples=dt, fill_padding=False,
+                                                                        arith=1 if args.fast else 0))
+            report("cfg2 %s(+flip) u8 HWC 224x224 (batch %d)%s" % (op, n, " fast arithmetic" if args.fast else ""), n, _time_launches(fns, args.steps), n * 2 * 3 * 224 * 224)
         elif op == "warp":
             n, rot = 128, 2
             fns = []
@@ -667,6 +672,7 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4],
                     help="BASELINE configuration; 1 (default) is the headline workload, the others run on one GPU only")
     ap.add_argument("--op", default=None, help="operator-level cases, comma separated (see run_ops)")
+    ap.add_argument("--fast", action="store_true", help="colour operators with RB200_ARITH_FAST (--config 2 and the colour --op cases)")
     args = ap.parse_args()
     if args.op:
         run_ops(args)
@@ -674,7 +680,7 @@ def main():
     if args.config != 1:
         if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.impl != "ours":
             raise SystemExit("--config %d runs our arm on one GPU only" % args.config)
-        print(json.dumps(measure_config(args.config, args.steps, args.warmup, max(args.steps, 20), True)), flush=True)
+        print(json.dumps(measure_config(args.config, args.steps, args.warmup, max(args.steps, 20), True, fast=args.fast)), flush=True)
         return
     global BATCH
     if args.batch:

@@ -26,6 +26,32 @@ constexpr unsigned long long kDefaultWaitCycles = 2000000000ull;   // about a se
         if (_rc) return _rc;                                           \
     } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Kernels of this library that follow one another in a stream overlap their ramp-up with the predecessor's
+// tail: a launch made with launch_overlapped() may be scheduled as soon as every CTA of the preceding kernel has
+// started (each calls pdl_launch_dependents() on entry), and its CTAs park in pdl_wait() until that kernel has
+// completed and its writes are visible. Everything that reads or writes global memory comes after pdl_wait(), so
+// the result is that of a plain in-order launch; what is saved is the launch gap and the block-scheduling ramp
+// of small batches. Behind anything that is not a kernel (a copy, an event wait) the launch is an ordinary one.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                            Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // ---- arithmetic with one rounding per operation ------------------------------------------
 // The CPU checker is built without contraction, so every product that feeds a sum is written
 // with the non-fusing intrinsics; fused operations are spelled fmaf().

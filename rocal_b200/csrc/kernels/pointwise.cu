@@ -160,6 +160,86 @@ __device__ __forceinline__ void color_twist_px2(float2 r, float2 g, float2 b, fl
     o2 = out[2];
 }
 
+
+// ---- RB200_ARITH_FAST: ColorTwist with fused operations, within one uint8 level of the exact sequence ----
+// Internal operator code of the fast instantiation (not part of the C ABI).
+constexpr int kColorTwistFast = 100;
+
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// Per-sample constants of the fast path.
+struct TwistFast {
+    float2 hue_turns;     // hue / 360
+    float2 sat;
+    float a255, b255;     // alpha / 255, beta / 255: the affine step lands on the 0..1 scale so that .sat clamps it
+};
+__device__ __forceinline__ TwistFast twist_fast_setup(float alpha, float beta, float hue, float sat) {
+    TwistFast t;
+    const float ht = hue * (1.0f / 360.0f);
+    t.hue_turns = make_float2(ht, ht);
+    t.sat = make_float2(sat, sat);
+    t.a255 = alpha * (1.0f / 255.0f);
+    t.b255 = beta * (1.0f / 255.0f);
+    return t;
+}
+
+// Two pixels (lanes x, y). The function is that of color_twist_px followed by alpha*x + beta, rearranged:
+//   hue in turns  u = ((g-b | b-r | r-g) / delta + (0 | 2 | 4)) / 6 + hue/360      (one hardware reciprocal)
+//   V*S           vs = clamp(delta * sat, 0, max)      (equal to max * clamp(delta/max * sat, 0, 1))
+//   channel c     max - vs + vs * clamp(2 - 6 * |(u + K_c) - rint(u + K_c)|, 0, 1),  K = 1, 2/3, 1/3
+// the last line being the periodic form of V - V*S*clamp(min(k, 4-k), 0, 1): no wrap-around selects are needed
+// because the distance to the nearest integer is taken instead of a value modulo 6. Returns the three channels of both
+// pixels as integers in the low mantissa byte of 1.5 * 2^23 + value.
+__device__ __forceinline__ void color_twist_fast_px2(float2 r, float2 g, float2 b, const TwistFast& P, float2 (&o)[3]) {
+    float2 cmax, cmin;
+    cmax.x = fmaxf(r.x, fmaxf(g.x, b.x)); cmax.y = fmaxf(r.y, fmaxf(g.y, b.y));
+    cmin.x = fminf(r.x, fminf(g.x, b.x)); cmin.y = fminf(r.y, fminf(g.y, b.y));
+    const float2 neg1 = make_float2(-1.0f, -1.0f);
+    const float2 delta = fma2(cmin, neg1, cmax);
+    float2 rd;
+    rd.x = rcp_approx(fmaxf(delta.x, 1e-20f));
+    rd.y = rcp_approx(fmaxf(delta.y, 1e-20f));
+    const float2 gb = fma2(b, neg1, g), br = fma2(r, neg1, b), rg = fma2(g, neg1, r);
+    float2 num, offs;
+    {
+        const bool ir = cmax.x == r.x, ig = cmax.x == g.x;
+        num.x = ir ? gb.x : (ig ? br.x : rg.x);
+        offs.x = ir ? 0.f : (ig ? (2.0f / 6.0f) : (4.0f / 6.0f));
+    }
+    {
+        const bool ir = cmax.y == r.y, ig = cmax.y == g.y;
+        num.y = ir ? gb.y : (ig ? br.y : rg.y);
+        offs.y = ir ? 0.f : (ig ? (2.0f / 6.0f) : (4.0f / 6.0f));
+    }
+    const float2 sixth = make_float2(1.0f / 6.0f, 1.0f / 6.0f);
+    const float2 u0 = fma2(mul2(num, rd), sixth, add2(offs, P.hue_turns));
+    float2 vs = mul2(delta, P.sat);
+    vs.x = fminf(fmaxf(vs.x, 0.f), cmax.x);
+    vs.y = fminf(fmaxf(vs.y, 0.f), cmax.y);
+    const float2 vms = fma2(vs, neg1, cmax);
+    const float2 big = make_float2(12582912.0f, 12582912.0f), nbig = make_float2(-12582912.0f, -12582912.0f);
+    const float2 k255 = make_float2(255.0f, 255.0f);
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const float kc = c == 0 ? 1.0f : (c == 1 ? (2.0f / 3.0f) : (1.0f / 3.0f));
+        const float2 uc = add2(u0, make_float2(kc, kc));
+        const float2 ri = add2(add2(uc, big), nbig);            // nearest integer (|uc| is far below 2^22)
+        const float2 fr = fma2(ri, neg1, uc);                   // in [-0.5, 0.5]
+        float2 cc;
+        cc.x = __saturatef(fmaf(-6.0f, fabsf(fr.x), 2.0f));
+        cc.y = __saturatef(fmaf(-6.0f, fabsf(fr.y), 2.0f));
+        const float2 ch = fma2(vs, cc, vms);
+        float2 q;
+        q.x = __saturatef(fmaf(P.a255, ch.x, P.b255));
+        q.y = __saturatef(fmaf(P.a255, ch.y, P.b255));
+        o[c] = fma2(q, k255, big);                              // round to nearest even, value in the low byte
+    }
+}
+
 // The colour result before rounding and saturation.
 template <int COLOR_OP>
 __device__ __forceinline__ void color_raw(float& v0, float& v1, float& v2, float alpha, float beta, float hue, float sat,
@@ -176,7 +256,7 @@ __device__ __forceinline__ void color_raw(float& v0, float& v1, float& v2, float
         v0 = add_rn(mul_rn(sub_rn(v0, beta), alpha), beta);
         v1 = add_rn(mul_rn(sub_rn(v1, beta), alpha), beta);
         v2 = add_rn(mul_rn(sub_rn(v2, beta), alpha), beta);
-    } else if (COLOR_OP == RB200_COLOR_TWIST) {
+    } else if (COLOR_OP == RB200_COLOR_TWIST || COLOR_OP == kColorTwistFast) {
         float t0, t1, t2;
         color_twist_px(v0, v1, v2, hue, sat, rcp, t0, t1, t2);
         v0 = add_rn(mul_rn(alpha, t0), beta);
@@ -290,6 +370,31 @@ __device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t 
                                                float hue, float sat, const float* rcp) {
     if (COLOR_OP == RB200_COLOR_NONE) {
         e[0] = d[0]; e[1] = d[1]; e[2] = d[2];
+    } else if (COLOR_OP == kColorTwistFast) {
+        const TwistFast P = twist_fast_setup(alpha, beta, hue, sat);
+        const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
+        uint32_t q[12];
+#pragma unroll
+        for (int k = 0; k < 4; k += 2) {
+            float2 c3[3];
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                const int ba = 3 * k + c, bb = 3 * (k + 1) + c;
+                c3[c].x = __uint_as_float(__byte_perm(d[ba >> 2], magic, 0x7650u + (ba & 3)));
+                c3[c].y = __uint_as_float(__byte_perm(d[bb >> 2], magic, 0x7650u + (bb & 3)));
+                c3[c] = add2(c3[c], nk23);
+            }
+            float2 o[3];
+            color_twist_fast_px2(c3[0], c3[1], c3[2], P, o);
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                q[3 * k + c] = __float_as_uint(o[c].x);
+                q[3 * k + 3 + c] = __float_as_uint(o[c].y);
+            }
+        }
+#pragma unroll
+        for (int wd = 0; wd < 3; wd++)
+            e[wd] = __byte_perm(__byte_perm(q[4 * wd], q[4 * wd + 1], 0x0040u), __byte_perm(q[4 * wd + 2], q[4 * wd + 3], 0x0040u), 0x5410u);
     } else if (COLOR_OP == RB200_COLOR_TWIST) {
         uint32_t q[12];
         const float2 nk23 = make_float2(-8388608.0f, -8388608.0f);
@@ -345,7 +450,12 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
     // Layout: mbarrier (16 bytes) | rcp[256] | staged source rows (th x pitch)
     extern __shared__ __align__(16) uint8_t pw_smem[];
     __shared__ int stage_flag;
+    pdl_launch_dependents();
     float* rcp = reinterpret_cast<float*>(pw_smem + 16);
+    // the reciprocal table depends on nothing in memory: it is built while the preceding kernel drains
+    if (COLOR_OP == RB200_COLOR_TWIST || COLOR_OP == kColorTwistFast)
+        for (int k = threadIdx.x; k < 256; k += blockDim.x) rcp[k] = k ? div_rn(1.0f, (float)k) : 0.f;
+    pdl_wait();
     uint8_t* stage = pw_smem + 16 + 1024;
     const uint32_t bar = pw_smem_u32(pw_smem);
     const int n = blockIdx.y;
@@ -368,8 +478,6 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
-        if (COLOR_OP == RB200_COLOR_TWIST)
-            for (int k = threadIdx.x; k < 256; k += blockDim.x) rcp[k] = k ? div_rn(1.0f, (float)k) : 0.f;
         __syncthreads();
         if (threadIdx.x < 32 && (int)threadIdx.x < rows) {
             uint32_t total = 0;
@@ -652,7 +760,7 @@ static void launch_one(bool vec, dim3 grid, int threads, size_t smem, cudaStream
     if (vec) {
         auto k = pointwise_vec_kernel<OutT, LAYOUT, COLOR_OP>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<grid, threads, smem, stream>>>(arena, samples, L);
+        launch_overlapped(k, grid, dim3((unsigned)threads), smem, stream, arena, samples, L);
     } else
         pointwise_kernel<OutT, LAYOUT, COLOR_OP><<<grid, threads, 0, stream>>>(arena, samples, L);
 }
@@ -665,6 +773,10 @@ static int launch_color(int color_op, bool vec, dim3 grid, int threads, size_t s
         case RB200_COLOR_BRIGHTNESS: launch_one<OutT, LAYOUT, RB200_COLOR_BRIGHTNESS>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_CONTRAST: launch_one<OutT, LAYOUT, RB200_COLOR_CONTRAST>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_TWIST: launch_one<OutT, LAYOUT, RB200_COLOR_TWIST>(vec, grid, threads, smem, stream, arena, samples, L); break;
+        case kColorTwistFast:
+            // only the uint8 vector kernel has a fast block; every other shape was routed to the exact operator
+            launch_one<OutT, LAYOUT, sizeof(OutT) == 1 ? kColorTwistFast : RB200_COLOR_TWIST>(true, grid, threads, smem, stream, arena, samples, L);
+            break;
         case RB200_COLOR_GAMMA: launch_one<OutT, LAYOUT, RB200_COLOR_GAMMA>(vec, grid, threads, smem, stream, arena, samples, L); break;
         case RB200_COLOR_BLEND:   // two sources: the scalar kernel only
             pointwise_kernel<OutT, LAYOUT, RB200_COLOR_BLEND><<<grid, threads, 0, stream>>>(arena, samples, L);
@@ -763,7 +875,11 @@ static int pointwise_launch(const uint8_t* arena, const rb200_pointwise_sample* 
         grid = dim3((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
     }
 
-#define RB200_DISPATCH(T, LAY) return launch_color<T, LAY>(p->color_op, vec, grid, threads, smem, stream, arena, samples, L)
+    // the fast arithmetic exists for ColorTwist (Hue / Saturation are the same operator) on the uint8 vector kernel
+    // without normalisation or channel reversal; everything else runs the exact code
+    const int op = (p->color_op == RB200_COLOR_TWIST && p->arith == RB200_ARITH_FAST && vec && p->out_dtype == RB200_UINT8 &&
+                    !p->normalize && !p->reverse_channels) ? kColorTwistFast : p->color_op;
+#define RB200_DISPATCH(T, LAY) return launch_color<T, LAY>(op, vec, grid, threads, smem, stream, arena, samples, L)
     if (p->out_layout == RB200_NCHW) {
         if (p->out_dtype == RB200_FP32) RB200_DISPATCH(float, RB200_NCHW);
         if (p->out_dtype == RB200_FP16) RB200_DISPATCH(__half, RB200_NCHW);

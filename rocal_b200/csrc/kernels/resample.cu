@@ -314,6 +314,8 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                                                               const rb200_resample_sample* __restrict__ samples,
                                                               const ResampleLaunch L) {
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     // Layout: full[NS] | empty[NS] (128 bytes reserved) | StreamRow[32] | StreamSrc[32] | stages
     const int NS = L.ns, ns_mask = L.ns - 1, ns_lg = L.ns_log2;
     StreamRow* rowtab = reinterpret_cast<StreamRow*>(smem + 128);
@@ -1016,7 +1018,8 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
             if (rc) return rc;
         }
         // compute threads rounded up to whole warps + one producer warp
-        k<<<grid, ((L.twh + 31) & ~31) + 32, smem, stream>>>(arena, samples, L);
+        cudaError_t le = launch_overlapped(k, grid, dim3((unsigned)(((L.twh + 31) & ~31) + 32)), smem, stream, arena, samples, L);
+        if (le != cudaSuccess) return check_cuda(le, "launch of resample_stream_kernel");
     } else if (mode == MODE_STAGED) {
         int tiles_y = (L.ext_h + L.th - 1) / L.th;
         dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);

@@ -180,6 +180,8 @@ __global__ void __launch_bounds__(256, 5) warp_affine_kernel(const uint8_t* __re
     // Layout: staged source rows | per-row offset pairs
     extern __shared__ __align__(16) uint8_t stage[];
     __shared__ WarpHeader hdr;
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int n = blockIdx.y;
     const int tile_x0 = (blockIdx.x % L.tiles_x) * kWarpTileW;
@@ -317,7 +319,7 @@ extern "C" int rb200k_warp_affine(const uint8_t* arena, const rb200_warp_sample*
     L.tiles_x = (p->out_w + kWarpTileW - 1) / kWarpTileW;
     int tiles_y = (p->out_h + kWarpTileH - 1) / kWarpTileH;
     dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);
-    warp_affine_kernel<<<grid, 256, kWarpStageBytes, (cudaStream_t)stream_v>>>(arena, samples, L);
+    launch_overlapped(warp_affine_kernel, grid, dim3(256), (size_t)kWarpStageBytes, (cudaStream_t)stream_v, arena, samples, L);
     RB200_CHECK_LAUNCH("warp_affine_kernel");
     return RB200_OK;
 }

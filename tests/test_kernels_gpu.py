@@ -525,3 +525,37 @@ def test_empty_batch_and_bad_arguments(cuda):
         K.resample(arena, t, 8, 8, fill_padding=False)
     with pytest.raises(Rb200Error):
         K.resample(arena, t, 0, 8)
+
+
+def test_color_twist_fast_arithmetic_within_one_level(cuda):
+    """RB200_ARITH_FAST: ColorTwist (and Hue / Saturation, the same operator) with fused operations, one hardware
+    reciprocal and the periodic HSV -> RGB form. Every byte lies within one level of the exact result and all but a
+    few per million are equal; greys, fully saturated colours, negative and large saturation factors, hue shifts
+    beyond a full turn, flips and both uint8 layouts are covered. Other operators ignore the setting."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(50)
+    n = 48
+    arena, hs, ws, offs = S.make_images(rng, n, (96, 96), (128, 128), content="noise")
+    px = arena[:96 * 128 * 3].reshape(-1, 3)
+    px[:4000] = np.repeat(rng.integers(0, 256, 4000, dtype=np.uint8)[:, None], 3, 1)     # greys
+    px[4000:8000, 0] = 255                                                                # red at its maximum
+    px[8000:12000, 2] = 0
+    t = S.color_twist_tables(rng, hs, ws, offs)
+    t["alpha"] = rng.uniform(0.1, 1.95, n)
+    t["beta"] = rng.uniform(0.0, 25.0, n)
+    t["hue"] = rng.uniform(-400.0, 400.0, n)
+    t["sat"] = rng.uniform(-0.2, 2.5, n)
+    a = _dev(arena, cuda)
+    for layout in (T.NHWC, T.NCHW):
+        ref = O.pointwise(arena, t, 128, 96, T.COLOR_TWIST, T.UINT8, layout)
+        exact = K.pointwise(a, t, 128, 96, T.COLOR_TWIST, T.UINT8, layout, arith=0).cpu().numpy()
+        fast = K.pointwise(a, t, 128, 96, T.COLOR_TWIST, T.UINT8, layout, arith=1).cpu().numpy()
+        assert np.array_equal(exact, ref)
+        d = np.abs(fast.astype(np.int32) - ref.astype(np.int32))
+        assert d.max() <= 1, "fast arithmetic left the one-level band"
+        assert np.count_nonzero(d) < d.size * 1e-4, "%d of %d bytes differ" % (np.count_nonzero(d), d.size)
+    # operators without a fast instantiation, and float outputs, are exact under either setting
+    ref = O.pointwise(arena, t, 128, 96, T.COLOR_BRIGHTNESS)
+    assert np.array_equal(K.pointwise(a, t, 128, 96, T.COLOR_BRIGHTNESS, arith=1).cpu().numpy(), ref)
+    ref = O.pointwise(arena, t, 128, 96, T.COLOR_TWIST, T.FP32, T.NCHW)
+    assert np.array_equal(K.pointwise(a, t, 128, 96, T.COLOR_TWIST, T.FP32, T.NCHW, arith=1).cpu().numpy(), ref)
