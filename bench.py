@@ -245,7 +245,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=F
             a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
             o = torch.empty((n, 3, 224, 224), dtype=torch.float32, device=dev)
             resident.append(lambda a=a, t=t, dt=dt, o=o: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=o,
-                                                                      d_samples=dt, stream=stream))
+                                                                      d_samples=dt, stream=stream, overlap=True))
             ap_ = torch.from_numpy(arena).pin_memory()
             anchors = (rng.random(n).astype(np.float32), rng.random(n).astype(np.float32))
             feeders.append(lambda ap_=ap_, hs=hs, ws=ws, offs=offs, anchors=anchors: (pipe.set_crop_anchors(outn, *anchors),
@@ -277,7 +277,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=F
             a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
             o = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
             resident.append(lambda a=a, t=t, dt=dt, o=o: K.pointwise(a, t, 224, 224, T.COLOR_TWIST, out=o, d_samples=dt, fill_padding=False,
-                                                                       stream=stream, arith=1 if fast else 0))
+                                                                       stream=stream, arith=1 if fast else 0, overlap=True))
             ap_ = torch.from_numpy(arena).pin_memory()
             feeders.append(lambda ap_=ap_, hs=hs, ws=ws, offs=offs: pipe.feed_ragged(ap_, hs, ws, offs))
             if k == 0:
@@ -299,7 +299,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=F
             t = S.warp_tables(rng, hs, ws, offs, 640, 480)
             a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
             o = torch.empty((n, 480, 640, 3), dtype=torch.uint8, device=dev)
-            resident.append(lambda a=a, t=t, dt=dt, o=o: K.warp_affine(a, t, 640, 480, out=o, d_samples=dt, stream=stream))
+            resident.append(lambda a=a, t=t, dt=dt, o=o: K.warp_affine(a, t, 640, 480, out=o, d_samples=dt, stream=stream, overlap=True))
             ap_ = torch.from_numpy(arena).pin_memory()
             feeders.append(lambda ap_=ap_, hs=hs, ws=ws, offs=offs, m=t["m"].copy(): (pipe.set_affine(outn, m), pipe.feed_ragged(ap_, hs, ws, offs)))
             if k == 0:
@@ -426,7 +426,7 @@ def other_configs(sampler):
     against the roofline."""
     out = []
     for cfg, fast in ((0, False), (2, False), (2, True), (3, False), (4, False)):
-        r = measure_config(cfg, steps=40, warmup=5, e2e_steps=12, with_cpu=False, sampler=sampler, fast=fast)
+        r = measure_config(cfg, steps=400, warmup=20, e2e_steps=12, with_cpu=False, sampler=sampler, fast=fast)
         out.append({"workload": r["config"]["workload"], "ms_per_step": r["ms_per_step"], "value": r["value"], "unit": r["unit"],
                     "roofline": {"kernel": r["roofline"]["kernel"], "frac": r["roofline"]["frac"], "achieved": r["roofline"]["achieved"],
                                  "algorithmic_bytes_per_launch": r["roofline"]["algorithmic_bytes_per_launch"]},
@@ -465,6 +465,7 @@ def run_ops(args):
     dev = torch.device("cuda:0")
     peak, peak_src = peak_hbm()
     mul, add = S.normalize_tables()
+    ov = not args.no_overlap      # the rotating batches are independent of one another
 
     def report(name, n, ms, algo_bytes, extra=None):
         line = {"op": name, "images_per_launch": n, "launch_ms": ms, "images_per_s": n / (ms * 1e-3),
@@ -486,7 +487,7 @@ def run_ops(args):
                 algo = float((3.0 * (np.ceil(224 / (256 / short)) + 1) ** 2).sum() + n * 3 * 224 * 224 * 4)
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device=dev)
-                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt, overlap=ov))
             report("cfg0 resize+CMN fp32 NCHW (batch 64, 256..512 px)", n, _time_launches(fns, args.steps), algo)
         elif op in ("color_twist", "brightness", "contrast", "flip"):
             n, rot = args.batch or 256, 4
@@ -499,7 +500,7 @@ def run_ops(args):
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device=dev)
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.pointwise(a, t, 224, 224, code, out=out, d_samples=dt, fill_padding=False,
-                                                                        arith=1 if args.fast else 0))
+                                                                        arith=1 if args.fast else 0, overlap=ov))
             report("cfg2 %s(+flip) u8 HWC 224x224 (batch %d)%s" % (op, n, " fast arithmetic" if args.fast else ""), n, _time_launches(fns, args.steps), n * 2 * 3 * 224 * 224)
         elif op == "warp":
             n, rot = 128, 2
@@ -510,7 +511,7 @@ def run_ops(args):
                 t = S.warp_tables(rng, hs, ws, offs, 640, 480)
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 480, 640, 3), dtype=torch.uint8, device=dev)
-                fns.append(lambda a=a, t=t, dt=dt, out=out: K.warp_affine(a, t, 640, 480, out=out, d_samples=dt))
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.warp_affine(a, t, 640, 480, out=out, d_samples=dt, overlap=ov))
             report("cfg3 warp_affine u8 480x640 (batch 128)", n, _time_launches(fns, args.steps), n * 2 * 3 * 480 * 640)
         elif op == "ssd_chain":
             n, rot = 128, 2
@@ -524,7 +525,7 @@ def run_ops(args):
                 algo = float((3.0 * t["roi_w"].astype(np.float64) * t["roi_h"]).sum() + n * 3 * 300 * 300 * 4)
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 3, 300, 300), dtype=torch.float32, device=dev)
-                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 300, 300, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt))
+                fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 300, 300, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt, overlap=ov))
             report("cfg4 crop->resize 300x300->CMN fp32 NCHW (batch 128)", n, _time_launches(fns, args.steps), algo)
         elif op == "box_encoder":
             n, rot = 128, 4
@@ -672,6 +673,7 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4],
                     help="BASELINE configuration; 1 (default) is the headline workload, the others run on one GPU only")
     ap.add_argument("--op", default=None, help="operator-level cases, comma separated (see run_ops)")
+    ap.add_argument("--no-overlap", action="store_true", help="--op cases: plain stream order between the launches")
     ap.add_argument("--fast", action="store_true", help="colour operators with RB200_ARITH_FAST (--config 2 and the colour --op cases)")
     args = ap.parse_args()
     if args.op:
@@ -723,7 +725,7 @@ def main():
 
     def step_resident():
         K.resample(arena_d, t, OUT, OUT, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=table_d,
-                   stream=stream)
+                   stream=stream)      # the same output buffer every step: plain stream order, no overlap
 
     # ---- device-resident throughput + per-launch kernel time (kernel-level C-ABI, CUDA events) ----
     sampler = ClockSampler(local_rank)

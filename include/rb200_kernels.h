@@ -98,6 +98,9 @@ typedef struct rb200_resample_params {
     float add[3];
     int32_t interpolation;
     int32_t path;                /* RB200_RESAMPLE_PATH_*: which of the bilinear kernels runs; the results are identical */
+    int32_t overlap;             /* 1 = this launch may overlap the tail of the kernel enqueued just before it in the
+                                    stream, see "Overlapping launches" below; 0 = plain stream order */
+    int32_t reserved;
     int32_t* status;             /* where a kernel that gives up on a bounded wait writes 1: a 4-byte word the device can
                                     write (device memory, or mapped pinned host memory); NULL = the library-wide word of
                                     this device that rb200k_device_status() reads */
@@ -164,6 +167,7 @@ typedef struct rb200_pointwise_params {
     float mul[3];
     float add[3];
     int32_t arith;               /* RB200_ARITH_EXACT (0) or RB200_ARITH_FAST (1), see below */
+    int32_t overlap;             /* as rb200_resample_params.overlap */
     int32_t* status;             /* as rb200_resample_params.status */
 } rb200_pointwise_params;
 
@@ -202,7 +206,7 @@ typedef struct rb200_warp_params {
     void* out;                   /* uint8 NHWC [N][out_h][out_w][3]                          */
     int32_t out_w, out_h;
     int32_t fill_padding;
-    int32_t reserved;
+    int32_t overlap;             /* as rb200_resample_params.overlap */
 } rb200_warp_params;
 
 /* replaces: vxExtRppWarpAffine (node_warp_affine.cpp:61), vxExtRppRotate (node_rotate.cpp:43). */
@@ -257,6 +261,21 @@ typedef struct rb200_box_matcher_params {
 
 RB200_API int rb200k_box_iou_match(const float* boxes, const int32_t* box_offsets, int n, int max_boxes_per_sample,
                          const rb200_box_matcher_params* params, int32_t* out_matches, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Overlapping launches
+ * ------------------------------------------------------------------------------------- */
+
+/* The row-streaming resample kernel, the pointwise vector kernel and the affine kernel are launched with
+ * programmatic stream serialization: behind another kernel of the same stream their CTAs may become resident while
+ * that kernel's last CTAs still run. With overlap = 0 they then wait, before they touch global memory, until the
+ * preceding kernel has completed and its writes are visible - the result is that of a plain in-order launch and only
+ * the launch gap is saved. overlap = 1 states that the launch is independent of the kernel enqueued just before it:
+ * it reads nothing that kernel writes (images, tables) and writes nothing that kernel reads or writes. Its CTAs then
+ * start working at once, which hides the ramp-up and tail of small batches, and wait for the preceding kernel only
+ * before they exit, so that completion of this launch still implies completion of everything before it in the
+ * stream. Batches of a device-resident loop that use separate input and output buffers qualify; a step that reads
+ * the previous step's output does not. Behind a copy or an event wait the launch is an ordinary one either way. */
 
 /* ---------------------------------------------------------------------------------------
  * Bounded waits

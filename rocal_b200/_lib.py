@@ -21,7 +21,7 @@ class ResampleParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32),
-                ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p)]
 
 
 class PointwiseParams(ctypes.Structure):
@@ -30,12 +30,12 @@ class PointwiseParams(ctypes.Structure):
                 ("color_op", ctypes.c_int32), ("normalize", ctypes.c_int32),
                 ("fill_padding", ctypes.c_int32), ("reverse_channels", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("arith", ctypes.c_int32),
-                ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p)]
 
 
 class WarpParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
-                ("fill_padding", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+                ("fill_padding", ctypes.c_int32), ("overlap", ctypes.c_int32)]
 
 
 class BoxEncoderParams(ctypes.Structure):

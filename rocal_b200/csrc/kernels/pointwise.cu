@@ -36,6 +36,7 @@ struct PointwiseLaunch {
     int* status;         // vector kernel: written with 1 when the bounded wait on the staged rows gives up
     long long wait_cycles;   // vector kernel: limit of that wait, SM clock cycles
     int skip_row;        // vector kernel, self-test: the copy of this tile row is never issued (-1: all are)
+    int overlap;         // vector kernel: 1 = independent of the preceding kernel, wait for it only before exit
 };
 
 __device__ __forceinline__ uint32_t pw_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -455,7 +456,7 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
     // the reciprocal table depends on nothing in memory: it is built while the preceding kernel drains
     if (COLOR_OP == RB200_COLOR_TWIST || COLOR_OP == kColorTwistFast)
         for (int k = threadIdx.x; k < 256; k += blockDim.x) rcp[k] = k ? div_rn(1.0f, (float)k) : 0.f;
-    pdl_wait();
+    if (!L.overlap) pdl_wait();
     uint8_t* stage = pw_smem + 16 + 1024;
     const uint32_t bar = pw_smem_u32(pw_smem);
     const int n = blockIdx.y;
@@ -693,6 +694,7 @@ __global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __res
             if (y >= h || x >= w) pw_store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, x, 0.f, 0.f, 0.f);
         }
     }
+    if (L.overlap) pdl_wait();      // completion of this launch implies completion of the kernel before it
 }
 
 // Scalar kernel: one thread per output column, any width and alignment.
@@ -829,6 +831,7 @@ static int pointwise_launch(const uint8_t* arena, const rb200_pointwise_sample* 
     }
     L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
     L.skip_row = skip_row;
+    L.overlap = p->overlap ? 1 : 0;
     int ext_w = p->out_w, ext_h = p->out_h;
     if (h_samples && !p->fill_padding) {
         ext_w = 1; ext_h = 1;

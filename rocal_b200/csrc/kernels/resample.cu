@@ -49,6 +49,7 @@ struct ResampleLaunch {
     int* status;        // stream kernel: written with 1 when a bounded wait gives up
     long long wait_cycles;   // stream kernel: limit of every mbarrier wait, SM clock cycles
     int skip_row;       // stream kernel, self-test: the producer issues no copy from this strip row on (-1: all)
+    int overlap;        // stream kernel: 1 = independent of the preceding kernel, wait for it only before exit
 };
 
 struct RowInfo {
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                                                               const ResampleLaunch L) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
-    pdl_wait();
+    if (!L.overlap) pdl_wait();
     // Layout: full[NS] | empty[NS] (128 bytes reserved) | StreamRow[32] | StreamSrc[32] | stages
     const int NS = L.ns, ns_mask = L.ns - 1, ns_lg = L.ns_log2;
     StreamRow* rowtab = reinterpret_cast<StreamRow*>(smem + 128);
@@ -473,6 +474,7 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
             }
         }
     }
+    if (L.overlap) pdl_wait();      // completion of this launch implies completion of the kernel before it
 }
 
 template <typename OutT, int LAYOUT, bool NORMALIZE>
@@ -1093,6 +1095,7 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
     }
     L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
     L.skip_row = skip_row;
+    L.overlap = p->overlap ? 1 : 0;
 
     // Extent the grid has to cover.
     int ext_w = p->out_w, ext_h = p->out_h;

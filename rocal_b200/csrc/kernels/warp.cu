@@ -28,6 +28,7 @@ struct WarpLaunch {
     int fill_padding;
     uint32_t magic;     // 0x4B000000
     int vec_store;      // rows of the output start on 4-byte boundaries
+    int overlap;        // 1 = independent of the preceding kernel, wait for it only before exit
 };
 
 struct WarpMap {
@@ -174,14 +175,8 @@ __device__ __forceinline__ void warp_pixels(uint32_t (&px)[kWarpPx], const WarpM
     }
 }
 
-__global__ void __launch_bounds__(256, 5) warp_affine_kernel(const uint8_t* __restrict__ arena,
-                                                          const rb200_warp_sample* __restrict__ samples,
-                                                          const WarpLaunch L) {
-    // Layout: staged source rows | per-row offset pairs
-    extern __shared__ __align__(16) uint8_t stage[];
-    __shared__ WarpHeader hdr;
-    pdl_launch_dependents();
-    pdl_wait();
+__device__ __forceinline__ void warp_affine_tile(const uint8_t* __restrict__ arena, const rb200_warp_sample* __restrict__ samples,
+                                                 const WarpLaunch& L, uint8_t* stage, WarpHeader& hdr) {
 
     const int n = blockIdx.y;
     const int tile_x0 = (blockIdx.x % L.tiles_x) * kWarpTileW;
@@ -294,6 +289,18 @@ __global__ void __launch_bounds__(256, 5) warp_affine_kernel(const uint8_t* __re
     }
 }
 
+__global__ void __launch_bounds__(256, 5) warp_affine_kernel(const uint8_t* __restrict__ arena,
+                                                          const rb200_warp_sample* __restrict__ samples,
+                                                          const WarpLaunch L) {
+    // Layout: staged source rows | per-row offset pairs
+    extern __shared__ __align__(16) uint8_t stage[];
+    __shared__ WarpHeader hdr;
+    pdl_launch_dependents();
+    if (!L.overlap) pdl_wait();
+    warp_affine_tile(arena, samples, L, stage, hdr);
+    if (L.overlap) pdl_wait();      // completion of this launch implies completion of the kernel before it
+}
+
 }  // namespace rb200
 
 using namespace rb200;
@@ -316,6 +323,7 @@ extern "C" int rb200k_warp_affine(const uint8_t* arena, const rb200_warp_sample*
     L.fill_padding = p->fill_padding;
     L.magic = 0x4B000000u;
     L.vec_store = (p->out_w % 4 == 0) && (((uintptr_t)p->out & 3) == 0);
+    L.overlap = p->overlap ? 1 : 0;
     L.tiles_x = (p->out_w + kWarpTileW - 1) / kWarpTileW;
     int tiles_y = (p->out_h + kWarpTileH - 1) / kWarpTileH;
     dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);

@@ -37,8 +37,8 @@ def _alloc_out(n, out_w, out_h, dtype, layout, device, out):
 
 def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
              fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0,
-             status=None, probe=None):
-    """rb200k_resample. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
+             status=None, probe=None, overlap=False):
+    """rb200k_resample. overlap=True states that the launch is independent of the kernel enqueued just before it. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
     already on the device (uploaded here when None). staged=False withholds the host table from
     the launch so that the kernel gathers straight from global memory; path=1 (RB200_RESAMPLE_PATH_TILE)
     forces the shared-memory tile kernel. status: an int32 CUDA tensor that receives 1 when a bounded wait gives up
@@ -58,6 +58,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0
     p.status = status.data_ptr() if status is not None else None
+    p.overlap = 1 if overlap else 0
     h_ptr = samples.ctypes.data_as(ctypes.c_void_p) if staged else None
     if probe is not None:
         check(lib.rb200k_resample_probe(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
@@ -70,7 +71,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
 
 def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.UINT8, out_layout=T.NHWC,
               mul=None, add=None, reverse_channels=False, fill_padding=True, out=None, d_samples=None,
-              stream=None, arith=0, status=None, probe=None):
+              stream=None, arith=0, status=None, probe=None, overlap=False):
     """rb200k_pointwise. arith: 0 exact, 1 fast colour arithmetic; status / probe as for resample."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
@@ -87,6 +88,7 @@ def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.U
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0
     p.arith = int(arith)
+    p.overlap = 1 if overlap else 0
     p.status = status.data_ptr() if status is not None else None
     if probe is not None:
         check(lib.rb200k_pointwise_probe(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
@@ -98,7 +100,7 @@ def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.U
     return out
 
 
-def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_samples=None, stream=None):
+def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_samples=None, stream=None, overlap=False):
     """rb200k_warp_affine: uint8 NHWC output."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, T.UINT8, T.NHWC, arena.device, out)
@@ -108,6 +110,7 @@ def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_sam
     p.out = out.data_ptr()
     p.out_w, p.out_h = out_w, out_h
     p.fill_padding = 1 if fill_padding else 0
+    p.overlap = 1 if overlap else 0
     check(lib.rb200k_warp_affine(arena.data_ptr(), d_samples.data_ptr(), n, ctypes.byref(p), _stream_ptr(stream)),
           "rb200k_warp_affine")
     return out

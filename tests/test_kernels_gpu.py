@@ -559,3 +559,38 @@ def test_color_twist_fast_arithmetic_within_one_level(cuda):
     assert np.array_equal(K.pointwise(a, t, 128, 96, T.COLOR_BRIGHTNESS, arith=1).cpu().numpy(), ref)
     ref = O.pointwise(arena, t, 128, 96, T.COLOR_TWIST, T.FP32, T.NCHW)
     assert np.array_equal(K.pointwise(a, t, 128, 96, T.COLOR_TWIST, T.FP32, T.NCHW, arith=1).cpu().numpy(), ref)
+
+
+def test_overlapped_launches_are_exact(cuda):
+    """overlap = 1: independent launches enqueued back to back may run under one another's tails. Sixty launches
+    rotating over three batches with their own outputs, resample / pointwise / affine interleaved, then readers that
+    know nothing of the overlap (torch copies) - every output still equals the oracle."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(51)
+    mul, add = S.normalize_tables()
+    sets = []
+    for _ in range(3):
+        arena, hs, ws, offs = S.make_images(rng, 24, (256, 400), (256, 400))
+        t = S.classification_tables(rng, hs, ws, offs)
+        pt = S.color_twist_tables(rng, np.minimum(hs, 224), np.minimum(ws, 224), offs)
+        pt["src_stride"] = ws * 3
+        wt = S.warp_tables(rng, hs, ws, offs, 160, 120)
+        a = _dev(arena, cuda)
+        sets.append({"arena": arena, "a": a, "t": t, "pt": pt, "wt": wt,
+                     "o1": torch.zeros((24, 3, 224, 224), dtype=torch.float32, device=cuda),
+                     "o2": torch.zeros((24, 224, 224, 3), dtype=torch.uint8, device=cuda),
+                     "o3": torch.zeros((24, 120, 160, 3), dtype=torch.uint8, device=cuda),
+                     "dt": K.to_device_table(t, cuda), "dpt": K.to_device_table(pt, cuda), "dwt": K.to_device_table(wt, cuda)})
+    for i in range(20):
+        s = sets[i % 3]
+        K.resample(s["a"], s["t"], 224, 224, T.FP32, T.NCHW, mul, add, out=s["o1"], d_samples=s["dt"], overlap=True)
+        K.pointwise(s["a"], s["pt"], 224, 224, T.COLOR_BRIGHTNESS, out=s["o2"], d_samples=s["dpt"], overlap=True)
+        K.warp_affine(s["a"], s["wt"], 160, 120, out=s["o3"], d_samples=s["dwt"], overlap=True)
+    copies = [(s["o1"].clone(), s["o2"].clone(), s["o3"].clone()) for s in sets]      # ordinary stream-ordered readers
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    for s, (c1, c2, c3) in zip(sets, copies):
+        assert np.array_equal(c1.cpu().numpy(), O.resample(s["arena"], s["t"], 224, 224, T.FP32, T.NCHW, mul, add))
+        assert np.array_equal(c2.cpu().numpy(), O.pointwise(s["arena"], s["pt"], 224, 224, T.COLOR_BRIGHTNESS))
+        assert np.array_equal(c3.cpu().numpy(), O.warp_affine(s["arena"], s["wt"], 160, 120))
