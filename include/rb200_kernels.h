@@ -263,6 +263,49 @@ RB200_API int rb200k_box_iou_match(const float* boxes, const int32_t* box_offset
                          const rb200_box_matcher_params* params, int32_t* out_matches, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Normalize / Transpose (neighbouring operators of the augmentation path)
+ * ------------------------------------------------------------------------------------- */
+
+/* Mean / standard-deviation normalisation of uint8 HWC images:  out = scale * (x - mean) / stddev + shift, float32 or
+ * float16, same layout (NHWC, [N][out_h][out_w][3], the sample's window at the origin). axis_mask names the axes that
+ * are reduced when mean and / or stddev are computed from the data: bit 0 = height, bit 1 = width, bit 2 = channel
+ * (the reference's convention for an NHWC tensor, node_normalize.cpp:42-50); the statistics then have one value per
+ * index of the remaining axes - mask 3 gives one mean per channel, mask 7 one per image, mask 1 one per column and
+ * channel. Given values (compute_* = 0) are per-channel constants. Computed statistics are those of the whole
+ * population (divisor = number of values); a zero standard deviation yields out = shift.
+ *
+ * The statistics are accumulated exactly (integer sums of x and x^2, 64-bit atomics) in `scratch`: device memory of at
+ * least rb200k_normalize_scratch_bytes(n, max_w, max_h, axis_mask) bytes that the caller owns; it needs no
+ * initialisation (the call clears what it uses) and holds nothing of value afterwards. With neither statistic
+ * computed no scratch is needed (NULL is accepted). The call enqueues a clear, the sums, a small finishing kernel and the
+ * element-wise pass on `stream`.
+ * replaces: vxExtRppNormalize (rocAL/source/augmentations/effects_augmentations/node_normalize.cpp:105),
+ *           rocalNormalize (rocAL/include/api/rocal_api_augmentation.h:1294). The arithmetic lives in RPP; the
+ *           definitions above are this library's reading of the documented formula (rocAL_pybind/amd/rocal/fn.py:1216-1223). */
+typedef struct rb200_normalize_params {
+    void* out;
+    int32_t out_w, out_h;
+    int32_t out_dtype;           /* RB200_FP32 or RB200_FP16 */
+    int32_t axis_mask;           /* 1..7 when a statistic is computed */
+    int32_t compute_mean, compute_stddev;
+    int32_t fill_padding;        /* 1 = elements outside a sample's window are written as 0 */
+    float mean[3], stddev[3];    /* per-channel values for the statistic(s) that are not computed */
+    float scale, shift;
+} rb200_normalize_params;
+
+RB200_API size_t rb200k_normalize_scratch_bytes(int n, int max_w, int max_h, int axis_mask);
+RB200_API int rb200k_normalize(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                     const rb200_pointwise_sample* h_samples, int n, const rb200_normalize_params* params,
+                     void* scratch, size_t scratch_bytes, void* stream);
+
+/* Axis permutation of uint8 HWC images: out dims = (d[perm[0]], d[perm[1]], d[perm[2]]) with d = (h, w, 3) of the
+ * sample's window; every sample's result is written densely at the start of its out_stride-byte slot. flip_* of the
+ * sample table are ignored.
+ * replaces: vxExtRppTranspose, rocalTranspose (rocAL/include/api/rocal_api_augmentation.h:1338). */
+RB200_API int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_sample* samples, int n, const int32_t perm[3],
+                     uint8_t* out, size_t out_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Overlapping launches
  * ------------------------------------------------------------------------------------- */
 

@@ -654,4 +654,129 @@ ORC_API void orc_crop_fixed(unsigned in_w, unsigned in_h, unsigned crop_w, unsig
     (void)x2; (void)y2;
 }
 
+/* ------------------------------------------------------------------------------------------
+ * Normalize: out = scale * (x - mean) / stddev + shift (rocAL_pybind/amd/rocal/fn.py:1216-1223,
+ * rocAL/source/augmentations/effects_augmentations/node_normalize.cpp:31-105 for the meaning of the axis mask and
+ * of given / computed statistics). The reference keeps the arithmetic in RPP: PARITY UNPINNED. Definitions used
+ * here: statistics of the whole population from exact integer sums, evaluated in double (mean = S1/N,
+ * var = (S2 - 2 m S1)/N + m^2 about the float mean m in use, negative values from rounding count as 0), both
+ * rounded to float; mult = scale / stddev in float (0 when stddev is 0); out = fmaf(x - mean, mult, shift).
+ * ---------------------------------------------------------------------------------------- */
+static int norm_stat_index(int mask, int y, int x, int c, int w) {
+    switch (mask) {
+        case 1: return x * 3 + c;
+        case 2: return y * 3 + c;
+        case 3: return c;
+        case 4: return y * w + x;
+        case 5: return x;
+        case 6: return y;
+        default: return 0;
+    }
+}
+
+static int norm_stat_slots(int mask, int w, int h) {
+    switch (mask) {
+        case 1: return 3 * w;
+        case 2: return 3 * h;
+        case 3: return 3;
+        case 4: return w * h;
+        case 5: return w;
+        case 6: return h;
+        default: return 1;
+    }
+}
+
+typedef struct orc_normalize_params {
+    void* out;
+    int32_t out_w, out_h, out_dtype, axis_mask, compute_mean, compute_stddev, fill_padding;
+    float mean[3], stddev[3], scale, shift;
+} orc_normalize_params;
+
+ORC_API int orc_normalize(const uint8_t* arena, const rb200_pointwise_sample* s, int n, const orc_normalize_params* p) {
+    if (!arena || !s || !p || !p->out || n < 0) return RB200_E_INVALID;
+    const int mask = p->axis_mask & 7;
+    const int computes = p->compute_mean || p->compute_stddev;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n; i++) {
+        const rb200_pointwise_sample* q = &s[i];
+        const uint8_t* img = arena + q->src_offset + (size_t)q->roi_y * q->src_stride + (size_t)q->roi_x * 3;
+        const int w = q->roi_w < p->out_w ? q->roi_w : p->out_w;
+        const int h = q->roi_h < p->out_h ? q->roi_h : p->out_h;
+        if (p->fill_padding) {
+            size_t elems = (size_t)3 * p->out_w * p->out_h, esz = p->out_dtype == RB200_FP32 ? 4 : 2;
+            memset((uint8_t*)p->out + (size_t)i * elems * esz, 0, elems * esz);
+        }
+        if (w <= 0 || h <= 0) continue;
+        const int slots = computes ? norm_stat_slots(mask, w, h) : 0;
+        uint64_t* s1 = (uint64_t*)calloc((size_t)(slots > 0 ? slots : 1), sizeof(uint64_t));
+        uint64_t* s2 = (uint64_t*)calloc((size_t)(slots > 0 ? slots : 1), sizeof(uint64_t));
+        if (computes)
+            for (int y = 0; y < h; y++)
+                for (int x = 0; x < w; x++)
+                    for (int c = 0; c < 3; c++) {
+                        uint64_t v = img[(size_t)y * q->src_stride + x * 3 + c];
+                        int k = norm_stat_index(mask, y, x, c, w);
+                        s1[k] += v;
+                        s2[k] += v * v;
+                    }
+        double cnt;
+        switch (mask) {
+            case 1: cnt = h; break;
+            case 2: cnt = w; break;
+            case 3: cnt = (double)w * h; break;
+            case 4: cnt = 3.0; break;
+            case 5: cnt = 3.0 * h; break;
+            case 6: cnt = 3.0 * w; break;
+            default: cnt = 3.0 * w * h;
+        }
+        for (int y = 0; y < h; y++)
+            for (int x = 0; x < w; x++)
+                for (int c = 0; c < 3; c++) {
+                    float mean_f = p->mean[c], std_f = p->stddev[c];
+                    if (computes) {
+                        int k = norm_stat_index(mask, y, x, c, w);
+                        int ch = (mask == 1 || mask == 2 || mask == 3) ? c : 0;
+                        mean_f = p->compute_mean ? (float)((double)s1[k] / cnt) : p->mean[ch];
+                        if (p->compute_stddev) {
+                            double m = (double)mean_f;
+                            double var = ((double)s2[k] - 2.0 * m * (double)s1[k]) / cnt + m * m;
+                            if (!(var > 0.0)) var = 0.0;
+                            std_f = (float)sqrt(var);
+                        } else {
+                            std_f = p->stddev[ch];
+                        }
+                    }
+                    float mult = std_f > 0.f ? p->scale / std_f : 0.f;
+                    float px = (float)img[(size_t)y * q->src_stride + x * 3 + c];
+                    float o = fmaf(px - mean_f, mult, p->shift);
+                    store_elem(p->out, p->out_dtype, (((size_t)i * p->out_h + y) * p->out_w + x) * 3 + c, o);
+                }
+        free(s1);
+        free(s2);
+    }
+    return RB200_OK;
+}
+
+/* Axis permutation of the sample's h x w x 3 window: out dims (d[perm[0]], d[perm[1]], d[perm[2]]), densely packed at
+ * the start of the sample's out_stride-byte slot (rocalTranspose, rocal_api_augmentation.cpp:2349-2378: pure indexing). */
+ORC_API int orc_transpose(const uint8_t* arena, const rb200_pointwise_sample* s, int n, const int32_t* perm, uint8_t* out,
+                          size_t out_stride) {
+    if (!arena || !s || !perm || !out) return RB200_E_INVALID;
+    for (int i = 0; i < n; i++) {
+        const rb200_pointwise_sample* q = &s[i];
+        const uint8_t* img = arena + q->src_offset + (size_t)q->roi_y * q->src_stride + (size_t)q->roi_x * 3;
+        const int d[3] = {q->roi_h, q->roi_w, 3};
+        const int o0 = d[perm[0]], o1 = d[perm[1]], o2 = d[perm[2]];
+        uint8_t* o = out + (size_t)i * out_stride;
+        for (int i0 = 0; i0 < o0; i0++)
+            for (int i1 = 0; i1 < o1; i1++)
+                for (int i2 = 0; i2 < o2; i2++) {
+                    int idx[3];
+                    idx[perm[0]] = i0; idx[perm[1]] = i1; idx[perm[2]] = i2;
+                    o[((size_t)i0 * o1 + i1) * o2 + i2] = img[(size_t)idx[0] * q->src_stride + idx[1] * 3 + idx[2]];
+                }
+    }
+    return RB200_OK;
+}
+
 ORC_API const char* orc_version(void) { return "rocal_b200 oracle 1"; }

@@ -137,6 +137,45 @@ def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None):
     return out
 
 
+class _NormalizeParams(ctypes.Structure):
+    _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+                ("axis_mask", ctypes.c_int32), ("compute_mean", ctypes.c_int32), ("compute_stddev", ctypes.c_int32),
+                ("fill_padding", ctypes.c_int32), ("mean", ctypes.c_float * 3), ("stddev", ctypes.c_float * 3),
+                ("scale", ctypes.c_float), ("shift", ctypes.c_float)]
+
+
+def normalize(arena, samples, out_w, out_h, axis_mask=3, mean=None, stddev=None, scale=1.0, shift=0.0, out_dtype=FP32,
+              fill_padding=True):
+    """orc_normalize: statistics are computed where mean / stddev is None, else per-channel constants. Returns
+    [n][out_h][out_w][3] float32 or float16."""
+    n = len(samples)
+    out = np.zeros((n, out_h, out_w, 3), dtype=_NP[out_dtype])
+    p = _NormalizeParams()
+    p.out = out.ctypes.data
+    p.out_w, p.out_h, p.out_dtype, p.axis_mask = out_w, out_h, out_dtype, axis_mask
+    p.compute_mean, p.compute_stddev = int(mean is None), int(stddev is None)
+    p.fill_padding = 1 if fill_padding else 0
+    for c in range(3):
+        p.mean[c] = float(mean[c]) if mean is not None else 0.0
+        p.stddev[c] = float(stddev[c]) if stddev is not None else 1.0
+    p.scale, p.shift = float(scale), float(shift)
+    lib().orc_normalize.restype = ctypes.c_int
+    rc = lib().orc_normalize(_ptr(arena), _ptr(samples), ctypes.c_int(n), ctypes.byref(p))
+    assert rc == 0
+    return out
+
+
+def transpose(arena, samples, perm, out_stride):
+    """orc_transpose: uint8 [n][out_stride] with every sample's permuted window packed at the start of its slot."""
+    n = len(samples)
+    out = np.zeros((n, out_stride), dtype=np.uint8)
+    pm = np.asarray(perm, dtype=np.int32)
+    lib().orc_transpose.restype = ctypes.c_int
+    rc = lib().orc_transpose(_ptr(arena), _ptr(samples), ctypes.c_int(n), _ptr(pm), _ptr(out), ctypes.c_size_t(out_stride))
+    assert rc == 0
+    return out
+
+
 def _box_call(fn, boxes, labels, offsets, anchors, criteria, means, stds, offset, scale):
     n = len(offsets) - 1
     a = anchors.shape[0]

@@ -49,6 +49,19 @@ class BoxMatcherParams(ctypes.Structure):
                 ("low_threshold", ctypes.c_float), ("allow_low_quality_matches", ctypes.c_int32)]
 
 
+class NormalizeParams(ctypes.Structure):
+    _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+                ("axis_mask", ctypes.c_int32), ("compute_mean", ctypes.c_int32), ("compute_stddev", ctypes.c_int32),
+                ("fill_padding", ctypes.c_int32), ("mean", ctypes.c_float * 3), ("stddev", ctypes.c_float * 3),
+                ("scale", ctypes.c_float), ("shift", ctypes.c_float)]
+
+
+lib.rb200k_normalize_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
+lib.rb200k_normalize_scratch_bytes.restype = ctypes.c_size_t
+lib.rb200k_normalize.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(NormalizeParams), c_void_p, ctypes.c_size_t, c_void_p]
+lib.rb200k_normalize.restype = c_int
+lib.rb200k_transpose.argtypes = [c_void_p, c_void_p, c_int, ctypes.POINTER(ctypes.c_int32), c_void_p, ctypes.c_size_t, c_void_p]
+lib.rb200k_transpose.restype = c_int
 lib.rb200k_resample.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(ResampleParams), c_void_p]
 lib.rb200k_resample.restype = c_int
 lib.rb200k_pointwise.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(PointwiseParams), c_void_p]

@@ -445,7 +445,10 @@ __device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t 
 }
 
 template <typename OutT, int LAYOUT, int COLOR_OP>
-__global__ void __launch_bounds__(256) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
+// The ColorTwist instantiations are bound by latency (the CTA waits once for its staged rows) as much as by issue:
+// five resident CTAs per SM (48 registers) measured 37 / 27 us per 256-image launch (exact / fast arithmetic)
+// against 51 / 33 us at the register count the compiler picks on its own (122 / 70: two or three CTAs per SM).
+__global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP == RB200_COLOR_TWIST) ? 5 : 1) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
                                                             const rb200_pointwise_sample* __restrict__ samples,
                                                             const PointwiseLaunch L) {
     // Layout: mbarrier (16 bytes) | rcp[256] | staged source rows (th x pitch)

@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 from . import tables as T
-from ._lib import (BoxEncoderParams, BoxMatcherParams, PointwiseParams, ResampleParams, WarpParams, check, lib)
+from ._lib import (BoxEncoderParams, BoxMatcherParams, NormalizeParams, PointwiseParams, ResampleParams, WarpParams, check, lib)
 
 _TORCH_DTYPE = {T.FP32: torch.float32, T.FP16: torch.float16, T.UINT8: torch.uint8}
 
@@ -156,4 +156,53 @@ def box_iou_match(boxes, box_offsets, anchors, high_threshold, low_threshold, al
     p.allow_low_quality_matches = 1 if allow_low_quality_matches else 0
     check(lib.rb200k_box_iou_match(boxes.data_ptr(), box_offsets.data_ptr(), n, int(max_boxes), ctypes.byref(p),
                                    out.data_ptr(), _stream_ptr(stream)), "rb200k_box_iou_match")
+    return out
+
+
+def normalize_scratch_bytes(n, max_w, max_h, axis_mask):
+    return int(lib.rb200k_normalize_scratch_bytes(int(n), int(max_w), int(max_h), int(axis_mask)))
+
+
+def _normalize_params(out, out_w, out_h, out_dtype, axis_mask, mean, stddev, scale, shift, fill_padding):
+    p = NormalizeParams()
+    p.out = out.data_ptr()
+    p.out_w, p.out_h, p.out_dtype, p.axis_mask = out_w, out_h, out_dtype, int(axis_mask)
+    p.compute_mean, p.compute_stddev = int(mean is None), int(stddev is None)
+    p.fill_padding = 1 if fill_padding else 0
+    for c in range(3):
+        p.mean[c] = float(mean[c]) if mean is not None else 0.0
+        p.stddev[c] = float(stddev[c]) if stddev is not None else 1.0
+    p.scale, p.shift = float(scale), float(shift)
+    return p
+
+
+def normalize(arena, samples, out_w, out_h, axis_mask=3, mean=None, stddev=None, scale=1.0, shift=0.0, out_dtype=T.FP32,
+              fill_padding=True, out=None, d_samples=None, scratch=None, stream=None):
+    """rb200k_normalize: uint8 HWC windows (POINTWISE_SAMPLE table) -> [n][out_h][out_w][3] float32 / float16.
+    mean / stddev None = computed over the axes of axis_mask (bit 0 height, 1 width, 2 channel). `scratch`: a uint8
+    CUDA tensor of at least normalize_scratch_bytes(...) bytes (allocated here when None and needed)."""
+    n = len(samples)
+    out = _alloc_out(n, out_w, out_h, out_dtype, T.NHWC, arena.device, out)
+    if d_samples is None:
+        d_samples = to_device_table(samples, arena.device)
+    p = _normalize_params(out, out_w, out_h, out_dtype, axis_mask, mean, stddev, scale, shift, fill_padding)
+    need = normalize_scratch_bytes(n, out_w, out_h, axis_mask) if (mean is None or stddev is None) else 0
+    if scratch is None and need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=arena.device)
+    check(lib.rb200k_normalize(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n, ctypes.byref(p),
+                               scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
+                               _stream_ptr(stream)), "rb200k_normalize")
+    return out
+
+
+def transpose(arena, samples, perm, out_stride, out=None, d_samples=None, stream=None):
+    """rb200k_transpose: uint8 [n][out_stride], every sample's permuted window packed at the start of its slot."""
+    n = len(samples)
+    if out is None:
+        out = torch.zeros((n, out_stride), dtype=torch.uint8, device=arena.device)
+    if d_samples is None:
+        d_samples = to_device_table(samples, arena.device)
+    pm = (ctypes.c_int32 * 3)(*[int(v) for v in perm])
+    check(lib.rb200k_transpose(arena.data_ptr(), d_samples.data_ptr(), n, pm, out.data_ptr(), int(out_stride), _stream_ptr(stream)),
+          "rb200k_transpose")
     return out
