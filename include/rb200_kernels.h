@@ -298,6 +298,30 @@ RB200_API int rb200k_normalize(const uint8_t* arena, const rb200_pointwise_sampl
                      const rb200_pointwise_sample* h_samples, int n, const rb200_normalize_params* params,
                      void* scratch, size_t scratch_bytes, void* stream);
 
+/* rb200k_normalize without a scratch argument: the statistics are accumulated in a fixed 1 MiB array that is part of
+ * the library itself (65 536 slots of 16 bytes; every GPU that loads the library holds it until the process exits).
+ * The entry point has no counterpart in the reference. It is for callers that cannot hand rb200k_normalize a scratch
+ * buffer: a host program that binds this C ABI from a language without a CUDA binding of its own (cgo, JNI, ctypes)
+ * has no way to create device memory, and a loader that runs beside a framework whose allocator has already claimed
+ * the whole device may find that an allocation of its own fails or stalls. Nothing is allocated here or further down:
+ * no cudaMalloc, no cudaFree, no allocating library routine; the call enqueues a clear of the slots it uses, the same
+ * kernels as rb200k_normalize, and returns.
+ *   limit   n x (statistics per sample) <= 65 536, where the statistics per sample follow axis_mask and the OUTPUT
+ *           size: 3 (mask 3), 1 (mask 7), 3*out_w (mask 1), 3*out_h (mask 2), out_w (5), out_h (6), out_w*out_h (4).
+ *           A larger batch is refused with RB200_E_LIMIT and a message that names both numbers. When neither statistic
+ *           is computed the array is not touched and no limit applies.
+ *   set-up  the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *           current) and keeps it; make that first call before any stream capture is started on the device. Devices
+ *           0..63 are supported.
+ *   sharing every call on a device uses the same array, and the array keeps what the last call left in it (each call
+ *           clears the slots it is about to use). Two calls whose GPU work can overlap - different streams, or
+ *           different host threads - race on it and corrupt each other's statistics: issue them on one stream, or
+ *           order them with events.
+ * Results are identical to rb200k_normalize's. */
+RB200_API int rb200k_normalize_static(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                            const rb200_pointwise_sample* h_samples, int n, const rb200_normalize_params* params,
+                            void* stream);
+
 /* Axis permutation of uint8 HWC images: out dims = (d[perm[0]], d[perm[1]], d[perm[2]]) with d = (h, w, 3) of the
  * sample's window; every sample's result is written densely at the start of its out_stride-byte slot. flip_* of the
  * sample table are ignored.

@@ -339,6 +339,50 @@ extern "C" int rb200k_normalize(const uint8_t* arena, const rb200_pointwise_samp
     return RB200_OK;
 }
 
+// ---- rb200k_normalize_static: the same operator with its statistics scratch inside the library image ----
+//
+// 65 536 slots of 16 bytes = 1 MiB of device memory, held by every GPU that loads the library until the process exits.
+// In host code the array's name only stands for the device object: the address the kernels need is obtained once per
+// device with cudaGetSymbolAddress while that device is current, and cached.
+namespace rb200 {
+constexpr size_t kStaticStatSlots = 65536;
+static __device__ __align__(256) StatSlot g_static_stats[kStaticStatSlots];
+static StatSlot* g_static_stats_ptr[64] = {nullptr};     // per device ordinal; written once, then only read
+}  // namespace rb200
+
+extern "C" int rb200k_normalize_static(const uint8_t* arena, const rb200_pointwise_sample* samples,
+                                       const rb200_pointwise_sample* h_samples, int n, const rb200_normalize_params* p,
+                                       void* stream_v) {
+    if (!p) {
+        set_error("rb200k_normalize_static: null parameter block");
+        return RB200_E_INVALID;
+    }
+    const bool computes = p->compute_mean || p->compute_stddev;
+    if (!computes || n <= 0) return rb200k_normalize(arena, samples, h_samples, n, p, nullptr, 0, stream_v);
+    const size_t slots = (size_t)n * (size_t)stat_slots(p->axis_mask & 7, p->out_w > 0 ? p->out_w : 0, p->out_h > 0 ? p->out_h : 0);
+    if (slots > kStaticStatSlots) {
+        set_error("rb200k_normalize_static: this batch needs %zu statistic slots (%d samples x %zu values each for axis_mask %d "
+                  "on a %d x %d output), the built-in scratch holds %zu; use rb200k_normalize with scratch of your own",
+                  slots, n, slots / (size_t)n, p->axis_mask, p->out_w, p->out_h, kStaticStatSlots);
+        return RB200_E_LIMIT;
+    }
+    int dev = -1;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) {
+        set_error("rb200k_normalize_static: device ordinal %d is beyond the 64 this entry point keeps an address for", dev);
+        return RB200_E_LIMIT;
+    }
+    StatSlot* ptr = g_static_stats_ptr[dev];
+    if (!ptr) {
+        // first call on this device: resolve the array's device address (the device is current)
+        rc = check_cuda(cudaGetSymbolAddress((void**)&ptr, g_static_stats), "cudaGetSymbolAddress(built-in normalize scratch)");
+        if (rc) return rc;
+        g_static_stats_ptr[dev] = ptr;
+    }
+    return rb200k_normalize(arena, samples, h_samples, n, p, ptr, kStaticStatSlots * sizeof(StatSlot), stream_v);
+}
+
 extern "C" int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_sample* samples, int n, const int32_t perm[3],
                                 uint8_t* out, size_t out_stride, void* stream_v) {
     if (n == 0) return RB200_OK;
