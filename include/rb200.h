@@ -263,6 +263,17 @@ RB200_API rb200_tensor rb200_color_temp(rb200_context ctx, rb200_tensor in, int 
 /* rocalBlend: in*ratio + in2*(1 - ratio) per pixel, rounded; both inputs have the same maximum size. */
 RB200_API rb200_tensor rb200_blend(rb200_context ctx, rb200_tensor in, rb200_tensor in2, int is_output, rb200_param ratio,
                                    int out_layout, int out_dtype);
+/* rocalNormalize (rocAL/include/api/rocal_api_augmentation.h:1294): out = scale * (x - mean) / std_dev + shift on the
+ * uint8 NHWC input, FP32 or FP16 output of the same shape. axes: 0 = height, 1 = width, 2 = channel - what a computed
+ * statistic is taken over; num_mean / num_std = 0 asks for that statistic to be computed per sample, else one value or
+ * one per channel. */
+RB200_API rb200_tensor rb200_normalize(rb200_context ctx, rb200_tensor in, const unsigned* axes, unsigned num_axes,
+                                       const float* mean, unsigned num_mean, const float* std_dev, unsigned num_std,
+                                       int is_output, float scale, float shift, int out_dtype);
+/* rocalTranspose (rocal_api_augmentation.h:1338): perm over (height, width, channel); uint8 output whose dims are
+ * {batch, d[perm[0]], d[perm[1]], d[perm[2]]} of the input's maximum shape, every sample at the origin of its slot. */
+RB200_API rb200_tensor rb200_transpose(rb200_context ctx, rb200_tensor in, const unsigned* perm, unsigned num_perm,
+                                       int is_output, int out_layout);
 RB200_API rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout,
                                  int out_dtype);
 RB200_API rb200_tensor rb200_saturation(rb200_context ctx, rb200_tensor in, int is_output, rb200_param sat,

@@ -322,12 +322,14 @@ RB200_API int rb200k_normalize_static(const uint8_t* arena, const rb200_pointwis
                             const rb200_pointwise_sample* h_samples, int n, const rb200_normalize_params* params,
                             void* stream);
 
-/* Axis permutation of uint8 HWC images: out dims = (d[perm[0]], d[perm[1]], d[perm[2]]) with d = (h, w, 3) of the
- * sample's window; every sample's result is written densely at the start of its out_stride-byte slot. flip_* of the
- * sample table are ignored.
+/* Axis permutation of uint8 HWC images: sample i's window, d = (h, w, 3), becomes an array of extents
+ * (d[perm[0]], d[perm[1]], d[perm[2]]) at the origin of its slot out[i][out_dims[0]][out_dims[1]][out_dims[2]] (the
+ * maximum shape of the output tensor, the reference's padded-tensor convention); elements of the slot outside the
+ * sample's extents are left untouched, a window larger than the slot is clipped. flip_* of the sample table are
+ * ignored.
  * replaces: vxExtRppTranspose, rocalTranspose (rocAL/include/api/rocal_api_augmentation.h:1338). */
 RB200_API int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_sample* samples, int n, const int32_t perm[3],
-                     uint8_t* out, size_t out_stride, void* stream);
+                     uint8_t* out, const int32_t out_dims[3], void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Overlapping launches

@@ -355,6 +355,13 @@ RB200_ROCAL RocalTensor ROCAL_API_CALL rocalSaturation /* [826] */ (
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalSaturationFixed /* [842] */ (
     RocalContext context, RocalTensor input, float saturation, bool is_output,
     RocalTensorLayout output_layout = ROCAL_NONE, RocalTensorOutputType output_datatype = ROCAL_UINT8);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalNormalize /* [1294] */ (
+    RocalContext context, RocalTensor input, std::vector<unsigned>& axes, std::vector<float>& mean,
+    std::vector<float>& std_dev, bool is_output, float scale = 1.0, float shift = 0.0,
+    RocalTensorOutputType output_datatype = ROCAL_FP32);
+RB200_ROCAL RocalTensor ROCAL_API_CALL rocalTranspose /* [1338] */ (
+    RocalContext context, RocalTensor input, std::vector<unsigned> perm, bool is_output,
+    RocalTensorLayout output_layout = ROCAL_NONE);
 RB200_ROCAL RocalTensor ROCAL_API_CALL rocalColorTwist /* [878] */ (
     RocalContext context, RocalTensor input, bool is_output, RocalFloatParam alpha = NULL, RocalFloatParam beta = NULL,
     RocalFloatParam hue = NULL, RocalFloatParam sat = NULL, RocalTensorLayout output_layout = ROCAL_NONE,

@@ -757,23 +757,25 @@ ORC_API int orc_normalize(const uint8_t* arena, const rb200_pointwise_sample* s,
     return RB200_OK;
 }
 
-/* Axis permutation of the sample's h x w x 3 window: out dims (d[perm[0]], d[perm[1]], d[perm[2]]), densely packed at
- * the start of the sample's out_stride-byte slot (rocalTranspose, rocal_api_augmentation.cpp:2349-2378: pure indexing). */
+/* Axis permutation of the sample's h x w x 3 window: extents (d[perm[0]], d[perm[1]], d[perm[2]]) at the origin of the
+ * sample's slot of out_dims[0] x out_dims[1] x out_dims[2] bytes (rocalTranspose, rocal_api_augmentation.cpp:2349-2378:
+ * the output tensor's maximum shape is the permuted maximum shape of the input; pure indexing). */
 ORC_API int orc_transpose(const uint8_t* arena, const rb200_pointwise_sample* s, int n, const int32_t* perm, uint8_t* out,
-                          size_t out_stride) {
-    if (!arena || !s || !perm || !out) return RB200_E_INVALID;
+                          const int32_t* out_dims) {
+    if (!arena || !s || !perm || !out || !out_dims) return RB200_E_INVALID;
+    const int m0 = out_dims[0], m1 = out_dims[1], m2 = out_dims[2];
     for (int i = 0; i < n; i++) {
         const rb200_pointwise_sample* q = &s[i];
         const uint8_t* img = arena + q->src_offset + (size_t)q->roi_y * q->src_stride + (size_t)q->roi_x * 3;
         const int d[3] = {q->roi_h, q->roi_w, 3};
         const int o0 = d[perm[0]], o1 = d[perm[1]], o2 = d[perm[2]];
-        uint8_t* o = out + (size_t)i * out_stride;
-        for (int i0 = 0; i0 < o0; i0++)
-            for (int i1 = 0; i1 < o1; i1++)
-                for (int i2 = 0; i2 < o2; i2++) {
+        uint8_t* o = out + (size_t)i * m0 * m1 * m2;
+        for (int i0 = 0; i0 < o0 && i0 < m0; i0++)
+            for (int i1 = 0; i1 < o1 && i1 < m1; i1++)
+                for (int i2 = 0; i2 < o2 && i2 < m2; i2++) {
                     int idx[3];
                     idx[perm[0]] = i0; idx[perm[1]] = i1; idx[perm[2]] = i2;
-                    o[((size_t)i0 * o1 + i1) * o2 + i2] = img[(size_t)idx[0] * q->src_stride + idx[1] * 3 + idx[2]];
+                    o[((size_t)i0 * m1 + i1) * m2 + i2] = img[(size_t)idx[0] * q->src_stride + idx[1] * 3 + idx[2]];
                 }
     }
     return RB200_OK;

@@ -165,13 +165,14 @@ def normalize(arena, samples, out_w, out_h, axis_mask=3, mean=None, stddev=None,
     return out
 
 
-def transpose(arena, samples, perm, out_stride):
-    """orc_transpose: uint8 [n][out_stride] with every sample's permuted window packed at the start of its slot."""
+def transpose(arena, samples, perm, out_dims):
+    """orc_transpose: uint8 [n][out_dims...] with every sample's permuted window at the origin of its slot."""
     n = len(samples)
-    out = np.zeros((n, out_stride), dtype=np.uint8)
+    out = np.zeros((n,) + tuple(int(v) for v in out_dims), dtype=np.uint8)
     pm = np.asarray(perm, dtype=np.int32)
+    od = np.asarray(out_dims, dtype=np.int32)
     lib().orc_transpose.restype = ctypes.c_int
-    rc = lib().orc_transpose(_ptr(arena), _ptr(samples), ctypes.c_int(n), _ptr(pm), _ptr(out), ctypes.c_size_t(out_stride))
+    rc = lib().orc_transpose(_ptr(arena), _ptr(samples), ctypes.c_int(n), _ptr(pm), _ptr(out), _ptr(od))
     assert rc == 0
     return out
 

@@ -106,6 +106,9 @@ ssd_random_crop = _proto("rb200_ssd_random_crop", _P, _P, _P, c_int, c_int, c_in
 flip = _proto("rb200_flip", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 brightness = _proto("rb200_brightness", _P, _P, _P, c_int, _P, _P, c_int, c_int)
 contrast = _proto("rb200_contrast", _P, _P, _P, c_int, _P, _P, c_int, c_int)
+normalize = _proto("rb200_normalize", _P, _P, _P, ctypes.POINTER(ctypes.c_uint), ctypes.c_uint, ctypes.POINTER(ctypes.c_float), ctypes.c_uint,
+                   ctypes.POINTER(ctypes.c_float), ctypes.c_uint, c_int, ctypes.c_float, ctypes.c_float, c_int)
+transpose = _proto("rb200_transpose", _P, _P, _P, ctypes.POINTER(ctypes.c_uint), ctypes.c_uint, c_int, c_int)
 hue = _proto("rb200_hue", _P, _P, _P, c_int, _P, c_int, c_int)
 blend = _proto("rb200_blend", _P, _P, _P, _P, c_int, _P, c_int, c_int)
 exposure = _proto("rb200_exposure", _P, _P, _P, c_int, _P, c_int, c_int)

@@ -60,7 +60,7 @@ lib.rb200k_normalize_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
 lib.rb200k_normalize_scratch_bytes.restype = ctypes.c_size_t
 lib.rb200k_normalize.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(NormalizeParams), c_void_p, ctypes.c_size_t, c_void_p]
 lib.rb200k_normalize.restype = c_int
-lib.rb200k_transpose.argtypes = [c_void_p, c_void_p, c_int, ctypes.POINTER(ctypes.c_int32), c_void_p, ctypes.c_size_t, c_void_p]
+lib.rb200k_transpose.argtypes = [c_void_p, c_void_p, c_int, ctypes.POINTER(ctypes.c_int32), c_void_p, ctypes.POINTER(ctypes.c_int32), c_void_p]
 lib.rb200k_transpose.restype = c_int
 lib.rb200k_resample.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.POINTER(ResampleParams), c_void_p]
 lib.rb200k_resample.restype = c_int

@@ -309,6 +309,7 @@ Pipeline::~Pipeline() {
     }
     if (_d_anchors) cudaFree(_d_anchors);
     if (_d_match_anchors) cudaFree(_d_match_anchors);
+    if (_norm_scratch) cudaFree(_norm_scratch);
     if (_d_boxes) cudaFree(_d_boxes);
     if (_d_labels) cudaFree(_d_labels);
     if (_d_offsets) cudaFree(_d_offsets);
@@ -666,6 +667,14 @@ void Pipeline::plan() {
                 st.kind = Step::WARP;
                 st.warp = (int)k;
                 break;
+            case NodeKind::NORMALIZE:
+                st.kind = Step::NORMALIZE;
+                st.node = (int)k;
+                break;
+            case NodeKind::TRANSPOSE:
+                st.kind = Step::TRANSPOSE;
+                st.node = (int)k;
+                break;
             default:
                 st.kind = Step::POINTWISE;
                 st.color = (int)k;
@@ -732,6 +741,14 @@ void Pipeline::verify() {
         }
         if (_box_matcher) RB200_CUDA(cudaMalloc((void**)&s.d_matches, _batch * (size_t)_match.num_anchors * sizeof(int)));
     }
+    for (const Step& st : _steps) {
+        if (st.kind != Step::NORMALIZE) continue;
+        const Node& nd = _nodes[st.node];
+        if (!nd.stat_mean.empty() && !nd.stat_std.empty()) continue;       // nothing is computed
+        TensorImpl* out = _tensors[st.out_tensor].get();
+        _norm_scratch_bytes = std::max(_norm_scratch_bytes, rb200k_normalize_scratch_bytes((int)_batch, out->max_w, out->max_h, nd.axis_mask));
+    }
+    if (_norm_scratch_bytes) RB200_CUDA(cudaMalloc(&_norm_scratch, _norm_scratch_bytes));
     for (int k = 0; k < 2; k++) RB200_CUDA(cudaEventCreateWithFlags(&_arena_free[k], cudaEventDisableTiming));
     if (_box_matcher) {
         RB200_CUDA(cudaMalloc((void**)&_d_match_anchors, _match_anchors.size() * sizeof(float)));
@@ -1366,7 +1383,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                 consumers++;
                 // kernels that fetch every tap on its own (affine gathers, the triangular filter) would cross
                 // the link once per tap
-                gather = gather || st.kind == Step::WARP ||
+                gather = gather || st.kind == Step::WARP || st.kind == Step::NORMALIZE || st.kind == Step::TRANSPOSE ||
                          (st.kind == Step::RESAMPLE && _nodes[st.resize].interpolation != RB200_INTERP_BILINEAR);
             }
         }
@@ -1451,6 +1468,17 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
                         q.mirror = (ma.size() == n ? ma[i] : R.mirror->get()) ? 1 : 0;
                     }
                 }
+            }
+        } else if (st.kind == Step::NORMALIZE || st.kind == Step::TRANSPOSE) {
+            auto* tab = reinterpret_cast<rb200_pointwise_sample*>(h_tab + k * n * 64);
+            for (size_t i = 0; i < n; i++) {
+                SampleView v = view_of(st.in_tensor, i, base);
+                rb200_pointwise_sample& q = tab[i];
+                std::memset(&q, 0, sizeof(q));
+                q.src_offset = v.offset;
+                q.src_stride = v.stride;
+                q.roi_w = in->roi_w[i];
+                q.roi_h = in->roi_h[i];
             }
         } else if (st.kind == Step::POINTWISE) {
             auto* tab = reinterpret_cast<rb200_pointwise_sample*>(h_tab + k * n * 64);
@@ -1614,6 +1642,30 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             rc = probe_cycles ? rb200k_pointwise_probe(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk,
                                                        (int)n, &p, _stream, probe_cycles, probe_skip)
                               : rb200k_pointwise(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p, _stream);
+        } else if (st.kind == Step::NORMALIZE) {
+            const Node& nd = _nodes[st.node];
+            rb200_normalize_params p{};
+            p.out = out_ptr;
+            p.out_w = out->max_w;
+            p.out_h = out->max_h;
+            p.out_dtype = out_dtype;
+            p.axis_mask = nd.axis_mask;
+            p.compute_mean = nd.stat_mean.empty() ? 1 : 0;
+            p.compute_stddev = nd.stat_std.empty() ? 1 : 0;
+            p.fill_padding = 1;
+            for (int c = 0; c < 3; c++) {
+                p.mean[c] = nd.stat_mean.empty() ? 0.f : nd.stat_mean[std::min<size_t>(c, nd.stat_mean.size() - 1)];
+                p.stddev[c] = nd.stat_std.empty() ? 1.f : nd.stat_std[std::min<size_t>(c, nd.stat_std.size() - 1)];
+            }
+            p.scale = nd.stat_scale;
+            p.shift = nd.stat_shift;
+            rc = rb200k_normalize(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p,
+                                  _norm_scratch, _norm_scratch_bytes, _stream);
+        } else if (st.kind == Step::TRANSPOSE) {
+            const Node& nd = _nodes[st.node];
+            const int32_t od[3] = {(int32_t)out->custom_dims[1], (int32_t)out->custom_dims[2], (int32_t)out->custom_dims[3]};
+            RB200_CUDA(cudaMemsetAsync(out_ptr, 0, out->data_size(), _stream));
+            rc = rb200k_transpose(base, (const rb200_pointwise_sample*)d_tab, (int)n, nd.perm, (uint8_t*)out_ptr, od, _stream);
         } else {
             rb200_warp_params p{};
             p.out = out_ptr;

@@ -35,7 +35,8 @@ namespace rb200 {
 
 enum class NodeKind {
     RESIZE, RESIZE_CROP_MIRROR, RESIZE_MIRROR_NORMALIZE, CROP, CROP_MIRROR_NORMALIZE, SSD_RANDOM_CROP, FLIP,
-    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, EXPOSURE, GAMMA, COLOR_TEMP, BLEND, WARP_AFFINE, ROTATE
+    BRIGHTNESS, CONTRAST, HUE, SATURATION, COLOR_TWIST, EXPOSURE, GAMMA, COLOR_TEMP, BLEND, WARP_AFFINE, ROTATE,
+    NORMALIZE, TRANSPOSE
 };
 
 // Crop window rules of RocalCropParam::fill_crop_dims (source/parameters/parameter_rocal_crop.cpp:49-85) and, for
@@ -75,6 +76,12 @@ struct Node {
     Parameter<float>* angle = nullptr;
     std::vector<float> next_affine;    // [n][6] of the next batch (extension)
     std::vector<float> affine_v;       // [n][6] packed {x0,y0,x1,y1,o0,o1}
+    // Normalize: axes reduced for computed statistics (bit 0 height, 1 width, 2 channel), given per-channel
+    // statistics (empty = computed), scale and shift; Transpose: permutation of (h, w, c)
+    int axis_mask = 0;
+    std::vector<float> stat_mean, stat_std;
+    float stat_scale = 1.f, stat_shift = 0.f;
+    int perm[3] = {0, 1, 2};
     int ssd_attempts = 20;
     unsigned batch_counter = 0;        // batches this node has seen (seeds the SSD crop sampler)
     // fusion
@@ -184,12 +191,13 @@ struct InputBatch {
 };
 
 struct Step {
-    enum Kind { RESAMPLE, POINTWISE, WARP } kind;
+    enum Kind { RESAMPLE, POINTWISE, WARP, NORMALIZE, TRANSPOSE } kind;
     int in_tensor, out_tensor;
     int in2_tensor = -1;                         // POINTWISE with a second source (blend)
     int pre_crop = -1, resize = -1, post = -1;   // RESAMPLE: node indices
     int window = -1, color = -1, flip = -1;      // POINTWISE
     int warp = -1;                               // WARP
+    int node = -1;                               // NORMALIZE / TRANSPOSE
 };
 
 struct Slot {
@@ -412,6 +420,8 @@ class Pipeline {
     std::atomic<unsigned long long> _t_load{0}, _t_decode{0}, _t_process{0}, _t_transfer{0};
     std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
     int _upload_mode = UPLOAD_ZERO_COPY;
+    void* _norm_scratch = nullptr;                        // statistics scratch shared by the Normalize steps
+    size_t _norm_scratch_bytes = 0;
     int _arith = RB200_ARITH_EXACT;                       // arithmetic of the colour operators (rb200_set_arithmetic)
     std::atomic<unsigned long long> _probe_wait_cycles{0};  // self-test: non-zero = launch through the probe entries
     std::atomic<int> _probe_skip_row{-1};

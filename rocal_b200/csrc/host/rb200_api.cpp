@@ -1013,6 +1013,58 @@ rb200_tensor rb200_blend(rb200_context ctx, rb200_tensor in, rb200_tensor in2, i
     API_END
 }
 
+// rocalNormalize (rocal_api_augmentation.h:1294, rocal_api_augmentation.cpp:2288-2308): axes of the per-sample
+// tensor (0 = height, 1 = width, 2 = channel for the NHWC images of this pipeline) whose extent is reduced when a
+// statistic is computed; an empty mean / std_dev list asks for that statistic to be computed (node_normalize.cpp:34-41).
+rb200_tensor rb200_normalize(rb200_context ctx, rb200_tensor in, const unsigned* axes, unsigned num_axes, const float* mean,
+                             unsigned num_mean, const float* std_dev, unsigned num_std, int is_output, float scale, float shift,
+                             int out_dtype) {
+    API_BEGIN
+    Node nd;
+    nd.kind = NodeKind::NORMALIZE;
+    for (unsigned k = 0; k < num_axes; k++) {
+        if (!axes || axes[k] > 2) RB200_THROW("rocalNormalize: axes are 0 (height), 1 (width) or 2 (channel)");
+        nd.axis_mask |= 1 << axes[k];
+    }
+    if (num_mean) nd.stat_mean.assign(mean, mean + num_mean);
+    if (num_std) nd.stat_std.assign(std_dev, std_dev + num_std);
+    if ((num_mean == 0 || num_std == 0) && nd.axis_mask == 0)
+        RB200_THROW("rocalNormalize: axes must name what a computed mean / standard deviation is taken over");
+    if ((num_mean && num_mean != 1 && num_mean != 3) || (num_std && num_std != 1 && num_std != 3))
+        RB200_THROW("rocalNormalize: mean and std_dev hold one value or one per channel");
+    nd.stat_scale = scale;
+    nd.stat_shift = shift;
+    if (out_dtype != ROCAL_FP32 && out_dtype != ROCAL_FP16) RB200_THROW("rocalNormalize: the output is FP32 or FP16");
+    return finish(p, std::move(nd), T(in), (unsigned)T(in)->max_w, (unsigned)T(in)->max_h, ROCAL_NHWC, out_dtype, is_output);
+    API_END
+}
+
+// rocalTranspose (rocal_api_augmentation.h:1338, rocal_api_augmentation.cpp:2349-2378): perm over the per-sample axes
+// (height, width, channel); the output's maximum shape is the permuted maximum shape of the input.
+rb200_tensor rb200_transpose(rb200_context ctx, rb200_tensor in, const unsigned* perm, unsigned num_perm, int is_output,
+                             int out_layout) {
+    API_BEGIN
+    if (!perm || num_perm != 3) RB200_THROW("Transpose permutation must match with the input dims");
+    Node nd;
+    nd.kind = NodeKind::TRANSPOSE;
+    int seen = 0;
+    for (int k = 0; k < 3; k++) {
+        if (perm[k] > 2) RB200_THROW("rocalTranspose: perm holds 0, 1 and 2");
+        nd.perm[k] = (int)perm[k];
+        seen |= 1 << perm[k];
+    }
+    if (seen != 7) RB200_THROW("rocalTranspose: perm is not a permutation");
+    TensorImpl* tin = T(in);
+    rb200_tensor out = finish(p, std::move(nd), tin, (unsigned)tin->max_w, (unsigned)tin->max_h,
+                              out_layout == ROCAL_NONE ? ROCAL_NHWC : out_layout, ROCAL_UINT8, is_output);
+    if (out) {
+        const size_t d[3] = {(size_t)tin->max_h, (size_t)tin->max_w, 3};
+        T(out)->custom_dims = {(size_t)tin->n, d[perm[0]], d[perm[1]], d[perm[2]]};
+    }
+    return out;
+    API_END
+}
+
 rb200_tensor rb200_hue(rb200_context ctx, rb200_tensor in, int is_output, rb200_param hue, int out_layout, int out_dtype) {
     API_BEGIN
     Node nd;

@@ -350,6 +350,14 @@ RocalTensor ROCAL_API_CALL rocalSaturationFixed(RocalContext c, RocalTensor in, 
                                                 RocalTensorOutputType t) {
     return RT(rb200_saturation(c, in, out, rb200_create_float_parameter(s), (int)l, (int)t));
 }
+RocalTensor ROCAL_API_CALL rocalNormalize(RocalContext c, RocalTensor in, std::vector<unsigned>& axes, std::vector<float>& mean,
+                                          std::vector<float>& std_dev, bool out, float scale, float shift, RocalTensorOutputType t) {
+    return RT(rb200_normalize(c, in, axes.data(), (unsigned)axes.size(), mean.data(), (unsigned)mean.size(), std_dev.data(),
+                              (unsigned)std_dev.size(), out, scale, shift, (int)t));
+}
+RocalTensor ROCAL_API_CALL rocalTranspose(RocalContext c, RocalTensor in, std::vector<unsigned> perm, bool out, RocalTensorLayout l) {
+    return RT(rb200_transpose(c, in, perm.data(), (unsigned)perm.size(), out, (int)l));
+}
 RocalTensor ROCAL_API_CALL rocalColorTwist(RocalContext c, RocalTensor in, bool out, RocalFloatParam a, RocalFloatParam b, RocalFloatParam h,
                                            RocalFloatParam s, RocalTensorLayout l, RocalTensorOutputType t) {
     return RT(rb200_color_twist(c, in, out, a, b, h, s, (int)l, (int)t));

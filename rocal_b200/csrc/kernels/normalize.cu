@@ -250,21 +250,22 @@ __global__ void __launch_bounds__(256) normalize_apply_kernel(const uint8_t* __r
 
 __global__ void __launch_bounds__(256) transpose_kernel(const uint8_t* __restrict__ arena,
                                                          const rb200_pointwise_sample* __restrict__ samples, int p0, int p1,
-                                                         int p2, uint8_t* __restrict__ out, size_t out_stride) {
+                                                         int p2, uint8_t* __restrict__ out, int m0, int m1, int m2) {
     const int n = blockIdx.y;
     const rb200_pointwise_sample s = samples[n];
     const uint8_t* img = arena + s.src_offset + (size_t)s.roi_y * s.src_stride + (size_t)s.roi_x * 3;
     const int d[3] = {s.roi_h, s.roi_w, 3};
     const int o0 = d[p0], o1 = d[p1], o2 = d[p2];
     const size_t total = (size_t)o0 * o1 * o2;
-    uint8_t* o = out + (size_t)n * out_stride;
+    uint8_t* o = out + (size_t)n * m0 * m1 * m2;
     for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
         const int i2 = (int)(e % o2), i1 = (int)((e / o2) % o1), i0 = (int)(e / ((size_t)o2 * o1));
+        if (i0 >= m0 || i1 >= m1 || i2 >= m2) continue;
         int idx[3];
         idx[p0] = i0;
         idx[p1] = i1;
         idx[p2] = i2;
-        o[e] = img[(size_t)idx[0] * s.src_stride + idx[1] * 3 + idx[2]];
+        o[((size_t)i0 * m1 + i1) * m2 + i2] = img[(size_t)idx[0] * s.src_stride + idx[1] * 3 + idx[2]];
     }
 }
 
@@ -384,9 +385,9 @@ extern "C" int rb200k_normalize_static(const uint8_t* arena, const rb200_pointwi
 }
 
 extern "C" int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_sample* samples, int n, const int32_t perm[3],
-                                uint8_t* out, size_t out_stride, void* stream_v) {
+                                uint8_t* out, const int32_t out_dims[3], void* stream_v) {
     if (n == 0) return RB200_OK;
-    if (!arena || !samples || !perm || !out || n < 0) {
+    if (!arena || !samples || !perm || !out || !out_dims || n < 0 || out_dims[0] <= 0 || out_dims[1] <= 0 || out_dims[2] <= 0) {
         set_error("rb200k_transpose: null pointer");
         return RB200_E_INVALID;
     }
@@ -397,7 +398,8 @@ extern "C" int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_samp
     }
     if (seen != 7) { set_error("rb200k_transpose: perm is not a permutation of 0, 1, 2"); return RB200_E_INVALID; }
     if (n > 65535) { set_error("rb200k_transpose: batch %d exceeds 65535", n); return RB200_E_LIMIT; }
-    transpose_kernel<<<dim3(296, (unsigned)n), 256, 0, (cudaStream_t)stream_v>>>(arena, samples, perm[0], perm[1], perm[2], out, out_stride);
+    transpose_kernel<<<dim3(296, (unsigned)n), 256, 0, (cudaStream_t)stream_v>>>(arena, samples, perm[0], perm[1], perm[2], out, out_dims[0], out_dims[1],
+                                                                             out_dims[2]);
     RB200_CHECK_LAUNCH("transpose_kernel");
     return RB200_OK;
 }

@@ -223,6 +223,22 @@ def color_temp(*inputs, adjustment_value=50, device=None, output_layout=types.NH
     return _ret(p, C.color_temp(p._handle, inputs[0], 0, _iparam(adjustment_value), output_layout, output_dtype))
 
 
+def normalize(*inputs, axes=[], mean=[], stddev=[], scale=1.0, shift=0.0, output_datatype=types.FLOAT):
+    """fn.py:1216: out = scale * (in - mean) / stddev + shift. axes (0 height, 1 width, 2 channel) name what a computed
+    mean / stddev is taken over; an empty mean / stddev list asks for it to be computed per sample."""
+    p = _pipe()
+    ax = (ctypes.c_uint * max(len(axes), 1))(*[int(a) for a in axes])
+    return _ret(p, C.normalize(p._handle, inputs[0], ax, len(axes), _farr(mean) if len(mean) else None, len(mean),
+                               _farr(stddev) if len(stddev) else None, len(stddev), 0, float(scale), float(shift), output_datatype))
+
+
+def transpose(*inputs, perm=[], output_layout=types.NHWC, output_dtype=types.UINT8):
+    """fn.py:1239: reorders the per-sample axes (height, width, channel) by perm."""
+    p = _pipe()
+    pm = (ctypes.c_uint * max(len(perm), 1))(*[int(a) for a in perm])
+    return _ret(p, C.transpose(p._handle, inputs[0], pm, len(perm), 0, output_layout))
+
+
 def hue(*inputs, hue=None, device=None, seed=0, output_layout=types.NHWC, output_dtype=types.UINT8):
     p = _pipe()
     return _ret(p, C.hue(p._handle, inputs[0], 0, _fparam(hue), output_layout, output_dtype))

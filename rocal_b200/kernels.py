@@ -195,14 +195,15 @@ def normalize(arena, samples, out_w, out_h, axis_mask=3, mean=None, stddev=None,
     return out
 
 
-def transpose(arena, samples, perm, out_stride, out=None, d_samples=None, stream=None):
-    """rb200k_transpose: uint8 [n][out_stride], every sample's permuted window packed at the start of its slot."""
+def transpose(arena, samples, perm, out_dims, out=None, d_samples=None, stream=None):
+    """rb200k_transpose: uint8 [n][out_dims...], every sample's permuted window at the origin of its slot."""
     n = len(samples)
     if out is None:
-        out = torch.zeros((n, out_stride), dtype=torch.uint8, device=arena.device)
+        out = torch.zeros((n,) + tuple(int(v) for v in out_dims), dtype=torch.uint8, device=arena.device)
     if d_samples is None:
         d_samples = to_device_table(samples, arena.device)
     pm = (ctypes.c_int32 * 3)(*[int(v) for v in perm])
-    check(lib.rb200k_transpose(arena.data_ptr(), d_samples.data_ptr(), n, pm, out.data_ptr(), int(out_stride), _stream_ptr(stream)),
+    od = (ctypes.c_int32 * 3)(*[int(v) for v in out_dims])
+    check(lib.rb200k_transpose(arena.data_ptr(), d_samples.data_ptr(), n, pm, out.data_ptr(), od, _stream_ptr(stream)),
           "rb200k_transpose")
     return out

@@ -226,3 +226,40 @@ def test_boxes_follow_ssd_crop(cuda):
         assert np.array_equal(xl, el) and np.allclose(xb, eb, rtol=1e-5, atol=1e-6)
     assert kept > 100
     pipe.rocal_release()
+
+
+def test_normalize_and_transpose_through_the_api(cuda):
+    """rocalNormalize with computed per-channel statistics, with given statistics, and per-image statistics behind a
+    crop; rocalTranspose HWC -> CHW and the height / width swap. Four outputs of one graph against the oracle."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(34)
+    n = 12
+    pipe = Pipeline(batch_size=n, device_id=0, seed=29)
+    with pipe:
+        img = _source(200, 160)
+        o_stat = fn.normalize(img, axes=[0, 1])                                             # per-channel mean / stddev, computed
+        o_given = fn.normalize(img, mean=list(S.MEAN), stddev=list(S.STD), scale=2.0, shift=0.5, output_datatype=types.FLOAT16)
+        c = fn.crop(img, crop=[64, 96], crop_pos_x=10, crop_pos_y=5)
+        o_img = fn.normalize(c, axes=[0, 1, 2], stddev=[50.0])                              # per-image mean, given deviation
+        o_chw = fn.transpose(img, perm=[2, 0, 1])
+        o_swap = fn.transpose(c, perm=[1, 0, 2])
+        pipe.set_outputs(o_stat, o_given, o_img, o_chw, o_swap)
+    pipe.build()
+    for _ in range(2):
+        arena, hs, ws, offs = S.make_images(rng, n, (70, 160), (100, 200))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        t_stat, t_given, t_img, t_chw, t_swap = pipe.get_output_tensors()
+        tab = _pointwise_table(hs, ws, offs)
+        assert np.array_equal(t_stat.numpy(), O.normalize(arena, tab, 200, 160, axis_mask=3))
+        exp = O.normalize(arena, tab, 200, 160, mean=S.MEAN, stddev=S.STD, scale=2.0, shift=0.5, out_dtype=T.FP16)
+        assert np.array_equal(t_given.numpy().view(np.uint16), exp.view(np.uint16))
+        win = pipe.get_crop_windows(c).astype(np.int64)
+        ctab = _pointwise_table(hs, ws, offs)
+        ctab["roi_x"], ctab["roi_y"], ctab["roi_w"], ctab["roi_h"] = win[:, 0], win[:, 1], win[:, 2], win[:, 3]
+        assert np.array_equal(t_img.numpy(), O.normalize(arena, ctab, 96, 64, axis_mask=7, stddev=(50.0, 50.0, 50.0)))
+        assert t_chw.dims() == [n, 3, 160, 200] and t_swap.dims() == [n, 96, 64, 3]
+        assert np.array_equal(t_chw.numpy(), O.transpose(arena, tab, (2, 0, 1), (3, 160, 200)))
+        assert np.array_equal(t_swap.numpy(), O.transpose(arena, ctab, (1, 0, 2), (96, 64, 3)))
+    pipe.rocal_release()

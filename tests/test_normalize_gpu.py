@@ -80,5 +80,11 @@ def test_transpose(cuda, perm):
     rng = S.rng_for(80)
     arena, t = _windows(rng, 6, (10, 60), (10, 70), content="noise")
     a = torch.from_numpy(arena).to(cuda)
-    stride = 60 * 70 * 3
-    assert np.array_equal(K.transpose(a, t, perm, stride).cpu().numpy(), O.transpose(arena, t, perm, stride))
+    dims = [(60, 70, 3)[k] for k in perm]                    # the permuted maximum shape
+    got = K.transpose(a, t, perm, dims).cpu().numpy()
+    assert np.array_equal(got, O.transpose(arena, t, perm, dims))
+    q = t[1]
+    o, st = int(q["src_offset"]), int(q["src_stride"])
+    win = np.stack([arena[o + (q["roi_y"] + y) * st + q["roi_x"] * 3:][:q["roi_w"] * 3] for y in range(q["roi_h"])]).reshape(q["roi_h"], q["roi_w"], 3)
+    e = win.transpose(perm)
+    assert np.array_equal(got[1][:e.shape[0], :e.shape[1], :e.shape[2]], e)
