@@ -13,7 +13,8 @@ One step = one pass of the path over one batch. Rank 0 prints one JSON line:
   roofline  algorithmic bytes of the resample kernel / its mean launch time, against the measured
             HBM copy bandwidth (MEASURED_PEAKS.json, else the 6650 GB/s fallback)
   cpu_baseline  the CPU oracle (OpenMP over samples) on whole passes over the same batch
-  per_rank  every rank's own device-resident and end-to-end times, uploaded bytes and host-link rate
+  per_rank  every rank's own device-resident and end-to-end times, uploaded bytes, host-link rate during the e2e run and
+            the rate of plain pinned-to-device copies issued by all ranks at once (the link's ceiling at this GPU count)
   other_configs (one GPU only) short runs of configs[0], [2], [3], [4]: ms per step, images/s, roofline fraction, e2e
 `--impl reference` times the CPU implementation alone on rank 0's whole batch (the oracle port: the reference's own
 pixel code lives in the RPP library, which is not available) and prints the same line shape; it does not load the
@@ -795,7 +796,17 @@ def main():
     barrier()
     pipe.rocal_release()
 
-    mine = torch.tensor([total_ms, e2e_ms, float(h2d_per_step), float(np.mean(launch_ms))], dtype=torch.float64, device=dev)
+    # ---- what the host link gives this rank while every rank pulls at once: plain copies of the pinned arena ----
+    link_reps = 6
+    barrier()
+    tl = time.perf_counter()
+    for _ in range(link_reps):
+        arena_d.copy_(arena_pinned, non_blocking=True)
+    torch.cuda.synchronize()
+    link_gbs = link_reps * arena_pinned.numel() / (time.perf_counter() - tl) / 1e9
+    barrier()
+
+    mine = torch.tensor([total_ms, e2e_ms, float(h2d_per_step), float(np.mean(launch_ms)), link_gbs], dtype=torch.float64, device=dev)
     if world > 1:
         gathered = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
@@ -807,7 +818,8 @@ def main():
     for r_, g in enumerate(gathered):
         g = [float(v) for v in g.cpu()]
         per_rank.append({"rank": r_, "device_ms_per_step": g[0] / args.steps, "kernel_ms": g[3], "e2e_ms_per_step": g[1] / e2e_steps,
-                         "h2d_bytes_per_step": int(g[2]), "host_link_gbs": g[2] * e2e_steps / (g[1] * 1e-3) / 1e9, "numa": numas[r_]})
+                         "h2d_bytes_per_step": int(g[2]), "host_link_gbs": g[2] * e2e_steps / (g[1] * 1e-3) / 1e9,
+                         "link_copy_gbs": g[4], "numa": numas[r_]})
     total_ms = max(p_["device_ms_per_step"] for p_ in per_rank) * args.steps
     e2e_ms = max(p_["e2e_ms_per_step"] for p_ in per_rank) * e2e_steps
 
@@ -829,7 +841,12 @@ def main():
                                "footprint rectangles, an upper bound of what crosses the link"}[upload_mode],
                     "d2h_bytes_per_step": int(host_back.numel() * 2) * world,
                     "d2h_note": "one sample per rank and step: outputs are consumed on the device (DLPack), by design",
-                    "steps": e2e_steps, "timed": "clock starts before the first feed; every batch's feed, transfer and kernel inside"},
+                    "steps": e2e_steps, "timed": "clock starts before the first feed; every batch's feed, transfer and kernel inside",
+                    "host_link_gbs": sum(p_["host_link_gbs"] for p_ in per_rank),
+                    "link_copy_gbs": sum(p_["link_copy_gbs"] for p_ in per_rank),
+                    "link_note": "host_link_gbs = footprint bytes the zero-copy kernels pulled per second, all ranks; link_copy_gbs = "
+                                 "plain pinned-to-device copies of the same arenas issued by all ranks at once (what the host "
+                                 "and its PCIe links deliver to this many GPUs together)"},
             "gpu_launches": int(launches),
             "per_rank": per_rank,
             "roofline": {"bound": "hbm", "kernel": "resample_stream_kernel<half,NCHW,normalize>", "achieved": achieved,
