@@ -181,6 +181,27 @@ RB200_API int rb200_get_decoder_crop_windows(rb200_context ctx, unsigned* xywh, 
  * shapes_hw[n][2] = {height, width}. */
 RB200_API int rb200_random_crop_windows(unsigned batch_seed, const int* shapes_hw, size_t n, const float* area_factor,
                                         const float* aspect_ratio, unsigned num_attempts, unsigned* out_xywh);
+/* rocalRandomBBoxCrop (rocal_api_meta_data.h:245; fn.random_bbox_crop): every source image of a batch reaches the graph
+ * cut to a window sampled around its boxes, and the boxes follow the window (a box is kept when its centre lies strictly
+ * inside; kept boxes are clipped and re-normalised to the window). The window of a sample: one of seven minimum-IoU
+ * options {-1, 0.1, 0.3, 0.5, 0.7, 0.9, whole image}; width and height factors in 0.3 .. 1 with a ratio in 0.5 .. 2; left
+ * edge aligned to 8 pixels; with all_boxes_overlap every box must reach the option's IoU with the window; one box centre
+ * must lie inside; a failed draw starts over (RandomBBoxCropReader::get_batch_crop_coords,
+ * source/meta_data/randombboxcrop_reader.cpp:216-313). has_shape != 0 keeps the whole image, as there. The window is a
+ * view into the source (only its pixels are uploaded), so the crop costs no pass of its own. The arguments the
+ * reference accepts and never reads (no_crop, aspect_ratio, crop size, num_attempts, scaling, total_num_attempts) are
+ * taken by the rocalRandomBBoxCrop shim and dropped. seed starts the 128 per-position generators, which the reference
+ * seeds from std::random_device. Call after the source and before rb200_verify; the batches must carry boxes
+ * (rb200_feed_boxes or a COCO source). */
+RB200_API int rb200_random_bbox_crop(rb200_context ctx, int all_boxes_overlap, int has_shape, unsigned seed);
+/* [extension] The windows of the current batch as sampled: n x {x, y, w, h} as fractions of the image. The pixel
+ * windows are what rb200_get_decoder_crop_windows returns. */
+RB200_API int rb200_get_bbox_crop_windows(rb200_context ctx, float* xywh);
+/* [extension] Host only, no context: the windows a fresh sampler gives n samples in turn. boxes_ltrb holds
+ * box_offsets[n] boxes normalized to their image, sample i owning boxes box_offsets[i] .. box_offsets[i + 1] - 1;
+ * img_widths[n] in pixels (for the 8-pixel alignment). */
+RB200_API int rb200_bbox_crop_windows(unsigned seed, int all_boxes_overlap, int has_shape, const float* boxes_ltrb,
+                                      const int* box_offsets, size_t n, const int* img_widths, float* out_xywh);
 /* [extension] Ground-truth boxes of the next fed batch: normalized ltrb, labels, counts[n]. The reference
  * can attach boxes only through a dataset reader keyed by file name (master_graph.cpp:983-984). */
 RB200_API int rb200_feed_boxes(rb200_context ctx, const float* ltrb, const int* labels, const int* counts, size_t n);

@@ -430,6 +430,12 @@ RB200_ROCAL RocalStatus ROCAL_API_CALL rocalToTensor(RocalContext rocal_context,
 RB200_ROCAL void ROCAL_API_CALL rocalSetOutputs(RocalContext p_context, unsigned int num_of_outputs, std::vector<RocalTensor>& output_images);
 RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetOutputTensors(RocalContext p_context);
 
+/* ---- random bounding-box crop of the source images (rocal_api_meta_data.h:245) ---- */
+RB200_ROCAL void ROCAL_API_CALL rocalRandomBBoxCrop(RocalContext p_context, bool all_boxes_overlap, bool no_crop,
+                                                    RocalFloatParam aspect_ratio = NULL, bool has_shape = false, int crop_width = 0,
+                                                    int crop_height = 0, int num_attempts = 1, RocalFloatParam scaling = NULL,
+                                                    int total_num_attempts = 0, int64_t seed = 0);
+
 /* ---- SSD box encoder (rocal_api_meta_data.h:270-286) ---- */
 RB200_ROCAL void ROCAL_API_CALL rocalBoxEncoder(RocalContext p_context, std::vector<float>& anchors, float criteria,
                                                 std::vector<float>& means, std::vector<float>& stds,

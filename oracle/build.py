@@ -7,7 +7,8 @@ liboracle.so   the CPU restatement in oracle.c (gcc, -ffp-contract=off so that e
                rocAL/CMakeLists.txt:375).
 _ref/libref.so reference-owned CPU code compiled where it lies (never copied):
                rocAL/source/meta_data/bounding_box_graph.cpp, rocAL/source/parameters/
-               parameter_{factory,random_crop_decoder,crop,rocal_crop,random_crop}.cpp + ref_driver.cpp,
+               parameter_{factory,random_crop_decoder,crop,rocal_crop,random_crop}.cpp,
+               rocAL/source/meta_data/randombboxcrop_reader.cpp + ref_driver.cpp + ref_bbox_crop_driver.cpp,
                against the stand-in headers in ref_stubs/. Only built when the reference tree exists.
 _ref/libref_hip.so the reference's own pixel kernels, rocAL/rocAL_hip/rocal_hip_kernels.cpp, compiled for the
                host where they lie against ref_stubs/hip/ (vector types, thread indices set by a launch
@@ -72,7 +73,8 @@ def build_ref(force=False):
             os.path.join(r, "source", "parameters", "parameter_crop.cpp"),
             os.path.join(r, "source", "parameters", "parameter_rocal_crop.cpp"),
             os.path.join(r, "source", "parameters", "parameter_random_crop.cpp"),
-            os.path.join(HERE, "ref_driver.cpp")]
+            os.path.join(r, "source", "meta_data", "randombboxcrop_reader.cpp"),
+            os.path.join(HERE, "ref_driver.cpp"), os.path.join(HERE, "ref_bbox_crop_driver.cpp")]
     if force or _stale(REF_SO, srcs):
         os.makedirs(REF_DIR, exist_ok=True)
         cmd = ["g++", "-std=c++17", "-O3", "-fPIC", "-shared", "-fopenmp", "-ffp-contract=off",

@@ -813,3 +813,143 @@ def ref_random_bbox_meta(boxes, labels, offsets, crop_xywh, roi_wh):
     k = r.ref_random_bbox_meta(_ptr(boxes), _ptr(labels), _ptr(offsets), ctypes.c_int(n), _ptr(crops), _ptr(roi), _ptr(ob),
                                _ptr(ol), _ptr(oc))
     return ob[:k].copy(), ol[:k].copy(), np.concatenate([[0], np.cumsum(oc)]).astype(np.int32)
+
+
+# ---- random-bbox-crop windows (rocalRandomBBoxCrop) -----------------------------------------------------------
+
+class _Mt19937Seq:
+    """std::mt19937 constructed from a std::seed_seq over `words`: the 624-word state is seed_seq::generate's
+    output, and libstdc++ replaces an all-zero state (ignoring the low 31 bits of word 0) by 2^31."""
+
+    def __init__(self, words):
+        state = _seed_seq_generate([int(w) & 0xFFFFFFFF for w in words], 624)
+        if (state[0] & 0x80000000) == 0 and not any(state[1:]):
+            state[0] = 0x80000000
+        self._rs = np.random.RandomState()
+        self._rs.set_state(("MT19937", np.array(state, dtype=np.uint32), 624))
+
+    def __call__(self):
+        return int(self._rs.randint(0, 1 << 32, size=1, dtype=np.uint64)[0])
+
+
+def _seed_seq_generate(v, n):
+    """std::seed_seq{v...}.generate over n 32-bit words ([rand.util.seedseq])."""
+    s = len(v)
+    b = [0x8b8b8b8b] * n
+    t = 11 if n >= 623 else 7 if n >= 68 else 5 if n >= 39 else 3 if n >= 7 else (n - 1) // 2
+    p, q = (n - t) // 2, (n - t) // 2 + t
+    m = max(s + 1, n)
+    M = 0xFFFFFFFF
+
+    def T_(x):
+        return x ^ (x >> 27)
+
+    for k in range(m):
+        r1 = (1664525 * T_(b[k % n] ^ b[(k + p) % n] ^ b[(k - 1) % n])) & M
+        if k == 0:
+            r2 = (r1 + s) & M
+        elif k <= s:
+            r2 = (r1 + (k % n) + v[k - 1]) & M
+        else:
+            r2 = (r1 + (k % n)) & M
+        b[(k + p) % n] = (b[(k + p) % n] + r1) & M
+        b[(k + q) % n] = (b[(k + q) % n] + r2) & M
+        b[k % n] = r2
+    for k in range(m, m + n):
+        r3 = (1566083941 * T_((b[k % n] + b[(k + p) % n] + b[(k - 1) % n]) & M)) & M
+        r4 = (r3 - (k % n)) & M
+        b[(k + p) % n] ^= r3
+        b[(k + q) % n] ^= r4
+        b[k % n] = r4
+    return b
+
+
+class BBoxCropSampler:
+    """RandomBBoxCropReader::get_batch_crop_coords (randombboxcrop_reader.cpp:216-313): per sample, from that
+    sample position's own generator, draw one of seven minimum-IoU options (the last keeps the whole image), a width
+    and a height factor in 0.3 .. 1 whose ratio lies in 0.5 .. 2, and a position whose left edge is aligned to 8
+    pixels; with all_boxes_overlap every box must reach the option's IoU with the window, and at least one box centre
+    must lie strictly inside it; otherwise everything is drawn again. 128 generators serve the samples in turn
+    (SeededRNG<std::mt19937, 4>, randombboxcrop_reader.h:41-72); here each is seeded through std::seed_seq from four
+    consecutive outputs of std::mt19937(seed) (the reference takes those words from std::random_device)."""
+
+    OPTIONS = (-1.0, 0.1, 0.3, 0.5, 0.7, 0.9, 0.0)
+
+    def __init__(self, seed, all_boxes_overlap=True):
+        master = _Mt19937(seed)
+        self.rngs = [_Mt19937Seq([master() for _ in range(4)]) for _ in range(128)]
+        self.count = 0
+        self.all_boxes_overlap = all_boxes_overlap
+
+    @staticmethod
+    def _iou(box, crop):
+        f32 = np.float32
+        xa, ya = max(box[0], crop[0]), max(box[1], crop[1])
+        xb, yb = min(box[2], crop[2]), min(box[3], crop[3])
+        inter = f32(max(f32(0), f32(xb - xa)) * max(f32(0), f32(yb - ya)))
+        a1 = f32(f32(box[3] - box[1]) * f32(box[2] - box[0]))
+        a2 = f32(f32(crop[3] - crop[1]) * f32(crop[2] - crop[0]))
+        with np.errstate(divide="ignore", invalid="ignore"):
+            return f32(inter / f32(f32(a1 + a2) - inter))
+
+    def window(self, boxes, img_w):
+        """One sample: boxes [k][4] float32 ltrb as the sampler sees them; returns (x, y, w, h) float32."""
+        f32 = np.float32
+        gen = self.rngs[self.count % 128]
+        self.count += 1
+        boxes = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+        crop = None
+        while True:
+            option = _uniform_int(gen, 0, 6)
+            if option == 6:
+                crop = (f32(0), f32(0), f32(1), f32(1))
+                break
+            min_iou = f32(self.OPTIONS[option])
+            wf = _uniform_real_f32(gen, 0.3, 1.0)
+            hf = _uniform_real_f32(gen, 0.3, 1.0)
+            ratio = f32(wf / hf)
+            if float(ratio) < 0.5 or float(ratio) > 2.0:
+                continue
+            # the reference builds the position distributions from double bounds 1.0 - factor, narrowed to float
+            x = _uniform_real_f32(gen, 0.0, f32(1.0 - float(wf)))
+            y = _uniform_real_f32(gen, 0.0, f32(1.0 - float(hf)))
+            x = f32(f32(int(_lround_f32(f32(x * f32(img_w)))) & ~7) / f32(img_w))
+            crop = (x, y, f32(x + wf), f32(y + hf))
+            if self.all_boxes_overlap and any(self._iou(b, crop) < min_iou for b in boxes):
+                continue
+            inside = 0
+            for b in boxes:
+                xc, yc = 0.5 * float(f32(b[0] + b[2])), 0.5 * float(f32(b[1] + b[3]))
+                if float(crop[0]) < xc < float(crop[2]) and float(crop[1]) < yc < float(crop[3]):
+                    inside += 1
+            if inside == 0:
+                continue
+            break
+        return (crop[0], crop[1], f32(crop[2] - crop[0]), f32(crop[3] - crop[1]))
+
+    def windows(self, boxes, offsets, img_w):
+        boxes = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+        return np.array([self.window(boxes[offsets[i]:offsets[i + 1]], int(img_w[i])) for i in range(len(offsets) - 1)],
+                        dtype=np.float32)
+
+
+def _lround_f32(x):
+    """std::lround of a non-negative float: halves away from zero."""
+    return int(np.floor(np.float64(x) + 0.5))
+
+
+def ref_random_bbox_crop(boxes, offsets, img_w, seed, all_boxes_overlap=True):
+    """The reference's own sampler with its generators replaced as described in ref_bbox_crop_driver.cpp."""
+    r = ref()
+    if r is None:
+        return None
+    boxes = np.ascontiguousarray(boxes, dtype=np.float32).reshape(-1, 4)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+    img_w = np.ascontiguousarray(img_w, dtype=np.int32)
+    n = len(offsets) - 1
+    out = np.zeros((n, 4), dtype=np.float32)
+    r.ref_random_bbox_crop.restype = ctypes.c_int
+    rc = r.ref_random_bbox_crop(_ptr(boxes), _ptr(offsets), ctypes.c_int(n), _ptr(img_w), ctypes.c_uint(seed),
+                                ctypes.c_int(1 if all_boxes_overlap else 0), _ptr(out))
+    assert rc == 0
+    return out

@@ -425,6 +425,18 @@ void Pipeline::top_up() {
     }
 }
 
+void Pipeline::set_random_bbox_crop(bool all_boxes_overlap, bool has_shape, uint32_t seed) {
+    if (_verified) RB200_THROW("rocalRandomBBoxCrop must be called before rocalVerify");
+    _bbox_crop = std::make_unique<BBoxCropSampler>(seed, all_boxes_overlap, has_shape);
+}
+
+void Pipeline::bbox_crop_windows(float* xywh) {
+    if (_held < 0) RB200_THROW("no batch is available yet (call rocalRun first)");
+    const Slot& s = _slots[_held];
+    if (s.bbox_crop_windows.size() != _batch * 4) RB200_THROW("the current batch was not cut by rocalRandomBBoxCrop");
+    if (xywh) std::memcpy(xywh, s.bbox_crop_windows.data(), s.bbox_crop_windows.size() * sizeof(float));
+}
+
 void Pipeline::set_random_crop_decoder(const RandomCropRanges& r) {
     if (_verified) RB200_THROW("the graph is already verified");
     if (_source < 0) RB200_THROW("the context has no source yet");
@@ -701,6 +713,7 @@ void Pipeline::mark_output(TensorImpl* t) {
 void Pipeline::verify() {
     if (_verified) RB200_THROW("rocalVerify was already called");
     if (_source < 0) RB200_THROW("the graph has no input source");
+    if (_bbox_crop && _tensors[_source]->is_output) RB200_THROW("a source cut by rocalRandomBBoxCrop cannot be a graph output");
     RB200_CUDA(cudaSetDevice(_gpu_id));
     plan();
     _slots.resize(_depth);
@@ -1297,13 +1310,45 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     // ---- 1. input: device views of the n source images (the upload itself follows the tables) ----
     _src_views.resize(n);
     s.decoder_windows.clear();
+    s.bbox_crop_windows.clear();
+    _whole_w.assign(n, 0);
+    _whole_h.assign(n, 0);
+    size_t bbox_box0 = 0;
+    if (_bbox_crop) {
+        if (_crop_dec) RB200_THROW("rocalRandomBBoxCrop and a random-crop JPEG source cannot both cut the source images");
+        if (!b.has_boxes || b.counts.size() != n)
+            RB200_THROW("rocalRandomBBoxCrop: the batch carries no bounding boxes (feed them, or use a COCO source)");
+        s.decoder_windows.resize(n * 4);
+        s.bbox_crop_windows.resize(n * 4);
+    }
+    // random bbox crop: sample i's window inside its W x H image, in pixels as the reference's fused decoder rounds it
+    // (FusedCropTJDecoder::decode, source/decoders/image/fused_crop_decoder.cpp:76-85), kept inside the image
+    auto bbox_window = [&](size_t i, int W, int H) -> CropRect {
+        float* f = &s.bbox_crop_windows[i * 4];
+        _bbox_crop->window(b.boxes.data() + bbox_box0 * 4, b.counts[i], W, f);
+        bbox_box0 += (size_t)b.counts[i];
+        CropRect win;
+        win.x = (unsigned)std::min<long>(std::lround(f[0] * W), W - 1);
+        win.y = (unsigned)std::min<long>(std::lround(f[1] * H), H - 1);
+        win.w = (unsigned)std::max<long>(1, std::min<long>(std::lround(f[2] * W), W - (long)win.x));
+        win.h = (unsigned)std::max<long>(1, std::min<long>(std::lround(f[3] * H), H - (long)win.y));
+        unsigned* dw = &s.decoder_windows[i * 4];
+        dw[0] = win.x; dw[1] = win.y; dw[2] = win.w; dw[3] = win.h;
+        return win;
+    };
     const bool host_input = !(b.kind == InputBatch::RAGGED && b.mem_kind == RB200_MEM_DEVICE);
     int arena_used = -1;
     if (b.kind == InputBatch::RAGGED) {
         for (size_t i = 0; i < n; i++) {
             _src_views[i] = {b.descs[i].offset, b.descs[i].stride};
-            src->roi_w[i] = (int)b.descs[i].width;
-            src->roi_h[i] = (int)b.descs[i].height;
+            src->roi_w[i] = _whole_w[i] = (int)b.descs[i].width;
+            src->roi_h[i] = _whole_h[i] = (int)b.descs[i].height;
+            if (_bbox_crop) {
+                const CropRect win = bbox_window(i, _whole_w[i], _whole_h[i]);
+                _src_views[i].offset += (size_t)win.y * b.descs[i].stride + (size_t)win.x * 3;
+                src->roi_w[i] = (int)win.w;
+                src->roi_h[i] = (int)win.h;
+            }
         }
         if (!host_input) _src_base = (const uint8_t*)b.arena;
     } else if (b.kind == InputBatch::ENCODED) {
@@ -1335,16 +1380,21 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             _decode_off[i] = total;
             _decode_h[i] = h;
             _src_views[i] = {total, (uint32_t)w * 3};
-            src->roi_w[i] = w;
-            src->roi_h[i] = h;
-            if (_crop_dec) {
+            src->roi_w[i] = _whole_w[i] = w;
+            src->roi_h[i] = _whole_h[i] = h;
+            if (_crop_dec || _bbox_crop) {
                 // the whole image is decoded; the graph sees the window as its source image (a view into it)
-                const CropRect win = _crop_dec->window(h, w, i);
+                CropRect win;
+                if (_crop_dec) {
+                    win = _crop_dec->window(h, w, i);
+                    unsigned* dw = &s.decoder_windows[i * 4];
+                    dw[0] = win.x; dw[1] = win.y; dw[2] = win.w; dw[3] = win.h;
+                } else {
+                    win = bbox_window(i, w, h);
+                }
                 _src_views[i].offset = total + (size_t)win.y * w * 3 + (size_t)win.x * 3;
                 src->roi_w[i] = (int)win.w;
                 src->roi_h[i] = (int)win.h;
-                unsigned* dw = &s.decoder_windows[i * 4];
-                dw[0] = win.x; dw[1] = win.y; dw[2] = win.w; dw[3] = win.h;
             }
             total += ((size_t)w * h * 3 + 255) & ~(size_t)255;
         }
@@ -1352,6 +1402,13 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     } else {
         size_t total = 0;
         for (size_t i = 0; i < n; i++) {
+            _whole_w[i] = (int)b.roi[i * 4 + 2];
+            _whole_h[i] = (int)b.roi[i * 4 + 3];
+            if (_bbox_crop) {          // only the window is uploaded: the slot's region of interest becomes the window
+                const CropRect win = bbox_window(i, _whole_w[i], _whole_h[i]);
+                b.roi[i * 4] += win.x; b.roi[i * 4 + 1] += win.y;
+                b.roi[i * 4 + 2] = win.w; b.roi[i * 4 + 3] = win.h;
+            }
             unsigned w = b.roi[i * 4 + 2], h = b.roi[i * 4 + 3];
             _src_views[i] = {total, w * 3};
             src->roi_w[i] = (int)w;
@@ -1365,10 +1422,10 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         s.source_wh[i * 2] = src->roi_w[i];
         s.source_wh[i * 2 + 1] = src->roi_h[i];
     }
-    if (!s.decoder_windows.empty())   // the views show the windows; the images are the stride wide
+    if (!s.decoder_windows.empty())   // the views show the windows; report the images they were cut from
         for (size_t i = 0; i < n; i++) {
-            s.source_wh[i * 2] = (int)(_src_views[i].stride / 3);
-            s.source_wh[i * 2 + 1] = (int)_decode_h[i];
+            s.source_wh[i * 2] = _whole_w[i];
+            s.source_wh[i * 2 + 1] = _whole_h[i];
         }
     // Pinned host input that exactly one staging kernel consumes is not uploaded at all: the kernel's bulk
     // copies read the tap rows straight from host memory, so only the bytes the batch needs cross the link.
@@ -1414,6 +1471,15 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     s.file_labels = b.file_labels;
     s.names = b.names;
     s.padded = b.padded;
+    if (_bbox_crop) {
+        // the boxes follow the window by the centre rule (BoundingBoxGraph::update_random_bbox_meta_data)
+        std::vector<unsigned> wx(n), wy(n), ww(n), wh(n);
+        for (size_t i = 0; i < n; i++) {
+            wx[i] = s.decoder_windows[i * 4]; wy[i] = s.decoder_windows[i * 4 + 1];
+            ww[i] = s.decoder_windows[i * 4 + 2]; wh[i] = s.decoder_windows[i * 4 + 3];
+        }
+        transform_boxes_window(s, wx, wy, ww, wh, _whole_w, _whole_h, true);
+    }
     update_nodes(b, s);
 
     auto view_of = [&](int tensor_id, size_t i, const uint8_t*& base) -> SampleView {

@@ -27,6 +27,7 @@
 #include "file_source.h"
 #include "jpeg_decoder.h"
 #include "params.h"
+#include "bbox_crop.h"
 #include "random_crop_window.h"
 #include "rb200.h"
 #include "rocal_api.h"
@@ -220,7 +221,8 @@ struct Slot {
     std::vector<std::string> names;  // file source: file name per sample
     size_t padded = 0;
     std::vector<int> source_wh;              // n x {width, height} of the whole source images (before a decoder crop)
-    std::vector<unsigned> decoder_windows;   // fused JPEG crop: n x {x,y,w,h} inside the decoded images
+    std::vector<unsigned> decoder_windows;   // fused JPEG crop / random bbox crop: n x {x,y,w,h} inside the whole images
+    std::vector<float> bbox_crop_windows;    // random bbox crop: n x {x,y,w,h} as fractions of the image, as sampled
     unsigned decoder_batch_seed = 0;
     size_t n = 0;
     std::string error;
@@ -240,6 +242,9 @@ class Pipeline {
                                 int last_batch_policy, bool pad_last_batch_repeated);
     // rocalFusedJpegCrop*: every image of an encoded source is cut to a random-resized-crop window before the graph
     void set_random_crop_decoder(const RandomCropRanges& r);
+    // rocalRandomBBoxCrop: every image (and its boxes) of the source is cut to a window sampled around the boxes
+    void set_random_bbox_crop(bool all_boxes_overlap, bool has_shape, uint32_t seed);
+    void bbox_crop_windows(float* xywh);
     void decoder_crop_windows(unsigned* xywh, unsigned* batch_seed);
     void reset_loaders();
     // Orders the reuse of the held batch's buffers behind the work already queued on `consumer_stream`
@@ -420,6 +425,8 @@ class Pipeline {
     std::atomic<unsigned long long> _t_load{0}, _t_decode{0}, _t_process{0}, _t_transfer{0};
     std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
     int _upload_mode = UPLOAD_ZERO_COPY;
+    std::unique_ptr<BBoxCropSampler> _bbox_crop;
+    std::vector<int> _whole_w, _whole_h;                  // the images the source views were cut from
     void* _norm_scratch = nullptr;                        // statistics scratch shared by the Normalize steps
     size_t _norm_scratch_bytes = 0;
     int _arith = RB200_ARITH_EXACT;                       // arithmetic of the colour operators (rb200_set_arithmetic)

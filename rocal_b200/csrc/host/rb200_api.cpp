@@ -481,6 +481,44 @@ int rb200_get_decoder_crop_windows(rb200_context ctx, unsigned* xywh, unsigned* 
     return ROCAL_OK;
 }
 
+int rb200_random_bbox_crop(rb200_context ctx, int all_boxes_overlap, int has_shape, unsigned seed) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->set_random_bbox_crop(all_boxes_overlap != 0, has_shape != 0, seed);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_INVALID_PARAMETER_TYPE;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_get_bbox_crop_windows(rb200_context ctx, float* xywh) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->bbox_crop_windows(xywh);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
+int rb200_bbox_crop_windows(unsigned seed, int all_boxes_overlap, int has_shape, const float* boxes_ltrb, const int* box_offsets,
+                            size_t n, const int* img_widths, float* out_xywh) {
+    try {
+        if (n && (!box_offsets || !img_widths || !out_xywh)) return ROCAL_INVALID_PARAMETER_TYPE;
+        rb200::BBoxCropSampler sampler(seed, all_boxes_overlap != 0, has_shape != 0);
+        for (size_t i = 0; i < n; i++) {
+            const int nb = box_offsets[i + 1] - box_offsets[i];
+            if (nb < 0 || (nb > 0 && !boxes_ltrb) || img_widths[i] <= 0) return ROCAL_INVALID_PARAMETER_TYPE;
+            sampler.window(boxes_ltrb + (size_t)box_offsets[i] * 4, nb, img_widths[i], out_xywh + i * 4);
+        }
+    } catch (const std::exception&) {
+        return ROCAL_RUNTIME_ERROR;
+    }
+    return ROCAL_OK;
+}
+
 int rb200_random_crop_windows(unsigned batch_seed, const int* shapes_hw, size_t n, const float* area_factor,
                               const float* aspect_ratio, unsigned num_attempts, unsigned* out_xywh) {
     try {

@@ -466,6 +466,12 @@ RocalTensorList ROCAL_API_CALL rocalGetOutputTensors(RocalContext c) {
     return P(c)->outputs();
 }
 
+void ROCAL_API_CALL rocalRandomBBoxCrop(RocalContext c, bool all_boxes_overlap, bool, RocalFloatParam, bool has_shape, int, int, int,
+                                        RocalFloatParam, int, int64_t seed) {
+    if (!c) return;
+    rb200_random_bbox_crop(c, all_boxes_overlap, has_shape, (unsigned)seed);
+}
+
 void ROCAL_API_CALL rocalBoxEncoder(RocalContext c, std::vector<float>& anchors, float criteria, std::vector<float>& means,
                                     std::vector<float>& stds, bool offset, float scale) {
     if (!c) {

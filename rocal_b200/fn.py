@@ -176,6 +176,17 @@ def ssd_random_crop(*inputs, p_threshold=None, crop_area_factor=None, crop_aspec
     return _ret(p, C.ssd_random_crop(p._handle, inputs[0], 0, num_attempts, output_layout, output_dtype))
 
 
+def random_bbox_crop(*inputs, all_boxes_above_threshold=True, allow_no_crop=True, aspect_ratio=None, bbox_layout="",
+                     threshold_type="iou", thresholds=None, crop_shape=None, num_attempts=1, scaling=None, seed=1,
+                     shape_layout="", input_shape=None, total_num_attempts=0, device=None, ltrb=True, labels=None):
+    """rocalRandomBBoxCrop (amd/rocal/fn.py:901-940): the source images of every batch reach the graph cut to a window
+    sampled around their boxes. Returns the reference's 4-tuple; its first element is None here (the reference returns
+    the metadata reader's handle, which nothing consumes)."""
+    p = _pipe()
+    p._check(C.random_bbox_crop(p._handle, int(bool(all_boxes_above_threshold)), int(bool(crop_shape)), int(seed) & 0xFFFFFFFF))
+    return (None, [], [], [])
+
+
 def flip(*inputs, horizontal=0, vertical=0, device=None, output_layout=types.NHWC, output_dtype=types.UINT8):
     p = _pipe()
     return _ret(p, C.flip(p._handle, inputs[0], 0, _iparam(horizontal), _iparam(vertical), output_layout, output_dtype))

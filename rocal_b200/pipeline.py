@@ -370,6 +370,13 @@ class Pipeline(object):
         self._check(C.get_decoder_crop_windows(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint)), ctypes.byref(seed)))
         return out, int(seed.value)
 
+    def get_bbox_crop_windows(self):
+        """[extension] The windows rocalRandomBBoxCrop sampled for the current batch, float32 [N, 4] = (x, y, w, h) as
+        fractions of the image; get_decoder_crop_windows() gives the same windows in pixels."""
+        out = np.zeros((self._batch_size, 4), dtype=np.float32)
+        self._check(C.get_bbox_crop_windows(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float))))
+        return out
+
     def get_image_names(self):
         """rocalGetImageNameLen + rocalGetImageName: file names of the current batch."""
         lens = (ctypes.c_int * self._batch_size)()

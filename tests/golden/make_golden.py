@@ -176,6 +176,21 @@ def crop_and_boxes():
         for name, v in (("boxes", boxes), ("labels", labels), ("offsets", offsets), ("crops", crops), ("roi", roi),
                         ("out_boxes", ob), ("out_labels", ol), ("out_offsets", oo)):
             out["bbox_%s_%d" % (name, k)] = v
+    # RandomBBoxCropReader::get_batch_crop_coords with its 128 generators re-seeded (see ref_bbox_crop_driver.cpp):
+    # 160 samples each, so the generators wrap around once; case 2 has samples whose boxes are all tiny (many rejections)
+    for k, (seed, overlap) in enumerate(((7, 1), (1234, 0), (99, 1))):
+        n = 160
+        counts = rng.integers(1, 7, n)
+        tot = int(counts.sum())
+        ctr = rng.uniform(0.05, 0.95, (tot, 2))
+        sz = rng.uniform(0.02, 0.7 if k < 2 else 0.1, (tot, 2))
+        boxes = np.concatenate([np.clip(ctr - sz / 2, 0, 1), np.clip(ctr + sz / 2, 0, 1)], 1).astype(np.float32)
+        offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        img_w = rng.integers(64, 1400, n).astype(np.int32)
+        win = O.ref_random_bbox_crop(boxes, offsets, img_w, seed, bool(overlap))
+        for name, v in (("boxes", boxes), ("offsets", offsets), ("img_w", img_w), ("args", np.array([seed, overlap], np.int64)),
+                        ("windows", win)):
+            out["bboxcrop_%s_%d" % (name, k)] = v
     np.savez_compressed(os.path.join(HERE, "crop_and_boxes.npz"), **out)
     print("wrote crop_and_boxes.npz")
 

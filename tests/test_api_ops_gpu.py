@@ -228,6 +228,65 @@ def test_boxes_follow_ssd_crop(cuda):
     pipe.rocal_release()
 
 
+def test_random_bbox_crop_cuts_images_and_boxes(cuda):
+    """rocalRandomBBoxCrop on an external source, fed three ways (packed host arena, pinned arena read in place,
+    max-size slots): the sampled windows are the pinned restatement's (the sampler's counter runs on across batches),
+    their pixel form is the fused decoder's rounding, the pixels behind a Resize are the oracle's resize of that
+    window, and the boxes follow by the centre rule of update_random_bbox_meta_data."""
+    import torch
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(36)
+    n = 16
+    seed = 4321
+    pipe = Pipeline(batch_size=n, device_id=0, seed=31)
+    with pipe:
+        img = _source(640, 480)
+        ret = fn.random_bbox_crop(img, all_boxes_above_threshold=False, seed=seed)
+        assert ret[1:] == ([], [], [])
+        pipe.set_outputs(fn.resize(img, resize_width=96, resize_height=64, scaling_mode=types.SCALING_MODE_STRETCH))
+    pipe.build()
+    sampler = O.BBoxCropSampler(seed, False)
+    cropped = kept = 0
+    for mode in ("arena", "pinned", "slots"):
+        arena, hs, ws, offs = S.make_images(rng, n, (100, 480), (100, 640))
+        boxes, labels, boffs = S.random_boxes(rng, n)
+        pipe.feed_boxes(boxes, labels, np.diff(boffs))
+        if mode == "slots":
+            pipe.feed_input([arena[int(offs[i]):int(offs[i]) + int(hs[i]) * int(ws[i]) * 3].reshape(int(hs[i]), int(ws[i]), 3)
+                             for i in range(n)])
+        elif mode == "pinned":
+            pipe.feed_ragged(torch.from_numpy(arena).pin_memory(), hs, ws, offs)
+        else:
+            pipe.feed_ragged(arena, hs, ws, offs)
+        out = pipe.run()[0].numpy()
+        frac = pipe.get_bbox_crop_windows()
+        assert np.array_equal(frac, sampler.windows(boxes, boffs, ws)), mode
+        win, _ = pipe.get_decoder_crop_windows()
+        exp_win = np.zeros((n, 4), dtype=np.int64)
+        for i in range(n):
+            W, H = int(ws[i]), int(hs[i])
+            x, y = min(O._lround_f32(frac[i, 0] * np.float32(W)), W - 1), min(O._lround_f32(frac[i, 1] * np.float32(H)), H - 1)
+            exp_win[i] = (x, y, max(1, min(O._lround_f32(frac[i, 2] * np.float32(W)), W - x)),
+                          max(1, min(O._lround_f32(frac[i, 3] * np.float32(H)), H - y)))
+        assert np.array_equal(win.astype(np.int64), exp_win), mode
+        assert np.array_equal(pipe.get_image_sizes(), np.stack([ws, hs], 1)), mode    # the images the windows were cut from
+        cropped += int((win[:, 2] < ws).sum())
+        t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        t["src_stride"] = ws.astype(np.int64) * 3
+        t["src_offset"] = offs + win[:, 1].astype(np.int64) * t["src_stride"] + win[:, 0].astype(np.int64) * 3
+        t["roi_w"], t["roi_h"], t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = win[:, 2], win[:, 3], 96, 64, 96, 64
+        assert np.array_equal(out, O.resample(arena, t, 96, 64, T.UINT8, T.NHWC)), mode
+        wf = win.astype(np.float32)
+        pf = np.stack([wf[:, 0] / ws, wf[:, 1] / hs, (wf[:, 0] + wf[:, 2]) / ws - wf[:, 0] / ws,
+                       (wf[:, 1] + wf[:, 3]) / hs - wf[:, 1] / hs], 1).astype(np.float32)
+        b, l, o = O.random_bbox_meta(boxes, labels, boffs, pf, np.ones((n, 2), np.uint32))
+        rep = np.repeat(pf[:, 2:], np.diff(o), axis=0)
+        kept += _compare_boxes(pipe, (b / np.concatenate([rep, rep], 1)).astype(np.float32), l, o, [(1, 1)] * n)
+    assert cropped > 20 and kept > 40
+    pipe.rocal_release()
+
+
 def test_normalize_and_transpose_through_the_api(cuda):
     """rocalNormalize with computed per-channel statistics, with given statistics, and per-image statistics behind a
     crop; rocalTranspose HWC -> CHW and the height / width swap. Four outputs of one graph against the oracle."""

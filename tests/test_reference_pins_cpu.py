@@ -193,6 +193,59 @@ def test_random_bbox_meta_matches_reference_build():
             assert np.array_equal(x, y), k
 
 
+# ---- random bbox crop windows -----------------------------------------------------------------------------------
+
+def _product_bbox_windows(seed, overlap, boxes, offsets, img_w):
+    """The library's own sampler through its host-only entry point (no device is touched)."""
+    import ctypes
+    from rocal_b200 import _capi as C
+    boxes = np.ascontiguousarray(boxes, dtype=np.float32)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+    img_w = np.ascontiguousarray(img_w, dtype=np.int32)
+    out = np.zeros((len(img_w), 4), dtype=np.float32)
+    fp, ip = ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)
+    rc = C.bbox_crop_windows(int(seed), int(overlap), 0, boxes.ctypes.data_as(fp), offsets.ctypes.data_as(ip), len(img_w),
+                             img_w.ctypes.data_as(ip), out.ctypes.data_as(fp))
+    assert rc == 0
+    return out
+
+
+def test_bbox_crop_windows_match_golden():
+    """RandomBBoxCropReader::get_batch_crop_coords (randombboxcrop_reader.cpp:216-313), recorded from the reference
+    build: the numpy restatement and the library's sampler both reproduce every window bit for bit."""
+    g = np.load(os.path.join(GOLDEN, "crop_and_boxes.npz"))
+    cropped = 0
+    for k in range(3):
+        seed, overlap = (int(v) for v in g["bboxcrop_args_%d" % k])
+        boxes, offsets, img_w, want = (g["bboxcrop_%s_%d" % (name, k)] for name in ("boxes", "offsets", "img_w", "windows"))
+        got = O.BBoxCropSampler(seed, bool(overlap)).windows(boxes, offsets, img_w)
+        assert np.array_equal(got, want), k
+        assert np.array_equal(_product_bbox_windows(seed, overlap, boxes, offsets, img_w), want), k
+        cropped += int((want[:, 2] < 1).sum())
+        # every window is a legal one: inside the image, left edge on an 8-pixel boundary
+        assert np.all(want[:, :2] >= 0) and np.all(want[:, 0] + want[:, 2] <= 1.0001) and np.all(want[:, 1] + want[:, 3] <= 1.0001)
+        assert np.all(np.abs(np.rint(want[:, 0] * img_w) % 8) < 1e-3)
+    assert cropped > 200
+
+
+def test_bbox_crop_windows_match_reference_build():
+    if O.ref() is None:
+        pytest.skip("reference tree not present")
+    rng = np.random.Generator(np.random.PCG64(35))
+    for k in range(4):
+        n = 300
+        counts = rng.integers(1, 9, n)
+        tot = int(counts.sum())
+        ctr, sz = rng.uniform(0.02, 0.98, (tot, 2)), rng.uniform(0.01, 0.8, (tot, 2))
+        boxes = np.concatenate([np.clip(ctr - sz / 2, 0, 1), np.clip(ctr + sz / 2, 0, 1)], 1).astype(np.float32)
+        offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        img_w = rng.integers(16, 4000, n).astype(np.int32)
+        seed, overlap = int(rng.integers(0, 2 ** 31)), k % 2
+        want = O.ref_random_bbox_crop(boxes, offsets, img_w, seed, bool(overlap))
+        assert np.array_equal(O.BBoxCropSampler(seed, bool(overlap)).windows(boxes, offsets, img_w), want), k
+        assert np.array_equal(_product_bbox_windows(seed, overlap, boxes, offsets, img_w), want), k
+
+
 def test_meta_node_restatements_are_consistent():
     """The crop / flip / resize meta-node restatements on hand-checked cases (the node classes themselves need the
     OpenVX graph and are not compiled here)."""
