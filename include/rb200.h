@@ -36,6 +36,22 @@ RB200_API int rb200_release(rb200_context ctx);
 RB200_API int rb200_get_status(rb200_context ctx);
 RB200_API const char* rb200_get_error_message(rb200_context ctx);
 RB200_API void rb200_get_timing(rb200_context ctx, unsigned long long out_load_decode_process_transfer[4]);
+/* [extension] Device time per launch. The reference times its stages on the host (TimingDbg,
+ * include/pipeline/timing_debug.h:36-100); with profiling on, this pipeline also brackets the upload and every kernel
+ * launch of a batch with CUDA events on its stream and adds the elapsed device times up when the batch is returned by
+ * rb200_run. Choose before rb200_verify; RB200_PROFILE=1 in the environment turns it on for every context. Off by
+ * default (an event record per launch on the loader thread). rb200_get_step_timing writes up to `capacity` entries -
+ * "upload" first, then one per launch of the plan in order - and returns the number of entries there are.
+ * The pipeline also marks its stages as NVTX ranges ("rb200 tables", "rb200 upload", "rb200 decode", "rb200 launches")
+ * for timeline tools, and RB200_LOG_LEVEL (0 silent, 1 errors - the default, 2 plan at verify and a timing summary at
+ * release) controls what it writes to stderr. */
+typedef struct rb200_step_timing {
+    char name[32];               /* "upload", "resample", "pointwise", "warp_affine", "normalize", "transpose" */
+    double gpu_us;               /* device time accumulated over `batches` batches */
+    unsigned long long batches;
+} rb200_step_timing;
+RB200_API int rb200_set_profiling(rb200_context ctx, int on);
+RB200_API size_t rb200_get_step_timing(rb200_context ctx, rb200_step_timing* out, size_t capacity);
 /* rocalGetRemainingImages / rocalIsEmpty (rocal_api_info.h:66-74): fed but not yet returned samples */
 RB200_API size_t rb200_get_remaining_images(rb200_context ctx);
 /* Extensions without a reference counterpart: how host-resident source pixels reach the kernels.

@@ -104,6 +104,8 @@ typedef struct rb200_resample_params {
     int32_t* status;             /* where a kernel that gives up on a bounded wait writes 1: a 4-byte word the device can
                                     write (device memory, or mapped pinned host memory); NULL = the library-wide word of
                                     this device that rb200k_device_status() reads */
+    uint64_t arena_bytes;        /* size of the source arena, 0 = unknown; see "Sizes and the bounds-checking build" */
+    uint64_t out_bytes;          /* size of the output buffer, 0 = unknown */
 } rb200_resample_params;
 
 /* Resize / ResizeCropMirror / ResizeMirrorNormalize / fused Resize+CropMirrorNormalize.
@@ -169,6 +171,8 @@ typedef struct rb200_pointwise_params {
     int32_t arith;               /* RB200_ARITH_EXACT (0) or RB200_ARITH_FAST (1), see below */
     int32_t overlap;             /* as rb200_resample_params.overlap */
     int32_t* status;             /* as rb200_resample_params.status */
+    uint64_t arena_bytes;        /* as rb200_resample_params.arena_bytes / out_bytes */
+    uint64_t out_bytes;
 } rb200_pointwise_params;
 
 /* Crop / Flip / CropMirrorNormalize / Brightness / Contrast / Hue / Saturation / ColorTwist
@@ -207,6 +211,9 @@ typedef struct rb200_warp_params {
     int32_t out_w, out_h;
     int32_t fill_padding;
     int32_t overlap;             /* as rb200_resample_params.overlap */
+    int32_t* status;             /* as rb200_resample_params.status (only the bounds-checking build writes it) */
+    uint64_t arena_bytes;        /* as rb200_resample_params.arena_bytes / out_bytes */
+    uint64_t out_bytes;
 } rb200_warp_params;
 
 /* replaces: vxExtRppWarpAffine (node_warp_affine.cpp:61), vxExtRppRotate (node_rotate.cpp:43). */
@@ -291,6 +298,8 @@ typedef struct rb200_normalize_params {
     int32_t fill_padding;        /* 1 = elements outside a sample's window are written as 0 */
     float mean[3], stddev[3];    /* per-channel values for the statistic(s) that are not computed */
     float scale, shift;
+    uint64_t arena_bytes;        /* as rb200_resample_params.arena_bytes / out_bytes; trouble goes to the library-wide */
+    uint64_t out_bytes;          /* status word */
 } rb200_normalize_params;
 
 RB200_API size_t rb200k_normalize_scratch_bytes(int n, int max_w, int max_h, int axis_mask);
@@ -365,12 +374,35 @@ RB200_API int rb200k_pointwise_probe(const uint8_t* arena, const rb200_pointwise
                            void* stream, uint64_t wait_cycles, int skip_row);
 
 /* ---------------------------------------------------------------------------------------
+ * Sizes and the bounds-checking build
+ * ------------------------------------------------------------------------------------- */
+
+/* The source arena. Every sample table addresses its image as arena + src_offset with a row pitch of src_stride
+ * bytes. The staging copies fetch whole 16-byte granules (by address), so a launch may read from the granule that
+ * holds the first byte of a sample's source rectangle to the end of the granule that holds its last byte: an arena
+ * whose images end within 15 bytes of an allocation that is not a multiple of 16 bytes long must be padded. Device and
+ * pinned host allocations are far coarser than that, so only sub-allocated arenas need care.
+ *
+ * out_bytes (resample, pointwise, warp, normalize parameter blocks): when non-zero, every build refuses, with
+ * RB200_E_INVALID and before anything is launched, a call whose dense output (n x out_h x out_w x 3 elements) does not
+ * fit. The kernels store nowhere else.
+ *
+ * arena_bytes: when non-zero, the BOUNDS-CHECKING BUILD of the library (`python -m rocal_b200.build --debug-bounds`,
+ * librocal_b200_bounds.so; rb200k_version() ends in "+bounds") checks, inside the kernels, each sample's source
+ * rectangle as its table row describes it, and every staging copy it issues, against [arena, arena + arena_bytes)
+ * widened to whole granules. A sample or a copy that fails is not read: the kernel writes 2 to the launch's status
+ * word (see "Bounded waits" for where that word lives), leaves that sample's output unwritten or incomplete, and
+ * returns normally; nothing traps and the context stays usable. The release build ignores the field and performs no
+ * such checks. rb200k_transpose and the box kernels take no sizes and are not covered. */
+
+/* ---------------------------------------------------------------------------------------
  * Misc
  * ------------------------------------------------------------------------------------- */
 
-/* The library-wide status word of the current device: 0 = fine; 1 = a kernel launched without a status pointer of
- * its own gave up on one of its bounded waits (a copy that never completed) since the last call, its output is then
- * incomplete; -1 = the query itself failed. Synchronises with the device. */
+/* The library-wide status word of the current device, read and cleared: 0 = fine; 1 = a kernel launched without a
+ * status pointer of its own gave up on one of its bounded waits (a copy that never completed) since the last call, its
+ * output is then incomplete; 2 = (bounds-checking build) a kernel found a sample or a copy outside the arena and did
+ * not read it; -1 = the query itself failed. Synchronises with the device. */
 RB200_API int rb200k_device_status(void);
 
 /* Text of the last error on the calling thread ("" if none). */
@@ -379,7 +411,7 @@ RB200_API const char* rb200k_last_error(void);
 /* Number of kernel launches issued through this library by the calling process so far. */
 RB200_API uint64_t rb200k_launch_count(void);
 
-/* Build identification: "rocal_b200 <version> sm_100a". */
+/* Build identification: "rocal_b200 <version> sm_100a", with "+bounds" appended by the bounds-checking build. */
 RB200_API const char* rb200k_version(void);
 
 #ifdef __cplusplus

@@ -23,7 +23,8 @@ class _ResampleParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32),
-                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 class _PointwiseParams(ctypes.Structure):
@@ -32,12 +33,14 @@ class _PointwiseParams(ctypes.Structure):
                 ("color_op", ctypes.c_int32), ("normalize", ctypes.c_int32),
                 ("fill_padding", ctypes.c_int32), ("reverse_channels", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("arith", ctypes.c_int32),
-                ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 class _WarpParams(ctypes.Structure):
     _fields_ = [("out", ctypes.c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
-                ("fill_padding", ctypes.c_int32), ("overlap", ctypes.c_int32)]
+                ("fill_padding", ctypes.c_int32), ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 _lib = None

@@ -53,6 +53,12 @@ fused_jpeg_crop_file_source = _proto("rb200_fused_jpeg_crop_file_source", _P, _P
                                      POINTER(c_float), POINTER(c_float), c_uint, c_int, c_int, c_uint, c_uint, c_int, c_int)
 set_random_crop_decoder = _proto("rb200_set_random_crop_decoder", c_int, _P, POINTER(c_float), POINTER(c_float), c_uint)
 get_decoder_crop_windows = _proto("rb200_get_decoder_crop_windows", c_int, _P, POINTER(c_uint), POINTER(c_uint))
+class StepTiming(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 32), ("gpu_us", ctypes.c_double), ("batches", ctypes.c_ulonglong)]
+
+
+set_profiling = _proto("rb200_set_profiling", c_int, _P, c_int)
+get_step_timing = _proto("rb200_get_step_timing", c_size_t, _P, POINTER(StepTiming), c_size_t)
 random_bbox_crop = _proto("rb200_random_bbox_crop", c_int, _P, c_int, c_int, c_uint)
 get_bbox_crop_windows = _proto("rb200_get_bbox_crop_windows", c_int, _P, POINTER(c_float))
 bbox_crop_windows = _proto("rb200_bbox_crop_windows", c_int, c_uint, c_int, c_int, POINTER(c_float), POINTER(c_int), c_size_t,

@@ -4,7 +4,8 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "librocal_b200.so")
+# RB200_LIBRARY names another build of the same library (the bounds-checking one, a sanitizer build)
+LIB_PATH = os.environ.get("RB200_LIBRARY") or os.path.join(_PKG, "librocal_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -21,7 +22,8 @@ class ResampleParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32),
-                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 class PointwiseParams(ctypes.Structure):
@@ -30,12 +32,14 @@ class PointwiseParams(ctypes.Structure):
                 ("color_op", ctypes.c_int32), ("normalize", ctypes.c_int32),
                 ("fill_padding", ctypes.c_int32), ("reverse_channels", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("arith", ctypes.c_int32),
-                ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p)]
+                ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 class WarpParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32),
-                ("fill_padding", ctypes.c_int32), ("overlap", ctypes.c_int32)]
+                ("fill_padding", ctypes.c_int32), ("overlap", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 class BoxEncoderParams(ctypes.Structure):
@@ -53,7 +57,8 @@ class NormalizeParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
                 ("axis_mask", ctypes.c_int32), ("compute_mean", ctypes.c_int32), ("compute_stddev", ctypes.c_int32),
                 ("fill_padding", ctypes.c_int32), ("mean", ctypes.c_float * 3), ("stddev", ctypes.c_float * 3),
-                ("scale", ctypes.c_float), ("shift", ctypes.c_float)]
+                ("scale", ctypes.c_float), ("shift", ctypes.c_float),
+                ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 
 lib.rb200k_normalize_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]

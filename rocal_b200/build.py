@@ -1,6 +1,11 @@
 """Builds librocal_b200.so (CUDA kernels + C-ABI + host pipeline) in-tree for sm_100a.
 
-    python -m rocal_b200.build [--force] [--verbose]
+    python -m rocal_b200.build [--force] [--verbose] [--debug-bounds]
+
+--debug-bounds builds librocal_b200_bounds.so instead: the same sources with RB200_DEBUG_BOUNDS defined, in which the
+kernels check every sample's source rectangle and every staging copy against the arena size the caller states and
+report through the status word (include/rb200_kernels.h, "Sizes and the bounds-checking build"). Load it by setting
+RB200_LIBRARY to its path.
 
 nvcc cross-compiles without a GPU. The library links the CUDA runtime statically, so it loads
 in any process whether or not another CUDA runtime (e.g. torch's) is already present.
@@ -32,17 +37,23 @@ def headers():
             glob.glob(os.path.join(ROOT, "include", "*.h")))
 
 
-def build(force=False, verbose=False):
-    os.makedirs(OBJ_DIR, exist_ok=True)
+LIB_BOUNDS = os.path.join(PKG, "librocal_b200_bounds.so")
+
+
+def build(force=False, verbose=False, debug_bounds=False):
+    lib = LIB_BOUNDS if debug_bounds else LIB
+    obj_dir = OBJ_DIR + ("_bounds" if debug_bounds else "")
+    defines = ["-DRB200_DEBUG_BOUNDS"] if debug_bounds else []
+    os.makedirs(obj_dir, exist_ok=True)
     hdr_time = max([os.path.getmtime(h) for h in headers()] + [os.path.getmtime(__file__)])
     objs, procs = [], []
     for src in sources():
-        obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
         objs.append(obj)
         if (not force and os.path.exists(obj) and os.path.getmtime(obj) > os.path.getmtime(src)
                 and os.path.getmtime(obj) > hdr_time):
             continue
-        cmd = [NVCC] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
+        cmd = [NVCC] + ARCH + COMMON + defines + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
@@ -54,11 +65,11 @@ def build(force=False, verbose=False):
             sys.stderr.write("nvcc failed for %s\n" % src)
     if failed:
         raise RuntimeError("rocal_b200: nvcc build failed")
-    if procs or force or not os.path.exists(LIB):
-        cmd = [NVCC] + ARCH + ["-shared", "-o", LIB] + objs + ["-Xlinker", "--exclude-libs,ALL", "-lpthread"]
+    if procs or force or not os.path.exists(lib):
+        cmd = [NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-Xlinker", "--exclude-libs,ALL", "-lpthread"]
         subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, debug_bounds="--debug-bounds" in sys.argv))

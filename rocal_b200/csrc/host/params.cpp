@@ -12,6 +12,14 @@ ParameterFactory::ParameterFactory() {
     set_seed(rd());
 }
 
+// Parameters and their handles live as long as the process: a handle may be created before any context exists and be
+// shared by several.
+ParameterFactory::~ParameterFactory() {
+    for (auto* p : _ints) delete p;
+    for (auto* p : _floats) delete p;
+    for (const void* h : _handles) ::operator delete(const_cast<void*>(h));
+}
+
 void ParameterFactory::set_seed(unsigned seed) {
     std::lock_guard<std::mutex> lk(_mutex);
     _seed = seed;

@@ -196,6 +196,8 @@ class ParameterFactory {
 
     bool owns(const void* handle);
 
+    ~ParameterFactory();
+
    private:
     ParameterFactory();
     int64_t next_seed();

@@ -1,11 +1,15 @@
 #include "pipeline.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <algorithm>
 #include <cstdio>
 
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
+#include <optional>
 
 namespace rb200 {
 
@@ -30,6 +34,22 @@ static inline unsigned long long now_us() {
                std::chrono::steady_clock::now().time_since_epoch())
         .count();
 }
+
+int log_level() {
+    static const int level = [] {
+        const char* e = std::getenv("RB200_LOG_LEVEL");
+        return e && *e ? std::atoi(e) : 1;
+    }();
+    return level;
+}
+
+// A named range on the profiler's timeline (NVTX; costs a few nanoseconds when no tool is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 // ------------------------------------------------------------------------------------------
 // Host-side size rules
@@ -286,6 +306,14 @@ Pipeline::~Pipeline() {
     _cv_work.notify_all();
     _cv_ready.notify_all();
     if (_worker.joinable()) _worker.join();
+    if (log_level() >= 2) {
+        std::fprintf(stderr, "[rb200] host time (us): load %llu, decode %llu, tables+launch %llu, transfer %llu\n", _t_load.load(),
+                     _t_decode.load(), _t_process.load(), _t_transfer.load());
+        for (const StepTiming& t : _step_timing)
+            if (t.batches)
+                std::fprintf(stderr, "[rb200]   %-12s %10.1f us device time per batch over %llu batches\n", t.name.c_str(),
+                             t.gpu_us / (double)t.batches, t.batches);
+    }
     cudaSetDevice(_gpu_id);
     if (_stream) cudaStreamSynchronize(_stream);
     if (_meta_stream) cudaStreamSynchronize(_meta_stream);
@@ -294,6 +322,8 @@ Pipeline::~Pipeline() {
         if (t->scratch) cudaFree(t->scratch);
     }
     for (auto& s : _slots) {
+        for (cudaEvent_t ev : s.step_ev)
+            if (ev) cudaEventDestroy(ev);
         if (s.done) cudaEventDestroy(s.done);
         if (s.consumer_done) cudaEventDestroy(s.consumer_done);
         if (s.h_status) cudaFreeHost(s.h_status);
@@ -738,7 +768,25 @@ void Pipeline::verify() {
         TensorImpl* t = _tensors[(size_t)id].get();
         if (t->is_output && !t->is_source) _output_list.items.push_back(t);
     }
+    if (const char* e = std::getenv("RB200_PROFILE")) _profiling = _profiling || std::atoi(e) != 0;
+    if (_profiling) {
+        _step_timing.clear();
+        _step_timing.push_back({"upload", 0.0, 0});
+        for (const Step& st : _steps) _step_timing.push_back({step_name(st), 0.0, 0});
+    }
+    if (log_level() >= 2) {
+        std::fprintf(stderr, "[rb200] plan: batch %zu, %zu launches per batch, ring depth %zu\n", _batch, _steps.size(), _depth);
+        for (size_t k = 0; k < _steps.size(); k++) {
+            TensorImpl* o = _tensors[_steps[k].out_tensor].get();
+            std::fprintf(stderr, "[rb200]   step %zu: %s -> %d x %d, %zu bytes%s\n", k, step_name(_steps[k]).c_str(), o->max_w, o->max_h,
+                         (size_t)o->data_size(), o->is_output ? " (output)" : "");
+        }
+    }
     for (auto& s : _slots) {
+        if (_profiling) {
+            s.step_ev.resize(_steps.size() + 2, nullptr);
+            for (auto& ev : s.step_ev) RB200_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDefault));
+        }
         RB200_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
         RB200_CUDA(cudaEventCreateWithFlags(&s.consumer_done, cudaEventDisableTiming));
         RB200_CUDA(cudaHostAlloc((void**)&s.h_status, 64, cudaHostAllocMapped));
@@ -1465,6 +1513,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     t0 = now_us();
 
     // ---- 2. per-sample tables ----
+    std::optional<NvtxRange> tables_range;
+    tables_range.emplace("rb200 tables");
     s.boxes = b.boxes;
     s.labels = b.labels;
     s.counts = b.counts;
@@ -1629,7 +1679,11 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             }
         }
     }
+    tables_range.reset();
+    s.step_ev_valid = false;
+    if (_profiling) RB200_CUDA(cudaEventRecord(s.step_ev[0], _stream));
     if (b.kind == InputBatch::ENCODED) {
+        NvtxRange range("rb200 decode");
         unsigned long long tl = now_us();
         _jpeg_dst.resize(n);
         _jpeg_pitch.resize(n);
@@ -1643,6 +1697,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         _h2d_bytes += enc;
         _t_decode += now_us() - tl;
     } else if (host_input) {
+        NvtxRange range("rb200 upload");
         unsigned long long tl = now_us();
         upload_sources(b, arena_used, (const uint8_t*)s.h_tables);
         _t_load += now_us() - tl;
@@ -1652,7 +1707,10 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         _h2d_bytes += _steps.size() * n * 64;
     }
 
+    if (_profiling) RB200_CUDA(cudaEventRecord(s.step_ev[1], _stream));
+
     // ---- 3. launches ----
+    NvtxRange launch_range("rb200 launches");
     for (size_t k = 0; k < _steps.size(); k++) {
         const Step& st = _steps[k];
         TensorImpl* out = _tensors[st.out_tensor].get();
@@ -1663,6 +1721,10 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         const void* h_tabk = h_tab + k * n * 64;
         int out_dtype = out->dtype == ROCAL_FP32 ? RB200_FP32 : (out->dtype == ROCAL_FP16 ? RB200_FP16 : RB200_UINT8);
         int out_layout = out->lay == ROCAL_NCHW ? RB200_NCHW : RB200_NHWC;
+        // sizes of what the launch reads and writes (checked by the bounds-checking build of the kernels)
+        TensorImpl* in_t = _tensors[st.in_tensor].get();
+        const uint64_t in_bytes = in_t->is_source ? (uint64_t)b.arena_bytes : (uint64_t)in_t->data_size();
+        const uint64_t out_bytes = (uint64_t)out->data_size();
         int rc = 0;
         if (st.kind == Step::RESAMPLE) {
             rb200_resample_params p{};
@@ -1679,6 +1741,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             p.fill_padding = (st.post >= 0 || _nodes[st.resize].kind != NodeKind::RESIZE) ? 1 : 0;
             p.interpolation = _nodes[st.resize].interpolation;
             p.status = s.d_status;
+            p.arena_bytes = in_bytes;
+            p.out_bytes = out_bytes;
             rc = probe_cycles ? rb200k_resample_probe(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk,
                                                       (int)n, &p, _stream, probe_cycles, probe_skip)
                               : rb200k_resample(base, (const rb200_resample_sample*)d_tab, (const rb200_resample_sample*)h_tabk, (int)n, &p, _stream);
@@ -1705,6 +1769,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             p.fill_padding = (st.window >= 0) ? 1 : 0;
             p.arith = _arith;
             p.status = s.d_status;
+            p.arena_bytes = in_bytes;
+            p.out_bytes = out_bytes;
             rc = probe_cycles ? rb200k_pointwise_probe(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk,
                                                        (int)n, &p, _stream, probe_cycles, probe_skip)
                               : rb200k_pointwise(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p, _stream);
@@ -1725,6 +1791,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             }
             p.scale = nd.stat_scale;
             p.shift = nd.stat_shift;
+            p.arena_bytes = in_bytes;
+            p.out_bytes = out_bytes;
             rc = rb200k_normalize(base, (const rb200_pointwise_sample*)d_tab, (const rb200_pointwise_sample*)h_tabk, (int)n, &p,
                                   _norm_scratch, _norm_scratch_bytes, _stream);
         } else if (st.kind == Step::TRANSPOSE) {
@@ -1738,10 +1806,15 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             p.out_w = out->max_w;
             p.out_h = out->max_h;
             p.fill_padding = 1;
+            p.status = s.d_status;
+            p.arena_bytes = in_bytes;
+            p.out_bytes = out_bytes;
             rc = rb200k_warp_affine(base, (const rb200_warp_sample*)d_tab, (int)n, &p, _stream);
         }
         if (rc != 0) RB200_THROW(rb200k_last_error());
+        if (_profiling) RB200_CUDA(cudaEventRecord(s.step_ev[k + 2], _stream));
     }
+    s.step_ev_valid = _profiling;
     if (arena_used >= 0) RB200_CUDA(cudaEventRecord(_arena_free[arena_used], _stream));
 
     // ---- 4. box encoder / box IoU matcher ----
@@ -1873,9 +1946,13 @@ void Pipeline::run() {
     unsigned long long t0 = now_us();
     RB200_CUDA(cudaEventSynchronize(s.done));
     _t_process += now_us() - t0;
-    if (*static_cast<volatile int*>(s.h_status) != 0) {
-        // a kernel of this batch gave up on a bounded wait for its source rows and left its output incomplete
+    if (s.step_ev_valid) collect_step_timing(s);
+    if (const int st = *static_cast<volatile int*>(s.h_status)) {
         *s.h_status = 0;
+        if (st == 2)    // bounds-checking build of the kernels
+            RB200_THROW("rocalRun: a kernel of this batch found a sample outside its source arena and did not read it; the batch's "
+                        "outputs are incomplete");
+        // a kernel of this batch gave up on a bounded wait for its source rows and left its output incomplete
         RB200_THROW("rocalRun: a kernel of this batch gave up waiting for its staged source rows; the batch's outputs are incomplete");
     }
     for (auto& t : _tensors) {
@@ -2039,6 +2116,41 @@ void Pipeline::to_tensor(void* out_ptr, int layout, int dtype, const float* mul,
     if (tmp) cudaFree(tmp);
     if (rc != 0) RB200_THROW(rb200k_last_error());
     if (err != cudaSuccess) RB200_THROW(std::string("rocalToTensor: ") + cudaGetErrorString(err));
+}
+
+void Pipeline::set_profiling(bool on) {
+    if (_verified) RB200_THROW("profiling must be chosen before rocalVerify");
+    _profiling = on;
+}
+
+std::string Pipeline::step_name(const Step& st) const {
+    switch (st.kind) {
+        case Step::RESAMPLE: return "resample";
+        case Step::POINTWISE: return "pointwise";
+        case Step::NORMALIZE: return "normalize";
+        case Step::TRANSPOSE: return "transpose";
+        default: return "warp_affine";
+    }
+}
+
+// The batch's done event has completed, so every event of the slot has: device time between consecutive events.
+void Pipeline::collect_step_timing(Slot& s) {
+    std::lock_guard<std::mutex> lk(_prof_m);
+    for (size_t k = 0; k + 1 < s.step_ev.size() && k < _step_timing.size(); k++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, s.step_ev[k], s.step_ev[k + 1]) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+        }
+        _step_timing[k].gpu_us += (double)ms * 1000.0;
+        _step_timing[k].batches++;
+    }
+    s.step_ev_valid = false;
+}
+
+std::vector<StepTiming> Pipeline::step_timing() {
+    std::lock_guard<std::mutex> lk(_prof_m);
+    return _step_timing;
 }
 
 TimingInfo Pipeline::timing() {

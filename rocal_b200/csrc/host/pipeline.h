@@ -226,7 +226,20 @@ struct Slot {
     unsigned decoder_batch_seed = 0;
     size_t n = 0;
     std::string error;
+    std::vector<cudaEvent_t> step_ev;        // profiling: before the upload, after it, after every launch of the batch
+    bool step_ev_valid = false;              // the events of this slot were recorded for the batch it holds
 };
+
+// One line of the per-launch device timing (profiling on): the name of the step, the device time it has taken so far
+// and the number of batches measured.
+struct StepTiming {
+    std::string name;
+    double gpu_us = 0.0;
+    unsigned long long batches = 0;
+};
+
+// RB200_LOG_LEVEL: 0 = silent, 1 = errors (default), 2 = also the plan at verify and a timing summary at release.
+int log_level();
 
 class Pipeline {
    public:
@@ -241,6 +254,10 @@ class Pipeline {
                                 unsigned shard_count, bool shuffle, bool loop, unsigned max_w, unsigned max_h, bool is_output,
                                 int last_batch_policy, bool pad_last_batch_repeated);
     // rocalFusedJpegCrop*: every image of an encoded source is cut to a random-resized-crop window before the graph
+    // Per-launch device timing with CUDA events (off by default; RB200_PROFILE=1 in the environment turns it on for
+    // every context). Must be chosen before verify().
+    void set_profiling(bool on);
+    std::vector<StepTiming> step_timing();
     void set_random_crop_decoder(const RandomCropRanges& r);
     // rocalRandomBBoxCrop: every image (and its boxes) of the source is cut to a window sampled around the boxes
     void set_random_bbox_crop(bool all_boxes_overlap, bool has_shape, uint32_t seed);
@@ -423,6 +440,11 @@ class Pipeline {
 
     // timing (us)
     std::atomic<unsigned long long> _t_load{0}, _t_decode{0}, _t_process{0}, _t_transfer{0};
+    bool _profiling = false;
+    std::mutex _prof_m;
+    std::vector<StepTiming> _step_timing;    // [0] = upload, [1 + k] = step k, last = box encoder / matcher
+    void collect_step_timing(Slot& s);
+    std::string step_name(const Step& st) const;
     std::atomic<unsigned long long> _h2d_bytes{0};   // bytes the worker uploaded (pixels, tables, boxes)
     int _upload_mode = UPLOAD_ZERO_COPY;
     std::unique_ptr<BBoxCropSampler> _bbox_crop;

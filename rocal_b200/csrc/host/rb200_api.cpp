@@ -19,7 +19,7 @@ inline FloatParam* FP(rb200_param p) { return static_cast<FloatParam*>(p); }
 
 void report(Pipeline* p, const std::exception& e) {
     p->capture_error(e.what());
-    std::cerr << e.what() << '\n';
+    if (rb200::log_level() >= 1) std::cerr << e.what() << '\n';
 }
 
 #define CTX_OR(ret)                                        \
@@ -479,6 +479,29 @@ int rb200_get_decoder_crop_windows(rb200_context ctx, unsigned* xywh, unsigned* 
         return ROCAL_RUNTIME_ERROR;
     }
     return ROCAL_OK;
+}
+
+int rb200_set_profiling(rb200_context ctx, int on) {
+    CTX_OR(ROCAL_CONTEXT_INVALID);
+    try {
+        P(ctx)->set_profiling(on != 0);
+    } catch (const std::exception& e) {
+        report(P(ctx), e);
+        return ROCAL_INVALID_PARAMETER_TYPE;
+    }
+    return ROCAL_OK;
+}
+
+size_t rb200_get_step_timing(rb200_context ctx, rb200_step_timing* out, size_t capacity) {
+    if (ctx == nullptr) return 0;
+    const std::vector<rb200::StepTiming> v = P(ctx)->step_timing();
+    for (size_t i = 0; i < v.size() && i < capacity && out; i++) {
+        std::memset(&out[i], 0, sizeof(out[i]));
+        std::strncpy(out[i].name, v[i].name.c_str(), sizeof(out[i].name) - 1);
+        out[i].gpu_us = v[i].gpu_us;
+        out[i].batches = v[i].batches;
+    }
+    return v.size();
 }
 
 int rb200_random_bbox_crop(rb200_context ctx, int all_boxes_overlap, int has_shape, unsigned seed) {

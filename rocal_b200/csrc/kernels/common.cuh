@@ -26,6 +26,61 @@ constexpr unsigned long long kDefaultWaitCycles = 2000000000ull;   // about a se
         if (_rc) return _rc;                                           \
     } while (0)
 
+static inline uint64_t out_elem_size(int out_dtype) { return out_dtype == RB200_FP32 ? 4 : out_dtype == RB200_FP16 ? 2 : 1; }
+
+// ---- status word and the bounds-checking build ------------------------------------------------
+// A kernel reports trouble by writing its status word and returning normally: 1 = a bounded wait ran out,
+// 2 = (bounds-checking build only) a read would have left the source arena and was not made. The larger value stays.
+constexpr int kStatusWaitRanOut = 1, kStatusOutOfBounds = 2;
+__device__ __forceinline__ void raise_status(int* status, int value = kStatusWaitRanOut) {
+    volatile int* p = reinterpret_cast<volatile int*>(status);
+    if (*p < value) *p = value;
+    __threadfence_system();
+}
+
+#ifdef RB200_DEBUG_BOUNDS
+constexpr bool kCheckBounds = true;
+#else
+constexpr bool kCheckBounds = false;
+#endif
+
+// The addresses a launch may read: the source arena widened to whole 16-byte granules (the staging copies fetch the
+// granules that enclose a row span; device and pinned allocations are far coarser than 16 bytes). hi == nullptr: the
+// caller gave no size, nothing is checked. The checks below compile to nothing outside the bounds-checking build.
+struct ArenaBounds {
+    const uint8_t* lo;
+    const uint8_t* hi;
+};
+static inline ArenaBounds arena_bounds(const uint8_t* arena, uint64_t bytes) {
+    ArenaBounds b = {nullptr, nullptr};
+    if (kCheckBounds && bytes) {
+        b.lo = reinterpret_cast<const uint8_t*>((uintptr_t)arena & ~(uintptr_t)15);
+        b.hi = reinterpret_cast<const uint8_t*>(((uintptr_t)arena + bytes + 15) & ~(uintptr_t)15);
+    }
+    return b;
+}
+// One contiguous read [p, p + bytes).
+__device__ __forceinline__ bool span_in_bounds(const ArenaBounds& b, const void* p, size_t bytes, int* status) {
+    if (!kCheckBounds || b.hi == nullptr) return true;
+    const uint8_t* q = reinterpret_cast<const uint8_t*>(p);
+    if (q >= b.lo && q <= b.hi && bytes <= (size_t)(b.hi - q)) return true;
+    raise_status(status, kStatusOutOfBounds);
+    return false;
+}
+// The w x h pixel rectangle at (x, y) of a 3-byte-per-pixel image, each row span widened to its 16-byte granules.
+__device__ __forceinline__ bool rect_in_bounds(const ArenaBounds& b, const uint8_t* img, uint32_t stride, int x, int y, int w, int h,
+                                               int* status) {
+    if (!kCheckBounds || b.hi == nullptr) return true;
+    bool ok = x >= 0 && y >= 0 && w > 0 && h > 0;
+    if (ok) {
+        const uintptr_t first = ((uintptr_t)img + (size_t)y * stride + (size_t)x * 3) & ~(uintptr_t)15;
+        const uintptr_t end = ((uintptr_t)img + (size_t)(y + h - 1) * stride + (size_t)(x + w) * 3 + 15) & ~(uintptr_t)15;
+        ok = first >= (uintptr_t)b.lo && end <= (uintptr_t)b.hi && first < end;
+    }
+    if (!ok) raise_status(status, kStatusOutOfBounds);
+    return ok;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------
 // Kernels of this library that follow one another in a stream overlap their ramp-up with the predecessor's
 // tail: a launch made with launch_overlapped() may be scheduled as soon as every CTA of the preceding kernel has

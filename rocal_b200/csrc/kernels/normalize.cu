@@ -32,6 +32,8 @@ struct NormLaunch {
     float mean[3], stddev[3], scale, shift;
     StatSlot* stats;
     int th;                         // rows per tile
+    int* status;                    // bounds-checking build: written with 2 when a sample's window leaves the arena
+    ArenaBounds bounds;             // bounds-checking build: the addresses the launch may read
 };
 
 // Slot index of element (y, x, c) under a mask; the slot count is stat_slots().
@@ -74,6 +76,7 @@ __global__ void __launch_bounds__(192) normalize_sums_kernel(const uint8_t* __re
     const int w = min(s.roi_w, L.out_w), h = min(s.roi_h, L.out_h);
     const int y0 = blockIdx.x * L.th, y1 = min(y0 + L.th, h);
     if (y0 >= h || w <= 0) return;
+    if (!rect_in_bounds(L.bounds, arena + s.src_offset, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status)) return;
     const uint8_t* img = arena + s.src_offset + (size_t)s.roi_y * s.src_stride + (size_t)s.roi_x * 3;
     StatSlot* st = L.stats + (size_t)n * L.slots;
     const int rowbytes = 3 * w;
@@ -217,6 +220,9 @@ __global__ void __launch_bounds__(256) normalize_apply_kernel(const uint8_t* __r
     const int y0 = blockIdx.x * L.th;
     const int rows = min(L.th, L.out_h - y0);
     if (rows <= 0) return;
+    if (w > 0 && h > 0 &&
+        !rect_in_bounds(L.bounds, arena + s.src_offset, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status))
+        return;
     const uint8_t* img = arena + s.src_offset + (size_t)s.roi_y * s.src_stride + (size_t)s.roi_x * 3;
     OutT* out = reinterpret_cast<OutT*>(L.out) + ((size_t)n * L.out_h + y0) * L.out_w * 3;
     const StatSlot* st = L.stats ? L.stats + (size_t)n * L.slots : nullptr;
@@ -316,6 +322,17 @@ extern "C" int rb200k_normalize(const uint8_t* arena, const rb200_pointwise_samp
     L.stats = nullptr;
     L.slots = 0;
     L.th = 16;
+    L.status = default_status_word();
+    L.bounds = arena_bounds(arena, p->arena_bytes);
+    if (kCheckBounds && p->arena_bytes && !L.status) {
+        set_error("rb200k_normalize: the device's status word cannot be addressed");
+        return RB200_E_CUDA;
+    }
+    if (p->out_bytes && (uint64_t)n * p->out_w * p->out_h * 3 * out_elem_size(p->out_dtype) > p->out_bytes) {
+        set_error("rb200k_normalize: %d samples of %d x %d x 3 elements do not fit the %llu-byte output", n, p->out_w, p->out_h,
+                  (unsigned long long)p->out_bytes);
+        return RB200_E_INVALID;
+    }
     const int tiles = (p->out_h + L.th - 1) / L.th;
     if (computes) {
         L.slots = stat_slots(L.mask, p->out_w, p->out_h);

@@ -37,6 +37,7 @@ struct PointwiseLaunch {
     long long wait_cycles;   // vector kernel: limit of that wait, SM clock cycles
     int skip_row;        // vector kernel, self-test: the copy of this tile row is never issued (-1: all are)
     int overlap;         // vector kernel: 1 = independent of the preceding kernel, wait for it only before exit
+    ArenaBounds bounds;  // bounds-checking build: the addresses the launch may read
 };
 
 __device__ __forceinline__ uint32_t pw_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -469,7 +470,9 @@ __global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP 
     OutT* out = reinterpret_cast<OutT*>(L.out);
     const int w = min(s.roi_w, L.out_w);
     const int h = min(s.roi_h, L.out_h);
-    const int rows = min(L.th, h - tile_y0);
+    // bounds-checking build: a sample whose window leaves the arena is reported and none of it is read
+    const bool src_ok = rect_in_bounds(L.bounds, img, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status);
+    const int rows = src_ok ? min(L.th, h - tile_y0) : 0;
     const size_t plane = (size_t)L.out_w * L.out_h;
     // first source column of every row of the window (a horizontal flip shows the last w columns)
     const int x_src0 = s.flip_h ? (s.roi_x + s.roi_w - w) : s.roi_x;
@@ -500,6 +503,7 @@ __global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP 
                 const uint32_t m = (uint32_t)((uintptr_t)g & 15);
                 const uint32_t bytes = ((m + (uint32_t)w * 3 + 15) >> 4) << 4;
                 if (r == L.skip_row) continue;     // self-test: this row's bytes stay expected and never arrive
+                if (!span_in_bounds(L.bounds, g - m, bytes, L.status)) continue;   // (bounds-checking build)
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(pw_smem_u32(stage + (size_t)r * L.pitch)), "l"(g - m), "r"(bytes), "r"(bar) : "memory");
             }
@@ -510,8 +514,7 @@ __global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP 
             if (threadIdx.x == 0) {
                 stage_flag = ok ? 1 : 0;
                 if (!ok) {
-                    *reinterpret_cast<volatile int*>(L.status) = 1;
-                    __threadfence_system();
+                    raise_status(L.status);
                     pw_mbar_wait_bounded(bar, 0, L.wait_cycles);   // second bounded chance for copies still in flight
                 }
             }
@@ -721,8 +724,10 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const uint8_t* __restric
     OutT* out = reinterpret_cast<OutT*>(L.out);
     const int w = min(s.roi_w, L.out_w);
     const int h = min(s.roi_h, L.out_h);
+    // (bounds-checking build; the second image of a blend may live in another allocation and is not checked)
+    const bool src_ok = rect_in_bounds(L.bounds, img, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status);
 
-    if (xi < w) {
+    if (xi < w && src_ok) {
         const int sx = s.roi_x + (s.flip_h ? (s.roi_w - 1 - xi) : xi);
         const int rows = min(L.th, h - tile_y0);
         for (int j = 0; j < rows; j++) {
@@ -835,6 +840,12 @@ static int pointwise_launch(const uint8_t* arena, const rb200_pointwise_sample* 
     L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
     L.skip_row = skip_row;
     L.overlap = p->overlap ? 1 : 0;
+    L.bounds = arena_bounds(arena, p->arena_bytes);
+    if (p->out_bytes && (uint64_t)n * p->out_w * p->out_h * 3 * out_elem_size(p->out_dtype) > p->out_bytes) {
+        set_error("rb200k_pointwise: %d samples of %d x %d x 3 elements do not fit the %llu-byte output", n, p->out_w, p->out_h,
+                  (unsigned long long)p->out_bytes);
+        return RB200_E_INVALID;
+    }
     int ext_w = p->out_w, ext_h = p->out_h;
     if (h_samples && !p->fill_padding) {
         ext_w = 1; ext_h = 1;

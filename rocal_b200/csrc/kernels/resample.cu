@@ -50,6 +50,7 @@ struct ResampleLaunch {
     long long wait_cycles;   // stream kernel: limit of every mbarrier wait, SM clock cycles
     int skip_row;       // stream kernel, self-test: the producer issues no copy from this strip row on (-1: all)
     int overlap;        // stream kernel: 1 = independent of the preceding kernel, wait for it only before exit
+    ArenaBounds bounds; // bounds-checking build: the addresses the launch may read
 };
 
 struct RowInfo {
@@ -264,11 +265,6 @@ __device__ __forceinline__ void column_setup(int xi0, bool second, int crop_x, i
 // stage by arriving on its "empty" mbarrier. Every wait is bounded: on a time-out the kernel sets
 // the launch's status word, drains the copies it has in flight (bounded again) and returns.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void raise_status(int* status) {
-    *reinterpret_cast<volatile int*>(status) = 1;
-    __threadfence_system();
-}
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -344,7 +340,10 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
     const int rows_valid = min(L.strip_rows, ch - y_begin);
     const int cols_valid = min(TW, cw - tile_x0);
 
-    if (rows_valid > 0 && cols_valid > 0) {
+    // bounds-checking build: a sample whose source rectangle leaves the arena is reported and none of it is read
+    const bool src_ok = rect_in_bounds(L.bounds, arena + sp->src_offset, sp->src_stride, sp->roi_x, sp->roi_y, sp->roi_w, sp->roi_h,
+                                       L.status);
+    if (rows_valid > 0 && cols_valid > 0 && src_ok) {
         const uint8_t* img = arena + sp->src_offset;
         const uint32_t stride = sp->src_stride;
         const int roi_x = sp->roi_x, roi_w = sp->roi_w;
@@ -416,6 +415,8 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                     const uint2 bytes = *reinterpret_cast<const uint2*>(&rowtab[j].b0);
                     const StreamSrc src = srctab[j];
                     const uint32_t bar = bar_base + 8 * s;
+                    if (!span_in_bounds(L.bounds, src.g0, bytes.x, L.status) || !span_in_bounds(L.bounds, src.g1, bytes.y, L.status))
+                        break;                         // (bounds-checking build) the copy is not made; the consumers give up
                     mbar_expect_tx(bar, bytes.x + bytes.y);
                     bulk_g2s(stage_base + (2 * s) * L.pitch, src.g0, bytes.x, bar);
                     bulk_g2s(stage_base + (2 * s + 1) * L.pitch, src.g1, bytes.y, bar);
@@ -511,7 +512,10 @@ __global__ void __launch_bounds__(256) resample_staged_kernel(const uint8_t* __r
     const int rows_valid = min(L.th, ch - tile_y0);     // rows of this tile inside the crop
     const int cols_valid = min(TW, cw - tile_x0);       // columns of this tile inside the crop
 
-    if (rows_valid > 0 && cols_valid > 0) {
+    // bounds-checking build: a sample whose source rectangle leaves the arena is reported and none of it is read
+    const bool src_ok = rect_in_bounds(L.bounds, arena + sp->src_offset, sp->src_stride, sp->roi_x, sp->roi_y, sp->roi_w, sp->roi_h,
+                                       L.status);
+    if (rows_valid > 0 && cols_valid > 0 && src_ok) {
         const uint8_t* img = arena + sp->src_offset;
         const uint32_t stride = sp->src_stride;
         const int roi_x = sp->roi_x, roi_w = sp->roi_w;
@@ -596,6 +600,7 @@ __global__ void __launch_bounds__(256) resample_staged_kernel(const uint8_t* __r
                 const int need = (int)(m + nbytes + 15) >> 4;
                 const uint8_t* ga = g - m;
                 uint8_t* sd = stage + (size_t)r * L.pitch;
+                if (!span_in_bounds(L.bounds, ga, (size_t)need * 16, L.status)) continue;   // (bounds-checking build)
                 for (int ck = lane; ck < need; ck += 32) cp_async16(sd + ck * 16, ga + ck * 16);
             }
             cp_async_commit_wait_all();
@@ -673,7 +678,8 @@ __global__ void __launch_bounds__(256) resample_direct_kernel(const uint8_t* __r
     const int rows_valid = min(L.th, ch - tile_y0);
     const int cols_valid = min(TW, cw - tile_x0);
 
-    if (rows_valid > 0 && cols_valid > 0) {
+    const bool src_ok = rect_in_bounds(L.bounds, img, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status);
+    if (rows_valid > 0 && cols_valid > 0 && src_ok) {
         const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
         const float ratio_h = div_rn((float)s.roi_h, (float)s.dst_h);
         const float off_w = mul_rn(sub_rn(ratio_w, 1.0f), 0.5f);
@@ -978,7 +984,8 @@ __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t*
     const int ch = min(s.crop_h, L.out_h);
     const int rows_valid = min(L.th, ch - tile_y0);
 
-    if (rows_valid > 0 && xi < cw) {
+    const bool src_ok = rect_in_bounds(L.bounds, img, s.src_stride, s.roi_x, s.roi_y, s.roi_w, s.roi_h, L.status);
+    if (rows_valid > 0 && xi < cw && src_ok) {
         const float ratio_w = div_rn((float)s.roi_w, (float)s.dst_w);
         const float ratio_h = div_rn((float)s.roi_h, (float)s.dst_h);
         const TriAxis ax = filter_axis_make(ratio_w, L.filter), ay = filter_axis_make(ratio_h, L.filter);
@@ -1096,6 +1103,12 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
     L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
     L.skip_row = skip_row;
     L.overlap = p->overlap ? 1 : 0;
+    L.bounds = arena_bounds(arena, p->arena_bytes);
+    if (p->out_bytes && (uint64_t)n * p->out_w * p->out_h * 3 * out_elem_size(p->out_dtype) > p->out_bytes) {
+        set_error("rb200k_resample: %d samples of %d x %d x 3 elements do not fit the %llu-byte output", n, p->out_w, p->out_h,
+                  (unsigned long long)p->out_bytes);
+        return RB200_E_INVALID;
+    }
 
     // Extent the grid has to cover.
     int ext_w = p->out_w, ext_h = p->out_h;

@@ -50,4 +50,8 @@ int read_default_status_word() {
 extern "C" int rb200k_device_status(void) { return rb200::read_default_status_word(); }
 extern "C" const char* rb200k_last_error(void) { return rb200::g_error; }
 extern "C" uint64_t rb200k_launch_count(void) { return rb200::g_launches.load(std::memory_order_relaxed); }
+#ifdef RB200_DEBUG_BOUNDS
+extern "C" const char* rb200k_version(void) { return "rocal_b200 0.1 sm_100a+bounds"; }
+#else
 extern "C" const char* rb200k_version(void) { return "rocal_b200 0.1 sm_100a"; }
+#endif

@@ -29,6 +29,8 @@ struct WarpLaunch {
     uint32_t magic;     // 0x4B000000
     int vec_store;      // rows of the output start on 4-byte boundaries
     int overlap;        // 1 = independent of the preceding kernel, wait for it only before exit
+    int* status;        // bounds-checking build: written with 2 when a sample's source leaves the arena
+    ArenaBounds bounds; // bounds-checking build: the addresses the launch may read
 };
 
 struct WarpMap {
@@ -187,7 +189,9 @@ __device__ __forceinline__ void warp_affine_tile(const uint8_t* __restrict__ are
     const uint8_t* img = arena + s.src_offset;
     const int w = min(s.dst_w, L.out_w), h = min(s.dst_h, L.out_h);
     const int W = s.src_w, H = s.src_h;
-    const bool tile_valid = tile_x0 < w && tile_y0 < h && W > 0 && H > 0;
+    // (bounds-checking build) a sample whose source image leaves the arena is reported and treated as empty
+    const bool tile_valid = tile_x0 < w && tile_y0 < h && W > 0 && H > 0 &&
+                            rect_in_bounds(L.bounds, img, s.src_stride, 0, 0, W, H, L.status);
     if (!tile_valid && !L.fill_padding) return;
 
     WarpMap M;
@@ -324,6 +328,17 @@ extern "C" int rb200k_warp_affine(const uint8_t* arena, const rb200_warp_sample*
     L.magic = 0x4B000000u;
     L.vec_store = (p->out_w % 4 == 0) && (((uintptr_t)p->out & 3) == 0);
     L.overlap = p->overlap ? 1 : 0;
+    L.status = p->status ? p->status : default_status_word();
+    if (!L.status) {
+        set_error("rb200k_warp_affine: the device's status word cannot be addressed");
+        return RB200_E_CUDA;
+    }
+    L.bounds = arena_bounds(arena, p->arena_bytes);
+    if (p->out_bytes && (uint64_t)n * p->out_w * p->out_h * 3 > p->out_bytes) {
+        set_error("rb200k_warp_affine: %d samples of %d x %d x 3 bytes do not fit the %llu-byte output", n, p->out_w, p->out_h,
+                  (unsigned long long)p->out_bytes);
+        return RB200_E_INVALID;
+    }
     L.tiles_x = (p->out_w + kWarpTileW - 1) / kWarpTileW;
     int tiles_y = (p->out_h + kWarpTileH - 1) / kWarpTileH;
     dim3 grid((unsigned)(L.tiles_x * tiles_y), (unsigned)n);

@@ -35,10 +35,16 @@ def _alloc_out(n, out_w, out_h, dtype, layout, device, out):
     return out
 
 
+def _sizes(p, arena, out, arena_bytes, out_bytes):
+    """The sizes a launch states to the library: the tensors' own unless the caller overrides them."""
+    p.arena_bytes = int(arena.numel() * arena.element_size() if arena_bytes is None else arena_bytes)
+    p.out_bytes = int(out.numel() * out.element_size() if out_bytes is None else out_bytes)
+
+
 def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
              fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0,
-             status=None, probe=None, overlap=False):
-    """rb200k_resample. overlap=True states that the launch is independent of the kernel enqueued just before it. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
+             status=None, probe=None, overlap=False, arena_bytes=None, out_bytes=None):
+    """rb200k_resample. arena_bytes / out_bytes: the sizes stated to the library (None: those of the tensors). overlap=True states that the launch is independent of the kernel enqueued just before it. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
     already on the device (uploaded here when None). staged=False withholds the host table from
     the launch so that the kernel gathers straight from global memory; path=1 (RB200_RESAMPLE_PATH_TILE)
     forces the shared-memory tile kernel. status: an int32 CUDA tensor that receives 1 when a bounded wait gives up
@@ -59,6 +65,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
         p.add[c] = float(add[c]) if add is not None else 0.0
     p.status = status.data_ptr() if status is not None else None
     p.overlap = 1 if overlap else 0
+    _sizes(p, arena, out, arena_bytes, out_bytes)
     h_ptr = samples.ctypes.data_as(ctypes.c_void_p) if staged else None
     if probe is not None:
         check(lib.rb200k_resample_probe(arena.data_ptr(), d_samples.data_ptr(), h_ptr, n, ctypes.byref(p),
@@ -71,8 +78,8 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
 
 def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.UINT8, out_layout=T.NHWC,
               mul=None, add=None, reverse_channels=False, fill_padding=True, out=None, d_samples=None,
-              stream=None, arith=0, status=None, probe=None, overlap=False):
-    """rb200k_pointwise. arith: 0 exact, 1 fast colour arithmetic; status / probe as for resample."""
+              stream=None, arith=0, status=None, probe=None, overlap=False, arena_bytes=None, out_bytes=None):
+    """rb200k_pointwise. arena_bytes / out_bytes as for resample. arith: 0 exact, 1 fast colour arithmetic; status / probe as for resample."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, out_dtype, out_layout, arena.device, out)
     if d_samples is None:
@@ -90,6 +97,7 @@ def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.U
     p.arith = int(arith)
     p.overlap = 1 if overlap else 0
     p.status = status.data_ptr() if status is not None else None
+    _sizes(p, arena, out, arena_bytes, out_bytes)
     if probe is not None:
         check(lib.rb200k_pointwise_probe(arena.data_ptr(), d_samples.data_ptr(), samples.ctypes.data_as(ctypes.c_void_p), n,
                                          ctypes.byref(p), _stream_ptr(stream), int(probe[0]), int(probe[1])),
@@ -100,8 +108,9 @@ def pointwise(arena, samples, out_w, out_h, color_op=T.COLOR_NONE, out_dtype=T.U
     return out
 
 
-def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_samples=None, stream=None, overlap=False):
-    """rb200k_warp_affine: uint8 NHWC output."""
+def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_samples=None, stream=None, overlap=False,
+                status=None, arena_bytes=None, out_bytes=None):
+    """rb200k_warp_affine: uint8 NHWC output. status / arena_bytes / out_bytes as for resample."""
     n = len(samples)
     out = _alloc_out(n, out_w, out_h, T.UINT8, T.NHWC, arena.device, out)
     if d_samples is None:
@@ -111,6 +120,8 @@ def warp_affine(arena, samples, out_w, out_h, fill_padding=True, out=None, d_sam
     p.out_w, p.out_h = out_w, out_h
     p.fill_padding = 1 if fill_padding else 0
     p.overlap = 1 if overlap else 0
+    p.status = status.data_ptr() if status is not None else None
+    _sizes(p, arena, out, arena_bytes, out_bytes)
     check(lib.rb200k_warp_affine(arena.data_ptr(), d_samples.data_ptr(), n, ctypes.byref(p), _stream_ptr(stream)),
           "rb200k_warp_affine")
     return out
@@ -186,6 +197,7 @@ def normalize(arena, samples, out_w, out_h, axis_mask=3, mean=None, stddev=None,
     if d_samples is None:
         d_samples = to_device_table(samples, arena.device)
     p = _normalize_params(out, out_w, out_h, out_dtype, axis_mask, mean, stddev, scale, shift, fill_padding)
+    _sizes(p, arena, out, None, None)
     need = normalize_scratch_bytes(n, out_w, out_h, axis_mask) if (mean is None or stddev is None) else 0
     if scratch is None and need:
         scratch = torch.empty(need, dtype=torch.uint8, device=arena.device)

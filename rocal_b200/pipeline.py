@@ -370,6 +370,17 @@ class Pipeline(object):
         self._check(C.get_decoder_crop_windows(self._handle, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint)), ctypes.byref(seed)))
         return out, int(seed.value)
 
+    def set_profiling(self, on=True):
+        """[extension] Per-launch device timing with CUDA events; call before build()."""
+        self._check(C.set_profiling(self._handle, int(bool(on))))
+
+    def step_timing(self):
+        """[extension] [(name, device microseconds per batch, batches measured)]: the upload, then every launch of the
+        plan in order. Empty unless profiling is on."""
+        buf = (C.StepTiming * 64)()
+        k = min(int(C.get_step_timing(self._handle, buf, 64)), 64)
+        return [(buf[i].name.decode(), buf[i].gpu_us / max(1, buf[i].batches), int(buf[i].batches)) for i in range(k)]
+
     def get_bbox_crop_windows(self):
         """[extension] The windows rocalRandomBBoxCrop sampled for the current batch, float32 [N, 4] = (x, y, w, h) as
         fractions of the image; get_decoder_crop_windows() gives the same windows in pixels."""

@@ -287,6 +287,35 @@ def test_random_bbox_crop_cuts_images_and_boxes(cuda):
     pipe.rocal_release()
 
 
+def test_per_launch_device_timing(cuda):
+    """Profiling on: the upload and every launch of a batch are bracketed by CUDA events; the accumulated device times
+    come back by step, in plan order, once per returned batch."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(37)
+    n = 32
+    pipe = Pipeline(batch_size=n, device_id=0, seed=3)
+    with pipe:
+        img = _source(500, 400)
+        r = fn.resize(img, resize_width=224, resize_height=224, scaling_mode=types.SCALING_MODE_STRETCH)
+        b = fn.brightness(r, brightness=1.1, brightness_shift=3.0)
+        pipe.set_outputs(fn.rotate(b, angle=10.0))
+        pipe.set_profiling(True)
+    pipe.build()
+    assert pipe.step_timing()[0][2] == 0
+    for _ in range(6):
+        arena, hs, ws, offs = S.make_images(rng, n, (200, 400), (300, 500))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+    t = pipe.step_timing()
+    assert [x[0] for x in t] == ["upload", "resample", "pointwise", "warp_affine"]
+    for name, us, batches in t:
+        assert batches == 6 and 0.5 < us < 50000.0, t
+    info = pipe.timing_info()
+    assert info is not None
+    pipe.rocal_release()
+
+
 def test_normalize_and_transpose_through_the_api(cuda):
     """rocalNormalize with computed per-channel statistics, with given statistics, and per-image statistics behind a
     crop; rocalTranspose HWC -> CHW and the height / width swap. Four outputs of one graph against the oracle."""

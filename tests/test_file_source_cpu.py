@@ -1,10 +1,12 @@
 """The folder reader behind rocalJpegFileSource (rocal_b200/csrc/host/file_source.cpp), compiled into a small
-harness: class numbering, extension filter, shard ranges, last-batch policies, seeded shuffle, looping."""
+harness: class numbering, extension filter, shard ranges, last-batch policies, seeded shuffle, looping. The harnesses
+are built with the address and undefined-behaviour sanitizers: a finding aborts the run and fails the test."""
 import os
 import subprocess
 
 import pytest
 
+SANITIZE = ["-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer"]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HOST = os.path.join(ROOT, "rocal_b200", "csrc", "host")
 
@@ -13,7 +15,7 @@ HOST = os.path.join(ROOT, "rocal_b200", "csrc", "host")
 def harness(tmp_path_factory):
     d = tmp_path_factory.mktemp("fs")
     exe = str(d / "harness")
-    subprocess.run(["g++", "-std=c++17", "-O1", "-I", HOST, os.path.join(ROOT, "tests", "harness", "file_source_harness.cpp"),
+    subprocess.run(["g++", "-std=c++17", "-O1"] + SANITIZE + ["-I", HOST, os.path.join(ROOT, "tests", "harness", "file_source_harness.cpp"),
                     os.path.join(HOST, "file_source.cpp"), "-o", exe], check=True)
     data = d / "data"
     for cls, count in (("cat", 3), ("dog", 4), ("emu", 2)):
@@ -28,9 +30,11 @@ def harness(tmp_path_factory):
         (flat / ("f%d.jpeg" % i)).write_bytes(b"x")
 
     def run(root, batch, shard_id, shard_count, shuffle=0, loop_batches=0, policy=0, pad_repeat=0, file_list=None):
-        out = subprocess.run([exe, str(root), str(batch), str(shard_id), str(shard_count), str(shuffle), str(loop_batches),
-                              str(policy), str(pad_repeat)] + ([str(file_list)] if file_list else []),
-                             capture_output=True, text=True).stdout.strip().splitlines()
+        r = subprocess.run([exe, str(root), str(batch), str(shard_id), str(shard_count), str(shuffle), str(loop_batches),
+                            str(policy), str(pad_repeat)] + ([str(file_list)] if file_list else []),
+                           capture_output=True, text=True)
+        assert "Sanitizer" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-2000:]
+        out = r.stdout.strip().splitlines()
         if out and out[0].startswith("ERROR"):
             return out[0], [], []
         return out[0], [ln.split("|")[0].split() for ln in out[1:]], [int(ln.split("pad")[1]) for ln in out[1:]]
@@ -81,7 +85,7 @@ def test_coco_annotation_reader(tmp_path):
     annotations kept, unknown images dropped, output sorted by file name."""
     import json
     exe = str(tmp_path / "coco")
-    subprocess.run(["g++", "-std=c++17", "-O1", "-I", HOST, os.path.join(ROOT, "tests", "harness", "coco_reader_harness.cpp"),
+    subprocess.run(["g++", "-std=c++17", "-O1"] + SANITIZE + ["-I", HOST, os.path.join(ROOT, "tests", "harness", "coco_reader_harness.cpp"),
                     os.path.join(HOST, "coco_reader.cpp"), "-o", exe], check=True)
     doc = {
         "info": {"description": "synthetic \"set\"", "nested": [1, [2, {"a": None}], True], "year": 2026},
@@ -102,8 +106,9 @@ def test_coco_annotation_reader(tmp_path):
     path.write_text(json.dumps(doc, indent=1))
 
     def run(avoid):
-        out = subprocess.run([exe, str(path), str(avoid)], capture_output=True, text=True).stdout.strip().splitlines()
-        return [ln.split(" | ") for ln in out]
+        r = subprocess.run([exe, str(path), str(avoid)], capture_output=True, text=True)
+        assert "Sanitizer" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-2000:]
+        return [ln.split(" | ") for ln in r.stdout.strip().splitlines()]
 
     rows = run(0)
     assert [r[0] for r in rows] == ["a_img.jpg 100 50 1", "b_img.jpg 200 100 2", "c_empty.jpg 64 64 0"]
