@@ -100,7 +100,8 @@ typedef struct rb200_resample_params {
     int32_t path;                /* RB200_RESAMPLE_PATH_*: which of the bilinear kernels runs; the results are identical */
     int32_t overlap;             /* 1 = this launch may overlap the tail of the kernel enqueued just before it in the
                                     stream, see "Overlapping launches" below; 0 = plain stream order */
-    int32_t reserved;
+    int32_t strip_rows;          /* tuning: output rows per CTA of the row-streaming kernel, 4..32; 0 = chosen by the
+                                    library from the grid size and the kernel's occupancy. The results do not depend on it */
     int32_t* status;             /* where a kernel that gives up on a bounded wait writes 1: a 4-byte word the device can
                                     write (device memory, or mapped pinned host memory); NULL = the library-wide word of
                                     this device that rb200k_device_status() reads */

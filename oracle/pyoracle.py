@@ -23,7 +23,7 @@ class _ResampleParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("out_layout", ctypes.c_int32),
                 ("normalize", ctypes.c_int32), ("fill_padding", ctypes.c_int32),
                 ("mul", ctypes.c_float * 3), ("add", ctypes.c_float * 3), ("interpolation", ctypes.c_int32), ("path", ctypes.c_int32),
-                ("overlap", ctypes.c_int32), ("reserved", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("overlap", ctypes.c_int32), ("strip_rows", ctypes.c_int32), ("status", ctypes.c_void_p),
                 ("arena_bytes", ctypes.c_uint64), ("out_bytes", ctypes.c_uint64)]
 
 

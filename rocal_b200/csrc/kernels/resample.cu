@@ -25,6 +25,9 @@
 // TL*(1-wy)(1-wx) + (TR*(1-wy)wx + (BL*wy(1-wx) + BR*wy*wx)), round-to-nearest-even uint8.
 #include <cstdlib>
 
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace rb200 {
@@ -1013,13 +1016,53 @@ __global__ void __launch_bounds__(256) resample_triangular_kernel(const uint8_t*
 
 enum { MODE_DIRECT = 0, MODE_STAGED = 1, MODE_STREAM = 2, MODE_TRIANGULAR = 3 };
 
+// CTAs of `kernel` the whole device holds at once for this block size and shared-memory request (asked of the
+// runtime once per combination).
+static long resident_ctas(const void* kernel, int threads, size_t smem) {
+    struct Entry { const void* k; int threads; size_t smem; int dev; long ctas; };
+    static std::mutex m;
+    static std::vector<Entry> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(m);
+    for (const Entry& e : cache)
+        if (e.k == kernel && e.threads == threads && e.smem == smem && e.dev == dev) return e.ctas;
+    int per_sm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm <= 0) {
+        cudaGetLastError();
+        per_sm = 4;
+    }
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        cudaGetLastError();
+        sms = 148;
+    }
+    cache.push_back({kernel, threads, smem, dev, (long)per_sm * sms});
+    return cache.back().ctas;
+}
+
+// Output rows per CTA of the row-streaming kernel. Strips are balanced (ceil(ext_h / k) rows for a whole number k of
+// strips, so no CTA gets a short leftover). A grid of at least four waves at 32 rows keeps 32 (least set-up per row).
+// Smaller grids are latency-bound - a CTA's life is its set-up plus one copy round trip per ring refill - and run
+// fastest with about 14 rows per CTA (measured on 64 .. 256 images of 224 rows: 14 beats 8, 16 and 32 by 3 .. 40 %);
+// grids that would not even fill half the device at 14 rows go down to 8.
+static int choose_strip_rows(long resident, long columns_of_ctas, int ext_h) {
+    auto ctas_at = [&](int rows) { return columns_of_ctas * ((ext_h + rows - 1) / rows); };
+    int target = 14;
+    if (ctas_at(32) >= 4 * resident) target = 32;
+    else if (ctas_at(14) * 2 < resident) target = 8;
+    int k = (ext_h + target / 2) / target;
+    if (k < 1) k = 1;
+    int rows = (ext_h + k - 1) / k;
+    if (rows > kMaxStripRows) rows = kMaxStripRows;
+    if (rows < 4) rows = ext_h < 4 ? ext_h : 4;
+    return rows < 1 ? 1 : rows;
+}
+
 template <typename OutT, int LAYOUT>
 static int launch_typed(const uint8_t* arena, const rb200_resample_sample* samples, int n, ResampleLaunch L,
                         int mode, size_t smem, cudaStream_t stream) {
     L.pair_ok = (L.out_w % 2 == 0) && (((uintptr_t)L.out) % (2 * sizeof(OutT)) == 0);
     if (mode == MODE_STREAM) {
-        int strips = (L.ext_h + L.strip_rows - 1) / L.strip_rows;
-        dim3 grid((unsigned)(L.tiles_x * strips), (unsigned)n);
         auto k = L.normalize ? resample_stream_kernel<OutT, LAYOUT, true> : resample_stream_kernel<OutT, LAYOUT, false>;
         if (smem > 48 * 1024) {
             int rc = check_cuda(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
@@ -1027,7 +1070,11 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
             if (rc) return rc;
         }
         // compute threads rounded up to whole warps + one producer warp
-        cudaError_t le = launch_overlapped(k, grid, dim3((unsigned)(((L.twh + 31) & ~31) + 32)), smem, stream, arena, samples, L);
+        const int threads = ((L.twh + 31) & ~31) + 32;
+        if (L.strip_rows == 0) L.strip_rows = choose_strip_rows(resident_ctas((const void*)k, threads, smem), n * L.tiles_x, L.ext_h);
+        int strips = (L.ext_h + L.strip_rows - 1) / L.strip_rows;
+        dim3 grid((unsigned)(L.tiles_x * strips), (unsigned)n);
+        cudaError_t le = launch_overlapped(k, grid, dim3((unsigned)threads), smem, stream, arena, samples, L);
         if (le != cudaSuccess) return check_cuda(le, "launch of resample_stream_kernel");
     } else if (mode == MODE_STAGED) {
         int tiles_y = (L.ext_h + L.th - 1) / L.th;
@@ -1077,6 +1124,10 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
     }
     if (p->interpolation < RB200_INTERP_BILINEAR || p->interpolation > RB200_INTERP_NEAREST) {
         set_error("rb200k_resample: bad interpolation %d", p->interpolation);
+        return RB200_E_INVALID;
+    }
+    if (p->strip_rows != 0 && (p->strip_rows < 4 || p->strip_rows > kMaxStripRows)) {
+        set_error("rb200k_resample: strip_rows %d is outside 4..%d", p->strip_rows, kMaxStripRows);
         return RB200_E_INVALID;
     }
     if (p->path != RB200_RESAMPLE_PATH_AUTO && p->path != RB200_RESAMPLE_PATH_TILE) {
@@ -1166,11 +1217,7 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
                 mode = MODE_STREAM;
                 L.ns = ns;
                 L.ns_log2 = ns == 4 ? 2 : 1;
-                int rows = 32;
-                // shorter strips until the grid holds about twelve CTAs per SM (measured: 16-row strips beat 32-row
-                // ones by 7 % on a 128-image batch of 300-row outputs; 1024-image batches keep 32 rows)
-                while (rows > 8 && (long)n * L.tiles_x * ((ext_h + rows - 1) / rows) < 12 * 148) rows >>= 1;
-                L.strip_rows = rows;
+                L.strip_rows = p->strip_rows;      // 0: chosen in launch_typed, where the kernel's occupancy is known
                 smem = 128 + (sizeof(StreamRow) + sizeof(StreamSrc)) * kMaxStripRows + (size_t)2 * ns * pitch;
             }
         }

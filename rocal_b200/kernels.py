@@ -43,8 +43,8 @@ def _sizes(p, arena, out, arena_bytes, out_bytes):
 
 def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, mul=None, add=None,
              fill_padding=True, out=None, d_samples=None, stream=None, staged=True, interpolation=0, path=0,
-             status=None, probe=None, overlap=False, arena_bytes=None, out_bytes=None):
-    """rb200k_resample. arena_bytes / out_bytes: the sizes stated to the library (None: those of the tensors). overlap=True states that the launch is independent of the kernel enqueued just before it. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
+             status=None, probe=None, overlap=False, arena_bytes=None, out_bytes=None, strip_rows=0):
+    """rb200k_resample. strip_rows: rows per CTA of the row-streaming kernel (0 = the library chooses). arena_bytes / out_bytes: the sizes stated to the library (None: those of the tensors). overlap=True states that the launch is independent of the kernel enqueued just before it. `samples`: numpy RESAMPLE_SAMPLE table (host); `d_samples`: the same table
     already on the device (uploaded here when None). staged=False withholds the host table from
     the launch so that the kernel gathers straight from global memory; path=1 (RB200_RESAMPLE_PATH_TILE)
     forces the shared-memory tile kernel. status: an int32 CUDA tensor that receives 1 when a bounded wait gives up
@@ -60,6 +60,7 @@ def resample(arena, samples, out_w, out_h, out_dtype=T.FP32, out_layout=T.NCHW, 
     p.fill_padding = 1 if fill_padding else 0
     p.interpolation = int(interpolation)
     p.path = int(path)
+    p.strip_rows = int(strip_rows)
     for c in range(3):
         p.mul[c] = float(mul[c]) if mul is not None else 1.0
         p.add[c] = float(add[c]) if add is not None else 0.0
