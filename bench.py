@@ -47,9 +47,9 @@ H_RANGE = (300, 1080)
 W_RANGE = (300, 1080)
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one resample launch, per image, from
-#   ncu --set full --clock-control none -k regex:resample_stream -s 4 -c 1 python bench.py --batch 512 --steps 2 --warmup 1 --no-cpu-baseline --no-other-configs
+#   ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:resample -s 4 -c 2 python bench.py --batch 512 --steps 2 --warmup 3 --no-cpu-baseline --no-other-configs
 # (a 512-image launch: traffic grows in proportion to the images processed, so it is scaled by the batch size).
-NCU_TRAFFIC_BYTES_PER_IMAGE = (337829376 + 126903808) / 512.0
+NCU_TRAFFIC_BYTES_PER_IMAGE = (337206784 + 127553792) / 512.0
 
 
 def peak_hbm():
@@ -511,7 +511,7 @@ def run_ops(args):
                 a, dt = torch.from_numpy(arena).to(dev), K.to_device_table(t, dev)
                 out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device=dev)
                 fns.append(lambda a=a, t=t, dt=dt, out=out: K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, fill_padding=False, out=out, d_samples=dt,
-                                                                       overlap=ov))
+                                                                       overlap=ov, strip_rows=args.strip_rows))
             report("cfg0 resize+CMN fp32 NCHW (batch 64, 256..512 px)", n, _time_launches(fns, args.steps), algo)
         elif op in ("color_twist", "brightness", "contrast", "flip"):
             n, rot = args.batch or 256, 4
@@ -698,6 +698,7 @@ def main():
                     help="BASELINE configuration; 1 (default) is the headline workload, the others run on one GPU only")
     ap.add_argument("--op", default=None, help="operator-level cases, comma separated (see run_ops)")
     ap.add_argument("--no-overlap", action="store_true", help="--op cases: plain stream order between the launches")
+    ap.add_argument("--strip-rows", type=int, default=0, help="--op cfg0: output rows per CTA of the row-streaming kernel (0 = the library's choice)")
     ap.add_argument("--fast", action="store_true", help="colour operators with RB200_ARITH_FAST (--config 2 and the colour --op cases)")
     args = ap.parse_args()
     if args.op:

@@ -444,7 +444,11 @@ RB200_ROCAL void ROCAL_API_CALL rocalCopyEncodedBoxesAndLables(RocalContext p_co
 RB200_ROCAL RocalMetaData ROCAL_API_CALL rocalGetEncodedBoxesAndLables(RocalContext p_context, int num_encoded_boxes);
 
 /* ---- boxes of the current batch after the graph's crops and mirrors (rocal_api_meta_data.h:173-211): total
- * count, and one host tensor per sample - [count][4] float32 normalized ltrb, [count] int32 labels ---- */
+ * count, and one host tensor per sample - [count][4] float32 normalized ltrb, [count] int32 labels.
+ * DIFFERS FROM THE REFERENCE: coordinates are fractions of the image the boxes currently belong to (0..1), whatever
+ * the source. The reference's COCO reader keeps PIXEL coordinates (coco_meta_data_reader.cpp:140-325) and its meta
+ * nodes rescale them along the graph, so a caller that took pixels from rocalGetBoundingBoxCords multiplies by the
+ * output width / height here. ---- */
 RB200_ROCAL unsigned ROCAL_API_CALL rocalGetBoundingBoxCount(RocalContext rocal_context);
 RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxCords(RocalContext rocal_context);
 RB200_ROCAL RocalTensorList ROCAL_API_CALL rocalGetBoundingBoxLabel(RocalContext rocal_context);
