@@ -132,7 +132,13 @@ enum { RB200_MEM_HOST = 0, RB200_MEM_HOST_PINNED = 1, RB200_MEM_DEVICE = 2 };
 /* [extension] Feeds one batch as a single arena + per-image descriptors instead of n max-size slots
  * (which would move 3-4x the bytes for variable-size images). mem_kind says where the arena lives;
  * a device arena is used in place (no copy), a host arena is uploaded with one asynchronous copy.
- * The arena must stay valid until the batch has been returned by rb200_run. */
+ * The arena must stay valid until the batch has been returned by rb200_run.
+ * Reads reach the whole 16-byte granules (by address) that enclose each image's rows: device and pinned allocations
+ * cover that by themselves; an arena carved out of a larger buffer of the caller's should start on a 16-byte boundary
+ * and leave 15 readable bytes after its last image (nothing is ever written there, and an aligned 16-byte read never
+ * crosses a page, so a tighter arena cannot fault - it is merely read a few bytes beyond its ends).
+ * A RB200_MEM_DEVICE arena is read by the pipeline's own stream without any ordering against the stream that filled it:
+ * complete that work (an event the caller waits on, or a stream synchronisation) before feeding. */
 RB200_API int rb200_feed_ragged(rb200_context ctx, const void* arena, size_t arena_bytes,
                                 const rb200_image_desc* descs, size_t n, int mem_kind);
 /* [extension] JPEG streams with their lengths as size_t (same lifetime rule as rb200_feed_input), and JPEG

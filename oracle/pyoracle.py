@@ -5,6 +5,7 @@ Takes the same numpy tables as the CUDA path (layouts of include/rb200_kernels.h
 numpy arrays, so a parity test is `np.array_equal(gpu.cpu().numpy(), oracle(...))`.
 """
 import ctypes
+import math
 import os
 
 import numpy as np
@@ -737,6 +738,46 @@ def meta_flip(boxes, labels, offsets, roi_wh, h_flip, v_flip):
             if v_flip[i]:
                 q[1], q[3] = f32(h - q[3]), f32(h - q[1])
         per.append((b, l))
+    return _join(per)
+
+
+def meta_rotate(boxes, labels, offsets, roi_wh, angles_deg, dst_w, dst_h):
+    """RotateMetaNode (meta_node_rotate.cpp:27-103), in pixels as written: the corners of a box are rotated about the
+    image centres (source: roi / 2 in float; destination: size // 2), the new box is their bounding box with
+    l = min(0, .) and t = min(0, .), kept when inter / area(new box) >= 0.25 against the destination image and clipped
+    to it; a sample left without boxes gets the whole destination image with label 0."""
+    f32 = np.float32
+    W, H = f32(dst_w), f32(dst_h)
+    per = []
+    for i, (b, l) in enumerate(_split(boxes, labels, offsets)):
+        radian = f32(np.float64(f32(angles_deg[i])) * 3.14159265 / 180)
+        r0, r1 = f32(math.cos(float(radian))), f32(math.sin(float(radian)))
+        r2, r3 = f32(-1 * r1), r0
+        dcx, dcy = f32(int(dst_w) // 2), f32(int(dst_h) // 2)
+        scx, scy = f32(f32(roi_wh[i][0]) / 2), f32(f32(roi_wh[i][1]) / 2)
+        kb, kl = [], []
+        for q, lab in zip(b, l):
+            x, y = f32(q[0]), f32(q[1])
+            bw, bh = f32(q[2] - q[0]), f32(q[3] - q[1])
+
+            def rot(px, py):
+                return (f32(f32(f32(r0 * f32(px - scx)) + f32(r1 * f32(py - scy))) + dcx),
+                        f32(f32(f32(r2 * f32(px - scx)) + f32(r3 * f32(py - scy))) + dcy))
+            pts = [rot(x, y), rot(f32(x + bw), y), rot(x, f32(y + bh)), rot(f32(x + bw), f32(y + bh))]
+            xs, ys = [p[0] for p in pts], [p[1] for p in pts]
+            bl, bt = min(f32(0), min(xs)), min(f32(0), min(ys))
+            br, bb = max(xs), max(ys)
+            xa, ya, xb, yb = max(bl, f32(0)), max(bt, f32(0)), min(br, W), min(bb, H)
+            inter = f32(max(f32(0), f32(xb - xa)) * max(f32(0), f32(yb - ya)))
+            area = f32(f32(bb - bt) * f32(br - bl))
+            with np.errstate(divide="ignore", invalid="ignore"):
+                keep = f32(inter / area) >= f32(0.25)
+            if keep:
+                kb.append((max(f32(0), bl), max(f32(0), bt), min(W, br), min(H, bb)))
+                kl.append(lab)
+        if not kb:
+            kb, kl = [(0, 0, W, H)], [0]
+        per.append((kb, kl))
     return _join(per)
 
 

@@ -1125,6 +1125,62 @@ void Pipeline::mirror_boxes(Slot& s, const std::vector<int>& flags, bool vertica
     }
 }
 
+// Boxes behind a Rotate operator: RotateMetaNode::update_parameters (source/meta_data/meta_node_rotate.cpp:27-103),
+// in the pixel coordinates it works in. The four corners of a box are rotated about the image centres (source
+// centre = roi size / 2 in float, destination centre = size / 2 in integer arithmetic, as there), the new box is
+// their bounding box - with its left and top edge taken as min(0, .), as the node writes it, so every kept box starts
+// at the image's corner after the clip -, kept when at least a quarter of it lies in the destination image, clipped to
+// it; a sample left without boxes gets the whole destination image with label 0. Results are re-normalised to the
+// destination size.
+void Pipeline::rotate_boxes(Slot& s, const std::vector<float>& angle_deg, const std::vector<int>& in_w, const std::vector<int>& in_h,
+                            int dst_w, int dst_h) {
+    if (s.counts.empty()) return;
+    std::vector<float> nb;
+    std::vector<int> nl, nc(s.counts.size(), 0);
+    size_t box0 = 0;
+    const float W = (float)dst_w, H = (float)dst_h;
+    for (size_t i = 0; i < s.counts.size(); i++) {
+        const float radian = (float)((double)angle_deg[i] * 3.14159265 / 180);
+        const float r0 = (float)std::cos((double)radian), r1 = (float)std::sin((double)radian), r2 = -1 * r1, r3 = r0;
+        const float dcx = (float)(dst_w / 2), dcy = (float)(dst_h / 2);
+        const float scx = (float)in_w[i] / 2, scy = (float)in_h[i] / 2;
+        for (int j = 0; j < s.counts[i]; j++) {
+            const float* q = s.boxes.data() + (box0 + j) * 4;
+            const float x = q[0] * in_w[i], y = q[1] * in_h[i];
+            const float bw = q[2] * in_w[i] - x, bh = q[3] * in_h[i] - y;
+            const float x1 = (r0 * (x - scx)) + (r1 * (y - scy)) + dcx, y1 = (r2 * (x - scx)) + (r3 * (y - scy)) + dcy;
+            const float x2 = (r0 * ((x + bw) - scx)) + (r1 * (y - scy)) + dcx, y2 = (r2 * ((x + bw) - scx)) + (r3 * (y - scy)) + dcy;
+            const float x3 = (r0 * (x - scx)) + (r1 * ((y + bh) - scy)) + dcx, y3 = (r2 * (x - scx)) + (r3 * ((y + bh) - scy)) + dcy;
+            const float x4 = (r0 * ((x + bw) - scx)) + (r1 * ((y + bh) - scy)) + dcx,
+                        y4 = (r2 * ((x + bw) - scx)) + (r3 * ((y + bh) - scy)) + dcy;
+            float l = std::min(0.0f, std::min(x1, std::min(x2, std::min(x3, x4))));
+            float t = std::min(0.0f, std::min(y1, std::min(y2, std::min(y3, y4))));
+            float r = std::max(x1, std::max(x2, std::max(x3, x4)));
+            float b = std::max(y1, std::max(y2, std::max(y3, y4)));
+            const float xa = std::max(l, 0.f), ya = std::max(t, 0.f), xb = std::min(r, W), yb = std::min(b, H);
+            const float inter = std::max(0.f, xb - xa) * std::max(0.f, yb - ya);
+            const float area = (b - t) * (r - l);
+            if (inter / area >= 0.25f) {
+                nb.push_back(std::max(0.f, l) / W);
+                nb.push_back(std::max(0.f, t) / H);
+                nb.push_back(std::min(W, r) / W);
+                nb.push_back(std::min(H, b) / H);
+                nl.push_back(s.labels[box0 + j]);
+                nc[i]++;
+            }
+        }
+        if (nc[i] == 0) {
+            nb.insert(nb.end(), {0.f, 0.f, 1.f, 1.f});
+            nl.push_back(0);
+            nc[i] = 1;
+        }
+        box0 += (size_t)s.counts[i];
+    }
+    s.boxes.swap(nb);
+    s.labels.swap(nl);
+    s.counts.swap(nc);
+}
+
 void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
     size_t n = _batch;
     for (auto& a : b.anchors_x) _nodes[a.first].crop.next_anchor_x = a.second;
@@ -1230,9 +1286,13 @@ void Pipeline::update_nodes(const InputBatch& b, Slot& s) {
                 break;
             }
             case NodeKind::ROTATE: {
-                if (!s.counts.empty()) RB200_THROW("bounding boxes cannot follow a Rotate operator (its metadata rule is not implemented)");
                 nd.affine_v.resize(n * 6);
                 const auto& a = nd.angle->array();
+                if (!s.counts.empty()) {
+                    std::vector<float> deg(n);
+                    for (size_t i = 0; i < n; i++) deg[i] = a.size() == n ? a[i] : nd.angle->get();
+                    rotate_boxes(s, deg, in->roi_w, in->roi_h, out->max_w, out->max_h);
+                }
                 for (size_t i = 0; i < n; i++) {
                     float deg = a.size() == n ? a[i] : nd.angle->get();
                     float rad = deg * (float)(M_PI / 180.0);

@@ -340,6 +340,8 @@ class Pipeline {
                                 const std::vector<unsigned>& cw, const std::vector<unsigned>& ch,
                                 const std::vector<int>& in_w, const std::vector<int>& in_h, bool by_centre);
     void mirror_boxes(Slot& s, const std::vector<int>& flags, bool vertical = false);
+    void rotate_boxes(Slot& s, const std::vector<float>& angle_deg, const std::vector<int>& in_w, const std::vector<int>& in_h,
+                      int dst_w, int dst_h);
 
     size_t _batch;
     int _gpu_id;

@@ -228,6 +228,34 @@ def test_boxes_follow_ssd_crop(cuda):
     pipe.rocal_release()
 
 
+def test_boxes_follow_rotate(cuda):
+    """Boxes behind rocalRotate against the restatement of RotateMetaNode (corners rotated about the image centres,
+    bounding box with its left / top edge taken as min(0, .), quarter-area rule, clip to the destination)."""
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(38)
+    n = 16
+    pipe = Pipeline(batch_size=n, device_id=0, seed=41)
+    with pipe:
+        img = _source(400, 300)
+        angle = fn.random.uniform(range=(-60.0, 60.0))
+        pipe.set_outputs(fn.rotate(img, angle=angle, dest_width=320, dest_height=256))
+    pipe.build()
+    kept = 0
+    for _ in range(3):
+        arena, hs, ws, offs = S.make_images(rng, n, (120, 300), (160, 400))
+        boxes, labels, boffs = S.random_boxes(rng, n, (0, 8))
+        pipe.feed_boxes(boxes, labels, np.diff(boffs))
+        pipe.feed_ragged(arena, hs, ws, offs)
+        pipe.run()
+        rep = np.repeat(np.stack([ws, hs], 1).astype(np.float32), np.diff(boffs), axis=0)
+        px = (boxes * np.concatenate([rep, rep], 1)).astype(np.float32)
+        b, l, o = O.meta_rotate(px, labels, boffs, np.stack([ws, hs], 1), pipe.get_float_array(angle), 320, 256)
+        kept += _compare_boxes(pipe, b, l, o, [(320, 256)] * n)
+    assert kept > 30
+    pipe.rocal_release()
+
+
 def test_random_bbox_crop_cuts_images_and_boxes(cuda):
     """rocalRandomBBoxCrop on an external source, fed three ways (packed host arena, pinned arena read in place,
     max-size slots): the sampled windows are the pinned restatement's (the sampler's counter runs on across batches),

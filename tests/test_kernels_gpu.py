@@ -90,6 +90,29 @@ def test_resize_cmn_config1_full_batch(cuda):
     assert int(per.sum()) == int(ref.view(np.uint16).astype(np.uint64).sum())
 
 
+@pytest.mark.parametrize("n", [3, 64, 200])
+def test_strip_rows_do_not_change_the_result(cuda, n):
+    """The row-streaming kernel cuts the output into strips of rows per CTA; the library picks the strip height from the
+    grid size and the kernel's occupancy (8, about 14, or 32 rows), `strip_rows` forces it. Every choice - including
+    heights that leave a ragged last strip and the smallest and largest allowed - gives the oracle's bits; a value
+    outside 4..32 is refused."""
+    from rocal_b200 import kernels as K
+    from rocal_b200._lib import Rb200Error
+    rng = S.rng_for(0, 7 + n)
+    arena, hs, ws, offs = S.make_images(rng, n, (256, 512), (256, 512))
+    t = S.classification_tables(rng, hs, ws, offs)
+    mul, add = S.normalize_tables()
+    ref = O.resample(arena, t, 224, 224, T.FP32, T.NCHW, mul, add)
+    a = _dev(arena, cuda)
+    for rows in (0, 4, 5, 14, 15, 31, 32):
+        got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, strip_rows=rows).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), rows
+    for rows in (3, 33, -1):
+        with pytest.raises(Rb200Error):
+            K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, strip_rows=rows)
+    assert _device_status() == 0
+
+
 def test_resize_only_ragged_output(cuda):
     """Plain Resize: uint8 HWC out, per-sample output sizes inside a larger max-shape tensor; only
     the ROI is defined (padding not filled), up- and down-scaling, odd sizes."""

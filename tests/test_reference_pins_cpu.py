@@ -246,6 +246,20 @@ def test_bbox_crop_windows_match_reference_build():
         assert np.array_equal(_product_bbox_windows(seed, overlap, boxes, offsets, img_w), want), k
 
 
+def test_rotate_meta_restatement_on_hand_cases():
+    """RotateMetaNode restated: no rotation keeps the right / bottom edges and, as the node is written, pulls the left /
+    top edges to the image corner; a box rotated out of the destination is dropped and the sample gets the whole image."""
+    boxes = np.array([[20, 10, 60, 50]], dtype=np.float32)
+    b, l, o = O.meta_rotate(boxes, np.array([7], np.int32), np.array([0, 1], np.int32), [(100, 80)], [0.0], 100, 80)
+    assert l.tolist() == [7] and np.allclose(b, [[0, 0, 60, 50]], atol=1e-4)
+    # a quarter turn about the centre of a 100 x 100 image: x' = y, y' = 100 - x
+    b, l, o = O.meta_rotate(boxes, np.array([7], np.int32), np.array([0, 1], np.int32), [(100, 100)], [90.0], 100, 100)
+    assert l.tolist() == [7] and np.allclose(b, [[0, 0, 50, 80]], atol=1e-3)
+    far = np.array([[0, 0, 4, 4]], dtype=np.float32)
+    b, l, o = O.meta_rotate(far, np.array([7], np.int32), np.array([0, 1], np.int32), [(400, 400)], [45.0], 50, 50)
+    assert l.tolist() == [0] and b.tolist() == [[0, 0, 50, 50]]
+
+
 def test_meta_node_restatements_are_consistent():
     """The crop / flip / resize meta-node restatements on hand-checked cases (the node classes themselves need the
     OpenVX graph and are not compiled here)."""
