@@ -87,8 +87,12 @@ enum { RB200_INTERP_BILINEAR = 0, RB200_INTERP_TRIANGULAR = 1, RB200_INTERP_BICU
        RB200_INTERP_GAUSSIAN = 4, RB200_INTERP_NEAREST = 5 };
 /* Kernel choice for bilinear launches. AUTO picks by output width and source span; TILE forces the shared-memory
  * tile kernel where AUTO would stream rows through the bulk-copy ring; withholding h_samples selects the direct
- * (global gather) kernel. All three compute the same values. */
-enum { RB200_RESAMPLE_PATH_AUTO = 0, RB200_RESAMPLE_PATH_TILE = 1 };
+ * (global gather) kernel. The row-streaming kernel has two rings: PAIRS stages the two tap rows of every output row
+ * (a source row that two output rows share is fetched twice - an L2 hit in device memory), ROWS stages every distinct
+ * source row once (what a source in mapped host memory wants: nothing crosses the link twice). AUTO asks the runtime
+ * where `arena` lives and takes ROWS for host memory, PAIRS otherwise; a caller that knows can say so and save the
+ * query. All of them compute the same values. */
+enum { RB200_RESAMPLE_PATH_AUTO = 0, RB200_RESAMPLE_PATH_TILE = 1, RB200_RESAMPLE_PATH_ROWS = 2, RB200_RESAMPLE_PATH_PAIRS = 3 };
 typedef struct rb200_resample_params {
     void* out;
     int32_t out_w, out_h;
@@ -364,8 +368,8 @@ RB200_API int rb200k_transpose(const uint8_t* arena, const rb200_pointwise_sampl
  * such wait gives up after a limit (about a second of SM clock): the kernel then writes 1 to its status word, waits
  * (bounded again) for the copies it may still have in flight, and returns with its output incomplete; the context
  * stays usable. The two entries below run the same launches with a caller-chosen limit (SM clock cycles) and, for
- * self-tests, with the producer told not to issue the copies of one row (skip_row, counted inside each CTA's strip or
- * tile; -1 = issue everything), so that the give-up path can be exercised without any faulting or endless wait: the
+ * self-tests, with the producer told not to issue the copies from one row on (skip_row, counted over the source rows a
+ * CTA fetches for its strip or tile; -1 = issue everything), so that the give-up path can be exercised without any faulting or endless wait: the
  * skipped copy never starts, so nothing is left in flight. */
 RB200_API int rb200k_resample_probe(const uint8_t* arena, const rb200_resample_sample* samples,
                           const rb200_resample_sample* h_samples, int n, const rb200_resample_params* params,

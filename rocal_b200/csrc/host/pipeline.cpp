@@ -1800,6 +1800,8 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             // plain resize into its max-shape tensor defines only the ROI, as the reference does.
             p.fill_padding = (st.post >= 0 || _nodes[st.resize].kind != NodeKind::RESIZE) ? 1 : 0;
             p.interpolation = _nodes[st.resize].interpolation;
+            // a source read in place from pinned host memory is streamed row by row, every row once
+            p.path = (zero_copy && in_t->is_source) ? RB200_RESAMPLE_PATH_ROWS : RB200_RESAMPLE_PATH_PAIRS;
             p.status = s.d_status;
             p.arena_bytes = in_bytes;
             p.out_bytes = out_bytes;

@@ -4,7 +4,7 @@
 // CTAs' results read through distributed shared memory. The winner's "forced match" is an atomicMax
 // into the shared memory of the CTA that owns that anchor. Splitting a sample over a cluster (rather
 // than one large CTA per sample) gives 8 x batch work items, so the ragged box counts balance over the
-// 148 SMs.
+// 148 SMs; batches of up to 512 samples are also taken longest sample first.
 //
 // Semantics (and tie rules) of the CPU encoder, rocAL/source/meta_data/bounding_box_graph.cpp:
 //   :61-69    IoU = inter / (area_box + area_anchor - inter), float32, one rounding per op
@@ -29,6 +29,7 @@ namespace rb200 {
 constexpr int kCluster = 8;     // CTAs per sample (the portable maximum cluster size)
 constexpr int kBoxChunk = 64;   // boxes reduced per round of cluster barriers
 constexpr int kMaxWarps = 16;   // CTAs have at most 512 threads
+constexpr int kOrderMax = 512;  // batches up to this size are processed longest sample first (<= kBoxChunk * kMaxWarps)
 
 struct BoxLaunch {
     const float4* anchors;
@@ -79,6 +80,34 @@ __device__ __forceinline__ void box_step(const float4 b, int j, int box, const f
     }
 }
 
+// Which sample this cluster takes. A cluster's life is proportional to its sample's box count (1..50 in SSD training),
+// and clusters are handed out in grid order, so taking the samples in their given order leaves the device to a few
+// long samples at the end. Up to kOrderMax samples are therefore taken longest first: cluster y finds the sample whose
+// box count ranks y-th (ties by index). Every CTA works the small ranking out for itself from the offsets, so no
+// scratch memory or extra launch is needed; `cnt` is shared memory of at least kOrderMax ints that is free on entry
+// and on return. Kept out of line so that its registers do not add to the main loop's.
+__device__ __noinline__ int pick_sample(const int* __restrict__ box_offsets, int* cnt) {
+    const int ns = (int)gridDim.y;
+    if (ns <= 1 || ns > kOrderMax) return (int)blockIdx.y;
+    __shared__ int s_sample;
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    for (int i = tid; i < ns; i += nthreads) cnt[i] = box_offsets[i + 1] - box_offsets[i];
+    __syncthreads();
+    for (int i = tid; i < ns; i += nthreads) {
+        const int c = cnt[i];
+        int r = 0;
+        for (int j = 0; j < ns; j++) {
+            const int cj = cnt[j];
+            r += (cj > c || (cj == c && j < i)) ? 1 : 0;
+        }
+        if (r == (int)blockIdx.y) s_sample = i;
+    }
+    __syncthreads();
+    const int n = s_sample;
+    __syncthreads();                        // cnt is free again
+    return n;
+}
+
 // K = anchors per thread: per_cta <= K * blockDim.x.
 template <int K>
 __global__ void __launch_bounds__((K == 4 ? 320 : 512), (K == 4 ? 3 : 1)) box_encode_kernel(const float4* __restrict__ boxes,
@@ -96,12 +125,12 @@ __global__ void __launch_bounds__((K == 4 ? 320 : 512), (K == 4 ? 3 : 1)) box_en
     __shared__ int cta_idx[kBoxChunk];
     __shared__ float4 sbox[kBoxChunk];
 
-    const int n = blockIdx.y;
     const int rank = (int)cluster.block_rank();
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
     const int A = L.num_anchors;
     const int a_base = rank * L.per_cta;
+    const int n = pick_sample(box_offsets, &part_idx[0][0]);
     const int b_begin = box_offsets[n], nb = box_offsets[n + 1] - b_begin;
 
     float4 anc[K];

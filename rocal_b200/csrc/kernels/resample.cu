@@ -53,6 +53,7 @@ struct ResampleLaunch {
     long long wait_cycles;   // stream kernel: limit of every mbarrier wait, SM clock cycles
     int skip_row;       // stream kernel, self-test: the producer issues no copy from this strip row on (-1: all)
     int overlap;        // stream kernel: 1 = independent of the preceding kernel, wait for it only before exit
+    int row_ring;       // stream kernel: 1 = ring of distinct source rows (host-memory sources), 0 = ring of tap-row pairs
     ArenaBounds bounds; // bounds-checking build: the addresses the launch may read
 };
 
@@ -262,11 +263,11 @@ __device__ __forceinline__ void column_setup(int xi0, bool second, int crop_x, i
 
 // ------------------------------------------------------------------------------------------
 // Stream kernel: a CTA owns a strip of `strip_rows` output rows of one tile column of one sample.
-// Column set-up happens once per thread for the whole strip. Source rows arrive through a ring of
-// NS stages, each holding the two tap rows of one output row, filled by thread 0 with two 1-D bulk
-// copies (cp.async.bulk, the TMA unit) that complete on the stage's mbarrier; consumers release a
-// stage by arriving on its "empty" mbarrier. Every wait is bounded: on a time-out the kernel sets
-// the launch's status word, drains the copies it has in flight (bounded again) and returns.
+// Column set-up happens once per thread for the whole strip. The source rows the strip's taps touch arrive, each
+// exactly once, through a ring of 2 NS row slots filled by one producer lane with 1-D bulk copies (cp.async.bulk, the
+// TMA unit) that complete on the slot's "full" mbarrier; consumers release a row by arriving on the slot's "empty"
+// mbarrier after the last output row that reads it. Every wait is bounded: on a time-out the kernel sets the
+// launch's status word, drains the copies it has in flight (bounded again) and returns.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -284,9 +285,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` SM clock cycles (and after 2^24 polls at the latest).
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait: gives up after `limit` SM clock cycles (and after 2^24 polls at the latest). The polling loop is kept
+// out of line: the callers' fast path is one try_wait.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, long long limit) {
     const long long t0 = clock64();
     for (int i = 0; i < (1 << 24); i++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -294,33 +295,43 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
     return false;
 }
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_poll(bar, parity, limit);
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-struct StreamRow {           // per strip row, built once per CTA (32 bytes + 16 bytes)
+constexpr int kMaxStripRows = 32;
+
+// ---- pair ring: each stage holds the two tap rows of one output row ------------------------------------------------
+// The variant for sources in device memory. A row that two output rows share (down-scale ratios below 2, up-scales) is
+// fetched for each of them; in device memory the second fetch is an L2 hit and this ring's simpler bookkeeping (one
+// barrier wait and one release per output row) makes it the faster of the two there. Sources in mapped host memory
+// use the row ring below, which fetches every row once.
+struct PairRow {           // per strip row, built once per CTA (32 bytes + 16 bytes)
     float2 wy2, owy2;
     int off0, off1;          // byte offset of the first staged pixel of the two tap rows (stage included)
     uint32_t b0, b1;         // bytes of the two bulk copies
 };
-struct StreamSrc {
+struct PairSrc {
     const uint8_t *g0, *g1;  // 16-byte aligned global sources of the two copies
 };
-constexpr int kMaxStripRows = 32;
 
 template <typename OutT, int LAYOUT, bool NORMALIZE>
-__global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __restrict__ arena,
+__global__ void __launch_bounds__(288) resample_stream_pairs_kernel(const uint8_t* __restrict__ arena,
                                                               const rb200_resample_sample* __restrict__ samples,
                                                               const ResampleLaunch L) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     if (!L.overlap) pdl_wait();
-    // Layout: full[NS] | empty[NS] (128 bytes reserved) | StreamRow[32] | StreamSrc[32] | stages
+    // Layout: full[NS] | empty[NS] (128 bytes reserved) | PairRow[32] | PairSrc[32] | stages
     const int NS = L.ns, ns_mask = L.ns - 1, ns_lg = L.ns_log2;
-    StreamRow* rowtab = reinterpret_cast<StreamRow*>(smem + 128);
-    StreamSrc* srctab = reinterpret_cast<StreamSrc*>(smem + 128 + sizeof(StreamRow) * kMaxStripRows);
-    uint8_t* stage = smem + 128 + (sizeof(StreamRow) + sizeof(StreamSrc)) * kMaxStripRows;
+    PairRow* rowtab = reinterpret_cast<PairRow*>(smem + 128);
+    PairSrc* srctab = reinterpret_cast<PairSrc*>(smem + 128 + sizeof(PairRow) * kMaxStripRows);
+    uint8_t* stage = smem + 128 + (sizeof(PairRow) + sizeof(PairSrc)) * kMaxStripRows;
     const uint32_t bar_base = smem_u32(smem);
     const uint32_t stage_base = smem_u32(stage);
 
@@ -383,7 +394,7 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
             const uint8_t* g1 = img + (size_t)y1 * stride + (size_t)x_first * 3;
             const uint32_t m0 = (uint32_t)((uintptr_t)g0 & 15), m1 = (uint32_t)((uintptr_t)g1 & 15);
             float wy = sub_rn(sy, fy), owy = sub_rn(1.0f, wy);
-            StreamRow r;
+            PairRow r;
             r.wy2 = make_float2(wy, wy);
             r.owy2 = make_float2(owy, owy);
             r.off0 = (2 * s) * L.pitch + (int)m0;
@@ -416,7 +427,7 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     const uint2 bytes = *reinterpret_cast<const uint2*>(&rowtab[j].b0);
-                    const StreamSrc src = srctab[j];
+                    const PairSrc src = srctab[j];
                     const uint32_t bar = bar_base + 8 * s;
                     if (!span_in_bounds(L.bounds, src.g0, bytes.x, L.status) || !span_in_bounds(L.bounds, src.g1, bytes.y, L.status))
                         break;                         // (bounds-checking build) the copy is not made; the consumers give up
@@ -463,6 +474,257 @@ __global__ void __launch_bounds__(288) resample_stream_kernel(const uint8_t* __r
                 if (tid == 0)
                     for (int jj = j; jj < min(j + NS, rows_valid); jj++)
                         mbar_wait_bounded(bar_base + 8 * (jj & ns_mask), (jj >> ns_lg) & 1, L.wait_cycles);
+            }
+        }
+    }
+
+    if (L.fill_padding && tid < L.twh) {
+        const int j_end = min(L.strip_rows, L.out_h - y_begin);
+        for (int jj = 0; jj < j_end; jj++) {
+            int y = y_begin + jj;
+#pragma unroll
+            for (int p = 0; p < 2; p++) {
+                int xi = xi0 + p;
+                if (xi < L.out_w && (y >= ch || xi >= cw)) store3<OutT, LAYOUT>(out, L.out_w, L.out_h, n, y, xi, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+    if (L.overlap) pdl_wait();      // completion of this launch implies completion of the kernel before it
+}
+
+
+// ---- row ring: every distinct source row of the strip is fetched once --------------------------------------------
+struct StreamRow {           // per output row of the strip, built once per CTA (32 bytes)
+    float2 wy2, owy2;
+    int off0, off1;          // byte offset of the first staged pixel of the two tap rows (slot and alignment included)
+    uint32_t ctl;            // what the consumer needs per row, ready to use: bits 0-7 / 8-15 byte offset of the "full"
+                             // barrier of the top / bottom tap row's slot (the "empty" one lies 64 bytes further),
+                             // bit 16 / 17 the phase parity to wait for, bit 18 the bottom row is another row than the
+                             // top one, bits 20-21 how many rows (0..2, top first) no later output row needs
+    int u0;                  // index of the top tap row in the strip's list of distinct source rows
+};
+struct StreamSrc {           // per distinct source row of the strip (16 bytes)
+    const uint8_t* g;        // 16-byte aligned global source of the copy
+    uint32_t bytes;          // bytes of the copy (a multiple of 16)
+    uint32_t pad;
+};
+constexpr size_t kStreamTableBytes = sizeof(StreamRow) * kMaxStripRows + sizeof(StreamSrc) * 2 * kMaxStripRows;
+
+// The strip's two tables, by one warp (lane = output row of the strip): per output row the vertical weights, where its
+// two tap rows lie in the ring and which rows it releases; per distinct source row the copy the producer issues.
+// The tap rows never decrease from one output row to the next and the bottom tap is the top tap or the row below it,
+// so a lane only has to look at its predecessor's bottom row to know which of its rows are new. Kept out of line so
+// that its registers do not add to those of the pixel loop.
+__device__ __noinline__ void build_strip_tables(const rb200_resample_sample* __restrict__ sp, const uint8_t* __restrict__ img,
+                                                int x_first, int nbytes, int y_begin, int rows_valid, int smask, int slog,
+                                                int pitch, StreamRow* rowtab, StreamSrc* srctab, int* distinct_out) {
+    const int tid = threadIdx.x;
+    const bool have = tid < rows_valid;
+    const uint32_t stride = sp->src_stride;
+    const int roi_y = sp->roi_y, roi_h = sp->roi_h;
+    const float ratio_h = div_rn((float)roi_h, (float)sp->dst_h);
+    const float off_h = mul_rn(sub_rn(ratio_h, 1.0f), 0.5f);
+    const int y_lo = roi_y, y_hi = max(roi_y + roi_h - 2, roi_y);
+    float sy = src_location(sp->crop_y + y_begin + min(tid, rows_valid - 1), ratio_h, off_h, roi_y);
+    float fy = floorf(sy);
+    int y0, y1;
+    clamp_taps(fy, y_lo, y_hi, y0, y1);
+    const int py1 = __shfl_up_sync(0xffffffffu, y1, 1);
+    const bool first = tid == 0;
+    const int new0 = (have && (first || y0 > py1)) ? 1 : 0;
+    const int new1 = (have && y1 > y0 && (first || y1 > py1)) ? 1 : 0;
+    const int cnt = new0 + new1;
+    int inc = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, d);
+        if (tid >= d) inc += t;
+    }
+    const int before = inc - cnt;          // distinct rows listed before this output row's new ones
+    const int u0 = new0 ? before : before - 1 - (py1 - y0);
+    const int u1 = (y1 == y0) ? u0 : (new1 ? before + new0 : before - 1 - (py1 - y1));
+    const int total = __shfl_sync(0xffffffffu, inc, rows_valid - 1);
+    const int u0_next = __shfl_down_sync(0xffffffffu, u0, 1);
+    if (have) {
+        const uint8_t* g0 = img + (size_t)y0 * stride + (size_t)x_first * 3;
+        const uint8_t* g1 = img + (size_t)y1 * stride + (size_t)x_first * 3;
+        const uint32_t m0 = (uint32_t)((uintptr_t)g0 & 15), m1 = (uint32_t)((uintptr_t)g1 & 15);
+        float wy = sub_rn(sy, fy), owy = sub_rn(1.0f, wy);
+        StreamRow r;
+        r.wy2 = make_float2(wy, wy);
+        r.owy2 = make_float2(owy, owy);
+        r.off0 = (u0 & smask) * pitch + (int)m0;
+        r.off1 = (u1 & smask) * pitch + (int)m1;
+        const int rel = (tid == rows_valid - 1) ? total - u0 : u0_next - u0;
+        r.ctl = (uint32_t)((u0 & smask) * 8) | ((uint32_t)((u1 & smask) * 8) << 8) | ((uint32_t)((u0 >> slog) & 1) << 16) |
+                ((uint32_t)((u1 >> slog) & 1) << 17) | ((u1 != u0) ? (1u << 18) : 0u) | ((uint32_t)rel << 20);
+        r.u0 = u0;
+        rowtab[tid] = r;
+        if (new0) {
+            srctab[before].g = g0 - m0;
+            srctab[before].bytes = ((m0 + nbytes + 15) >> 4) << 4;
+        }
+        if (new1) {
+            srctab[before + new0].g = g1 - m1;
+            srctab[before + new0].bytes = ((m1 + nbytes + 15) >> 4) << 4;
+        }
+    }
+    if (tid == 0) *distinct_out = total;
+}
+
+// The ring holds source rows, each fetched once: the rows the strip's taps touch, in ascending order, form a list of
+// distinct rows (skipped rows of a strong down-scale are not in it; a row that two or more output rows share - every
+// down-scale ratio below 2, every up-scale - is in it once). Row u of the list lives in slot u mod (2 NS). An output
+// row waits for the one or two slots of its tap rows and, when done, releases the rows that no later output row needs.
+template <typename OutT, int LAYOUT, bool NORMALIZE>
+__global__ void __launch_bounds__(288, 4) resample_stream_kernel(const uint8_t* __restrict__ arena,
+                                                              const rb200_resample_sample* __restrict__ samples,
+                                                              const ResampleLaunch L) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_distinct;
+    pdl_launch_dependents();
+    if (!L.overlap) pdl_wait();
+    // Layout: full[slots] (64 bytes) | empty[slots] (64 bytes) | StreamRow[32] | StreamSrc[64] | row slots
+    const int slots = 2 * L.ns, smask = slots - 1, slog = L.ns_log2 + 1;
+    StreamRow* rowtab = reinterpret_cast<StreamRow*>(smem + 128);
+    StreamSrc* srctab = reinterpret_cast<StreamSrc*>(smem + 128 + sizeof(StreamRow) * kMaxStripRows);
+    uint8_t* stage = smem + 128 + kStreamTableBytes;
+    const uint32_t full_base = smem_u32(smem), empty_base = smem_u32(smem + 64);
+    const uint32_t stage_base = smem_u32(stage);
+
+    const int n = blockIdx.y;
+    const int tx = blockIdx.x % L.tiles_x;
+    const int strip = blockIdx.x / L.tiles_x;
+    const int tid = threadIdx.x;
+    const int TW = 2 * L.twh;
+    const int producer_tid = (int)blockDim.x - 32;      // lane 0 of the last warp
+
+    const rb200_resample_sample* sp = samples + n;
+    const int crop_w = sp->crop_w, crop_h = sp->crop_h;
+    const int cw = min(crop_w, L.out_w);
+    const int ch = min(crop_h, L.out_h);
+    const int tile_x0 = tx * TW;
+    const int y_begin = strip * L.strip_rows;
+    const int xi0 = tile_x0 + 2 * tid;
+    OutT* out = reinterpret_cast<OutT*>(L.out);
+
+    const int rows_valid = min(L.strip_rows, ch - y_begin);
+    const int cols_valid = min(TW, cw - tile_x0);
+
+    // bounds-checking build: a sample whose source rectangle leaves the arena is reported and none of it is read
+    const bool src_ok = rect_in_bounds(L.bounds, arena + sp->src_offset, sp->src_stride, sp->roi_x, sp->roi_y, sp->roi_w, sp->roi_h,
+                                       L.status);
+    if (rows_valid > 0 && cols_valid > 0 && src_ok) {
+        const uint8_t* img = arena + sp->src_offset;
+        const uint32_t stride = sp->src_stride;
+        const int roi_x = sp->roi_x, roi_w = sp->roi_w;
+        const int crop_x = sp->crop_x, mirror = sp->mirror;
+        const int x_lo = roi_x, x_hi = max(roi_x + roi_w - 2, roi_x);
+        const float ratio_w = div_rn((float)roi_w, (float)sp->dst_w);
+        const float off_w = mul_rn(sub_rn(ratio_w, 1.0f), 0.5f);
+        int x_first, x_last;
+        {
+            int ca = tile_x0, cb = tile_x0 + cols_valid - 1;
+            int ra = crop_x + (mirror ? (crop_w - 1 - ca) : ca);
+            int rb = crop_x + (mirror ? (crop_w - 1 - cb) : cb);
+            int r_lo = min(ra, rb), r_hi = max(ra, rb);
+            int t0, t1;
+            clamp_taps(floorf(src_location(r_lo, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+            x_first = t0;
+            clamp_taps(floorf(src_location(r_hi, ratio_w, off_w, roi_x)), x_lo, x_hi, t0, t1);
+            x_last = t1;
+        }
+
+        // Row tables of the strip, by the first warp (one lane per output row), and barrier initialisation.
+        if (tid < 32)
+            build_strip_tables(sp, img, x_first, (x_last - x_first + 1) * 3, y_begin, rows_valid, smask, slog, L.pitch, rowtab,
+                               srctab, &s_distinct);
+        if (tid == producer_tid) {
+            for (int s = 0; s < slots; s++) {
+                mbar_init(full_base + 8 * s, 1);                  // full: one arrive (+ tx bytes)
+                mbar_init(empty_base + 8 * s, (L.twh + 31) >> 5); // empty: one arrive per compute warp
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();
+
+        if (tid >= producer_tid) {
+            // ---- producer warp: lane 0 keeps the ring full ----
+            if (tid == producer_tid) {
+                const int distinct = s_distinct;
+                for (int u = 0; u < distinct; u++) {
+                    const int s = u & smask;
+                    if (u == L.skip_row) break;        // self-test: this row's copy (and all later ones) never starts
+                    if (u >= slots && !mbar_wait_bounded(empty_base + 8 * s, ((u >> slog) - 1) & 1, L.wait_cycles)) {
+                        raise_status(L.status);
+                        break;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    const StreamSrc src = srctab[u];
+                    const uint32_t bar = full_base + 8 * s;
+                    if (!span_in_bounds(L.bounds, src.g, src.bytes, L.status))
+                        break;                         // (bounds-checking build) the copy is not made; the consumers give up
+                    mbar_expect_tx(bar, src.bytes);
+                    bulk_g2s(stage_base + s * L.pitch, src.g, src.bytes, bar);
+                }
+            }
+        } else if (tid < L.twh) {
+            // ---- compute threads ----
+            const bool active = 2 * tid < cols_valid;
+            const bool second = (2 * tid + 1) < cols_valid;
+            ColumnTaps ct[2];
+            float2 wx2, owx2;
+            column_setup(active ? xi0 : tile_x0, second, crop_x, crop_w, mirror, ratio_w, off_w, roi_x, x_lo, x_hi, x_first, ct, wx2, owx2);
+            const size_t plane = (size_t)L.out_w * L.out_h;
+            OutT* po = out + out_index<OutT, LAYOUT>(L.out_w, L.out_h, n, 0, y_begin, active ? xi0 : tile_x0);
+            const size_t row_step = LAYOUT == RB200_NCHW ? (size_t)L.out_w : (size_t)L.out_w * 3;
+            const bool paired = second && L.pair_ok;
+            // the compute lanes of this warp (the last warp may be half full: twh is a multiple of 16)
+            const int lanes = min(32, L.twh - (tid & ~31));
+            const unsigned wmask = lanes == 32 ? 0xffffffffu : ((1u << lanes) - 1u);
+            const bool releaser = (tid & 31) == 0;
+            int j = 0, u_fail = 0;
+            bool ok = true;
+            for (; j < rows_valid; j++, po += row_step) {
+                const int4 info = *reinterpret_cast<const int4*>(&rowtab[j].off0);     // off0, off1, ctl, u0
+                const uint32_t ctl = (uint32_t)info.z;
+                ok = mbar_wait_bounded(full_base + (ctl & 0xffu), (ctl >> 16) & 1u, L.wait_cycles);
+                if (ok && (ctl & (1u << 18))) ok = mbar_wait_bounded(full_base + ((ctl >> 8) & 0xffu), (ctl >> 17) & 1u, L.wait_cycles);
+                // a warp gives up as a whole: its lanes meet again at the release below
+                ok = __all_sync(wmask, ok) != 0;
+                if (!ok) {
+                    u_fail = info.w;
+                    break;
+                }
+                if (active) {
+                    const float4 wts = *reinterpret_cast<const float4*>(&rowtab[j]);
+                    if (paired)
+                        blend_store<OutT, LAYOUT, NORMALIZE, true>(stage, info.x, info.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
+                                                                   ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
+                    else
+                        blend_store<OutT, LAYOUT, NORMALIZE, false>(stage, info.x, info.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
+                                                                    ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
+                }
+                // release the rows no later output row reads, once per warp after all its lanes have read them (the
+                // "empty" barriers lie 64 bytes behind the "full" ones)
+                if (ctl & (3u << 20)) {
+                    __syncwarp(wmask);
+                    if (releaser) {
+                        mbar_arrive(full_base + 64 + (ctl & 0xffu));
+                        if (ctl & (2u << 20)) mbar_arrive(full_base + 64 + ((ctl >> 8) & 0xffu));
+                    }
+                }
+            }
+            if (!ok) {
+                raise_status(L.status);
+                // Before the CTA's shared memory is given away, wait (bounded) for the copies that may
+                // still be in flight: the producer is never more than the ring's slots ahead.
+                if (tid == 0) {
+                    const int distinct = s_distinct;
+                    for (int u = u_fail; u < min(u_fail + slots, distinct); u++)
+                        mbar_wait_bounded(full_base + 8 * (u & smask), (u >> slog) & 1, L.wait_cycles);
+                }
             }
         }
     }
@@ -1063,7 +1325,9 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
                         int mode, size_t smem, cudaStream_t stream) {
     L.pair_ok = (L.out_w % 2 == 0) && (((uintptr_t)L.out) % (2 * sizeof(OutT)) == 0);
     if (mode == MODE_STREAM) {
-        auto k = L.normalize ? resample_stream_kernel<OutT, LAYOUT, true> : resample_stream_kernel<OutT, LAYOUT, false>;
+        auto k = L.row_ring ? (L.normalize ? resample_stream_kernel<OutT, LAYOUT, true> : resample_stream_kernel<OutT, LAYOUT, false>)
+                            : (L.normalize ? resample_stream_pairs_kernel<OutT, LAYOUT, true>
+                                           : resample_stream_pairs_kernel<OutT, LAYOUT, false>);
         if (smem > 48 * 1024) {
             int rc = check_cuda(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                                 "cudaFuncSetAttribute(resample_stream)");
@@ -1130,7 +1394,7 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
         set_error("rb200k_resample: strip_rows %d is outside 4..%d", p->strip_rows, kMaxStripRows);
         return RB200_E_INVALID;
     }
-    if (p->path != RB200_RESAMPLE_PATH_AUTO && p->path != RB200_RESAMPLE_PATH_TILE) {
+    if (p->path < RB200_RESAMPLE_PATH_AUTO || p->path > RB200_RESAMPLE_PATH_PAIRS) {
         set_error("rb200k_resample: bad path %d", p->path);
         return RB200_E_INVALID;
     }
@@ -1154,6 +1418,14 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
     L.wait_cycles = (long long)(wait_cycles ? wait_cycles : kDefaultWaitCycles);
     L.skip_row = skip_row;
     L.overlap = p->overlap ? 1 : 0;
+    // Which ring the row-streaming kernel runs: every source row once for a source in host memory (each re-read would
+    // cross the link again), tap-row pairs for device memory (re-reads are L2 hits and the bookkeeping is lighter).
+    L.row_ring = p->path == RB200_RESAMPLE_PATH_ROWS;
+    if (p->path == RB200_RESAMPLE_PATH_AUTO) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, arena) == cudaSuccess) L.row_ring = attr.type == cudaMemoryTypeHost;
+        else cudaGetLastError();
+    }
     L.bounds = arena_bounds(arena, p->arena_bytes);
     if (p->out_bytes && (uint64_t)n * p->out_w * p->out_h * 3 * out_elem_size(p->out_dtype) > p->out_bytes) {
         set_error("rb200k_resample: %d samples of %d x %d x 3 elements do not fit the %llu-byte output", n, p->out_w, p->out_h,
@@ -1218,7 +1490,7 @@ static int resample_launch(const uint8_t* arena, const rb200_resample_sample* sa
                 L.ns = ns;
                 L.ns_log2 = ns == 4 ? 2 : 1;
                 L.strip_rows = p->strip_rows;      // 0: chosen in launch_typed, where the kernel's occupancy is known
-                smem = 128 + (sizeof(StreamRow) + sizeof(StreamSrc)) * kMaxStripRows + (size_t)2 * ns * pitch;
+                smem = 128 + kStreamTableBytes + (size_t)2 * ns * pitch;
             }
         }
         if (mode == MODE_STAGED) {

@@ -53,7 +53,8 @@ def main():
     arena, hs, ws, offs = S.make_images(rng, n, (300, 420), (340, 500))
     t = S.classification_tables(rng, hs, ws, offs)
     ref = O.resample(arena, t, 224, 224, T.FP16, T.NCHW, mul, add)
-    for name, kw in (("resample stream", {}), ("resample tile", {"path": 1}), ("resample direct", {"staged": False})):
+    for name, kw in (("resample stream rows", {"path": 2}), ("resample stream pairs", {"path": 3}), ("resample tile", {"path": 1}),
+                     ("resample direct", {"staged": False})):
         run(name, arena, offs, hs, ws,
             lambda d, ab, out, kw=kw: K.resample(d, t, 224, 224, T.FP16, T.NCHW, mul, add, fill_padding=False, out=out, status=status,
                                                  arena_bytes=ab, **kw), ref, np.float16)

@@ -24,7 +24,7 @@ def _run(args, timeout):
 def test_out_of_bounds_samples_are_reported_and_skipped():
     out = _run([os.path.join(ROOT, "tests", "harness", "bounds_build_check.py")], 600)
     assert "bounds build check passed" in out
-    for name in ("resample stream", "resample tile", "resample direct", "resample triangular", "pointwise vector", "pointwise scalar",
+    for name in ("resample stream rows", "resample stream pairs", "resample tile", "resample direct", "resample triangular", "pointwise vector", "pointwise scalar",
                  "warp affine", "output size refused"):
         assert "ok " + name in out, out
 

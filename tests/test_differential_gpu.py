@@ -45,8 +45,9 @@ def _case(seed, cuda):
             t[i]["mirror"] = int(rng.integers(0, 2))
         staged = bool(rng.integers(0, 2))
         ref = O.resample(arena, t, out_w, out_h, dtype, layout, m, a, interpolation=interp)
-        got = K.resample(d_arena, t, out_w, out_h, dtype, layout, m, a, staged=staged, interpolation=interp).cpu().numpy()
-        assert np.array_equal(got.view(np.uint8), ref.view(np.uint8)), ("resample", seed, interp, dtype, layout, staged, out_w, out_h)
+        path = seed % 4      # automatic choice, tile kernel, row ring, pair ring
+        got = K.resample(d_arena, t, out_w, out_h, dtype, layout, m, a, staged=staged, interpolation=interp, path=path).cpu().numpy()
+        assert np.array_equal(got.view(np.uint8), ref.view(np.uint8)), ("resample", seed, interp, dtype, layout, staged, path, out_w, out_h)
     elif kind == 1:
         out_w, out_h = int(rng.integers(1, 90)) * int(rng.choice([1, 4])), int(rng.integers(1, 200))
         op = int(rng.choice([T.COLOR_NONE, T.COLOR_BRIGHTNESS, T.COLOR_CONTRAST, T.COLOR_TWIST]))

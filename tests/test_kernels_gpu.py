@@ -93,7 +93,8 @@ def test_resize_cmn_config1_full_batch(cuda):
 @pytest.mark.parametrize("n", [3, 64, 200])
 def test_strip_rows_do_not_change_the_result(cuda, n):
     """The row-streaming kernel cuts the output into strips of rows per CTA; the library picks the strip height from the
-    grid size and the kernel's occupancy (8, about 14, or 32 rows), `strip_rows` forces it. Every choice - including
+    grid size and the kernel's occupancy (8, about 14, or 32 rows), `strip_rows` forces it; `path` picks the ring (2: every
+    distinct source row staged once, the choice for host memory; 3: the two tap rows of each output row). Every choice - including
     heights that leave a ragged last strip and the smallest and largest allowed - gives the oracle's bits; a value
     outside 4..32 is refused."""
     from rocal_b200 import kernels as K
@@ -104,9 +105,10 @@ def test_strip_rows_do_not_change_the_result(cuda, n):
     mul, add = S.normalize_tables()
     ref = O.resample(arena, t, 224, 224, T.FP32, T.NCHW, mul, add)
     a = _dev(arena, cuda)
-    for rows in (0, 4, 5, 14, 15, 31, 32):
-        got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, strip_rows=rows).cpu().numpy()
-        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), rows
+    for path in (2, 3):         # both rings of the row-streaming kernel: distinct rows once / tap-row pairs
+        for rows in (0, 4, 5, 14, 15, 31, 32):
+            got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, strip_rows=rows, path=path).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), (path, rows)
     for rows in (3, 33, -1):
         with pytest.raises(Rb200Error):
             K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, strip_rows=rows)

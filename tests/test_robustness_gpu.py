@@ -29,7 +29,9 @@ def _library_status():
     return lib.rb200k_device_status()
 
 
-def test_stream_kernel_wait_runs_out_and_recovers(cuda):
+@pytest.mark.parametrize("path", [2, 3])
+def test_stream_kernel_wait_runs_out_and_recovers(cuda, path):
+    """Both rings of the row-streaming kernel (2: distinct source rows, 3: tap-row pairs)."""
     import torch
     from rocal_b200 import kernels as K
     rng = S.rng_for(40)
@@ -42,19 +44,19 @@ def test_stream_kernel_wait_runs_out_and_recovers(cuda):
     assert _library_status() == 0
     # row 3 of every strip is never copied: the compute threads wait for it, give up after the limit, raise the
     # status word and the kernel returns
-    K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status, probe=(WAIT_CYCLES, 3))
+    K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status, probe=(WAIT_CYCLES, 3), path=path)
     torch.cuda.synchronize()
     assert int(status.item()) == 1
     assert _library_status() == 0                       # the launch had its own word
     status.zero_()
-    got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status).cpu().numpy()
+    got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status, path=path).cpu().numpy()
     assert int(status.item()) == 0 and np.array_equal(got, ref)
     # without a word of its own the launch reports through the library-wide one, which reads 1 once and then 0
-    K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, probe=(WAIT_CYCLES, 0))
+    K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, probe=(WAIT_CYCLES, 0), path=path)
     torch.cuda.synchronize()
     assert _library_status() == 1 and _library_status() == 0
     # a probe that skips nothing is an ordinary launch
-    got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status, probe=(WAIT_CYCLES * 1000, -1)).cpu().numpy()
+    got = K.resample(a, t, 224, 224, T.FP32, T.NCHW, mul, add, status=status, probe=(WAIT_CYCLES * 1000, -1), path=path).cpu().numpy()
     assert int(status.item()) == 0 and np.array_equal(got, ref)
 
 
