@@ -27,4 +27,34 @@ __device__ __forceinline__ float key_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
+constexpr int kOrderMax = 512;  // batches up to this size are processed longest sample first
+
+// Which sample this cluster takes. A cluster's life is proportional to its sample's box count (1..50 in SSD training),
+// and clusters are handed out in grid order, so taking the samples in their given order leaves the device to a few
+// long samples at the end. Up to kOrderMax samples are therefore taken longest first: cluster y finds the sample whose
+// box count ranks y-th (ties by index). Every CTA works the small ranking out for itself from the offsets, so no
+// scratch memory or extra launch is needed; `cnt` is shared memory of at least kOrderMax ints that is free on entry
+// and on return. Kept out of line so that its registers do not add to the main loop's.
+static __device__ __noinline__ int pick_sample(const int* __restrict__ box_offsets, int* cnt) {
+    const int ns = (int)gridDim.y;
+    if (ns <= 1 || ns > kOrderMax) return (int)blockIdx.y;
+    __shared__ int s_sample;
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    for (int i = tid; i < ns; i += nthreads) cnt[i] = box_offsets[i + 1] - box_offsets[i];
+    __syncthreads();
+    for (int i = tid; i < ns; i += nthreads) {
+        const int c = cnt[i];
+        int r = 0;
+        for (int j = 0; j < ns; j++) {
+            const int cj = cnt[j];
+            r += (cj > c || (cj == c && j < i)) ? 1 : 0;
+        }
+        if (r == (int)blockIdx.y) s_sample = i;
+    }
+    __syncthreads();
+    const int n = s_sample;
+    __syncthreads();                        // cnt is free again
+    return n;
+}
+
 }  // namespace rb200

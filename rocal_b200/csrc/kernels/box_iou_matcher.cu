@@ -41,7 +41,9 @@ __global__ void __launch_bounds__(256) box_iou_match_kernel(const float4* __rest
     __shared__ uint32_t best_key[kMatchMaxBoxes];   // read by the other CTAs of the cluster
     __shared__ float best_val[kMatchMaxBoxes];
 
-    const int n = blockIdx.y;
+    // samples are taken longest first (most boxes first), see pick_sample
+    static_assert(kMatchMaxBoxes >= kOrderMax, "best_key doubles as the ranking's scratch");
+    const int n = pick_sample(box_offsets, reinterpret_cast<int*>(best_key));
     const int rank = (int)cluster.block_rank();
     const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31;
     const int A = L.num_anchors;
