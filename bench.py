@@ -859,14 +859,14 @@ def main():
                     "h2d_bytes_per_step": int(sum(p_["h2d_bytes_per_step"] for p_ in per_rank)),
                     "h2d_whole_images_bytes": int(arena_pinned.numel()) * world,
                     "h2d": {0: "whole images, one copy", 1: "one strided copy per image of the rectangle the crop can read",
-                            2: "zero-copy: the kernel's bulk copies read the tap rows from the pinned arena; bytes = "
-                               "footprint rectangles, an upper bound of what crosses the link"}[upload_mode],
+                            2: "zero-copy: the kernel's bulk copies read the rows its taps touch from the pinned arena, each "
+                               "row once; bytes = rows x 16-byte-rounded spans, computed from the batch's table"}[upload_mode],
                     "d2h_bytes_per_step": int(host_back.numel() * 2) * world,
                     "d2h_note": "one sample per rank and step: outputs are consumed on the device (DLPack), by design",
                     "steps": e2e_steps, "timed": "clock starts before the first feed; every batch's feed, transfer and kernel inside",
                     "host_link_gbs": sum(p_["host_link_gbs"] for p_ in per_rank),
                     "link_copy_gbs": sum(p_["link_copy_gbs"] for p_ in per_rank),
-                    "link_note": "host_link_gbs = footprint bytes the zero-copy kernels pulled per second, all ranks; link_copy_gbs = "
+                    "link_note": "host_link_gbs = bytes the zero-copy kernels pulled per second, all ranks; link_copy_gbs = "
                                  "plain pinned-to-device copies of the same arenas issued by all ranks at once (what the host "
                                  "and its PCIe links deliver to this many GPUs together)"},
             "gpu_launches": int(launches),

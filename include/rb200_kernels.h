@@ -275,6 +275,36 @@ RB200_API int rb200k_box_iou_match(const float* boxes, const int32_t* box_offset
                          const rb200_box_matcher_params* params, int32_t* out_matches, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Boxes through a crop window and a mirror (metadata of the crop-type operators)
+ * ------------------------------------------------------------------------------------- */
+
+/* One sample (32 bytes): the window in the normalised coordinates of the sample's boxes, and whether the boxes are
+ * mirrored afterwards (left-right, top-bottom). */
+typedef struct rb200_box_window {
+    float l, t, r, b;
+    int32_t mirror_h, mirror_v;
+    int32_t reserved[2];
+} rb200_box_window;
+enum { RB200_BOX_RULE_QUARTER_AREA = 0, RB200_BOX_RULE_CENTRE = 1 };
+
+/* The box update of the reference's crop-type meta nodes for boxes that already live in device memory (the pipeline
+ * transforms its own boxes on the host, where they are fed and where the window samplers need them).
+ *   RB200_BOX_RULE_QUARTER_AREA: a box stays when at least a quarter of its area lies in the window
+ *     (MetaNode::BBoxIntersectionOverUnion without is_iou, threshold 0.25: meta_node_crop.cpp:59-78,
+ *     meta_node_crop_mirror_normalize.cpp:53-90, meta_node_resize_crop_mirror.cpp:66-100); a sample left without boxes
+ *     gets the whole window, label 0.
+ *   RB200_BOX_RULE_CENTRE: a box stays when its centre lies strictly inside the window (SSD crop and random bbox crop,
+ *     bounding_box_graph.cpp:98-110); a sample left without boxes gets one empty box, label 0.
+ * Kept boxes are clipped to the window, re-normalised to it, mirrored (meta_node_flip.cpp:40-60) and written in their
+ * original order: sample i's boxes at out_boxes[out_offsets[i] .. out_offsets[i + 1]), which makes the three output
+ * arrays direct inputs of rb200k_box_encode / rb200k_box_iou_match. All pointers are device pointers; boxes and
+ * out_boxes 16-byte aligned; out_boxes / out_labels hold at least (input boxes + n) entries, out_offsets n + 1.
+ * Enqueues three small kernels on `stream`. */
+RB200_API int rb200k_box_transform(const float* boxes, const int32_t* labels, const int32_t* box_offsets, int n,
+                         const rb200_box_window* windows, int rule, float* out_boxes, int32_t* out_labels,
+                         int32_t* out_offsets, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Normalize / Transpose (neighbouring operators of the augmentation path)
  * ------------------------------------------------------------------------------------- */
 

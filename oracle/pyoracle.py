@@ -741,6 +741,42 @@ def meta_flip(boxes, labels, offsets, roi_wh, h_flip, v_flip):
     return _join(per)
 
 
+def box_transform(boxes, labels, offsets, windows, rule, mirror_h=None, mirror_v=None):
+    """Normalised boxes through a window and a mirror, float32 operation by operation: the form in which the library
+    keeps boxes (every coordinate a fraction of the current image). rule 0: the quarter-area rule of the Crop /
+    CropMirrorNormalize / ResizeCropMirror meta nodes (stand-in: the whole window, label 0); rule 1: the centre rule
+    of update_random_bbox_meta_data (stand-in: an empty box, label 0). windows: [n][4] = l, t, r, b."""
+    f32 = np.float32
+    per = []
+    for i, (b, lab) in enumerate(_split(boxes, labels, offsets)):
+        l, t, r, bt = (f32(v) for v in windows[i])
+        ww, wh = f32(r - l), f32(bt - t)
+        kb, kl = [], []
+        for q, la in zip(b, lab):
+            if rule == 1:
+                xc, yc = f32(f32(0.5) * f32(q[0] + q[2])), f32(f32(0.5) * f32(q[1] + q[3]))
+                keep = xc > l and xc < r and yc > t and yc < bt
+            else:
+                xa, ya, xb, yb = max(q[0], l), max(q[1], t), min(q[2], r), min(q[3], bt)
+                inter = f32(max(f32(0), f32(xb - xa)) * max(f32(0), f32(yb - ya)))
+                area = f32(f32(q[3] - q[1]) * f32(q[2] - q[0]))
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    keep = f32(inter / area) >= f32(0.25)
+            if keep:
+                kb.append([f32(f32(max(q[0], l) - l) / ww), f32(f32(max(q[1], t) - t) / wh),
+                           f32(f32(min(q[2], r) - l) / ww), f32(f32(min(q[3], bt) - t) / wh)])
+                kl.append(la)
+        if not kb:
+            kb, kl = [[f32(0), f32(0), f32(0), f32(0)] if rule == 1 else [f32(0), f32(0), f32(1), f32(1)]], [0]
+        for q in kb:
+            if mirror_h is not None and mirror_h[i]:
+                q[0], q[2] = f32(f32(1) - q[2]), f32(f32(1) - q[0])
+            if mirror_v is not None and mirror_v[i]:
+                q[1], q[3] = f32(f32(1) - q[3]), f32(f32(1) - q[1])
+        per.append((kb, kl))
+    return _join(per)
+
+
 def meta_rotate(boxes, labels, offsets, roi_wh, angles_deg, dst_w, dst_h):
     """RotateMetaNode (meta_node_rotate.cpp:27-103), in pixels as written: the corners of a box are rotated about the
     image centres (source: roi / 2 in float; destination: size // 2), the new box is their bounding box with

@@ -53,6 +53,11 @@ class BoxMatcherParams(ctypes.Structure):
                 ("low_threshold", ctypes.c_float), ("allow_low_quality_matches", ctypes.c_int32)]
 
 
+class BoxWindow(ctypes.Structure):
+    _fields_ = [("l", ctypes.c_float), ("t", ctypes.c_float), ("r", ctypes.c_float), ("b", ctypes.c_float),
+                ("mirror_h", ctypes.c_int32), ("mirror_v", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
+
+
 class NormalizeParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("out_w", ctypes.c_int32), ("out_h", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
                 ("axis_mask", ctypes.c_int32), ("compute_mean", ctypes.c_int32), ("compute_stddev", ctypes.c_int32),
@@ -83,6 +88,8 @@ lib.rb200k_box_encode.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, ct
 lib.rb200k_box_encode.restype = c_int
 lib.rb200k_box_iou_match.argtypes = [c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(BoxMatcherParams), c_void_p, c_void_p]
 lib.rb200k_box_iou_match.restype = c_int
+lib.rb200k_box_transform.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+lib.rb200k_box_transform.restype = c_int
 lib.rb200k_last_error.restype = c_char_p
 lib.rb200k_launch_count.restype = c_uint64
 lib.rb200k_version.restype = c_char_p

@@ -1374,8 +1374,30 @@ void Pipeline::upload_sources(InputBatch& b, int a, const uint8_t* h_tab) {
         need += (size_t)(x1 - x0 + 1) * (y1 - y0 + 1) * 3;
         full += (size_t)W * H * 3;
     }
-    if (a < 0) {            // zero copy: the kernels fetch (at most) these rectangles themselves
-        _h2d_bytes += need;
+    if (a < 0) {
+        // zero copy: the one kernel that consumes the source fetches its rows itself, each row once - every row of the
+        // window for ratios below 2, the two tap rows of every output row above - as whole 16-byte granules around the
+        // span its taps cover (about 15 bytes of rounding per row)
+        size_t pulled = 0;
+        for (size_t k = 0; k < _steps.size(); k++) {
+            const Step& st = _steps[k];
+            if (st.in_tensor != _source) continue;
+            const TensorImpl* ot = _tensors[st.out_tensor].get();
+            for (size_t i = 0; i < n; i++) {
+                if (st.kind == Step::RESAMPLE) {
+                    const rb200_resample_sample& q = reinterpret_cast<const rb200_resample_sample*>(h_tab + k * n * 64)[i];
+                    const double rx = (double)q.roi_w / q.dst_w, ry = (double)q.roi_h / q.dst_h;
+                    const int out_rows = std::min(q.crop_h, ot->max_h), out_cols = std::min(q.crop_w, ot->max_w);
+                    const long rows = std::min<long>(std::min<long>(2L * out_rows, (long)std::ceil(out_rows * ry) + 1), q.roi_h);
+                    const long span = std::min<long>((long)std::ceil(out_cols * rx) + 2, q.roi_w);
+                    pulled += (size_t)rows * (size_t)(span * 3 + 15);
+                } else {
+                    const rb200_pointwise_sample& q = reinterpret_cast<const rb200_pointwise_sample*>(h_tab + k * n * 64)[i];
+                    pulled += (size_t)std::min(q.roi_h, ot->max_h) * (size_t)(std::min(q.roi_w, ot->max_w) * 3 + 15);
+                }
+            }
+        }
+        _h2d_bytes += pulled ? pulled : need;
         return;
     }
     uint8_t* dst = (uint8_t*)_arena[a];

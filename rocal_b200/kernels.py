@@ -171,6 +171,22 @@ def box_iou_match(boxes, box_offsets, anchors, high_threshold, low_threshold, al
     return out
 
 
+def box_transform(boxes, labels, box_offsets, windows, rule, stream=None):
+    """rb200k_box_transform. boxes [total,4] f32, labels [total] i32, box_offsets [n+1] i32 - CUDA tensors; windows: numpy
+    BOX_WINDOW table (uploaded here) or a CUDA uint8 tensor holding one. Returns (out_boxes, out_labels, out_offsets) with
+    capacity total + n; out_offsets[n] is the number of valid entries."""
+    n = box_offsets.numel() - 1
+    total = boxes.shape[0]
+    d_win = to_device_table(windows, boxes.device) if isinstance(windows, np.ndarray) else windows
+    out_boxes = torch.empty((total + n, 4), dtype=torch.float32, device=boxes.device)
+    out_labels = torch.empty((total + n,), dtype=torch.int32, device=boxes.device)
+    out_offsets = torch.empty((n + 1,), dtype=torch.int32, device=boxes.device)
+    check(lib.rb200k_box_transform(boxes.data_ptr(), labels.data_ptr(), box_offsets.data_ptr(), n, d_win.data_ptr(), int(rule),
+                                   out_boxes.data_ptr(), out_labels.data_ptr(), out_offsets.data_ptr(), _stream_ptr(stream)),
+          "rb200k_box_transform")
+    return out_boxes, out_labels, out_offsets
+
+
 def normalize_scratch_bytes(n, max_w, max_h, axis_mask):
     return int(lib.rb200k_normalize_scratch_bytes(int(n), int(max_w), int(max_h), int(axis_mask)))
 

@@ -26,6 +26,11 @@ WARP_SAMPLE = np.dtype([
     ("dst_w", "<i4"), ("dst_h", "<i4"),
     ("reserved", "<i4", (3,))], align=True)
 
+BOX_WINDOW = np.dtype([("l", "<f4"), ("t", "<f4"), ("r", "<f4"), ("b", "<f4"), ("mirror_h", "<i4"), ("mirror_v", "<i4"),
+                       ("reserved", "<i4", (2,))], align=True)
+BOX_RULE_QUARTER_AREA, BOX_RULE_CENTRE = 0, 1
+
 assert RESAMPLE_SAMPLE.itemsize == 64 and POINTWISE_SAMPLE.itemsize == 64 and WARP_SAMPLE.itemsize == 64
+assert BOX_WINDOW.itemsize == 32
 
 NP_DTYPE = {FP32: np.float32, FP16: np.float16, UINT8: np.uint8}

@@ -619,3 +619,39 @@ def test_overlapped_launches_are_exact(cuda):
         assert np.array_equal(c1.cpu().numpy(), O.resample(s["arena"], s["t"], 224, 224, T.FP32, T.NCHW, mul, add))
         assert np.array_equal(c2.cpu().numpy(), O.pointwise(s["arena"], s["pt"], 224, 224, T.COLOR_BRIGHTNESS))
         assert np.array_equal(c3.cpu().numpy(), O.warp_affine(s["arena"], s["wt"], 160, 120))
+
+
+@pytest.mark.parametrize("rule", [0, 1])
+def test_box_transform_on_the_device(cuda, rule):
+    """rb200k_box_transform: boxes that live in device memory through a crop window and mirrors, bit for bit the
+    float32 restatement (quarter-area rule of the crop meta nodes / centre rule of the SSD crop), samples without
+    boxes and samples that lose all of theirs included; its outputs feed the encoder directly."""
+    import torch
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(4, 900 + rule)
+    n = 97
+    boxes, labels, offs = S.random_boxes(rng, n, (0, 40), size_range=(0.02, 0.6))
+    win = np.zeros(n, dtype=T.BOX_WINDOW)
+    l, t = rng.uniform(0, 0.6, n), rng.uniform(0, 0.6, n)
+    win["l"], win["t"] = l, t
+    win["r"], win["b"] = l + rng.uniform(0.05, 0.4, n), t + rng.uniform(0.05, 0.4, n)
+    win["l"][0], win["t"][0], win["r"][0], win["b"][0] = 0, 0, 1, 1            # the whole image
+    win["mirror_h"], win["mirror_v"] = rng.integers(0, 2, n), rng.integers(0, 2, n)
+    if len(boxes):
+        boxes[0, 2:] = boxes[0, :2]                                          # an empty box: 0 / 0 under the area rule
+    windows = np.stack([win["l"], win["t"], win["r"], win["b"]], 1)
+    eb, el, eo = O.box_transform(boxes, labels, offs, windows, rule, win["mirror_h"], win["mirror_v"])
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    gb, gl, go = K.box_transform(d(boxes), d(labels), d(offs), win, rule)
+    go = go.cpu().numpy()
+    assert np.array_equal(go, eo)
+    total = int(go[-1])
+    assert np.array_equal(gl.cpu().numpy()[:total], el)
+    assert np.array_equal(gb.cpu().numpy()[:total].view(np.uint32), eb.view(np.uint32))
+    assert int((el > 0).sum()) > 50 and int((el == 0).sum()) > 5             # both kinds of samples occurred
+    # straight into the encoder
+    anchors = S.ssd300_anchors()[::7].copy()
+    xb, xl = K.box_encode(gb, gl, torch.from_numpy(go).to(cuda), d(anchors), 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0, 64)
+    rb, rl = O.box_encode(eb, el, eo, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
+    assert np.array_equal(xl.cpu().numpy(), rl) and np.allclose(xb.cpu().numpy(), rb, rtol=1e-5, atol=1e-6)
+    assert _device_status() == 0
