@@ -246,6 +246,41 @@ def test_bbox_crop_windows_match_reference_build():
         assert np.array_equal(_product_bbox_windows(seed, overlap, boxes, offsets, img_w), want), k
 
 
+def test_normalised_box_transform_agrees_with_the_pinned_rules():
+    """The normalised form the library uses (pyoracle.box_transform: what the host pipeline and rb200k_box_transform are
+    compared with) against the restatements that are pinned to, or written from, the reference's pixel-space code: the
+    centre rule against update_random_bbox_meta_data (pinned), the quarter-area rule against the CropMetaNode
+    restatement. Same boxes kept, same order, coordinates equal after the change of units."""
+    rng = np.random.Generator(np.random.PCG64(36))
+    n = 40
+    boxes, labels, offs = S.random_boxes(rng, n, (0, 12), size_range=(0.02, 0.7))
+    l, t = rng.uniform(0, 0.5, n), rng.uniform(0, 0.5, n)
+    win = np.stack([l, t, l + rng.uniform(0.2, 0.5, n), t + rng.uniform(0.2, 0.5, n)], 1).astype(np.float32)
+    # centre rule: the pinned function on a 1 x 1 "decoded size" works on normalised boxes; it shifts, we also divide
+    xywh = np.stack([win[:, 0], win[:, 1], win[:, 2] - win[:, 0], win[:, 3] - win[:, 1]], 1).astype(np.float32)
+    pb, pl, po = O.random_bbox_meta(boxes, labels, offs, xywh, np.ones((n, 2), np.uint32))
+    nb, nl, no = O.box_transform(boxes, labels, offs, win, 1)
+    assert np.array_equal(po, no) and np.array_equal(pl, nl)
+    rep = np.repeat(xywh[:, 2:], np.diff(po), axis=0)
+    assert np.allclose(pb / np.concatenate([rep, rep], 1), nb, atol=2e-6)
+    # quarter-area rule: CropMetaNode works in pixels of a W x H image with an integer window
+    wh = rng.integers(200, 900, (n, 2))
+    pxwin = np.stack([(win[:, 0] * wh[:, 0]).astype(int), (win[:, 1] * wh[:, 1]).astype(int),
+                      np.maximum(1, ((win[:, 2] - win[:, 0]) * wh[:, 0]).astype(int)),
+                      np.maximum(1, ((win[:, 3] - win[:, 1]) * wh[:, 1]).astype(int))], 1)
+    rep = np.repeat(wh.astype(np.float32), np.diff(offs), axis=0)
+    px = (boxes * np.concatenate([rep, rep], 1)).astype(np.float32)
+    cb, cl, co = O.meta_crop(px, labels, offs, [tuple(int(v) for v in w) for w in pxwin])
+    nwin = np.stack([pxwin[:, 0] / wh[:, 0], pxwin[:, 1] / wh[:, 1], (pxwin[:, 0] + pxwin[:, 2]) / wh[:, 0],
+                     (pxwin[:, 1] + pxwin[:, 3]) / wh[:, 1]], 1).astype(np.float32)
+    nb, nl, no = O.box_transform(boxes, labels, offs, nwin, 0)
+    # (a box exactly at the 0.25 threshold could fall on either side in the two units; none does for this seed)
+    assert np.array_equal(co, no) and np.array_equal(cl, nl)
+    rep = np.repeat(pxwin[:, 2:].astype(np.float32), np.diff(co), axis=0)
+    assert np.allclose(cb / np.concatenate([rep, rep], 1), nb, atol=1e-4)
+    assert int((nl > 0).sum()) > 40
+
+
 def test_rotate_meta_restatement_on_hand_cases():
     """RotateMetaNode restated: no rotation keeps the right / bottom edges and, as the node is written, pulls the left /
     top edges to the image corner; a box rotated out of the destination is dropped and the sample gets the whole image."""
