@@ -827,8 +827,20 @@ def main():
     torch.cuda.synchronize()
     link_gbs = link_reps * arena_pinned.numel() / (time.perf_counter() - tl) / 1e9
     barrier()
+    # ---- and what the host's memory gives its cores at the same moment: every rank streams its pinned arena ----
+    read_threads = max(1, (os.cpu_count() or 1) // max(world, 1) // 2)
+    torch.set_num_threads(read_threads)
+    words = arena_pinned[:arena_pinned.numel() // 8 * 8].view(torch.int64)
+    words.sum()
+    barrier()
+    tl = time.perf_counter()
+    for _ in range(3):
+        words.sum()
+    host_read_gbs = 3 * words.numel() * 8 / (time.perf_counter() - tl) / 1e9
+    barrier()
 
-    mine = torch.tensor([total_ms, e2e_ms, float(h2d_per_step), float(np.mean(launch_ms)), link_gbs], dtype=torch.float64, device=dev)
+    mine = torch.tensor([total_ms, e2e_ms, float(h2d_per_step), float(np.mean(launch_ms)), link_gbs, host_read_gbs, float(read_threads)],
+                        dtype=torch.float64, device=dev)
     if world > 1:
         gathered = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
@@ -841,7 +853,7 @@ def main():
         g = [float(v) for v in g.cpu()]
         per_rank.append({"rank": r_, "device_ms_per_step": g[0] / args.steps, "kernel_ms": g[3], "e2e_ms_per_step": g[1] / e2e_steps,
                          "h2d_bytes_per_step": int(g[2]), "host_link_gbs": g[2] * e2e_steps / (g[1] * 1e-3) / 1e9,
-                         "link_copy_gbs": g[4], "numa": numas[r_]})
+                         "link_copy_gbs": g[4], "host_read_gbs": g[5], "host_read_threads": int(g[6]), "numa": numas[r_]})
     total_ms = max(p_["device_ms_per_step"] for p_ in per_rank) * args.steps
     e2e_ms = max(p_["e2e_ms_per_step"] for p_ in per_rank) * e2e_steps
 
@@ -866,9 +878,11 @@ def main():
                     "steps": e2e_steps, "timed": "clock starts before the first feed; every batch's feed, transfer and kernel inside",
                     "host_link_gbs": sum(p_["host_link_gbs"] for p_ in per_rank),
                     "link_copy_gbs": sum(p_["link_copy_gbs"] for p_ in per_rank),
+                    "host_read_gbs": sum(p_["host_read_gbs"] for p_ in per_rank),
                     "link_note": "host_link_gbs = bytes the zero-copy kernels pulled per second, all ranks; link_copy_gbs = "
                                  "plain pinned-to-device copies of the same arenas issued by all ranks at once (what the host "
-                                 "and its PCIe links deliver to this many GPUs together)"},
+                                 "and its PCIe links deliver to this many GPUs together); host_read_gbs = the same arenas summed "
+                                 "by host threads of every rank at once (what the host's memory gives its own cores)"},
             "gpu_launches": int(launches),
             "per_rank": per_rank,
             "roofline": {"bound": "hbm", "kernel": "resample_stream_kernel<half,NCHW,normalize>", "achieved": achieved,
