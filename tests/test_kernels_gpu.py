@@ -115,6 +115,27 @@ def test_strip_rows_do_not_change_the_result(cuda, n):
     assert _device_status() == 0
 
 
+@pytest.mark.parametrize("path", [2, 3])
+def test_stream_kernel_wide_sources_take_the_short_ring(cuda, path):
+    """Source spans above 12 KB per tile row leave room for only half the ring (2 stages of row pairs / 4 row slots
+    instead of 4 / 8): 6000-pixel-wide images squeezed into one 512-column tile, down- and up-scaled vertically, both
+    rings, against the oracle."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(11, path)
+    arena, hs, ws, offs = S.make_images(rng, 3, (20, 90), (5200, 6000), content="noise")
+    n = len(hs)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    t["roi_w"], t["roi_h"] = ws, hs
+    t["dst_w"], t["dst_h"] = [512, 400, 300], [45, 30, 64]             # 10 .. 20 source pixels per output pixel across
+    t["crop_w"], t["crop_h"] = t["dst_w"], t["dst_h"]
+    t["mirror"] = [0, 1, 0]
+    ref = O.resample(arena, t, 512, 64, T.UINT8, T.NHWC)
+    got = K.resample(_dev(arena, cuda), t, 512, 64, T.UINT8, T.NHWC, path=path).cpu().numpy()
+    assert np.array_equal(got, ref)
+    assert _device_status() == 0
+
+
 def test_resize_only_ragged_output(cuda):
     """Plain Resize: uint8 HWC out, per-sample output sizes inside a larger max-shape tensor; only
     the ROI is defined (padding not filled), up- and down-scaling, odd sizes."""
