@@ -386,7 +386,11 @@ RB200_API size_t rb200_get_bounding_boxes(rb200_context ctx, float* ltrb, int* l
  * source window of the crop-type operator (Crop*, CropMirrorNormalize, ResizeCropMirror, SSDRandomCrop)
  * that produced `t`. rb200_get_int_array / rb200_get_float_array: the current per-sample values of a
  * parameter (n = batch size; the parameter must be in use by a verified graph); they return the number
- * of values written. */
+ * of values written. Parameters are process-wide objects that the loader thread renews for every batch it prepares:
+ * with an external source fed one batch at a time the values are those of the batch rb200_run just returned; with a
+ * folder or COCO source, which keeps the ring filled ahead, they already belong to the newest prepared batch. The
+ * windows (rb200_get_crop_windows, rb200_get_decoder_crop_windows, rb200_get_bbox_crop_windows) and the boxes are kept
+ * per batch and always describe the returned one. */
 RB200_API int rb200_get_crop_windows(rb200_context ctx, rb200_tensor t, unsigned* xywh);
 RB200_API size_t rb200_get_int_array(rb200_param p, int* out, size_t n);
 RB200_API size_t rb200_get_float_array(rb200_param p, float* out, size_t n);

@@ -1445,7 +1445,6 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
     _whole_h.assign(n, 0);
     size_t bbox_box0 = 0;
     if (_bbox_crop) {
-        if (_crop_dec) RB200_THROW("rocalRandomBBoxCrop and a random-crop JPEG source cannot both cut the source images");
         if (!b.has_boxes || b.counts.size() != n)
             RB200_THROW("rocalRandomBBoxCrop: the batch carries no bounding boxes (feed them, or use a COCO source)");
         s.decoder_windows.resize(n * 4);
@@ -1497,7 +1496,9 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         size_t total = 0;
         _decode_off.resize(n);
         _decode_h.resize(n);
-        if (_crop_dec) {
+        // behind rocalRandomBBoxCrop the fused decoder cuts the box-aware windows, not its own random ones
+        // (FusedCropTJDecoder::decode, fused_crop_decoder.cpp:76-85: the bbox coordinates win when there are any)
+        if (_crop_dec && !_bbox_crop) {
             s.decoder_batch_seed = _crop_dec->next_batch(n);
             s.decoder_windows.resize(n * 4);
         }
@@ -1515,7 +1516,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
             if (_crop_dec || _bbox_crop) {
                 // the whole image is decoded; the graph sees the window as its source image (a view into it)
                 CropRect win;
-                if (_crop_dec) {
+                if (_crop_dec && !_bbox_crop) {
                     win = _crop_dec->window(h, w, i);
                     unsigned* dw = &s.decoder_windows[i * 4];
                     dw[0] = win.x; dw[1] = win.y; dw[2] = win.w; dw[3] = win.h;

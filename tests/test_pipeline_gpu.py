@@ -320,6 +320,91 @@ def test_coco_source_pipeline(cuda, tmp_path):
     pipe.rocal_release()
 
 
+def test_ssd_training_pipeline_from_coco_files(cuda, tmp_path):
+    """The reference's SSD training graph from a COCO folder (readers.coco -> random_bbox_crop -> decoders.image_slice ->
+    resize 300 x 300 -> crop_mirror_normalize(mirror) -> box_encoder), two batches. Behind random_bbox_crop the fused
+    decoder cuts the box-aware windows: they are the pinned sampler's (its counter runs on across batches), the pixels
+    are the oracle's resize + mirror + normalise of that window of the decoder's own pixels, the boxes follow by the
+    centre rule, then the mirror, and reach the encoder. (The mirror is a constant here: with a folder source the loader
+    works ahead, so a random parameter's array already belongs to a later batch when this one is read.)"""
+    import json
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    rng = S.rng_for(27)
+    n, files = 4, 8
+    imgs, streams = _jpeg_batch(rng, files, (150, 320))
+    pixels = _decoded_by_pipeline(streams, 320)
+    images, anns, truth = [], [], {}
+    for i, (im, sb) in enumerate(zip(imgs, streams)):
+        name = "s%02d.jpg" % i
+        (tmp_path / name).write_bytes(sb)
+        h, w = im.shape[:2]
+        images.append({"id": 500 + i, "file_name": name, "width": w, "height": h})
+        bx = []
+        for _ in range(int(rng.integers(1, 5))):
+            x, y = float(rng.uniform(0, w * 0.6)), float(rng.uniform(0, h * 0.6))
+            bw, bh = float(rng.uniform(w * 0.15, w * 0.4)), float(rng.uniform(h * 0.15, h * 0.4))
+            anns.append({"id": len(anns), "image_id": 500 + i, "category_id": 9, "bbox": [x, y, bw, bh], "iscrowd": 0})
+            # the reader's arithmetic: corners summed in double, narrowed to float, divided by the float size
+            bx.append([np.float32(x) / np.float32(w), np.float32(y) / np.float32(h),
+                       np.float32(x + bw) / np.float32(w), np.float32(y + bh) / np.float32(h)])
+        truth[name] = np.array(bx, dtype=np.float32)
+    (tmp_path / "ann.json").write_text(json.dumps({"images": images, "annotations": anns, "categories": [{"id": 9}]}))
+    anchors = S.ssd300_anchors()[::4].copy()
+    seed = 77
+    pipe = Pipeline(batch_size=n, device_id=0, seed=8)
+    with pipe:
+        jpegs, _, _ = fn.readers.coco(annotations_file=str(tmp_path / "ann.json"), ltrb=True, is_box_encoder=True)
+        fn.random_bbox_crop(all_boxes_above_threshold=False, seed=seed)
+        img = fn.decoders.image_slice(jpegs, file_root=str(tmp_path), annotations_file=str(tmp_path / "ann.json"),
+                                      max_decoded_width=320, max_decoded_height=320)
+        r = fn.resize(img, resize_width=300, resize_height=300, scaling_mode=types.SCALING_MODE_STRETCH)
+        out = fn.crop_mirror_normalize(r, crop=[300, 300], crop_pos_x=0.0, crop_pos_y=0.0, mean=MEAN, std=STD, mirror=1,
+                                       output_layout=types.NCHW, output_dtype=types.FLOAT)
+        fn.box_encoder(anchors=anchors, criteria=0.5, means=[0, 0, 0, 0], stds=[0.1, 0.1, 0.2, 0.2], offset=True, scale=1.0)
+        pipe.set_outputs(out)
+    pipe.build()
+    sampler = O.BBoxCropSampler(seed, False)
+    mul, add = S.normalize_tables()
+    flags = np.ones(n, dtype=np.int32)
+    cropped = 0
+    for batch in range(2):
+        got = pipe.run()[0].numpy()
+        names = pipe.get_image_names()
+        idx = [int(nm[1:3]) for nm in names]
+        assert idx == list(range(batch * n, batch * n + n))
+        boxes = np.concatenate([truth[nm] for nm in names])
+        offs = np.concatenate([[0], np.cumsum([len(truth[nm]) for nm in names])]).astype(np.int32)
+        ws = np.array([pixels[i].shape[1] for i in idx])
+        hs = np.array([pixels[i].shape[0] for i in idx])
+        frac = sampler.windows(boxes, offs, ws)
+        assert np.array_equal(pipe.get_bbox_crop_windows(), frac)
+        win, _ = pipe.get_decoder_crop_windows()
+        cropped += int((win[:, 2] < ws).sum())
+        # pixels: window of the decoder's pixels -> 300 x 300 -> mirror -> normalise, one launch in the oracle too
+        arena = np.concatenate([pixels[i].reshape(-1) for i in idx])
+        poffs = np.concatenate([[0], np.cumsum([pixels[i].size for i in idx])])[:-1]
+        t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        t["src_stride"] = ws * 3
+        t["src_offset"] = poffs + win[:, 1].astype(np.int64) * t["src_stride"] + win[:, 0].astype(np.int64) * 3
+        t["roi_w"], t["roi_h"], t["dst_w"], t["dst_h"], t["crop_w"], t["crop_h"] = win[:, 2], win[:, 3], 300, 300, 300, 300
+        t["mirror"] = flags
+        assert np.array_equal(got, O.resample(arena, t, 300, 300, T.FP32, T.NCHW, mul, add))
+        # boxes: centre rule against the pixel window, then the whole-image CropMirrorNormalize with its mirror
+        wf = win.astype(np.float32)
+        nwin = np.stack([wf[:, 0] / ws, wf[:, 1] / hs, (wf[:, 0] + wf[:, 2]) / ws, (wf[:, 1] + wf[:, 3]) / hs], 1).astype(np.float32)
+        b1, l1, o1 = O.box_transform(boxes, np.ones(len(boxes), np.int32), offs, nwin, 1)
+        b2, l2, o2 = O.box_transform(b1, l1, o1, np.tile(np.array([[0, 0, 1, 1]], np.float32), (n, 1)), 0, mirror_h=flags)
+        gb, gl, gc = pipe.get_bounding_boxes()
+        assert np.array_equal(np.concatenate([[0], np.cumsum(gc)]), o2) and np.array_equal(gl, l2)
+        assert np.allclose(gb, b2, atol=3e-6)
+        eb, el = O.box_encode(gb, gl, o2, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
+        xb, xl = pipe.get_encoded_boxes_and_lables()
+        assert np.array_equal(xl, el) and np.allclose(xb, eb, rtol=1e-5, atol=1e-6)
+    assert cropped > 0
+    pipe.rocal_release()
+
+
 def test_resize_mirror_normalize_min_max(cuda):
     """rocalResizeMirrorNormalize with ROCAL_SCALING_MODE_MIN_MAX (the MaskRCNN resize): the shorter side becomes the
     minimum size unless the longer one would pass the maximum size; one fused launch, ragged outputs with their ROI."""
