@@ -394,6 +394,10 @@ RB200_API size_t rb200_get_bounding_boxes(rb200_context ctx, float* ltrb, int* l
 RB200_API int rb200_get_crop_windows(rb200_context ctx, rb200_tensor t, unsigned* xywh);
 RB200_API size_t rb200_get_int_array(rb200_param p, int* out, size_t n);
 RB200_API size_t rb200_get_float_array(rb200_param p, float* out, size_t n);
+/* [extension] The same for the batch rb200_run returned, whatever the loader has prepared since: every batch keeps a
+ * copy of the per-sample values it was built with. */
+RB200_API size_t rb200_get_batch_int_array(rb200_context ctx, rb200_param p, int* out, size_t n);
+RB200_API size_t rb200_get_batch_float_array(rb200_context ctx, rb200_param p, float* out, size_t n);
 
 #ifdef __cplusplus
 }

@@ -156,3 +156,5 @@ get_bounding_boxes = _proto("rb200_get_bounding_boxes", c_size_t, _P, POINTER(c_
 get_crop_windows = _proto("rb200_get_crop_windows", c_int, _P, _P, POINTER(c_uint))
 get_int_array = _proto("rb200_get_int_array", c_size_t, _P, POINTER(c_int), c_size_t)
 get_float_array = _proto("rb200_get_float_array", c_size_t, _P, POINTER(c_float), c_size_t)
+get_batch_int_array = _proto("rb200_get_batch_int_array", c_size_t, _P, _P, POINTER(c_int), c_size_t)
+get_batch_float_array = _proto("rb200_get_batch_float_array", c_size_t, _P, _P, POINTER(c_float), c_size_t)

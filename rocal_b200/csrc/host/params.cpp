@@ -122,6 +122,17 @@ Parameter<float>* ParameterFactory::default_float(float v) {
     return g;
 }
 
+void ParameterFactory::snapshot(size_t n, std::vector<std::pair<const void*, std::vector<int>>>& ints,
+                                std::vector<std::pair<const void*, std::vector<float>>>& floats) {
+    std::lock_guard<std::mutex> lk(_mutex);
+    ints.clear();
+    floats.clear();
+    for (auto* p : _ints)
+        if (p->array().size() == n) ints.emplace_back(p, p->array());
+    for (auto* p : _floats)
+        if (p->array().size() == n) floats.emplace_back(p, p->array());
+}
+
 bool ParameterFactory::owns(const void* handle) {
     std::lock_guard<std::mutex> lk(_mutex);
     return _handles.count(handle) != 0;

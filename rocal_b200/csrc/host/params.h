@@ -195,6 +195,9 @@ class ParameterFactory {
     Parameter<float>* default_float(float v);
 
     bool owns(const void* handle);
+    // Per-sample values of every parameter that currently holds an array of n values (what a batch was built with).
+    void snapshot(size_t n, std::vector<std::pair<const void*, std::vector<int>>>& ints,
+                  std::vector<std::pair<const void*, std::vector<float>>>& floats);
 
     ~ParameterFactory();
 

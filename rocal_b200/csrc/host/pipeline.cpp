@@ -1614,6 +1614,7 @@ void Pipeline::process(InputBatch& b, Slot& s, int slot_idx) {
         transform_boxes_window(s, wx, wy, ww, wh, _whole_w, _whole_h, true);
     }
     update_nodes(b, s);
+    ParameterFactory::instance().snapshot(n, s.int_params, s.float_params);
 
     auto view_of = [&](int tensor_id, size_t i, const uint8_t*& base) -> SampleView {
         TensorImpl* t = _tensors[tensor_id].get();
@@ -2201,6 +2202,28 @@ void Pipeline::to_tensor(void* out_ptr, int layout, int dtype, const float* mul,
     if (tmp) cudaFree(tmp);
     if (rc != 0) RB200_THROW(rb200k_last_error());
     if (err != cudaSuccess) RB200_THROW(std::string("rocalToTensor: ") + cudaGetErrorString(err));
+}
+
+size_t Pipeline::batch_int_array(const void* core, int* out, size_t n) {
+    if (_held < 0 || !out) return 0;
+    for (const auto& kv : _slots[_held].int_params)
+        if (kv.first == core) {
+            const size_t k = std::min(n, kv.second.size());
+            std::copy(kv.second.begin(), kv.second.begin() + k, out);
+            return k;
+        }
+    return 0;
+}
+
+size_t Pipeline::batch_float_array(const void* core, float* out, size_t n) {
+    if (_held < 0 || !out) return 0;
+    for (const auto& kv : _slots[_held].float_params)
+        if (kv.first == core) {
+            const size_t k = std::min(n, kv.second.size());
+            std::copy(kv.second.begin(), kv.second.begin() + k, out);
+            return k;
+        }
+    return 0;
 }
 
 void Pipeline::set_profiling(bool on) {

@@ -226,6 +226,8 @@ struct Slot {
     unsigned decoder_batch_seed = 0;
     size_t n = 0;
     std::string error;
+    std::vector<std::pair<const void*, std::vector<int>>> int_params;       // per-sample parameter values this batch
+    std::vector<std::pair<const void*, std::vector<float>>> float_params;   // was built with, by parameter object
     std::vector<cudaEvent_t> step_ev;        // profiling: before the upload, after it, after every launch of the batch
     bool step_ev_valid = false;              // the events of this slot were recorded for the batch it holds
 };
@@ -256,6 +258,9 @@ class Pipeline {
     // rocalFusedJpegCrop*: every image of an encoded source is cut to a random-resized-crop window before the graph
     // Per-launch device timing with CUDA events (off by default; RB200_PROFILE=1 in the environment turns it on for
     // every context). Must be chosen before verify().
+    // The per-sample values of a parameter for the batch that run() returned (0 values when it has none).
+    size_t batch_int_array(const void* core, int* out, size_t n);
+    size_t batch_float_array(const void* core, float* out, size_t n);
     void set_profiling(bool on);
     std::vector<StepTiming> step_timing();
     void set_random_crop_decoder(const RandomCropRanges& r);

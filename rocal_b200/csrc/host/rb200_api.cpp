@@ -1388,6 +1388,16 @@ size_t rb200_get_int_array(rb200_param p, int* out, size_t n) {
     return k;
 }
 
+size_t rb200_get_batch_int_array(rb200_context ctx, rb200_param p, int* out, size_t n) {
+    if (!ctx || !p || !out || !ParameterFactory::instance().owns(p)) return 0;
+    return P(ctx)->batch_int_array(IP(p)->core, out, n);
+}
+
+size_t rb200_get_batch_float_array(rb200_context ctx, rb200_param p, float* out, size_t n) {
+    if (!ctx || !p || !out || !ParameterFactory::instance().owns(p)) return 0;
+    return P(ctx)->batch_float_array(FP(p)->core, out, n);
+}
+
 size_t rb200_get_float_array(rb200_param p, float* out, size_t n) {
     if (!p || !out || !ParameterFactory::instance().owns(p)) return 0;
     const auto& a = FP(p)->core->array();

@@ -478,12 +478,17 @@ class Pipeline(object):
 
     def get_int_array(self, param):
         out = np.zeros(self._batch_size, dtype=np.int32)
-        k = C.get_int_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), self._batch_size)
+        # the values the returned batch was built with; before the first run(), the parameter's current ones
+        k = C.get_batch_int_array(self._handle, param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), self._batch_size)
+        if k == 0:
+            k = C.get_int_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), self._batch_size)
         return out[:k]
 
     def get_float_array(self, param):
         out = np.zeros(self._batch_size, dtype=np.float32)
-        k = C.get_float_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), self._batch_size)
+        k = C.get_batch_float_array(self._handle, param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), self._batch_size)
+        if k == 0:
+            k = C.get_float_array(param, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), self._batch_size)
         return out[:k]
 
     def get_remaining_images(self):

@@ -40,7 +40,8 @@ int main(int argc, char** argv) {
     RocalTensor b = rocalBrightnessFixed(ctx, r, 1.0f, 0.0f, false);
     CHECK(ctx, b);
     std::vector<float> mean{0.f, 0.f, 0.f}, sd{1.f, 1.f, 1.f};
-    RocalTensor o = rocalCropMirrorNormalize(ctx, b, 8, 8, 0.5f, 0.5f, mean, sd, true, rocalCreateIntUniformRand(0, 1), ROCAL_NCHW, ROCAL_FP32);
+    RocalIntParam coin = rocalCreateIntUniformRand(0, 1);
+    RocalTensor o = rocalCropMirrorNormalize(ctx, b, 8, 8, 0.5f, 0.5f, mean, sd, true, coin, ROCAL_NCHW, ROCAL_FP32);
     CHECK(ctx, o);
     std::vector<float> anchors;
     for (int i = 0; i < 32; i++) { anchors.insert(anchors.end(), {0.03f * i, 0.02f * i, 0.03f * i + 0.1f, 0.02f * i + 0.2f}); }
@@ -97,6 +98,9 @@ int main(int argc, char** argv) {
         CHECK(ctx, total >= (size_t)n && total <= 64);
         rocalCopyEncodedBoxesAndLables(ctx, enc.data(), enc_labels.data());
         for (int i = 0; i < n; i++) CHECK(ctx, enc_labels[(size_t)i * 32] == gc[(size_t)i]);    // the encoder saw this batch's boxes
+        int coins[6];          // the returned batch's own draws, read while the loader prepares later batches
+        CHECK(ctx, rb200_get_batch_int_array(ctx, coin, coins, 6) == 6);
+        for (int i = 0; i < n; i++) CHECK(ctx, coins[i] == 0 || coins[i] == 1);
         unsigned win[6 * 4];
         CHECK(ctx, rb200_get_decoder_crop_windows(ctx, win, nullptr) == 0);
         for (int i = 0; i < n; i++) CHECK(ctx, win[i * 4] + win[i * 4 + 2] <= (unsigned)W && win[i * 4 + 1] + win[i * 4 + 3] <= (unsigned)H);

@@ -325,8 +325,9 @@ def test_ssd_training_pipeline_from_coco_files(cuda, tmp_path):
     resize 300 x 300 -> crop_mirror_normalize(mirror) -> box_encoder), two batches. Behind random_bbox_crop the fused
     decoder cuts the box-aware windows: they are the pinned sampler's (its counter runs on across batches), the pixels
     are the oracle's resize + mirror + normalise of that window of the decoder's own pixels, the boxes follow by the
-    centre rule, then the mirror, and reach the encoder. (The mirror is a constant here: with a folder source the loader
-    works ahead, so a random parameter's array already belongs to a later batch when this one is read.)"""
+    centre rule, then the mirror, and reach the encoder. The mirror is a coin flip per sample: its values are read back per
+    batch (the loader works ahead with a folder source, so the parameter object itself already holds a later batch's
+    draws when this one is returned)."""
     import json
     from rocal_b200 import fn, types
     from rocal_b200.pipeline import Pipeline
@@ -359,17 +360,19 @@ def test_ssd_training_pipeline_from_coco_files(cuda, tmp_path):
         img = fn.decoders.image_slice(jpegs, file_root=str(tmp_path), annotations_file=str(tmp_path / "ann.json"),
                                       max_decoded_width=320, max_decoded_height=320)
         r = fn.resize(img, resize_width=300, resize_height=300, scaling_mode=types.SCALING_MODE_STRETCH)
-        out = fn.crop_mirror_normalize(r, crop=[300, 300], crop_pos_x=0.0, crop_pos_y=0.0, mean=MEAN, std=STD, mirror=1,
+        mirror = fn.random.coin_flip()
+        out = fn.crop_mirror_normalize(r, crop=[300, 300], crop_pos_x=0.0, crop_pos_y=0.0, mean=MEAN, std=STD, mirror=mirror,
                                        output_layout=types.NCHW, output_dtype=types.FLOAT)
         fn.box_encoder(anchors=anchors, criteria=0.5, means=[0, 0, 0, 0], stds=[0.1, 0.1, 0.2, 0.2], offset=True, scale=1.0)
         pipe.set_outputs(out)
     pipe.build()
     sampler = O.BBoxCropSampler(seed, False)
     mul, add = S.normalize_tables()
-    flags = np.ones(n, dtype=np.int32)
-    cropped = 0
+    cropped, seen_flags = 0, set()
     for batch in range(2):
         got = pipe.run()[0].numpy()
+        flags = pipe.get_int_array(mirror)
+        seen_flags.update(int(v) for v in flags)
         names = pipe.get_image_names()
         idx = [int(nm[1:3]) for nm in names]
         assert idx == list(range(batch * n, batch * n + n))
@@ -401,7 +404,7 @@ def test_ssd_training_pipeline_from_coco_files(cuda, tmp_path):
         eb, el = O.box_encode(gb, gl, o2, anchors, 0.5, (0, 0, 0, 0), (0.1, 0.1, 0.2, 0.2), True, 1.0)
         xb, xl = pipe.get_encoded_boxes_and_lables()
         assert np.array_equal(xl, el) and np.allclose(xb, eb, rtol=1e-5, atol=1e-6)
-    assert cropped > 0
+    assert cropped > 0 and seen_flags == {0, 1}
     pipe.rocal_release()
 
 
