@@ -81,7 +81,7 @@ __device__ __forceinline__ void box_step(const float4 b, int j, int box, const f
 
 // K = anchors per thread: per_cta <= K * blockDim.x.
 template <int K>
-__global__ void __launch_bounds__((K == 4 ? 320 : 512), (K == 4 ? 3 : 1)) box_encode_kernel(const float4* __restrict__ boxes,
+__global__ void __launch_bounds__((K == 4 ? 320 : 512), (K == 4 ? 4 : 1)) box_encode_kernel(const float4* __restrict__ boxes,
                                                           const int* __restrict__ labels,
                                                           const int* __restrict__ box_offsets,
                                                           float4* __restrict__ out_boxes,
