@@ -446,10 +446,12 @@ __device__ __forceinline__ void color_block_u8(const uint32_t (&d)[3], uint32_t 
 }
 
 template <typename OutT, int LAYOUT, int COLOR_OP>
-// The ColorTwist instantiations are bound by latency (the CTA waits once for its staged rows) as much as by issue:
-// five resident CTAs per SM (48 registers) measured 37 / 27 us per 256-image launch (exact / fast arithmetic)
-// against 51 / 33 us at the register count the compiler picks on its own (122 / 70: two or three CTAs per SM).
-__global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP == RB200_COLOR_TWIST) ? 5 : 1) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
+// Every instantiation is bound by latency (a CTA waits once for its staged rows) as much as by issue, so the minimum
+// number of resident CTAs per SM is asked for explicitly. ColorTwist: six (40 registers) measured 37 / 27 us per
+// 256-image launch (exact / fast arithmetic) against 51 / 33 us at the register count the compiler picks on its own
+// (122 / 70: two or three CTAs per SM). The others: seven (32 registers, a few dozen bytes of spills in some) measured
+// 15.5 us (brightness) and 15.4 us (flip) against 21.9 / 19.1 us at the compiler's 48-50 registers.
+__global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP == RB200_COLOR_TWIST) ? 6 : 7) pointwise_vec_kernel(const uint8_t* __restrict__ arena,
                                                             const rb200_pointwise_sample* __restrict__ samples,
                                                             const PointwiseLaunch L) {
     // Layout: mbarrier (16 bytes) | rcp[256] | staged source rows (th x pitch)
