@@ -227,7 +227,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=F
     resident, feeders, extra, image_only = [], [], {}, []
     if cfg == 0:
         n, rot, name = 64, 6, "configs[0]: Resize(shorter=256)+CropMirrorNormalize 224x224 fp32 NCHW, batch 64, H,W~U[256,512]"
-        kernel = "resample_stream_kernel<float,NCHW,normalize>"
+        kernel = "resample_stream_pairs_kernel<float,NCHW,normalize>"
         pipe = Pipeline(batch_size=n, device_id=0, seed=1234, prefetch_queue_depth=2)
         with pipe:
             img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=512, max_height=512)
@@ -310,7 +310,7 @@ def measure_config(cfg, steps, warmup, e2e_steps, with_cpu, sampler=None, fast=F
     else:
         n, rot, name = 128, 2, ("configs[4]: SSDRandomCrop -> Resize 300x300 -> CropMirrorNormalize fp32 NCHW + BoxEncoder "
                                 "(8732 anchors, criteria 0.5, offset), batch 128, H,W~U[300,800], 1-50 boxes")
-        kernel = "resample_stream_kernel<float,NCHW,normalize> (+ box_encode_kernel<4>)"
+        kernel = "resample_stream_pairs_kernel<float,NCHW,normalize> (+ box_encode_kernel<4>)"
         anchors_np = S.ssd300_anchors()
         anchors_d = torch.from_numpy(anchors_np).to(dev)
         meta_stream = torch.cuda.Stream()
@@ -885,7 +885,7 @@ def main():
                                  "by host threads of every rank at once (what the host's memory gives its own cores)"},
             "gpu_launches": int(launches),
             "per_rank": per_rank,
-            "roofline": {"bound": "hbm", "kernel": "resample_stream_kernel<half,NCHW,normalize>", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "resample_stream_pairs_kernel<half,NCHW,normalize>", "achieved": achieved,
                          "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                          "algorithmic_bytes_per_launch": algo, "launch_ms": mean_launch_ms,
                          "traffic": NCU_TRAFFIC_BYTES_PER_IMAGE * n, "traffic_source": "ncu, 512-image launch scaled by images"},
