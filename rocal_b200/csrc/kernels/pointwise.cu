@@ -551,7 +551,8 @@ __global__ void __launch_bounds__(256, (COLOR_OP == kColorTwistFast || COLOR_OP 
         if (w16 > 0) {
             const int upr = w16 >> 4;
             const int units = rows * upr;
-            const uint32_t upr_magic = (uint32_t)((0x100000000ull + (uint32_t)upr - 1) / (uint32_t)upr);
+            const uint32_t upr_div = (uint32_t)(upr > 0 ? upr : 1);     // upr >= 1 here; spelled out for instantiations where w16 folds to 0
+            const uint32_t upr_magic = (uint32_t)((0x100000000ull + upr_div - 1) / upr_div);
             uint8_t* const out_bytes = reinterpret_cast<uint8_t*>(out_tile);
             const bool st16 = ((reinterpret_cast<uintptr_t>(out_bytes) | (uintptr_t)(L.out_w * 3)) & 15u) == 0;
             for (int unit = threadIdx.x; unit < units; unit += blockDim.x) {

@@ -616,7 +616,6 @@ __global__ void __launch_bounds__(288, 4) resample_stream_kernel(const uint8_t* 
                                        L.status);
     if (rows_valid > 0 && cols_valid > 0 && src_ok) {
         const uint8_t* img = arena + sp->src_offset;
-        const uint32_t stride = sp->src_stride;
         const int roi_x = sp->roi_x, roi_w = sp->roi_w;
         const int crop_x = sp->crop_x, mirror = sp->mirror;
         const int x_lo = roi_x, x_hi = max(roi_x + roi_w - 2, roi_x);
@@ -747,7 +746,7 @@ template <typename OutT, int LAYOUT, bool NORMALIZE>
 __global__ void __launch_bounds__(256) resample_staged_kernel(const uint8_t* __restrict__ arena,
                                                               const rb200_resample_sample* __restrict__ samples,
                                                               const ResampleLaunch L) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     // Layout: TileHeader | StagedRow[th] | int srow[2*th+2] | (16-byte aligned) staged rows
     TileHeader* hdr = reinterpret_cast<TileHeader*>(smem);
     StagedRow* rows = reinterpret_cast<StagedRow*>(smem + sizeof(TileHeader));
