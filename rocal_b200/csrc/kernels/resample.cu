@@ -28,6 +28,8 @@
 #include <mutex>
 #include <vector>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace rb200 {
@@ -151,7 +153,9 @@ struct StagedRow {
 
 // One output row of one thread: two adjacent pixels, three channels, blended from staged rows at byte
 // offsets off0 / off1 (the row's first staged pixel) and stored at po.
-template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED>
+// EDGE = false promises that no lane's right tap is clamped onto its left one (ct[p].same is false for both
+// columns), which drops the four selects that serve those border lanes.
+template <typename OutT, int LAYOUT, bool NORMALIZE, bool PAIRED, bool EDGE = true>
 __device__ __forceinline__ void blend_store(const uint8_t* stage, int off0, int off1, float2 wy2, float2 owy2,
                                             const ColumnTaps (&ct)[2], float2 wx2, float2 owx2, bool second,
                                             const float (&mulv)[3], const float (&addv)[3], const uint32_t magic,
@@ -164,8 +168,10 @@ __device__ __forceinline__ void blend_store(const uint8_t* stage, int off0, int 
     for (int p = 0; p < 2; p++) {
         fetch_pair(stage, off0 + ct[p].o_left, l0[p], r0[p]);
         fetch_pair(stage, off1 + ct[p].o_left, l1[p], r1[p]);
-        r0[p] = ct[p].same ? l0[p] : r0[p];
-        r1[p] = ct[p].same ? l1[p] : r1[p];
+        if (EDGE) {
+            r0[p] = ct[p].same ? l0[p] : r0[p];
+            r1[p] = ct[p].same ? l1[p] : r1[p];
+        }
     }
     const float2 w00 = mul2(owy2, owx2), w01 = mul2(owy2, wx2), w10 = mul2(wy2, owx2);
     float2 v[3];
@@ -447,26 +453,42 @@ __global__ void __launch_bounds__(288) resample_stream_pairs_kernel(const uint8_
             OutT* po = out + out_index<OutT, LAYOUT>(L.out_w, L.out_h, n, 0, y_begin, active ? xi0 : tile_x0);
             const size_t row_step = LAYOUT == RB200_NCHW ? (size_t)L.out_w : (size_t)L.out_w * 3;
             const bool paired = second && L.pair_ok;
+            // The row loop is written out per kind of warp, so that the common one (every lane owns two columns, none at
+            // the image border) tests nothing but the barrier and carries no border selects. The choice is made per warp
+            // (votes over the lanes that are here), never per lane: all lanes of a warp stay in one loop.
             int j = 0;
             bool ok = true;
-            for (; j < rows_valid; j++, po += row_step) {
-                const int s = j & ns_mask;
-                if (!mbar_wait_bounded(bar_base + 8 * s, (j >> ns_lg) & 1, L.wait_cycles)) {
-                    ok = false;
-                    break;
+            auto rows_loop = [&](auto kind) {
+                constexpr int KIND = decltype(kind)::value;      // 0 idle, 1 mixed, 2 full + border lanes, 3 full
+                for (; j < rows_valid; j++, po += row_step) {
+                    const int s = j & ns_mask;
+                    if (!mbar_wait_bounded(bar_base + 8 * s, (j >> ns_lg) & 1, L.wait_cycles)) {
+                        ok = false;
+                        break;
+                    }
+                    if (KIND != 0 && (KIND != 1 || active)) {
+                        const float4 wts = *reinterpret_cast<const float4*>(&rowtab[j]);
+                        const int2 offs = *reinterpret_cast<const int2*>(&rowtab[j].off0);
+                        if (KIND != 1 || paired)
+                            blend_store<OutT, LAYOUT, NORMALIZE, true, KIND != 3>(
+                                stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w), ct, wx2, owx2,
+                                second, L.mul, L.add, L.magic, po, plane);
+                        else
+                            blend_store<OutT, LAYOUT, NORMALIZE, false, true>(
+                                stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w), ct, wx2, owx2,
+                                second, L.mul, L.add, L.magic, po, plane);
+                    }
+                    mbar_arrive(bar_base + 8 * (NS + s));
                 }
-                if (active) {
-                    const float4 wts = *reinterpret_cast<const float4*>(&rowtab[j]);
-                    const int2 offs = *reinterpret_cast<const int2*>(&rowtab[j].off0);
-                    if (paired)
-                        blend_store<OutT, LAYOUT, NORMALIZE, true>(stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
-                                                                   ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
-                    else
-                        blend_store<OutT, LAYOUT, NORMALIZE, false>(stage, offs.x, offs.y, make_float2(wts.x, wts.y), make_float2(wts.z, wts.w),
-                                                                    ct, wx2, owx2, second, L.mul, L.add, L.magic, po, plane);
-                }
-                mbar_arrive(bar_base + 8 * (NS + s));
-            }
+            };
+            const unsigned lanes = __activemask();
+            const bool none_active = !__any_sync(lanes, active);
+            const bool all_full = __all_sync(lanes, active && paired);
+            const bool border = __any_sync(lanes, active && (ct[0].same || ct[1].same));
+            if (none_active) rows_loop(std::integral_constant<int, 0>());
+            else if (!all_full) rows_loop(std::integral_constant<int, 1>());
+            else if (border) rows_loop(std::integral_constant<int, 2>());
+            else rows_loop(std::integral_constant<int, 3>());
             if (!ok) {
                 raise_status(L.status);
                 // Before the CTA's shared memory is given away, wait (bounded) for the copies that may
