@@ -327,7 +327,7 @@ struct PairSrc {
 };
 
 template <typename OutT, int LAYOUT, bool NORMALIZE>
-__global__ void __launch_bounds__(288) resample_stream_pairs_kernel(const uint8_t* __restrict__ arena,
+__global__ void __launch_bounds__(288, 4) resample_stream_pairs_kernel(const uint8_t* __restrict__ arena,
                                                               const rb200_resample_sample* __restrict__ samples,
                                                               const ResampleLaunch L) {
     extern __shared__ __align__(128) uint8_t smem[];
