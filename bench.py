@@ -47,9 +47,9 @@ H_RANGE = (300, 1080)
 W_RANGE = (300, 1080)
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one resample launch, per image, from
-#   ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:resample -s 4 -c 2 python bench.py --batch 512 --steps 2 --warmup 3 --no-cpu-baseline --no-other-configs
+#   ncu --set full --clock-control none -k regex:resample_stream_pairs -s 3 -c 1 python bench.py --batch 512 --steps 3 --warmup 3 --no-cpu-baseline --no-other-configs
 # (a 512-image launch: traffic grows in proportion to the images processed, so it is scaled by the batch size).
-NCU_TRAFFIC_BYTES_PER_IMAGE = (337206784 + 127553792) / 512.0
+NCU_TRAFFIC_BYTES_PER_IMAGE = (337212416 + 128423936) / 512.0
 
 
 def peak_hbm():
