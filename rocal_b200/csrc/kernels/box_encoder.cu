@@ -54,7 +54,8 @@ __device__ __forceinline__ void box_step(const float4 b, int j, int box, const f
                                          const bool (&valid)[K], float (&best_iou)[K], int (&best_box)[K], int a0,
                                          int nthreads, int lane, int warp, float (*part_val)[kMaxWarps],
                                          int (*part_idx)[kMaxWarps]) {
-    const float area_b = mul_rn(sub_rn(b.w, b.y), sub_rn(b.z, b.x));
+    float area_b = mul_rn(sub_rn(b.w, b.y), sub_rn(b.z, b.x));
+    asm volatile("" : "+f"(area_b));      // computed once per box: the value is opaque from here on, so it is kept, not recomputed per anchor
     float tv = -INFINITY;
     int ti = 0x7fffffff;
 #pragma unroll
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__((K == 4 ? 320 : 512), (K == 4 ? 4 : 1)) box_en
         valid[k] = la < L.per_cta && a_base + la < A;
         anc[k] = valid[k] ? L.anchors[a_base + la] : make_float4(0.f, 0.f, 0.f, 0.f);
         area_a[k] = mul_rn(sub_rn(anc[k].w, anc[k].y), sub_rn(anc[k].z, anc[k].x));
+        asm volatile("" : "+f"(area_a[k]));   // likewise: one register per anchor instead of three operations per pair
         best_iou[k] = -1.f;
         best_box[k] = 0;
         forced[la] = -1;
