@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(256) box_iou_match_kernel(const float4* __rest
                 valid[k] = la < n_local;
                 anc[k] = valid[k] ? L.anchors[a_base + la] : make_float4(0.f, 0.f, 0.f, 0.f);
                 area_a[k] = mul_rn(sub_rn(anc[k].w, anc[k].y), sub_rn(anc[k].z, anc[k].x));
+                asm volatile("" : "+f"(area_a[k]));   // opaque from here on: kept in a register, not recomputed per box
             }
             for (int j = 0; j < nb; j++) {
                 const float4 b = sbox[j];
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(256) box_iou_match_kernel(const float4* __rest
             const int la = (g * kMatchK + k) * T + tid;
             anc[k] = la < n_local ? L.anchors[a_base + la] : make_float4(0.f, 0.f, 0.f, 0.f);
             area_a[k] = mul_rn(sub_rn(anc[k].w, anc[k].y), sub_rn(anc[k].z, anc[k].x));
+            asm volatile("" : "+f"(area_a[k]));       // opaque from here on: kept in a register, not recomputed per box
             mval[k] = -1.0f;
             midx[k] = -1;
             lq[k] = false;
