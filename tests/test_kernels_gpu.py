@@ -136,6 +136,40 @@ def test_stream_kernel_wide_sources_take_the_short_ring(cuda, path):
     assert _device_status() == 0
 
 
+@pytest.mark.parametrize("dtype,layout", [(T.FP16, T.NCHW), (T.UINT8, T.NHWC)])
+def test_pair_ring_warp_kinds(cuda, dtype, layout):
+    """The pair ring picks one of four row loops per warp. One batch holds a sample for each: a crop narrower than the tile
+    (warps with no column at all and a warp whose upper lanes are idle), an odd crop width (a last column without a
+    partner), a whole-image window whose first and last columns clamp their right tap onto the left one (up-scale from a
+    3-pixel-wide ROI: the border variant in every warp), a one-pixel-wide source, and the common full case; up- and
+    down-scaling, mirrored and not. Both rings and the automatic choice give the oracle's bits."""
+    from rocal_b200 import kernels as K
+    rng = S.rng_for(12, 3)
+    arena, hs, ws, offs = S.make_images(rng, 8, (60, 400), (260, 900), content="noise")
+    n = len(hs)
+    t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+    t["src_offset"], t["src_stride"] = offs, ws * 3
+    t["roi_w"], t["roi_h"] = ws, hs
+    t["dst_w"], t["dst_h"] = 256, 96
+    t["crop_w"], t["crop_h"] = 256, 96
+    t["mirror"] = np.arange(n) % 2
+    t[1]["crop_w"] = 70                                  # warps 2, 3 idle, warp 1 half idle
+    t[2]["crop_w"], t[2]["crop_x"] = 133, 40             # odd width: the last thread owns one column
+    t[3]["roi_x"], t[3]["roi_w"] = 5, 3                  # 3 source columns -> 256: most columns sit on a border
+    t[4]["roi_x"], t[4]["roi_w"] = 17, 1                 # one source column
+    t[5]["roi_y"], t[5]["roi_h"] = 9, 2                  # two source rows
+    t[6]["dst_w"], t[6]["crop_w"] = 255, 255             # odd resized width, crop = whole
+    t[7]["dst_w"], t[7]["dst_h"], t[7]["crop_w"], t[7]["crop_h"] = 1024, 300, 256, 96
+    t[7]["crop_x"], t[7]["crop_y"] = 768, 204            # window in the far corner of a larger resized image
+    ref = O.resample(arena, t, 256, 96, dtype, layout)
+    a = _dev(arena, cuda)
+    for path in (0, 2, 3):
+        for rows in (0, 8, 32):
+            got = K.resample(a, t, 256, 96, dtype, layout, strip_rows=rows, path=path).cpu().numpy()
+            assert np.array_equal(got.view(np.uint8), ref.view(np.uint8)), (path, rows)
+    assert _device_status() == 0
+
+
 def test_resize_only_ragged_output(cuda):
     """Plain Resize: uint8 HWC out, per-sample output sizes inside a larger max-shape tensor; only
     the ROI is defined (padding not filled), up- and down-scaling, odd sizes."""
