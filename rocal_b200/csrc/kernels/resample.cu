@@ -1328,10 +1328,13 @@ static long resident_ctas(const void* kernel, int threads, size_t smem) {
 // Smaller grids are latency-bound - a CTA's life is its set-up plus one copy round trip per ring refill - and run
 // fastest with about 14 rows per CTA (measured on 64 .. 256 images of 224 rows: 14 beats 8, 16 and 32 by 3 .. 40 %);
 // grids that would not even fill half the device at 14 rows go down to 8.
-static int choose_strip_rows(long resident, long columns_of_ctas, int ext_h) {
+// A source in host memory is a different case: the launch is bound by the link, not by latency, and every strip border
+// makes two CTAs pull the rows their taps share, so the tallest strips win as soon as the grid keeps the link busy
+// (measured on 64 images: 32 rows 396 us, 14 rows 404 us, 8 rows 412 us).
+static int choose_strip_rows(long resident, long columns_of_ctas, int ext_h, bool host_source) {
     auto ctas_at = [&](int rows) { return columns_of_ctas * ((ext_h + rows - 1) / rows); };
     int target = 14;
-    if (ctas_at(32) >= 4 * resident) target = 32;
+    if (ctas_at(32) >= 4 * resident || (host_source && ctas_at(32) * 3 >= resident)) target = 32;
     else if (ctas_at(14) * 2 < resident) target = 8;
     int k = (ext_h + target / 2) / target;
     if (k < 1) k = 1;
@@ -1356,7 +1359,7 @@ static int launch_typed(const uint8_t* arena, const rb200_resample_sample* sampl
         }
         // compute threads rounded up to whole warps + one producer warp
         const int threads = ((L.twh + 31) & ~31) + 32;
-        if (L.strip_rows == 0) L.strip_rows = choose_strip_rows(resident_ctas((const void*)k, threads, smem), n * L.tiles_x, L.ext_h);
+        if (L.strip_rows == 0) L.strip_rows = choose_strip_rows(resident_ctas((const void*)k, threads, smem), n * L.tiles_x, L.ext_h, L.row_ring != 0);
         int strips = (L.ext_h + L.strip_rows - 1) / L.strip_rows;
         dim3 grid((unsigned)(L.tiles_x * strips), (unsigned)n);
         cudaError_t le = launch_overlapped(k, grid, dim3((unsigned)threads), smem, stream, arena, samples, L);
