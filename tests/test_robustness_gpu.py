@@ -5,7 +5,8 @@
   - zero-copy outputs consumed on another stream while later batches are produced (rb200_consumer_fence through the
     DLPack `stream` argument);
   - host buffers of batches that are fed far ahead of rocalRun stay alive until their batch has been returned;
-  - contexts that are built, run and released leave neither device nor host memory behind."""
+  - contexts that are built, run and released leave neither device nor host memory behind;
+  - contexts driven by concurrent threads."""
 import gc
 
 import numpy as np
@@ -218,3 +219,67 @@ def test_contexts_and_batches_leave_no_memory_behind(cuda):
             free0, rss0 = torch.cuda.mem_get_info()[0], rss()
     assert abs(free0 - torch.cuda.mem_get_info()[0]) <= 8 << 20
     assert rss() - rss0 <= 32 << 20
+
+
+def test_contexts_in_concurrent_threads(cuda):
+    """The reference's threading rule (tests/cpp_api/dataloader_multithread/dataloader_multithread.cpp:54-66: one context per
+    thread, creation under a mutex): four
+    contexts, created one after the other, each driven by a thread of its own for 25 batches at the same time - different
+    batch sizes, output types and mirror settings, pageable and pinned arenas. Every batch of every thread equals the
+    oracle's bits; no thread sees another's error text."""
+    import threading
+    import torch
+    from rocal_b200 import fn, types
+    from rocal_b200.pipeline import Pipeline
+    mul, add = S.normalize_tables()
+    jobs = []
+    for k, (n, dtype, mirror, pinned) in enumerate(((16, T.FP32, 0, True), (24, T.FP16, 1, False), (8, T.FP32, 1, True),
+                                                     (32, T.FP16, 0, True))):
+        rng = S.rng_for(42, k)
+        arena, hs, ws, offs = S.make_images(rng, n, (150, 400), (150, 400))
+        t = np.zeros(n, dtype=T.RESAMPLE_SAMPLE)
+        for i in range(n):
+            dw, dh = O.resize_dst_size(int(ws[i]), int(hs[i]), 128, 128, 2, cap_w=768, cap_h=768)
+            x1, y1, cw, ch = O.crop_fixed(dw, dh, 112, 112, 0.5, 0.5)
+            t[i]["src_offset"], t[i]["src_stride"] = offs[i], ws[i] * 3
+            t[i]["roi_w"], t[i]["roi_h"] = ws[i], hs[i]
+            t[i]["dst_w"], t[i]["dst_h"] = dw, dh
+            t[i]["crop_x"], t[i]["crop_y"], t[i]["crop_w"], t[i]["crop_h"] = x1, y1, cw, ch
+            t[i]["mirror"] = mirror
+        ref = O.resample(arena, t, 112, 112, dtype, T.NCHW, mul, add)
+        pipe = Pipeline(batch_size=n, device_id=0, seed=3 + k, prefetch_queue_depth=2)      # created serially
+        with pipe:
+            img, _ = fn.external_source(None, mode=types.EXTSOURCE_RAW_UNCOMPRESSED, max_width=400, max_height=400)
+            r = fn.resize(img, resize_shorter=128)
+            out = fn.crop_mirror_normalize(r, crop=[112, 112], mean=list(S.MEAN), std=list(S.STD), mirror=mirror,
+                                           output_layout=types.NCHW, output_dtype=types.FLOAT if dtype == T.FP32 else types.FLOAT16)
+            pipe.set_outputs(out)
+        pipe.build()
+        src = torch.from_numpy(arena).pin_memory() if pinned else arena
+        jobs.append((pipe, src, hs, ws, offs, ref))
+    failures = []
+    start = threading.Barrier(len(jobs))
+
+    def drive(k):
+        pipe, src, hs, ws, offs, ref = jobs[k]
+        try:
+            start.wait()
+            for batch in range(25):
+                pipe.feed_ragged(src, hs, ws, offs)
+                pipe.run()
+                got = torch.from_dlpack(pipe.get_output_tensors()[0]).cpu().numpy()
+                if not np.array_equal(got.view(np.uint8), ref.view(np.uint8)):
+                    failures.append("context %d, batch %d differs from the oracle" % (k, batch))
+                    return
+        except Exception as e:          # noqa: BLE001 - reported through the list below
+            failures.append("context %d: %r" % (k, e))
+
+    threads = [threading.Thread(target=drive, args=(k,)) for k in range(len(jobs))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    for pipe, *_ in jobs:
+        pipe.rocal_release()
+    assert not failures, failures
+    assert _library_status() == 0
